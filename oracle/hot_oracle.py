@@ -1,0 +1,349 @@
+"""CPU oracle for the HOT linear-layer backward path.  TEST INFRASTRUCTURE ONLY.
+
+This module restates, in numpy float32 arithmetic, the algorithm of the
+reference's fake-quant path so that the CUDA kernels can be compared with it
+bit for bit.  It is imported by the tests, by the smoke check and by the CPU
+baseline leg of the benchmark, and by nothing that ships: the product path
+never routes through this file.
+
+Parity status: PINNED.  ``tests/golden/make_golden.py`` runs the unmodified
+reference (utils/quant_matmul.py, utils/hadamard_matmul.py) on seeded inputs
+and stores its outputs under ``tests/golden/``; ``tests/test_oracle_golden.py``
+checks every function below against those files.
+
+Where the reference leaves the floating-point summation order to a BLAS matmul
+(the +-1 transforms of utils/hadamard_matmul.py:121-161) this oracle fixes the
+order to the radix-2 butterfly ``h = 1, 2, 4, ...`` with ``(x + y, x - y)`` per
+pair, the order of cuda_measure/HLQ_backward_kernel.cu:63-78.  Everything after
+the transform (scale, division, rounding) follows the reference expression by
+expression.
+"""
+from __future__ import annotations
+
+import math
+
+import numpy as np
+
+F32 = np.float32
+EPS = F32(1e-11)  # args.py:34 and the literal at utils/quant_matmul.py:22
+
+
+# ----------------------------------------------------------------------------
+# transform generators (utils/hadamard_matmul.py)
+# ----------------------------------------------------------------------------
+def pow2_factor(size: int) -> int:
+    """Largest power of two dividing ``size`` (utils/hadamard_matmul.py:9-15)."""
+    if size < 1:
+        raise ValueError("size must be positive")
+    return size & -size
+
+
+def block_order(size: int) -> int:
+    """Hadamard block order used along a dim of ``size``: the largest power of two
+    dividing it, capped at 16 (utils/hadamard_matmul.py:17-27)."""
+    p = pow2_factor(size)
+    return 16 if (p > 16 and size > 16) else p
+
+
+def hadamard(n: int) -> np.ndarray:
+    """Sylvester Hadamard matrix in natural order, entries +-1, unnormalised
+    (utils/hadamard_matmul.py:32-51).  H[i, j] = (-1)^popcount(i & j)."""
+    if n < 1 or (n & (n - 1)):
+        raise ValueError("n must be int and power of 2.")
+    i = np.arange(n)
+    bits = i[:, None] & i[None, :]
+    par = np.zeros_like(bits)
+    b = bits.copy()
+    while b.any():
+        par ^= b & 1
+        b >>= 1
+    return (1 - 2 * par).astype(np.int64)
+
+
+def make_hadamard(size: int) -> np.ndarray:
+    """utils/hadamard_matmul.py:57-59."""
+    return hadamard(block_order(size))
+
+
+def sequency(row: np.ndarray) -> int:
+    """Number of sign changes along a +-1 row (utils/hadamard_matmul.py:211-212)."""
+    return int(np.sum(row[:-1] != row[1:]))
+
+
+def sequency_order(n: int) -> np.ndarray:
+    """Natural-order row index of H_n for each sequency 0..n-1.  The sequencies of a
+    Sylvester matrix are a permutation of 0..n-1, so the stable sort the reference
+    uses (utils/hadamard_matmul.py:213) has no ties."""
+    h = hadamard(n)
+    seq = np.array([sequency(h[i]) for i in range(n)])
+    return np.argsort(seq, kind="stable")
+
+
+def wht_selection(size: int, percentile: float = 50) -> tuple[int, np.ndarray]:
+    """(n, natural-order row indices) of the low-rank basis ``make_WHT(size, pct)``
+    keeps (utils/hadamard_matmul.py:209-226): n = largest power of two dividing
+    ``size`` (uncapped); rows sorted by sequency; the first q*q of them viewed as q
+    groups of q (q*q = largest even power of two <= n); group i keeps q-(i+sf)
+    rows, from the front for even i and from the back for odd i."""
+    n = 1 if size == 1 else pow2_factor(size)
+    order = sequency_order(n)
+    # biggest_sqrt_factor: largest i <= n that is a perfect square and a power of two
+    q2 = 1
+    while q2 * 4 <= n:
+        q2 *= 4
+    q = int(math.isqrt(q2))
+    sf = int(0.1 * (-np.sqrt(2 * q ** 2 * percentile + 25) + 10 * q + 5))
+    kept: list[int] = []
+    for i in range(q):
+        if i % 2 == 0:
+            lo, hi = q * i, q * (i + 1) - (i + sf)
+        else:
+            lo, hi = q * i + (i + sf), q * (i + 1)
+        kept.extend(range(lo, max(lo, hi)))
+    return n, order[np.array(kept, dtype=np.int64)] if kept else np.zeros(0, np.int64)
+
+
+def make_WHT(size: int, percentile: float = 50) -> np.ndarray:
+    n, sel = wht_selection(size, percentile)
+    return hadamard(n)[sel]
+
+
+def lowrank_preset(n: int, r: int) -> np.ndarray:
+    """The r lowest-sequency rows of H_n as natural-order indices ("half16" is
+    n=16, r=8: the analytic model's r=8 of n=16, utils/analysis_calculator.py:174-175)."""
+    return sequency_order(n)[:r]
+
+
+def selection_from_matrix(p: np.ndarray) -> tuple[int, np.ndarray]:
+    """Recover (n, natural-order row indices) from an [r, n] +-1 matrix whose rows
+    are rows of the Sylvester matrix H_n; raises ValueError otherwise."""
+    p = np.asarray(p)
+    r, n = p.shape
+    h = hadamard(n)
+    sel = np.empty(r, np.int64)
+    for j in range(r):
+        hit = np.nonzero((h == np.rint(p[j]).astype(np.int64)[None, :]).all(axis=1))[0]
+        if hit.size != 1:
+            raise ValueError("row %d is not a row of the order-%d Hadamard matrix" % (j, n))
+        sel[j] = hit[0]
+    return n, sel
+
+
+# ----------------------------------------------------------------------------
+# fixed-order transforms
+# ----------------------------------------------------------------------------
+def fwht_last(a: np.ndarray, n: int) -> np.ndarray:
+    """Block transform of the LAST dim in blocks of n: out[..., c*n+k] =
+    sum_t a[..., c*n+t] * H_n[t, k]  (lowering_matmul_front,
+    utils/hadamard_matmul.py:121-141), evaluated as the butterfly
+    h = 1, 2, 4, ...: (x, y) -> (x + y, x - y) in float32."""
+    a = np.ascontiguousarray(a, dtype=F32)
+    shp = a.shape
+    v = a.reshape(-1, n).copy()
+    h = 1
+    while h < n:
+        w = v.reshape(-1, n // (2 * h), 2, h)
+        x = w[:, :, 0, :].copy()
+        y = w[:, :, 1, :].copy()
+        w[:, :, 0, :] = x + y
+        w[:, :, 1, :] = x - y
+        h *= 2
+    return v.reshape(shp)
+
+
+def fwht_first(a: np.ndarray, n: int) -> np.ndarray:
+    """Block transform of the FIRST dim of a 2-D array in blocks of n:
+    out[b*n+k, :] = sum_t H_n[k, t] * a[b*n+t, :]  (lowering_matmul_back with a
+    square H, utils/hadamard_matmul.py:143-161), same butterfly order."""
+    a = np.asarray(a, dtype=F32)
+    return np.ascontiguousarray(fwht_last(np.ascontiguousarray(a.T), n).T)
+
+
+def hla(a: np.ndarray, n: int, sel: np.ndarray) -> np.ndarray:
+    """Hadamard low-rank projection along the first dim: out[b*r+j, :] =
+    sum_t H_n[sel[j], t] * a[b*n+t, :]  (lowering_matmul_back with the [r, n]
+    matrix of make_WHT, utils/hadamard_matmul.py:152), evaluated as the full
+    order-n butterfly followed by the row selection."""
+    a = np.asarray(a, dtype=F32)
+    R, C = a.shape
+    full = fwht_first(a, n).reshape(R // n, n, C)
+    return np.ascontiguousarray(full[:, np.asarray(sel), :].reshape(-1, C))
+
+
+# ----------------------------------------------------------------------------
+# quantisers (utils/quant_matmul.py:19-122); codes are returned as int32
+# ----------------------------------------------------------------------------
+def _qmax(bits: int) -> F32:
+    return F32(2 ** (bits - 1) - 1)
+
+
+def _round_codes(y: np.ndarray, u: np.ndarray | None) -> np.ndarray:
+    if u is None:  # torch.round: half to even (utils/quant_matmul.py:47,115)
+        return np.rint(y).astype(np.int32)
+    a = np.abs(y)
+    f = np.floor(a)
+    frac = a - f
+    flip = (np.asarray(u, dtype=F32) < frac).astype(F32)  # torch.bernoulli(frac) == (u < frac)
+    return (np.sign(y) * (f + flip)).astype(np.int32)
+
+
+def quant_tensor(x: np.ndarray, bits: int, u: np.ndarray | None):
+    """stoch_quantizer_BWD (u given, :86-100) / int_quantizer_BWD (u None, :108-115):
+    one abs-max scale for the whole tensor.  Returns (codes int32, s float32)."""
+    x = np.asarray(x, dtype=F32)
+    mx = np.max(np.abs(x)) if x.size else F32(0)
+    s = F32(mx / _qmax(bits))
+    y = np.clip(x, -mx, mx) / F32(s + EPS)
+    return _round_codes(y, u), s
+
+
+def quant_rows(x: np.ndarray, bits: int, u: np.ndarray | None):
+    """norm_quantizer_BWD (:19-31): abs-max scale per row (dim=1).  Returns
+    (codes int32, s float32[rows]); the reference returns codes*s and scale 1."""
+    x = np.asarray(x, dtype=F32)
+    mx = np.max(np.abs(x), axis=1, keepdims=True)
+    s = (mx / _qmax(bits)).astype(F32)
+    y = np.clip(x, -mx, mx) / (s + EPS).astype(F32)
+    return _round_codes(y, u), s[:, 0]
+
+
+def quant_sawb(x: np.ndarray, bits: int):
+    """sawb_quantizer_BWD (:40-49): clip = 12.1*sqrt(mean(x^2)) - 12.2*mean(|x|),
+    nearest rounding.  Means are taken in float64 and rounded once (the reference's
+    float32 mean has an unspecified summation order)."""
+    x = np.asarray(x, dtype=F32)
+    xd = x.astype(np.float64)
+    clip = F32(F32(12.1) * F32(np.sqrt(F32(np.mean(xd * xd)))) - F32(12.2) * F32(np.mean(np.abs(xd))))
+    s = F32(clip / _qmax(bits))
+    y = np.clip(x, -clip, clip) / F32(s + EPS)
+    return np.rint(y).astype(np.int32), s
+
+
+# ----------------------------------------------------------------------------
+# counter-based uniforms (Philox4x32-10); mirrored bit for bit by the CUDA kernels
+# ----------------------------------------------------------------------------
+_M0, _M1 = np.uint64(0xD2511F53), np.uint64(0xCD9E8D57)
+_W0, _W1 = 0x9E3779B9, 0xBB67AE85
+_MASK = np.uint64(0xFFFFFFFF)
+
+
+def philox4x32_10(c0, c1, c2, c3, k0: int, k1: int):
+    c0, c1, c2, c3 = (np.asarray(c, dtype=np.uint64) for c in (c0, c1, c2, c3))
+    for _ in range(10):
+        p0 = _M0 * c0
+        p1 = _M1 * c2
+        hi0, lo0 = p0 >> np.uint64(32), p0 & _MASK
+        hi1, lo1 = p1 >> np.uint64(32), p1 & _MASK
+        c0, c1, c2, c3 = (hi1 ^ c1 ^ np.uint64(k0)) & _MASK, lo1, (hi0 ^ c3 ^ np.uint64(k1)) & _MASK, lo0
+        k0 = (k0 + _W0) & 0xFFFFFFFF
+        k1 = (k1 + _W1) & 0xFFFFFFFF
+    return c0, c1, c2, c3
+
+
+def philox_uniform16(seed: int, offset: int, shape) -> np.ndarray:
+    """float32 uniforms k/65536, k a 16-bit integer, for the elements 0..N-1 of a
+    tensor in row-major order.  Elements 8g..8g+7 share the Philox block with
+    counter (g_lo, g_hi, offset_lo, offset_hi) and key (seed_lo, seed_hi); element
+    8g+j takes the low (j even) or high (j odd) half of output word j // 2."""
+    n = int(np.prod(shape))
+    g = np.arange((n + 7) // 8, dtype=np.uint64)
+    w = philox4x32_10(g & _MASK, g >> np.uint64(32), np.uint64(offset & 0xFFFFFFFF),
+                      np.uint64((offset >> 32) & 0xFFFFFFFF), seed & 0xFFFFFFFF, (seed >> 32) & 0xFFFFFFFF)
+    words = np.stack(w, axis=1).astype(np.uint64)                       # [G, 4]
+    halves = np.stack([words & np.uint64(0xFFFF), (words >> np.uint64(16)) & np.uint64(0xFFFF)], axis=2)
+    r16 = halves.reshape(-1)[:n].astype(F32)
+    return (r16 / F32(65536.0)).reshape(shape)
+
+
+# ----------------------------------------------------------------------------
+# int4 packing (cuda_measure/HLQ_backward_kernel.cu:140: low nibble = even element)
+# ----------------------------------------------------------------------------
+def pack_int4(codes: np.ndarray) -> np.ndarray:
+    c = np.asarray(codes).astype(np.int32)
+    lo = c[..., 0::2] & 0xF
+    hi = c[..., 1::2] & 0xF
+    return (lo | (hi << 4)).astype(np.uint8)
+
+
+def unpack_int4(packed: np.ndarray) -> np.ndarray:
+    p = np.asarray(packed).astype(np.int32)
+    lo = ((p & 0xF) ^ 8) - 8
+    hi = (((p >> 4) & 0xF) ^ 8) - 8
+    out = np.empty(p.shape[:-1] + (p.shape[-1] * 2,), np.int32)
+    out[..., 0::2] = lo
+    out[..., 1::2] = hi
+    return out
+
+
+# ----------------------------------------------------------------------------
+# FLinearQ forward context + backward, scheme gih_gwlr (utils/quant_matmul.py:177-348)
+# ----------------------------------------------------------------------------
+def abc_compress(x: np.ndarray, n_l: int, sel: np.ndarray, bits: int, u, mode: str = "stoch"):
+    """setup_context (:177-212): HLA of x along tokens then quantisation to int8.
+    mode: 'stoch' (u required), 'int', 'sawb'."""
+    x_lr = hla(x, n_l, sel)
+    if mode == "sawb":
+        return quant_sawb(x_lr, bits)
+    return quant_tensor(x_lr, bits, u if mode == "stoch" else None)
+
+
+def linear_backward(go, w, x_q, s_x, *, n_o: int, n_l: int, sel, bits_gx: int = 4, bits_w: int = 4,
+                    bits_gw: int = 8, u_go=None, u_w=None, u_gw=None, gx_per_token: bool = False,
+                    gw_per_channel: bool = False, w_mode: str = "stoch"):
+    """FLinearQ.backward (:214-348) for 2-D tensors.  ``u_*`` None selects nearest
+    rounding for that operand.  Returns a dict with every intermediate the CUDA
+    path can be compared on."""
+    go = np.asarray(go, dtype=F32)
+    w = np.asarray(w, dtype=F32)
+    out = {}
+    # g_x: Hadamard along O, INT4 x INT4 (:237-290)
+    go_h = fwht_last(go, n_o)
+    if gx_per_token:
+        q_go, s_go = quant_rows(go_h, bits_gx, u_go)
+    else:
+        q_go, s_go = quant_tensor(go_h, bits_gx, u_go)
+    w_h = fwht_first(w, n_o)
+    if w_mode == "sawb":
+        q_w, s_w = quant_sawb(w_h, bits_w)
+    else:
+        q_w, s_w = quant_tensor(w_h, bits_w, u_w if w_mode == "stoch" else None)
+    acc_x = q_go.astype(np.int64) @ q_w.astype(np.int64)
+    if gx_per_token:
+        gx = (acc_x.astype(F32) * s_go[:, None]) * F32(s_w)
+    else:
+        gx = (acc_x.astype(F32) * F32(s_go)) * F32(s_w)
+    gx = gx / F32(n_o)                                               # :342
+    # g_w: low-rank along L, INT8 x INT8 (:300-324)
+    go_lr_t = np.ascontiguousarray(hla(go, n_l, sel).T)              # [O, L']
+    if gw_per_channel:
+        q_gw, s_gw = quant_rows(go_lr_t, bits_gw, u_gw)
+    else:
+        q_gw, s_gw = quant_tensor(go_lr_t, bits_gw, u_gw)
+    acc_w = q_gw.astype(np.int64) @ np.asarray(x_q).astype(np.int64)
+    if gw_per_channel:
+        gw = (acc_w.astype(F32) * s_gw[:, None]) * F32(s_x)
+    else:
+        gw = (acc_w.astype(F32) * F32(s_gw)) * F32(s_x)
+    gw = gw / F32(n_l)                                               # :344
+    out.update(q_go=q_go, s_go=s_go, q_w=q_w, s_w=s_w, acc_x=acc_x, grad_input=gx.astype(F32),
+               q_gw=q_gw, s_gw=s_gw, acc_w=acc_w, grad_w=gw.astype(F32))
+    return out
+
+
+# ----------------------------------------------------------------------------
+# layer-wise quantiser selection (ViT_main.py:183-211)
+# ----------------------------------------------------------------------------
+def lqs_select(grad_out: np.ndarray, u_stoch: np.ndarray, u_norm: np.ndarray, bits: int = 4):
+    """Per-layer choice between per-tensor ('stoch_quantizer') and per-token
+    ('norm_quantizer') quantisation of grad_out: the per-token quantiser is taken for
+    g_x only when it cuts the per-tensor L2 error by more than half; g_w always keeps
+    'stoch_quantizer'.  Returns (gx_name, gw_name, err_stoch, err_norm)."""
+    g = np.asarray(grad_out, dtype=F32)
+    q, s = quant_tensor(g, bits, u_stoch)
+    e_st = float(np.sqrt(np.sum((g.astype(np.float64) - (q.astype(F32) * s).astype(np.float64)) ** 2)))
+    qn, sn = quant_rows(g, bits, u_norm)
+    e_nq = float(np.sqrt(np.sum((g.astype(np.float64) - (qn.astype(F32) * sn[:, None]).astype(np.float64)) ** 2)))
+    gx = "stoch_quantizer"
+    if e_nq < e_st and (e_st - e_nq) > e_st * 0.5:
+        gx = "norm_quantizer"
+    return gx, "stoch_quantizer", e_st, e_nq

@@ -1,0 +1,175 @@
+"""Generate tests/golden/*.npz by running the UNMODIFIED reference implementation.
+
+Usage (in a container where the reference checkout is mounted):
+
+    python tests/golden/make_golden.py /path/to/reference
+
+The reference's ``args.py`` imports ``utils/plot.py`` which needs matplotlib; three
+empty stand-in modules are registered before the import so that ``args``,
+``utils.hadamard_matmul`` and ``utils.quant_matmul`` import and run as they are.
+``torch.bernoulli`` is replaced by ``u < p`` for a supplied uniform tensor ``u`` (on
+CPU the two are the same draw), which is what makes the stochastic quantisers
+reproducible outside torch.  Nothing here is used at test time: the tests read only
+the ``.npz`` files this script wrote.
+"""
+from __future__ import annotations
+
+import os
+import sys
+import types
+
+import numpy as np
+import torch
+
+
+def _import_reference(ref_root: str):
+    for name in ("matplotlib", "matplotlib.pyplot", "matplotlib.ticker"):
+        m = types.ModuleType(name)
+        m.ScalarFormatter = m.LinearLocator = m.MaxNLocator = object
+        sys.modules.setdefault(name, m)
+    sys.modules["matplotlib"].pyplot = sys.modules["matplotlib.pyplot"]
+    sys.modules["matplotlib"].ticker = sys.modules["matplotlib.ticker"]
+    sys.path.insert(0, ref_root)
+    import args as ref_args  # noqa: E402
+    import utils.hadamard_matmul as hm  # noqa: E402
+    import utils.quant_matmul as qm  # noqa: E402
+    return ref_args, hm, qm
+
+
+class NoiseQueue:
+    """Stand-in for torch.bernoulli that consumes supplied uniforms in call order."""
+
+    def __init__(self):
+        self.queue: list[torch.Tensor] = []
+        self._orig = torch.bernoulli
+
+    def __enter__(self):
+        torch.bernoulli = self._draw
+        return self
+
+    def __exit__(self, *exc):
+        torch.bernoulli = self._orig
+
+    def _draw(self, p):
+        u = self.queue.pop(0)
+        assert u.shape == p.shape, (u.shape, p.shape)
+        return (u < p).to(p.dtype)
+
+
+def main(ref_root: str, out_dir: str):
+    ref_args, hm, qm = _import_reference(ref_root)
+    rng = np.random.default_rng(20250321)
+    T = torch.from_numpy
+
+    # ---- transforms ---------------------------------------------------------
+    tr = {}
+    for n in (1, 2, 4, 8, 16, 32, 64):
+        tr["hadamard_%d" % n] = hm.hadamard(n).astype(np.int8)
+    sizes = (768, 2304, 3072, 4096, 11008, 1000, 100, 197, 196, 48, 24)
+    tr["make_hadamard_sizes"] = np.array(sizes)
+    tr["make_hadamard_orders"] = np.array([hm.make_hadamard(s).shape[0] for s in sizes])
+    tr["pow2_max16"] = np.array([hm.biggest_power2_factor_max16(s) for s in sizes])
+    tr["pow2"] = np.array([hm.biggest_power2_factor(s) for s in sizes])
+    wht_cases = [(6304, 50), (12608, 50), (196, 50), (197, 50), (160, 50), (48, 50), (48, 25), (48, 75),
+                 (48, 100), (640, 50), (256, 50), (256, 25), (2, 50), (24, 50)]
+    tr["wht_cases"] = np.array(wht_cases)
+    for size, pct in wht_cases:
+        tr["wht_%d_%d" % (size, pct)] = hm.make_WHT(size, pct).astype(np.int8)
+    a = rng.standard_normal((64, 96)).astype(np.float32)
+    h16 = torch.tensor(hm.hadamard(16), dtype=torch.float32)
+    tr["lower_in"] = a
+    tr["lower_front16"] = hm.lowering_matmul_front(T(a), h16).numpy()
+    tr["lower_back16"] = hm.lowering_matmul_back(h16, T(a)).numpy()
+    p = torch.tensor(hm.make_WHT(64, 50), dtype=torch.float32)       # [r, 64]
+    tr["lower_back_wht64"] = hm.lowering_matmul_back(p, T(a)).numpy()
+    np.savez_compressed(os.path.join(out_dir, "transforms.npz"), **tr)
+
+    # ---- quantisers ---------------------------------------------------------
+    q = {}
+    x = (rng.standard_normal((48, 64)) * 1e-3).astype(np.float32)
+    x[5] *= 40.0                                                      # an outlier token
+    u = rng.random((48, 64), dtype=np.float32)
+    q["x"], q["u"] = x, u
+    for bits in (4, 8):
+        with NoiseQueue() as nq:
+            nq.queue.append(T(u))
+            c, s = qm.stoch_quantizer(T(x), bits, False)
+        q["stoch%d_codes" % bits], q["stoch%d_scale" % bits] = c.numpy(), s.numpy()
+        c, s = qm.int_quantizer(T(x), bits, False)
+        q["int%d_codes" % bits], q["int%d_scale" % bits] = c.numpy(), s.numpy()
+        with NoiseQueue() as nq:
+            nq.queue.append(T(u))
+            d, one = qm.norm_quantizer(T(x), bits, False)
+        q["norm%d_deq" % bits] = d.numpy()
+        assert one == 1.0
+        c, s = qm.sawb_quantizer(T(x), bits, False)
+        q["sawb%d_codes" % bits], q["sawb%d_scale" % bits] = c.numpy(), s.numpy()
+    np.savez_compressed(os.path.join(out_dir, "quantizers.npz"), **q)
+
+    # ---- FLinearQ forward context + backward, scheme gih_gwlr ------------------
+    for tag, (L, O, I, low_rank) in {"lr_ref": (160, 96, 48, "ref"), "lr_half16": (160, 96, 48, "half16")}.items():
+        f = {}
+        ref_args.transform_scheme = "gih_gwlr"
+        ref_args.TransformGogi = ref_args.TransformWgt = ref_args.TransformGogw = ref_args.TransformInput = True
+        ref_args.GogiQuantBit, ref_args.weightQuantBit, ref_args.GogwQuantBit, ref_args.actQuantBit = 4, 4, 8, 8
+        ref_args.quantBWDGogi = ref_args.quantBWDWgt = ref_args.quantBWDGogw = ref_args.quantBWDAct = "stoch"
+        ref_args.quantAuto = False
+        xx = rng.standard_normal((L, I)).astype(np.float32)
+        xx[:, 3] *= 20.0
+        ww = ((rng.random((O, I)) * 2 - 1) / np.sqrt(I)).astype(np.float32)
+        go = (rng.standard_normal((L, O)) * 1e-3).astype(np.float32)
+        h_out = torch.tensor(hm.make_hadamard(O), dtype=torch.float32)
+        if low_rank == "ref":
+            pm = hm.make_WHT(L, 50)
+        else:
+            h = hm.hadamard(16)
+            seq = [int(np.sum(r[:-1] != r[1:])) for r in h]
+            pm = h[np.argsort(seq, kind="stable")[:8]]
+        h_bs = torch.tensor(pm, dtype=torch.float32)
+        r, n = pm.shape
+        Lp = L * r // n
+        u_x = rng.random((Lp, I), dtype=np.float32)
+        u_go = rng.random((L, O), dtype=np.float32)
+        u_w = rng.random((O, I), dtype=np.float32)
+        u_gw = rng.random((O, Lp), dtype=np.float32)
+        xt = T(xx).requires_grad_(True)
+        wt = T(ww).requires_grad_(True)
+        with NoiseQueue() as nq:
+            nq.queue += [T(u_x), T(u_go), T(u_w), T(u_gw)]
+            y = qm.FLinearQ.apply(xt, wt, h_out, h_bs, "layer")
+            saved = y.grad_fn.saved_tensors
+            y.backward(T(go))
+            assert not nq.queue
+        f.update(x=xx, w=ww, go=go, p=pm.astype(np.int8), u_x=u_x, u_go=u_go, u_w=u_w, u_gw=u_gw,
+                 y=y.detach().numpy(), x_q=saved[0].numpy(), scale_x=saved[4].numpy(),
+                 grad_input=xt.grad.numpy(), grad_w=wt.grad.numpy())
+        np.savez_compressed(os.path.join(out_dir, "flinearq_%s.npz" % tag), **f)
+
+    # ---- layer-wise quantiser selection rule (ViT_main.py:183-211, restated around
+    #      the reference's own quantisers because ViT_main needs timm/peft) ----------
+    l = {}
+    for tag, g in {"flat": (rng.standard_normal((64, 48)) * 1e-3).astype(np.float32),
+                   "outlier": (rng.standard_normal((64, 48)) * 1e-3).astype(np.float32)}.items():
+        if tag == "outlier":
+            g[7] *= 30.0
+        u1 = rng.random(g.shape, dtype=np.float32)
+        u2 = rng.random(g.shape, dtype=np.float32)
+        errs = []
+        with NoiseQueue() as nq:
+            nq.queue += [T(u1), T(u2)]
+            qg, sg = qm.stoch_quantizer(T(g), 4, False)
+            errs.append(float(torch.dist(T(g), qg * sg)))
+            qg, sg = qm.norm_quantizer(T(g), 4, False)
+            errs.append(float(torch.dist(T(g), qg * sg)))
+        choice = "stoch_quantizer"
+        if errs[1] < errs[0] and (errs[0] - errs[1]) > errs[0] * 0.5:
+            choice = "norm_quantizer"
+        l[tag + "_g"], l[tag + "_u1"], l[tag + "_u2"] = g, u1, u2
+        l[tag + "_errs"] = np.array(errs)
+        l[tag + "_gx"] = np.array(choice)
+    np.savez_compressed(os.path.join(out_dir, "lqs.npz"), **l)
+    print("golden vectors written to", out_dir)
+
+
+if __name__ == "__main__":
+    main(sys.argv[1], os.path.dirname(os.path.abspath(__file__)))

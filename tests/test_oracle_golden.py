@@ -1,0 +1,111 @@
+"""The CPU oracle against the golden vectors the unmodified reference produced
+(tests/golden/make_golden.py).  Integer artefacts must match exactly; the +-1
+transforms, whose summation order the reference leaves to BLAS, to 1e-6 relative."""
+import numpy as np
+import pytest
+
+from oracle import hot_oracle as oc
+
+
+def test_hadamard_and_orders(golden):
+    g = golden("transforms")
+    for n in (1, 2, 4, 8, 16, 32, 64):
+        assert np.array_equal(oc.hadamard(n), g["hadamard_%d" % n])
+    sizes = g["make_hadamard_sizes"]
+    assert [oc.block_order(int(s)) for s in sizes] == list(g["pow2_max16"])
+    assert [oc.make_hadamard(int(s)).shape[0] for s in sizes] == list(g["make_hadamard_orders"])
+    assert [oc.pow2_factor(int(s)) for s in sizes] == list(g["pow2"])
+    with pytest.raises(ValueError):
+        oc.hadamard(12)
+
+
+def test_make_wht(golden):
+    g = golden("transforms")
+    for size, pct in g["wht_cases"]:
+        ref = g["wht_%d_%d" % (size, pct)]
+        got = oc.make_WHT(int(size), int(pct))
+        assert got.shape == ref.shape, (size, pct, got.shape, ref.shape)
+        assert np.array_equal(got, ref), (size, pct)
+        n, sel = oc.selection_from_matrix(ref)
+        assert np.array_equal(oc.hadamard(n)[sel], ref)
+    n, sel = oc.wht_selection(6304, 50)
+    assert n == 32 and len(sel) == 10
+    assert sorted(oc.sequency(oc.hadamard(32)[i]) for i in sel) == [0, 1, 2, 3, 5, 6, 7, 8, 9, 15]
+
+
+def test_butterfly_transforms_match_reference_matmul(golden):
+    g = golden("transforms")
+    a = g["lower_in"]
+    np.testing.assert_allclose(oc.fwht_last(a, 16), g["lower_front16"], rtol=0, atol=1e-5)
+    np.testing.assert_allclose(oc.fwht_first(a, 16), g["lower_back16"], rtol=0, atol=1e-5)
+    n, sel = oc.wht_selection(64, 50)
+    np.testing.assert_allclose(oc.hla(a, n, sel), g["lower_back_wht64"], rtol=0, atol=2e-5)
+    # the butterfly is exact on integers, where order cannot matter
+    ai = np.rint(a * 8).astype(np.float32)
+    assert np.array_equal(oc.fwht_last(ai, 16), (ai.reshape(-1, 16) @ oc.hadamard(16).astype(np.float32)).reshape(ai.shape))
+
+
+@pytest.mark.parametrize("bits", [4, 8])
+def test_quantisers_bit_exact(golden, bits):
+    g = golden("quantizers")
+    x, u = g["x"], g["u"]
+    c, s = oc.quant_tensor(x, bits, u)
+    assert np.array_equal(c, g["stoch%d_codes" % bits].astype(np.int32))
+    assert s.tobytes() == g["stoch%d_scale" % bits].astype(np.float32).tobytes()
+    c, s = oc.quant_tensor(x, bits, None)
+    assert np.array_equal(c, g["int%d_codes" % bits].astype(np.int32))
+    assert s.tobytes() == g["int%d_scale" % bits].astype(np.float32).tobytes()
+    c, s = oc.quant_rows(x, bits, u)
+    assert np.array_equal(c.astype(np.float32) * s[:, None], g["norm%d_deq" % bits])
+    c, s = oc.quant_sawb(x, bits)
+    assert np.mean(c != g["sawb%d_codes" % bits]) < 1e-3          # float32 mean order differs
+    np.testing.assert_allclose(s, g["sawb%d_scale" % bits], rtol=1e-5)
+    qmax = 2 ** (bits - 1) - 1
+    assert np.abs(oc.quant_tensor(x, bits, u)[0]).max() <= qmax
+
+
+@pytest.mark.parametrize("tag", ["lr_ref", "lr_half16"])
+def test_flinearq_backward(golden, tag):
+    g = golden("flinearq_" + tag)
+    n_l, sel = oc.selection_from_matrix(g["p"])
+    x_q, s_x = oc.abc_compress(g["x"], n_l, sel, 8, g["u_x"])
+    # the saved activation is the HLA of x; its transform order differs from BLAS only in the
+    # last ulp, so a handful of codes may flip; none do on this fixture
+    assert np.array_equal(x_q, g["x_q"].astype(np.int32))
+    np.testing.assert_allclose(s_x, g["scale_x"], rtol=1e-6)
+    O = g["w"].shape[0]
+    out = oc.linear_backward(g["go"], g["w"], x_q, s_x, n_o=oc.block_order(O), n_l=n_l, sel=sel,
+                             u_go=g["u_go"], u_w=g["u_w"], u_gw=g["u_gw"])
+    for name in ("grad_input", "grad_w"):
+        ref = g[name]
+        rel = np.linalg.norm(out[name] - ref) / np.linalg.norm(ref)
+        assert rel < 1e-3, (name, rel)
+    assert np.abs(out["q_go"]).max() <= 7 and np.abs(out["q_gw"]).max() <= 127
+
+
+def test_int4_pack_roundtrip():
+    rng = np.random.default_rng(0)
+    c = rng.integers(-7, 8, size=(5, 32))
+    p = oc.pack_int4(c)
+    assert p.shape == (5, 16) and p.dtype == np.uint8
+    assert (p[0, 0] & 0xF) == (c[0, 0] & 0xF) and (p[0, 0] >> 4) == (c[0, 1] & 0xF)
+    assert np.array_equal(oc.unpack_int4(p), c)
+
+
+def test_lqs_rule(golden):
+    g = golden("lqs")
+    for tag in ("flat", "outlier"):
+        gx, gw, e_st, e_nq = oc.lqs_select(g[tag + "_g"], g[tag + "_u1"], g[tag + "_u2"])
+        np.testing.assert_allclose([e_st, e_nq], g[tag + "_errs"], rtol=1e-4)
+        assert gx == str(g[tag + "_gx"]) and gw == "stoch_quantizer"
+    assert str(g["flat_gx"]) == "stoch_quantizer" and str(g["outlier_gx"]) == "norm_quantizer"
+
+
+def test_philox_known_answer():
+    # Random123 known-answer vectors for philox4x32-10
+    out = oc.philox4x32_10(0, 0, 0, 0, 0, 0)
+    assert [int(v) for v in out] == [0x6627E8D5, 0xE169C58D, 0xBC57AC4C, 0x9B00DBD8]
+    out = oc.philox4x32_10(0xFFFFFFFF, 0xFFFFFFFF, 0xFFFFFFFF, 0xFFFFFFFF, 0xFFFFFFFF, 0xFFFFFFFF)
+    assert [int(v) for v in out] == [0x408F276D, 0x41C83B0E, 0xA20BC7C6, 0x6D5451FD]
+    u = oc.philox_uniform16(1, 2, (3, 7))
+    assert u.shape == (3, 7) and u.dtype == np.float32 and (u >= 0).all() and (u < 1).all()
