@@ -1,0 +1,350 @@
+// Fused block Walsh-Hadamard transform along the FIRST dim (with row selection: the Hadamard
+// low-rank projection) + INT4/INT8 quantisation, written transposed.
+//
+// A CTA owns a tile of NB token blocks (NB * n rows) by CC columns.  Phase 1: each warp takes
+// whole token blocks; a thread loads its columns of the n rows of a block with warp-coalesced
+// 4-byte loads, runs the order-n butterfly in registers (stages h = 1, 2, 4, ... on pairs
+// (t, t + h) -> (x + y, x - y), the order the CPU oracle fixes) and drops the kept rows into a
+// float tile in shared memory, transposed: tile[column][block * r + j].  Phase 2: threads walk
+// the tile rows, 8 consecutive codes each, quantise (one Philox block per 8 codes) and store
+// 4 or 8 contiguous bytes, so that rows of the transposed output are written in full sectors.
+//
+// Per-tensor and per-output-row scales need the abs-max of the transformed tensor first: a
+// first launch runs phase 1 only and reduces into the scratch words.
+#include "common.cuh"
+
+namespace hot {
+namespace {
+
+constexpr int kThreads = 256;
+constexpr int kWarps = kThreads / 32;
+
+struct ColParams {
+  int64_t rows, ldx, ld_codes;
+  int cols, r, nb;            // nb: token blocks per tile
+  int pitch;                  // floats per tile row
+  int64_t out_len;            // rows * r / n
+  int scale_row, store4, noise_transposed;
+  signed char pos[64];        // pos[k] = output slot of natural row k, or -1
+};
+
+template <typename T>
+struct ColTraits;
+template <>
+struct ColTraits<float> {
+  static constexpr int kCpl = 1;  // columns per 4-byte load
+  static __device__ __forceinline__ void load(const float* p, bool ok, float (&o)[1]) { o[0] = ok ? __ldg(p) : 0.0f; }
+};
+template <>
+struct ColTraits<__nv_bfloat16> {
+  static constexpr int kCpl = 2;
+  static __device__ __forceinline__ void load(const __nv_bfloat16* p, bool ok, float (&o)[2]) {
+    const uint32_t w = ok ? __ldg(reinterpret_cast<const uint32_t*>(p)) : 0u;
+    o[0] = __uint_as_float(w << 16);
+    o[1] = __uint_as_float(w & 0xFFFF0000u);
+  }
+};
+
+// column groups per thread, bounding the register tile at 64 floats (128 for bf16 at n = 64)
+template <typename T, int N>
+__host__ __device__ constexpr int vec_for() {
+  return (64 / (N * ColTraits<T>::kCpl)) >= 4 ? 4 : ((64 / (N * ColTraits<T>::kCpl)) >= 2 ? 2 : 1);
+}
+
+template <int N>
+__device__ __forceinline__ void butterfly_regs(float (&v)[N]) {
+#pragma unroll
+  for (int h = 1; h < N; h <<= 1) {
+#pragma unroll
+    for (int i = 0; i < N; ++i) {
+      if ((i & h) == 0) {
+        const float a = v[i], b = v[i + h];
+        v[i] = a + b;
+        v[i + h] = a - b;
+      }
+    }
+  }
+}
+
+// Loads the block `blk` (global block index) for this thread's columns and transforms it.
+template <typename T, int N, int VEC>
+__device__ __forceinline__ void load_transform(const T* __restrict__ x, const ColParams& p, int64_t blk, int c0, int lane,
+                                               float (&v)[VEC * ColTraits<T>::kCpl][N]) {
+  constexpr int CPL = ColTraits<T>::kCpl;
+  const T* base = x + blk * N * p.ldx;
+#pragma unroll
+  for (int t = 0; t < N; ++t) {
+#pragma unroll
+    for (int vv = 0; vv < VEC; ++vv) {
+      const int c = c0 + (lane + 32 * vv) * CPL;
+      float o[CPL];
+      ColTraits<T>::load(base + (int64_t)t * p.ldx + c, c < p.cols, o);
+#pragma unroll
+      for (int q = 0; q < CPL; ++q) v[vv * CPL + q][t] = o[q];
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < VEC * CPL; ++i) butterfly_regs<N>(v[i]);
+}
+
+// ---- pass 1: abs-max of the kept, transformed rows --------------------------------------
+template <typename T, int N>
+__global__ void __launch_bounds__(kThreads) col_ht_absmax_kernel(const T* __restrict__ x, ColParams p,
+                                                                 uint32_t* __restrict__ absmax) {
+  constexpr int VEC = vec_for<T, N>();
+  constexpr int CPL = ColTraits<T>::kCpl;
+  constexpr int CC = 32 * VEC * CPL;
+  __shared__ uint32_t s_max[CC];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int c0 = blockIdx.x * CC;
+  const int64_t nblk = p.rows / N;
+  const int64_t blk0 = (int64_t)blockIdx.y * p.nb;
+  for (int i = threadIdx.x; i < CC; i += kThreads) s_max[i] = 0u;
+  __syncthreads();
+  float cm[VEC * CPL];
+#pragma unroll
+  for (int i = 0; i < VEC * CPL; ++i) cm[i] = 0.0f;
+  for (int b = warp; b < p.nb; b += kWarps) {
+    if (blk0 + b >= nblk) break;
+    float v[VEC * CPL][N];
+    load_transform<T, N, VEC>(x, p, blk0 + b, c0, lane, v);
+#pragma unroll
+    for (int k = 0; k < N; ++k) {
+      if (p.pos[k] >= 0) {
+#pragma unroll
+        for (int i = 0; i < VEC * CPL; ++i) cm[i] = fmaxf(cm[i], fabsf(v[i][k]));
+      }
+    }
+  }
+  if (p.scale_row) {
+#pragma unroll
+    for (int vv = 0; vv < VEC; ++vv)
+#pragma unroll
+      for (int q = 0; q < CPL; ++q) atomicMax(&s_max[(lane + 32 * vv) * CPL + q], __float_as_uint(cm[vv * CPL + q]));
+    __syncthreads();
+    for (int i = threadIdx.x; i < CC; i += kThreads)
+      if (c0 + i < p.cols) atomicMax(absmax + c0 + i, s_max[i]);
+  } else {
+    float m = 0.0f;
+#pragma unroll
+    for (int i = 0; i < VEC * CPL; ++i) m = fmaxf(m, cm[i]);
+    m = warp_max(m);
+    if (lane == 0) atomicMax(&s_max[0], __float_as_uint(m));
+    __syncthreads();
+    if (threadIdx.x == 0) atomicMax(absmax, s_max[0]);
+  }
+}
+
+// uniforms for 8 consecutive codes starting at stored-layout element e0
+__device__ __forceinline__ void philox_span8(const QuantDev& q, uint64_t e0, float (&u)[8]) {
+  if ((e0 & 7u) == 0) {
+    philox_uniform8(q, e0 >> 3, u);
+    return;
+  }
+  float a[8], b[8];
+  philox_uniform8(q, e0 >> 3, a);
+  philox_uniform8(q, (e0 >> 3) + 1, b);
+  const int off = (int)(e0 & 7u);
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    float pick = 0.0f;
+#pragma unroll
+    for (int s = 0; s < 16; ++s) {
+      const float cand = s < 8 ? a[s] : b[s - 8];
+      pick = (s == i + off) ? cand : pick;
+    }
+    u[i] = pick;
+  }
+}
+
+// ---- pass 2: transform, stage transposed in shared memory, quantise, store ----------------
+template <typename T, int N, int ROUND>
+__global__ void __launch_bounds__(kThreads) col_ht_quant_kernel(const T* __restrict__ x, ColParams p, QuantDev q,
+                                                                uint8_t* __restrict__ codes, float* __restrict__ scales,
+                                                                const uint32_t* __restrict__ absmax) {
+  constexpr int VEC = vec_for<T, N>();
+  constexpr int CPL = ColTraits<T>::kCpl;
+  constexpr int CC = 32 * VEC * CPL;
+  extern __shared__ __align__(16) float tile[];  // [CC][pitch]
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int c0 = blockIdx.x * CC;
+  const int64_t nblk = p.rows / N;
+  const int64_t blk0 = (int64_t)blockIdx.y * p.nb;
+  const int r = p.r;
+
+  for (int b = warp; b < p.nb; b += kWarps) {
+    if (blk0 + b < nblk) {
+      float v[VEC * CPL][N];
+      load_transform<T, N, VEC>(x, p, blk0 + b, c0, lane, v);
+#pragma unroll
+      for (int k = 0; k < N; ++k) {
+        const int j = p.pos[k];
+        if (j >= 0) {
+#pragma unroll
+          for (int vv = 0; vv < VEC; ++vv)
+#pragma unroll
+            for (int qq = 0; qq < CPL; ++qq)
+              tile[((lane + 32 * vv) * CPL + qq) * p.pitch + b * r + j] = v[vv * CPL + qq][k];
+        }
+      }
+    } else {
+      for (int j = 0; j < r; ++j)
+#pragma unroll
+        for (int vv = 0; vv < VEC; ++vv)
+#pragma unroll
+          for (int qq = 0; qq < CPL; ++qq) tile[((lane + 32 * vv) * CPL + qq) * p.pitch + b * r + j] = 0.0f;
+    }
+  }
+  __syncthreads();
+
+  float s_t = 0.0f, d_t = 0.0f;
+  if (!p.scale_row) {
+    scale_from_absmax(__uint_as_float(absmax[0]), q.qmax, s_t, d_t);
+    if (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) scales[0] = s_t;
+  }
+  const int cpr = (p.nb * r) >> 3;  // 8-code chunks per tile row
+  const int64_t pos0 = blk0 * r;    // first stored position of this tile within an output row
+  for (int item = threadIdx.x; item < CC * cpr; item += kThreads) {
+    const int cl = item / cpr, ch = item - cl * cpr;
+    const int c = c0 + cl;
+    const int64_t l0 = pos0 + (int64_t)ch * 8;
+    if (c >= p.cols || l0 >= p.out_len) continue;
+    float v[8];
+    const float4 a = *reinterpret_cast<const float4*>(tile + cl * p.pitch + ch * 8);
+    const float4 b = *reinterpret_cast<const float4*>(tile + cl * p.pitch + ch * 8 + 4);
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
+    v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+    float s = s_t, d = d_t;
+    if (p.scale_row) {
+      scale_from_absmax(__uint_as_float(absmax[c]), q.qmax, s, d);
+      if (blockIdx.y == 0 && ch == 0) scales[c] = s;
+    }
+    float u[8];
+    if (ROUND == HOT_ROUND_STOCH_PHILOX) {
+      philox_span8(q, (uint64_t)c * (uint64_t)p.out_len + (uint64_t)l0, u);
+    } else if (ROUND == HOT_ROUND_STOCH_NOISE) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int64_t l = l0 + i;
+        float un = 1.0f;
+        if (l < p.out_len)
+          un = p.noise_transposed ? q.noise[(int64_t)c * p.out_len + l] : q.noise[l * (int64_t)p.cols + c];
+        u[i] = un;
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) u[i] = 0.0f;
+    }
+    int code[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      code[i] = quantise_one<ROUND>(v[i], d, u[i]);
+      code[i] = max(-(int)q.qmax, min((int)q.qmax, code[i]));
+    }
+    if (p.store4) {
+      uint32_t w = 0;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) w |= (uint32_t)(code[i] & 0xF) << (4 * i);
+      *reinterpret_cast<uint32_t*>(codes + (int64_t)c * p.ld_codes + (l0 >> 1)) = w;
+    } else {
+      uint32_t w0 = 0, w1 = 0;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        w0 |= (uint32_t)(code[i] & 0xFF) << (8 * i);
+        w1 |= (uint32_t)(code[i + 4] & 0xFF) << (8 * i);
+      }
+      *reinterpret_cast<uint2*>(codes + (int64_t)c * p.ld_codes + l0) = make_uint2(w0, w1);
+    }
+  }
+}
+
+template <typename T, int N>
+int launch_n(const T* x, const ColParams& p, const hot_quant_t& hq, uint8_t* codes, float* scales, uint32_t* ws,
+             cudaStream_t st) {
+  constexpr int VEC = vec_for<T, N>();
+  constexpr int CC = 32 * VEC * ColTraits<T>::kCpl;
+  const QuantDev q = make_quant_dev(hq);
+  const int64_t nblk = p.rows / N;
+  dim3 grid((unsigned)((p.cols + CC - 1) / CC), (unsigned)((nblk + p.nb - 1) / p.nb));
+  const size_t smem = (size_t)CC * p.pitch * sizeof(float);
+  HOT_CUDA(cudaMemsetAsync(ws, 0, sizeof(uint32_t) * (p.scale_row ? p.cols : 1), st));
+  col_ht_absmax_kernel<T, N><<<grid, kThreads, 0, st>>>(x, p, ws);
+  auto launch = [&](auto kernel) -> int {
+    HOT_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    kernel<<<grid, kThreads, smem, st>>>(x, p, q, codes, scales, ws);
+    return HOT_OK;
+  };
+  int rc;
+  switch (hq.rounding) {
+    case HOT_ROUND_NEAREST: rc = launch(col_ht_quant_kernel<T, N, HOT_ROUND_NEAREST>); break;
+    case HOT_ROUND_STOCH_PHILOX: rc = launch(col_ht_quant_kernel<T, N, HOT_ROUND_STOCH_PHILOX>); break;
+    default: rc = launch(col_ht_quant_kernel<T, N, HOT_ROUND_STOCH_NOISE>); break;
+  }
+  if (rc) return rc;
+  HOT_CUDA(cudaGetLastError());
+  return HOT_OK;
+}
+
+template <typename T>
+int launch_t(const T* x, int n, const ColParams& p, const hot_quant_t& hq, uint8_t* codes, float* scales, uint32_t* ws,
+             cudaStream_t st) {
+  switch (n) {
+    case 1: return launch_n<T, 1>(x, p, hq, codes, scales, ws, st);
+    case 2: return launch_n<T, 2>(x, p, hq, codes, scales, ws, st);
+    case 4: return launch_n<T, 4>(x, p, hq, codes, scales, ws, st);
+    case 8: return launch_n<T, 8>(x, p, hq, codes, scales, ws, st);
+    case 16: return launch_n<T, 16>(x, p, hq, codes, scales, ws, st);
+    case 32: return launch_n<T, 32>(x, p, hq, codes, scales, ws, st);
+    case 64: return launch_n<T, 64>(x, p, hq, codes, scales, ws, st);
+  }
+  HOT_FAIL(HOT_ERR_UNSUPPORTED, "hot_col_ht_quant: order %d not in {1,2,4,8,16,32,64}", n);
+}
+
+}  // namespace
+}  // namespace hot
+
+extern "C" int hot_col_ht_quant(const void* x, int dtype, int64_t rows, int64_t cols, int64_t ldx, int order,
+                                const int32_t* sel, int r, const hot_quant_t* q, int logical_layout, void* codes_t,
+                                int64_t ld_codes, float* scales, uint32_t* absmax_ws, hot_stream_t stream) {
+  using namespace hot;
+  if (!x || !q || !codes_t || !scales || !sel || !absmax_ws) HOT_FAIL(HOT_ERR_ARG, "hot_col_ht_quant: null pointer");
+  if (rows < 0 || cols <= 0 || cols > (1 << 30)) HOT_FAIL(HOT_ERR_ARG, "hot_col_ht_quant: bad shape");
+  if (int rc = validate_quant(q, "hot_col_ht_quant")) return rc;
+  if (order < 1 || order > 64 || (order & (order - 1)))
+    HOT_FAIL(HOT_ERR_UNSUPPORTED, "hot_col_ht_quant: order %d not a power of two in [1, 64]", order);
+  if (rows % order != 0) HOT_FAIL(HOT_ERR_UNSUPPORTED, "hot_col_ht_quant: rows %lld not a multiple of order %d", (long long)rows, order);
+  if (r < 1 || r > order) HOT_FAIL(HOT_ERR_ARG, "hot_col_ht_quant: rank %d outside [1, %d]", r, order);
+  const int esz = dtype == HOT_F32 ? 4 : 2;
+  if (dtype != HOT_F32 && dtype != HOT_BF16) HOT_FAIL(HOT_ERR_UNSUPPORTED, "hot_col_ht_quant: dtype %d", dtype);
+  if (ldx < cols || (ldx * esz) % 4 != 0 || ((uintptr_t)x) % 4 != 0 || (dtype == HOT_BF16 && cols % 2 != 0))
+    HOT_FAIL(HOT_ERR_ARG, "hot_col_ht_quant: x pitch must be >= cols and 4-byte aligned (bf16: even cols)");
+  ColParams p;
+  p.rows = rows;
+  p.cols = (int)cols;
+  p.ldx = ldx;
+  p.ld_codes = ld_codes;
+  p.r = r;
+  p.out_len = rows / order * r;
+  p.scale_row = q->scale_mode == HOT_SCALE_ROW;
+  p.store4 = q->storage == HOT_STORE_INT4;
+  p.noise_transposed = logical_layout == HOT_LAYOUT_TRANSPOSED;
+  for (int k = 0; k < 64; ++k) p.pos[k] = -1;
+  for (int j = 0; j < r; ++j) {
+    if (sel[j] < 0 || sel[j] >= order || p.pos[sel[j]] >= 0)
+      HOT_FAIL(HOT_ERR_ARG, "hot_col_ht_quant: sel[%d] = %d out of range or repeated", j, sel[j]);
+    p.pos[sel[j]] = (signed char)j;
+  }
+  // blocks per tile: a multiple of 8 (so that nb * r is a multiple of 8 codes) near 128 / r
+  int nb = (128 / r) / 8 * 8;
+  if (nb < 8) nb = 8;
+  p.nb = nb;
+  p.pitch = ((nb * r + 31) / 32) * 32 + 4;
+  const int64_t row_bytes = p.store4 ? (p.out_len + 1) / 2 : p.out_len;
+  if (ld_codes % 16 != 0 || ld_codes < ((row_bytes + 7) / 8) * 8 || ((uintptr_t)codes_t) % 16 != 0)
+    HOT_FAIL(HOT_ERR_ARG, "hot_col_ht_quant: codes pitch %lld must be a multiple of 16 and >= %lld", (long long)ld_codes,
+             (long long)row_bytes);
+  if (rows == 0) return HOT_OK;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (dtype == HOT_F32) return launch_t<float>((const float*)x, order, p, *q, (uint8_t*)codes_t, scales, absmax_ws, st);
+  return launch_t<__nv_bfloat16>((const __nv_bfloat16*)x, order, p, *q, (uint8_t*)codes_t, scales, absmax_ws, st);
+}

@@ -1,0 +1,56 @@
+// Host-side plumbing shared by the entry points: last-error text, argument validation,
+// device properties.
+#include <cstdarg>
+#include <cstdio>
+
+#include "common.cuh"
+
+namespace hot {
+
+namespace {
+thread_local char g_last_error[512] = "";
+}
+
+void set_error(const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_last_error, sizeof(g_last_error), fmt, ap);
+  va_end(ap);
+}
+
+int validate_quant(const hot_quant_t* q, const char* who) {
+  if (q->bits < 2 || q->bits > 8) HOT_FAIL(HOT_ERR_ARG, "%s: bits %d outside [2, 8]", who, q->bits);
+  if (q->storage != HOT_STORE_INT8 && q->storage != HOT_STORE_INT4) HOT_FAIL(HOT_ERR_ARG, "%s: storage %d", who, q->storage);
+  if (q->storage == HOT_STORE_INT4 && q->bits > 4) HOT_FAIL(HOT_ERR_ARG, "%s: INT4 storage needs bits <= 4 (got %d)", who, q->bits);
+  if (q->rounding < HOT_ROUND_NEAREST || q->rounding > HOT_ROUND_STOCH_NOISE) HOT_FAIL(HOT_ERR_ARG, "%s: rounding %d", who, q->rounding);
+  if (q->scale_mode != HOT_SCALE_TENSOR && q->scale_mode != HOT_SCALE_ROW) HOT_FAIL(HOT_ERR_ARG, "%s: scale_mode %d", who, q->scale_mode);
+  if (q->rounding == HOT_ROUND_STOCH_NOISE && !q->noise) HOT_FAIL(HOT_ERR_ARG, "%s: explicit-noise rounding without a noise pointer", who);
+  return HOT_OK;
+}
+
+int device_sm_count() {
+  int dev = 0, sms = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) {
+    set_error("cannot query the current CUDA device");
+    return -1;
+  }
+  return sms;
+}
+
+}  // namespace hot
+
+extern "C" const char* hot_status_string(int status) {
+  switch (status) {
+    case HOT_OK: return "ok";
+    case HOT_ERR_ARG: return "invalid argument";
+    case HOT_ERR_UNSUPPORTED: return "unsupported size or mode";
+    case HOT_ERR_CUDA: return "CUDA call failed";
+    case HOT_ERR_TIMEOUT: return "bounded device-side wait ran out";
+    case HOT_ERR_WORKSPACE: return "workspace too small";
+  }
+  return "unknown status";
+}
+
+extern "C" const char* hot_last_error(void) { return hot::g_last_error; }
+
+extern "C" int hot_abi_version(void) { return 1; }

@@ -1,0 +1,468 @@
+// Integer GEMM  out[m, n] = dequant( sum_k a[m, k] * b[n, k] )  on the 5th-generation tensor
+// cores: tcgen05.mma kind::i8, int32 accumulators in tensor memory, operands brought in by TMA.
+//
+// One CTA computes one 128 x BN output tile.  Warp roles:
+//   warp 0      TMA producer: per 128-byte K slab, one tiled bulk copy for A (128 rows) and one
+//               for B (BN rows) into a 128B-swizzled shared-memory stage; completion on full[s]
+//   warp 1      allocates tensor memory, issues 4 x (M128, N BN, K32) MMAs per stage from one
+//               elected lane, releases the stage with tcgen05.commit -> empty[s]
+//   warps 2..5  epilogue: tcgen05.ld the accumulator (each warp its 32-lane quarter), convert,
+//               apply (acc * sa) * sb * post, store fp32 / bf16 / raw int32
+// Operands stored as packed INT4 take a detour: TMA lands the packed bytes in a raw stage and
+// the four epilogue warps sign-extend them to int8 into the swizzled stage before the MMA warp
+// is signalled (Blackwell has no 4-bit integer MMA kind).
+//
+// Every wait on an mbarrier is bounded in time; when a wait runs out the CTA ORs a code into
+// the caller's status word, stops issuing work, frees its tensor memory and returns.
+#include <cuda.h>
+
+#include "common.cuh"
+
+namespace hot {
+namespace {
+
+constexpr int kBM = 128;
+constexpr int kBK = 128;  // int8 elements (= bytes) of K per stage: one 128B swizzle span
+constexpr int kGemmThreads = 192;
+constexpr uint64_t kWaitLimitNs = 1500ull * 1000ull * 1000ull;
+
+struct GemmParams {
+  int M, N, K, num_kb;
+  const float* sa;
+  const float* sb;
+  int sa_row, sb_row;
+  float post;
+  void* out;
+  int64_t ldo;
+  int out_dtype;
+  uint32_t* status;
+};
+
+// ---- PTX wrappers ------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ uint64_t global_timer_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+// Bounded wait.  Returns false when it gave up (time limit, or another role already aborted).
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const uint64_t t0 = global_timer_ns();
+  for (uint32_t it = 1;; ++it) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((it & 63u) == 0) {
+      if (*abort_flag) return false;
+      if (global_timer_ns() - t0 > kWaitLimitNs) {
+        *abort_flag = 1u;
+        return false;
+      }
+    }
+  }
+}
+
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(
+          smem_u32(dst)),
+      "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(c0), "r"(c1)
+      : "memory");
+}
+__device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* map) {
+  asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");
+}
+
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tmem_alloc(uint32_t* slot, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(slot)), "r"(ncols)
+               : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void umma_i8(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// Arrive on an mbarrier once all MMAs issued so far by this thread have completed.
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+               : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+// Shared-memory matrix descriptor: K-major operand, 128B swizzle, rows 128 bytes apart,
+// 8-row groups 1024 bytes apart (SBO), descriptor version 1 (sm_100).
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr >> 4) & 0x3FFFu);
+  d |= (uint64_t)1u << 16;            // leading byte offset (unused for swizzled K-major), 16 B
+  d |= (uint64_t)(1024u >> 4) << 32;  // stride byte offset
+  d |= (uint64_t)1u << 46;            // version
+  d |= (uint64_t)2u << 61;            // SWIZZLE_128B
+  return d;
+}
+// Instruction descriptor: D = S32, A = B = signed 8-bit, both K-major, M = 128, N = BN.
+__host__ __device__ constexpr uint32_t instr_desc_i8(int bn) {
+  return (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(bn >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
+}
+
+template <int BN, int STAGES, bool A4, bool B4>
+struct SmemLayout {
+  static constexpr int kA = kBM * kBK;       // int8 stage of A
+  static constexpr int kB = BN * kBK;        // int8 stage of B
+  static constexpr int kRawA = A4 ? kBM * kBK / 2 : 0;
+  static constexpr int kRawB = B4 ? BN * kBK / 2 : 0;
+  static constexpr int kOffA = 0;
+  static constexpr int kOffB = kOffA + STAGES * kA;
+  static constexpr int kOffRawA = kOffB + STAGES * kB;
+  static constexpr int kOffRawB = kOffRawA + STAGES * kRawA;
+  static constexpr int kOffBar = kOffRawB + STAGES * kRawB;
+  static constexpr int kBytes = kOffBar + 256 + 1024;  // barriers + slack to align the base to 1024
+};
+
+// Sign-extend the 8 nibbles of a word to two words of int8 (low nibble first).
+__device__ __forceinline__ void unpack8(uint32_t w, uint32_t& lo, uint32_t& hi) {
+  // even nibbles -> bytes 0, 2 of each half; odd nibbles -> bytes 1, 3
+  const uint32_t e = w & 0x0F0F0F0Fu;          // nibbles 0, 2, 4, 6 in bytes 0..3
+  const uint32_t o = (w >> 4) & 0x0F0F0F0Fu;   // nibbles 1, 3, 5, 7
+  // interleave: result bytes = n0 n1 n2 n3 | n4 n5 n6 n7
+  uint32_t l = __byte_perm(e, o, 0x5140);      // e0 o0 e1 o1
+  uint32_t h = __byte_perm(e, o, 0x7362);      // e2 o2 e3 o3
+  // sign-extend each 4-bit value held in a byte: (x ^ 8) - 8 per byte
+  l = __vsub4(l ^ 0x08080808u, 0x08080808u);
+  h = __vsub4(h ^ 0x08080808u, 0x08080808u);
+  lo = l;
+  hi = h;
+}
+
+// Expand a raw stage of `rows` rows x 64 packed bytes into the swizzled int8 stage
+// (row r at r * 128, 16-byte chunk c at chunk position c ^ (r & 7)).  128 threads cooperate.
+__device__ __forceinline__ void unpack_stage(const uint8_t* raw, uint8_t* dst, int rows, int tid128) {
+  // each thread converts 16 packed bytes (32 codes = two output chunks) at a time
+  const int items = rows * 4;
+  for (int it = tid128; it < items; it += 128) {
+    const int r = it >> 2, qd = it & 3;
+    const uint4 w = *reinterpret_cast<const uint4*>(raw + r * 64 + qd * 16);
+    uint4 o0, o1;
+    unpack8(w.x, o0.x, o0.y);
+    unpack8(w.y, o0.z, o0.w);
+    unpack8(w.z, o1.x, o1.y);
+    unpack8(w.w, o1.z, o1.w);
+    const int c0 = qd * 2, c1 = qd * 2 + 1;
+    *reinterpret_cast<uint4*>(dst + r * 128 + ((c0 ^ (r & 7)) << 4)) = o0;
+    *reinterpret_cast<uint4*>(dst + r * 128 + ((c1 ^ (r & 7)) << 4)) = o1;
+  }
+}
+
+template <int BN, int STAGES, bool A4, bool B4>
+__global__ void __launch_bounds__(kGemmThreads) gemm_i8_kernel(const __grid_constant__ CUtensorMap tma_a,
+                                                                const __grid_constant__ CUtensorMap tma_b,
+                                                                GemmParams p) {
+  using L = SmemLayout<BN, STAGES, A4, B4>;
+  constexpr bool kUnpack = A4 || B4;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  uint8_t* sA = smem + L::kOffA;
+  uint8_t* sB = smem + L::kOffB;
+  uint8_t* rawA = smem + L::kOffRawA;
+  uint8_t* rawB = smem + L::kOffRawB;
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + L::kOffBar);  // TMA landed
+  uint64_t* empty = full + STAGES;                                   // MMAs of the stage retired
+  uint64_t* ready = empty + STAGES;                                  // unpacked (INT4 operands only)
+  uint64_t* tmem_full = ready + STAGES;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_full + 1);
+  volatile uint32_t* abort_flag = tmem_slot + 1;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int m0 = blockIdx.y * kBM, n0 = blockIdx.x * BN;
+  constexpr uint32_t kTmemCols = BN < 32 ? 32 : BN;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+      mbar_init(&ready[s], 128);
+    }
+    mbar_init(tmem_full, 1);
+    *abort_flag = 0u;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    tma_prefetch_desc(&tma_a);
+    tma_prefetch_desc(&tma_b);
+  }
+  if (warp == 1) tmem_alloc(tmem_slot, kTmemCols);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      constexpr uint32_t kTx = (A4 ? L::kRawA : L::kA) + (B4 ? L::kRawB : L::kB);
+      for (int kb = 0; kb < p.num_kb; ++kb) {
+        const int s = kb % STAGES;
+        const uint32_t ph = (uint32_t)(kb / STAGES) & 1u;
+        if (!mbar_wait(&empty[s], ph ^ 1u, abort_flag)) break;
+        mbar_expect_tx(&full[s], kTx);
+        if (A4) tma_load_2d(rawA + s * L::kRawA, &tma_a, &full[s], kb * (kBK / 2), m0);
+        else tma_load_2d(sA + s * L::kA, &tma_a, &full[s], kb * kBK, m0);
+        if (B4) tma_load_2d(rawB + s * L::kRawB, &tma_b, &full[s], kb * (kBK / 2), n0);
+        else tma_load_2d(sB + s * L::kB, &tma_b, &full[s], kb * kBK, n0);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = instr_desc_i8(BN);
+      bool ok = true;
+      for (int kb = 0; kb < p.num_kb && ok; ++kb) {
+        const int s = kb % STAGES;
+        const uint32_t ph = (uint32_t)(kb / STAGES) & 1u;
+        ok = mbar_wait(kUnpack ? &ready[s] : &full[s], ph, abort_flag);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t a_addr = smem_u32(sA + s * L::kA), b_addr = smem_u32(sB + s * L::kB);
+#pragma unroll
+        for (int k4 = 0; k4 < kBK / 32; ++k4)
+          umma_i8(tmem_base, smem_desc_sw128(a_addr + k4 * 32), smem_desc_sw128(b_addr + k4 * 32), idesc,
+                  (kb | k4) != 0 ? 1u : 0u);
+        umma_commit(&empty[s]);
+      }
+      if (ok) umma_commit(tmem_full);
+    }
+  } else {
+    const int tid128 = threadIdx.x - 64;
+    bool ok = true;
+    if (kUnpack) {
+      for (int kb = 0; kb < p.num_kb && ok; ++kb) {
+        const int s = kb % STAGES;
+        const uint32_t ph = (uint32_t)(kb / STAGES) & 1u;
+        ok = mbar_wait(&full[s], ph, abort_flag);
+        if (!ok) break;
+        if (A4) unpack_stage(rawA + s * L::kRawA, sA + s * L::kA, kBM, tid128);
+        if (B4) unpack_stage(rawB + s * L::kRawB, sB + s * L::kB, BN, tid128);
+        fence_proxy_async_smem();  // generic-proxy writes -> visible to the tensor core (async proxy)
+        mbar_arrive(&ready[s]);
+      }
+    }
+    if (ok) ok = mbar_wait(tmem_full, 0u, abort_flag);
+    if (ok) {
+      tc_fence_after();
+      const int q = warp & 3;  // tensor-memory lane quarter this warp may read
+      const int row = m0 + q * 32 + lane;
+      const bool row_ok = row < p.M;
+      const bool raw = p.out_dtype == HOT_I32;  // raw accumulators: no scales to read
+      const float sa = (row_ok && !raw) ? (p.sa_row ? p.sa[row] : p.sa[0]) : 0.0f;
+      const float sb0 = (p.sb_row || raw) ? 0.0f : p.sb[0];
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t acc[32];
+        tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(c * 32), acc);
+        const int col0 = n0 + c * 32;
+        if (!row_ok || col0 >= p.N) continue;
+        if (raw) {
+          int32_t* o = reinterpret_cast<int32_t*>(p.out) + (int64_t)row * p.ldo + col0;
+          if (col0 + 32 <= p.N && (p.ldo & 3) == 0) {
+#pragma unroll
+            for (int i = 0; i < 32; i += 4)
+              *reinterpret_cast<int4*>(o + i) = make_int4((int)acc[i], (int)acc[i + 1], (int)acc[i + 2], (int)acc[i + 3]);
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              if (col0 + i < p.N) o[i] = (int)acc[i];
+          }
+          continue;
+        }
+        float f[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const float sb = p.sb_row ? ((col0 + i < p.N) ? p.sb[col0 + i] : 0.0f) : sb0;
+          f[i] = __fmul_rn(__fmul_rn(__fmul_rn((float)(int)acc[i], sa), sb), p.post);
+        }
+        if (p.out_dtype == HOT_F32) {
+          float* o = reinterpret_cast<float*>(p.out) + (int64_t)row * p.ldo + col0;
+          if (col0 + 32 <= p.N && (p.ldo & 3) == 0) {
+#pragma unroll
+            for (int i = 0; i < 32; i += 4) *reinterpret_cast<float4*>(o + i) = make_float4(f[i], f[i + 1], f[i + 2], f[i + 3]);
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              if (col0 + i < p.N) o[i] = f[i];
+          }
+        } else {
+          __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(p.out) + (int64_t)row * p.ldo + col0;
+          if (col0 + 32 <= p.N && (p.ldo & 7) == 0) {
+#pragma unroll
+            for (int i = 0; i < 32; i += 8) {
+              uint4 w;
+              __nv_bfloat162 t0 = __floats2bfloat162_rn(f[i], f[i + 1]);
+              __nv_bfloat162 t1 = __floats2bfloat162_rn(f[i + 2], f[i + 3]);
+              __nv_bfloat162 t2 = __floats2bfloat162_rn(f[i + 4], f[i + 5]);
+              __nv_bfloat162 t3 = __floats2bfloat162_rn(f[i + 6], f[i + 7]);
+              w.x = *reinterpret_cast<uint32_t*>(&t0);
+              w.y = *reinterpret_cast<uint32_t*>(&t1);
+              w.z = *reinterpret_cast<uint32_t*>(&t2);
+              w.w = *reinterpret_cast<uint32_t*>(&t3);
+              *reinterpret_cast<uint4*>(o + i) = w;
+            }
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              if (col0 + i < p.N) o[i] = __float2bfloat16_rn(f[i]);
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+  if (threadIdx.x == 0 && *abort_flag) {
+    if (p.status) atomicOr(p.status, 1u);
+    // bulk copies issued before the abort land within microseconds; give them time before the
+    // shared memory of this CTA is released
+    const uint64_t t0 = global_timer_ns();
+    while (global_timer_ns() - t0 < 100000ull) {
+    }
+  }
+}
+
+// ---- host side ---------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static bool tried = false;
+  if (!tried) {
+    tried = true;
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  }
+  return fn;
+}
+
+// Tensor map over a [rows, row_bytes] byte matrix with pitch ld, box = box_bytes x box_rows.
+int make_map(CUtensorMap* map, const void* base, int64_t rows, int64_t row_bytes, int64_t ld, int box_bytes,
+             int box_rows, bool swizzle128) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) HOT_FAIL(HOT_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+  cuuint64_t dims[2] = {(cuuint64_t)row_bytes, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)ld};
+  cuuint32_t box[2] = {(cuuint32_t)box_bytes, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) HOT_FAIL(HOT_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+  return HOT_OK;
+}
+
+template <int BN, int STAGES, bool A4, bool B4>
+int launch_gemm(const void* a, int64_t lda, const void* b, int64_t ldb, const GemmParams& p, cudaStream_t st) {
+  using L = SmemLayout<BN, STAGES, A4, B4>;
+  CUtensorMap ma, mb;
+  int rc;
+  if (A4) rc = make_map(&ma, a, p.M, (p.K + 1) / 2, lda, kBK / 2, kBM, false);
+  else rc = make_map(&ma, a, p.M, p.K, lda, kBK, kBM, true);
+  if (rc) return rc;
+  if (B4) rc = make_map(&mb, b, p.N, (p.K + 1) / 2, ldb, kBK / 2, BN, false);
+  else rc = make_map(&mb, b, p.N, p.K, ldb, kBK, BN, true);
+  if (rc) return rc;
+  auto kernel = gemm_i8_kernel<BN, STAGES, A4, B4>;
+  HOT_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kBytes));
+  dim3 grid((unsigned)((p.N + BN - 1) / BN), (unsigned)((p.M + kBM - 1) / kBM));
+  kernel<<<grid, kGemmThreads, L::kBytes, st>>>(ma, mb, p);
+  HOT_CUDA(cudaGetLastError());
+  return HOT_OK;
+}
+
+}  // namespace
+}  // namespace hot
+
+extern "C" int hot_gemm_i8(const void* a, int a_storage, int64_t lda, const void* b, int b_storage, int64_t ldb,
+                           int64_t M, int64_t N, int64_t K, const float* scale_a, int scale_a_per_row,
+                           const float* scale_b, int scale_b_per_row, float post, void* out, int out_dtype, int64_t ldo,
+                           uint32_t* status_word, hot_stream_t stream) {
+  using namespace hot;
+  if (!a || !b || !out) HOT_FAIL(HOT_ERR_ARG, "hot_gemm_i8: null pointer");
+  if (M <= 0 || N <= 0 || K <= 0 || M > (1 << 30) || N > (1 << 30) || K > (1 << 30))
+    HOT_FAIL(HOT_ERR_ARG, "hot_gemm_i8: bad shape M=%lld N=%lld K=%lld", (long long)M, (long long)N, (long long)K);
+  if (out_dtype != HOT_I32 && (!scale_a || !scale_b)) HOT_FAIL(HOT_ERR_ARG, "hot_gemm_i8: null scale pointer");
+  const bool a4 = a_storage == HOT_STORE_INT4, b4 = b_storage == HOT_STORE_INT4;
+  if ((a4 || b4) && (K % 2 != 0)) HOT_FAIL(HOT_ERR_ARG, "hot_gemm_i8: packed INT4 operands need an even K");
+  const int64_t abytes = a4 ? K / 2 : K, bbytes = b4 ? K / 2 : K;
+  if (lda % 16 || ldb % 16 || lda < abytes || ldb < bbytes || ((uintptr_t)a) % 16 || ((uintptr_t)b) % 16)
+    HOT_FAIL(HOT_ERR_ARG, "hot_gemm_i8: operand base and pitch must be 16-byte aligned and cover K");
+  if (ldo < N) HOT_FAIL(HOT_ERR_ARG, "hot_gemm_i8: ldo < N");
+  const int osz = out_dtype == HOT_BF16 ? 2 : 4;
+  if (out_dtype != HOT_F32 && out_dtype != HOT_BF16 && out_dtype != HOT_I32)
+    HOT_FAIL(HOT_ERR_UNSUPPORTED, "hot_gemm_i8: out dtype %d", out_dtype);
+  if (((uintptr_t)out) % 16 != 0 || (ldo * osz) % 4 != 0) HOT_FAIL(HOT_ERR_ARG, "hot_gemm_i8: out must be 16-byte aligned");
+  GemmParams p;
+  p.M = (int)M;
+  p.N = (int)N;
+  p.K = (int)K;
+  p.num_kb = (int)((K + kBK - 1) / kBK);
+  p.sa = scale_a;
+  p.sb = scale_b;
+  p.sa_row = scale_a_per_row;
+  p.sb_row = scale_b_per_row;
+  p.post = post;
+  p.out = out;
+  p.ldo = ldo;
+  p.out_dtype = out_dtype;
+  p.status = status_word;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (!a4 && !b4) return launch_gemm<128, 3, false, false>(a, lda, b, ldb, p, st);
+  if (a4 && !b4) return launch_gemm<128, 3, true, false>(a, lda, b, ldb, p, st);
+  if (!a4 && b4) return launch_gemm<128, 3, false, true>(a, lda, b, ldb, p, st);
+  return launch_gemm<128, 3, true, true>(a, lda, b, ldb, p, st);
+}

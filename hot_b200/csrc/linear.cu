@@ -1,0 +1,112 @@
+// The HOT backward of one linear layer as a sequence of the three kernels, plus the
+// forward-side activation-buffer compression.  All intermediates live in a caller-owned
+// workspace; nothing here allocates or synchronises.
+#include "common.cuh"
+
+namespace hot {
+namespace {
+
+constexpr size_t kAlign = 256;
+inline size_t up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+inline int64_t code_pitch(int64_t len, int storage) { return (int64_t)up((size_t)(storage == HOT_STORE_INT4 ? (len + 1) / 2 : len), 16); }
+
+struct Workspace {
+  size_t off_qgo, off_sgo, off_qw, off_sw, off_qgw, off_sgw, off_scratch, total;
+  int64_t ld_qgo, ld_qw, ld_qgw, lp;
+};
+
+int plan(int64_t L, int64_t O, int64_t I, const hot_linear_cfg_t& c, Workspace& w) {
+  if (c.order_l < 1 || c.rank_l < 1 || c.rank_l > c.order_l || L % c.order_l != 0)
+    HOT_FAIL(HOT_ERR_ARG, "hot_linear: tokens %lld not a multiple of the low-rank order %d (rank %d)", (long long)L,
+             c.order_l, c.rank_l);
+  w.lp = L / c.order_l * c.rank_l;
+  w.ld_qgo = code_pitch(O, c.q_gx.storage);
+  w.ld_qw = code_pitch(O, c.q_w.storage);
+  w.ld_qgw = code_pitch(w.lp, c.q_gw.storage);
+  size_t o = 0;
+  w.off_qgo = o; o += up((size_t)L * w.ld_qgo, kAlign);
+  w.off_sgo = o; o += up((size_t)L * sizeof(float), kAlign);
+  w.off_qw = o;  o += up((size_t)I * w.ld_qw, kAlign);
+  w.off_sw = o;  o += kAlign;
+  w.off_qgw = o; o += up((size_t)O * w.ld_qgw, kAlign);
+  w.off_sgw = o; o += up((size_t)O * sizeof(float), kAlign);
+  w.off_scratch = o; o += up((size_t)(O > I ? O : I) * sizeof(uint32_t) + 64, kAlign);
+  w.total = o;
+  return HOT_OK;
+}
+
+}  // namespace
+}  // namespace hot
+
+extern "C" size_t hot_linear_workspace_bytes(int64_t L, int64_t O, int64_t I, const hot_linear_cfg_t* cfg) {
+  hot::Workspace w;
+  if (!cfg || L <= 0 || O <= 0 || I <= 0 || hot::plan(L, O, I, *cfg, w)) return 0;
+  return w.total;
+}
+
+extern "C" int64_t hot_abc_pitch(int64_t L, const hot_linear_cfg_t* cfg) {
+  if (!cfg || cfg->order_l < 1 || L % cfg->order_l != 0) return 0;
+  return hot::code_pitch(L / cfg->order_l * cfg->rank_l, cfg->q_x.storage);
+}
+
+extern "C" int hot_abc_compress(const void* x, int64_t L, int64_t I, int64_t ldx, const hot_linear_cfg_t* cfg,
+                                void* x_q_t, float* scale_x, void* workspace, size_t workspace_bytes,
+                                hot_stream_t stream) {
+  using namespace hot;
+  if (!x || !cfg || !x_q_t || !scale_x || !workspace) HOT_FAIL(HOT_ERR_ARG, "hot_abc_compress: null pointer");
+  if (workspace_bytes < 64) HOT_FAIL(HOT_ERR_WORKSPACE, "hot_abc_compress: workspace needs 64 bytes");
+  if (cfg->q_x.scale_mode != HOT_SCALE_TENSOR) HOT_FAIL(HOT_ERR_UNSUPPORTED, "hot_abc_compress: the activation buffer takes one scale");
+  const int64_t pitch = hot_abc_pitch(L, cfg);
+  if (pitch == 0) HOT_FAIL(HOT_ERR_ARG, "hot_abc_compress: tokens %lld not a multiple of the low-rank order %d", (long long)L, cfg->order_l);
+  return hot_col_ht_quant(x, cfg->dtype, L, I, ldx, cfg->order_l, cfg->sel_l, cfg->rank_l, &cfg->q_x, HOT_LAYOUT_NATURAL,
+                          x_q_t, pitch, scale_x, (uint32_t*)workspace, stream);
+}
+
+extern "C" int hot_linear_backward(const void* go, int64_t ldgo, const void* w, int64_t ldw, const void* x_q_t,
+                                   const float* scale_x, int64_t L, int64_t O, int64_t I, const hot_linear_cfg_t* cfg,
+                                   void* grad_x, int64_t ldgx, void* grad_w, int64_t ldgw, void* workspace,
+                                   size_t workspace_bytes, uint32_t* status_word, hot_stream_t stream) {
+  using namespace hot;
+  if (!go || !w || !x_q_t || !scale_x || !cfg || !workspace) HOT_FAIL(HOT_ERR_ARG, "hot_linear_backward: null pointer");
+  if (!grad_x && !grad_w) HOT_FAIL(HOT_ERR_ARG, "hot_linear_backward: no output requested");
+  if (L <= 0 || O <= 0 || I <= 0) HOT_FAIL(HOT_ERR_ARG, "hot_linear_backward: bad shape");
+  Workspace ws;
+  if (int rc = plan(L, O, I, *cfg, ws)) return rc;
+  if (workspace_bytes < ws.total)
+    HOT_FAIL(HOT_ERR_WORKSPACE, "hot_linear_backward: workspace %zu < %zu bytes", workspace_bytes, ws.total);
+  if (((uintptr_t)workspace) % kAlign != 0) HOT_FAIL(HOT_ERR_ARG, "hot_linear_backward: workspace must be 256-byte aligned");
+  if (cfg->order_o < 1 || cfg->order_o > 16 || O % cfg->order_o != 0)
+    HOT_FAIL(HOT_ERR_ARG, "hot_linear_backward: order_o %d does not divide O = %lld", cfg->order_o, (long long)O);
+  uint8_t* base = (uint8_t*)workspace;
+  uint32_t* scratch = (uint32_t*)(base + ws.off_scratch);
+  int rc;
+  if (grad_x) {
+    float* s_go = (float*)(base + ws.off_sgo);
+    float* s_w = (float*)(base + ws.off_sw);
+    rc = hot_row_ht_quant(go, cfg->dtype, L, O, ldgo, cfg->order_o, &cfg->q_gx, base + ws.off_qgo, ws.ld_qgo, s_go, scratch,
+                          stream);
+    if (rc) return rc;
+    int32_t ident[64];
+    for (int i = 0; i < 64; ++i) ident[i] = i;
+    if (cfg->q_w.scale_mode != HOT_SCALE_TENSOR) HOT_FAIL(HOT_ERR_UNSUPPORTED, "hot_linear_backward: the weight takes one scale");
+    rc = hot_col_ht_quant(w, cfg->dtype, O, I, ldw, cfg->order_o, ident, cfg->order_o, &cfg->q_w, HOT_LAYOUT_NATURAL,
+                          base + ws.off_qw, ws.ld_qw, s_w, scratch + 16, stream);
+    if (rc) return rc;
+    rc = hot_gemm_i8(base + ws.off_qgo, cfg->q_gx.storage, ws.ld_qgo, base + ws.off_qw, cfg->q_w.storage, ws.ld_qw, L, I, O,
+                     s_go, cfg->q_gx.scale_mode == HOT_SCALE_ROW, s_w, 0, 1.0f / (float)cfg->order_o, grad_x, cfg->dtype,
+                     ldgx, status_word, stream);
+    if (rc) return rc;
+  }
+  if (grad_w) {
+    float* s_gw = (float*)(base + ws.off_sgw);
+    rc = hot_col_ht_quant(go, cfg->dtype, L, O, ldgo, cfg->order_l, cfg->sel_l, cfg->rank_l, &cfg->q_gw,
+                          HOT_LAYOUT_TRANSPOSED, base + ws.off_qgw, ws.ld_qgw, s_gw, scratch + 32, stream);
+    if (rc) return rc;
+    rc = hot_gemm_i8(base + ws.off_qgw, cfg->q_gw.storage, ws.ld_qgw, x_q_t, cfg->q_x.storage, hot_abc_pitch(L, cfg), O, I,
+                     ws.lp, s_gw, cfg->q_gw.scale_mode == HOT_SCALE_ROW, scale_x, 0, 1.0f / (float)cfg->order_l, grad_w,
+                     cfg->dtype, ldgw, status_word, stream);
+    if (rc) return rc;
+  }
+  return HOT_OK;
+}

@@ -1,0 +1,206 @@
+"""Tensor-level wrappers over the C ABI: torch owns the memory and the stream, the library
+does the work.  Every function launches on ``torch.cuda.current_stream()`` of the input's
+device and returns without synchronising.
+"""
+from __future__ import annotations
+
+import ctypes
+from dataclasses import dataclass, field
+from typing import Optional, Sequence
+
+import torch
+
+from . import _cabi as C
+
+_DTYPES = {torch.float32: C.HOT_F32, torch.bfloat16: C.HOT_BF16}
+_ROUNDING = {"nearest": C.ROUND_NEAREST, "philox": C.ROUND_STOCH_PHILOX, "noise": C.ROUND_STOCH_NOISE}
+
+
+@dataclass
+class Quant:
+    """How one operand is quantised (mirrors ``hot_quant_t``)."""
+    bits: int = 8
+    storage: str = "int8"            # "int8" | "int4" (two codes per byte, low nibble = even index)
+    rounding: str = "philox"         # "nearest" | "philox" | "noise"
+    scale: str = "tensor"            # "tensor" | "row"
+    seed: int = 0
+    offset: int = 0
+    noise: Optional[torch.Tensor] = field(default=None, repr=False)
+
+    def to_c(self) -> C.HotQuant:
+        q = C.HotQuant()
+        q.bits = self.bits
+        q.storage = C.STORE_INT4 if self.storage == "int4" else C.STORE_INT8
+        q.rounding = _ROUNDING[self.rounding]
+        q.scale_mode = C.SCALE_ROW if self.scale == "row" else C.SCALE_TENSOR
+        q.seed, q.offset = self.seed & (2 ** 64 - 1), self.offset & (2 ** 64 - 1)
+        if self.rounding == "noise":
+            if self.noise is None or self.noise.dtype != torch.float32 or not self.noise.is_contiguous():
+                raise ValueError("rounding='noise' needs a contiguous float32 noise tensor")
+            q.noise = self.noise.data_ptr()
+        else:
+            q.noise = None
+        return q
+
+
+def _require_cuda(*tensors: torch.Tensor) -> None:
+    for t in tensors:
+        if not t.is_cuda:
+            raise RuntimeError("hot_b200 runs on CUDA tensors only (there is no CPU path)")
+
+
+def _stream(t: torch.Tensor) -> int:
+    return torch.cuda.current_stream(t.device).cuda_stream
+
+
+def _dtype(t: torch.Tensor) -> int:
+    try:
+        return _DTYPES[t.dtype]
+    except KeyError:
+        raise TypeError("hot_b200 supports float32 and bfloat16 tensors, got %s" % t.dtype) from None
+
+
+def _pitch16(nbytes: int) -> int:
+    return (nbytes + 15) // 16 * 16
+
+
+def row_ht_quant(x: torch.Tensor, order: int, q: Quant):
+    """Block-Hadamard transform of the last dim of ``x`` [rows, cols] + quantisation.
+    Returns (codes uint8 [rows, cols] or [rows, cols/2] packed (a view whose row pitch is a
+    multiple of 16 bytes), scales float32 [1] or [rows])."""
+    _require_cuda(x)
+    if x.dim() != 2 or x.stride(1) != 1:
+        raise ValueError("x must be 2-D with a contiguous last dim")
+    rows, cols = x.shape
+    row_bytes = cols // 2 if q.storage == "int4" else cols
+    codes = torch.empty((rows, _pitch16(row_bytes)), dtype=torch.uint8, device=x.device)[:, :row_bytes]
+    scales = torch.empty((rows if q.scale == "row" else 1,), dtype=torch.float32, device=x.device)
+    ws = torch.empty((16,), dtype=torch.int32, device=x.device)
+    with torch.cuda.device(x.device):
+        C.check(C.lib().hot_row_ht_quant(x.data_ptr(), _dtype(x), rows, cols, x.stride(0), order, ctypes.byref(q.to_c()),
+                                         codes.data_ptr(), codes.stride(0), scales.data_ptr(), ws.data_ptr(), _stream(x)),
+                "hot_row_ht_quant")
+    return codes, scales
+
+
+def col_ht_quant(x: torch.Tensor, order: int, sel: Sequence[int], q: Quant, logical_layout: str = "natural"):
+    """Block Walsh-Hadamard transform of the FIRST dim of ``x`` [rows, cols] keeping the rows
+    ``sel`` of H_order, + quantisation, written transposed.  Returns (codes_t uint8
+    [cols, pitch] whose first rows*r/order (int8) or half that (int4) bytes per row are codes,
+    scales float32 [1] or [cols], out_len)."""
+    _require_cuda(x)
+    if x.dim() != 2 or x.stride(1) != 1:
+        raise ValueError("x must be 2-D with a contiguous last dim")
+    rows, cols = x.shape
+    r = len(sel)
+    out_len = rows // order * r
+    pitch = _pitch16((out_len + 1) // 2 if q.storage == "int4" else out_len)
+    codes = torch.empty((cols, pitch), dtype=torch.uint8, device=x.device)
+    scales = torch.empty((cols if q.scale == "row" else 1,), dtype=torch.float32, device=x.device)
+    ws = torch.empty((max(cols, 16),), dtype=torch.int32, device=x.device)
+    sel_c = (C.c_i32 * r)(*[int(s) for s in sel])
+    with torch.cuda.device(x.device):
+        C.check(C.lib().hot_col_ht_quant(x.data_ptr(), _dtype(x), rows, cols, x.stride(0), order, sel_c, r,
+                                         ctypes.byref(q.to_c()),
+                                         C.LAYOUT_TRANSPOSED if logical_layout == "transposed" else C.LAYOUT_NATURAL,
+                                         codes.data_ptr(), pitch, scales.data_ptr(), ws.data_ptr(), _stream(x)),
+                "hot_col_ht_quant")
+    return codes, scales, out_len
+
+
+def gemm_i8(a: torch.Tensor, a_storage: str, b: torch.Tensor, b_storage: str, M: int, N: int, K: int,
+            scale_a: Optional[torch.Tensor], scale_b: Optional[torch.Tensor], post: float = 1.0,
+            out_dtype: torch.dtype = torch.float32, status: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out [M, N] = ((a . b^T) * scale_a[m or 0]) * scale_b[n or 0] * post on the tcgen05 integer path;
+    ``a`` [M, pitch] and ``b`` [N, pitch] are uint8/int8 code matrices with K contiguous.
+    ``out_dtype=torch.int32`` returns the raw accumulator."""
+    _require_cuda(a, b)
+    odt = {torch.float32: C.HOT_F32, torch.bfloat16: C.HOT_BF16, torch.int32: C.HOT_I32}[out_dtype]
+    out = torch.empty((M, N), dtype=out_dtype, device=a.device)
+    sa = scale_a.data_ptr() if scale_a is not None else None
+    sb = scale_b.data_ptr() if scale_b is not None else None
+    with torch.cuda.device(a.device):
+        C.check(C.lib().hot_gemm_i8(a.data_ptr(), C.STORE_INT4 if a_storage == "int4" else C.STORE_INT8, a.stride(0),
+                                    b.data_ptr(), C.STORE_INT4 if b_storage == "int4" else C.STORE_INT8, b.stride(0),
+                                    M, N, K, sa, int(scale_a is not None and scale_a.numel() > 1), sb,
+                                    int(scale_b is not None and scale_b.numel() > 1), float(post), out.data_ptr(), odt,
+                                    out.stride(0), status.data_ptr() if status is not None else None, _stream(a)),
+                "hot_gemm_i8")
+    return out
+
+
+@dataclass
+class LinearConfig:
+    """Per-layer backward configuration (mirrors ``hot_linear_cfg_t``)."""
+    order_o: int
+    order_l: int
+    sel_l: Sequence[int]
+    q_gx: Quant = field(default_factory=lambda: Quant(4, "int4"))
+    q_w: Quant = field(default_factory=lambda: Quant(4, "int4"))
+    q_gw: Quant = field(default_factory=lambda: Quant(8, "int8"))
+    q_x: Quant = field(default_factory=lambda: Quant(8, "int8"))
+
+    def to_c(self, dtype: torch.dtype) -> C.HotLinearCfg:
+        c = C.HotLinearCfg()
+        c.dtype = _DTYPES[dtype]
+        c.order_o, c.order_l, c.rank_l = self.order_o, self.order_l, len(self.sel_l)
+        for i, s in enumerate(self.sel_l):
+            c.sel_l[i] = int(s)
+        c.q_gx, c.q_w, c.q_gw, c.q_x = self.q_gx.to_c(), self.q_w.to_c(), self.q_gw.to_c(), self.q_x.to_c()
+        return c
+
+    def out_len(self, L: int) -> int:
+        return L // self.order_l * len(self.sel_l)
+
+
+def abc_compress(x: torch.Tensor, cfg: LinearConfig):
+    """Activation-buffer compression: x [L, I] -> (x_q_t uint8 [I, pitch], scale_x float32 [1])."""
+    _require_cuda(x)
+    L, I = x.shape
+    cc = cfg.to_c(x.dtype)
+    pitch = C.lib().hot_abc_pitch(L, ctypes.byref(cc))
+    if pitch <= 0:
+        raise ValueError("token count %d is not a multiple of the low-rank order %d" % (L, cfg.order_l))
+    x_q_t = torch.empty((I, pitch), dtype=torch.uint8, device=x.device)
+    scale = torch.empty((1,), dtype=torch.float32, device=x.device)
+    ws = torch.empty((64,), dtype=torch.uint8, device=x.device)
+    with torch.cuda.device(x.device):
+        C.check(C.lib().hot_abc_compress(x.data_ptr(), L, I, x.stride(0), ctypes.byref(cc), x_q_t.data_ptr(),
+                                         scale.data_ptr(), ws.data_ptr(), ws.numel(), _stream(x)), "hot_abc_compress")
+    return x_q_t, scale
+
+
+_workspaces: dict = {}
+
+
+def _workspace(device: torch.device, nbytes: int) -> torch.Tensor:
+    """One growing scratch buffer per (device, stream): kernels of consecutive layers on a
+    stream run in order, so they can share it."""
+    key = (device.index, torch.cuda.current_stream(device).cuda_stream)
+    buf = _workspaces.get(key)
+    if buf is None or buf.numel() < nbytes:
+        buf = torch.empty((max(nbytes, 1 << 20),), dtype=torch.uint8, device=device)
+        _workspaces[key] = buf
+    return buf
+
+
+def linear_backward(go: torch.Tensor, w: torch.Tensor, x_q_t: torch.Tensor, scale_x: torch.Tensor, cfg: LinearConfig,
+                    need_gx: bool = True, need_gw: bool = True, status: Optional[torch.Tensor] = None):
+    """HOT backward of one linear layer: returns (grad_x [L, I] or None, grad_w [O, I] or None)."""
+    _require_cuda(go, w, x_q_t)
+    L, O = go.shape
+    I = w.shape[1]
+    cc = cfg.to_c(go.dtype)
+    nbytes = C.lib().hot_linear_workspace_bytes(L, O, I, ctypes.byref(cc))
+    if nbytes == 0:
+        raise ValueError("unsupported sizes L=%d O=%d I=%d for this configuration" % (L, O, I))
+    ws = _workspace(go.device, nbytes)
+    gx = torch.empty((L, I), dtype=go.dtype, device=go.device) if need_gx else None
+    gw = torch.empty((O, I), dtype=go.dtype, device=go.device) if need_gw else None
+    with torch.cuda.device(go.device):
+        C.check(C.lib().hot_linear_backward(go.data_ptr(), go.stride(0), w.data_ptr(), w.stride(0), x_q_t.data_ptr(),
+                                            scale_x.data_ptr(), L, O, I, ctypes.byref(cc),
+                                            gx.data_ptr() if need_gx else None, I, gw.data_ptr() if need_gw else None, I,
+                                            ws.data_ptr(), ws.numel(), status.data_ptr() if status is not None else None,
+                                            _stream(go)), "hot_linear_backward")
+    return gx, gw

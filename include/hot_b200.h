@@ -1,0 +1,166 @@
+/*
+ * hot_b200 -- C ABI of the B200 (sm_100a) implementation of the HOT linear-layer backward.
+ *
+ * Every entry point takes raw DEVICE pointers, sizes and a CUDA stream, launches its
+ * kernels on that stream and returns without synchronising (except where stated).  No
+ * entry point allocates device memory: the caller owns every buffer, including the
+ * workspaces whose sizes the *_workspace_bytes() queries return.  The return value is a
+ * hot_status; hot_status_string() turns it into text.
+ *
+ * Each declaration names the piece of the reference (sungonuni/HOT) it stands in for,
+ * as file:line within that project.
+ */
+#ifndef HOT_B200_H
+#define HOT_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef void* hot_stream_t; /* a cudaStream_t; NULL is the legacy default stream */
+
+enum hot_status {
+  HOT_OK = 0,
+  HOT_ERR_ARG = 1,         /* null pointer, non-positive size, misaligned pointer or pitch      */
+  HOT_ERR_UNSUPPORTED = 2, /* a size or mode the kernels do not cover (message names it)        */
+  HOT_ERR_CUDA = 3,        /* a CUDA runtime/driver call failed; see hot_last_error()           */
+  HOT_ERR_TIMEOUT = 4,     /* a bounded device-side wait ran out (reported via the status word) */
+  HOT_ERR_WORKSPACE = 5    /* workspace too small                                               */
+};
+
+enum hot_dtype { HOT_F32 = 0, HOT_BF16 = 1, HOT_I32 = 2 };
+enum hot_rounding { HOT_ROUND_NEAREST = 0, HOT_ROUND_STOCH_PHILOX = 1, HOT_ROUND_STOCH_NOISE = 2 };
+enum hot_scale_mode { HOT_SCALE_TENSOR = 0, HOT_SCALE_ROW = 1 };
+enum hot_storage { HOT_STORE_INT8 = 0, HOT_STORE_INT4 = 1 }; /* INT4: two codes per byte, low nibble = even index */
+enum hot_layout { HOT_LAYOUT_NATURAL = 0, HOT_LAYOUT_TRANSPOSED = 1 };
+
+/* How one operand is quantised.  Codes lie in [-(2^(bits-1)-1), 2^(bits-1)-1]. */
+typedef struct hot_quant {
+  int32_t bits;       /* 2..8; HOT_STORE_INT4 needs bits <= 4                                      */
+  int32_t storage;    /* hot_storage                                                             */
+  int32_t rounding;   /* hot_rounding                                                            */
+  int32_t scale_mode; /* hot_scale_mode                                                          */
+  uint64_t seed;      /* Philox key   (HOT_ROUND_STOCH_PHILOX)                                   */
+  uint64_t offset;    /* Philox stream offset: a different value per quantiser call              */
+  const float* noise; /* HOT_ROUND_STOCH_NOISE: uniforms in [0,1), one per code, in the layout   */
+                      /* the quantiser sees (see each function); a code rounds up iff u < frac   */
+} hot_quant_t;
+
+const char* hot_status_string(int status);
+/* Text of the most recent failure on the calling thread ("" if none). */
+const char* hot_last_error(void);
+/* Library ABI version (bumped on any signature change). */
+int hot_abi_version(void);
+
+/*
+ * Fused block-Hadamard transform along the LAST (contiguous) dim + quantisation.
+ *   x      [rows, cols] row-major, pitch ldx elements, dtype HOT_F32 | HOT_BF16
+ *   order  Hadamard block order: 1, 2, 4, ..., 64; cols % max(order, 8) == 0
+ *   codes  HOT_STORE_INT8: [rows, cols] int8, pitch ld_codes bytes
+ *          HOT_STORE_INT4: [rows, cols/2] bytes, pitch ld_codes bytes
+ *   scales [1] (HOT_SCALE_TENSOR) or [rows] (HOT_SCALE_ROW): s = absmax / (2^(bits-1)-1)
+ *   absmax_ws  one 32-bit word of scratch, used in HOT_SCALE_TENSOR mode only
+ * noise / Philox element index: row * cols + col.
+ * Stands in for lowering_matmul_front (utils/hadamard_matmul.py:121-141) followed by
+ * stoch_quantizer / int_quantizer / norm_quantizer (utils/quant_matmul.py:19-37,86-122),
+ * and for fwht_kernel + find_scale_kernel + quant_int4_kernel / quant_int4_per_token_kernel /
+ * quant_int8_kernel (cuda_measure/HLQ_backward_kernel.cu:39-178,282-307).
+ */
+int hot_row_ht_quant(const void* x, int dtype, int64_t rows, int64_t cols, int64_t ldx, int order,
+                     const hot_quant_t* q, void* codes, int64_t ld_codes, float* scales,
+                     uint32_t* absmax_ws, hot_stream_t stream);
+
+/*
+ * Fused block Walsh-Hadamard transform along the FIRST dim with row selection (the
+ * Hadamard low-rank projection; all rows kept = plain Hadamard) + quantisation, written
+ * TRANSPOSED so that the transformed dim becomes the contiguous (contraction) dim.
+ *   x      [rows, cols] row-major, pitch ldx elements; rows % order == 0
+ *   order  n = 2..64 (power of two)
+ *   sel    HOST array of r natural-order row indices of the Sylvester matrix H_n, in
+ *          output order (out row b*r+j = sum_t H_n[sel[j], t] * x[b*n+t, :])
+ *   codes_t [cols, rows*r/n] codes (int8, or packed int4 along the transformed dim),
+ *          pitch ld_codes bytes, a multiple of 16
+ *   scales [1] (HOT_SCALE_TENSOR) or [cols] (HOT_SCALE_ROW: one scale per row of the
+ *          transposed output, i.e. per input column)
+ *   absmax_ws  1 word (TENSOR) or cols words (ROW) of scratch
+ *   logical_layout  layout in which the reference's quantiser sees the tensor, which fixes
+ *          the noise / Philox element index: HOT_LAYOUT_NATURAL [rows*r/n, cols] or
+ *          HOT_LAYOUT_TRANSPOSED [cols, rows*r/n]
+ * Stands in for lowering_matmul_back (utils/hadamard_matmul.py:143-161) with the matrices
+ * of make_hadamard / make_WHT (:57-59,209-226) followed by a quantiser, as used at
+ * utils/quant_matmul.py:189-204 (activation buffer), :269-285 (weight), :300-320 (g_w side
+ * of grad_output); and for the transpose + "first L/2 rows" stand-in at
+ * cuda_measure/HLQ_backward_kernel.cu:536-549,587-611.
+ */
+int hot_col_ht_quant(const void* x, int dtype, int64_t rows, int64_t cols, int64_t ldx, int order,
+                     const int32_t* sel, int r, const hot_quant_t* q, int logical_layout,
+                     void* codes_t, int64_t ld_codes, float* scales, uint32_t* absmax_ws,
+                     hot_stream_t stream);
+
+/*
+ * Integer GEMM on tcgen05 (kind::i8) with fused dequantisation:
+ *   out[m, n] = ((float)(sum_k a[m,k] * b[n,k]) * sa[m or 0]) * sb[n or 0] * post
+ *   a [M, K] and b [N, K]: K contiguous, pitches lda/ldb in BYTES (multiples of 16),
+ *       storage HOT_STORE_INT8 or HOT_STORE_INT4 (K even, packed along K)
+ *   scale_a / scale_b: device floats, [1] or per row ([M] / [N]) when *_per_row != 0
+ *   out: HOT_F32 | HOT_BF16 [M, N] pitch ldo elements, or HOT_I32 for the raw accumulator
+ *   status_word: device word the kernel ORs a non-zero code into when a bounded wait runs
+ *       out (may be NULL); the caller clears and reads it
+ * Stands in for CutlassSgemmNN_int4 / CutlassSgemmNN_int8 + dequantize_cuda_kernel /
+ * dequantize_cuda_per_token_kernel (cuda_measure/HLQ_backward_kernel.cu:181-280,309-450)
+ * and for the float matmuls on integer values at utils/quant_matmul.py:288-290,322-324.
+ */
+int hot_gemm_i8(const void* a, int a_storage, int64_t lda, const void* b, int b_storage, int64_t ldb,
+                int64_t M, int64_t N, int64_t K, const float* scale_a, int scale_a_per_row,
+                const float* scale_b, int scale_b_per_row, float post, void* out, int out_dtype,
+                int64_t ldo, uint32_t* status_word, hot_stream_t stream);
+
+/* Per-layer configuration of the backward pass (scheme gih_gwlr, utils/quant_matmul.py:214-348). */
+typedef struct hot_linear_cfg {
+  int32_t dtype;      /* dtype of grad_out, w, x and of the returned gradients                  */
+  int32_t order_o;    /* Hadamard block order along O (make_hadamard(O): min(16, 2-adic part))  */
+  int32_t order_l;    /* low-rank block order n along tokens                                    */
+  int32_t rank_l;     /* kept rows r (<= n)                                                     */
+  int32_t sel_l[64];  /* the r natural-order row indices                                        */
+  hot_quant_t q_gx;   /* grad_out on the g_x path   (scale_mode ROW = per token)                */
+  hot_quant_t q_w;    /* weight                                                                 */
+  hot_quant_t q_gw;   /* grad_out on the g_w path   (scale_mode ROW = per output channel)       */
+  hot_quant_t q_x;    /* activation buffer                                                      */
+} hot_linear_cfg_t;
+
+/* Bytes of workspace hot_linear_backward / hot_abc_compress need for these sizes. */
+size_t hot_linear_workspace_bytes(int64_t L, int64_t O, int64_t I, const hot_linear_cfg_t* cfg);
+/* Pitch in bytes of the compressed activation buffer [I, L*r/n] for these sizes. */
+int64_t hot_abc_pitch(int64_t L, const hot_linear_cfg_t* cfg);
+
+/*
+ * Activation-buffer compression (forward side): x [L, I] -> x_q_t [I, L*r/n] int8 codes
+ * (pitch hot_abc_pitch) + scale_x [1].  noise layout: HOT_LAYOUT_NATURAL [L*r/n, I].
+ * Stands in for FLinearQ.setup_context (utils/quant_matmul.py:177-212).
+ */
+int hot_abc_compress(const void* x, int64_t L, int64_t I, int64_t ldx, const hot_linear_cfg_t* cfg,
+                     void* x_q_t, float* scale_x, void* workspace, size_t workspace_bytes,
+                     hot_stream_t stream);
+
+/*
+ * The HOT backward of one linear layer:
+ *   grad_x [L, I] = (Q(HT_O(go)) . Q(HT_O(w))) * s_go * s_w / order_o
+ *   grad_w [O, I] = (Q(HLA(go))^T . x_q) * s_gw * s_x / order_l
+ * go [L, O] pitch ldgo, w [O, I] pitch ldw (elements); x_q_t / scale_x from hot_abc_compress.
+ * status_word: device word, non-zero after the call completes if a device-side wait ran out.
+ * Stands in for FLinearQ.backward (utils/quant_matmul.py:214-348) and for backward_cuda
+ * (cuda_measure/HLQ_backward_kernel.cu:457-737).
+ */
+int hot_linear_backward(const void* go, int64_t ldgo, const void* w, int64_t ldw, const void* x_q_t,
+                        const float* scale_x, int64_t L, int64_t O, int64_t I,
+                        const hot_linear_cfg_t* cfg, void* grad_x, int64_t ldgx, void* grad_w,
+                        int64_t ldgw, void* workspace, size_t workspace_bytes, uint32_t* status_word,
+                        hot_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* HOT_B200_H */

@@ -1,0 +1,278 @@
+"""GPU parity tests of the three kernels, called through the C ABI and compared with the CPU
+oracle on the same seeded inputs.  Integer artefacts (codes, accumulators) and scales must be
+bit-exact; dequantised outputs are compared bit-for-bit too where the oracle evaluates the
+same float expression, else to 1e-3 relative Frobenius error (the tolerance the target names).
+"""
+import numpy as np
+import pytest
+import torch
+
+from oracle import hot_oracle as oc
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def ops():
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    from hot_b200 import ops as _ops
+    return _ops
+
+
+def _dev(a, dtype=None):
+    t = torch.from_numpy(np.ascontiguousarray(a)).cuda()
+    return t.to(dtype) if dtype is not None else t
+
+
+def _as_f32(a, dtype):
+    """What the kernel sees: bf16 inputs are rounded to bf16 first, then widened exactly."""
+    t = torch.from_numpy(np.ascontiguousarray(a))
+    return t.to(dtype).to(torch.float32).numpy()
+
+
+def _codes_from(codes_t, storage, n):
+    c = codes_t.cpu().numpy()
+    if storage == "int4":
+        return oc.unpack_int4(c)[..., :n]
+    return c.view(np.int8).astype(np.int32)[..., :n]
+
+
+def _noise_for(rounding, shape, rng, seed, offset):
+    if rounding == "noise":
+        return rng.random(shape, dtype=np.float32)
+    if rounding == "philox":
+        return oc.philox_uniform16(seed, offset, shape)
+    return None
+
+
+ROW_CASES = [
+    # rows, cols, order
+    (37, 768, 16), (5, 192, 32), (64, 1024, 64), (3, 64, 1), (9, 40, 8), (130, 3072, 16), (2, 16384, 16),
+]
+
+
+@pytest.mark.parametrize("rows,cols,order", ROW_CASES)
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("storage,bits", [("int4", 4), ("int8", 8), ("int8", 4)])
+@pytest.mark.parametrize("rounding", ["nearest", "noise", "philox"])
+@pytest.mark.parametrize("scale", ["tensor", "row"])
+def test_row_ht_quant(ops, rows, cols, order, dtype, storage, bits, rounding, scale):
+    rng = np.random.default_rng(rows * 131 + cols + order)
+    x = (rng.standard_normal((rows, cols)) * 1e-3).astype(np.float32)
+    x[rows // 2] *= 25.0
+    seed, offset = 0x1234ABCD5678, 77
+    u = _noise_for(rounding, (rows, cols), rng, seed, offset)
+    q = ops.Quant(bits, storage, rounding, scale, seed, offset, _dev(u) if rounding == "noise" else None)
+    codes, scales = ops.row_ht_quant(_dev(x, dtype), order, q)
+    torch.cuda.synchronize()
+    xh = oc.fwht_last(_as_f32(x, dtype), order)
+    ref_c, ref_s = (oc.quant_rows if scale == "row" else oc.quant_tensor)(xh, bits, u)
+    got_c = _codes_from(codes, storage, cols)
+    assert np.array_equal(np.atleast_1d(ref_s).astype(np.float32).view(np.uint32), scales.cpu().numpy().view(np.uint32))
+    assert np.array_equal(got_c, ref_c), "%d codes differ" % int((got_c != ref_c).sum())
+
+
+def _sel_cases():
+    return [
+        (16, list(range(16))),                         # plain Hadamard (weight side)
+        (16, list(oc.lowrank_preset(16, 8))),          # half16
+        (32, list(oc.wht_selection(6304, 50)[1])),     # the reference's 10 of 32
+        (64, list(oc.wht_selection(12608, 50)[1])),    # 36 of 64
+        (4, list(oc.wht_selection(196, 50)[1])),       # 3 of 4
+        (1, [0]),                                      # identity (odd token counts)
+        (8, list(range(8))),
+    ]
+
+
+@pytest.mark.parametrize("order,sel", _sel_cases())
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("storage,bits", [("int4", 4), ("int8", 8)])
+@pytest.mark.parametrize("rounding,layout", [("nearest", "natural"), ("noise", "natural"), ("noise", "transposed"),
+                                             ("philox", "natural")])
+@pytest.mark.parametrize("scale", ["tensor", "row"])
+def test_col_ht_quant(ops, order, sel, dtype, storage, bits, rounding, layout, scale):
+    nblk = 21 if order <= 16 else 9
+    rows, cols = order * nblk, 200
+    r = len(sel)
+    out_len = nblk * r
+    rng = np.random.default_rng(order * 1000 + r)
+    x = rng.standard_normal((rows, cols)).astype(np.float32)
+    x[:, 7] *= 20.0
+    seed, offset = 99, 3
+    if rounding == "noise":
+        u_t = rng.random((cols, out_len), dtype=np.float32)          # as seen in the stored layout
+        u_dev = _dev(u_t if layout == "transposed" else np.ascontiguousarray(u_t.T))
+    elif rounding == "philox":
+        u_t, u_dev = oc.philox_uniform16(seed, offset, (cols, out_len)), None
+    else:
+        u_t, u_dev = None, None
+    q = ops.Quant(bits, storage, rounding, scale, seed, offset, u_dev)
+    codes, scales, got_len = ops.col_ht_quant(_dev(x, dtype), order, sel, q, layout)
+    torch.cuda.synchronize()
+    assert got_len == out_len
+    y_t = np.ascontiguousarray(oc.hla(_as_f32(x, dtype), order, np.array(sel)).T)   # [cols, out_len]
+    ref_c, ref_s = (oc.quant_rows if scale == "row" else oc.quant_tensor)(y_t, bits, u_t)
+    got_c = _codes_from(codes, storage, out_len)
+    assert np.array_equal(np.atleast_1d(ref_s).astype(np.float32).view(np.uint32), scales.cpu().numpy().view(np.uint32))
+    assert np.array_equal(got_c, ref_c), "%d codes differ" % int((got_c != ref_c).sum())
+
+
+GEMM_CASES = [
+    # M, N, K
+    (128, 128, 128), (200, 96, 320), (37, 48, 96), (1000, 768, 3072), (384, 130, 50), (256, 256, 1970),
+]
+
+
+@pytest.mark.parametrize("M,N,K", GEMM_CASES)
+@pytest.mark.parametrize("a_storage,b_storage", [("int8", "int8"), ("int4", "int4"), ("int4", "int8"), ("int8", "int4")])
+def test_gemm_i8_accumulators_and_dequant(ops, M, N, K, a_storage, b_storage):
+    rng = np.random.default_rng(M + N + K)
+
+    def make(rows, storage):
+        lim = 7 if storage == "int4" else 127
+        c = rng.integers(-lim, lim + 1, size=(rows, K)).astype(np.int32)
+        if storage == "int4":
+            kk = K + (K % 2)
+            cp = np.zeros((rows, kk), np.int32)
+            cp[:, :K] = c
+            packed = oc.pack_int4(cp)
+        else:
+            packed = c.astype(np.int8).view(np.uint8)
+        pitch = (packed.shape[1] + 15) // 16 * 16
+        buf = np.full((rows, pitch), 0x5A, np.uint8)           # junk in the pitch padding must not leak in
+        buf[:, :packed.shape[1]] = packed
+        return c, _dev(buf)
+
+    if (a_storage == "int4" or b_storage == "int4") and K % 2:
+        pytest.skip("packed operands need an even K")
+    a, a_dev = make(M, a_storage)
+    b, b_dev = make(N, b_storage)
+    ref = a.astype(np.int64) @ b.astype(np.int64).T
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    acc = ops.gemm_i8(a_dev, a_storage, b_dev, b_storage, M, N, K, None, None, out_dtype=torch.int32, status=status)
+    sa = (rng.random(M, dtype=np.float32) + 0.5) * 1e-4
+    sb = np.array([3.3e-3], np.float32)
+    out = ops.gemm_i8(a_dev, a_storage, b_dev, b_storage, M, N, K, _dev(sa), _dev(sb), post=1.0 / 16, status=status)
+    out_bf = ops.gemm_i8(a_dev, a_storage, b_dev, b_storage, M, N, K, _dev(sa[:1]), _dev(sb), post=0.25,
+                         out_dtype=torch.bfloat16, status=status)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0, "a bounded device-side wait ran out"
+    assert np.array_equal(acc.cpu().numpy().astype(np.int64), ref)
+    want = ((ref.astype(np.float32) * sa[:, None]) * sb[0]) * np.float32(1.0 / 16)
+    assert np.array_equal(out.cpu().numpy(), want)
+    want_bf = torch.from_numpy(((ref.astype(np.float32) * sa[0]) * sb[0]) * np.float32(0.25)).to(torch.bfloat16)
+    assert torch.equal(out_bf.cpu(), want_bf)
+
+
+def _run_backward(ops, x, w, go, order_l, sel, dtype, *, gx_row=False, gw_row=False, rounding="noise", rng=None,
+                  storage4="int4"):
+    L, I = x.shape
+    O = w.shape[0]
+    n_o = oc.block_order(O)
+    r = len(sel)
+    Lp = L // order_l * r
+    seeds = dict(x=(11, 1), go=(11, 2), w=(11, 3), gw=(11, 4))
+    shapes = dict(x=(Lp, I), go=(L, O), w=(O, I), gw=(O, Lp))
+    us, qs = {}, {}
+    for k in shapes:
+        if rounding == "noise":
+            us[k] = rng.random(shapes[k], dtype=np.float32)
+        elif rounding == "philox":
+            # Philox streams are indexed in the stored layout: transposed for x and w
+            if k in ("x", "w"):
+                us[k] = np.ascontiguousarray(oc.philox_uniform16(*seeds[k], shapes[k][::-1]).T)
+            else:
+                us[k] = oc.philox_uniform16(*seeds[k], shapes[k])
+        else:
+            us[k] = None
+    def mk(k, bits, storage, scale="tensor"):
+        return ops.Quant(bits, storage, rounding, scale, seeds[k][0], seeds[k][1],
+                         _dev(us[k]) if rounding == "noise" else None)
+    cfg = ops.LinearConfig(order_o=n_o, order_l=order_l, sel_l=list(sel),
+                           q_gx=mk("go", 4, storage4, "row" if gx_row else "tensor"), q_w=mk("w", 4, storage4),
+                           q_gw=mk("gw", 8, "int8", "row" if gw_row else "tensor"), q_x=mk("x", 8, "int8"))
+    xd, wd, god = _dev(x, dtype), _dev(w, dtype), _dev(go, dtype)
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    x_q_t, s_x = ops.abc_compress(xd, cfg)
+    gx, gw = ops.linear_backward(god, wd, x_q_t, s_x, cfg, status=status)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    # oracle
+    xf, wf, gof = _as_f32(x, dtype), _as_f32(w, dtype), _as_f32(go, dtype)
+    xq_ref, sx_ref = oc.abc_compress(xf, order_l, np.array(sel), 8, us["x"], "stoch" if rounding != "nearest" else "int")
+    ref = oc.linear_backward(gof, wf, xq_ref, sx_ref, n_o=n_o, n_l=order_l, sel=np.array(sel), u_go=us["go"],
+                             u_w=us["w"], u_gw=us["gw"], gx_per_token=gx_row, gw_per_channel=gw_row,
+                             w_mode="stoch" if rounding != "nearest" else "int")
+    got_xq = x_q_t.cpu().numpy().view(np.int8).astype(np.int32)[:, :Lp].T
+    assert np.array_equal(got_xq, xq_ref)
+    assert np.float32(sx_ref).view(np.uint32) == s_x.cpu().numpy().view(np.uint32)[0]
+    return gx, gw, ref
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("rounding", ["noise", "philox", "nearest"])
+@pytest.mark.parametrize("gx_row,gw_row", [(False, False), (True, True)])
+@pytest.mark.parametrize("preset", ["half16", "ref32"])
+def test_linear_backward_vs_oracle(ops, dtype, rounding, gx_row, gw_row, preset):
+    rng = np.random.default_rng(5)
+    L, O, I = 32 * 13, 384, 136
+    order_l, sel = (16, oc.lowrank_preset(16, 8)) if preset == "half16" else (32, oc.wht_selection(6304, 50)[1])
+    x = rng.standard_normal((L, I)).astype(np.float32)
+    x[:, 5] *= 20.0
+    w = ((rng.random((O, I)) * 2 - 1) / np.sqrt(I)).astype(np.float32)
+    go = (rng.standard_normal((L, O)) * 1e-3).astype(np.float32)
+    go[17] *= 30.0
+    gx, gw, ref = _run_backward(ops, x, w, go, order_l, sel, dtype, gx_row=gx_row, gw_row=gw_row, rounding=rounding,
+                                rng=rng)
+    for got, name in ((gx, "grad_input"), (gw, "grad_w")):
+        want = ref[name]
+        g = got.float().cpu().numpy()
+        if dtype == torch.float32:
+            assert np.array_equal(g, want), "%s: %d of %d values differ" % (name, (g != want).sum(), g.size)
+        else:
+            rel = np.linalg.norm(g - want) / np.linalg.norm(want)
+            assert rel < 4e-3, (name, rel)     # bf16 output rounding: 2^-9 per element
+
+
+@pytest.mark.parametrize("tag", ["lr_ref", "lr_half16"])
+def test_linear_backward_vs_reference_golden(ops, golden, tag):
+    """Against outputs of the unmodified reference (FLinearQ forward context + backward with
+    explicit rounding noise).  The reference's transforms are BLAS matmuls, so a transformed
+    value can differ in the last ulp and flip a code: the comparison is the 1e-3 relative
+    Frobenius bound on the dequantised gradients."""
+    g = golden("flinearq_" + tag)
+    n_l, sel = oc.selection_from_matrix(g["p"])
+    x, w, go = g["x"], g["w"], g["go"]
+    L, I = x.shape
+    O = w.shape[0]
+    Lp = L // n_l * len(sel)
+    q = lambda bits, storage, u: ops.Quant(bits, storage, "noise", "tensor", 0, 0, _dev(u))
+    cfg = ops.LinearConfig(order_o=oc.block_order(O), order_l=n_l, sel_l=list(sel), q_gx=q(4, "int4", g["u_go"]),
+                           q_w=q(4, "int4", g["u_w"]), q_gw=q(8, "int8", g["u_gw"]), q_x=q(8, "int8", g["u_x"]))
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    x_q_t, s_x = ops.abc_compress(_dev(x), cfg)
+    gx, gw = ops.linear_backward(_dev(go), _dev(w), x_q_t, s_x, cfg, status=status)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    got_xq = x_q_t.cpu().numpy().view(np.int8).astype(np.int32)[:, :Lp].T
+    assert np.mean(got_xq != g["x_q"].astype(np.int32)) < 1e-3
+    np.testing.assert_allclose(s_x.cpu().numpy()[0], g["scale_x"], rtol=1e-6)
+    for got, name in ((gx, "grad_input"), (gw, "grad_w")):
+        rel = np.linalg.norm(got.cpu().numpy() - g[name]) / np.linalg.norm(g[name])
+        assert rel < 1e-3, (name, rel)
+
+
+def test_errors_are_reported(ops):
+    x = torch.zeros((4, 24), device="cuda")
+    with pytest.raises(RuntimeError, match="multiple of 8"):
+        ops.row_ht_quant(x[:, :20].contiguous(), 4, ops.Quant(4, "int4"))
+    with pytest.raises(RuntimeError, match="INT4 storage needs bits"):
+        ops.row_ht_quant(x, 8, ops.Quant(8, "int4"))
+    with pytest.raises(RuntimeError, match="CUDA tensors only"):
+        ops.row_ht_quant(x.cpu(), 8, ops.Quant(8, "int8"))
+    with pytest.raises(RuntimeError, match="not a multiple of order"):
+        ops.col_ht_quant(torch.zeros((10, 8), device="cuda"), 4, [0, 1], ops.Quant(8, "int8"))
+    # empty input is a no-op
+    codes, scales = ops.row_ht_quant(torch.zeros((0, 64), device="cuda"), 16, ops.Quant(8, "int8", scale="row"))
+    assert codes.shape == (0, 64)
