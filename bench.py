@@ -1,0 +1,451 @@
+#!/usr/bin/env python
+"""Benchmark of the HOT linear-layer backward on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl hot|reference]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \
+        --master-port P bench.py --gpus N --steps K --warmup W
+
+Workload ("vit_b16_backward_48_linears_12608_tokens"): one step is the HOT backward of all 48
+block linears of ViT-B/16 (12 x {qkv 768->2304, proj 768->768, fc1 768->3072, fc2 3072->768})
+at batch 64 = 12,608 tokens per GPU, bf16 tensors, seeded synthetic data: weights with the
+nn.Linear default init, grad_out ~ N(0, 1e-3), activations ~ N(0, 1) compressed ahead of time
+(the activation buffer is produced in forward, not in backward).  Every layer has its own
+grad_out / weight / buffer (2.1 GB per GPU in total, far more than the 126 MB L2), so no layer
+finds its inputs in cache.  At N > 1 every rank runs the same step on its own tokens and the
+weight gradients are summed over ranks by NCCL, one bucket per transformer block, overlapped
+with the remaining backward ("weak" scaling).
+
+The metric is effective TOPS = 4*L*O*I summed over the layers / step time (the FLOPs of the
+two full-precision GEMMs the backward replaces), whole job.  ``e2e`` is the same metric
+through the public plugin call ``HLQ_backward.backward(Go, W, X, ...)`` with Go and X starting
+in pinned host memory and both gradients read back to the host.  One printed JSON line.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+LAYERS = (("qkv", 768, 2304), ("proj", 768, 768), ("fc1", 768, 3072), ("fc2", 3072, 768))
+METRIC, UNIT = "hot_backward_effective_tops", "TOPS"
+WORKLOAD = "vit_b16_backward_48_linears_12608_tokens"
+
+
+def parse():
+    p = argparse.ArgumentParser()
+    p.add_argument("--gpus", type=int, default=1)
+    p.add_argument("--steps", type=int, default=20)
+    p.add_argument("--warmup", type=int, default=3)
+    p.add_argument("--impl", default="hot", choices=["hot", "reference"])
+    p.add_argument("--tokens", type=int, default=12608)
+    p.add_argument("--blocks", type=int, default=12)
+    p.add_argument("--dtype", default="bf16", choices=["bf16", "fp32"])
+    p.add_argument("--e2e-steps", type=int, default=2)
+    p.add_argument("--no-cpu-baseline", action="store_true")
+    p.add_argument("--no-kernels", action="store_true", help="skip the per-kernel roofline legs")
+    return p.parse_args()
+
+
+def step_flops(tokens: int, blocks: int) -> float:
+    return float(sum(4 * tokens * o * i for _, i, o in LAYERS) * blocks)
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        d = json.load(open(path))
+        return dict(hbm=float(d["hbm_gbs"]), bf16=float(d["bf16_tflops"]), bf16_sustained=float(d["bf16_tflops_sustained"]),
+                    source="measured")
+    return dict(hbm=6650.0, bf16=1590.0, bf16_sustained=1400.0, source="fallback")
+
+
+# ---------------------------------------------------------------------------------------------
+# clocks
+# ---------------------------------------------------------------------------------------------
+class ClockSampler:
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.proc = None
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(index), "--query-gpu=" + self.FIELDS,
+                                          "--format=csv,noheader,nounits", "-lms", "100"], stdout=subprocess.PIPE,
+                                         stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            pass
+
+    def stop(self):
+        if self.proc is None:
+            return None
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            out, _ = self.proc.communicate()
+        sm, mx, reasons = [], 0.0, set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for line in out.splitlines():
+            f = [v.strip() for v in line.split(",")]
+            if len(f) < 7:
+                continue
+            try:
+                sm.append(float(f[0]))
+                mx = max(mx, float(f[1]))
+            except ValueError:
+                continue
+            for n, v in zip(names, f[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        if not sm:
+            return None
+        busy = [v for v in sm if v > 0.5 * max(sm)] or sm
+        return {"sm_mhz": statistics.median(busy), "sm_max_mhz": mx, "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# ---------------------------------------------------------------------------------------------
+# the hot arm
+# ---------------------------------------------------------------------------------------------
+def build_layers(ops, tokens, blocks, dtype, device, rank):
+    """Per block and layer: weight, grad_out, compressed activation, config."""
+    from hot_b200.hadamard_matmul import biggest_power2_factor_max16, lowrank_selection
+    gw_seed = torch.Generator(device=device).manual_seed(0)            # same weights on every rank
+    gd = torch.Generator(device=device).manual_seed(1000 + rank)       # own data per rank
+    order_l, sel = lowrank_selection(tokens, "half16")
+    layers = []
+    call = 0
+    for b in range(blocks):
+        blk = []
+        for name, i_f, o_f in LAYERS:
+            bound = 1.0 / (i_f ** 0.5)                                 # kaiming_uniform(a=sqrt(5)) == U(-1/sqrt(in), +)
+            w = ((torch.rand((o_f, i_f), device=device, generator=gw_seed) * 2 - 1) * bound).to(dtype)
+            go = (torch.randn((tokens, o_f), device=device, generator=gd) * 1e-3).to(dtype)
+            x = torch.randn((tokens, i_f), device=device, generator=gd).to(dtype)
+            call += 4
+            cfg = ops.LinearConfig(order_o=biggest_power2_factor_max16(o_f), order_l=order_l, sel_l=sel,
+                                   q_gx=ops.Quant(4, "int4", "philox", "tensor", 0, call + 1),
+                                   q_w=ops.Quant(4, "int4", "philox", "tensor", 0, call + 2),
+                                   q_gw=ops.Quant(8, "int8", "philox", "tensor", 0, call + 3),
+                                   q_x=ops.Quant(8, "int8", "philox", "tensor", 0, call + 4))
+            x_q_t, s_x = ops.abc_compress(x, cfg)
+            del x
+            blk.append(dict(name=name, w=w, go=go, x_q_t=x_q_t, s_x=s_x, cfg=cfg, I=i_f, O=o_f))
+        layers.append(blk)
+    torch.cuda.synchronize(device)
+    return layers
+
+
+def run_hot(a):
+    import torch.distributed as dist
+    from hot_b200 import ops
+    rank = int(os.environ.get("RANK", 0))
+    world = int(os.environ.get("WORLD_SIZE", 1))
+    local = int(os.environ.get("LOCAL_RANK", 0))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the HOT kernels have no CPU path")
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    dtype = torch.bfloat16 if a.dtype == "bf16" else torch.float32
+    pk = peaks()
+    layers = build_layers(ops, a.tokens, a.blocks, dtype, device, rank)
+    status = torch.zeros(1, dtype=torch.int32, device=device)
+    # gradient buffers: grad_x is consumed by the layer below (one reusable buffer per width);
+    # grad_w lands in one flat bucket per block, the unit of the all-reduce
+    gx_buf = {i_f: torch.empty((a.tokens, i_f), dtype=dtype, device=device) for _, i_f, _ in LAYERS}
+    bucket_elems = sum(i * o for _, i, o in LAYERS)
+    buckets = [torch.empty((bucket_elems,), dtype=dtype, device=device) for _ in range(a.blocks)]
+    gw_views = []
+    for b in range(a.blocks):
+        off, views = 0, []
+        for _, i_f, o_f in LAYERS:
+            views.append(buckets[b][off:off + i_f * o_f].view(o_f, i_f))
+            off += i_f * o_f
+        gw_views.append(views)
+
+    def block_backward(b):
+        for li in reversed(range(len(LAYERS))):
+            l = layers[b][li]
+            ops.linear_backward(l["go"], l["w"], l["x_q_t"], l["s_x"], l["cfg"], status=status,
+                                gx_out=gx_buf[l["I"]], gw_out=gw_views[b][li])
+
+    # one CUDA graph per transformer block: launch overhead off the critical path, and the
+    # all-reduce of a block's bucket can be enqueued between graph launches
+    side = torch.cuda.Stream(device)
+    graphs = []
+    with torch.cuda.stream(side):
+        for b in range(a.blocks):
+            block_backward(b)                       # warm-up outside capture (lazy init, attributes)
+        torch.cuda.synchronize(device)
+        for b in range(a.blocks):
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=side):
+                block_backward(b)
+            graphs.append(g)
+    torch.cuda.synchronize(device)
+
+    def step():
+        works = []
+        for b in reversed(range(a.blocks)):
+            graphs[b].replay()
+            if world > 1:
+                works.append(dist.all_reduce(buckets[b], op=dist.ReduceOp.SUM, async_op=True))
+        for w in works:
+            w.wait()
+
+    def sync_all():
+        torch.cuda.synchronize(device)
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize(device)
+
+    for _ in range(max(a.warmup, 3)):
+        step()
+    sync_all()
+    sampler = ClockSampler(local) if rank == 0 else None
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(a.steps):
+        step()
+    e1.record()
+    sync_all()
+    ms = torch.tensor([e0.elapsed_time(e1)], device=device)
+    if world > 1:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    clocks = sampler.stop() if sampler else None
+    ms_step = float(ms.item()) / a.steps
+    if int(status.item()) != 0:
+        raise SystemExit("a bounded device-side wait ran out during the benchmark (status %d)" % int(status.item()))
+    flops = step_flops(a.tokens, a.blocks)
+    value = flops * world / (ms_step * 1e-3) / 1e12
+    n_layers = a.blocks * len(LAYERS)
+
+    out = {"metric": METRIC, "value": round(value, 2), "unit": UNIT, "n_gpus": world, "steps": a.steps,
+           "warmup": max(a.warmup, 3), "ms_per_step": round(ms_step, 4), "ms_per_layer": round(ms_step / n_layers, 5),
+           "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8/int4 codes, int32 accumulate",
+           "data": "synthetic", "gpu_launches": n_layers * 8 * a.steps,
+           "config": {"workload": WORKLOAD, "tokens_per_gpu": a.tokens, "layers": n_layers, "tensor_dtype": a.dtype,
+                      "hadamard_order": 16, "low_rank": "8 of 16 (lowest sequency)", "g_x": "INT4 x INT4, per-tensor, Philox stochastic",
+                      "g_w": "INT8 x INT8, per-tensor, Philox stochastic", "activation_buffer": "compressed in forward (not timed)",
+                      "cache": "inputs 2.1 GB per GPU, distinct per layer (> 126 MB L2)",
+                      "parallelism": "dp%d, grad_w all-reduce (NCCL) per block" % world if world > 1 else "single GPU"}}
+    if clocks:
+        out["clocks"] = clocks
+    if rank == 0 and world == 1:
+        if not a.no_kernels:
+            out["kernels"], out["roofline"], out["fp_backward_bf16_cublas"] = kernel_legs(ops, layers, a, dtype, device, pk, status)
+        out["e2e"] = e2e_leg(layers, a, dtype, device, flops)
+        if not a.no_cpu_baseline:
+            out["cpu_baseline"] = cpu_baseline(threads=1)
+    elif rank == 0:
+        out["e2e"] = None
+    if rank == 0:
+        print(json.dumps(out), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def _graph_time(fn, iters, device, warm=3):
+    """Average device time of fn() in microseconds: captured once per distinct call, replayed."""
+    side = torch.cuda.Stream(device)
+    with torch.cuda.stream(side):
+        fn(0)
+        torch.cuda.synchronize(device)
+        gs = []
+        for i in range(iters):
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=side):
+                fn(i)
+            gs.append(g)
+    torch.cuda.synchronize(device)
+    for _ in range(warm):
+        for g in gs:
+            g.replay()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize(device)
+    e0.record()
+    for g in gs:
+        g.replay()
+    e1.record()
+    torch.cuda.synchronize(device)
+    return e0.elapsed_time(e1) * 1e3 / iters
+
+
+def kernel_legs(ops, layers, a, dtype, device, pk, status):
+    """Per-kernel device times on the fc1 layers (one distinct layer per launch, so inputs come
+    from HBM), the roofline of the kernel with the largest share, and the bf16 cuBLAS backward
+    of the same layer for comparison."""
+    fc1 = [blk[2] for blk in layers]
+    n = len(fc1)
+    L, O, I = a.tokens, fc1[0]["O"], fc1[0]["I"]
+    esz = 2 if dtype == torch.bfloat16 else 4
+    cfg = fc1[0]["cfg"]
+    lp = cfg.out_len(L)
+    kern = {}
+    # kernel A: Hadamard along O + INT4, per-tensor (two launches: abs-max, quantise)
+    t = _graph_time(lambda i: ops.row_ht_quant(fc1[i % n]["go"], 16, cfg.q_gx), n, device)
+    kern["row_ht_quant_int4_tensor"] = dict(us=t, bytes=L * O * esz + L * O // 2 + 4, bound="hbm")
+    q_row = ops.Quant(4, "int4", "philox", "row", 0, 7)
+    t = _graph_time(lambda i: ops.row_ht_quant(fc1[i % n]["go"], 16, q_row), n, device)
+    kern["row_ht_quant_int4_token"] = dict(us=t, bytes=L * O * esz + L * O // 2 + 4 * L, bound="hbm")
+    q_near = ops.Quant(8, "int8", "nearest", "row", 0, 7)
+    t = _graph_time(lambda i: ops.row_ht_quant(fc1[i % n]["go"], 16, q_near), n, device)
+    kern["row_ht_quant_int8_token_nearest"] = dict(us=t, bytes=L * O * esz + L * O + 4 * L, bound="hbm")
+    # kernel B: low-rank along tokens + INT8, transposed out
+    t = _graph_time(lambda i: ops.col_ht_quant(fc1[i % n]["go"], cfg.order_l, cfg.sel_l, cfg.q_gw, "transposed"), n, device)
+    kern["col_hla_quant_int8_go"] = dict(us=t, bytes=L * O * esz + lp * O, bound="hbm")
+    t = _graph_time(lambda i: ops.col_ht_quant(fc1[i % n]["w"], 16, list(range(16)), cfg.q_w, "natural"), n, device)
+    kern["col_ht_quant_int4_w"] = dict(us=t, bytes=O * I * esz + O * I // 2, bound="hbm")
+    # kernel C: the two integer GEMMs
+    q_go, s_go = ops.row_ht_quant(fc1[0]["go"], 16, cfg.q_gx)
+    q_w, s_w, _ = ops.col_ht_quant(fc1[0]["w"], 16, list(range(16)), cfg.q_w, "natural")
+    q_gw, s_gw, _ = ops.col_ht_quant(fc1[0]["go"], cfg.order_l, cfg.sel_l, cfg.q_gw, "transposed")
+    t = _graph_time(lambda i: ops.gemm_i8(q_go, "int4", q_w, "int4", L, I, O, s_go, s_w, 1 / 16, dtype, status), 8, device)
+    kern["gemm_gx_int4"] = dict(us=t, ops=2 * L * I * O, bound="tensor")
+    t = _graph_time(lambda i: ops.gemm_i8(q_gw, "int8", fc1[0]["x_q_t"], "int8", O, I, lp, s_gw, fc1[0]["s_x"], 1 / 16, dtype, status), 8, device)
+    kern["gemm_gw_int8"] = dict(us=t, ops=2 * O * I * lp, bound="tensor")
+    t_layer = _graph_time(lambda i: ops.linear_backward(fc1[i % n]["go"], fc1[i % n]["w"], fc1[i % n]["x_q_t"], fc1[i % n]["s_x"], cfg, status=status), n, device)
+    xs = [torch.randn((L, I), device=device).to(dtype) for _ in range(2)]
+    t_fp = _graph_time(lambda i: (torch.matmul(fc1[i % n]["go"], fc1[i % n]["w"]), torch.matmul(fc1[i % n]["go"].t(), xs[i % 2])), n, device)
+    int8_peak = 2.0 * pk["bf16"]   # no measured INT8 figure: nominal INT8 is twice the bf16 rate
+    for k, v in kern.items():
+        v["us"] = round(v["us"], 2)
+        if v["bound"] == "hbm":
+            v["achieved"], v["unit"], v["peak"] = round(v["bytes"] / v["us"] / 1e3, 1), "GB/s", pk["hbm"]
+        else:
+            v["achieved"], v["unit"], v["peak"] = round(v["ops"] / v["us"] / 1e6, 1), "TOP/s", int8_peak
+        v["frac"] = round(v["achieved"] / v["peak"], 4)
+    in_layer = ["row_ht_quant_int4_tensor", "col_hla_quant_int8_go", "col_ht_quant_int4_w", "gemm_gx_int4", "gemm_gw_int8"]
+    top = max(in_layer, key=lambda k: kern[k]["us"])
+    tk = kern[top]
+    roof = {"kernel": top, "bound": tk["bound"], "achieved": tk["achieved"], "peak": tk["peak"], "unit": tk["unit"],
+            "frac": tk["frac"], "traffic": None, "launch_us": tk["us"],
+            "peak_source": ("%s hbm_gbs" % pk["source"]) if tk["bound"] == "hbm" else
+                           ("2 x %s bf16_tflops (no measured INT8 peak; nominal INT8:bf16 = 2)" % pk["source"]),
+            "share_of_fc1_layer": round(tk["us"] / t_layer, 3)}
+    fp = {"fc1_hot_us": round(t_layer, 2), "fc1_bf16_matmul_us": round(t_fp, 2), "speedup": round(t_fp / t_layer, 3),
+          "dtype": a.dtype}
+    return kern, roof, fp
+
+
+def e2e_leg(layers, a, dtype, device, flops):
+    """The same step through HLQ_backward.backward with Go and X in pinned host memory and both
+    gradients copied back, every layer, every step."""
+    import HLQ_backward
+    shapes = {}
+    for name, i_f, o_f in LAYERS:
+        shapes[name] = dict(go=torch.empty((a.tokens, o_f), dtype=dtype).pin_memory(),
+                            x=torch.empty((a.tokens, i_f), dtype=dtype).pin_memory(),
+                            gx=torch.empty((a.tokens, i_f), dtype=dtype).pin_memory(),
+                            gw=torch.empty((o_f, i_f), dtype=dtype).pin_memory())
+        shapes[name]["go"].normal_(0, 1e-3)
+        shapes[name]["x"].normal_(0, 1)
+    h2d = d2h = 0
+    for name, i_f, o_f in LAYERS:
+        h2d += (a.tokens * o_f + a.tokens * i_f) * shapes[name]["go"].element_size()
+        d2h += (a.tokens * i_f + o_f * i_f) * shapes[name]["go"].element_size()
+    h2d *= a.blocks
+    d2h *= a.blocks
+
+    def step():
+        for b in reversed(range(a.blocks)):
+            for li in reversed(range(len(LAYERS))):
+                l = layers[b][li]
+                s = shapes[l["name"]]
+                go = s["go"].to(device, non_blocking=True)
+                x = s["x"].to(device, non_blocking=True)
+                gx, gw, _ = HLQ_backward.backward(go, l["w"], x, 0, 0, 16, False)
+                s["gx"].copy_(gx, non_blocking=True)
+                s["gw"].copy_(gw, non_blocking=True)
+        torch.cuda.synchronize(device)
+
+    step()
+    t0 = time.perf_counter()
+    for _ in range(a.e2e_steps):
+        step()
+    dt = (time.perf_counter() - t0) / a.e2e_steps
+    return {"value": round(flops / dt / 1e12, 3), "unit": UNIT, "ms_per_step": round(dt * 1e3, 3),
+            "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h), "api": "HLQ_backward.backward(Go, W, X, 0, 0, 16, False)"}
+
+
+# ---------------------------------------------------------------------------------------------
+# the CPU arm: the oracle's restatement of the reference fake-quant path
+# ---------------------------------------------------------------------------------------------
+def cpu_layer_seconds(tokens, i_f, o_f, seed=0):
+    import numpy as np
+    from oracle import hot_oracle as oc
+    rng = np.random.default_rng(seed)
+    x = rng.standard_normal((tokens, i_f)).astype(np.float32)
+    w = ((rng.random((o_f, i_f)) * 2 - 1) / np.sqrt(i_f)).astype(np.float32)
+    go = (rng.standard_normal((tokens, o_f)) * 1e-3).astype(np.float32)
+    sel = oc.lowrank_preset(16, 8)
+    lp = tokens // 16 * 8
+    u = [rng.random(s, dtype=np.float32) for s in ((lp, i_f), (tokens, o_f), (o_f, i_f), (o_f, lp))]
+    x_q, s_x = oc.abc_compress(x, 16, sel, 8, u[0])                     # forward side, not timed
+    t0 = time.perf_counter()
+    oc.linear_backward(go, w, x_q, s_x, n_o=oc.block_order(o_f), n_l=16, sel=sel, u_go=u[1], u_w=u[2], u_gw=u[3],
+                       exact_matmul=False)
+    return time.perf_counter() - t0
+
+
+def cpu_baseline(threads):
+    """Oracle port of the reference's fake-quant backward on a bounded sample: one fc1 layer
+    (768 -> 3072) at 6,304 tokens, float32."""
+    from threadpoolctl import threadpool_limits
+    tokens, (name, i_f, o_f) = 6304, LAYERS[2]
+    with threadpool_limits(limits=threads):
+        cpu_layer_seconds(256, i_f, o_f)
+        sec = cpu_layer_seconds(tokens, i_f, o_f)
+    return {"value": round(4.0 * tokens * i_f * o_f / sec / 1e12, 5), "unit": UNIT, "cores": threads, "kind": "port",
+            "seconds": round(sec, 3),
+            "sample": "one fc1 (768->3072) backward at 6304 tokens, fp32, oracle/hot_oracle.py linear_backward "
+                      "(numpy restatement of utils/quant_matmul.py:214-348 with float32 BLAS matmuls as the reference runs)"}
+
+
+def run_reference(a):
+    """The reference arm: the CPU restatement of the reference's own implementation of the path,
+    all host threads, on a bounded sample of the workload; rank 0 only."""
+    if int(os.environ.get("RANK", 0)) != 0:
+        return
+    threads = os.cpu_count() or 1
+    tokens = 1600                                     # about 1/8 of the workload's tokens per layer shape
+    for _, i_f, o_f in LAYERS:
+        cpu_layer_seconds(64, i_f, o_f)
+    for _ in range(max(a.warmup, 0)):
+        for _, i_f, o_f in LAYERS:
+            cpu_layer_seconds(tokens, i_f, o_f)
+    t0 = time.perf_counter()
+    for _ in range(a.steps):
+        for _, i_f, o_f in LAYERS:
+            cpu_layer_seconds(tokens, i_f, o_f)
+    sec = (time.perf_counter() - t0) / a.steps
+    flops = float(sum(4 * tokens * o * i for _, i, o in LAYERS))
+    value = round(flops / sec / 1e12, 5)
+    sample = "per step: one layer of each of the 4 shapes at 1600 tokens (about 1/8 of the tokens, 1/12 of the blocks), fp32"
+    print(json.dumps({"impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": a.gpus,
+                      "steps": a.steps, "warmup": a.warmup, "ms_per_step": round(sec * 1e3, 3), "higher_is_better": True,
+                      "scaling": "weak", "vs_baseline": None, "dtype": "f32 holding integer codes", "data": "synthetic",
+                      "config": {"workload": WORKLOAD, "sample": sample},
+                      "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample},
+                      "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}), flush=True)
+
+
+if __name__ == "__main__":
+    args = parse()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_hot(args)

@@ -185,8 +185,11 @@ def _workspace(device: torch.device, nbytes: int) -> torch.Tensor:
 
 
 def linear_backward(go: torch.Tensor, w: torch.Tensor, x_q_t: torch.Tensor, scale_x: torch.Tensor, cfg: LinearConfig,
-                    need_gx: bool = True, need_gw: bool = True, status: Optional[torch.Tensor] = None):
-    """HOT backward of one linear layer: returns (grad_x [L, I] or None, grad_w [O, I] or None)."""
+                    need_gx: bool = True, need_gw: bool = True, status: Optional[torch.Tensor] = None,
+                    gx_out: Optional[torch.Tensor] = None, gw_out: Optional[torch.Tensor] = None):
+    """HOT backward of one linear layer: returns (grad_x [L, I] or None, grad_w [O, I] or None).
+    ``gx_out`` / ``gw_out`` are optional preallocated row-major destinations (e.g. a slice of a
+    gradient bucket)."""
     _require_cuda(go, w, x_q_t)
     L, O = go.shape
     I = w.shape[1]
@@ -195,12 +198,16 @@ def linear_backward(go: torch.Tensor, w: torch.Tensor, x_q_t: torch.Tensor, scal
     if nbytes == 0:
         raise ValueError("unsupported sizes L=%d O=%d I=%d for this configuration" % (L, O, I))
     ws = _workspace(go.device, nbytes)
-    gx = torch.empty((L, I), dtype=go.dtype, device=go.device) if need_gx else None
-    gw = torch.empty((O, I), dtype=go.dtype, device=go.device) if need_gw else None
+    gx = (gx_out if gx_out is not None else torch.empty((L, I), dtype=go.dtype, device=go.device)) if need_gx else None
+    gw = (gw_out if gw_out is not None else torch.empty((O, I), dtype=go.dtype, device=go.device)) if need_gw else None
+    for t, shape in ((gx, (L, I)), (gw, (O, I))):
+        if t is not None and (tuple(t.shape) != shape or t.dtype != go.dtype or t.stride(1) != 1):
+            raise ValueError("gradient buffer must be %s %s with a contiguous last dim" % (shape, go.dtype))
     with torch.cuda.device(go.device):
         C.check(C.lib().hot_linear_backward(go.data_ptr(), go.stride(0), w.data_ptr(), w.stride(0), x_q_t.data_ptr(),
                                             scale_x.data_ptr(), L, O, I, ctypes.byref(cc),
-                                            gx.data_ptr() if need_gx else None, I, gw.data_ptr() if need_gw else None, I,
+                                            gx.data_ptr() if need_gx else None, gx.stride(0) if need_gx else I,
+                                            gw.data_ptr() if need_gw else None, gw.stride(0) if need_gw else I,
                                             ws.data_ptr(), ws.numel(), status.data_ptr() if status is not None else None,
                                             _stream(go)), "hot_linear_backward")
     return gx, gw

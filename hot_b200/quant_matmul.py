@@ -1,0 +1,302 @@
+"""The HOT layer: quantiser callables, the ``FLinearQ`` autograd function and the ``HQ_Linear``
+module, with the public names, argument meaning and error behaviour of the reference's
+``utils/quant_matmul.py`` -- and CUDA kernels underneath instead of fake-quant float ops.
+
+What runs natively is the scheme the reference trains with: ``transform_scheme = "gih_gwlr"``
+with all four transforms on (main.sh:13-25): Hadamard + INT4 for grad_input, Hadamard
+low-rank + INT8 for grad_weight, the compressed activation buffer saved in forward.  Any
+other combination of flags raises; nothing falls back to float emulation.
+"""
+from __future__ import annotations
+
+import sys
+from typing import Optional
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+from torch import Tensor
+from torch.autograd.function import Function
+
+from . import ops
+from .hadamard_matmul import (Transform_Dict, biggest_power2_factor, biggest_power2_factor_max16, lowrank_selection,
+                              make_hadamard, selection_from_matrix)
+
+
+def _args():
+    """The configuration module: a host program's own top-level ``args`` if it has one (the
+    reference's scripts do), else ``hot_b200.args``."""
+    mod = sys.modules.get("args")
+    if mod is not None and hasattr(mod, "transform_scheme"):
+        return mod
+    from . import args as own
+    return own
+
+
+TD = Transform_Dict()
+_philox_calls = 0
+
+
+def _next_offset() -> int:
+    """A fresh Philox stream offset per quantiser call, so no two calls share random bits."""
+    global _philox_calls
+    _philox_calls += 1
+    return _philox_calls
+
+
+def _seed() -> int:
+    return int(getattr(_args(), "SEED", 0) or 0)
+
+
+# ---------------------------------------------------------------------------------------------
+# quantiser callables: f(x, quantBits, is_batched) -> (x_int as float tensor, scale)
+# (utils/quant_matmul.py:19-37, 86-122, 160-166).  No transform is applied (block order 1).
+# ---------------------------------------------------------------------------------------------
+def _quantise_2d(x: Tensor, bits: int, rounding: str, scale: str):
+    x2 = x if x.dim() == 2 else x.reshape(-1, x.shape[-1])
+    if not x2.is_contiguous():
+        x2 = x2.contiguous()
+    pad = (-x2.shape[1]) % 8
+    if pad:  # the kernels work on vectors of 8; zero columns change neither abs-max nor codes
+        x2 = F.pad(x2, (0, pad))
+    q = ops.Quant(bits, "int8", rounding, scale, _seed(), _next_offset())
+    codes, scales = ops.row_ht_quant(x2, 1, q)
+    codes = codes.view(torch.int8)[:, :x2.shape[1] - pad].to(x.dtype).reshape(x.shape)
+    return codes, scales
+
+
+def _no_batched(name: str, is_batched: bool) -> None:
+    if is_batched:
+        raise NotImplementedError("%s: per-sample (3-D, vmap) scales are not built; flatten tokens to 2-D" % name)
+
+
+def stoch_quantizer(x: Tensor, quantBits: int, is_batched: bool = False):
+    """Per-tensor abs-max scale, stochastic rounding (utils/quant_matmul.py:86-106)."""
+    _no_batched("stoch_quantizer", is_batched)
+    codes, s = _quantise_2d(x, quantBits, "philox", "tensor")
+    return codes, s[0]
+
+
+def int_quantizer(x: Tensor, quantBits: int, is_batched: bool = False):
+    """Per-tensor abs-max scale, round half to even (utils/quant_matmul.py:108-122)."""
+    _no_batched("int_quantizer", is_batched)
+    codes, s = _quantise_2d(x, quantBits, "nearest", "tensor")
+    return codes, s[0]
+
+
+def norm_quantizer(x: Tensor, quantBits: int, is_batched: bool = False):
+    """Per-row abs-max scale, stochastic rounding; returns the DEQUANTISED tensor and the scale
+    1.0, as the reference does (utils/quant_matmul.py:19-37)."""
+    _no_batched("norm_quantizer", is_batched)
+    if x.dim() != 2:
+        raise NotImplementedError("norm_quantizer takes a 2-D tensor")
+    codes, s = _quantise_2d(x, quantBits, "philox", "row")
+    return codes * s.to(x.dtype).unsqueeze(1), 1.
+
+
+quant_scheme_dict = {
+    "int_quantizer": int_quantizer,
+    "stoch_quantizer": stoch_quantizer,
+    "norm_quantizer": norm_quantizer,
+}
+
+
+# ---------------------------------------------------------------------------------------------
+# configuration -> kernel modes
+# ---------------------------------------------------------------------------------------------
+def _storage(bits: int) -> str:
+    return "int4" if bits <= 4 else "int8"
+
+
+def _operand(kind: str, scheme, bits: int, what: str, row_ok: bool) -> ops.Quant:
+    if scheme == "stoch":
+        rounding, scale = "philox", "tensor"
+    elif scheme == "int":
+        rounding, scale = "nearest", "tensor"
+    elif scheme == "nq" and row_ok:
+        rounding, scale = "philox", "row"
+    elif scheme in ("sawb", "luq", "no", False):
+        raise NotImplementedError("%s rounding scheme %r is not built on the native path" % (what, scheme))
+    else:
+        raise Exception("%s rounding scheme not implemented: %s" % (what, scheme))
+    if not 2 <= int(bits) <= 8:
+        raise ValueError("%s: quantBits %r outside [2, 8]" % (what, bits))
+    return ops.Quant(int(bits), _storage(int(bits)), rounding, scale, _seed(), _next_offset())
+
+
+def _check_scheme(a) -> None:
+    if a.transform_scheme != "gih_gwlr":
+        if a.transform_scheme in ("hadamard", "low_rank", "gilr_gwh", "gilro_gwh"):
+            raise NotImplementedError("transform_scheme %r is not built on the native path (only 'gih_gwlr')"
+                                      % a.transform_scheme)
+        raise Exception("args.transform_scheme not implemented: " + str(a.transform_scheme))
+    if not (a.TransformGogi and a.TransformWgt and a.TransformGogw and a.TransformInput):
+        raise NotImplementedError("the native path needs TransformGogi/Wgt/Gogw/Input all True")
+
+
+_selection_cache: dict = {}
+
+
+def _selection(h_bs: Tensor):
+    """(n, sel) of the low-rank matrix a layer carries; cached on the matrix's identity."""
+    key = (h_bs.data_ptr(), tuple(h_bs.shape), h_bs._version)
+    hit = _selection_cache.get(key)
+    if hit is None:
+        hit = selection_from_matrix(h_bs)
+        if len(_selection_cache) > 256:
+            _selection_cache.clear()
+        _selection_cache[key] = hit
+    return hit
+
+
+class FLinearQ(Function):
+    """``FLinearQ.apply(x, w, h_out, h_bs, name)`` (utils/quant_matmul.py:169-348).
+
+    forward: ``F.linear(x, w)`` in full precision.  setup_context: the activation buffer is the
+    Hadamard low-rank projection of ``x`` along tokens, quantised to INT8 (what the reference
+    saves), produced by one fused kernel.  backward: grad_input and grad_weight from the
+    integer tensor-core path; exactly two real gradients are returned.
+    3-D inputs [B, L, I] are treated as B*L flat tokens with one scale (the reference takes one
+    scale per sample)."""
+
+    @staticmethod
+    def forward(x, w, h_out, h_bs, name):
+        return F.linear(x, w)
+
+    @staticmethod
+    def setup_context(ctx, inputs, output):
+        x, w, h_out, h_bs, name = inputs
+        a = _args()
+        _check_scheme(a)
+        x2 = x.detach().reshape(-1, x.shape[-1])
+        if not x2.is_contiguous():
+            x2 = x2.contiguous()
+        n_l, sel = _selection(h_bs)
+        if x2.shape[0] % n_l:
+            raise ValueError("token count %d is not a multiple of the low-rank order %d" % (x2.shape[0], n_l))
+        q_x = _operand("x", a.quantBWDAct, a.actQuantBit, "Activation", row_ok=False)
+        cfg = ops.LinearConfig(order_o=int(h_out.shape[0]), order_l=n_l, sel_l=sel, q_x=q_x)
+        x_q_t, scale_x = ops.abc_compress(x2, cfg)
+        ctx.name = name
+        ctx.x_shape = tuple(x.shape)
+        ctx.order_o, ctx.order_l, ctx.sel = int(h_out.shape[0]), n_l, sel
+        ctx.q_x = q_x
+        ctx.save_for_backward(x_q_t, w, scale_x)
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        x_q_t, w, scale_x = ctx.saved_tensors
+        a = _args()
+        _check_scheme(a)
+        name = ctx.name
+        go = grad_output.reshape(-1, grad_output.shape[-1])
+        if not go.is_contiguous():
+            go = go.contiguous()
+        if go.dtype != w.dtype:
+            go = go.to(w.dtype)
+        if a.quantAuto and len(a.layer_quant_dict) > 0:
+            # layer-wise quantiser selection; both sides take GogiQuantBit here, as the reference
+            # does (utils/quant_matmul.py:244-245, 307-308)
+            pick = {"stoch_quantizer": "stoch", "norm_quantizer": "nq", "int_quantizer": "int"}
+            try:
+                gx_scheme = pick[a.layer_quant_dict[name + "_gx"]]
+                gw_scheme = pick[a.layer_quant_dict[name + "_gw"]]
+            except KeyError as e:
+                raise NotImplementedError("layer_quant_dict entry %s is not built on the native path" % e) from None
+            q_gx = _operand("gx", gx_scheme, a.GogiQuantBit, "GradHo", row_ok=True)
+            q_gw = _operand("gw", gw_scheme, a.GogiQuantBit, "GradHb", row_ok=True)
+        else:
+            q_gx = _operand("gx", a.quantBWDGogi, a.GogiQuantBit, "GradHo", row_ok=True)
+            q_gw = _operand("gw", a.quantBWDGogw, a.GogwQuantBit, "GradHb", row_ok=True)
+        q_w = _operand("w", a.quantBWDWgt, a.weightQuantBit, "Weight", row_ok=False)
+        cfg = ops.LinearConfig(order_o=ctx.order_o, order_l=ctx.order_l, sel_l=ctx.sel, q_gx=q_gx, q_w=q_w, q_gw=q_gw,
+                               q_x=ctx.q_x)
+        need_gx, need_gw = ctx.needs_input_grad[0], ctx.needs_input_grad[1]
+        gx = gw = None
+        if need_gx or need_gw:
+            gx, gw = ops.linear_backward(go, w.detach(), x_q_t, scale_x, cfg, need_gx=need_gx, need_gw=need_gw)
+        if gx is not None:
+            gx = gx.reshape(ctx.x_shape)
+        return gx, gw, None, None, None
+
+
+class HQ_Linear(nn.Linear):
+    """Drop-in ``nn.Linear`` whose backward is HOT (utils/quant_matmul.py:350-422).  Buffers
+    ``hadamard_out`` [n_O, n_O] and ``hadamard_bs`` [r, n_L] and the attribute ``layer_name``
+    keep the reference's names so state dicts and the layer-naming loop carry over."""
+
+    def __init__(self, in_features, out_features, bias=True) -> None:
+        super().__init__(in_features, out_features, bias)
+        a = _args()
+        _check_scheme_name(a)
+        self.register_buffer("hadamard_out", torch.tensor(TD.get_or_register("hadamard", self.out_features),
+                                                          dtype=self.weight.dtype))
+        n, sel = lowrank_selection(max(int(a.BATCH_SIZE), 1), None, a.vectorPercentile)
+        self.register_buffer("hadamard_bs", self._basis(n, sel, self.weight.device))
+        self._bs_tokens = None
+        self.layer_name = " "
+
+    def _basis(self, n, sel, device) -> Tensor:
+        from .hadamard_matmul import hadamard
+        return torch.tensor(hadamard(n)[sel], dtype=self.weight.dtype, device=device)
+
+    def forward(self, input: Tensor) -> Tensor:
+        a = _args()
+        # the low-rank basis follows the live token count, as in the reference (:374-413); here it
+        # is rebuilt only when that count changes, and straight on the device
+        tokens = input.shape[0] if input.dim() == 2 else input.shape[0] * input.shape[1]
+        if input.dim() == 3 and getattr(a, "lowRankPreset", None) is None:
+            tokens = input.shape[1]   # the reference sizes the basis from the per-sample length
+        if tokens != self._bs_tokens or self.hadamard_bs.device != self.weight.device:
+            n, sel = lowrank_selection(tokens, getattr(a, "lowRankPreset", None), a.vectorPercentile)
+            self.hadamard_bs = self._basis(n, sel, self.weight.device)
+            self._bs_tokens = tokens
+        output = FLinearQ.apply(input, self.weight, self.hadamard_out, self.hadamard_bs, self.layer_name)
+        if self.bias is not None:
+            output += self.bias.to(output.device)
+        return output
+
+
+def _check_scheme_name(a) -> None:
+    if a.transform_scheme not in ("hadamard", "low_rank", "gilr_gwh", "gilro_gwh", "gih_gwlr"):
+        raise Exception("Transformation method not implemented: " + str(a.transform_scheme))
+    if a.transform_scheme != "gih_gwlr":
+        raise NotImplementedError("transform_scheme %r is not built on the native path (only 'gih_gwlr')"
+                                  % a.transform_scheme)
+
+
+def replace_layers(model: nn.Module, old, new) -> None:
+    """Recursively swap ``nn.Linear`` children for ``new`` (``HQ_Linear``), sharing weight and
+    bias storage with the replaced module (utils/utils.py:53-74).  LoRA sub-layers named
+    ``base_layer`` / ``default`` are skipped unless ``args.HLQ_on_base`` / ``HLQ_on_decompose``."""
+    a = _args()
+    for n, module in model.named_children():
+        if len(list(module.children())) > 0:
+            replace_layers(module, old, new)
+        if old == nn.Linear and isinstance(module, old) and not isinstance(module, new):
+            if "base_layer" in n and not getattr(a, "HLQ_on_base", False):
+                continue
+            if "default" in n and not getattr(a, "HLQ_on_decompose", False):
+                continue
+            new_layer = new(module.in_features, module.out_features)   # always built with a bias (:73)
+            new_layer = new_layer.to(device=module.weight.device, dtype=module.weight.dtype)
+            new_layer.weight.data = module.weight.data
+            new_layer.weight.requires_grad = module.weight.requires_grad
+            if module.bias is not None:
+                new_layer.bias.data = module.bias.data
+            setattr(model, n, new_layer)
+        elif old == nn.Conv2d and isinstance(module, old):
+            raise NotImplementedError("HQ_Conv2d is not built; leave convolutions in full precision")
+
+
+def precision_scheduler(current_epoch, max_bit=8, min_bit=4, milestones=()):
+    """Bit-width schedule (utils/utils.py:149-159): everything at ``max_bit`` in epoch 0; at each
+    milestone the grad_output (g_x side) and weight widths halve, if their scheme is stoch/int."""
+    a = _args()
+    if current_epoch == 0:
+        a.GogiQuantBit = a.weightQuantBit = a.GogwQuantBit = a.actQuantBit = max_bit
+    elif current_epoch in milestones and min(a.GogiQuantBit, a.weightQuantBit, a.GogwQuantBit, a.actQuantBit) > min_bit:
+        if a.quantBWDGogi in ("stoch", "int"):
+            a.GogiQuantBit = a.GogiQuantBit // 2
+        if a.quantBWDWgt in ("stoch", "int"):
+            a.weightQuantBit = a.weightQuantBit // 2

@@ -287,9 +287,17 @@ def abc_compress(x: np.ndarray, n_l: int, sel: np.ndarray, bits: int, u, mode: s
     return quant_tensor(x_lr, bits, u if mode == "stoch" else None)
 
 
+def _int_matmul(a: np.ndarray, b: np.ndarray, exact: bool) -> np.ndarray:
+    """a @ b on integer codes.  exact: int64 (slow, no BLAS).  Otherwise float32 BLAS, which is
+    what the reference runs (utils/quant_matmul.py:288,322) and is exact while |acc| < 2^24."""
+    if exact:
+        return a.astype(np.int64) @ b.astype(np.int64)
+    return a.astype(F32) @ b.astype(F32)
+
+
 def linear_backward(go, w, x_q, s_x, *, n_o: int, n_l: int, sel, bits_gx: int = 4, bits_w: int = 4,
                     bits_gw: int = 8, u_go=None, u_w=None, u_gw=None, gx_per_token: bool = False,
-                    gw_per_channel: bool = False, w_mode: str = "stoch"):
+                    gw_per_channel: bool = False, w_mode: str = "stoch", exact_matmul: bool = True):
     """FLinearQ.backward (:214-348) for 2-D tensors.  ``u_*`` None selects nearest
     rounding for that operand.  Returns a dict with every intermediate the CUDA
     path can be compared on."""
@@ -307,7 +315,7 @@ def linear_backward(go, w, x_q, s_x, *, n_o: int, n_l: int, sel, bits_gx: int = 
         q_w, s_w = quant_sawb(w_h, bits_w)
     else:
         q_w, s_w = quant_tensor(w_h, bits_w, u_w if w_mode == "stoch" else None)
-    acc_x = q_go.astype(np.int64) @ q_w.astype(np.int64)
+    acc_x = _int_matmul(q_go, q_w, exact_matmul)
     if gx_per_token:
         gx = (acc_x.astype(F32) * s_go[:, None]) * F32(s_w)
     else:
@@ -319,7 +327,7 @@ def linear_backward(go, w, x_q, s_x, *, n_o: int, n_l: int, sel, bits_gx: int = 
         q_gw, s_gw = quant_rows(go_lr_t, bits_gw, u_gw)
     else:
         q_gw, s_gw = quant_tensor(go_lr_t, bits_gw, u_gw)
-    acc_w = q_gw.astype(np.int64) @ np.asarray(x_q).astype(np.int64)
+    acc_w = _int_matmul(q_gw, np.asarray(x_q), exact_matmul)
     if gw_per_channel:
         gw = (acc_w.astype(F32) * s_gw[:, None]) * F32(s_x)
     else:

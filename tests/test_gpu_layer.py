@@ -1,0 +1,180 @@
+"""GPU tests of the reference-facing layer: the quantiser callables, FLinearQ / HQ_Linear,
+replace_layers, layer-wise quantiser selection and the HLQ_backward plugin call."""
+import numpy as np
+import pytest
+import torch
+import torch.nn as nn
+
+from oracle import hot_oracle as oc
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture()
+def hot():
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    import hot_b200.args as args
+    import hot_b200.quant_matmul as qm
+    saved = {k: getattr(args, k) for k in dir(args) if not k.startswith("_")}
+    args.transform_scheme = "gih_gwlr"
+    args.TransformGogi = args.TransformWgt = args.TransformGogw = args.TransformInput = True
+    args.GogiQuantBit, args.weightQuantBit, args.GogwQuantBit, args.actQuantBit = 4, 4, 8, 8
+    args.quantBWDGogi = args.quantBWDWgt = args.quantBWDGogw = args.quantBWDAct = "stoch"
+    args.quantAuto = False
+    args.layer_quant_dict.clear()
+    args.lowRankPreset = "half16"
+    yield args, qm
+    for k, v in saved.items():
+        setattr(args, k, v)
+    args.layer_quant_dict.clear()
+
+
+def test_quantiser_callables_follow_the_reference_contract(hot):
+    _, qm = hot
+    g = torch.randn(48, 100, device="cuda") * 1e-3            # 100 columns: not a multiple of 8
+    g[5] *= 40
+    gn = g.cpu().numpy()
+    q, s = qm.int_quantizer(g, 4, False)
+    ref_q, ref_s = oc.quant_tensor(gn, 4, None)
+    assert q.dtype == g.dtype and q.shape == g.shape
+    assert np.array_equal(q.cpu().numpy().astype(np.int32), ref_q)
+    assert np.float32(s.item()) == ref_s
+    q, s = qm.stoch_quantizer(g, 4, False)
+    qn = q.cpu().numpy()
+    assert np.abs(qn).max() <= 7 and np.array_equal(qn, np.rint(qn))
+    y = gn / (ref_s + np.float32(1e-11))
+    assert np.all(np.abs(qn - y) < 1.0 + 1e-6)                 # each code is floor or ceil of the exact quotient
+    assert abs(float((qn - y).mean())) < 0.02                  # and unbiased
+    d, one = qm.norm_quantizer(g, 4, False)
+    assert one == 1.0 and d.shape == g.shape
+    row_err = (d - g).abs().amax(dim=1) / g.abs().amax(dim=1)
+    assert float(row_err.max()) < 1.0 / 7 + 1e-3               # error bounded by one per-row step
+    with pytest.raises(NotImplementedError):
+        qm.stoch_quantizer(g.reshape(4, 12, 100), 4, True)
+    assert set(qm.quant_scheme_dict) >= {"int_quantizer", "stoch_quantizer", "norm_quantizer"}
+
+
+def test_hq_linear_matches_oracle_with_nearest_rounding(hot):
+    args, qm = hot
+    args.quantBWDGogi = args.quantBWDWgt = args.quantBWDGogw = args.quantBWDAct = "int"   # deterministic
+    torch.manual_seed(0)
+    L, I, O = 320, 64, 96
+    lin = qm.HQ_Linear(I, O).cuda()
+    lin.layer_name = "blocks.0.mlp.fc1"
+    x = torch.randn(L, I, device="cuda", requires_grad=True)
+    go = torch.randn(L, O, device="cuda") * 1e-3
+    y = lin(x)
+    assert torch.allclose(y, torch.nn.functional.linear(x, lin.weight, lin.bias), atol=1e-5)
+    y.backward(go)
+    assert tuple(lin.hadamard_out.shape) == (16, 16) and tuple(lin.hadamard_bs.shape) == (8, 16)
+    sel = np.array(oc.lowrank_preset(16, 8))
+    xq, sx = oc.abc_compress(x.detach().cpu().numpy(), 16, sel, 8, None, "int")
+    ref = oc.linear_backward(go.cpu().numpy(), lin.weight.detach().cpu().numpy(), xq, sx, n_o=16, n_l=16, sel=sel,
+                             w_mode="int")
+    assert np.array_equal(x.grad.cpu().numpy(), ref["grad_input"])
+    assert np.array_equal(lin.weight.grad.cpu().numpy(), ref["grad_w"])
+    assert torch.allclose(lin.bias.grad, go.sum(0), rtol=1e-4, atol=1e-6)   # bias grad is ordinary autograd
+
+
+def test_hq_linear_3d_and_reference_low_rank_basis(hot):
+    args, qm = hot
+    args.lowRankPreset = None                                    # follow make_WHT(tokens, 50)
+    lin = qm.HQ_Linear(64, 96).cuda()
+    x = torch.randn(4, 160, 64, device="cuda", requires_grad=True)   # per-sample length 160 -> n=32, r=10
+    y = lin(x)
+    assert tuple(lin.hadamard_bs.shape) == (10, 32)
+    y.backward(torch.randn_like(y) * 1e-3)
+    assert x.grad.shape == x.shape and lin.weight.grad.shape == lin.weight.shape
+    assert torch.isfinite(x.grad).all() and torch.isfinite(lin.weight.grad).all()
+    x2 = torch.randn(3, 197, 64, device="cuda", requires_grad=True)  # ViT token count: identity basis
+    lin(x2).sum().backward()
+    assert tuple(lin.hadamard_bs.shape) == (1, 1)
+
+
+def test_stochastic_backward_is_unbiased_enough(hot):
+    """Against full precision the HOT gradients carry quantisation and low-rank error, not bias:
+    grad_input correlates strongly with the exact one."""
+    args, qm = hot
+    torch.manual_seed(1)
+    L, I, O = 1024, 128, 256
+    lin = qm.HQ_Linear(I, O, bias=False).cuda()
+    x = torch.randn(L, I, device="cuda", requires_grad=True)
+    go = torch.randn(L, O, device="cuda") * 1e-3
+    lin(x).backward(go)
+    exact = go @ lin.weight.detach()
+    cos = torch.nn.functional.cosine_similarity(x.grad.flatten(), exact.flatten(), dim=0)
+    assert float(cos) > 0.85
+
+
+def test_unbuilt_modes_raise(hot):
+    args, qm = hot
+    lin = qm.HQ_Linear(64, 64).cuda()
+    x = torch.randn(32, 64, device="cuda", requires_grad=True)
+    args.quantBWDAct = "sawb"
+    with pytest.raises(NotImplementedError):
+        lin(x)
+    args.quantBWDAct = "bogus"
+    with pytest.raises(Exception, match="rounding scheme not implemented"):
+        lin(x)
+    args.quantBWDAct = "stoch"
+    args.transform_scheme = "low_rank"
+    with pytest.raises(NotImplementedError):
+        lin(x)
+    args.transform_scheme = "nonsense"
+    with pytest.raises(Exception, match="not implemented"):
+        qm.HQ_Linear(8, 8)
+
+
+def test_replace_layers_and_lqs(hot):
+    args, qm = hot
+    from hot_b200 import lqs
+    torch.manual_seed(0)
+    model = nn.Sequential(nn.Linear(64, 128), nn.GELU(), nn.Linear(128, 64)).cuda()
+    w0 = model[0].weight
+    qm.replace_layers(model, nn.Linear, qm.HQ_Linear)
+    assert isinstance(model[0], qm.HQ_Linear) and isinstance(model[2], qm.HQ_Linear)
+    assert model[0].weight.data_ptr() == w0.data_ptr()            # storage shared with the replaced layer
+    for name, layer in model.named_modules():
+        if isinstance(layer, qm.HQ_Linear):
+            layer.layer_name = name
+    x = torch.randn(64, 64, device="cuda")
+    tgt = torch.randn(64, 64, device="cuda")
+    picked = lqs.calibrate(model, [(x, tgt)], nn.functional.mse_loss)
+    assert set(picked) == {"0_gx", "0_gw", "2_gx", "2_gw"}
+    assert all(v in ("stoch_quantizer", "norm_quantizer") for v in picked.values())
+    assert picked["0_gw"] == picked["2_gw"] == "stoch_quantizer"
+    # the rule itself, on the golden cases' shapes: an outlier token flips g_x to per-token
+    g = torch.randn(64, 48, device="cuda") * 1e-3
+    assert lqs.select_quantizer(g)[0] == "stoch_quantizer"
+    g[7] *= 30
+    assert lqs.select_quantizer(g)[:2] == ("norm_quantizer", "stoch_quantizer")
+    # the table drives the backward
+    args.quantAuto = True
+    args.layer_quant_dict["0_gx"] = "norm_quantizer"
+    model.zero_grad()
+    nn.functional.mse_loss(model(x), tgt).backward()
+    assert torch.isfinite(model[0].weight.grad).all()
+
+
+def test_hlq_backward_plugin_call(hot):
+    import HLQ_backward
+    torch.manual_seed(0)
+    L, O, I = 784, 3072, 768                                       # 16 x 49 tokens, the harness's layer widths
+    go = torch.randn(L, O, device="cuda") * 1e-3
+    w = torch.randn(O, I, device="cuda") * 0.03
+    x = torch.randn(L, I, device="cuda")
+    for per_token in (True, False):
+        gx, gw, times = HLQ_backward.backward(go, w, x, 0, 0, 16, per_token)
+        assert gx.shape == (L, I) and gw.shape == (O, I) and gx.dtype == go.dtype
+        assert len(times) == 4 and all(t >= 0 for t in times) and times[0] > 0 and times[2] > 0
+        cos = torch.nn.functional.cosine_similarity(gx.flatten(), (go @ w).flatten(), dim=0)
+        assert float(cos) > 0.85
+        cosw = torch.nn.functional.cosine_similarity(gw.flatten(), (go.t() @ x).flatten(), dim=0)
+        assert float(cosw) > 0.5                                   # half of the token basis is dropped
+    with pytest.raises(RuntimeError, match="must be a CUDA tensor"):
+        HLQ_backward.backward(go.cpu(), w, x, 0, 0, 16, False)
+    with pytest.raises(RuntimeError, match="must be contiguous"):
+        HLQ_backward.backward(go.t().contiguous().t(), w, x, 0, 0, 16, False)
+    with pytest.raises(RuntimeError, match="must be 2D"):
+        HLQ_backward.backward(go[None], w, x, 0, 0, 16, False)
