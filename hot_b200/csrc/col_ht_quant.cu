@@ -348,3 +348,58 @@ extern "C" int hot_col_ht_quant(const void* x, int dtype, int64_t rows, int64_t 
   if (dtype == HOT_F32) return launch_t<float>((const float*)x, order, p, *q, (uint8_t*)codes_t, scales, absmax_ws, st);
   return launch_t<__nv_bfloat16>((const __nv_bfloat16*)x, order, p, *q, (uint8_t*)codes_t, scales, absmax_ws, st);
 }
+
+// ---------------------------------------------------------------------------------------
+// Variant for callers that cannot hand over scratch memory of their own.
+// ---------------------------------------------------------------------------------------
+namespace hot {
+namespace {
+
+constexpr int kStaticScratchWords = 16384;  // 64 KiB, resident on every GPU that loads this library
+
+// The abs-max words of hot_col_ht_quant_static live here instead of in a caller buffer.  In host
+// code this name is only a handle for cudaGetSymbolAddress; it is not a device address.
+static __device__ __align__(256) uint32_t g_static_scratch[kStaticScratchWords];
+
+constexpr int kMaxDevices = 64;
+uint32_t* g_static_scratch_ptr[kMaxDevices] = {};  // device address per device ordinal, filled on first use
+
+// Device address of g_static_scratch on the CURRENT device.  The first call on a device asks
+// the runtime for it (which may load the module: not something to do under stream capture).
+int static_scratch_for_current_device(uint32_t** out) {
+  int dev = -1;
+  HOT_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxDevices) HOT_FAIL(HOT_ERR_UNSUPPORTED, "hot_col_ht_quant_static: device ordinal %d", dev);
+  uint32_t* p = __atomic_load_n(&g_static_scratch_ptr[dev], __ATOMIC_ACQUIRE);
+  if (!p) {
+    void* sym = nullptr;
+    HOT_CUDA(cudaGetSymbolAddress(&sym, g_static_scratch));
+    if (!sym) HOT_FAIL(HOT_ERR_CUDA, "hot_col_ht_quant_static: cudaGetSymbolAddress returned a null address");
+    p = static_cast<uint32_t*>(sym);
+    __atomic_store_n(&g_static_scratch_ptr[dev], p, __ATOMIC_RELEASE);  // racing first calls store the same value
+  }
+  *out = p;
+  return HOT_OK;
+}
+
+}  // namespace
+}  // namespace hot
+
+extern "C" int hot_col_ht_quant_static(const void* x, int dtype, int64_t rows, int64_t cols, int64_t ldx, int order,
+                                       const int32_t* sel, int r, const hot_quant_t* q, int logical_layout,
+                                       void* codes_t, int64_t ld_codes, float* scales, hot_stream_t stream) {
+  using namespace hot;
+  if (!q) HOT_FAIL(HOT_ERR_ARG, "hot_col_ht_quant_static: null pointer");
+  const int64_t words = q->scale_mode == HOT_SCALE_ROW ? cols : 1;
+  if (words > kStaticScratchWords)
+    HOT_FAIL(HOT_ERR_UNSUPPORTED,
+             "hot_col_ht_quant_static: per-row scales over %lld columns need %lld scratch words, the built-in scratch "
+             "holds %d; use hot_col_ht_quant with a caller-owned scratch buffer",
+             (long long)cols, (long long)words, kStaticScratchWords);
+  uint32_t* scratch = nullptr;
+  if (int rc = static_scratch_for_current_device(&scratch)) return rc;
+  // hot_col_ht_quant zeroes the words it uses (a memset on the stream) before its first kernel,
+  // so whatever the previous call left in the array does not leak into this one
+  return hot_col_ht_quant(x, dtype, rows, cols, ldx, order, sel, r, q, logical_layout, codes_t, ld_codes, scales, scratch,
+                          stream);
+}

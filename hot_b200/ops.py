@@ -108,6 +108,30 @@ def col_ht_quant(x: torch.Tensor, order: int, sel: Sequence[int], q: Quant, logi
     return codes, scales, out_len
 
 
+def col_ht_quant_static(x: torch.Tensor, order: int, sel: Sequence[int], q: Quant, logical_layout: str = "natural"):
+    """``col_ht_quant`` through ``hot_col_ht_quant_static``: the library's built-in scratch array
+    stands in for the abs-max workspace, so this wrapper hands the library nothing but the
+    input and the two outputs.  Per-row scales are limited to 16384 columns.  Calls on one
+    device share that array: keep them on one stream (or otherwise ordered)."""
+    _require_cuda(x)
+    if x.dim() != 2 or x.stride(1) != 1:
+        raise ValueError("x must be 2-D with a contiguous last dim")
+    rows, cols = x.shape
+    r = len(sel)
+    out_len = rows // order * r
+    pitch = _pitch16((out_len + 1) // 2 if q.storage == "int4" else out_len)
+    codes = torch.empty((cols, pitch), dtype=torch.uint8, device=x.device)
+    scales = torch.empty((cols if q.scale == "row" else 1,), dtype=torch.float32, device=x.device)
+    sel_c = (C.c_i32 * r)(*[int(s) for s in sel])
+    with torch.cuda.device(x.device):
+        C.check(C.lib().hot_col_ht_quant_static(x.data_ptr(), _dtype(x), rows, cols, x.stride(0), order, sel_c, r,
+                                                ctypes.byref(q.to_c()),
+                                                C.LAYOUT_TRANSPOSED if logical_layout == "transposed" else C.LAYOUT_NATURAL,
+                                                codes.data_ptr(), pitch, scales.data_ptr(), _stream(x)),
+                "hot_col_ht_quant_static")
+    return codes, scales, out_len
+
+
 def gemm_i8(a: torch.Tensor, a_storage: str, b: torch.Tensor, b_storage: str, M: int, N: int, K: int,
             scale_a: Optional[torch.Tensor], scale_b: Optional[torch.Tensor], post: float = 1.0,
             out_dtype: torch.dtype = torch.float32, status: Optional[torch.Tensor] = None) -> torch.Tensor:

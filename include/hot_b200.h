@@ -101,6 +101,29 @@ int hot_col_ht_quant(const void* x, int dtype, int64_t rows, int64_t cols, int64
                      hot_stream_t stream);
 
 /*
+ * hot_col_ht_quant without a scratch argument, for callers that cannot supply device scratch
+ * of their own: code running where device allocation is off limits (a host that hands the
+ * library a fixed set of pre-registered buffers, an allocator-free inference/training runtime,
+ * a section of the program in which cudaMalloc would synchronise or is simply forbidden).
+ * The abs-max words live in a 64 KiB array inside the library's device image instead, which
+ * every GPU that loads the library carries until the process exits.
+ *   - Same arguments, results and errors as hot_col_ht_quant, minus absmax_ws.
+ *   - Limit: HOT_SCALE_ROW needs one word per column, so cols <= 16384 in that mode (any cols in
+ *     HOT_SCALE_TENSOR mode); beyond it the call fails with HOT_ERR_UNSUPPORTED and says so.
+ *   - It allocates nothing (no cudaMalloc / cudaFree / allocating library call).  The first call
+ *     on each device looks up the array's device address; make that first call outside any
+ *     stream capture, with the target device current.
+ *   - All calls on a device share the one array.  Each call clears the words it uses on its
+ *     stream before using them, so calls that run one after another are independent; calls
+ *     that can overlap on the GPU (different streams, no ordering between them) race on it and
+ *     must be serialised by the caller.
+ * This entry point has no counterpart in the reference.
+ */
+int hot_col_ht_quant_static(const void* x, int dtype, int64_t rows, int64_t cols, int64_t ldx, int order,
+                            const int32_t* sel, int r, const hot_quant_t* q, int logical_layout,
+                            void* codes_t, int64_t ld_codes, float* scales, hot_stream_t stream);
+
+/*
  * Integer GEMM on tcgen05 (kind::i8) with fused dequantisation:
  *   out[m, n] = ((float)(sum_k a[m,k] * b[n,k]) * sa[m or 0]) * sb[n or 0] * post
  *   a [M, K] and b [N, K]: K contiguous, pitches lda/ldb in BYTES (multiples of 16),
