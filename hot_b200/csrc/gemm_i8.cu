@@ -1,16 +1,17 @@
 // Integer GEMM  out[m, n] = dequant( sum_k a[m, k] * b[n, k] )  on the 5th-generation tensor
 // cores: tcgen05.mma kind::i8, int32 accumulators in tensor memory, operands brought in by TMA.
 //
-// One CTA computes one 128 x BN output tile.  Warp roles:
+// One persistent CTA per SM walks 128 x BN output tiles (BN chosen per problem).  Warp roles:
 //   warp 0      TMA producer: per 128-byte K slab, one tiled bulk copy for A (128 rows) and one
 //               for B (BN rows) into a 128B-swizzled shared-memory stage; completion on full[s]
 //   warp 1      allocates tensor memory, issues 4 x (M128, N BN, K32) MMAs per stage from one
 //               elected lane, releases the stage with tcgen05.commit -> empty[s]
 //   warps 2..5  epilogue: tcgen05.ld the accumulator (each warp its 32-lane quarter), convert,
-//               apply (acc * sa) * sb * post, store fp32 / bf16 / raw int32
-// Operands stored as packed INT4 take a detour: TMA lands the packed bytes in a raw stage and
-// the four epilogue warps sign-extend them to int8 into the swizzled stage before the MMA warp
-// is signalled (Blackwell has no 4-bit integer MMA kind).
+//               apply (acc * sa) * sb * post, store fp32 / bf16 / raw int32; the accumulator is
+//               double-buffered in tensor memory, so this overlaps the next tile's MMAs
+//   warps 6..9  (packed INT4 operands only) TMA lands the packed bytes in a raw stage and these
+//               warps expand them to int8 into the swizzled stage before the MMA warp is
+//               signalled (Blackwell has no 4-bit integer MMA kind)
 //
 // Every wait on an mbarrier is bounded in time; when a wait runs out the CTA ORs a code into
 // the caller's status word, stops issuing work, frees its tensor memory and returns.
@@ -23,7 +24,6 @@ namespace {
 
 constexpr int kBM = 128;
 constexpr int kBK = 128;  // int8 elements (= bytes) of K per stage: one 128B swizzle span
-constexpr int kGemmThreads = 192;
 constexpr uint64_t kWaitLimitNs = 1500ull * 1000ull * 1000ull;
 
 struct GemmParams {
@@ -147,60 +147,72 @@ __host__ __device__ constexpr uint32_t instr_desc_i8(int bn) {
   return (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(bn >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
 }
 
-template <int BN, int STAGES, bool A4, bool B4>
+constexpr int kSmemBudget = 225 * 1024;  // of the 227 KB a CTA may use
+
+template <int BN, bool A4, bool B4>
 struct SmemLayout {
   static constexpr int kA = kBM * kBK;       // int8 stage of A
   static constexpr int kB = BN * kBK;        // int8 stage of B
   static constexpr int kRawA = A4 ? kBM * kBK / 2 : 0;
   static constexpr int kRawB = B4 ? BN * kBK / 2 : 0;
+  static constexpr int kStage = kA + kB + kRawA + kRawB;
+  static constexpr int kStagesFit = (kSmemBudget - 2048) / kStage;
+  static constexpr int kStages = kStagesFit > 8 ? 8 : kStagesFit;
   static constexpr int kOffA = 0;
-  static constexpr int kOffB = kOffA + STAGES * kA;
-  static constexpr int kOffRawA = kOffB + STAGES * kB;
-  static constexpr int kOffRawB = kOffRawA + STAGES * kRawA;
-  static constexpr int kOffBar = kOffRawB + STAGES * kRawB;
-  static constexpr int kBytes = kOffBar + 256 + 1024;  // barriers + slack to align the base to 1024
+  static constexpr int kOffB = kOffA + kStages * kA;
+  static constexpr int kOffRawA = kOffB + kStages * kB;
+  static constexpr int kOffRawB = kOffRawA + kStages * kRawA;
+  static constexpr int kOffBar = kOffRawB + kStages * kRawB;
+  static constexpr int kBytes = kOffBar + 512 + 1024;  // barriers + slack to align the base to 1024
+  static_assert(kStages >= 2, "tile too large for shared memory");
 };
 
-// Sign-extend the 8 nibbles of a word to two words of int8 (low nibble first).
-__device__ __forceinline__ void unpack8(uint32_t w, uint32_t& lo, uint32_t& hi) {
-  // even nibbles -> bytes 0, 2 of each half; odd nibbles -> bytes 1, 3
-  const uint32_t e = w & 0x0F0F0F0Fu;          // nibbles 0, 2, 4, 6 in bytes 0..3
-  const uint32_t o = (w >> 4) & 0x0F0F0F0Fu;   // nibbles 1, 3, 5, 7
-  // interleave: result bytes = n0 n1 n2 n3 | n4 n5 n6 n7
-  uint32_t l = __byte_perm(e, o, 0x5140);      // e0 o0 e1 o1
-  uint32_t h = __byte_perm(e, o, 0x7362);      // e2 o2 e3 o3
-  // sign-extend each 4-bit value held in a byte: (x ^ 8) - 8 per byte
-  l = __vsub4(l ^ 0x08080808u, 0x08080808u);
-  h = __vsub4(h ^ 0x08080808u, 0x08080808u);
-  lo = l;
-  hi = h;
+// Tensor-memory columns: two accumulator buffers of BN columns, rounded up to a power of two.
+__host__ __device__ constexpr uint32_t tmem_cols(int bn) { return 2 * bn <= 128 ? 128u : (2 * bn <= 256 ? 256u : 512u); }
+
+// A packed byte holds code 2j in its low nibble and code 2j+1 in its high nibble.  Moving a
+// nibble into the HIGH half of a byte gives 16 * code as a signed int8 with no sign-extension
+// arithmetic, so operands unpacked this way are 16x too large and the accumulator is shifted
+// right by 4 bits per packed operand in the epilogue (exact: it is a multiple of 16).
+__device__ __forceinline__ void unpack8_x16(uint32_t w, uint32_t& lo, uint32_t& hi) {
+  const uint32_t e = (w << 4) & 0xF0F0F0F0u;  // codes 0, 2, 4, 6 (x16) in bytes 0..3
+  const uint32_t o = w & 0xF0F0F0F0u;         // codes 1, 3, 5, 7 (x16)
+  lo = __byte_perm(e, o, 0x5140);             // e0 o0 e1 o1
+  hi = __byte_perm(e, o, 0x7362);             // e2 o2 e3 o3
 }
 
 // Expand a raw stage of `rows` rows x 64 packed bytes into the swizzled int8 stage
 // (row r at r * 128, 16-byte chunk c at chunk position c ^ (r & 7)).  128 threads cooperate.
 __device__ __forceinline__ void unpack_stage(const uint8_t* raw, uint8_t* dst, int rows, int tid128) {
-  // each thread converts 16 packed bytes (32 codes = two output chunks) at a time
-  const int items = rows * 4;
+  const int items = rows * 4;  // 16 packed bytes (32 codes = two output chunks) per item
+#pragma unroll 2
   for (int it = tid128; it < items; it += 128) {
     const int r = it >> 2, qd = it & 3;
     const uint4 w = *reinterpret_cast<const uint4*>(raw + r * 64 + qd * 16);
     uint4 o0, o1;
-    unpack8(w.x, o0.x, o0.y);
-    unpack8(w.y, o0.z, o0.w);
-    unpack8(w.z, o1.x, o1.y);
-    unpack8(w.w, o1.z, o1.w);
+    unpack8_x16(w.x, o0.x, o0.y);
+    unpack8_x16(w.y, o0.z, o0.w);
+    unpack8_x16(w.z, o1.x, o1.y);
+    unpack8_x16(w.w, o1.z, o1.w);
     const int c0 = qd * 2, c1 = qd * 2 + 1;
     *reinterpret_cast<uint4*>(dst + r * 128 + ((c0 ^ (r & 7)) << 4)) = o0;
     *reinterpret_cast<uint4*>(dst + r * 128 + ((c1 ^ (r & 7)) << 4)) = o1;
   }
 }
 
-template <int BN, int STAGES, bool A4, bool B4>
-__global__ void __launch_bounds__(kGemmThreads) gemm_i8_kernel(const __grid_constant__ CUtensorMap tma_a,
-                                                                const __grid_constant__ CUtensorMap tma_b,
-                                                                GemmParams p) {
-  using L = SmemLayout<BN, STAGES, A4, B4>;
+// Persistent kernel: one CTA per SM walks the output tiles (n fastest, so CTAs running together
+// share A rows and the whole of B in L2).  The shared-memory ring runs on across tiles; the
+// accumulator is double-buffered in tensor memory so the epilogue of tile i overlaps the MMAs
+// of tile i + 1.
+template <int BN, bool A4, bool B4>
+__global__ void __launch_bounds__((A4 || B4) ? 320 : 192, 1)
+    gemm_i8_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b, GemmParams p) {
+  using L = SmemLayout<BN, A4, B4>;
+  constexpr int STAGES = L::kStages;
   constexpr bool kUnpack = A4 || B4;
+  constexpr uint32_t kTmemCols = tmem_cols(BN);
+  constexpr uint32_t kBufStride = kTmemCols / 2;
+  constexpr int kShift = (A4 ? 4 : 0) + (B4 ? 4 : 0);
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   uint8_t* sA = smem + L::kOffA;
@@ -210,13 +222,14 @@ __global__ void __launch_bounds__(kGemmThreads) gemm_i8_kernel(const __grid_cons
   uint64_t* full = reinterpret_cast<uint64_t*>(smem + L::kOffBar);  // TMA landed
   uint64_t* empty = full + STAGES;                                   // MMAs of the stage retired
   uint64_t* ready = empty + STAGES;                                  // unpacked (INT4 operands only)
-  uint64_t* tmem_full = ready + STAGES;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_full + 1);
+  uint64_t* tmem_full = ready + STAGES;                              // [2] accumulator complete
+  uint64_t* tmem_empty = tmem_full + 2;                              // [2] accumulator drained
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int m0 = blockIdx.y * kBM, n0 = blockIdx.x * BN;
-  constexpr uint32_t kTmemCols = BN < 32 ? 32 : BN;
+  const int n_tiles = (p.N + BN - 1) / BN;
+  const int num_tiles = ((p.M + kBM - 1) / kBM) * n_tiles;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -224,7 +237,10 @@ __global__ void __launch_bounds__(kGemmThreads) gemm_i8_kernel(const __grid_cons
       mbar_init(&empty[s], 1);
       mbar_init(&ready[s], 128);
     }
-    mbar_init(tmem_full, 1);
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&tmem_full[b], 1);
+      mbar_init(&tmem_empty[b], 128);
+    }
     *abort_flag = 0u;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     tma_prefetch_desc(&tma_a);
@@ -239,66 +255,81 @@ __global__ void __launch_bounds__(kGemmThreads) gemm_i8_kernel(const __grid_cons
   if (warp == 0) {
     if (lane == 0) {
       constexpr uint32_t kTx = (A4 ? L::kRawA : L::kA) + (B4 ? L::kRawB : L::kB);
-      for (int kb = 0; kb < p.num_kb; ++kb) {
-        const int s = kb % STAGES;
-        const uint32_t ph = (uint32_t)(kb / STAGES) & 1u;
-        if (!mbar_wait(&empty[s], ph ^ 1u, abort_flag)) break;
-        mbar_expect_tx(&full[s], kTx);
-        if (A4) tma_load_2d(rawA + s * L::kRawA, &tma_a, &full[s], kb * (kBK / 2), m0);
-        else tma_load_2d(sA + s * L::kA, &tma_a, &full[s], kb * kBK, m0);
-        if (B4) tma_load_2d(rawB + s * L::kRawB, &tma_b, &full[s], kb * (kBK / 2), n0);
-        else tma_load_2d(sB + s * L::kB, &tma_b, &full[s], kb * kBK, n0);
+      uint32_t g = 0;  // k-block counter across tiles: ring slot g % STAGES, phase (g / STAGES) & 1
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        const int m0 = (tile / n_tiles) * kBM, n0 = (tile % n_tiles) * BN;
+        for (int kb = 0; kb < p.num_kb; ++kb, ++g) {
+          const int s = g % STAGES;
+          const uint32_t ph = (g / STAGES) & 1u;
+          ok = mbar_wait(&empty[s], ph ^ 1u, abort_flag);
+          if (!ok) break;
+          mbar_expect_tx(&full[s], kTx);
+          if (A4) tma_load_2d(rawA + s * L::kRawA, &tma_a, &full[s], kb * (kBK / 2), m0);
+          else tma_load_2d(sA + s * L::kA, &tma_a, &full[s], kb * kBK, m0);
+          if (B4) tma_load_2d(rawB + s * L::kRawB, &tma_b, &full[s], kb * (kBK / 2), n0);
+          else tma_load_2d(sB + s * L::kB, &tma_b, &full[s], kb * kBK, n0);
+        }
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {
       constexpr uint32_t idesc = instr_desc_i8(BN);
+      uint32_t g = 0, it = 0;
       bool ok = true;
-      for (int kb = 0; kb < p.num_kb && ok; ++kb) {
-        const int s = kb % STAGES;
-        const uint32_t ph = (uint32_t)(kb / STAGES) & 1u;
-        ok = mbar_wait(kUnpack ? &ready[s] : &full[s], ph, abort_flag);
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++it) {
+        const uint32_t buf = it & 1u, bph = (it >> 1) & 1u;
+        ok = mbar_wait(&tmem_empty[buf], bph ^ 1u, abort_flag);  // epilogue drained this buffer
         if (!ok) break;
         tc_fence_after();
-        const uint32_t a_addr = smem_u32(sA + s * L::kA), b_addr = smem_u32(sB + s * L::kB);
+        const uint32_t d_tmem = tmem_base + buf * kBufStride;
+        for (int kb = 0; kb < p.num_kb; ++kb, ++g) {
+          const int s = g % STAGES;
+          const uint32_t ph = (g / STAGES) & 1u;
+          ok = mbar_wait(kUnpack ? &ready[s] : &full[s], ph, abort_flag);
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t a_addr = smem_u32(sA + s * L::kA), b_addr = smem_u32(sB + s * L::kB);
 #pragma unroll
-        for (int k4 = 0; k4 < kBK / 32; ++k4)
-          umma_i8(tmem_base, smem_desc_sw128(a_addr + k4 * 32), smem_desc_sw128(b_addr + k4 * 32), idesc,
-                  (kb | k4) != 0 ? 1u : 0u);
-        umma_commit(&empty[s]);
+          for (int k4 = 0; k4 < kBK / 32; ++k4)
+            umma_i8(d_tmem, smem_desc_sw128(a_addr + k4 * 32), smem_desc_sw128(b_addr + k4 * 32), idesc,
+                    (kb | k4) != 0 ? 1u : 0u);
+          umma_commit(&empty[s]);
+        }
+        if (ok) umma_commit(&tmem_full[buf]);
       }
-      if (ok) umma_commit(tmem_full);
     }
-  } else {
-    const int tid128 = threadIdx.x - 64;
+  } else if (warp < 6) {
+    // ---- epilogue warps ----
+    const int q = warp & 3;  // tensor-memory lane quarter this warp may read
+    const bool raw = p.out_dtype == HOT_I32;  // raw accumulators: no scales to read
+    const float sb0 = (p.sb_row || raw) ? 0.0f : p.sb[0];
+    uint32_t it = 0;
     bool ok = true;
-    if (kUnpack) {
-      for (int kb = 0; kb < p.num_kb && ok; ++kb) {
-        const int s = kb % STAGES;
-        const uint32_t ph = (uint32_t)(kb / STAGES) & 1u;
-        ok = mbar_wait(&full[s], ph, abort_flag);
-        if (!ok) break;
-        if (A4) unpack_stage(rawA + s * L::kRawA, sA + s * L::kA, kBM, tid128);
-        if (B4) unpack_stage(rawB + s * L::kRawB, sB + s * L::kB, BN, tid128);
-        fence_proxy_async_smem();  // generic-proxy writes -> visible to the tensor core (async proxy)
-        mbar_arrive(&ready[s]);
-      }
-    }
-    if (ok) ok = mbar_wait(tmem_full, 0u, abort_flag);
-    if (ok) {
-      tc_fence_after();
-      const int q = warp & 3;  // tensor-memory lane quarter this warp may read
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++it) {
+      const int m0 = (tile / n_tiles) * kBM, n0 = (tile % n_tiles) * BN;
+      const uint32_t buf = it & 1u, bph = (it >> 1) & 1u;
       const int row = m0 + q * 32 + lane;
       const bool row_ok = row < p.M;
-      const bool raw = p.out_dtype == HOT_I32;  // raw accumulators: no scales to read
       const float sa = (row_ok && !raw) ? (p.sa_row ? p.sa[row] : p.sa[0]) : 0.0f;
-      const float sb0 = (p.sb_row || raw) ? 0.0f : p.sb[0];
+      ok = mbar_wait(&tmem_full[buf], bph, abort_flag);
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t t_addr = tmem_base + buf * kBufStride + ((uint32_t)(q * 32) << 16);
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
         uint32_t acc[32];
-        tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(c * 32), acc);
+        tmem_ld32(t_addr + (uint32_t)(c * 32), acc);
+        if (c == BN / 32 - 1) {  // everything of this buffer is in registers: hand it back
+          tc_fence_before();
+          mbar_arrive(&tmem_empty[buf]);
+        }
         const int col0 = n0 + c * 32;
         if (!row_ok || col0 >= p.N) continue;
+        if (kShift) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) acc[i] = (uint32_t)((int)acc[i] >> kShift);
+        }
         if (raw) {
           int32_t* o = reinterpret_cast<int32_t*>(p.out) + (int64_t)row * p.ldo + col0;
           if (col0 + 32 <= p.N && (p.ldo & 3) == 0) {
@@ -350,6 +381,23 @@ __global__ void __launch_bounds__(kGemmThreads) gemm_i8_kernel(const __grid_cons
               if (col0 + i < p.N) o[i] = __float2bfloat16_rn(f[i]);
           }
         }
+      }
+    }
+  } else if (kUnpack) {
+    // ---- unpack warps (INT4 operands): raw stage -> swizzled int8 stage ----
+    const int tid128 = threadIdx.x - 192;
+    uint32_t g = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      for (int kb = 0; kb < p.num_kb; ++kb, ++g) {
+        const int s = g % STAGES;
+        const uint32_t ph = (g / STAGES) & 1u;
+        ok = mbar_wait(&full[s], ph, abort_flag);
+        if (!ok) break;
+        if (A4) unpack_stage(rawA + s * L::kRawA, sA + s * L::kA, kBM, tid128);
+        if (B4) unpack_stage(rawB + s * L::kRawB, sB + s * L::kB, BN, tid128);
+        fence_proxy_async_smem();  // generic-proxy writes -> visible to the tensor core (async proxy)
+        mbar_arrive(&ready[s]);
       }
     }
   }
@@ -405,9 +453,9 @@ int make_map(CUtensorMap* map, const void* base, int64_t rows, int64_t row_bytes
   return HOT_OK;
 }
 
-template <int BN, int STAGES, bool A4, bool B4>
-int launch_gemm(const void* a, int64_t lda, const void* b, int64_t ldb, const GemmParams& p, cudaStream_t st) {
-  using L = SmemLayout<BN, STAGES, A4, B4>;
+template <int BN, bool A4, bool B4>
+int launch_gemm(const void* a, int64_t lda, const void* b, int64_t ldb, const GemmParams& p, cudaStream_t st, int sms) {
+  using L = SmemLayout<BN, A4, B4>;
   CUtensorMap ma, mb;
   int rc;
   if (A4) rc = make_map(&ma, a, p.M, (p.K + 1) / 2, lda, kBK / 2, kBM, false);
@@ -416,15 +464,52 @@ int launch_gemm(const void* a, int64_t lda, const void* b, int64_t ldb, const Ge
   if (B4) rc = make_map(&mb, b, p.N, (p.K + 1) / 2, ldb, kBK / 2, BN, false);
   else rc = make_map(&mb, b, p.N, p.K, ldb, kBK, BN, true);
   if (rc) return rc;
-  auto kernel = gemm_i8_kernel<BN, STAGES, A4, B4>;
-  HOT_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kBytes));
-  dim3 grid((unsigned)((p.N + BN - 1) / BN), (unsigned)((p.M + kBM - 1) / kBM));
-  kernel<<<grid, kGemmThreads, L::kBytes, st>>>(ma, mb, p);
+  auto kernel = gemm_i8_kernel<BN, A4, B4>;
+  static bool attr_set = false;  // per instantiation
+  if (!attr_set) {
+    HOT_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kBytes));
+    attr_set = true;
+  }
+  const int64_t tiles = (int64_t)((p.M + kBM - 1) / kBM) * ((p.N + BN - 1) / BN);
+  const unsigned grid = (unsigned)(tiles < sms ? tiles : sms);
+  kernel<<<grid, (A4 || B4) ? 320 : 192, L::kBytes, st>>>(ma, mb, p);
   HOT_CUDA(cudaGetLastError());
   return HOT_OK;
 }
 
+// Tile width: fewest waves of the persistent grid, larger tiles preferred at equal cost (the
+// constant stands for per-tile fill/drain).
+int pick_bn(int M, int N, int sms) {
+  const int cands[4] = {256, 192, 128, 64};
+  int best = 128;
+  int64_t best_cost = -1;
+  const int64_t mt = (M + kBM - 1) / kBM;
+  for (int bn : cands) {
+    const int64_t tiles = mt * ((N + bn - 1) / bn);
+    const int64_t waves = (tiles + sms - 1) / sms;
+    const int64_t cost = waves * (bn + 24);
+    if (best_cost < 0 || cost < best_cost) {
+      best_cost = cost;
+      best = bn;
+    }
+  }
+  return best;
+}
+
+template <bool A4, bool B4>
+int launch_bn(int bn, const void* a, int64_t lda, const void* b, int64_t ldb, const GemmParams& p, cudaStream_t st, int sms) {
+  switch (bn) {
+    case 256: return launch_gemm<256, A4, B4>(a, lda, b, ldb, p, st, sms);
+    case 192: return launch_gemm<192, A4, B4>(a, lda, b, ldb, p, st, sms);
+    case 64: return launch_gemm<64, A4, B4>(a, lda, b, ldb, p, st, sms);
+    default: return launch_gemm<128, A4, B4>(a, lda, b, ldb, p, st, sms);
+  }
+}
+
 }  // namespace
+
+int device_sm_count();
+
 }  // namespace hot
 
 extern "C" int hot_gemm_i8(const void* a, int a_storage, int64_t lda, const void* b, int b_storage, int64_t ldb,
@@ -461,8 +546,11 @@ extern "C" int hot_gemm_i8(const void* a, int a_storage, int64_t lda, const void
   p.out_dtype = out_dtype;
   p.status = status_word;
   cudaStream_t st = (cudaStream_t)stream;
-  if (!a4 && !b4) return launch_gemm<128, 3, false, false>(a, lda, b, ldb, p, st);
-  if (a4 && !b4) return launch_gemm<128, 3, true, false>(a, lda, b, ldb, p, st);
-  if (!a4 && b4) return launch_gemm<128, 3, false, true>(a, lda, b, ldb, p, st);
-  return launch_gemm<128, 3, true, true>(a, lda, b, ldb, p, st);
+  const int sms = device_sm_count();
+  if (sms <= 0) return HOT_ERR_CUDA;
+  const int bn = pick_bn(p.M, p.N, sms);
+  if (!a4 && !b4) return launch_bn<false, false>(bn, a, lda, b, ldb, p, st, sms);
+  if (a4 && !b4) return launch_bn<true, false>(bn, a, lda, b, ldb, p, st, sms);
+  if (!a4 && b4) return launch_bn<false, true>(bn, a, lda, b, ldb, p, st, sms);
+  return launch_bn<true, true>(bn, a, lda, b, ldb, p, st, sms);
 }

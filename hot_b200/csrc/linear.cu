@@ -22,7 +22,7 @@ int plan(int64_t L, int64_t O, int64_t I, const hot_linear_cfg_t& c, Workspace& 
              c.order_l, c.rank_l);
   w.lp = L / c.order_l * c.rank_l;
   w.ld_qgo = code_pitch(O, c.q_gx.storage);
-  w.ld_qw = code_pitch(O, c.q_w.storage);
+  w.ld_qw = code_pitch(O, HOT_STORE_INT8);  // weight codes are kept one per byte (see hot_linear_backward)
   w.ld_qgw = code_pitch(w.lp, c.q_gw.storage);
   size_t o = 0;
   w.off_qgo = o; o += up((size_t)L * w.ld_qgo, kAlign);
@@ -90,10 +90,15 @@ extern "C" int hot_linear_backward(const void* go, int64_t ldgo, const void* w, 
     int32_t ident[64];
     for (int i = 0; i < 64; ++i) ident[i] = i;
     if (cfg->q_w.scale_mode != HOT_SCALE_TENSOR) HOT_FAIL(HOT_ERR_UNSUPPORTED, "hot_linear_backward: the weight takes one scale");
-    rc = hot_col_ht_quant(w, cfg->dtype, O, I, ldw, cfg->order_o, ident, cfg->order_o, &cfg->q_w, HOT_LAYOUT_NATURAL,
+    // The quantised weight is the B operand of every CTA of the g_x GEMM and is tiny (O * I bytes):
+    // it is stored one code per byte whatever its bit width, so that it reaches the tensor core by
+    // TMA alone and only grad_out (the large, streamed operand) is expanded in shared memory.
+    hot_quant_t q_w = cfg->q_w;
+    q_w.storage = HOT_STORE_INT8;
+    rc = hot_col_ht_quant(w, cfg->dtype, O, I, ldw, cfg->order_o, ident, cfg->order_o, &q_w, HOT_LAYOUT_NATURAL,
                           base + ws.off_qw, ws.ld_qw, s_w, scratch + 16, stream);
     if (rc) return rc;
-    rc = hot_gemm_i8(base + ws.off_qgo, cfg->q_gx.storage, ws.ld_qgo, base + ws.off_qw, cfg->q_w.storage, ws.ld_qw, L, I, O,
+    rc = hot_gemm_i8(base + ws.off_qgo, cfg->q_gx.storage, ws.ld_qgo, base + ws.off_qw, HOT_STORE_INT8, ws.ld_qw, L, I, O,
                      s_go, cfg->q_gx.scale_mode == HOT_SCALE_ROW, s_w, 0, 1.0f / (float)cfg->order_o, grad_x, cfg->dtype,
                      ldgx, status_word, stream);
     if (rc) return rc;
