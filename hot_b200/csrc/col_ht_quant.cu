@@ -135,25 +135,25 @@ __global__ void __launch_bounds__(kThreads) col_ht_absmax_kernel(const T* __rest
   }
 }
 
-// uniforms for 8 consecutive codes starting at stored-layout element e0
-__device__ __forceinline__ void philox_span8(const QuantDev& q, uint64_t e0, float (&u)[8]) {
+// Philox outputs for 8 consecutive codes starting at stored-layout element e0
+__device__ __forceinline__ void philox_span8(const QuantDev& q, uint64_t e0, uint32_t (&r)[8]) {
   if ((e0 & 7u) == 0) {
-    philox_uniform8(q, e0 >> 3, u);
+    philox_bits8(q, e0 >> 3, r);
     return;
   }
-  float a[8], b[8];
-  philox_uniform8(q, e0 >> 3, a);
-  philox_uniform8(q, (e0 >> 3) + 1, b);
+  uint32_t a[8], b[8];
+  philox_bits8(q, e0 >> 3, a);
+  philox_bits8(q, (e0 >> 3) + 1, b);
   const int off = (int)(e0 & 7u);
 #pragma unroll
   for (int i = 0; i < 8; ++i) {
-    float pick = 0.0f;
+    uint32_t pick = 0;
 #pragma unroll
     for (int s = 0; s < 16; ++s) {
-      const float cand = s < 8 ? a[s] : b[s - 8];
+      const uint32_t cand = s < 8 ? a[s] : b[s - 8];
       pick = (s == i + off) ? cand : pick;
     }
-    u[i] = pick;
+    r[i] = pick;
   }
 }
 
@@ -197,11 +197,9 @@ __global__ void __launch_bounds__(kThreads) col_ht_quant_kernel(const T* __restr
   }
   __syncthreads();
 
-  float s_t = 0.0f, d_t = 0.0f;
-  if (!p.scale_row) {
-    scale_from_absmax(__uint_as_float(absmax[0]), q.qmax, s_t, d_t);
-    if (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) scales[0] = s_t;
-  }
+  ScalePair sp_t = scale_from_absmax(p.scale_row ? 0.0f : __uint_as_float(absmax[0]), q.qmax);
+  if (!p.scale_row && blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) scales[0] = sp_t.s;
+  const int qmax = (int)q.qmax;
   const int cpr = (p.nb * r) >> 3;  // 8-code chunks per tile row
   const int64_t pos0 = blk0 * r;    // first stored position of this tile within an output row
   for (int item = threadIdx.x; item < CC * cpr; item += kThreads) {
@@ -214,14 +212,15 @@ __global__ void __launch_bounds__(kThreads) col_ht_quant_kernel(const T* __restr
     const float4 b = *reinterpret_cast<const float4*>(tile + cl * p.pitch + ch * 8 + 4);
     v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
     v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
-    float s = s_t, d = d_t;
+    ScalePair sp = sp_t;
     if (p.scale_row) {
-      scale_from_absmax(__uint_as_float(absmax[c]), q.qmax, s, d);
-      if (blockIdx.y == 0 && ch == 0) scales[c] = s;
+      sp = scale_from_absmax(__uint_as_float(absmax[c]), q.qmax);
+      if (blockIdx.y == 0 && ch == 0) scales[c] = sp.s;
     }
     float u[8];
+    uint32_t r16[8];
     if (ROUND == HOT_ROUND_STOCH_PHILOX) {
-      philox_span8(q, (uint64_t)c * (uint64_t)p.out_len + (uint64_t)l0, u);
+      philox_span8(q, (uint64_t)c * (uint64_t)p.out_len + (uint64_t)l0, r16);
     } else if (ROUND == HOT_ROUND_STOCH_NOISE) {
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
@@ -231,16 +230,12 @@ __global__ void __launch_bounds__(kThreads) col_ht_quant_kernel(const T* __restr
           un = p.noise_transposed ? q.noise[(int64_t)c * p.out_len + l] : q.noise[l * (int64_t)p.cols + c];
         u[i] = un;
       }
-    } else {
-#pragma unroll
-      for (int i = 0; i < 8; ++i) u[i] = 0.0f;
     }
     int code[8];
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      code[i] = quantise_one<ROUND>(v[i], d, u[i]);
-      code[i] = max(-(int)q.qmax, min((int)q.qmax, code[i]));
-    }
+    for (int i = 0; i < 8; ++i)
+      code[i] = quantise_one<ROUND>(v[i], sp, ROUND == HOT_ROUND_STOCH_NOISE ? u[i] : 0.0f,
+                                    ROUND == HOT_ROUND_STOCH_PHILOX ? r16[i] : 0u, qmax);
     if (p.store4) {
       uint32_t w = 0;
 #pragma unroll

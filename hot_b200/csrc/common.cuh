@@ -65,34 +65,78 @@ __device__ __forceinline__ uint4 philox4x32_10(uint32_t c0, uint32_t c1, uint32_
   return make_uint4(c0, c1, c2, c3);
 }
 
-// The eight 16-bit uniforms of Philox block g (elements 8g .. 8g+7), as floats k/65536.
-__device__ __forceinline__ void philox_uniform8(const QuantDev& q, uint64_t g, float (&u)[8]) {
+// The eight 16-bit outputs of Philox block g (elements 8g .. 8g+7): element j takes the low
+// (j even) or high (j odd) half of output word j / 2.
+__device__ __forceinline__ void philox_bits8(const QuantDev& q, uint64_t g, uint32_t (&r)[8]) {
   const uint4 w = philox4x32_10((uint32_t)g, (uint32_t)(g >> 32), q.o0, q.o1, q.k0, q.k1);
-  const uint32_t ws[4] = {w.x, w.y, w.z, w.w};
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    u[2 * i] = (float)(ws[i] & 0xFFFFu) * (1.0f / 65536.0f);
-    u[2 * i + 1] = (float)(ws[i] >> 16) * (1.0f / 65536.0f);
-  }
+  r[0] = w.x & 0xFFFFu; r[1] = w.x >> 16;
+  r[2] = w.y & 0xFFFFu; r[3] = w.y >> 16;
+  r[4] = w.z & 0xFFFFu; r[5] = w.z >> 16;
+  r[6] = w.w & 0xFFFFu; r[7] = w.w >> 16;
 }
 
-// scale and divisor of a quantiser from an abs-max: s = mx / qmax, d = s + eps (both fp32,
-// IEEE round-to-nearest: the reference divides, it does not multiply by a reciprocal).
-__device__ __forceinline__ void scale_from_absmax(float mx, float qmax, float& s, float& d) {
-  s = __fdiv_rn(mx, qmax);
-  d = __fadd_rn(s, kEps);
+// scale of a quantiser from an abs-max: s = mx / qmax, and the divisor d = s + eps the values are
+// divided by (both fp32, round-to-nearest: the reference divides, it does not multiply by a
+// reciprocal).
+struct Divisor {
+  float d;  // the divisor
+  float r;  // RN(1 / d)
+};
+
+__device__ __forceinline__ Divisor make_divisor(float d) {
+  Divisor v;
+  v.d = d;
+  v.r = __frcp_rn(d);
+  return v;
 }
 
-// One code.  ROUND: hot_rounding.  u is the uniform for stochastic modes.
+// x / d, correctly rounded, for a divisor shared by many elements: q0 = RN(x * r), residual
+// e = x - q0 * d (exact in an FMA), q = RN(q0 + e * r).  Equal to IEEE division for the ranges a
+// quantiser sees (|x| <= absmax, d = absmax / qmax + eps); the parity tests compare against true
+// division bit for bit.
+__device__ __forceinline__ float div_exact(float x, const Divisor& v) {
+  const float q0 = __fmul_rn(x, v.r);
+  const float e = __fmaf_rn(-q0, v.d, x);
+  return __fmaf_rn(e, v.r, q0);
+}
+
+struct ScalePair {
+  float s;      // the scale the caller gets back
+  Divisor dv;   // divide by s + eps
+  Divisor dv16; // divide by (s + eps) * 2^-16: the quotient scaled by 65536, exactly
+};
+
+__device__ __forceinline__ ScalePair scale_from_absmax(float mx, float qmax) {
+  ScalePair p;
+  p.s = __fdiv_rn(mx, qmax);
+  const float d = __fadd_rn(p.s, kEps);
+  p.dv = make_divisor(d);
+  p.dv16 = make_divisor(d * 1.52587890625e-05f);  // * 2^-16, exact
+  return p;
+}
+
+// One code, |code| <= qmax.  ROUND: hot_rounding.
+//   nearest : round-half-even of y = x / d (torch.round)
+//   noise   : sign(y) * (floor|y| + [u < frac|y|]) with the caller's uniform u
+//   Philox  : the same predicate in fixed point with the 16-bit Philox output R:
+//             T = floor(|y| * 2^16); |code| = (T + R) >> 16, i.e. round up iff
+//             (65535 - R) / 65536 < floor(frac * 2^16) / 2^16
 template <int ROUND>
-__device__ __forceinline__ int quantise_one(float x, float d, float u) {
-  const float y = __fdiv_rn(x, d);
-  if (ROUND == HOT_ROUND_NEAREST) return __float2int_rn(y);  // half to even, as torch.round
-  const float a = fabsf(y);
-  const float f = floorf(a);
-  const float frac = __fsub_rn(a, f);
-  int i = (int)f + ((u < frac) ? 1 : 0);
-  return (y < 0.0f) ? -i : i;
+__device__ __forceinline__ int quantise_one(float x, const ScalePair& sp, float u, uint32_t r16, int qmax) {
+  int mag;
+  if (ROUND == HOT_ROUND_NEAREST) {
+    const int c = __float2int_rn(div_exact(x, sp.dv));
+    return max(-qmax, min(qmax, c));
+  } else if (ROUND == HOT_ROUND_STOCH_PHILOX) {
+    const float a16 = fabsf(div_exact(x, sp.dv16));
+    mag = (int)((__float2uint_rd(a16) + r16) >> 16);
+  } else {
+    const float a = fabsf(div_exact(x, sp.dv));
+    const float f = floorf(a);
+    mag = (int)f + ((u < __fsub_rn(a, f)) ? 1 : 0);
+  }
+  mag = min(mag, qmax);  // the abs-max element can land an ulp above qmax and round up
+  return (x < 0.0f) ? -mag : mag;
 }
 
 __device__ __forceinline__ float warp_max(float v) {

@@ -70,24 +70,18 @@ __device__ __forceinline__ float absmax8(const float (&v)[8]) {
 // Quantise 8 transformed values whose first logical element index is `e0` (a multiple of 8)
 // and store them at `dst` (already offset to the vector).
 template <int ROUND, int STORE4>
-__device__ __forceinline__ void quantise_store8(const float (&v)[8], float d, const QuantDev& q, uint64_t e0,
+__device__ __forceinline__ void quantise_store8(const float (&v)[8], const ScalePair& sp, const QuantDev& q, uint64_t e0,
                                                 uint8_t* dst) {
   float u[8];
-  if (ROUND == HOT_ROUND_STOCH_PHILOX) {
-    philox_uniform8(q, e0 >> 3, u);
-  } else if (ROUND == HOT_ROUND_STOCH_NOISE) {
-    Load8<float>::run(q.noise + e0, u);
-  } else {
-#pragma unroll
-    for (int i = 0; i < 8; ++i) u[i] = 0.0f;
-  }
+  uint32_t r16[8];
+  if (ROUND == HOT_ROUND_STOCH_PHILOX) philox_bits8(q, e0 >> 3, r16);
+  if (ROUND == HOT_ROUND_STOCH_NOISE) Load8<float>::run(q.noise + e0, u);
+  const int qmax = (int)q.qmax;
   int c[8];
 #pragma unroll
-  for (int i = 0; i < 8; ++i) {
-    c[i] = quantise_one<ROUND>(v[i], d, u[i]);
-    // |y| can exceed qmax by an ulp on the abs-max element and then round up; keep the code range
-    c[i] = max(-(int)q.qmax, min((int)q.qmax, c[i]));
-  }
+  for (int i = 0; i < 8; ++i)
+    c[i] = quantise_one<ROUND>(v[i], sp, ROUND == HOT_ROUND_STOCH_NOISE ? u[i] : 0.0f,
+                               ROUND == HOT_ROUND_STOCH_PHILOX ? r16[i] : 0u, qmax);
   if (STORE4) {
     uint32_t w = 0;
 #pragma unroll
@@ -146,9 +140,8 @@ __global__ void __launch_bounds__(kThreads) row_ht_quant_rowscale_kernel(
     mx = 0.0f;
     for (int w = 0; w < tpr / 32; ++w) mx = fmaxf(mx, s_part[w0 + w]);
   }
-  float s, d;
-  scale_from_absmax(mx, q.qmax, s, d);
-  if (row_ok && t == 0) scales[row] = s;
+  const ScalePair sp = scale_from_absmax(mx, q.qmax);
+  if (row_ok && t == 0) scales[row] = sp.s;
   if (!row_ok) return;
   uint8_t* cr = codes + row * ld_codes;
 #pragma unroll
@@ -157,7 +150,7 @@ __global__ void __launch_bounds__(kThreads) row_ht_quant_rowscale_kernel(
       const int vi = t + j * tpr;
       if (vi < nvec) {
         const uint64_t e0 = (uint64_t)row * (uint64_t)cols + (uint64_t)vi * 8u;
-        quantise_store8<ROUND, STORE4>(v[j], d, q, e0, cr + (int64_t)vi * (STORE4 ? 4 : 8));
+        quantise_store8<ROUND, STORE4>(v[j], sp, q, e0, cr + (int64_t)vi * (STORE4 ? 4 : 8));
       }
     }
   }
@@ -168,7 +161,23 @@ __global__ void __launch_bounds__(kThreads) row_ht_quant_rowscale_kernel(
 // ---------------------------------------------------------------------------------------
 constexpr int kUnroll = 4;
 
-template <typename T>
+// Where vector `item` (row-major over rows x nvec) lives.  CONTIG: pitch == cols, so the tensor is
+// one flat run of vectors and no division is needed.
+template <bool CONTIG>
+__device__ __forceinline__ void locate(int64_t item, int nvec, int64_t ldx, int64_t ld_codes, int code_bytes,
+                                       int64_t& x_off, int64_t& c_off) {
+  if (CONTIG) {
+    x_off = item * 8;
+    c_off = item * code_bytes;
+  } else {
+    const int64_t row = item / nvec;
+    const int vi = (int)(item - row * nvec);
+    x_off = row * ldx + (int64_t)vi * 8;
+    c_off = row * ld_codes + (int64_t)vi * code_bytes;
+  }
+}
+
+template <typename T, bool CONTIG>
 __global__ void __launch_bounds__(kThreads) row_ht_absmax_kernel(const T* __restrict__ x, int64_t rows, int cols,
                                                                  int64_t ldx, int n, uint32_t* __restrict__ absmax) {
   const int lane = threadIdx.x & 31;
@@ -183,9 +192,9 @@ __global__ void __launch_bounds__(kThreads) row_ht_absmax_kernel(const T* __rest
     for (int u = 0; u < kUnroll; ++u) {
       const int64_t item = base + u * 32 + lane;
       if (item < total) {
-        const int64_t row = item / nvec;
-        const int vi = (int)(item - row * nvec);
-        Load8<T>::run(x + row * ldx + (int64_t)vi * 8, v[u]);
+        int64_t xo, co;
+        locate<CONTIG>(item, nvec, ldx, 0, 0, xo, co);
+        Load8<T>::run(x + xo, v[u]);
       } else {
 #pragma unroll
         for (int i = 0; i < 8; ++i) v[u][i] = 0.0f;
@@ -202,7 +211,7 @@ __global__ void __launch_bounds__(kThreads) row_ht_absmax_kernel(const T* __rest
   if (lane == 0) atomic_absmax(absmax, mx);
 }
 
-template <typename T, int ROUND, int STORE4>
+template <typename T, int ROUND, int STORE4, bool CONTIG>
 __global__ void __launch_bounds__(kThreads) row_ht_quant_tensorscale_kernel(
     const T* __restrict__ x, int64_t rows, int cols, int64_t ldx, int n, QuantDev q, uint8_t* __restrict__ codes,
     int64_t ld_codes, float* __restrict__ scales, const uint32_t* __restrict__ absmax) {
@@ -211,24 +220,19 @@ __global__ void __launch_bounds__(kThreads) row_ht_quant_tensorscale_kernel(
   const int64_t total = rows * nvec;
   const int64_t warp_id = ((int64_t)blockIdx.x * kThreads + threadIdx.x) >> 5;
   const int64_t nwarps = ((int64_t)gridDim.x * kThreads) >> 5;
-  float s, d;
-  scale_from_absmax(__uint_as_float(*absmax), q.qmax, s, d);
-  if (blockIdx.x == 0 && threadIdx.x == 0) scales[0] = s;
+  const ScalePair sp = scale_from_absmax(__uint_as_float(*absmax), q.qmax);
+  if (blockIdx.x == 0 && threadIdx.x == 0) scales[0] = sp.s;
   for (int64_t base = warp_id * (32 * kUnroll); base < total; base += nwarps * (32 * kUnroll)) {
     float v[kUnroll][8];
-    int64_t rowv[kUnroll];
-    int viv[kUnroll];
+    int64_t coff[kUnroll];
 #pragma unroll
     for (int u = 0; u < kUnroll; ++u) {
       const int64_t item = base + u * 32 + lane;
-      rowv[u] = -1;
-      viv[u] = 0;
+      coff[u] = -1;
       if (item < total) {
-        const int64_t row = item / nvec;
-        const int vi = (int)(item - row * nvec);
-        rowv[u] = row;
-        viv[u] = vi;
-        Load8<T>::run(x + row * ldx + (int64_t)vi * 8, v[u]);
+        int64_t xo;
+        locate<CONTIG>(item, nvec, ldx, ld_codes, STORE4 ? 4 : 8, xo, coff[u]);
+        Load8<T>::run(x + xo, v[u]);
       } else {
 #pragma unroll
         for (int i = 0; i < 8; ++i) v[u][i] = 0.0f;
@@ -238,11 +242,8 @@ __global__ void __launch_bounds__(kThreads) row_ht_quant_tensorscale_kernel(
     for (int u = 0; u < kUnroll; ++u) {
       butterfly8(v[u], n);
       butterfly_lanes(v[u], n, lane);
-      if (rowv[u] >= 0) {
-        const uint64_t e0 = (uint64_t)rowv[u] * (uint64_t)cols + (uint64_t)viv[u] * 8u;
-        quantise_store8<ROUND, STORE4>(v[u], d, q, e0,
-                                       codes + rowv[u] * ld_codes + (int64_t)viv[u] * (STORE4 ? 4 : 8));
-      }
+      // logical element index of the vector: row * cols + col == item * 8 in either layout
+      if (coff[u] >= 0) quantise_store8<ROUND, STORE4>(v[u], sp, q, (uint64_t)(base + u * 32 + lane) * 8u, codes + coff[u]);
     }
   }
 }
@@ -274,9 +275,16 @@ int launch_typed(const T* x, int64_t rows, int cols, int64_t ldx, int n, const h
   } else {
     const int grid = grid_for(rows * (cols >> 3), sms);
     HOT_CUDA(cudaMemsetAsync(absmax_ws, 0, sizeof(uint32_t), st));
-    row_ht_absmax_kernel<T><<<grid, kThreads, 0, st>>>(x, rows, cols, ldx, n, absmax_ws);
-    row_ht_quant_tensorscale_kernel<T, ROUND, STORE4>
-        <<<grid, kThreads, 0, st>>>(x, rows, cols, ldx, n, q, codes, ld_codes, scales, absmax_ws);
+    const bool contig = ldx == cols && ld_codes == (STORE4 ? cols / 2 : cols);
+    if (contig) {
+      row_ht_absmax_kernel<T, true><<<grid, kThreads, 0, st>>>(x, rows, cols, ldx, n, absmax_ws);
+      row_ht_quant_tensorscale_kernel<T, ROUND, STORE4, true>
+          <<<grid, kThreads, 0, st>>>(x, rows, cols, ldx, n, q, codes, ld_codes, scales, absmax_ws);
+    } else {
+      row_ht_absmax_kernel<T, false><<<grid, kThreads, 0, st>>>(x, rows, cols, ldx, n, absmax_ws);
+      row_ht_quant_tensorscale_kernel<T, ROUND, STORE4, false>
+          <<<grid, kThreads, 0, st>>>(x, rows, cols, ldx, n, q, codes, ld_codes, scales, absmax_ws);
+    }
   }
   HOT_CUDA(cudaGetLastError());
   return HOT_OK;

@@ -177,12 +177,22 @@ def _qmax(bits: int) -> F32:
     return F32(2 ** (bits - 1) - 1)
 
 
+class Fixed16(np.ndarray):
+    """Marker type for uniforms k/65536 that are to be compared in 16-bit fixed point: a code
+    rounds up iff u < floor(frac * 2^16) / 2^16 (the production Philox path of the kernels).
+    Plain arrays keep the reference's float predicate u < frac."""
+
+
 def _round_codes(y: np.ndarray, u: np.ndarray | None) -> np.ndarray:
     if u is None:  # torch.round: half to even (utils/quant_matmul.py:47,115)
         return np.rint(y).astype(np.int32)
     a = np.abs(y)
     f = np.floor(a)
     frac = a - f
+    if isinstance(u, Fixed16):
+        t = np.floor(a * F32(65536.0))                      # exact: a power-of-two scaling
+        frac = (t - f * F32(65536.0)) / F32(65536.0)        # floor(frac * 2^16) / 2^16, exact
+        u = np.asarray(u)
     flip = (np.asarray(u, dtype=F32) < frac).astype(F32)  # torch.bernoulli(frac) == (u < frac)
     return (np.sign(y) * (f + flip)).astype(np.int32)
 
@@ -241,10 +251,12 @@ def philox4x32_10(c0, c1, c2, c3, k0: int, k1: int):
 
 
 def philox_uniform16(seed: int, offset: int, shape) -> np.ndarray:
-    """float32 uniforms k/65536, k a 16-bit integer, for the elements 0..N-1 of a
-    tensor in row-major order.  Elements 8g..8g+7 share the Philox block with
-    counter (g_lo, g_hi, offset_lo, offset_hi) and key (seed_lo, seed_hi); element
-    8g+j takes the low (j even) or high (j odd) half of output word j // 2."""
+    """Uniforms (65535 - R)/65536 as a ``Fixed16`` array, R the 16-bit Philox output of each
+    element 0..N-1 of a tensor in row-major order.  Elements 8g..8g+7 share the Philox
+    block with counter (g_lo, g_hi, offset_lo, offset_hi) and key (seed_lo, seed_hi);
+    element 8g+j takes the low (j even) or high (j odd) half of output word j // 2.
+    The kernels compute |code| = (floor(|y| * 2^16) + R) >> 16, which rounds up exactly
+    when (65535 - R)/65536 < floor(frac * 2^16)/2^16."""
     n = int(np.prod(shape))
     g = np.arange((n + 7) // 8, dtype=np.uint64)
     w = philox4x32_10(g & _MASK, g >> np.uint64(32), np.uint64(offset & 0xFFFFFFFF),
@@ -252,7 +264,7 @@ def philox_uniform16(seed: int, offset: int, shape) -> np.ndarray:
     words = np.stack(w, axis=1).astype(np.uint64)                       # [G, 4]
     halves = np.stack([words & np.uint64(0xFFFF), (words >> np.uint64(16)) & np.uint64(0xFFFF)], axis=2)
     r16 = halves.reshape(-1)[:n].astype(F32)
-    return (r16 / F32(65536.0)).reshape(shape)
+    return ((F32(65535.0) - r16) / F32(65536.0)).reshape(shape).view(Fixed16)
 
 
 # ----------------------------------------------------------------------------

@@ -181,7 +181,7 @@ def _run_backward(ops, x, w, go, order_l, sel, dtype, *, gx_row=False, gw_row=Fa
         elif rounding == "philox":
             # Philox streams are indexed in the stored layout: transposed for x and w
             if k in ("x", "w"):
-                us[k] = np.ascontiguousarray(oc.philox_uniform16(*seeds[k], shapes[k][::-1]).T)
+                us[k] = np.ascontiguousarray(oc.philox_uniform16(*seeds[k], shapes[k][::-1]).T).view(oc.Fixed16)
             else:
                 us[k] = oc.philox_uniform16(*seeds[k], shapes[k])
         else:
