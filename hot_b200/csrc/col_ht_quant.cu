@@ -135,28 +135,6 @@ __global__ void __launch_bounds__(kThreads) col_ht_absmax_kernel(const T* __rest
   }
 }
 
-// Philox outputs for 8 consecutive codes starting at stored-layout element e0
-__device__ __forceinline__ void philox_span8(const QuantDev& q, uint64_t e0, uint32_t (&r)[8]) {
-  if ((e0 & 7u) == 0) {
-    philox_bits8(q, e0 >> 3, r);
-    return;
-  }
-  uint32_t a[8], b[8];
-  philox_bits8(q, e0 >> 3, a);
-  philox_bits8(q, (e0 >> 3) + 1, b);
-  const int off = (int)(e0 & 7u);
-#pragma unroll
-  for (int i = 0; i < 8; ++i) {
-    uint32_t pick = 0;
-#pragma unroll
-    for (int s = 0; s < 16; ++s) {
-      const uint32_t cand = s < 8 ? a[s] : b[s - 8];
-      pick = (s == i + off) ? cand : pick;
-    }
-    r[i] = pick;
-  }
-}
-
 // ---- pass 2: transform, stage transposed in shared memory, quantise, store ----------------
 template <typename T, int N, int ROUND>
 __global__ void __launch_bounds__(kThreads) col_ht_quant_kernel(const T* __restrict__ x, ColParams p, QuantDev q,
@@ -217,25 +195,36 @@ __global__ void __launch_bounds__(kThreads) col_ht_quant_kernel(const T* __restr
       sp = scale_from_absmax(__uint_as_float(absmax[c]), q.qmax);
       if (blockIdx.y == 0 && ch == 0) scales[c] = sp.s;
     }
-    float u[8];
-    uint32_t r16[8];
+    int code[8];
     if (ROUND == HOT_ROUND_STOCH_PHILOX) {
-      philox_span8(q, (uint64_t)c * (uint64_t)p.out_len + (uint64_t)l0, r16);
-    } else if (ROUND == HOT_ROUND_STOCH_NOISE) {
+      // random byte of stored-layout element e: byte e % 16 of Philox block e / 16
+      const uint64_t e0 = (uint64_t)c * (uint64_t)p.out_len + (uint64_t)l0;
+      uint4 blk = philox_block16(q, e0 >> 4);
+      int j = (int)(e0 & 15u);
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
-        const int64_t l = l0 + i;
+        if (j == 16) {  // the run crossed into the next block (unaligned row starts only)
+          blk = philox_block16(q, (e0 >> 4) + 1);
+          j = 0;
+        }
+        code[i] = (int)philox_offset_code(v[i], sp, philox_byte(blk, j)) - (qmax + 1);
+        ++j;
+      }
+    } else {
+      float u[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
         float un = 1.0f;
-        if (l < p.out_len)
-          un = p.noise_transposed ? q.noise[(int64_t)c * p.out_len + l] : q.noise[l * (int64_t)p.cols + c];
+        if (ROUND == HOT_ROUND_STOCH_NOISE) {
+          const int64_t l = l0 + i;
+          if (l < p.out_len)
+            un = p.noise_transposed ? q.noise[(int64_t)c * p.out_len + l] : q.noise[l * (int64_t)p.cols + c];
+        }
         u[i] = un;
       }
-    }
-    int code[8];
 #pragma unroll
-    for (int i = 0; i < 8; ++i)
-      code[i] = quantise_one<ROUND>(v[i], sp, ROUND == HOT_ROUND_STOCH_NOISE ? u[i] : 0.0f,
-                                    ROUND == HOT_ROUND_STOCH_PHILOX ? r16[i] : 0u, qmax);
+      for (int i = 0; i < 8; ++i) code[i] = quantise_one<ROUND>(v[i], sp, u[i], qmax);
+    }
     if (p.store4) {
       uint32_t w = 0;
 #pragma unroll

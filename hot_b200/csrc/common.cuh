@@ -65,19 +65,26 @@ __device__ __forceinline__ uint4 philox4x32_10(uint32_t c0, uint32_t c1, uint32_
   return make_uint4(c0, c1, c2, c3);
 }
 
-// The eight 16-bit outputs of Philox block g (elements 8g .. 8g+7): element j takes the low
-// (j even) or high (j odd) half of output word j / 2.
-__device__ __forceinline__ void philox_bits8(const QuantDev& q, uint64_t g, uint32_t (&r)[8]) {
-  const uint4 w = philox4x32_10((uint32_t)g, (uint32_t)(g >> 32), q.o0, q.o1, q.k0, q.k1);
-  r[0] = w.x & 0xFFFFu; r[1] = w.x >> 16;
-  r[2] = w.y & 0xFFFFu; r[3] = w.y >> 16;
-  r[4] = w.z & 0xFFFFu; r[5] = w.z >> 16;
-  r[6] = w.w & 0xFFFFu; r[7] = w.w >> 16;
+// The 16 random bytes of Philox block g: the stochastic-rounding bits of elements 16g .. 16g+15
+// (element 16g + j takes byte j, little-endian within the words x, y, z, w).
+__device__ __forceinline__ uint4 philox_block16(const QuantDev& q, uint64_t g) {
+  return philox4x32_10((uint32_t)g, (uint32_t)(g >> 32), q.o0, q.o1, q.k0, q.k1);
+}
+__device__ __forceinline__ uint32_t philox_byte(const uint4& r, int j) {
+  const uint32_t w = j < 4 ? r.x : (j < 8 ? r.y : (j < 12 ? r.z : r.w));
+  return (w >> (8 * (j & 3))) & 0xFFu;
 }
 
-// scale of a quantiser from an abs-max: s = mx / qmax, and the divisor d = s + eps the values are
-// divided by (both fp32, round-to-nearest: the reference divides, it does not multiply by a
-// reciprocal).
+// ---- packed fp32 (two IEEE round-to-nearest operations per instruction on sm_100) -------
+__device__ __forceinline__ float2 add2(float2 a, float2 b) { return __fadd2_rn(a, b); }
+__device__ __forceinline__ float2 sub2(float2 a, float2 b) {
+  return __ffma2_rn(b, make_float2(-1.0f, -1.0f), a);  // a - b: the product is exact, one rounding
+}
+
+// x / d, correctly rounded, for a divisor shared by many elements: q0 = RN(x * r) with
+// r = RN(1 / d), residual e = x - q0 * d (exact in an FMA), q = RN(q0 + e * r).  Equal to IEEE
+// division for the ranges a quantiser sees (|x| <= absmax, d = absmax / qmax + eps); the parity
+// tests compare against true division bit for bit.
 struct Divisor {
   float d;  // the divisor
   float r;  // RN(1 / d)
@@ -90,20 +97,28 @@ __device__ __forceinline__ Divisor make_divisor(float d) {
   return v;
 }
 
-// x / d, correctly rounded, for a divisor shared by many elements: q0 = RN(x * r), residual
-// e = x - q0 * d (exact in an FMA), q = RN(q0 + e * r).  Equal to IEEE division for the ranges a
-// quantiser sees (|x| <= absmax, d = absmax / qmax + eps); the parity tests compare against true
-// division bit for bit.
 __device__ __forceinline__ float div_exact(float x, const Divisor& v) {
   const float q0 = __fmul_rn(x, v.r);
   const float e = __fmaf_rn(-q0, v.d, x);
   return __fmaf_rn(e, v.r, q0);
 }
 
+__device__ __forceinline__ float2 div2_exact(float2 x, const Divisor& v) {
+  const float2 r2 = make_float2(v.r, v.r), nd2 = make_float2(-v.d, -v.d);
+  const float2 q0 = __fmul2_rn(x, r2);
+  const float2 e = __ffma2_rn(q0, nd2, x);
+  return __ffma2_rn(e, r2, q0);
+}
+
+// Everything a quantiser derives from an abs-max: the scale s = mx / qmax the caller gets back,
+// the divisor s + eps (fp32, round-to-nearest: the reference divides, it does not multiply by
+// a reciprocal), and the same divisor times 2^-8 with the offset (qmax + 1) * 2^8 for the
+// fixed-point stochastic rounding of the Philox path.
 struct ScalePair {
-  float s;      // the scale the caller gets back
+  float s;
   Divisor dv;   // divide by s + eps
-  Divisor dv16; // divide by (s + eps) * 2^-16: the quotient scaled by 65536, exactly
+  Divisor dv8;  // divide by (s + eps) * 2^-8: the quotient scaled by 256, exactly
+  float bias8;  // (qmax + 1) * 256
 };
 
 __device__ __forceinline__ ScalePair scale_from_absmax(float mx, float qmax) {
@@ -111,30 +126,33 @@ __device__ __forceinline__ ScalePair scale_from_absmax(float mx, float qmax) {
   p.s = __fdiv_rn(mx, qmax);
   const float d = __fadd_rn(p.s, kEps);
   p.dv = make_divisor(d);
-  p.dv16 = make_divisor(d * 1.52587890625e-05f);  // * 2^-16, exact
+  p.dv8 = make_divisor(d * 0.00390625f);  // * 2^-8, exact
+  p.bias8 = (qmax + 1.0f) * 256.0f;
   return p;
 }
 
-// One code, |code| <= qmax.  ROUND: hot_rounding.
+// Philox-path rounding of one value, as an offset code in [1, 2 * qmax + 1] (code + qmax + 1):
+//   t = RN_int( RN(x / d * 256) + (qmax + 1) * 256 );   offset code = (t + R) >> 8
+// with R the element's random byte: the quotient is rounded to the nearest 1/256, then rounded
+// stochastically to an integer (up with probability frac * 256 / 256).  Because |x / d| <=
+// qmax * (1 + 2^-22) the offset code stays within [1, 2 * qmax + 1] without clamping.
+__device__ __forceinline__ uint32_t philox_offset_code(float x, const ScalePair& sp, uint32_t r8) {
+  const float yb = __fadd_rn(div_exact(x, sp.dv8), sp.bias8);
+  return (__float2uint_rn(yb) + r8) >> 8;
+}
+
+// One code for the deterministic and the explicit-noise modes, |code| <= qmax.
 //   nearest : round-half-even of y = x / d (torch.round)
 //   noise   : sign(y) * (floor|y| + [u < frac|y|]) with the caller's uniform u
-//   Philox  : the same predicate in fixed point with the 16-bit Philox output R:
-//             T = floor(|y| * 2^16); |code| = (T + R) >> 16, i.e. round up iff
-//             (65535 - R) / 65536 < floor(frac * 2^16) / 2^16
 template <int ROUND>
-__device__ __forceinline__ int quantise_one(float x, const ScalePair& sp, float u, uint32_t r16, int qmax) {
-  int mag;
+__device__ __forceinline__ int quantise_one(float x, const ScalePair& sp, float u, int qmax) {
   if (ROUND == HOT_ROUND_NEAREST) {
     const int c = __float2int_rn(div_exact(x, sp.dv));
     return max(-qmax, min(qmax, c));
-  } else if (ROUND == HOT_ROUND_STOCH_PHILOX) {
-    const float a16 = fabsf(div_exact(x, sp.dv16));
-    mag = (int)((__float2uint_rd(a16) + r16) >> 16);
-  } else {
-    const float a = fabsf(div_exact(x, sp.dv));
-    const float f = floorf(a);
-    mag = (int)f + ((u < __fsub_rn(a, f)) ? 1 : 0);
   }
+  const float a = fabsf(div_exact(x, sp.dv));
+  const float f = floorf(a);
+  int mag = (int)f + ((u < __fsub_rn(a, f)) ? 1 : 0);
   mag = min(mag, qmax);  // the abs-max element can land an ulp above qmax and round up
   return (x < 0.0f) ? -mag : mag;
 }

@@ -1,10 +1,12 @@
 // Fused block-Hadamard transform along the contiguous dim + INT4/INT8 quantisation.
 //
-// Data layout: every thread owns vectors of 8 consecutive elements (two 128-bit loads for
-// fp32, one for bf16).  Butterfly stages h = 1, 2, 4 run inside the thread; stages
-// h = 8, 16, 32 exchange with lane ^ (h / 8) through warp shuffles, so a Hadamard block of
-// order n <= 64 lives in n / 8 adjacent lanes.  The arithmetic per stage is (x + y, x - y)
-// on the pair (i, i + h), the order the CPU oracle fixes.
+// Data layout: every thread owns runs of 16 consecutive elements, loaded with 128-bit loads as
+// two 8-element halves A and B and held as eight packed pairs (A_i, B_i).  Blackwell's packed
+// fp32 instructions (add/fma .f32x2, IEEE round-to-nearest per lane) then run the butterfly
+// stages h = 1, 2, 4 of both halves at once; stage h = 8 combines A_i with B_i; stages h = 16
+// and 32 exchange with lane ^ 1 and lane ^ 2 through warp shuffles.  Per stage the arithmetic
+// is (x + y, x - y) on the pair (i, i + h): the order the CPU oracle fixes.  The division by
+// the scale and the rounding run packed as well.
 //
 // Per-row ("per-token") scale: one launch; a row is held in registers by `tpr` threads,
 // reduced to its abs-max, then quantised and stored.
@@ -16,86 +18,153 @@ namespace hot {
 namespace {
 
 constexpr int kThreads = 256;
-constexpr int kVmax = 8;  // vectors per thread in the per-row kernel: cols <= 8 * 8 * 256
+constexpr int kVmax = 4;  // 16-element runs per thread in the per-row kernel: cols <= 4 * 16 * 256
 
-__device__ __forceinline__ void butterfly8(float (&v)[8], int n) {
+// ---- loads: 16 consecutive elements -> eight (A_i, B_i) pairs ----------------------------
+template <typename T>
+struct Load16;
+template <>
+struct Load16<float> {
+  static __device__ __forceinline__ void run(const float* p, float2 (&v)[8]) {
+    const float4* q = reinterpret_cast<const float4*>(p);
+    const float4 a0 = __ldg(q), a1 = __ldg(q + 1), b0 = __ldg(q + 2), b1 = __ldg(q + 3);
+    v[0] = make_float2(a0.x, b0.x); v[1] = make_float2(a0.y, b0.y);
+    v[2] = make_float2(a0.z, b0.z); v[3] = make_float2(a0.w, b0.w);
+    v[4] = make_float2(a1.x, b1.x); v[5] = make_float2(a1.y, b1.y);
+    v[6] = make_float2(a1.z, b1.z); v[7] = make_float2(a1.w, b1.w);
+  }
+};
+template <>
+struct Load16<__nv_bfloat16> {
+  static __device__ __forceinline__ void run(const __nv_bfloat16* p, float2 (&v)[8]) {
+    const uint4* q = reinterpret_cast<const uint4*>(p);
+    const uint4 a = __ldg(q), b = __ldg(q + 1);
+    const uint32_t wa[4] = {a.x, a.y, a.z, a.w}, wb[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      v[2 * k] = make_float2(__uint_as_float(wa[k] << 16), __uint_as_float(wb[k] << 16));
+      v[2 * k + 1] = make_float2(__uint_as_float(wa[k] & 0xFFFF0000u), __uint_as_float(wb[k] & 0xFFFF0000u));
+    }
+  }
+};
+
+__device__ __forceinline__ void zero16(float2 (&v)[8]) {
+#pragma unroll
+  for (int i = 0; i < 8; ++i) v[i] = make_float2(0.0f, 0.0f);
+}
+
+// Order-n transform of the 16-element run (n <= 16 entirely in registers, 32 and 64 with the
+// neighbouring lanes).  Must be executed by all 32 lanes when n > 16.
+__device__ __forceinline__ void butterfly16(float2 (&v)[8], int n, int lane) {
   if (n >= 2) {
 #pragma unroll
     for (int i = 0; i < 8; i += 2) {
-      const float a = v[i], b = v[i + 1];
-      v[i] = a + b;
-      v[i + 1] = a - b;
+      const float2 a = v[i], b = v[i + 1];
+      v[i] = add2(a, b);
+      v[i + 1] = sub2(a, b);
     }
   }
   if (n >= 4) {
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
       if ((i & 2) == 0) {
-        const float a = v[i], b = v[i + 2];
-        v[i] = a + b;
-        v[i + 2] = a - b;
+        const float2 a = v[i], b = v[i + 2];
+        v[i] = add2(a, b);
+        v[i + 2] = sub2(a, b);
       }
     }
   }
   if (n >= 8) {
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-      const float a = v[i], b = v[i + 4];
-      v[i] = a + b;
-      v[i + 4] = a - b;
+      const float2 a = v[i], b = v[i + 4];
+      v[i] = add2(a, b);
+      v[i + 4] = sub2(a, b);
     }
   }
-}
-
-// Stages h = 8 .. n/2 across lanes.  Must be executed by all 32 lanes.
-__device__ __forceinline__ void butterfly_lanes(float (&v)[8], int n, int lane) {
-  for (int h = 8; h < n; h <<= 1) {
-    const int m = h >> 3;
-    const bool upper = (lane & m) != 0;
+  if (n >= 16) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) v[i] = make_float2(__fadd_rn(v[i].x, v[i].y), __fsub_rn(v[i].x, v[i].y));
+  }
+  for (int h = 16; h < n; h <<= 1) {
+    const int m = h >> 4;
+    const float sg = (lane & m) ? -1.0f : 1.0f;  // upper half: partner - mine; lower: mine + partner
+    const float2 sg2 = make_float2(sg, sg);
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
-      const float o = __shfl_xor_sync(0xFFFFFFFFu, v[i], m);
-      v[i] = upper ? (o - v[i]) : (v[i] + o);
+      float2 o;
+      o.x = __shfl_xor_sync(0xFFFFFFFFu, v[i].x, m);
+      o.y = __shfl_xor_sync(0xFFFFFFFFu, v[i].y, m);
+      v[i] = __ffma2_rn(v[i], sg2, o);  // exact product, one rounding: o +- mine
     }
   }
 }
 
-__device__ __forceinline__ float absmax8(const float (&v)[8]) {
+__device__ __forceinline__ float absmax16(const float2 (&v)[8]) {
   float m = 0.0f;
 #pragma unroll
-  for (int i = 0; i < 8; ++i) m = fmaxf(m, fabsf(v[i]));
+  for (int i = 0; i < 8; ++i) m = fmaxf(m, fmaxf(fabsf(v[i].x), fabsf(v[i].y)));
   return m;
 }
 
-// Quantise 8 transformed values whose first logical element index is `e0` (a multiple of 8)
-// and store them at `dst` (already offset to the vector).
+// Quantise the 16 transformed values whose first logical element index is `e0` (a multiple of
+// 16) and store them at `dst` (8 bytes for INT4, 16 for INT8).
 template <int ROUND, int STORE4>
-__device__ __forceinline__ void quantise_store8(const float (&v)[8], const ScalePair& sp, const QuantDev& q, uint64_t e0,
-                                                uint8_t* dst) {
-  float u[8];
-  uint32_t r16[8];
-  if (ROUND == HOT_ROUND_STOCH_PHILOX) philox_bits8(q, e0 >> 3, r16);
-  if (ROUND == HOT_ROUND_STOCH_NOISE) Load8<float>::run(q.noise + e0, u);
-  const int qmax = (int)q.qmax;
-  int c[8];
+__device__ __forceinline__ void quantise_store16(const float2 (&v)[8], const ScalePair& sp, const QuantDev& q, uint64_t e0,
+                                                 uint8_t* dst) {
+  uint32_t wa0 = 0, wa1 = 0, wb0 = 0, wb1 = 0;  // INT4: wa0 = A, wb0 = B; INT8: (wa0, wa1) = A, (wb0, wb1) = B
+  if (ROUND == HOT_ROUND_STOCH_PHILOX) {
+    const uint4 r = philox_block16(q, e0 >> 4);
+    const uint32_t ra[2] = {r.x, r.y}, rb[2] = {r.z, r.w};
+    const float2 bias = make_float2(sp.bias8, sp.bias8);
 #pragma unroll
-  for (int i = 0; i < 8; ++i)
-    c[i] = quantise_one<ROUND>(v[i], sp, ROUND == HOT_ROUND_STOCH_NOISE ? u[i] : 0.0f,
-                               ROUND == HOT_ROUND_STOCH_PHILOX ? r16[i] : 0u, qmax);
-  if (STORE4) {
-    uint32_t w = 0;
-#pragma unroll
-    for (int i = 0; i < 8; ++i) w |= (uint32_t)(c[i] & 0xF) << (4 * i);
-    *reinterpret_cast<uint32_t*>(dst) = w;
-  } else {
-    uint32_t w0 = 0, w1 = 0;
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      w0 |= (uint32_t)(c[i] & 0xFF) << (8 * i);
-      w1 |= (uint32_t)(c[i + 4] & 0xFF) << (8 * i);
+    for (int i = 0; i < 8; ++i) {
+      const float2 yb = add2(div2_exact(v[i], sp.dv8), bias);
+      const uint32_t ca = (__float2uint_rn(yb.x) + ((ra[i >> 2] >> (8 * (i & 3))) & 0xFFu)) >> 8;
+      const uint32_t cb = (__float2uint_rn(yb.y) + ((rb[i >> 2] >> (8 * (i & 3))) & 0xFFu)) >> 8;
+      if (STORE4) {
+        wa0 |= ca << (4 * i);
+        wb0 |= cb << (4 * i);
+      } else {
+        if (i < 4) { wa0 |= ca << (8 * i); wb0 |= cb << (8 * i); }
+        else { wa1 |= ca << (8 * (i - 4)); wb1 |= cb << (8 * (i - 4)); }
+      }
     }
-    *reinterpret_cast<uint2*>(dst) = make_uint2(w0, w1);
+    // The codes above carry the offset qmax + 1 = 2^(bits-1) that made them non-negative.
+    // Removing it is a flip of that bit per nibble / byte; codes narrower than their nibble /
+    // byte are then sign-extended from that bit.
+    const uint32_t off = (uint32_t)(q.qmax + 1.0f);
+    const uint32_t lanes = STORE4 ? 0x11111111u : 0x01010101u;
+    const uint32_t ext = ((STORE4 ? 0x10u : 0x100u) - 2u * off);  // the bits above the sign bit (0 if none)
+    uint32_t* ws[4] = {&wa0, &wb0, &wa1, &wb1};
+#pragma unroll
+    for (int k = 0; k < (STORE4 ? 2 : 4); ++k) {
+      uint32_t w = *ws[k] ^ (off * lanes);
+      if (ext) w |= ((w & (off * lanes)) / off) * ext;
+      *ws[k] = w;
+    }
+  } else {
+    float ua[8], ub[8];
+    if (ROUND == HOT_ROUND_STOCH_NOISE) {
+      Load8<float>::run(q.noise + e0, ua);
+      Load8<float>::run(q.noise + e0 + 8, ub);
+    }
+    const int qmax = (int)q.qmax;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int ca = quantise_one<ROUND>(v[i].x, sp, ROUND == HOT_ROUND_STOCH_NOISE ? ua[i] : 0.0f, qmax);
+      const int cb = quantise_one<ROUND>(v[i].y, sp, ROUND == HOT_ROUND_STOCH_NOISE ? ub[i] : 0.0f, qmax);
+      if (STORE4) {
+        wa0 |= (uint32_t)(ca & 0xF) << (4 * i);
+        wb0 |= (uint32_t)(cb & 0xF) << (4 * i);
+      } else {
+        if (i < 4) { wa0 |= (uint32_t)(ca & 0xFF) << (8 * i); wb0 |= (uint32_t)(cb & 0xFF) << (8 * i); }
+        else { wa1 |= (uint32_t)(ca & 0xFF) << (8 * (i - 4)); wb1 |= (uint32_t)(cb & 0xFF) << (8 * (i - 4)); }
+      }
+    }
   }
+  if (STORE4) *reinterpret_cast<uint2*>(dst) = make_uint2(wa0, wb0);
+  else *reinterpret_cast<uint4*>(dst) = make_uint4(wa0, wa1, wb0, wb1);
 }
 
 // ---------------------------------------------------------------------------------------
@@ -110,26 +179,26 @@ __global__ void __launch_bounds__(kThreads) row_ht_quant_rowscale_kernel(
   const int rows_per_cta = kThreads / tpr;
   const int64_t row = (int64_t)blockIdx.x * rows_per_cta + threadIdx.x / tpr;
   const int t = threadIdx.x % tpr;
-  const int nvec = cols >> 3;
-  const int nv = (nvec + tpr - 1) / tpr;  // uniform over the CTA
+  const int nrun = cols >> 4;
+  const int nv = (nrun + tpr - 1) / tpr;  // uniform over the CTA
   const bool row_ok = row < rows;
   const T* xr = x + (row_ok ? row : 0) * ldx;
 
-  float v[kVmax][8];
+  float2 v[kVmax][8];
   float mx = 0.0f;
 #pragma unroll
   for (int j = 0; j < kVmax; ++j) {
     if (j < nv) {
-      const int vi = t + j * tpr;
-      if (row_ok && vi < nvec) {
-        Load8<T>::run(xr + (int64_t)vi * 8, v[j]);
-      } else {
+      const int ri = t + j * tpr;
+      if (row_ok && ri < nrun) Load16<T>::run(xr + (int64_t)ri * 16, v[j]);
+      else zero16(v[j]);
+    }
+  }
 #pragma unroll
-        for (int i = 0; i < 8; ++i) v[j][i] = 0.0f;
-      }
-      butterfly8(v[j], n);
-      butterfly_lanes(v[j], n, lane);
-      mx = fmaxf(mx, absmax8(v[j]));
+  for (int j = 0; j < kVmax; ++j) {
+    if (j < nv) {
+      butterfly16(v[j], n, lane);
+      mx = fmaxf(mx, absmax16(v[j]));
     }
   }
   mx = warp_max(mx);
@@ -147,33 +216,33 @@ __global__ void __launch_bounds__(kThreads) row_ht_quant_rowscale_kernel(
 #pragma unroll
   for (int j = 0; j < kVmax; ++j) {
     if (j < nv) {
-      const int vi = t + j * tpr;
-      if (vi < nvec) {
-        const uint64_t e0 = (uint64_t)row * (uint64_t)cols + (uint64_t)vi * 8u;
-        quantise_store8<ROUND, STORE4>(v[j], sp, q, e0, cr + (int64_t)vi * (STORE4 ? 4 : 8));
+      const int ri = t + j * tpr;
+      if (ri < nrun) {
+        const uint64_t e0 = (uint64_t)row * (uint64_t)cols + (uint64_t)ri * 16u;
+        quantise_store16<ROUND, STORE4>(v[j], sp, q, e0, cr + (int64_t)ri * (STORE4 ? 8 : 16));
       }
     }
   }
 }
 
 // ---------------------------------------------------------------------------------------
-// per-tensor scale: pass 1 (abs-max) and pass 2 (quantise), streaming over vectors
+// per-tensor scale: pass 1 (abs-max) and pass 2 (quantise), streaming over 16-element runs
 // ---------------------------------------------------------------------------------------
-constexpr int kUnroll = 4;
+constexpr int kUnroll = 2;
 
-// Where vector `item` (row-major over rows x nvec) lives.  CONTIG: pitch == cols, so the tensor is
-// one flat run of vectors and no division is needed.
+// Where run `item` (row-major over rows x nrun) lives.  CONTIG: pitch == cols, so the tensor is
+// one flat sequence of runs and no division is needed.
 template <bool CONTIG>
-__device__ __forceinline__ void locate(int64_t item, int nvec, int64_t ldx, int64_t ld_codes, int code_bytes,
+__device__ __forceinline__ void locate(int64_t item, int nrun, int64_t ldx, int64_t ld_codes, int code_bytes,
                                        int64_t& x_off, int64_t& c_off) {
   if (CONTIG) {
-    x_off = item * 8;
+    x_off = item * 16;
     c_off = item * code_bytes;
   } else {
-    const int64_t row = item / nvec;
-    const int vi = (int)(item - row * nvec);
-    x_off = row * ldx + (int64_t)vi * 8;
-    c_off = row * ld_codes + (int64_t)vi * code_bytes;
+    const int64_t row = item / nrun;
+    const int ri = (int)(item - row * nrun);
+    x_off = row * ldx + (int64_t)ri * 16;
+    c_off = row * ld_codes + (int64_t)ri * code_bytes;
   }
 }
 
@@ -181,30 +250,28 @@ template <typename T, bool CONTIG>
 __global__ void __launch_bounds__(kThreads) row_ht_absmax_kernel(const T* __restrict__ x, int64_t rows, int cols,
                                                                  int64_t ldx, int n, uint32_t* __restrict__ absmax) {
   const int lane = threadIdx.x & 31;
-  const int nvec = cols >> 3;
-  const int64_t total = rows * nvec;
+  const int nrun = cols >> 4;
+  const int64_t total = rows * nrun;
   const int64_t warp_id = ((int64_t)blockIdx.x * kThreads + threadIdx.x) >> 5;
   const int64_t nwarps = ((int64_t)gridDim.x * kThreads) >> 5;
   float mx = 0.0f;
   for (int64_t base = warp_id * (32 * kUnroll); base < total; base += nwarps * (32 * kUnroll)) {
-    float v[kUnroll][8];
+    float2 v[kUnroll][8];
 #pragma unroll
     for (int u = 0; u < kUnroll; ++u) {
       const int64_t item = base + u * 32 + lane;
       if (item < total) {
         int64_t xo, co;
-        locate<CONTIG>(item, nvec, ldx, 0, 0, xo, co);
-        Load8<T>::run(x + xo, v[u]);
+        locate<CONTIG>(item, nrun, ldx, 0, 0, xo, co);
+        Load16<T>::run(x + xo, v[u]);
       } else {
-#pragma unroll
-        for (int i = 0; i < 8; ++i) v[u][i] = 0.0f;
+        zero16(v[u]);
       }
     }
 #pragma unroll
     for (int u = 0; u < kUnroll; ++u) {
-      butterfly8(v[u], n);
-      butterfly_lanes(v[u], n, lane);
-      mx = fmaxf(mx, absmax8(v[u]));
+      butterfly16(v[u], n, lane);
+      mx = fmaxf(mx, absmax16(v[u]));
     }
   }
   mx = warp_max(mx);
@@ -216,14 +283,14 @@ __global__ void __launch_bounds__(kThreads) row_ht_quant_tensorscale_kernel(
     const T* __restrict__ x, int64_t rows, int cols, int64_t ldx, int n, QuantDev q, uint8_t* __restrict__ codes,
     int64_t ld_codes, float* __restrict__ scales, const uint32_t* __restrict__ absmax) {
   const int lane = threadIdx.x & 31;
-  const int nvec = cols >> 3;
-  const int64_t total = rows * nvec;
+  const int nrun = cols >> 4;
+  const int64_t total = rows * nrun;
   const int64_t warp_id = ((int64_t)blockIdx.x * kThreads + threadIdx.x) >> 5;
   const int64_t nwarps = ((int64_t)gridDim.x * kThreads) >> 5;
   const ScalePair sp = scale_from_absmax(__uint_as_float(*absmax), q.qmax);
   if (blockIdx.x == 0 && threadIdx.x == 0) scales[0] = sp.s;
   for (int64_t base = warp_id * (32 * kUnroll); base < total; base += nwarps * (32 * kUnroll)) {
-    float v[kUnroll][8];
+    float2 v[kUnroll][8];
     int64_t coff[kUnroll];
 #pragma unroll
     for (int u = 0; u < kUnroll; ++u) {
@@ -231,26 +298,25 @@ __global__ void __launch_bounds__(kThreads) row_ht_quant_tensorscale_kernel(
       coff[u] = -1;
       if (item < total) {
         int64_t xo;
-        locate<CONTIG>(item, nvec, ldx, ld_codes, STORE4 ? 4 : 8, xo, coff[u]);
-        Load8<T>::run(x + xo, v[u]);
+        locate<CONTIG>(item, nrun, ldx, ld_codes, STORE4 ? 8 : 16, xo, coff[u]);
+        Load16<T>::run(x + xo, v[u]);
       } else {
-#pragma unroll
-        for (int i = 0; i < 8; ++i) v[u][i] = 0.0f;
+        zero16(v[u]);
       }
     }
 #pragma unroll
     for (int u = 0; u < kUnroll; ++u) {
-      butterfly8(v[u], n);
-      butterfly_lanes(v[u], n, lane);
-      // logical element index of the vector: row * cols + col == item * 8 in either layout
-      if (coff[u] >= 0) quantise_store8<ROUND, STORE4>(v[u], sp, q, (uint64_t)(base + u * 32 + lane) * 8u, codes + coff[u]);
+      butterfly16(v[u], n, lane);
+      // logical element index of the run: row * cols + col == item * 16 in either layout
+      if (coff[u] >= 0)
+        quantise_store16<ROUND, STORE4>(v[u], sp, q, (uint64_t)(base + u * 32 + lane) * 16u, codes + coff[u]);
     }
   }
 }
 
-int grid_for(int64_t total_vec, int device_sms) {
+int grid_for(int64_t total_runs, int device_sms) {
   const int64_t per_cta = (int64_t)kThreads * kUnroll;
-  int64_t want = (total_vec + per_cta - 1) / per_cta;
+  int64_t want = (total_runs + per_cta - 1) / per_cta;
   const int64_t cap = (int64_t)device_sms * 8;  // 8 resident CTAs of 256 threads per SM
   if (want > cap) want = cap;
   if (want < 1) want = 1;
@@ -262,18 +328,18 @@ int launch_typed(const T* x, int64_t rows, int cols, int64_t ldx, int n, const h
                  int64_t ld_codes, float* scales, uint32_t* absmax_ws, cudaStream_t st, int sms) {
   const QuantDev q = make_quant_dev(hq);
   if (hq.scale_mode == HOT_SCALE_ROW) {
-    const int nvec = cols >> 3;
+    const int nrun = cols >> 4;
     int tpr = 32;
-    while (tpr < kThreads && (nvec + tpr - 1) / tpr > kVmax) tpr <<= 1;
-    if ((nvec + tpr - 1) / tpr > kVmax)
+    while (tpr < kThreads && (nrun + tpr - 1) / tpr > kVmax) tpr <<= 1;
+    if ((nrun + tpr - 1) / tpr > kVmax)
       HOT_FAIL(HOT_ERR_UNSUPPORTED, "hot_row_ht_quant: per-row scale supports cols <= %d (got %d)",
-               kVmax * 8 * kThreads, cols);
+               kVmax * 16 * kThreads, cols);
     const int rows_per_cta = kThreads / tpr;
     const int64_t grid = (rows + rows_per_cta - 1) / rows_per_cta;
     row_ht_quant_rowscale_kernel<T, ROUND, STORE4>
         <<<(unsigned)grid, kThreads, 0, st>>>(x, rows, cols, ldx, n, q, codes, ld_codes, scales, tpr);
   } else {
-    const int grid = grid_for(rows * (cols >> 3), sms);
+    const int grid = grid_for(rows * (cols >> 4), sms);
     HOT_CUDA(cudaMemsetAsync(absmax_ws, 0, sizeof(uint32_t), st));
     const bool contig = ldx == cols && ld_codes == (STORE4 ? cols / 2 : cols);
     if (contig) {
@@ -322,20 +388,20 @@ extern "C" int hot_row_ht_quant(const void* x, int dtype, int64_t rows, int64_t 
   if (int rc = validate_quant(q, "hot_row_ht_quant")) return rc;
   if (order < 1 || order > 64 || (order & (order - 1)))
     HOT_FAIL(HOT_ERR_UNSUPPORTED, "hot_row_ht_quant: order %d not a power of two in [1, 64]", order);
-  if (cols % 8 != 0 || cols % order != 0 || cols > (1 << 30))
-    HOT_FAIL(HOT_ERR_UNSUPPORTED, "hot_row_ht_quant: cols %lld must be a multiple of 8 and of the order %d",
+  if (cols % 16 != 0 || cols % order != 0 || cols > (1 << 30))
+    HOT_FAIL(HOT_ERR_UNSUPPORTED, "hot_row_ht_quant: cols %lld must be a multiple of 16 and of the order %d",
              (long long)cols, order);
   const int esz = dtype == HOT_F32 ? 4 : 2;
   if (ldx < cols || (ldx * esz) % 16 != 0 || ((uintptr_t)x) % 16 != 0)
     HOT_FAIL(HOT_ERR_ARG, "hot_row_ht_quant: x and its pitch must be 16-byte aligned, ldx >= cols");
   const int64_t row_bytes = q->storage == HOT_STORE_INT4 ? cols / 2 : cols;
-  if (ld_codes < row_bytes || ld_codes % 8 != 0 || ((uintptr_t)codes) % 8 != 0)
-    HOT_FAIL(HOT_ERR_ARG, "hot_row_ht_quant: codes pitch %lld must be >= %lld and 8-byte aligned", (long long)ld_codes,
-             (long long)row_bytes);
+  if (ld_codes < row_bytes || ld_codes % 8 != 0 || (q->storage == HOT_STORE_INT8 && ld_codes % 16 != 0) ||
+      ((uintptr_t)codes) % 16 != 0)
+    HOT_FAIL(HOT_ERR_ARG, "hot_row_ht_quant: codes pitch %lld must be >= %lld and 16-byte aligned (8 for INT4)",
+             (long long)ld_codes, (long long)row_bytes);
   if (q->scale_mode == HOT_SCALE_TENSOR && !absmax_ws) HOT_FAIL(HOT_ERR_ARG, "hot_row_ht_quant: absmax_ws is null");
   if (q->rounding == HOT_ROUND_STOCH_NOISE && ((uintptr_t)q->noise) % 16 != 0)
     HOT_FAIL(HOT_ERR_ARG, "hot_row_ht_quant: noise must be 16-byte aligned");
-  if (rows == 0) return HOT_OK;
   cudaStream_t st = (cudaStream_t)stream;
   const int sms = device_sm_count();
   if (sms <= 0) return HOT_ERR_CUDA;

@@ -56,8 +56,8 @@ def _quantise_2d(x: Tensor, bits: int, rounding: str, scale: str):
     x2 = x if x.dim() == 2 else x.reshape(-1, x.shape[-1])
     if not x2.is_contiguous():
         x2 = x2.contiguous()
-    pad = (-x2.shape[1]) % 8
-    if pad:  # the kernels work on vectors of 8; zero columns change neither abs-max nor codes
+    pad = (-x2.shape[1]) % 16
+    if pad:  # the kernels work on runs of 16; zero columns change neither abs-max nor codes
         x2 = F.pad(x2, (0, pad))
     q = ops.Quant(bits, "int8", rounding, scale, _seed(), _next_offset())
     codes, scales = ops.row_ht_quant(x2, 1, q)

@@ -58,7 +58,7 @@ int hot_abi_version(void);
 /*
  * Fused block-Hadamard transform along the LAST (contiguous) dim + quantisation.
  *   x      [rows, cols] row-major, pitch ldx elements, dtype HOT_F32 | HOT_BF16
- *   order  Hadamard block order: 1, 2, 4, ..., 64; cols % max(order, 8) == 0
+ *   order  Hadamard block order: 1, 2, 4, ..., 64; cols % max(order, 16) == 0
  *   codes  HOT_STORE_INT8: [rows, cols] int8, pitch ld_codes bytes
  *          HOT_STORE_INT4: [rows, cols/2] bytes, pitch ld_codes bytes
  *   scales [1] (HOT_SCALE_TENSOR) or [rows] (HOT_SCALE_ROW): s = absmax / (2^(bits-1)-1)

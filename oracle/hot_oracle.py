@@ -177,22 +177,23 @@ def _qmax(bits: int) -> F32:
     return F32(2 ** (bits - 1) - 1)
 
 
-class Fixed16(np.ndarray):
-    """Marker type for uniforms k/65536 that are to be compared in 16-bit fixed point: a code
-    rounds up iff u < floor(frac * 2^16) / 2^16 (the production Philox path of the kernels).
-    Plain arrays keep the reference's float predicate u < frac."""
+class PhiloxBytes(np.ndarray):
+    """Marker type: one random byte R per element, for the kernels' production rounding path
+    (8.8 fixed point):  t = rint(fl(y * 256 + (qmax + 1) * 256));  code = ((t + R) >> 8) - (qmax + 1).
+    Plain float arrays keep the reference's predicate  u < frac."""
 
 
-def _round_codes(y: np.ndarray, u: np.ndarray | None) -> np.ndarray:
+def _round_codes(y: np.ndarray, u: np.ndarray | None, qmax: F32 = F32(0)) -> np.ndarray:
     if u is None:  # torch.round: half to even (utils/quant_matmul.py:47,115)
         return np.rint(y).astype(np.int32)
+    if isinstance(u, PhiloxBytes):
+        off = int(qmax) + 1
+        yb = (y.astype(F32) * F32(256.0) + F32(off * 256)).astype(F32)   # two fp32 roundings, as on the GPU
+        t = np.rint(yb).astype(np.int64)
+        return (((t + np.asarray(u).astype(np.int64)) >> 8) - off).astype(np.int32)
     a = np.abs(y)
     f = np.floor(a)
     frac = a - f
-    if isinstance(u, Fixed16):
-        t = np.floor(a * F32(65536.0))                      # exact: a power-of-two scaling
-        frac = (t - f * F32(65536.0)) / F32(65536.0)        # floor(frac * 2^16) / 2^16, exact
-        u = np.asarray(u)
     flip = (np.asarray(u, dtype=F32) < frac).astype(F32)  # torch.bernoulli(frac) == (u < frac)
     return (np.sign(y) * (f + flip)).astype(np.int32)
 
@@ -204,7 +205,7 @@ def quant_tensor(x: np.ndarray, bits: int, u: np.ndarray | None):
     mx = np.max(np.abs(x)) if x.size else F32(0)
     s = F32(mx / _qmax(bits))
     y = np.clip(x, -mx, mx) / F32(s + EPS)
-    return _round_codes(y, u), s
+    return _round_codes(y, u, _qmax(bits)), s
 
 
 def quant_rows(x: np.ndarray, bits: int, u: np.ndarray | None):
@@ -214,7 +215,7 @@ def quant_rows(x: np.ndarray, bits: int, u: np.ndarray | None):
     mx = np.max(np.abs(x), axis=1, keepdims=True)
     s = (mx / _qmax(bits)).astype(F32)
     y = np.clip(x, -mx, mx) / (s + EPS).astype(F32)
-    return _round_codes(y, u), s[:, 0]
+    return _round_codes(y, u, _qmax(bits)), s[:, 0]
 
 
 def quant_sawb(x: np.ndarray, bits: int):
@@ -250,21 +251,18 @@ def philox4x32_10(c0, c1, c2, c3, k0: int, k1: int):
     return c0, c1, c2, c3
 
 
-def philox_uniform16(seed: int, offset: int, shape) -> np.ndarray:
-    """Uniforms (65535 - R)/65536 as a ``Fixed16`` array, R the 16-bit Philox output of each
-    element 0..N-1 of a tensor in row-major order.  Elements 8g..8g+7 share the Philox
-    block with counter (g_lo, g_hi, offset_lo, offset_hi) and key (seed_lo, seed_hi);
-    element 8g+j takes the low (j even) or high (j odd) half of output word j // 2.
-    The kernels compute |code| = (floor(|y| * 2^16) + R) >> 16, which rounds up exactly
-    when (65535 - R)/65536 < floor(frac * 2^16)/2^16."""
+def philox_bytes(seed: int, offset: int, shape) -> np.ndarray:
+    """The stochastic-rounding byte of every element 0..N-1 of a tensor in row-major order, as a
+    ``PhiloxBytes`` array.  Elements 16g..16g+15 share the Philox block with counter
+    (g_lo, g_hi, offset_lo, offset_hi) and key (seed_lo, seed_hi); element 16g+j takes byte
+    j % 4 (little-endian) of output word j // 4."""
     n = int(np.prod(shape))
-    g = np.arange((n + 7) // 8, dtype=np.uint64)
+    g = np.arange((n + 15) // 16, dtype=np.uint64)
     w = philox4x32_10(g & _MASK, g >> np.uint64(32), np.uint64(offset & 0xFFFFFFFF),
                       np.uint64((offset >> 32) & 0xFFFFFFFF), seed & 0xFFFFFFFF, (seed >> 32) & 0xFFFFFFFF)
-    words = np.stack(w, axis=1).astype(np.uint64)                       # [G, 4]
-    halves = np.stack([words & np.uint64(0xFFFF), (words >> np.uint64(16)) & np.uint64(0xFFFF)], axis=2)
-    r16 = halves.reshape(-1)[:n].astype(F32)
-    return ((F32(65535.0) - r16) / F32(65536.0)).reshape(shape).view(Fixed16)
+    words = np.stack(w, axis=1).astype(np.uint64)                                    # [G, 4]
+    by = np.stack([(words >> np.uint64(8 * k)) & np.uint64(0xFF) for k in range(4)], axis=2)   # [G, 4, 4]
+    return by.reshape(-1)[:n].astype(np.uint8).reshape(shape).view(PhiloxBytes)
 
 
 # ----------------------------------------------------------------------------

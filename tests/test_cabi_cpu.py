@@ -43,7 +43,7 @@ def test_argument_errors_need_no_device(cabi):
     rc = lib.hot_row_ht_quant(p, 0, 4, 64, 64, 16, ctypes.byref(q), p, 64, p, p, None)
     assert rc == cabi.HOT_ERR_ARG and b"bits" in lib.hot_last_error()
     q.bits = 4
-    rc = lib.hot_row_ht_quant(p, 0, 4, 60, 64, 4, ctypes.byref(q), p, 64, p, p, None)
+    rc = lib.hot_row_ht_quant(p, 0, 4, 56, 64, 4, ctypes.byref(q), p, 64, p, p, None)
     assert rc == cabi.HOT_ERR_UNSUPPORTED
     rc = lib.hot_gemm_i8(None, 0, 16, p, 0, 16, 1, 1, 1, p, 0, p, 0, 1.0, p, 0, 1, None, None)
     assert rc == cabi.HOT_ERR_ARG

@@ -42,19 +42,19 @@ def _noise_for(rounding, shape, rng, seed, offset):
     if rounding == "noise":
         return rng.random(shape, dtype=np.float32)
     if rounding == "philox":
-        return oc.philox_uniform16(seed, offset, shape)
+        return oc.philox_bytes(seed, offset, shape)
     return None
 
 
 ROW_CASES = [
     # rows, cols, order
-    (37, 768, 16), (5, 192, 32), (64, 1024, 64), (3, 64, 1), (9, 40, 8), (130, 3072, 16), (2, 16384, 16),
+    (37, 768, 16), (5, 192, 32), (64, 1024, 64), (3, 64, 1), (9, 48, 8), (130, 3072, 16), (2, 16384, 16),
 ]
 
 
 @pytest.mark.parametrize("rows,cols,order", ROW_CASES)
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("storage,bits", [("int4", 4), ("int8", 8), ("int8", 4)])
+@pytest.mark.parametrize("storage,bits", [("int4", 4), ("int8", 8), ("int8", 4), ("int4", 3), ("int8", 6)])
 @pytest.mark.parametrize("rounding", ["nearest", "noise", "philox"])
 @pytest.mark.parametrize("scale", ["tensor", "row"])
 def test_row_ht_quant(ops, rows, cols, order, dtype, storage, bits, rounding, scale):
@@ -104,7 +104,7 @@ def test_col_ht_quant(ops, order, sel, dtype, storage, bits, rounding, layout, s
         u_t = rng.random((cols, out_len), dtype=np.float32)          # as seen in the stored layout
         u_dev = _dev(u_t if layout == "transposed" else np.ascontiguousarray(u_t.T))
     elif rounding == "philox":
-        u_t, u_dev = oc.philox_uniform16(seed, offset, (cols, out_len)), None
+        u_t, u_dev = oc.philox_bytes(seed, offset, (cols, out_len)), None
     else:
         u_t, u_dev = None, None
     q = ops.Quant(bits, storage, rounding, scale, seed, offset, u_dev)
@@ -181,9 +181,9 @@ def _run_backward(ops, x, w, go, order_l, sel, dtype, *, gx_row=False, gw_row=Fa
         elif rounding == "philox":
             # Philox streams are indexed in the stored layout: transposed for x and w
             if k in ("x", "w"):
-                us[k] = np.ascontiguousarray(oc.philox_uniform16(*seeds[k], shapes[k][::-1]).T).view(oc.Fixed16)
+                us[k] = np.ascontiguousarray(oc.philox_bytes(*seeds[k], shapes[k][::-1]).T).view(oc.PhiloxBytes)
             else:
-                us[k] = oc.philox_uniform16(*seeds[k], shapes[k])
+                us[k] = oc.philox_bytes(*seeds[k], shapes[k])
         else:
             us[k] = None
     def mk(k, bits, storage, scale="tensor"):
@@ -265,7 +265,7 @@ def test_linear_backward_vs_reference_golden(ops, golden, tag):
 
 def test_errors_are_reported(ops):
     x = torch.zeros((4, 24), device="cuda")
-    with pytest.raises(RuntimeError, match="multiple of 8"):
+    with pytest.raises(RuntimeError, match="multiple of 16"):
         ops.row_ht_quant(x[:, :20].contiguous(), 4, ops.Quant(4, "int4"))
     with pytest.raises(RuntimeError, match="INT4 storage needs bits"):
         ops.row_ht_quant(x, 8, ops.Quant(8, "int4"))

@@ -107,5 +107,11 @@ def test_philox_known_answer():
     assert [int(v) for v in out] == [0x6627E8D5, 0xE169C58D, 0xBC57AC4C, 0x9B00DBD8]
     out = oc.philox4x32_10(0xFFFFFFFF, 0xFFFFFFFF, 0xFFFFFFFF, 0xFFFFFFFF, 0xFFFFFFFF, 0xFFFFFFFF)
     assert [int(v) for v in out] == [0x408F276D, 0x41C83B0E, 0xA20BC7C6, 0x6D5451FD]
-    u = oc.philox_uniform16(1, 2, (3, 7))
-    assert u.shape == (3, 7) and u.dtype == np.float32 and (u >= 0).all() and (u < 1).all()
+    r = oc.philox_bytes(1, 2, (3, 7))
+    assert r.shape == (3, 7) and r.dtype == np.uint8 and isinstance(r, oc.PhiloxBytes)
+    first = oc.philox4x32_10(0, 0, 2, 0, 1, 0)
+    assert int(r[0, 0]) == int(first[0]) & 0xFF and int(r[0, 5]) == (int(first[1]) >> 8) & 0xFF
+    # the fixed-point rounding is unbiased: mean code == mean of y to within noise
+    y = np.random.default_rng(0).uniform(-7, 7, 200000).astype(np.float32)
+    c, s = oc.quant_tensor(y, 4, oc.philox_bytes(3, 4, y.shape))
+    assert abs(float(np.mean(c - y / (s + oc.EPS)))) < 5e-3 and np.abs(c).max() <= 7
