@@ -1,0 +1,412 @@
+// grad_output feeds both halves of the backward: Hadamard along the channels + INT4 for g_x,
+// Hadamard low-rank along the tokens + INT8 for g_w.  These kernels serve both from ONE read of
+// each tile: a persistent CTA streams 256-token x 64-channel tiles through a two-stage
+// shared-memory ring filled by TMA (the next tile is in flight while this one is processed);
+// a row phase takes 16-channel runs of a token, a column phase takes two 16-token blocks of a
+// channel pair, both with packed fp32 butterflies in registers.
+//
+//   pass 1  (dual_stats)  abs-max of both transformed tensors (per tensor, per token, per channel)
+//   pass 2  (dual_quant)  the same transforms again, quantised against those abs-maxima:
+//                         q_go [L, O] (INT4 packed or INT8) and q_gw^T [O, L/2] (INT8, written
+//                         through a shared-memory transpose so rows go out in 128-byte pieces)
+//
+// Arithmetic, rounding and Philox indexing are those of row_ht_quant / col_ht_quant, so the
+// outputs are bit-identical to running those two kernels one after the other.  Covered here:
+// the token-side basis "8 lowest-sequency rows of H_16", channels a multiple of 64, tokens a multiple of 32,
+// nearest or Philox rounding; everything else takes the separate kernels.
+#include "ht_device.cuh"
+#include "tma.cuh"
+
+namespace hot {
+namespace {
+
+constexpr int kThreads = 256;
+constexpr int kTT = 256;  // tokens per tile
+constexpr int kTC = 64;   // channels per tile
+constexpr int kStagePitch = 144;  // bytes per channel row of the transposed INT8 staging (128 used)
+
+struct DualParams {
+  int64_t L;
+  int O;
+  int n_o;                 // Hadamard order along channels (1..64)
+  int x_row, w_row;        // per-token scale on the g_x side, per-channel scale on the g_w side
+  int x_store4;            // g_x codes packed INT4
+  QuantDev qx, qw;
+  uint8_t* q_go;
+  int64_t ld_qgo;
+  uint8_t* q_gw;
+  int64_t ld_qgw;
+  float* s_x;              // [1] or [L]
+  float* s_w;              // [1] or [O]
+  uint32_t* max_x;         // [1] or [L]
+  uint32_t* max_w;         // [1] or [O]
+  uint32_t* status;
+};
+
+template <typename T>
+struct Tile {
+  static constexpr int kRowBytes = kTC * (int)sizeof(T);
+  static constexpr int kBytes = kTT * kRowBytes;
+};
+
+// 16 consecutive channels of one token from the shared-memory tile -> eight (A_i, B_i) pairs
+template <typename T>
+__device__ __forceinline__ void lds_run16(const uint8_t* p, float2 (&v)[8]);
+template <>
+__device__ __forceinline__ void lds_run16<float>(const uint8_t* p, float2 (&v)[8]) {
+  const float4* q = reinterpret_cast<const float4*>(p);
+  const float4 a0 = q[0], a1 = q[1], b0 = q[2], b1 = q[3];
+  v[0] = make_float2(a0.x, b0.x); v[1] = make_float2(a0.y, b0.y);
+  v[2] = make_float2(a0.z, b0.z); v[3] = make_float2(a0.w, b0.w);
+  v[4] = make_float2(a1.x, b1.x); v[5] = make_float2(a1.y, b1.y);
+  v[6] = make_float2(a1.z, b1.z); v[7] = make_float2(a1.w, b1.w);
+}
+template <>
+__device__ __forceinline__ void lds_run16<__nv_bfloat16>(const uint8_t* p, float2 (&v)[8]) {
+  const uint4* q = reinterpret_cast<const uint4*>(p);
+  const uint4 a = q[0], b = q[1];
+  const uint32_t wa[4] = {a.x, a.y, a.z, a.w}, wb[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    v[2 * k] = make_float2(__uint_as_float(wa[k] << 16), __uint_as_float(wb[k] << 16));
+    v[2 * k + 1] = make_float2(__uint_as_float(wa[k] & 0xFFFF0000u), __uint_as_float(wb[k] & 0xFFFF0000u));
+  }
+}
+
+// Two adjacent channels (c, c + 1) of one token -> (x_c, x_c+1)
+template <typename T>
+__device__ __forceinline__ float2 lds_pair(const uint8_t* p);
+template <>
+__device__ __forceinline__ float2 lds_pair<float>(const uint8_t* p) {
+  return *reinterpret_cast<const float2*>(p);
+}
+template <>
+__device__ __forceinline__ float2 lds_pair<__nv_bfloat16>(const uint8_t* p) {
+  const uint32_t w = *reinterpret_cast<const uint32_t*>(p);
+  return make_float2(__uint_as_float(w << 16), __uint_as_float(w & 0xFFFF0000u));
+}
+
+// The token-side basis these kernels serve: the 8 lowest-sequency rows of H_16.  In natural
+// (Sylvester) order those are the even rows 0, 2, ..., 14; output slot of natural row 2i:
+__device__ constexpr int kSlotOfEvenRow[8] = {0, 7, 3, 4, 1, 6, 2, 5};
+constexpr int kHalf16Sel[8] = {0, 8, 12, 4, 6, 14, 10, 2};  // natural row of output slot j
+
+// Even rows of the order-16 butterfly over tokens for a channel pair: u[t] = (x[t][c], x[t][c+1]).
+// Stage h = 1 leaves the sums x[2i] + x[2i+1] at the even positions, and the later stages only
+// ever combine positions of equal parity, so the even outputs need the sums alone: e[i] is
+// natural row 2i.  Same operations, in the same order, as the full butterfly computes for them.
+__device__ __forceinline__ void butterfly_tokens16_even(const float2 (&u)[16], float2 (&e)[8]) {
+#pragma unroll
+  for (int i = 0; i < 8; ++i) e[i] = add2(u[2 * i], u[2 * i + 1]);
+#pragma unroll
+  for (int h = 1; h < 8; h <<= 1) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      if ((i & h) == 0) {
+        const float2 a = e[i], b = e[i + h];
+        e[i] = add2(a, b);
+        e[i + h] = sub2(a, b);
+      }
+    }
+  }
+}
+
+// Quantise 16 consecutive codes of one row of the transposed g_w operand (stored-layout element
+// index e0, a multiple of 16) into 16 bytes.
+template <int ROUND>
+__device__ __forceinline__ uint4 quantise16_int8(const float (&y)[16], const ScalePair& sp, const QuantDev& q, uint64_t e0) {
+  uint32_t w[4] = {0, 0, 0, 0};
+  if (ROUND == HOT_ROUND_STOCH_PHILOX) {
+    const uint4 r = philox_block16(q, e0 >> 4);
+    const uint32_t rr[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+    for (int i = 0; i < 16; i += 2) {
+      const float2 yb = add2(div2_exact(make_float2(y[i], y[i + 1]), sp.dv8), make_float2(sp.bias8, sp.bias8));
+      const uint32_t c0 = (__float2uint_rn(yb.x) + ((rr[i >> 2] >> (8 * (i & 3))) & 0xFFu)) >> 8;
+      const uint32_t c1 = (__float2uint_rn(yb.y) + ((rr[i >> 2] >> (8 * ((i + 1) & 3))) & 0xFFu)) >> 8;
+      w[i >> 2] |= (c0 << (8 * (i & 3))) | (c1 << (8 * ((i + 1) & 3)));
+    }
+    const uint32_t off = (uint32_t)(q.qmax + 1.0f);
+    const uint32_t ext = 0x100u - 2u * off;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      uint32_t x = w[k] ^ (off * 0x01010101u);
+      if (ext) x |= ((x & (off * 0x01010101u)) / off) * ext;
+      w[k] = x;
+    }
+  } else {
+    const int qmax = (int)q.qmax;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) w[i >> 2] |= (uint32_t)(quantise_one<ROUND>(y[i], sp, 0.0f, qmax) & 0xFF) << (8 * (i & 3));
+  }
+  return make_uint4(w[0], w[1], w[2], w[3]);
+}
+
+// PASS 0: statistics.  PASS 1: quantise (RX / RW: rounding of the g_x / g_w side).
+template <typename T, int PASS, int RX, int RW>
+__global__ void __launch_bounds__(kThreads) go_dual_kernel(const __grid_constant__ CUtensorMap tmap, DualParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~(uintptr_t)127);
+  uint8_t* tile[2] = {smem, smem + Tile<T>::kBytes};
+  uint8_t* stage_out = smem + 2 * Tile<T>::kBytes;                       // [kTC][kStagePitch] (PASS 1)
+  uint32_t* s_colmax = reinterpret_cast<uint32_t*>(stage_out);          // [kTC]             (PASS 0)
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + 2 * Tile<T>::kBytes + kTC * kStagePitch);
+  volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(full + 2);
+
+  const int tid = threadIdx.x, lane = tid & 31;
+  const int tiles_c = p.O / kTC;
+  const int tiles_t = (int)((p.L + kTT - 1) / kTT);
+  const int num_tiles = tiles_c * tiles_t;
+
+  if (tid == 0) {
+    mbar_init(&full[0], 1);
+    mbar_init(&full[1], 1);
+    *abort_flag = 0u;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    tma_prefetch_desc(&tmap);
+  }
+  __syncthreads();
+  // tile index -> (token tile, channel tile): channel tiles fastest, so that neighbouring CTAs
+  // work on the same token rows
+  auto issue = [&](int tile_idx, int s) {
+    const int tt = tile_idx / tiles_c, tc = tile_idx % tiles_c;
+    mbar_expect_tx(&full[s], Tile<T>::kBytes);
+    tma_load_2d(tile[s], &tmap, &full[s], tc * Tile<T>::kRowBytes, tt * kTT);
+  };
+  if (tid == 0 && (int)blockIdx.x < num_tiles) issue(blockIdx.x, 0);
+
+  ScalePair sp_x = scale_from_absmax(0.0f, p.qx.qmax), sp_w = scale_from_absmax(0.0f, p.qw.qmax);
+  if (PASS == 1) {
+    if (!p.x_row) sp_x = scale_from_absmax(__uint_as_float(p.max_x[0]), p.qx.qmax);
+    if (!p.w_row) sp_w = scale_from_absmax(__uint_as_float(p.max_w[0]), p.qw.qmax);
+    if (blockIdx.x == 0 && tid == 0) {
+      if (!p.x_row) p.s_x[0] = sp_x.s;
+      if (!p.w_row) p.s_w[0] = sp_w.s;
+    }
+  }
+  float tmax_x = 0.0f, tmax_w = 0.0f;  // per-tensor maxima of this thread (PASS 0)
+
+  uint32_t it = 0;
+  bool ok = true;
+  for (int t_idx = blockIdx.x; t_idx < num_tiles; t_idx += gridDim.x, ++it) {
+    const int s = it & 1;
+    const int next = t_idx + gridDim.x;
+    if (tid == 0 && next < num_tiles) issue(next, s ^ 1);  // stage s^1 was released by the barrier below
+    ok = mbar_wait(&full[s], (it >> 1) & 1u, abort_flag);
+    if (!ok) break;
+    const uint8_t* tl = tile[s];
+    const int tt = t_idx / tiles_c, tc = t_idx % tiles_c;
+    const int64_t tok0 = (int64_t)tt * kTT;
+    const int ch0 = tc * kTC;
+
+    if (PASS == 0 && p.w_row) {
+      if (tid < kTC) s_colmax[tid] = 0u;
+      __syncthreads();
+    }
+
+    // ---- row phase: 16-channel runs; run r of token k is item 4k + r (adjacent lanes) -------
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      float2 v[2][8];
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        const int item = tid + (half * 2 + u) * kThreads;
+        lds_run16<T>(tl + (item >> 2) * Tile<T>::kRowBytes + (item & 3) * 16 * (int)sizeof(T), v[u]);
+      }
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        const int item = tid + (half * 2 + u) * kThreads;
+        const int64_t tok = tok0 + (item >> 2);
+        const int ch = ch0 + (item & 3) * 16;
+        butterfly16(v[u], p.n_o, lane);
+        if (PASS == 0) {
+          float m = absmax16(v[u]);
+          if (p.x_row) {
+            m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, 1));
+            m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, 2));
+            if ((lane & 3) == 0 && tok < p.L) atomic_absmax(p.max_x + tok, m);
+          } else {
+            tmax_x = fmaxf(tmax_x, m);
+          }
+        } else if (tok < p.L) {
+          ScalePair sp = sp_x;
+          if (p.x_row) {
+            sp = scale_from_absmax(__uint_as_float(p.max_x[tok]), p.qx.qmax);
+            if (tc == 0 && (item & 3) == 0) p.s_x[tok] = sp.s;
+          }
+          const uint64_t e0 = (uint64_t)tok * (uint64_t)p.O + (uint64_t)ch;
+          uint8_t* dst = p.q_go + tok * p.ld_qgo + (p.x_store4 ? (ch >> 1) : ch);
+          if (p.x_store4) quantise_store16<RX, 1>(v[u], sp, p.qx, e0, dst);
+          else quantise_store16<RX, 0>(v[u], sp, p.qx, e0, dst);
+        }
+      }
+    }
+
+    // ---- column phase: channel pair cp (lane), token blocks 2*bp and 2*bp+1 (warp) ----------
+    {
+      const int cp = tid & 31, bp = tid >> 5;
+      const int c_loc = cp * 2;
+      float y[2][16];  // kept rows of [channel][block A slots 0..7 | block B slots 0..7]
+      float cmax0 = 0.0f, cmax1 = 0.0f;
+#pragma unroll
+      for (int blk = 0; blk < 2; ++blk) {
+        float2 u[16], e[8];
+        const uint8_t* base = tl + (bp * 32 + blk * 16) * Tile<T>::kRowBytes + c_loc * (int)sizeof(T);
+#pragma unroll
+        for (int t = 0; t < 16; ++t) u[t] = lds_pair<T>(base + t * Tile<T>::kRowBytes);
+        butterfly_tokens16_even(u, e);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          if (PASS == 0) {
+            cmax0 = fmaxf(cmax0, fabsf(e[i].x));
+            cmax1 = fmaxf(cmax1, fabsf(e[i].y));
+          } else {
+            y[0][blk * 8 + kSlotOfEvenRow[i]] = e[i].x;
+            y[1][blk * 8 + kSlotOfEvenRow[i]] = e[i].y;
+          }
+        }
+      }
+      const int64_t blk_pair = tok0 / 32 + bp;           // global index of this pair of token blocks
+      const bool pair_ok = tok0 + bp * 32 < p.L;          // tokens are a multiple of 32: all or nothing
+      if (PASS == 0) {
+        if (p.w_row) {
+          atomicMax(&s_colmax[c_loc], __float_as_uint(cmax0));
+          atomicMax(&s_colmax[c_loc + 1], __float_as_uint(cmax1));
+        } else {
+          tmax_w = fmaxf(tmax_w, fmaxf(cmax0, cmax1));
+        }
+      } else {
+        const int64_t out_len = p.L / 2;
+#pragma unroll
+        for (int cc = 0; cc < 2; ++cc) {
+          const int ch = ch0 + c_loc + cc;
+          ScalePair sp = sp_w;
+          if (p.w_row) {
+            sp = scale_from_absmax(__uint_as_float(p.max_w[ch]), p.qw.qmax);
+            if (tt == 0 && bp == 0) p.s_w[ch] = sp.s;
+          }
+          uint4 codes = make_uint4(0, 0, 0, 0);
+          if (pair_ok) codes = quantise16_int8<RW>(y[cc], sp, p.qw, (uint64_t)ch * (uint64_t)out_len + (uint64_t)blk_pair * 16u);
+          *reinterpret_cast<uint4*>(stage_out + (c_loc + cc) * kStagePitch + bp * 16) = codes;
+        }
+      }
+    }
+    __syncthreads();  // tile consumed; staging complete
+    if (PASS == 0) {
+      if (p.w_row && tid < kTC) atomicMax(p.max_w + ch0 + tid, s_colmax[tid]);
+    } else {
+      // transposed g_w codes of this tile: kTC rows x 128 bytes, written in 16-byte pieces
+      const int64_t pos0 = tok0 / 2;                       // first stored position of the tile in a row
+      const int64_t out_len = p.L / 2;
+#pragma unroll
+      for (int k = 0; k < 2; ++k) {
+        const int idx = tid + k * kThreads;
+        const int c = idx >> 3, piece = idx & 7;
+        if (pos0 + piece * 16 < out_len)
+          *reinterpret_cast<uint4*>(p.q_gw + (int64_t)(ch0 + c) * p.ld_qgw + pos0 + piece * 16) =
+              *reinterpret_cast<const uint4*>(stage_out + c * kStagePitch + piece * 16);
+      }
+    }
+    __syncthreads();  // staging / column maxima free for the next tile
+  }
+
+  if (PASS == 0) {
+    if (!p.x_row) {
+      tmax_x = warp_max(tmax_x);
+      if (lane == 0) atomic_absmax(p.max_x, tmax_x);
+    }
+    if (!p.w_row) {
+      tmax_w = warp_max(tmax_w);
+      if (lane == 0) atomic_absmax(p.max_w, tmax_w);
+    }
+  }
+  if (!ok && tid == 0 && p.status) atomicOr(p.status, 2u);
+  __syncthreads();
+  if (tid == 0 && *abort_flag) {
+    const uint64_t t0 = global_timer_ns();  // let bulk copies already issued land before exit
+    while (global_timer_ns() - t0 < 100000ull) {
+    }
+  }
+}
+
+template <typename T>
+constexpr int smem_bytes() { return 2 * Tile<T>::kBytes + kTC * kStagePitch + 64 + 128; }
+
+template <typename T, int PASS, int RX, int RW>
+int launch_pass(const CUtensorMap& tmap, const DualParams& p, int grid, cudaStream_t st) {
+  auto kernel = go_dual_kernel<T, PASS, RX, RW>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    HOT_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes<T>()));
+    attr_set = true;
+  }
+  kernel<<<grid, kThreads, smem_bytes<T>(), st>>>(tmap, p);
+  HOT_CUDA(cudaGetLastError());
+  return HOT_OK;
+}
+
+template <typename T>
+int launch_dual(const void* go, int64_t ldgo, const DualParams& p, int rx, int rw, int sms, cudaStream_t st) {
+  CUtensorMap tmap;
+  if (int rc = make_map(&tmap, go, p.L, (int64_t)p.O * sizeof(T), ldgo * (int64_t)sizeof(T), Tile<T>::kRowBytes, kTT, false))
+    return rc;
+  const int num_tiles = (p.O / kTC) * (int)((p.L + kTT - 1) / kTT);
+  const int per_sm = sizeof(T) == 2 ? 2 : 1;  // resident CTAs per SM by shared memory
+  int grid = sms * per_sm;
+  if (grid > num_tiles) grid = num_tiles;
+  HOT_CUDA(cudaMemsetAsync(p.max_x, 0, sizeof(uint32_t) * (p.x_row ? p.L : 1), st));
+  HOT_CUDA(cudaMemsetAsync(p.max_w, 0, sizeof(uint32_t) * (p.w_row ? p.O : 1), st));
+  if (int rc = launch_pass<T, 0, HOT_ROUND_NEAREST, HOT_ROUND_NEAREST>(tmap, p, grid, st)) return rc;
+  const bool px = rx == HOT_ROUND_STOCH_PHILOX, pw = rw == HOT_ROUND_STOCH_PHILOX;
+  if (px && pw) return launch_pass<T, 1, HOT_ROUND_STOCH_PHILOX, HOT_ROUND_STOCH_PHILOX>(tmap, p, grid, st);
+  if (px) return launch_pass<T, 1, HOT_ROUND_STOCH_PHILOX, HOT_ROUND_NEAREST>(tmap, p, grid, st);
+  if (pw) return launch_pass<T, 1, HOT_ROUND_NEAREST, HOT_ROUND_STOCH_PHILOX>(tmap, p, grid, st);
+  return launch_pass<T, 1, HOT_ROUND_NEAREST, HOT_ROUND_NEAREST>(tmap, p, grid, st);
+}
+
+}  // namespace
+
+int device_sm_count();
+
+// Whether the fused kernels cover this configuration (else the caller runs the two separate ones).
+bool go_dual_supported(int64_t L, int64_t O, int64_t ldgo, int dtype, int order_o, int order_l, int rank_l,
+                       const int32_t* sel_l, const hot_quant_t& q_gx, const hot_quant_t& q_gw) {
+  const int esz = dtype == HOT_F32 ? 4 : 2;
+  if (order_l != 16 || rank_l != 8) return false;
+  for (int j = 0; j < 8; ++j)
+    if (sel_l[j] != kHalf16Sel[j]) return false;
+  return (dtype == HOT_F32 || dtype == HOT_BF16) && order_l == 16 && rank_l == 8 && L % 32 == 0 && O % kTC == 0 &&
+         O <= (1 << 24) && (ldgo * esz) % 16 == 0 && order_o >= 1 && order_o <= 64 && q_gw.storage == HOT_STORE_INT8 &&
+         q_gx.rounding != HOT_ROUND_STOCH_NOISE && q_gw.rounding != HOT_ROUND_STOCH_NOISE;
+}
+
+int go_dual_quant(const void* go, int dtype, int64_t L, int64_t O, int64_t ldgo, int order_o, const int32_t* sel_l,
+                  const hot_quant_t& q_gx, const hot_quant_t& q_gw, void* q_go, int64_t ld_qgo, float* s_gx, void* q_gw_t,
+                  int64_t ld_qgw, float* s_gw, uint32_t* max_x, uint32_t* max_w, uint32_t* status, cudaStream_t st) {
+  DualParams p;
+  p.L = L;
+  p.O = (int)O;
+  p.n_o = order_o;
+  for (int j = 0; j < 8; ++j)
+    if (sel_l[j] != kHalf16Sel[j]) HOT_FAIL(HOT_ERR_UNSUPPORTED, "go_dual_quant: row selection is not the half16 preset");
+  p.x_row = q_gx.scale_mode == HOT_SCALE_ROW;
+  p.w_row = q_gw.scale_mode == HOT_SCALE_ROW;
+  p.x_store4 = q_gx.storage == HOT_STORE_INT4;
+  p.qx = make_quant_dev(q_gx);
+  p.qw = make_quant_dev(q_gw);
+  p.q_go = (uint8_t*)q_go;
+  p.ld_qgo = ld_qgo;
+  p.q_gw = (uint8_t*)q_gw_t;
+  p.ld_qgw = ld_qgw;
+  p.s_x = s_gx;
+  p.s_w = s_gw;
+  p.max_x = max_x;
+  p.max_w = max_w;
+  p.status = status;
+  const int sms = device_sm_count();
+  if (sms <= 0) return HOT_ERR_CUDA;
+  if (dtype == HOT_F32) return launch_dual<float>(go, ldgo, p, q_gx.rounding, q_gw.rounding, sms, st);
+  return launch_dual<__nv_bfloat16>(go, ldgo, p, q_gx.rounding, q_gw.rounding, sms, st);
+}
+
+}  // namespace hot

@@ -4,6 +4,13 @@
 #include "common.cuh"
 
 namespace hot {
+
+bool go_dual_supported(int64_t L, int64_t O, int64_t ldgo, int dtype, int order_o, int order_l, int rank_l,
+                       const int32_t* sel_l, const hot_quant_t& q_gx, const hot_quant_t& q_gw);
+int go_dual_quant(const void* go, int dtype, int64_t L, int64_t O, int64_t ldgo, int order_o, const int32_t* sel_l,
+                  const hot_quant_t& q_gx, const hot_quant_t& q_gw, void* q_go, int64_t ld_qgo, float* s_gx, void* q_gw_t,
+                  int64_t ld_qgw, float* s_gw, uint32_t* max_x, uint32_t* max_w, uint32_t* status, cudaStream_t st);
+
 namespace {
 
 constexpr size_t kAlign = 256;
@@ -31,7 +38,7 @@ int plan(int64_t L, int64_t O, int64_t I, const hot_linear_cfg_t& c, Workspace& 
   w.off_sw = o;  o += kAlign;
   w.off_qgw = o; o += up((size_t)O * w.ld_qgw, kAlign);
   w.off_sgw = o; o += up((size_t)O * sizeof(float), kAlign);
-  w.off_scratch = o; o += up((size_t)(O > I ? O : I) * sizeof(uint32_t) + 64, kAlign);
+  w.off_scratch = o; o += up((size_t)(L + O + I + 256) * sizeof(uint32_t), kAlign);
   w.total = o;
   return HOT_OK;
 }
@@ -79,14 +86,30 @@ extern "C" int hot_linear_backward(const void* go, int64_t ldgo, const void* w, 
   if (cfg->order_o < 1 || cfg->order_o > 16 || O % cfg->order_o != 0)
     HOT_FAIL(HOT_ERR_ARG, "hot_linear_backward: order_o %d does not divide O = %lld", cfg->order_o, (long long)O);
   uint8_t* base = (uint8_t*)workspace;
+  // scratch words: [0, 64) per-tensor maxima of the three quantiser calls and the weight's,
+  // then per-token (L) and per-channel (O) maxima
   uint32_t* scratch = (uint32_t*)(base + ws.off_scratch);
+  float* s_go = (float*)(base + ws.off_sgo);
+  float* s_w = (float*)(base + ws.off_sw);
+  float* s_gw = (float*)(base + ws.off_sgw);
   int rc;
-  if (grad_x) {
-    float* s_go = (float*)(base + ws.off_sgo);
-    float* s_w = (float*)(base + ws.off_sw);
-    rc = hot_row_ht_quant(go, cfg->dtype, L, O, ldgo, cfg->order_o, &cfg->q_gx, base + ws.off_qgo, ws.ld_qgo, s_go, scratch,
-                          stream);
+  // grad_out: one fused pair of kernels serves both operands when both gradients are wanted and
+  // the configuration is the one they cover; otherwise each side runs its own kernel
+  const bool dual = grad_x && grad_w &&
+                    go_dual_supported(L, O, ldgo, cfg->dtype, cfg->order_o, cfg->order_l, cfg->rank_l, cfg->sel_l, cfg->q_gx,
+                                      cfg->q_gw);
+  if (dual) {
+    rc = go_dual_quant(go, cfg->dtype, L, O, ldgo, cfg->order_o, cfg->sel_l, cfg->q_gx, cfg->q_gw, base + ws.off_qgo,
+                       ws.ld_qgo, s_go, base + ws.off_qgw, ws.ld_qgw, s_gw, scratch + 64, scratch + 64 + L, status_word,
+                       (cudaStream_t)stream);
     if (rc) return rc;
+  }
+  if (grad_x) {
+    if (!dual) {
+      rc = hot_row_ht_quant(go, cfg->dtype, L, O, ldgo, cfg->order_o, &cfg->q_gx, base + ws.off_qgo, ws.ld_qgo, s_go, scratch,
+                            stream);
+      if (rc) return rc;
+    }
     int32_t ident[64];
     for (int i = 0; i < 64; ++i) ident[i] = i;
     if (cfg->q_w.scale_mode != HOT_SCALE_TENSOR) HOT_FAIL(HOT_ERR_UNSUPPORTED, "hot_linear_backward: the weight takes one scale");
@@ -104,10 +127,11 @@ extern "C" int hot_linear_backward(const void* go, int64_t ldgo, const void* w, 
     if (rc) return rc;
   }
   if (grad_w) {
-    float* s_gw = (float*)(base + ws.off_sgw);
-    rc = hot_col_ht_quant(go, cfg->dtype, L, O, ldgo, cfg->order_l, cfg->sel_l, cfg->rank_l, &cfg->q_gw,
-                          HOT_LAYOUT_TRANSPOSED, base + ws.off_qgw, ws.ld_qgw, s_gw, scratch + 32, stream);
-    if (rc) return rc;
+    if (!dual) {
+      rc = hot_col_ht_quant(go, cfg->dtype, L, O, ldgo, cfg->order_l, cfg->sel_l, cfg->rank_l, &cfg->q_gw,
+                            HOT_LAYOUT_TRANSPOSED, base + ws.off_qgw, ws.ld_qgw, s_gw, scratch + 64 + L, stream);
+      if (rc) return rc;
+    }
     rc = hot_gemm_i8(base + ws.off_qgw, cfg->q_gw.storage, ws.ld_qgw, x_q_t, cfg->q_x.storage, hot_abc_pitch(L, cfg), O, I,
                      ws.lp, s_gw, cfg->q_gw.scale_mode == HOT_SCALE_ROW, scale_x, 0, 1.0f / (float)cfg->order_l, grad_w,
                      cfg->dtype, ldgw, status_word, stream);
