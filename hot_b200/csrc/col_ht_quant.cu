@@ -199,16 +199,30 @@ __global__ void __launch_bounds__(kThreads) col_ht_quant_kernel(const T* __restr
     if (ROUND == HOT_ROUND_STOCH_PHILOX) {
       // random byte of stored-layout element e: byte e % 16 of Philox block e / 16
       const uint64_t e0 = (uint64_t)c * (uint64_t)p.out_len + (uint64_t)l0;
-      uint4 blk = philox_block16(q, e0 >> 4);
-      int j = (int)(e0 & 15u);
+      if ((e0 & 7u) == 0) {
+        // aligned run: its 8 random bytes are one half of a Philox block
+        const uint4 blk = philox_block16(q, e0 >> 4);
+        const bool hi = (e0 & 8u) != 0;
+        const uint32_t rw[2] = {hi ? blk.z : blk.x, hi ? blk.w : blk.y};
+        const float2 bias = make_float2(sp.bias8, sp.bias8);
 #pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        if (j == 16) {  // the run crossed into the next block (unaligned row starts only)
-          blk = philox_block16(q, (e0 >> 4) + 1);
-          j = 0;
+        for (int i = 0; i < 8; i += 2) {
+          const float2 yb = add2(div2_exact(make_float2(v[i], v[i + 1]), sp.dv8), bias);
+          code[i] = (int)((__float2uint_rn(yb.x) + ((rw[i >> 2] >> (8 * (i & 3))) & 0xFFu)) >> 8) - (qmax + 1);
+          code[i + 1] = (int)((__float2uint_rn(yb.y) + ((rw[i >> 2] >> (8 * ((i + 1) & 3))) & 0xFFu)) >> 8) - (qmax + 1);
         }
-        code[i] = (int)philox_offset_code(v[i], sp, philox_byte(blk, j)) - (qmax + 1);
-        ++j;
+      } else {
+        uint4 blk = philox_block16(q, e0 >> 4);
+        int j = (int)(e0 & 15u);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          if (j == 16) {  // the run crossed into the next block (unaligned row starts only)
+            blk = philox_block16(q, (e0 >> 4) + 1);
+            j = 0;
+          }
+          code[i] = (int)philox_offset_code(v[i], sp, philox_byte(blk, j)) - (qmax + 1);
+          ++j;
+        }
       }
     } else {
       float u[8];

@@ -13,6 +13,34 @@ int go_dual_quant(const void* go, int dtype, int64_t L, int64_t O, int64_t ldgo,
 
 namespace {
 
+// A helper stream per device, so that the weight quantisation (independent of grad_out) runs
+// beside the grad_out kernels.  Created on first use: make the first call on a device outside
+// stream capture.  Fork and join are plain events, which also work under capture.
+struct SideStream {
+  cudaStream_t stream = nullptr;
+  cudaEvent_t fork = nullptr, join = nullptr;
+};
+SideStream g_side[64];
+
+int side_stream(SideStream** out) {
+  int dev = -1;
+  HOT_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) HOT_FAIL(HOT_ERR_UNSUPPORTED, "hot_linear_backward: device ordinal %d", dev);
+  SideStream& s = g_side[dev];
+  if (!s.stream) {
+    cudaStream_t st;
+    cudaEvent_t f, j;
+    HOT_CUDA(cudaStreamCreateWithFlags(&st, cudaStreamNonBlocking));
+    HOT_CUDA(cudaEventCreateWithFlags(&f, cudaEventDisableTiming));
+    HOT_CUDA(cudaEventCreateWithFlags(&j, cudaEventDisableTiming));
+    s.fork = f;
+    s.join = j;
+    s.stream = st;
+  }
+  *out = &s;
+  return HOT_OK;
+}
+
 constexpr size_t kAlign = 256;
 inline size_t up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
@@ -98,29 +126,53 @@ extern "C" int hot_linear_backward(const void* go, int64_t ldgo, const void* w, 
   const bool dual = grad_x && grad_w &&
                     go_dual_supported(L, O, ldgo, cfg->dtype, cfg->order_o, cfg->order_l, cfg->rank_l, cfg->sel_l, cfg->q_gx,
                                       cfg->q_gw);
-  if (dual) {
-    rc = go_dual_quant(go, cfg->dtype, L, O, ldgo, cfg->order_o, cfg->sel_l, cfg->q_gx, cfg->q_gw, base + ws.off_qgo,
-                       ws.ld_qgo, s_go, base + ws.off_qgw, ws.ld_qgw, s_gw, scratch + 64, scratch + 64 + L, status_word,
-                       (cudaStream_t)stream);
-    if (rc) return rc;
-  }
+  // the weight side starts first, on the helper stream
+  SideStream* side = nullptr;
+  cudaStream_t main_st = (cudaStream_t)stream;
   if (grad_x) {
-    if (!dual) {
-      rc = hot_row_ht_quant(go, cfg->dtype, L, O, ldgo, cfg->order_o, &cfg->q_gx, base + ws.off_qgo, ws.ld_qgo, s_go, scratch,
-                            stream);
-      if (rc) return rc;
-    }
+    if (cfg->q_w.scale_mode != HOT_SCALE_TENSOR) HOT_FAIL(HOT_ERR_UNSUPPORTED, "hot_linear_backward: the weight takes one scale");
+    if ((rc = side_stream(&side))) return rc;
+    HOT_CUDA(cudaEventRecord(side->fork, main_st));
+    HOT_CUDA(cudaStreamWaitEvent(side->stream, side->fork, 0));
     int32_t ident[64];
     for (int i = 0; i < 64; ++i) ident[i] = i;
-    if (cfg->q_w.scale_mode != HOT_SCALE_TENSOR) HOT_FAIL(HOT_ERR_UNSUPPORTED, "hot_linear_backward: the weight takes one scale");
     // The quantised weight is the B operand of every CTA of the g_x GEMM and is tiny (O * I bytes):
     // it is stored one code per byte whatever its bit width, so that it reaches the tensor core by
     // TMA alone and only grad_out (the large, streamed operand) is expanded in shared memory.
     hot_quant_t q_w = cfg->q_w;
     q_w.storage = HOT_STORE_INT8;
     rc = hot_col_ht_quant(w, cfg->dtype, O, I, ldw, cfg->order_o, ident, cfg->order_o, &q_w, HOT_LAYOUT_NATURAL,
-                          base + ws.off_qw, ws.ld_qw, s_w, scratch + 16, stream);
-    if (rc) return rc;
+                          base + ws.off_qw, ws.ld_qw, s_w, scratch + 16, (hot_stream_t)side->stream);
+    cudaEventRecord(side->join, side->stream);
+    if (rc) {
+      cudaStreamWaitEvent(main_st, side->join, 0);  // rejoin, so that a capture in progress stays well-formed
+      return rc;
+    }
+  }
+  bool joined = side == nullptr;
+  auto rejoin = [&]() {
+    if (!joined) cudaStreamWaitEvent(main_st, side->join, 0);
+    joined = true;
+  };
+  if (dual) {
+    rc = go_dual_quant(go, cfg->dtype, L, O, ldgo, cfg->order_o, cfg->sel_l, cfg->q_gx, cfg->q_gw, base + ws.off_qgo,
+                       ws.ld_qgo, s_go, base + ws.off_qgw, ws.ld_qgw, s_gw, scratch + 64, scratch + 64 + L, status_word,
+                       (cudaStream_t)stream);
+    if (rc) {
+      rejoin();
+      return rc;
+    }
+  }
+  if (grad_x) {
+    if (!dual) {
+      rc = hot_row_ht_quant(go, cfg->dtype, L, O, ldgo, cfg->order_o, &cfg->q_gx, base + ws.off_qgo, ws.ld_qgo, s_go, scratch,
+                            stream);
+      if (rc) {
+        rejoin();
+        return rc;
+      }
+    }
+    rejoin();  // the g_x GEMM needs the quantised weight
     rc = hot_gemm_i8(base + ws.off_qgo, cfg->q_gx.storage, ws.ld_qgo, base + ws.off_qw, HOT_STORE_INT8, ws.ld_qw, L, I, O,
                      s_go, cfg->q_gx.scale_mode == HOT_SCALE_ROW, s_w, 0, 1.0f / (float)cfg->order_o, grad_x, cfg->dtype,
                      ldgx, status_word, stream);
