@@ -165,22 +165,15 @@ def run_hot(a):
     status = torch.zeros(1, dtype=torch.int32, device=device)
     # gradient buffers: grad_x is consumed by the layer below (one reusable buffer per width);
     # grad_w lands in one flat bucket per block, the unit of the all-reduce
+    from hot_b200.dp import GradBuckets
     gx_buf = {i_f: torch.empty((a.tokens, i_f), dtype=dtype, device=device) for _, i_f, _ in LAYERS}
-    bucket_elems = sum(i * o for _, i, o in LAYERS)
-    buckets = [torch.empty((bucket_elems,), dtype=dtype, device=device) for _ in range(a.blocks)]
-    gw_views = []
-    for b in range(a.blocks):
-        off, views = 0, []
-        for _, i_f, o_f in LAYERS:
-            views.append(buckets[b][off:off + i_f * o_f].view(o_f, i_f))
-            off += i_f * o_f
-        gw_views.append(views)
+    grads = GradBuckets([[(o_f, i_f) for _, i_f, o_f in LAYERS] for _ in range(a.blocks)], dtype, device)
 
     def block_backward(b):
         for li in reversed(range(len(LAYERS))):
             l = layers[b][li]
             ops.linear_backward(l["go"], l["w"], l["x_q_t"], l["s_x"], l["cfg"], status=status,
-                                gx_out=gx_buf[l["I"]], gw_out=gw_views[b][li])
+                                gx_out=gx_buf[l["I"]], gw_out=grads.view(b, li))
 
     # one CUDA graph per transformer block: launch overhead off the critical path, and the
     # all-reduce of a block's bucket can be enqueued between graph launches
@@ -198,13 +191,10 @@ def run_hot(a):
     torch.cuda.synchronize(device)
 
     def step():
-        works = []
         for b in reversed(range(a.blocks)):
             graphs[b].replay()
-            if world > 1:
-                works.append(dist.all_reduce(buckets[b], op=dist.ReduceOp.SUM, async_op=True))
-        for w in works:
-            w.wait()
+            grads.reduce_async(b)
+        grads.wait_all()
 
     def sync_all():
         torch.cuda.synchronize(device)
@@ -307,14 +297,18 @@ def kernel_legs(ops, layers, a, dtype, device, pk, status):
     # kernel B: low-rank along tokens + INT8, transposed out
     t = _graph_time(lambda i: ops.col_ht_quant(fc1[i % n]["go"], cfg.order_l, cfg.sel_l, cfg.q_gw, "transposed"), n, device)
     kern["col_hla_quant_int8_go"] = dict(us=t, bytes=L * O * esz + lp * O, bound="hbm")
-    t = _graph_time(lambda i: ops.col_ht_quant(fc1[i % n]["w"], 16, list(range(16)), cfg.q_w, "natural"), n, device)
-    kern["col_ht_quant_int4_w"] = dict(us=t, bytes=O * I * esz + O * I // 2, bound="hbm")
+    t = _graph_time(lambda i: ops.col_ht_quant(fc1[i % n]["w"], 16, list(range(16)), ops.Quant(4, "int8", "philox", "tensor", 0, 9), "natural"), n, device)
+    kern["col_ht_quant_w"] = dict(us=t, bytes=O * I * esz + O * I, bound="hbm")
+    # the fused pair the layer runs on grad_out (stats pass + quantise pass, both operands)
+    t = _graph_time(lambda i: ops.go_dual_quant(fc1[i % n]["go"], cfg), n, device)
+    kern["go_dual_quant"] = dict(us=t, bytes=L * O * esz + L * O // 2 + lp * O + 8, bound="hbm")
     # kernel C: the two integer GEMMs
     q_go, s_go = ops.row_ht_quant(fc1[0]["go"], 16, cfg.q_gx)
-    q_w, s_w, _ = ops.col_ht_quant(fc1[0]["w"], 16, list(range(16)), cfg.q_w, "natural")
+    q_w8 = ops.Quant(4, "int8", "philox", "tensor", 0, 9)          # the layer keeps weight codes one per byte
+    q_w, s_w, _ = ops.col_ht_quant(fc1[0]["w"], 16, list(range(16)), q_w8, "natural")
     q_gw, s_gw, _ = ops.col_ht_quant(fc1[0]["go"], cfg.order_l, cfg.sel_l, cfg.q_gw, "transposed")
-    t = _graph_time(lambda i: ops.gemm_i8(q_go, "int4", q_w, "int4", L, I, O, s_go, s_w, 1 / 16, dtype, status), 8, device)
-    kern["gemm_gx_int4"] = dict(us=t, ops=2 * L * I * O, bound="tensor")
+    t = _graph_time(lambda i: ops.gemm_i8(q_go, "int4", q_w, "int8", L, I, O, s_go, s_w, 1 / 16, dtype, status), 8, device)
+    kern["gemm_gx_int4xint8"] = dict(us=t, ops=2 * L * I * O, bound="tensor")
     t = _graph_time(lambda i: ops.gemm_i8(q_gw, "int8", fc1[0]["x_q_t"], "int8", O, I, lp, s_gw, fc1[0]["s_x"], 1 / 16, dtype, status), 8, device)
     kern["gemm_gw_int8"] = dict(us=t, ops=2 * O * I * lp, bound="tensor")
     t_layer = _graph_time(lambda i: ops.linear_backward(fc1[i % n]["go"], fc1[i % n]["w"], fc1[i % n]["x_q_t"], fc1[i % n]["s_x"], cfg, status=status), n, device)
@@ -328,7 +322,7 @@ def kernel_legs(ops, layers, a, dtype, device, pk, status):
         else:
             v["achieved"], v["unit"], v["peak"] = round(v["ops"] / v["us"] / 1e6, 1), "TOP/s", int8_peak
         v["frac"] = round(v["achieved"] / v["peak"], 4)
-    in_layer = ["row_ht_quant_int4_tensor", "col_hla_quant_int8_go", "col_ht_quant_int4_w", "gemm_gx_int4", "gemm_gw_int8"]
+    in_layer = ["go_dual_quant", "col_ht_quant_w", "gemm_gx_int4xint8", "gemm_gw_int8"]
     top = max(in_layer, key=lambda k: kern[k]["us"])
     tk = kern[top]
     roof = {"kernel": top, "bound": tk["bound"], "achieved": tk["achieved"], "peak": tk["peak"], "unit": tk["unit"],

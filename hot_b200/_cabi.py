@@ -49,6 +49,8 @@ EXPORTS = {
     "hot_col_ht_quant_static": (ctypes.c_int, [c_vp, ctypes.c_int, c_i64, c_i64, c_i64, ctypes.c_int, ctypes.POINTER(c_i32),
                                                ctypes.c_int, ctypes.POINTER(HotQuant), ctypes.c_int, c_vp, c_i64, c_vp,
                                                c_vp]),
+    "hot_go_dual_quant": (ctypes.c_int, [c_vp, c_i64, c_i64, c_i64, ctypes.POINTER(HotLinearCfg), c_vp, c_i64, c_vp, c_vp,
+                                         c_i64, c_vp, c_vp, c_vp, c_vp]),
     "hot_gemm_i8": (ctypes.c_int, [c_vp, ctypes.c_int, c_i64, c_vp, ctypes.c_int, c_i64, c_i64, c_i64, c_i64, c_vp,
                                    ctypes.c_int, c_vp, ctypes.c_int, ctypes.c_float, c_vp, ctypes.c_int, c_i64, c_vp,
                                    c_vp]),

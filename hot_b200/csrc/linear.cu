@@ -98,6 +98,26 @@ extern "C" int hot_abc_compress(const void* x, int64_t L, int64_t I, int64_t ldx
                           x_q_t, pitch, scale_x, (uint32_t*)workspace, stream);
 }
 
+extern "C" int hot_go_dual_quant(const void* go, int64_t L, int64_t O, int64_t ldgo, const hot_linear_cfg_t* cfg, void* q_go,
+                                 int64_t ld_qgo, float* s_gx, void* q_gw_t, int64_t ld_qgw, float* s_gw,
+                                 uint32_t* scratch, uint32_t* status_word, hot_stream_t stream) {
+  using namespace hot;
+  if (!go || !cfg || !q_go || !s_gx || !q_gw_t || !s_gw || !scratch) HOT_FAIL(HOT_ERR_ARG, "hot_go_dual_quant: null pointer");
+  if (L <= 0 || O <= 0) HOT_FAIL(HOT_ERR_ARG, "hot_go_dual_quant: bad shape");
+  if (int rc = validate_quant(&cfg->q_gx, "hot_go_dual_quant")) return rc;
+  if (int rc = validate_quant(&cfg->q_gw, "hot_go_dual_quant")) return rc;
+  if (!go_dual_supported(L, O, ldgo, cfg->dtype, cfg->order_o, cfg->order_l, cfg->rank_l, cfg->sel_l, cfg->q_gx, cfg->q_gw))
+    HOT_FAIL(HOT_ERR_UNSUPPORTED,
+             "hot_go_dual_quant covers: low-rank basis = 8 lowest-sequency rows of H_16, tokens %% 32 == 0, channels %% 64 == 0, "
+             "INT8 storage on the g_w side, nearest or Philox rounding");
+  const int64_t need_x = cfg->q_gx.storage == HOT_STORE_INT4 ? O / 2 : O;
+  if (ld_qgo < need_x || ld_qgo % 16 || ld_qgw < L / 2 || ld_qgw % 16 || ((uintptr_t)q_go) % 16 || ((uintptr_t)q_gw_t) % 16 ||
+      ((uintptr_t)go) % 16)
+    HOT_FAIL(HOT_ERR_ARG, "hot_go_dual_quant: buffers and pitches must be 16-byte aligned and cover the codes");
+  return go_dual_quant(go, cfg->dtype, L, O, ldgo, cfg->order_o, cfg->sel_l, cfg->q_gx, cfg->q_gw, q_go, ld_qgo, s_gx, q_gw_t,
+                       ld_qgw, s_gw, scratch, scratch + L, status_word, (cudaStream_t)stream);
+}
+
 extern "C" int hot_linear_backward(const void* go, int64_t ldgo, const void* w, int64_t ldw, const void* x_q_t,
                                    const float* scale_x, int64_t L, int64_t O, int64_t I, const hot_linear_cfg_t* cfg,
                                    void* grad_x, int64_t ldgx, void* grad_w, int64_t ldgw, void* workspace,

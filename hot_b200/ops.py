@@ -194,6 +194,28 @@ def abc_compress(x: torch.Tensor, cfg: LinearConfig):
     return x_q_t, scale
 
 
+def go_dual_quant(go: torch.Tensor, cfg: LinearConfig, status: Optional[torch.Tensor] = None):
+    """Both quantised operands of grad_out from the fused kernels (one HBM read per pass):
+    returns (q_go codes [L, O/2 or O], s_gx [1] or [L], q_gw_t codes [O, pitch], s_gw [1] or [O]).
+    Raises for configurations the fused kernels do not cover (see ``hot_go_dual_quant``)."""
+    _require_cuda(go)
+    L, O = go.shape
+    cc = cfg.to_c(go.dtype)
+    gx4 = cfg.q_gx.storage == "int4"
+    q_go = torch.empty((L, _pitch16(O // 2 if gx4 else O)), dtype=torch.uint8, device=go.device)
+    lp = cfg.out_len(L)
+    q_gw = torch.empty((O, _pitch16(lp)), dtype=torch.uint8, device=go.device)
+    s_gx = torch.empty((L if cfg.q_gx.scale == "row" else 1,), dtype=torch.float32, device=go.device)
+    s_gw = torch.empty((O if cfg.q_gw.scale == "row" else 1,), dtype=torch.float32, device=go.device)
+    ws = torch.empty((L + O + 64,), dtype=torch.int32, device=go.device)
+    with torch.cuda.device(go.device):
+        C.check(C.lib().hot_go_dual_quant(go.data_ptr(), L, O, go.stride(0), ctypes.byref(cc), q_go.data_ptr(), q_go.stride(0),
+                                          s_gx.data_ptr(), q_gw.data_ptr(), q_gw.stride(0), s_gw.data_ptr(), ws.data_ptr(),
+                                          status.data_ptr() if status is not None else None, _stream(go)),
+                "hot_go_dual_quant")
+    return q_go[:, :(O // 2 if gx4 else O)], s_gx, q_gw, s_gw
+
+
 _workspaces: dict = {}
 
 

@@ -169,6 +169,22 @@ int hot_abc_compress(const void* x, int64_t L, int64_t I, int64_t ldx, const hot
                      hot_stream_t stream);
 
 /*
+ * Both quantised operands of grad_out in two fused launches (abs-max pass + quantise pass),
+ * each reading go [L, O] once through a TMA-fed shared-memory pipeline:
+ *   q_go   [L, O] codes of Q(HT_O(go)) for g_x (cfg->q_gx; INT4 packed or INT8), scale(s) s_gx
+ *   q_gw_t [O, L/2] INT8 codes of Q(HLA(go))^T for g_w (cfg->q_gw), scale(s) s_gw
+ * bit-identical to hot_row_ht_quant + hot_col_ht_quant on the same input.  Covers the low-rank
+ * basis "8 lowest-sequency rows of H_16" (cfg->order_l = 16, rank_l = 8), L % 32 == 0,
+ * O % 64 == 0, INT8 storage for q_gw, nearest or Philox rounding; HOT_ERR_UNSUPPORTED otherwise.
+ *   scratch  L + O + 2 words (per-token and per-channel abs-max, whichever mode is on)
+ * Stands in for the same reference code as those two functions (both read grad_output:
+ * utils/quant_matmul.py:237-257 and :300-320).
+ */
+int hot_go_dual_quant(const void* go, int64_t L, int64_t O, int64_t ldgo, const hot_linear_cfg_t* cfg,
+                      void* q_go, int64_t ld_qgo, float* s_gx, void* q_gw_t, int64_t ld_qgw, float* s_gw,
+                      uint32_t* scratch, uint32_t* status_word, hot_stream_t stream);
+
+/*
  * The HOT backward of one linear layer:
  *   grad_x [L, I] = (Q(HT_O(go)) . Q(HT_O(w))) * s_go * s_w / order_o
  *   grad_w [O, I] = (Q(HLA(go))^T . x_q) * s_gw * s_x / order_l

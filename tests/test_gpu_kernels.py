@@ -276,3 +276,38 @@ def test_errors_are_reported(ops):
     # empty input is a no-op
     codes, scales = ops.row_ht_quant(torch.zeros((0, 64), device="cuda"), 16, ops.Quant(8, "int8", scale="row"))
     assert codes.shape == (0, 64)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("rounding", ["philox", "nearest"])
+@pytest.mark.parametrize("gx_scale,gw_scale", [("tensor", "tensor"), ("row", "row")])
+@pytest.mark.parametrize("L,O,order_o,gx_storage", [(32 * 21, 192, 16, "int4"), (256 + 96, 128, 64, "int8"), (512, 64, 32, "int4")])
+def test_go_dual_quant_matches_the_separate_kernels(ops, dtype, rounding, gx_scale, gw_scale, L, O, order_o, gx_storage):
+    """The fused grad_out kernels against row_ht_quant + col_ht_quant (themselves checked against
+    the oracle above): codes and scales bit-identical, ragged last token tile included."""
+    torch.manual_seed(L + O)
+    go = (torch.randn(L, O, device="cuda") * 1e-3).to(dtype)
+    go[5] *= 30.0
+    go[:, 3] *= 10.0
+    sel = [int(v) for v in oc.lowrank_preset(16, 8)]
+    bits_x = 4 if gx_storage == "int4" else 8
+    cfg = ops.LinearConfig(order_o=order_o, order_l=16, sel_l=sel,
+                           q_gx=ops.Quant(bits_x, gx_storage, rounding, gx_scale, 21, 5),
+                           q_gw=ops.Quant(8, "int8", rounding, gw_scale, 21, 6))
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    q_go, s_gx, q_gw, s_gw = ops.go_dual_quant(go, cfg, status)
+    ref_go, ref_sx = ops.row_ht_quant(go, order_o, cfg.q_gx)
+    ref_gw, ref_sw, lp = ops.col_ht_quant(go, 16, sel, cfg.q_gw, "transposed")
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    assert torch.equal(s_gx.view(torch.int32), ref_sx.view(torch.int32))
+    assert torch.equal(s_gw.view(torch.int32), ref_sw.view(torch.int32))
+    assert torch.equal(q_go, ref_go)
+    assert torch.equal(q_gw[:, :lp], ref_gw[:, :lp])
+
+
+def test_go_dual_quant_rejects_what_it_does_not_cover(ops):
+    go = torch.zeros((64, 64), device="cuda")
+    cfg = ops.LinearConfig(order_o=16, order_l=32, sel_l=list(oc.wht_selection(6304, 50)[1]))
+    with pytest.raises(RuntimeError, match="hot_go_dual_quant covers"):
+        ops.go_dual_quant(go, cfg)
