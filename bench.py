@@ -237,7 +237,7 @@ def run_hot(a):
     if rank == 0 and world == 1:
         if not a.no_kernels:
             out["kernels"], out["roofline"], out["fp_backward_bf16_cublas"] = kernel_legs(ops, layers, a, dtype, device, pk, status)
-        out["e2e"] = e2e_leg(layers, a, dtype, device, flops)
+        out["e2e"] = e2e_leg(layers, a, dtype, device, flops) if a.e2e_steps > 0 else None
         if not a.no_cpu_baseline:
             out["cpu_baseline"] = cpu_baseline(threads=1)
     elif rank == 0:
