@@ -53,6 +53,12 @@ def parse():
     p.add_argument("--e2e-steps", type=int, default=2)
     p.add_argument("--no-cpu-baseline", action="store_true")
     p.add_argument("--no-kernels", action="store_true", help="skip the per-kernel roofline legs")
+    p.add_argument("--sweep", action="store_true",
+                   help="instead of the step: the stand-alone fused Hadamard+quantise sweep (M x K x order x "
+                        "format x rounding x scale x dtype), one JSON line with a table of GB/s")
+    p.add_argument("--large-mlp", action="store_true",
+                   help="instead of the step: HOT backward vs bf16 matmul on large transformer MLP linears "
+                        "(16384 tokens; 4096->11008, 11008->4096, 4096->4096; heavy-tailed outlier channels)")
     return p.parse_args()
 
 
@@ -248,6 +254,92 @@ def run_hot(a):
         dist.destroy_process_group()
 
 
+def run_sweep(a):
+    """BASELINE config 2: the fused transform + quantise kernel alone.  Algorithmic bytes per launch:
+    M*K*sizeof(in) + M*K*bits/8 + 4 (per tensor) or + 4*M (per token), over the CUDA-event time."""
+    from hot_b200 import ops
+    device = torch.device("cuda", 0)
+    torch.cuda.set_device(device)
+    pk = peaks()
+    rows = []
+    g = torch.Generator(device=device).manual_seed(0)
+    for dt_name, dt in (("bf16", torch.bfloat16), ("fp32", torch.float32)):
+        for M in (4096, 16384, 65536):
+            for K in (768, 1024, 4096, 8192):
+                x = torch.randn((M, K), device=device, generator=g).to(dt)
+                for order in (16, 32, 64):
+                    for fmt, bits in (("int4", 4), ("int8", 8)):
+                        for rounding in ("philox", "nearest"):
+                            for scale in ("tensor", "row"):
+                                q = ops.Quant(bits, fmt, rounding, scale, 0, 1)
+                                fn = lambda: ops.row_ht_quant(x, order, q)
+                                for _ in range(2):
+                                    fn()
+                                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                                torch.cuda.synchronize(device)
+                                n_it = 5
+                                e0.record()
+                                for _ in range(n_it):
+                                    fn()
+                                e1.record()
+                                torch.cuda.synchronize(device)
+                                us = e0.elapsed_time(e1) * 1e3 / n_it
+                                nbytes = M * K * x.element_size() + M * K * bits // 8 + (4 * M if scale == "row" else 4)
+                                rows.append(dict(dtype=dt_name, M=M, K=K, order=order, fmt=fmt, rounding=rounding, scale=scale,
+                                                 us=round(us, 1), gbs=round(nbytes / us / 1e3, 1)))
+                del x
+    best = max(rows, key=lambda r: r["gbs"])
+    big = [r for r in rows if r["M"] * r["K"] >= 16384 * 4096]          # tensors larger than L2
+
+    def med(sel):
+        v = sorted(r["gbs"] for r in big if sel(r))
+        return v[len(v) // 2] if v else None
+    summary = {"%s_%s_%s" % (d, rd, sc): med(lambda r: r["dtype"] == d and r["rounding"] == rd and r["scale"] == sc)
+               for d in ("bf16", "fp32") for rd in ("philox", "nearest") for sc in ("tensor", "row")}
+    print(json.dumps({"metric": "fused_hadamard_quant_hbm_gbs", "unit": "GB/s", "value": best["gbs"], "best": best,
+                      "median_gbs_large_tensors": summary, "peak": pk["hbm"], "peak_source": pk["source"] + " hbm_gbs",
+                      "frac_best": round(best["gbs"] / pk["hbm"], 4), "cases": len(rows), "table": rows,
+                      "note": "eager launches: cases under ~50 us include host launch latency"}), flush=True)
+
+
+def run_large_mlp(a):
+    """BASELINE config 4: large MLP linears in bf16 at 16384 tokens, activations with heavy-tailed
+    outlier channels (1 % of channels scaled by |Student-t(3)| draws), compressed activation buffer."""
+    from hot_b200 import ops
+    from hot_b200.hadamard_matmul import lowrank_selection
+    device = torch.device("cuda", 0)
+    torch.cuda.set_device(device)
+    torch.manual_seed(0)
+    M = 16384
+    order_l, sel = lowrank_selection(M, "half16")
+    status = torch.zeros(1, dtype=torch.int32, device=device)
+    out = []
+    for i_f, o_f in ((4096, 11008), (11008, 4096), (4096, 4096)):
+        x = torch.randn((M, i_f), device=device)
+        idx = torch.randperm(i_f, device=device)[:max(1, i_f // 100)]
+        x[:, idx] *= torch.distributions.StudentT(3.0).sample((idx.numel(),)).abs().to(device) * 10.0
+        x = x.to(torch.bfloat16)
+        w = ((torch.rand((o_f, i_f), device=device) * 2 - 1) / i_f ** 0.5).to(torch.bfloat16)
+        go = (torch.randn((M, o_f), device=device) * 1e-3).to(torch.bfloat16)
+        cfg = ops.LinearConfig(order_o=16, order_l=order_l, sel_l=sel)
+        x_q_t, s_x = ops.abc_compress(x, cfg)
+        t_hot = _graph_time(lambda i: ops.linear_backward(go, w, x_q_t, s_x, cfg, status=status), 3, device, warm=1)
+        t_fp = _graph_time(lambda i: (torch.matmul(go, w), torch.matmul(go.t(), x)), 3, device, warm=1)
+        gx, gw = ops.linear_backward(go, w, x_q_t, s_x, cfg, status=status)
+        ex, ew = torch.matmul(go, w).float(), torch.matmul(go.t(), x).float()
+        cos = lambda p_, q_: float(torch.nn.functional.cosine_similarity(p_.float().flatten(), q_.flatten(), dim=0))
+        flops = 4.0 * M * i_f * o_f
+        out.append({"in": i_f, "out": o_f, "hot_us": round(t_hot, 1), "bf16_matmul_us": round(t_fp, 1),
+                    "speedup_vs_bf16": round(t_fp / t_hot, 3), "hot_effective_tops": round(flops / t_hot / 1e6, 1),
+                    "activation_buffer_bytes": int(x_q_t.numel()), "activation_bytes_bf16": int(x.numel() * 2),
+                    "cos_gx_vs_fp": round(cos(gx, ex), 4), "cos_gw_vs_fp": round(cos(gw, ew), 4)})
+        del x, w, go, x_q_t, gx, gw, ex, ew
+    torch.cuda.synchronize(device)
+    if int(status.item()) != 0:
+        raise SystemExit("a bounded device-side wait ran out")
+    print(json.dumps({"metric": "hot_backward_large_mlp", "tokens": M, "dtype": "bf16", "layers": out}), flush=True)
+
+
 def _graph_time(fn, iters, device, warm=3):
     """Average device time of fn() in microseconds: captured once per distinct call, replayed."""
     side = torch.cuda.Stream(device)
@@ -441,5 +533,9 @@ if __name__ == "__main__":
     args = parse()
     if args.impl == "reference":
         run_reference(args)
+    elif args.sweep:
+        run_sweep(args)
+    elif args.large_mlp:
+        run_large_mlp(args)
     else:
         run_hot(args)

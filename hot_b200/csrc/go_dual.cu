@@ -144,7 +144,7 @@ __device__ __forceinline__ uint4 quantise16_int8(const float (&y)[16], const Sca
 
 // PASS 0: statistics.  PASS 1: quantise (RX / RW: rounding of the g_x / g_w side).
 template <typename T, int PASS, int RX, int RW>
-__global__ void __launch_bounds__(kThreads) go_dual_kernel(const __grid_constant__ CUtensorMap tmap, DualParams p) {
+__global__ void __launch_bounds__(kThreads, sizeof(T) == 2 ? 3 : 1) go_dual_kernel(const __grid_constant__ CUtensorMap tmap, DualParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~(uintptr_t)127);
   uint8_t* tile[2] = {smem, smem + Tile<T>::kBytes};
@@ -351,7 +351,7 @@ int launch_dual(const void* go, int64_t ldgo, const DualParams& p, int rx, int r
   if (int rc = make_map(&tmap, go, p.L, (int64_t)p.O * sizeof(T), ldgo * (int64_t)sizeof(T), Tile<T>::kRowBytes, kTT, false))
     return rc;
   const int num_tiles = (p.O / kTC) * (int)((p.L + kTT - 1) / kTT);
-  const int per_sm = sizeof(T) == 2 ? 2 : 1;  // resident CTAs per SM by shared memory
+  const int per_sm = sizeof(T) == 2 ? 3 : 1;  // resident CTAs per SM by shared memory (75 KB / 140 KB each)
   int grid = sms * per_sm;
   if (grid > num_tiles) grid = num_tiles;
   HOT_CUDA(cudaMemsetAsync(p.max_x, 0, sizeof(uint32_t) * (p.x_row ? p.L : 1), st));

@@ -18,12 +18,14 @@ namespace hot {
 namespace {
 
 constexpr int kThreads = 256;
-constexpr int kVmax = 4;  // 16-element runs per thread in the per-row kernel: cols <= 4 * 16 * 256
+constexpr int kVmaxLimit = 4;  // 16-element runs per thread in the per-row kernel: cols <= 4 * 16 * 256
 
 // ---------------------------------------------------------------------------------------
 // per-row scale: one pass, row resident in registers
 // ---------------------------------------------------------------------------------------
-template <typename T, int ROUND, int STORE4>
+// kVmax: runs per thread (1, 2 or 4): the launcher spreads a row over as many threads as it has
+// runs, so short rows cost few registers and more CTAs fit per SM.
+template <typename T, int ROUND, int STORE4, int kVmax>
 __global__ void __launch_bounds__(kThreads) row_ht_quant_rowscale_kernel(
     const T* __restrict__ x, int64_t rows, int cols, int64_t ldx, int n, QuantDev q, uint8_t* __restrict__ codes,
     int64_t ld_codes, float* __restrict__ scales, int tpr) {
@@ -183,14 +185,19 @@ int launch_typed(const T* x, int64_t rows, int cols, int64_t ldx, int n, const h
   if (hq.scale_mode == HOT_SCALE_ROW) {
     const int nrun = cols >> 4;
     int tpr = 32;
-    while (tpr < kThreads && (nrun + tpr - 1) / tpr > kVmax) tpr <<= 1;
-    if ((nrun + tpr - 1) / tpr > kVmax)
+    while (tpr < kThreads && tpr < nrun) tpr <<= 1;  // one run per thread while a CTA can hold the row
+    const int nv = (nrun + tpr - 1) / tpr;
+    if (nv > kVmaxLimit)
       HOT_FAIL(HOT_ERR_UNSUPPORTED, "hot_row_ht_quant: per-row scale supports cols <= %d (got %d)",
-               kVmax * 16 * kThreads, cols);
+               kVmaxLimit * 16 * kThreads, cols);
     const int rows_per_cta = kThreads / tpr;
-    const int64_t grid = (rows + rows_per_cta - 1) / rows_per_cta;
-    row_ht_quant_rowscale_kernel<T, ROUND, STORE4>
-        <<<(unsigned)grid, kThreads, 0, st>>>(x, rows, cols, ldx, n, q, codes, ld_codes, scales, tpr);
+    const unsigned grid = (unsigned)((rows + rows_per_cta - 1) / rows_per_cta);
+    if (nv == 1)
+      row_ht_quant_rowscale_kernel<T, ROUND, STORE4, 1><<<grid, kThreads, 0, st>>>(x, rows, cols, ldx, n, q, codes, ld_codes, scales, tpr);
+    else if (nv == 2)
+      row_ht_quant_rowscale_kernel<T, ROUND, STORE4, 2><<<grid, kThreads, 0, st>>>(x, rows, cols, ldx, n, q, codes, ld_codes, scales, tpr);
+    else
+      row_ht_quant_rowscale_kernel<T, ROUND, STORE4, 4><<<grid, kThreads, 0, st>>>(x, rows, cols, ldx, n, q, codes, ld_codes, scales, tpr);
   } else {
     const int grid = grid_for(rows * (cols >> 4), sms);
     HOT_CUDA(cudaMemsetAsync(absmax_ws, 0, sizeof(uint32_t), st));
