@@ -56,6 +56,10 @@ def parse():
     p.add_argument("--sweep", action="store_true",
                    help="instead of the step: the stand-alone fused Hadamard+quantise sweep (M x K x order x "
                         "format x rounding x scale x dtype), one JSON line with a table of GB/s")
+    p.add_argument("--vit-train", action="store_true",
+                   help="instead of the step: data-parallel ViT-B/16 training step (forward, HOT backward on the 48 "
+                        "block linears, DDP all-reduce, SGD), images/s, beside the same model with plain nn.Linear")
+    p.add_argument("--batch", type=int, default=256, help="images per GPU for --vit-train")
     p.add_argument("--large-mlp", action="store_true",
                    help="instead of the step: HOT backward vs bf16 matmul on large transformer MLP linears "
                         "(16384 tokens; 4096->11008, 11008->4096, 4096->4096; heavy-tailed outlier channels)")
@@ -340,6 +344,74 @@ def run_large_mlp(a):
     print(json.dumps({"metric": "hot_backward_large_mlp", "tokens": M, "dtype": "bf16", "layers": out}), flush=True)
 
 
+def run_vit_train(a):
+    """BASELINE config 5: synthetic 224x224x3 images N(0,1), 100 random classes, random-init ViT-B/16
+    in bf16, cross-entropy, SGD; per GPU `--batch` images (256 -> 50,432 tokens).  One process per
+    GPU, gradients all-reduced by DistributedDataParallel over NCCL as in the reference."""
+    import torch.distributed as dist
+    import torch.nn as nn
+    import hot_b200.args as hargs
+    from hot_b200.vit import apply_hot, vit_base_patch16_224
+    rank, world, local = (int(os.environ.get(k, d)) for k, d in (("RANK", 0), ("WORLD_SIZE", 1), ("LOCAL_RANK", 0)))
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    hargs.transform_scheme = "gih_gwlr"
+    hargs.TransformGogi = hargs.TransformWgt = hargs.TransformGogw = hargs.TransformInput = True
+    hargs.GogiQuantBit, hargs.weightQuantBit, hargs.GogwQuantBit, hargs.actQuantBit = 4, 4, 8, 8
+    hargs.quantBWDGogi = hargs.quantBWDWgt = hargs.quantBWDGogw = hargs.quantBWDAct = "stoch"
+    hargs.lowRankPreset = "half16"
+    g = torch.Generator(device=device).manual_seed(1000 + rank)
+    x = torch.randn((a.batch, 3, 224, 224), device=device, generator=g)
+    y = torch.randint(0, 100, (a.batch,), device=device, generator=g)
+    results = {}
+    for mode in ("hot", "bf16"):
+        torch.manual_seed(0)                                    # same weights on every rank and in both modes
+        model = vit_base_patch16_224(100).to(device=device, dtype=torch.bfloat16)
+        n_hot = apply_hot(model) if mode == "hot" else 0
+        net = nn.parallel.DistributedDataParallel(model, device_ids=[local]) if world > 1 else model
+        opt = torch.optim.SGD(net.parameters(), lr=1e-3)
+
+        def step():
+            opt.zero_grad(set_to_none=True)
+            loss = nn.functional.cross_entropy(net(x.to(torch.bfloat16)).float(), y)
+            loss.backward()
+            opt.step()
+            return loss
+
+        for _ in range(max(a.warmup, 3)):
+            step()
+        torch.cuda.synchronize(device)
+        if world > 1:
+            dist.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        steps = min(a.steps, 10)
+        e0.record()
+        for _ in range(steps):
+            loss = step()
+        e1.record()
+        torch.cuda.synchronize(device)
+        ms = torch.tensor([e0.elapsed_time(e1) / steps], device=device)
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        results[mode] = dict(ms_per_step=round(float(ms.item()), 3), images_per_s=round(a.batch * world / float(ms.item()) * 1e3, 1),
+                             loss=round(float(loss.item()), 4), hot_layers=n_hot,
+                             peak_mem_gb=round(torch.cuda.max_memory_allocated(device) / 2 ** 30, 2))
+        del model, net, opt
+        torch.cuda.empty_cache()
+        torch.cuda.reset_peak_memory_stats(device)
+    if rank == 0:
+        print(json.dumps({"metric": "vit_b16_train_images_per_s", "unit": "images/s", "value": results["hot"]["images_per_s"],
+                          "n_gpus": world, "scaling": "weak", "higher_is_better": True, "data": "synthetic", "dtype": "bf16",
+                          "config": {"workload": "vit_b16_dp_train_step", "images_per_gpu": a.batch, "tokens_per_gpu": a.batch * 197,
+                                     "optimizer": "SGD", "hot": "48 block linears, half16 low-rank, INT4 g_x / INT8 g_w, Philox"},
+                          "hot": results["hot"], "plain_bf16_linear": results["bf16"],
+                          "hot_vs_plain": round(results["hot"]["images_per_s"] / results["bf16"]["images_per_s"], 3)}), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def _graph_time(fn, iters, device, warm=3):
     """Average device time of fn() in microseconds: captured once per distinct call, replayed."""
     side = torch.cuda.Stream(device)
@@ -537,5 +609,7 @@ if __name__ == "__main__":
         run_sweep(args)
     elif args.large_mlp:
         run_large_mlp(args)
+    elif args.vit_train:
+        run_vit_train(args)
     else:
         run_hot(args)

@@ -178,3 +178,27 @@ def test_hlq_backward_plugin_call(hot):
         HLQ_backward.backward(go.t().contiguous().t(), w, x, 0, 0, 16, False)
     with pytest.raises(RuntimeError, match="must be 2D"):
         HLQ_backward.backward(go[None], w, x, 0, 0, 16, False)
+
+
+def test_vit_with_hot_linears_trains(hot):
+    """A small ViT of the benchmark's architecture: apply_hot swaps exactly the block linears, a few
+    SGD steps on a fixed batch reduce the loss, and gradients reach every parameter."""
+    args, qm = hot
+    from hot_b200.vit import VisionTransformer, apply_hot
+    torch.manual_seed(0)
+    model = VisionTransformer(img_size=64, patch=16, dim=64, depth=2, heads=4, num_classes=10).cuda()
+    assert apply_hot(model) == 8
+    assert isinstance(model.blocks[0].attn.qkv, qm.HQ_Linear) and model.blocks[1].mlp.fc2.layer_name == "blocks.1.mlp.fc2"
+    assert type(model.head) is nn.Linear
+    x = torch.randn(32, 3, 64, 64, device="cuda")            # 32 x 17 tokens = 544 = 16 * 34
+    y = torch.randint(0, 10, (32,), device="cuda")
+    opt = torch.optim.SGD(model.parameters(), lr=0.05)
+    losses = []
+    for _ in range(12):
+        opt.zero_grad()
+        loss = nn.functional.cross_entropy(model(x), y)
+        loss.backward()
+        opt.step()
+        losses.append(float(loss))
+    assert all(p.grad is not None and torch.isfinite(p.grad).all() for p in model.parameters())
+    assert losses[-1] < losses[0] - 0.1, losses
