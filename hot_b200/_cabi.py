@@ -14,7 +14,7 @@ LIB_PATH = os.path.join(HERE, "lib", "libhot_b200.so")
 HOT_OK, HOT_ERR_ARG, HOT_ERR_UNSUPPORTED, HOT_ERR_CUDA, HOT_ERR_TIMEOUT, HOT_ERR_WORKSPACE = range(6)
 HOT_F32, HOT_BF16, HOT_I32 = 0, 1, 2
 ROUND_NEAREST, ROUND_STOCH_PHILOX, ROUND_STOCH_NOISE = 0, 1, 2
-SCALE_TENSOR, SCALE_ROW = 0, 1
+SCALE_TENSOR, SCALE_ROW, SCALE_SAWB = 0, 1, 2
 STORE_INT8, STORE_INT4 = 0, 1
 LAYOUT_NATURAL, LAYOUT_TRANSPOSED = 0, 1
 
@@ -46,6 +46,7 @@ EXPORTS = {
     "hot_col_ht_quant": (ctypes.c_int, [c_vp, ctypes.c_int, c_i64, c_i64, c_i64, ctypes.c_int, ctypes.POINTER(c_i32),
                                         ctypes.c_int, ctypes.POINTER(HotQuant), ctypes.c_int, c_vp, c_i64, c_vp, c_vp,
                                         c_vp]),
+    "hot_col_ht_quant_scratch_words": (ctypes.c_size_t, [ctypes.c_int, c_i64, c_i64, ctypes.c_int, ctypes.c_int, ctypes.c_int]),
     "hot_col_ht_quant_static": (ctypes.c_int, [c_vp, ctypes.c_int, c_i64, c_i64, c_i64, ctypes.c_int, ctypes.POINTER(c_i32),
                                                ctypes.c_int, ctypes.POINTER(HotQuant), ctypes.c_int, c_vp, c_i64, c_vp,
                                                c_vp]),

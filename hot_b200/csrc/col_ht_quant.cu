@@ -25,6 +25,7 @@ struct ColParams {
   int pitch;                  // floats per tile row
   int64_t out_len;            // rows * r / n
   int scale_row, store4, noise_transposed;
+  int sawb;                   // clip from the second moment and the mean magnitude instead of the abs-max
   signed char pos[64];        // pos[k] = output slot of natural row k, or -1
 };
 
@@ -104,6 +105,7 @@ __global__ void __launch_bounds__(kThreads) col_ht_absmax_kernel(const T* __rest
   float cm[VEC * CPL];
 #pragma unroll
   for (int i = 0; i < VEC * CPL; ++i) cm[i] = 0.0f;
+  double sum_sq = 0.0, sum_abs = 0.0;  // SAWB statistics of this thread
   for (int b = warp; b < p.nb; b += kWarps) {
     if (blk0 + b >= nblk) break;
     float v[VEC * CPL][N];
@@ -113,8 +115,44 @@ __global__ void __launch_bounds__(kThreads) col_ht_absmax_kernel(const T* __rest
       if (p.pos[k] >= 0) {
 #pragma unroll
         for (int i = 0; i < VEC * CPL; ++i) cm[i] = fmaxf(cm[i], fabsf(v[i][k]));
+        if (p.sawb) {
+          float sq = 0.0f, ab = 0.0f;  // columns beyond the matrix were loaded as zeros
+#pragma unroll
+          for (int i = 0; i < VEC * CPL; ++i) {
+            sq = fmaf(v[i][k], v[i][k], sq);
+            ab += fabsf(v[i][k]);
+          }
+          sum_sq += (double)sq;
+          sum_abs += (double)ab;
+        }
       }
     }
+  }
+  if (p.sawb) {
+    // one (sum of squares, sum of magnitudes) pair per CTA, reduced in a fixed order; the second
+    // pass adds the pairs up in a fixed order too, so the clip value is reproducible
+    __shared__ double s_sum[2][kWarps];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      sum_sq += __shfl_xor_sync(0xFFFFFFFFu, sum_sq, o);
+      sum_abs += __shfl_xor_sync(0xFFFFFFFFu, sum_abs, o);
+    }
+    if (lane == 0) {
+      s_sum[0][warp] = sum_sq;
+      s_sum[1][warp] = sum_abs;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      double a = 0.0, b = 0.0;
+      for (int w = 0; w < kWarps; ++w) {
+        a += s_sum[0][w];
+        b += s_sum[1][w];
+      }
+      double* part = reinterpret_cast<double*>(absmax) + 2 * ((size_t)blockIdx.y * gridDim.x + blockIdx.x);
+      part[0] = a;
+      part[1] = b;
+    }
+    return;
   }
   if (p.scale_row) {
 #pragma unroll
@@ -175,7 +213,42 @@ __global__ void __launch_bounds__(kThreads) col_ht_quant_kernel(const T* __restr
   }
   __syncthreads();
 
-  ScalePair sp_t = scale_from_absmax(p.scale_row ? 0.0f : __uint_as_float(absmax[0]), q.qmax);
+  float clip = 0.0f;  // SAWB clamp bound
+  if (p.sawb) {
+    // clip = 12.1 * sqrt(mean(y^2)) - 12.2 * mean(|y|) over the whole transformed tensor
+    __shared__ double s_tot[2][kWarps];
+    __shared__ float s_clip;
+    const double* part = reinterpret_cast<const double*>(absmax);
+    const int nparts = (int)(gridDim.x * gridDim.y);
+    double a = 0.0, b = 0.0;
+    for (int i = threadIdx.x; i < nparts; i += kThreads) {
+      a += part[2 * i];
+      b += part[2 * i + 1];
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      a += __shfl_xor_sync(0xFFFFFFFFu, a, o);
+      b += __shfl_xor_sync(0xFFFFFFFFu, b, o);
+    }
+    if (lane == 0) {
+      s_tot[0][warp] = a;
+      s_tot[1][warp] = b;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      double ta = 0.0, tb = 0.0;
+      for (int w = 0; w < kWarps; ++w) {
+        ta += s_tot[0][w];
+        tb += s_tot[1][w];
+      }
+      const double count = (double)p.out_len * (double)p.cols;
+      const float rms = __fsqrt_rn((float)(ta / count));
+      s_clip = __fsub_rn(__fmul_rn(12.1f, rms), __fmul_rn(12.2f, (float)(tb / count)));
+    }
+    __syncthreads();
+    clip = s_clip;
+  }
+  ScalePair sp_t = scale_from_absmax(p.sawb ? clip : (p.scale_row ? 0.0f : __uint_as_float(absmax[0])), q.qmax);
   if (!p.scale_row && blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) scales[0] = sp_t.s;
   const int qmax = (int)q.qmax;
   const int cpr = (p.nb * r) >> 3;  // 8-code chunks per tile row
@@ -190,6 +263,10 @@ __global__ void __launch_bounds__(kThreads) col_ht_quant_kernel(const T* __restr
     const float4 b = *reinterpret_cast<const float4*>(tile + cl * p.pitch + ch * 8 + 4);
     v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
     v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+    if (p.sawb) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) v[i] = fminf(fmaxf(v[i], -clip), clip);  // torch.clamp(x, -clip, clip)
+    }
     ScalePair sp = sp_t;
     if (p.scale_row) {
       sp = scale_from_absmax(__uint_as_float(absmax[c]), q.qmax);
@@ -204,12 +281,12 @@ __global__ void __launch_bounds__(kThreads) col_ht_quant_kernel(const T* __restr
         const uint4 blk = philox_block16(q, e0 >> 4);
         const bool hi = (e0 & 8u) != 0;
         const uint32_t rw[2] = {hi ? blk.z : blk.x, hi ? blk.w : blk.y};
-        const float2 bias = make_float2(sp.bias8, sp.bias8);
 #pragma unroll
         for (int i = 0; i < 8; i += 2) {
-          const float2 yb = add2(div2_exact(make_float2(v[i], v[i + 1]), sp.dv8), bias);
-          code[i] = (int)((__float2uint_rn(yb.x) + ((rw[i >> 2] >> (8 * (i & 3))) & 0xFFu)) >> 8) - (qmax + 1);
-          code[i + 1] = (int)((__float2uint_rn(yb.y) + ((rw[i >> 2] >> (8 * ((i + 1) & 3))) & 0xFFu)) >> 8) - (qmax + 1);
+          const float2 t = philox_offset_bits2(make_float2(v[i], v[i + 1]), sp,
+                                               make_float2(philox_u128(rw[i >> 2], i & 3), philox_u128(rw[i >> 2], (i + 1) & 3)));
+          code[i] = (int)(__float_as_uint(t.x) & 0xFFu) - (qmax + 1);
+          code[i + 1] = (int)(__float_as_uint(t.y) & 0xFFu) - (qmax + 1);
         }
       } else {
         uint4 blk = philox_block16(q, e0 >> 4);
@@ -220,7 +297,7 @@ __global__ void __launch_bounds__(kThreads) col_ht_quant_kernel(const T* __restr
             blk = philox_block16(q, (e0 >> 4) + 1);
             j = 0;
           }
-          code[i] = (int)philox_offset_code(v[i], sp, philox_byte(blk, j)) - (qmax + 1);
+          code[i] = (int)philox_offset_code(v[i], sp, __uint_as_float(0x43000000u | (philox_byte(blk, j) << 8))) - (qmax + 1);
           ++j;
         }
       }
@@ -265,7 +342,7 @@ int launch_n(const T* x, const ColParams& p, const hot_quant_t& hq, uint8_t* cod
   const int64_t nblk = p.rows / N;
   dim3 grid((unsigned)((p.cols + CC - 1) / CC), (unsigned)((nblk + p.nb - 1) / p.nb));
   const size_t smem = (size_t)CC * p.pitch * sizeof(float);
-  HOT_CUDA(cudaMemsetAsync(ws, 0, sizeof(uint32_t) * (p.scale_row ? p.cols : 1), st));
+  if (!p.sawb) HOT_CUDA(cudaMemsetAsync(ws, 0, sizeof(uint32_t) * (p.scale_row ? p.cols : 1), st));
   col_ht_absmax_kernel<T, N><<<grid, kThreads, 0, st>>>(x, p, ws);
   auto launch = [&](auto kernel) -> int {
     HOT_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
@@ -301,6 +378,30 @@ int launch_t(const T* x, int n, const ColParams& p, const hot_quant_t& hq, uint8
 }  // namespace
 }  // namespace hot
 
+namespace hot {
+namespace {
+// tile geometry shared by the launcher and the scratch-size query
+void col_tile_geometry(int dtype, int order, int r, int* cc, int* nb) {
+  const int cpl = dtype == HOT_BF16 ? 2 : 1;
+  const int per = 64 / (order * cpl);
+  const int vec = per >= 4 ? 4 : (per >= 2 ? 2 : 1);
+  *cc = 32 * vec * cpl;
+  int b = (128 / r) / 8 * 8;
+  *nb = b < 8 ? 8 : b;
+}
+}  // namespace
+}  // namespace hot
+
+extern "C" size_t hot_col_ht_quant_scratch_words(int dtype, int64_t rows, int64_t cols, int order, int r, int scale_mode) {
+  if (rows < 0 || cols <= 0 || order < 1 || r < 1 || r > order) return 0;
+  if (scale_mode == HOT_SCALE_TENSOR) return 1;
+  if (scale_mode == HOT_SCALE_ROW) return (size_t)cols;
+  int cc, nb;
+  hot::col_tile_geometry(dtype, order, r, &cc, &nb);
+  const int64_t nblk = rows / order;
+  return 4 * (size_t)((cols + cc - 1) / cc) * (size_t)((nblk + nb - 1) / nb) + 4;  // two doubles per CTA
+}
+
 extern "C" int hot_col_ht_quant(const void* x, int dtype, int64_t rows, int64_t cols, int64_t ldx, int order,
                                 const int32_t* sel, int r, const hot_quant_t* q, int logical_layout, void* codes_t,
                                 int64_t ld_codes, float* scales, uint32_t* absmax_ws, hot_stream_t stream) {
@@ -324,6 +425,10 @@ extern "C" int hot_col_ht_quant(const void* x, int dtype, int64_t rows, int64_t 
   p.r = r;
   p.out_len = rows / order * r;
   p.scale_row = q->scale_mode == HOT_SCALE_ROW;
+  p.sawb = q->scale_mode == HOT_SCALE_SAWB;
+  if (p.sawb && q->rounding != HOT_ROUND_NEAREST)
+    HOT_FAIL(HOT_ERR_ARG, "hot_col_ht_quant: HOT_SCALE_SAWB goes with HOT_ROUND_NEAREST (the reference's sawb_quantizer rounds to nearest)");
+  if (p.sawb && ((uintptr_t)absmax_ws) % 8 != 0) HOT_FAIL(HOT_ERR_ARG, "hot_col_ht_quant: scratch must be 8-byte aligned for HOT_SCALE_SAWB");
   p.store4 = q->storage == HOT_STORE_INT4;
   p.noise_transposed = logical_layout == HOT_LAYOUT_TRANSPOSED;
   for (int k = 0; k < 64; ++k) p.pos[k] = -1;
@@ -388,10 +493,10 @@ extern "C" int hot_col_ht_quant_static(const void* x, int dtype, int64_t rows, i
                                        void* codes_t, int64_t ld_codes, float* scales, hot_stream_t stream) {
   using namespace hot;
   if (!q) HOT_FAIL(HOT_ERR_ARG, "hot_col_ht_quant_static: null pointer");
-  const int64_t words = q->scale_mode == HOT_SCALE_ROW ? cols : 1;
+  const int64_t words = (int64_t)hot_col_ht_quant_scratch_words(dtype, rows, cols, order, r, q->scale_mode);
   if (words > kStaticScratchWords)
     HOT_FAIL(HOT_ERR_UNSUPPORTED,
-             "hot_col_ht_quant_static: per-row scales over %lld columns need %lld scratch words, the built-in scratch "
+             "hot_col_ht_quant_static: this scale mode over %lld columns needs %lld scratch words, the built-in scratch "
              "holds %d; use hot_col_ht_quant with a caller-owned scratch buffer",
              (long long)cols, (long long)words, kStaticScratchWords);
   uint32_t* scratch = nullptr;

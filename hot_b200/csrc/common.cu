@@ -23,7 +23,7 @@ int validate_quant(const hot_quant_t* q, const char* who) {
   if (q->storage != HOT_STORE_INT8 && q->storage != HOT_STORE_INT4) HOT_FAIL(HOT_ERR_ARG, "%s: storage %d", who, q->storage);
   if (q->storage == HOT_STORE_INT4 && q->bits > 4) HOT_FAIL(HOT_ERR_ARG, "%s: INT4 storage needs bits <= 4 (got %d)", who, q->bits);
   if (q->rounding < HOT_ROUND_NEAREST || q->rounding > HOT_ROUND_STOCH_NOISE) HOT_FAIL(HOT_ERR_ARG, "%s: rounding %d", who, q->rounding);
-  if (q->scale_mode != HOT_SCALE_TENSOR && q->scale_mode != HOT_SCALE_ROW) HOT_FAIL(HOT_ERR_ARG, "%s: scale_mode %d", who, q->scale_mode);
+  if (q->scale_mode != HOT_SCALE_TENSOR && q->scale_mode != HOT_SCALE_ROW && q->scale_mode != HOT_SCALE_SAWB) HOT_FAIL(HOT_ERR_ARG, "%s: scale_mode %d", who, q->scale_mode);
   if (q->rounding == HOT_ROUND_STOCH_NOISE && !q->noise) HOT_FAIL(HOT_ERR_ARG, "%s: explicit-noise rounding without a noise pointer", who);
   return HOT_OK;
 }

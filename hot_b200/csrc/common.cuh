@@ -112,33 +112,57 @@ __device__ __forceinline__ float2 div2_exact(float2 x, const Divisor& v) {
 
 // Everything a quantiser derives from an abs-max: the scale s = mx / qmax the caller gets back,
 // the divisor s + eps (fp32, round-to-nearest: the reference divides, it does not multiply by
-// a reciprocal), and the same divisor times 2^-8 with the offset (qmax + 1) * 2^8 for the
-// fixed-point stochastic rounding of the Philox path.
+// a reciprocal), and the constant of the Philox rounding path.
 struct ScalePair {
   float s;
-  Divisor dv;   // divide by s + eps
-  Divisor dv8;  // divide by (s + eps) * 2^-8: the quotient scaled by 256, exactly
-  float bias8;  // (qmax + 1) * 256
+  Divisor dv;  // divide by s + eps
+  float c0;    // (qmax + 1) - 128 + 1/512, see philox_offset_code
 };
 
 __device__ __forceinline__ ScalePair scale_from_absmax(float mx, float qmax) {
   ScalePair p;
   p.s = __fdiv_rn(mx, qmax);
-  const float d = __fadd_rn(p.s, kEps);
-  p.dv = make_divisor(d);
-  p.dv8 = make_divisor(d * 0.00390625f);  // * 2^-8, exact
-  p.bias8 = (qmax + 1.0f) * 256.0f;
+  p.dv = make_divisor(__fadd_rn(p.s, kEps));
+  p.c0 = (qmax + 1.0f) - 128.0f + 0.001953125f;  // exact in fp32
   return p;
 }
 
-// Philox-path rounding of one value, as an offset code in [1, 2 * qmax + 1] (code + qmax + 1):
-//   t = RN_int( RN(x / d * 256) + (qmax + 1) * 256 );   offset code = (t + R) >> 8
-// with R the element's random byte: the quotient is rounded to the nearest 1/256, then rounded
-// stochastically to an integer (up with probability frac * 256 / 256).  Because |x / d| <=
-// qmax * (1 + 2^-22) the offset code stays within [1, 2 * qmax + 1] without clamping.
-__device__ __forceinline__ uint32_t philox_offset_code(float x, const ScalePair& sp, uint32_t r8) {
-  const float yb = __fadd_rn(div_exact(x, sp.dv8), sp.bias8);
-  return (__float2uint_rn(yb) + r8) >> 8;
+// Philox-path stochastic rounding.  With y = x / d, B = qmax + 1 and R the element's random byte,
+//     offset code = floor( y + B + (R + 0.5) / 256 )        (code = offset code - B)
+// evaluated as  t1 = RN(y + c0),  t2 = t1 + u  (exact),  floor(t2),  where u = 128 + R / 256 is built
+// by dropping R into the mantissa of 128.0f and c0 = B - 128 + 1/512.  The value is shifted to be
+// positive so that floor is the rounding for both signs; adding a uniform in (0, 1) and flooring
+// rounds up with probability frac(y) to within 1/256, and the +0.5 centres it (no bias).  Since
+// |y| <= qmax * (1 + 2^-22), the offset code stays in [1, 2 * qmax + 1]: no clamp needed.
+__device__ __forceinline__ float philox_u128(uint32_t word, int byte) {
+  return __uint_as_float(__byte_perm(word, 0x43000000u, 0x7404u | ((uint32_t)byte << 4)));
+}
+constexpr float kFloorMagic = 8388608.0f;  // 2^23: RD(t + 2^23) keeps floor(t) in the low mantissa bits
+
+__device__ __forceinline__ uint32_t philox_offset_code(float x, const ScalePair& sp, float u128) {
+  const float t2 = __fadd_rn(__fadd_rn(div_exact(x, sp.dv), sp.c0), u128);
+  return __float_as_uint(__fadd_rd(t2, kFloorMagic)) & 0xFFu;
+}
+// two values at once; returns the raw bits whose low bytes are the offset codes
+__device__ __forceinline__ float2 philox_offset_bits2(float2 x, const ScalePair& sp, float2 u128) {
+  const float2 t2 = add2(add2(div2_exact(x, sp.dv), make_float2(sp.c0, sp.c0)), u128);
+  return __fadd2_rd(t2, make_float2(kFloorMagic, kFloorMagic));
+}
+// low bytes of four words -> one word
+__device__ __forceinline__ uint32_t gather_low_bytes(uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+  return __byte_perm(__byte_perm(a, b, 0x0040u), __byte_perm(c, d, 0x0040u), 0x5410u);
+}
+// eight byte-wide codes (each < 16; lo = codes 0..3, hi = codes 4..7) -> eight nibbles
+__device__ __forceinline__ uint32_t squeeze_nibbles(uint32_t lo, uint32_t hi) {
+  return __byte_perm(lo | (lo >> 4), hi | (hi >> 4), 0x6420u);
+}
+// Remove the offset 2^(bits-1) from packed offset codes (a flip of that bit per lane) and
+// sign-extend codes narrower than their lane.  lanes: 0x11111111 (nibbles) or 0x01010101 (bytes).
+__device__ __forceinline__ uint32_t remove_offset(uint32_t w, uint32_t off, uint32_t lanes, uint32_t lane_span) {
+  w ^= off * lanes;
+  const uint32_t ext = lane_span - 2u * off;  // the bits above the sign bit (0 if the code fills its lane)
+  if (ext) w |= ((w & (off * lanes)) / off) * ext;
+  return w;
 }
 
 // One code for the deterministic and the explicit-noise modes, |code| <= qmax.

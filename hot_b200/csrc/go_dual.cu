@@ -119,21 +119,18 @@ __device__ __forceinline__ uint4 quantise16_int8(const float (&y)[16], const Sca
   if (ROUND == HOT_ROUND_STOCH_PHILOX) {
     const uint4 r = philox_block16(q, e0 >> 4);
     const uint32_t rr[4] = {r.x, r.y, r.z, r.w};
+    uint32_t bits[16];
 #pragma unroll
     for (int i = 0; i < 16; i += 2) {
-      const float2 yb = add2(div2_exact(make_float2(y[i], y[i + 1]), sp.dv8), make_float2(sp.bias8, sp.bias8));
-      const uint32_t c0 = (__float2uint_rn(yb.x) + ((rr[i >> 2] >> (8 * (i & 3))) & 0xFFu)) >> 8;
-      const uint32_t c1 = (__float2uint_rn(yb.y) + ((rr[i >> 2] >> (8 * ((i + 1) & 3))) & 0xFFu)) >> 8;
-      w[i >> 2] |= (c0 << (8 * (i & 3))) | (c1 << (8 * ((i + 1) & 3)));
+      const float2 t = philox_offset_bits2(make_float2(y[i], y[i + 1]), sp,
+                                           make_float2(philox_u128(rr[i >> 2], i & 3), philox_u128(rr[i >> 2], (i + 1) & 3)));
+      bits[i] = __float_as_uint(t.x);
+      bits[i + 1] = __float_as_uint(t.y);
     }
     const uint32_t off = (uint32_t)(q.qmax + 1.0f);
-    const uint32_t ext = 0x100u - 2u * off;
 #pragma unroll
-    for (int k = 0; k < 4; ++k) {
-      uint32_t x = w[k] ^ (off * 0x01010101u);
-      if (ext) x |= ((x & (off * 0x01010101u)) / off) * ext;
-      w[k] = x;
-    }
+    for (int k = 0; k < 4; ++k)
+      w[k] = remove_offset(gather_low_bytes(bits[4 * k], bits[4 * k + 1], bits[4 * k + 2], bits[4 * k + 3]), off, 0x01010101u, 0x100u);
   } else {
     const int qmax = (int)q.qmax;
 #pragma unroll

@@ -102,32 +102,26 @@ __device__ __forceinline__ void quantise_store16(const float2 (&v)[8], const Sca
   if (ROUND == HOT_ROUND_STOCH_PHILOX) {
     const uint4 r = philox_block16(q, e0 >> 4);
     const uint32_t ra[2] = {r.x, r.y}, rb[2] = {r.z, r.w};
-    const float2 bias = make_float2(sp.bias8, sp.bias8);
+    uint32_t ba[8], bb[8];  // raw bits; the low byte of each is an offset code
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
-      const float2 yb = add2(div2_exact(v[i], sp.dv8), bias);
-      const uint32_t ca = (__float2uint_rn(yb.x) + ((ra[i >> 2] >> (8 * (i & 3))) & 0xFFu)) >> 8;
-      const uint32_t cb = (__float2uint_rn(yb.y) + ((rb[i >> 2] >> (8 * (i & 3))) & 0xFFu)) >> 8;
-      if (STORE4) {
-        wa0 |= ca << (4 * i);
-        wb0 |= cb << (4 * i);
-      } else {
-        if (i < 4) { wa0 |= ca << (8 * i); wb0 |= cb << (8 * i); }
-        else { wa1 |= ca << (8 * (i - 4)); wb1 |= cb << (8 * (i - 4)); }
-      }
+      const float2 t = philox_offset_bits2(v[i], sp, make_float2(philox_u128(ra[i >> 2], i & 3), philox_u128(rb[i >> 2], i & 3)));
+      ba[i] = __float_as_uint(t.x);
+      bb[i] = __float_as_uint(t.y);
     }
-    // The codes above carry the offset qmax + 1 = 2^(bits-1) that made them non-negative.
-    // Removing it is a flip of that bit per nibble / byte; codes narrower than their nibble /
-    // byte are then sign-extended from that bit.
+    wa0 = gather_low_bytes(ba[0], ba[1], ba[2], ba[3]);
+    wa1 = gather_low_bytes(ba[4], ba[5], ba[6], ba[7]);
+    wb0 = gather_low_bytes(bb[0], bb[1], bb[2], bb[3]);
+    wb1 = gather_low_bytes(bb[4], bb[5], bb[6], bb[7]);
     const uint32_t off = (uint32_t)(q.qmax + 1.0f);
-    const uint32_t lanes = STORE4 ? 0x11111111u : 0x01010101u;
-    const uint32_t ext = ((STORE4 ? 0x10u : 0x100u) - 2u * off);  // the bits above the sign bit (0 if none)
-    uint32_t* ws[4] = {&wa0, &wb0, &wa1, &wb1};
-#pragma unroll
-    for (int k = 0; k < (STORE4 ? 2 : 4); ++k) {
-      uint32_t w = *ws[k] ^ (off * lanes);
-      if (ext) w |= ((w & (off * lanes)) / off) * ext;
-      *ws[k] = w;
+    if (STORE4) {
+      wa0 = remove_offset(squeeze_nibbles(wa0, wa1), off, 0x11111111u, 0x10u);
+      wb0 = remove_offset(squeeze_nibbles(wb0, wb1), off, 0x11111111u, 0x10u);
+    } else {
+      wa0 = remove_offset(wa0, off, 0x01010101u, 0x100u);
+      wa1 = remove_offset(wa1, off, 0x01010101u, 0x100u);
+      wb0 = remove_offset(wb0, off, 0x01010101u, 0x100u);
+      wb1 = remove_offset(wb1, off, 0x01010101u, 0x100u);
     }
   } else {
     float ua[8], ub[8];

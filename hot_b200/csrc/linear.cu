@@ -47,7 +47,7 @@ inline size_t up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 inline int64_t code_pitch(int64_t len, int storage) { return (int64_t)up((size_t)(storage == HOT_STORE_INT4 ? (len + 1) / 2 : len), 16); }
 
 struct Workspace {
-  size_t off_qgo, off_sgo, off_qw, off_sw, off_qgw, off_sgw, off_scratch, total;
+  size_t off_qgo, off_sgo, off_qw, off_sw, off_qgw, off_sgw, off_scratch, w_scratch_off, total;
   int64_t ld_qgo, ld_qw, ld_qgw, lp;
 };
 
@@ -66,7 +66,10 @@ int plan(int64_t L, int64_t O, int64_t I, const hot_linear_cfg_t& c, Workspace& 
   w.off_sw = o;  o += kAlign;
   w.off_qgw = o; o += up((size_t)O * w.ld_qgw, kAlign);
   w.off_sgw = o; o += up((size_t)O * sizeof(float), kAlign);
-  w.off_scratch = o; o += up((size_t)(L + O + I + 256) * sizeof(uint32_t), kAlign);
+  // scratch words: 64 fixed + per-token (L) + per-channel (O) maxima + the weight quantiser's own
+  w.w_scratch_off = (size_t)((64 + L + O + 1) / 2 * 2);
+  w.off_scratch = o;
+  o += up((w.w_scratch_off + hot_col_ht_quant_scratch_words(c.dtype, O, I, c.order_o, c.order_o, c.q_w.scale_mode) + 64) * sizeof(uint32_t), kAlign);
   w.total = o;
   return HOT_OK;
 }
@@ -90,8 +93,10 @@ extern "C" int hot_abc_compress(const void* x, int64_t L, int64_t I, int64_t ldx
                                 hot_stream_t stream) {
   using namespace hot;
   if (!x || !cfg || !x_q_t || !scale_x || !workspace) HOT_FAIL(HOT_ERR_ARG, "hot_abc_compress: null pointer");
-  if (workspace_bytes < 64) HOT_FAIL(HOT_ERR_WORKSPACE, "hot_abc_compress: workspace needs 64 bytes");
-  if (cfg->q_x.scale_mode != HOT_SCALE_TENSOR) HOT_FAIL(HOT_ERR_UNSUPPORTED, "hot_abc_compress: the activation buffer takes one scale");
+  if (cfg->q_x.scale_mode == HOT_SCALE_ROW) HOT_FAIL(HOT_ERR_UNSUPPORTED, "hot_abc_compress: the activation buffer takes one scale");
+  const size_t need = 4 * hot_col_ht_quant_scratch_words(cfg->dtype, L, I, cfg->order_l, cfg->rank_l, cfg->q_x.scale_mode);
+  if (need == 0 || workspace_bytes < need || ((uintptr_t)workspace) % 8 != 0)
+    HOT_FAIL(HOT_ERR_WORKSPACE, "hot_abc_compress: workspace needs %zu bytes, 8-byte aligned (got %zu)", need, workspace_bytes);
   const int64_t pitch = hot_abc_pitch(L, cfg);
   if (pitch == 0) HOT_FAIL(HOT_ERR_ARG, "hot_abc_compress: tokens %lld not a multiple of the low-rank order %d", (long long)L, cfg->order_l);
   return hot_col_ht_quant(x, cfg->dtype, L, I, ldx, cfg->order_l, cfg->sel_l, cfg->rank_l, &cfg->q_x, HOT_LAYOUT_NATURAL,
@@ -150,7 +155,7 @@ extern "C" int hot_linear_backward(const void* go, int64_t ldgo, const void* w, 
   SideStream* side = nullptr;
   cudaStream_t main_st = (cudaStream_t)stream;
   if (grad_x) {
-    if (cfg->q_w.scale_mode != HOT_SCALE_TENSOR) HOT_FAIL(HOT_ERR_UNSUPPORTED, "hot_linear_backward: the weight takes one scale");
+    if (cfg->q_w.scale_mode == HOT_SCALE_ROW) HOT_FAIL(HOT_ERR_UNSUPPORTED, "hot_linear_backward: the weight takes one scale");
     if ((rc = side_stream(&side))) return rc;
     HOT_CUDA(cudaEventRecord(side->fork, main_st));
     HOT_CUDA(cudaStreamWaitEvent(side->stream, side->fork, 0));
@@ -162,7 +167,7 @@ extern "C" int hot_linear_backward(const void* go, int64_t ldgo, const void* w, 
     hot_quant_t q_w = cfg->q_w;
     q_w.storage = HOT_STORE_INT8;
     rc = hot_col_ht_quant(w, cfg->dtype, O, I, ldw, cfg->order_o, ident, cfg->order_o, &q_w, HOT_LAYOUT_NATURAL,
-                          base + ws.off_qw, ws.ld_qw, s_w, scratch + 16, (hot_stream_t)side->stream);
+                          base + ws.off_qw, ws.ld_qw, s_w, scratch + ws.w_scratch_off, (hot_stream_t)side->stream);
     cudaEventRecord(side->join, side->stream);
     if (rc) {
       cudaStreamWaitEvent(main_st, side->join, 0);  // rejoin, so that a capture in progress stays well-formed

@@ -22,7 +22,7 @@ class Quant:
     bits: int = 8
     storage: str = "int8"            # "int8" | "int4" (two codes per byte, low nibble = even index)
     rounding: str = "philox"         # "nearest" | "philox" | "noise"
-    scale: str = "tensor"            # "tensor" | "row"
+    scale: str = "tensor"            # "tensor" | "row" | "sawb" (column kernel only, nearest rounding)
     seed: int = 0
     offset: int = 0
     noise: Optional[torch.Tensor] = field(default=None, repr=False)
@@ -32,7 +32,7 @@ class Quant:
         q.bits = self.bits
         q.storage = C.STORE_INT4 if self.storage == "int4" else C.STORE_INT8
         q.rounding = _ROUNDING[self.rounding]
-        q.scale_mode = C.SCALE_ROW if self.scale == "row" else C.SCALE_TENSOR
+        q.scale_mode = {"tensor": C.SCALE_TENSOR, "row": C.SCALE_ROW, "sawb": C.SCALE_SAWB}[self.scale]
         q.seed, q.offset = self.seed & (2 ** 64 - 1), self.offset & (2 ** 64 - 1)
         if self.rounding == "noise":
             if self.noise is None or self.noise.dtype != torch.float32 or not self.noise.is_contiguous():
@@ -97,7 +97,8 @@ def col_ht_quant(x: torch.Tensor, order: int, sel: Sequence[int], q: Quant, logi
     pitch = _pitch16((out_len + 1) // 2 if q.storage == "int4" else out_len)
     codes = torch.empty((cols, pitch), dtype=torch.uint8, device=x.device)
     scales = torch.empty((cols if q.scale == "row" else 1,), dtype=torch.float32, device=x.device)
-    ws = torch.empty((max(cols, 16),), dtype=torch.int32, device=x.device)
+    words = C.lib().hot_col_ht_quant_scratch_words(_dtype(x), rows, cols, order, r, q.to_c().scale_mode)
+    ws = torch.empty((max(int(words), 16) + 1) // 2, dtype=torch.int64, device=x.device)   # 8-byte aligned
     sel_c = (C.c_i32 * r)(*[int(s) for s in sel])
     with torch.cuda.device(x.device):
         C.check(C.lib().hot_col_ht_quant(x.data_ptr(), _dtype(x), rows, cols, x.stride(0), order, sel_c, r,
@@ -187,7 +188,8 @@ def abc_compress(x: torch.Tensor, cfg: LinearConfig):
         raise ValueError("token count %d is not a multiple of the low-rank order %d" % (L, cfg.order_l))
     x_q_t = torch.empty((I, pitch), dtype=torch.uint8, device=x.device)
     scale = torch.empty((1,), dtype=torch.float32, device=x.device)
-    ws = torch.empty((64,), dtype=torch.uint8, device=x.device)
+    words = C.lib().hot_col_ht_quant_scratch_words(_DTYPES[x.dtype], L, I, cfg.order_l, len(cfg.sel_l), cc.q_x.scale_mode)
+    ws = torch.empty((max(int(words), 16) * 4,), dtype=torch.uint8, device=x.device)
     with torch.cuda.device(x.device):
         C.check(C.lib().hot_abc_compress(x.data_ptr(), L, I, x.stride(0), ctypes.byref(cc), x_q_t.data_ptr(),
                                          scale.data_ptr(), ws.data_ptr(), ws.numel(), _stream(x)), "hot_abc_compress")

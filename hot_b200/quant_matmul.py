@@ -94,7 +94,21 @@ def norm_quantizer(x: Tensor, quantBits: int, is_batched: bool = False):
     return codes * s.to(x.dtype).unsqueeze(1), 1.
 
 
+def sawb_quantizer(x: Tensor, quantBits: int, is_batched: bool = False):
+    """One scale from clip = 12.1*sqrt(mean(x^2)) - 12.2*mean(|x|), values clamped to +-clip, round to
+    nearest (utils/quant_matmul.py:40-55).  Returns (codes as float, scale)."""
+    _no_batched("sawb_quantizer", is_batched)
+    x2 = x if x.dim() == 2 else x.reshape(-1, x.shape[-1])
+    if not x2.is_contiguous():
+        x2 = x2.contiguous()
+    q = ops.Quant(quantBits, "int8", "nearest", "sawb")
+    codes_t, s, n = ops.col_ht_quant(x2, 1, [0], q, "natural")      # identity transform, transposed codes
+    codes = codes_t.view(torch.int8)[:, :n].t().to(x.dtype).reshape(x.shape)
+    return codes, s[0]
+
+
 quant_scheme_dict = {
+    "sawb_quantizer": sawb_quantizer,
     "int_quantizer": int_quantizer,
     "stoch_quantizer": stoch_quantizer,
     "norm_quantizer": norm_quantizer,
@@ -115,6 +129,8 @@ def _operand(kind: str, scheme, bits: int, what: str, row_ok: bool) -> ops.Quant
         rounding, scale = "nearest", "tensor"
     elif scheme == "nq" and row_ok:
         rounding, scale = "philox", "row"
+    elif scheme == "sawb" and kind in ("w", "x"):
+        rounding, scale = "nearest", "sawb"
     elif scheme in ("sawb", "luq", "no", False):
         raise NotImplementedError("%s rounding scheme %r is not built on the native path" % (what, scheme))
     else:

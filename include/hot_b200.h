@@ -33,7 +33,10 @@ enum hot_status {
 
 enum hot_dtype { HOT_F32 = 0, HOT_BF16 = 1, HOT_I32 = 2 };
 enum hot_rounding { HOT_ROUND_NEAREST = 0, HOT_ROUND_STOCH_PHILOX = 1, HOT_ROUND_STOCH_NOISE = 2 };
-enum hot_scale_mode { HOT_SCALE_TENSOR = 0, HOT_SCALE_ROW = 1 };
+/* TENSOR / ROW: s = absmax / qmax over the tensor / each row.  SAWB (hot_col_ht_quant only, nearest
+ * rounding): one scale from clip = 12.1 * sqrt(mean(y^2)) - 12.2 * mean(|y|), values clamped to
+ * +-clip first (sawb_quantizer, utils/quant_matmul.py:40-55). */
+enum hot_scale_mode { HOT_SCALE_TENSOR = 0, HOT_SCALE_ROW = 1, HOT_SCALE_SAWB = 2 };
 enum hot_storage { HOT_STORE_INT8 = 0, HOT_STORE_INT4 = 1 }; /* INT4: two codes per byte, low nibble = even index */
 enum hot_layout { HOT_LAYOUT_NATURAL = 0, HOT_LAYOUT_TRANSPOSED = 1 };
 
@@ -85,7 +88,8 @@ int hot_row_ht_quant(const void* x, int dtype, int64_t rows, int64_t cols, int64
  *          pitch ld_codes bytes, a multiple of 16
  *   scales [1] (HOT_SCALE_TENSOR) or [cols] (HOT_SCALE_ROW: one scale per row of the
  *          transposed output, i.e. per input column)
- *   absmax_ws  1 word (TENSOR) or cols words (ROW) of scratch
+ *   absmax_ws  scratch, hot_col_ht_quant_scratch_words() 32-bit words: 1 (TENSOR), cols (ROW), or
+ *          two doubles per CTA (SAWB; 8-byte aligned)
  *   logical_layout  layout in which the reference's quantiser sees the tensor, which fixes
  *          the noise / Philox element index: HOT_LAYOUT_NATURAL [rows*r/n, cols] or
  *          HOT_LAYOUT_TRANSPOSED [cols, rows*r/n]
@@ -99,6 +103,8 @@ int hot_col_ht_quant(const void* x, int dtype, int64_t rows, int64_t cols, int64
                      const int32_t* sel, int r, const hot_quant_t* q, int logical_layout,
                      void* codes_t, int64_t ld_codes, float* scales, uint32_t* absmax_ws,
                      hot_stream_t stream);
+/* Scratch words hot_col_ht_quant needs for these sizes and this hot_scale_mode (0 on bad arguments). */
+size_t hot_col_ht_quant_scratch_words(int dtype, int64_t rows, int64_t cols, int order, int r, int scale_mode);
 
 /*
  * hot_col_ht_quant without a scratch argument, for callers that cannot supply device scratch

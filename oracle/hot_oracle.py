@@ -178,8 +178,9 @@ def _qmax(bits: int) -> F32:
 
 
 class PhiloxBytes(np.ndarray):
-    """Marker type: one random byte R per element, for the kernels' production rounding path
-    (8.8 fixed point):  t = rint(fl(y * 256 + (qmax + 1) * 256));  code = ((t + R) >> 8) - (qmax + 1).
+    """Marker type: one random byte R per element, for the kernels' production rounding path:
+    code = floor(y + B + (R + 0.5) / 256) - B with B = qmax + 1, evaluated in float32 as
+    t1 = fl(y + (B - 128 + 1/512)); t2 = t1 + (128 + R/256) (exact); floor(t2).
     Plain float arrays keep the reference's predicate  u < frac."""
 
 
@@ -188,9 +189,11 @@ def _round_codes(y: np.ndarray, u: np.ndarray | None, qmax: F32 = F32(0)) -> np.
         return np.rint(y).astype(np.int32)
     if isinstance(u, PhiloxBytes):
         off = int(qmax) + 1
-        yb = (y.astype(F32) * F32(256.0) + F32(off * 256)).astype(F32)   # two fp32 roundings, as on the GPU
-        t = np.rint(yb).astype(np.int64)
-        return (((t + np.asarray(u).astype(np.int64)) >> 8) - off).astype(np.int32)
+        c0 = F32(F32(off) - F32(128.0) + F32(1.0 / 512.0))
+        t1 = (y.astype(F32) + c0).astype(F32)
+        u128 = (F32(128.0) + np.asarray(u).astype(F32) / F32(256.0)).astype(F32)
+        t2 = (t1 + u128).astype(F32)
+        return (np.floor(t2).astype(np.int64) - off).astype(np.int32)
     a = np.abs(y)
     f = np.floor(a)
     frac = a - f

@@ -111,9 +111,13 @@ def test_unbuilt_modes_raise(hot):
     args, qm = hot
     lin = qm.HQ_Linear(64, 64).cuda()
     x = torch.randn(32, 64, device="cuda", requires_grad=True)
-    args.quantBWDAct = "sawb"
+    args.quantBWDAct = "luq"
     with pytest.raises(NotImplementedError):
         lin(x)
+    args.quantBWDAct, args.quantBWDGogi = "stoch", "sawb"       # sawb exists for W and X only
+    with pytest.raises(NotImplementedError):
+        lin(x).sum().backward()
+    args.quantBWDGogi = "stoch"
     args.quantBWDAct = "bogus"
     with pytest.raises(Exception, match="rounding scheme not implemented"):
         lin(x)
@@ -202,3 +206,40 @@ def test_vit_with_hot_linears_trains(hot):
         losses.append(float(loss))
     assert all(p.grad is not None and torch.isfinite(p.grad).all() for p in model.parameters())
     assert losses[-1] < losses[0] - 0.1, losses
+
+
+def test_sawb_for_weight_and_activation(hot, golden):
+    """The reference's default quantiser for W and X (ViT_main.py:102,104).  The clip value comes
+    from two means whose summation order differs from torch's, so the scale is compared to 1e-6
+    and the codes may differ in a vanishing fraction."""
+    args, qm = hot
+    g = golden("quantizers")
+    x = torch.from_numpy(g["x"]).cuda()
+    for bits in (4, 8):
+        codes, s = qm.sawb_quantizer(x, bits, False)
+        np.testing.assert_allclose(float(s), float(g["sawb%d_scale" % bits]), rtol=1e-6)
+        assert np.mean(codes.cpu().numpy() != g["sawb%d_codes" % bits]) < 1e-3
+    args.quantBWDWgt = args.quantBWDAct = "sawb"
+    args.quantBWDGogi = args.quantBWDGogw = "int"
+    torch.manual_seed(3)
+    L, I, O = 512, 96, 128
+    lin = qm.HQ_Linear(I, O, bias=False).cuda()
+    xin = torch.randn(L, I, device="cuda", requires_grad=True)
+    go = torch.randn(L, O, device="cuda") * 1e-3
+    lin(xin).backward(go)
+    sel = np.array(oc.lowrank_preset(16, 8))
+    xq, sx = oc.abc_compress(xin.detach().cpu().numpy(), 16, sel, 8, None, "sawb")
+    ref = oc.linear_backward(go.cpu().numpy(), lin.weight.detach().cpu().numpy(), xq, sx, n_o=16, n_l=16, sel=sel,
+                             w_mode="sawb")
+    for got, name in ((xin.grad, "grad_input"), (lin.weight.grad, "grad_w")):
+        rel = np.linalg.norm(got.cpu().numpy() - ref[name]) / np.linalg.norm(ref[name])
+        assert rel < 1e-3, (name, rel)
+    # deterministic: the same call twice gives the same bytes
+    a1, s1, n1 = hot_ops().col_ht_quant(xin.detach(), 16, list(sel), hot_ops().Quant(8, "int8", "nearest", "sawb"))
+    a2, s2, _ = hot_ops().col_ht_quant(xin.detach(), 16, list(sel), hot_ops().Quant(8, "int8", "nearest", "sawb"))
+    assert torch.equal(a1[:, :n1], a2[:, :n1]) and torch.equal(s1, s2)
+
+
+def hot_ops():
+    from hot_b200 import ops
+    return ops
