@@ -55,6 +55,10 @@ EXPORTS = {
     "hot_gemm_i8": (ctypes.c_int, [c_vp, ctypes.c_int, c_i64, c_vp, ctypes.c_int, c_i64, c_i64, c_i64, c_i64, c_vp,
                                    ctypes.c_int, c_vp, ctypes.c_int, ctypes.c_float, c_vp, ctypes.c_int, c_i64, c_vp,
                                    c_vp]),
+    "hot_gemm_i8_workspace_bytes": (ctypes.c_size_t, [c_i64, c_i64]),
+    "hot_gemm_i8_ws": (ctypes.c_int, [c_vp, ctypes.c_int, c_i64, c_vp, ctypes.c_int, c_i64, c_i64, c_i64, c_i64, c_vp,
+                                      ctypes.c_int, c_vp, ctypes.c_int, ctypes.c_float, c_vp, ctypes.c_int, c_i64, c_vp,
+                                      ctypes.c_size_t, c_vp, c_vp]),
     "hot_linear_workspace_bytes": (ctypes.c_size_t, [c_i64, c_i64, c_i64, ctypes.POINTER(HotLinearCfg)]),
     "hot_abc_pitch": (c_i64, [c_i64, ctypes.POINTER(HotLinearCfg)]),
     "hot_abc_compress": (ctypes.c_int, [c_vp, c_i64, c_i64, c_i64, ctypes.POINTER(HotLinearCfg), c_vp, c_vp, c_vp,

@@ -15,9 +15,14 @@
 //
 // Every wait on an mbarrier is bounded in time; when a wait runs out the CTA ORs a code into
 // the caller's status word, stops issuing work, frees its tensor memory and returns.
+#include <cstdlib>
+
 #include "tma.cuh"
 
 namespace hot {
+
+int device_sm_count();
+
 namespace {
 
 constexpr int kBM = 128;
@@ -33,6 +38,57 @@ struct GemmParams {
   int64_t ldo;
   int out_dtype;
   uint32_t* status;
+  // stream-K: CTAs take equal contiguous ranges of (tile, k-block) units; a tile cut by a range
+  // boundary is finished by whichever contributor arrives last
+  int stream_k;
+  int32_t* sk_partials;    // [2 * gridDim.x][128][BN] int32
+  uint32_t* sk_counters;   // [num_tiles] k-blocks delivered so far (zero before launch; left zero)
+};
+
+// One stretch of k-blocks of one output tile.
+struct Segment {
+  int tile, kb0, kb1;
+  bool first;  // first segment of this CTA (selects the partial slot)
+};
+
+// The sequence of segments of one CTA: whole tiles round-robin, or (stream-K) the units
+// [total * cta / n, total * (cta + 1) / n) with total = num_tiles * num_kb.  Every warp role walks
+// its own copy, so they agree on the sequence without communicating.
+struct SegmentIter {
+  bool stream_k, first;
+  int tile, stride, num_tiles, num_kb;
+  long long u, end;
+  __device__ SegmentIter(const GemmParams& p, int num_tiles_) {
+    stream_k = p.stream_k != 0;
+    first = true;
+    num_tiles = num_tiles_;
+    num_kb = p.num_kb;
+    tile = blockIdx.x;
+    stride = gridDim.x;
+    const long long total = (long long)num_tiles * num_kb;
+    u = total * blockIdx.x / gridDim.x;
+    end = total * (blockIdx.x + 1) / gridDim.x;
+  }
+  __device__ bool next(Segment& s) {
+    s.first = first;
+    first = false;
+    if (!stream_k) {
+      if (tile >= num_tiles) return false;
+      s.tile = tile;
+      s.kb0 = 0;
+      s.kb1 = num_kb;
+      tile += stride;
+      return true;
+    }
+    if (u >= end) return false;
+    s.tile = (int)(u / num_kb);
+    s.kb0 = (int)(u - (long long)s.tile * num_kb);
+    const long long left = end - u;
+    const int room = num_kb - s.kb0;
+    s.kb1 = s.kb0 + (int)(left < room ? left : room);
+    u += s.kb1 - s.kb0;
+    return true;
+  }
 };
 
 // ---- tcgen05 wrappers (mbarrier / TMA wrappers: tma.cuh) ------------------------------------
@@ -143,6 +199,64 @@ __device__ __forceinline__ void unpack_stage(const uint8_t* raw, uint8_t* dst, i
   }
 }
 
+// Dequantise and store 32 consecutive accumulators of one output row:
+// out = ((float)acc * sa) * sb * post  (three roundings, the reference's order), or the raw int32.
+__device__ __forceinline__ void store_chunk(const GemmParams& p, int row, bool row_ok, int col0, const uint32_t (&acc)[32],
+                                            float sa, float sb0) {
+  if (!row_ok || col0 >= p.N) return;
+  if (p.out_dtype == HOT_I32) {
+    int32_t* o = reinterpret_cast<int32_t*>(p.out) + (int64_t)row * p.ldo + col0;
+    if (col0 + 32 <= p.N && (p.ldo & 3) == 0) {
+#pragma unroll
+      for (int i = 0; i < 32; i += 4)
+        *reinterpret_cast<int4*>(o + i) = make_int4((int)acc[i], (int)acc[i + 1], (int)acc[i + 2], (int)acc[i + 3]);
+    } else {
+#pragma unroll
+      for (int i = 0; i < 32; ++i)
+        if (col0 + i < p.N) o[i] = (int)acc[i];
+    }
+    return;
+  }
+  float f[32];
+#pragma unroll
+  for (int i = 0; i < 32; ++i) {
+    const float sb = p.sb_row ? ((col0 + i < p.N) ? p.sb[col0 + i] : 0.0f) : sb0;
+    f[i] = __fmul_rn(__fmul_rn(__fmul_rn((float)(int)acc[i], sa), sb), p.post);
+  }
+  if (p.out_dtype == HOT_F32) {
+    float* o = reinterpret_cast<float*>(p.out) + (int64_t)row * p.ldo + col0;
+    if (col0 + 32 <= p.N && (p.ldo & 3) == 0) {
+#pragma unroll
+      for (int i = 0; i < 32; i += 4) *reinterpret_cast<float4*>(o + i) = make_float4(f[i], f[i + 1], f[i + 2], f[i + 3]);
+    } else {
+#pragma unroll
+      for (int i = 0; i < 32; ++i)
+        if (col0 + i < p.N) o[i] = f[i];
+    }
+  } else {
+    __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(p.out) + (int64_t)row * p.ldo + col0;
+    if (col0 + 32 <= p.N && (p.ldo & 7) == 0) {
+#pragma unroll
+      for (int i = 0; i < 32; i += 8) {
+        uint4 w;
+        __nv_bfloat162 t0 = __floats2bfloat162_rn(f[i], f[i + 1]);
+        __nv_bfloat162 t1 = __floats2bfloat162_rn(f[i + 2], f[i + 3]);
+        __nv_bfloat162 t2 = __floats2bfloat162_rn(f[i + 4], f[i + 5]);
+        __nv_bfloat162 t3 = __floats2bfloat162_rn(f[i + 6], f[i + 7]);
+        w.x = *reinterpret_cast<uint32_t*>(&t0);
+        w.y = *reinterpret_cast<uint32_t*>(&t1);
+        w.z = *reinterpret_cast<uint32_t*>(&t2);
+        w.w = *reinterpret_cast<uint32_t*>(&t3);
+        *reinterpret_cast<uint4*>(o + i) = w;
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < 32; ++i)
+        if (col0 + i < p.N) o[i] = __float2bfloat16_rn(f[i]);
+    }
+  }
+}
+
 // Persistent kernel: one CTA per SM walks the output tiles (n fastest, so CTAs running together
 // share A rows and the whole of B in L2).  The shared-memory ring runs on across tiles; the
 // accumulator is double-buffered in tensor memory so the epilogue of tile i overlaps the MMAs
@@ -200,9 +314,11 @@ __global__ void __launch_bounds__((A4 || B4) ? 320 : 192, 1)
       constexpr uint32_t kTx = (A4 ? L::kRawA : L::kA) + (B4 ? L::kRawB : L::kB);
       uint32_t g = 0;  // k-block counter across tiles: ring slot g % STAGES, phase (g / STAGES) & 1
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-        const int m0 = (tile / n_tiles) * kBM, n0 = (tile % n_tiles) * BN;
-        for (int kb = 0; kb < p.num_kb; ++kb, ++g) {
+      SegmentIter iter(p, num_tiles);
+      Segment seg;
+      while (ok && iter.next(seg)) {
+        const int m0 = (seg.tile / n_tiles) * kBM, n0 = (seg.tile % n_tiles) * BN;
+        for (int kb = seg.kb0; kb < seg.kb1; ++kb, ++g) {
           const int s = g % STAGES;
           const uint32_t ph = (g / STAGES) & 1u;
           ok = mbar_wait(&empty[s], ph ^ 1u, abort_flag);
@@ -220,13 +336,15 @@ __global__ void __launch_bounds__((A4 || B4) ? 320 : 192, 1)
       constexpr uint32_t idesc = instr_desc_i8(BN);
       uint32_t g = 0, it = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++it) {
+      SegmentIter iter(p, num_tiles);
+      Segment seg;
+      for (; ok && iter.next(seg); ++it) {
         const uint32_t buf = it & 1u, bph = (it >> 1) & 1u;
         ok = mbar_wait(&tmem_empty[buf], bph ^ 1u, abort_flag);  // epilogue drained this buffer
         if (!ok) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + buf * kBufStride;
-        for (int kb = 0; kb < p.num_kb; ++kb, ++g) {
+        for (int kb = seg.kb0; kb < seg.kb1; ++kb, ++g) {
           const int s = g % STAGES;
           const uint32_t ph = (g / STAGES) & 1u;
           ok = mbar_wait(kUnpack ? &ready[s] : &full[s], ph, abort_flag);
@@ -236,7 +354,7 @@ __global__ void __launch_bounds__((A4 || B4) ? 320 : 192, 1)
 #pragma unroll
           for (int k4 = 0; k4 < kBK / 32; ++k4)
             umma_i8(d_tmem, smem_desc_sw128(a_addr + k4 * 32), smem_desc_sw128(b_addr + k4 * 32), idesc,
-                    (kb | k4) != 0 ? 1u : 0u);
+                    (kb > seg.kb0 || k4 > 0) ? 1u : 0u);
           umma_commit(&empty[s]);
         }
         if (ok) umma_commit(&tmem_full[buf]);
@@ -247,14 +365,20 @@ __global__ void __launch_bounds__((A4 || B4) ? 320 : 192, 1)
     const int q = warp & 3;  // tensor-memory lane quarter this warp may read
     const bool raw = p.out_dtype == HOT_I32;  // raw accumulators: no scales to read
     const float sb0 = (p.sb_row || raw) ? 0.0f : p.sb[0];
+    __shared__ uint32_t s_finisher;
     uint32_t it = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++it) {
-      const int m0 = (tile / n_tiles) * kBM, n0 = (tile % n_tiles) * BN;
+    SegmentIter iter(p, num_tiles);
+    Segment seg;
+    for (; ok && iter.next(seg); ++it) {
+      const int m0 = (seg.tile / n_tiles) * kBM, n0 = (seg.tile % n_tiles) * BN;
       const uint32_t buf = it & 1u, bph = (it >> 1) & 1u;
-      const int row = m0 + q * 32 + lane;
+      const int row_loc = q * 32 + lane;
+      const int row = m0 + row_loc;
       const bool row_ok = row < p.M;
       const float sa = (row_ok && !raw) ? (p.sa_row ? p.sa[row] : p.sa[0]) : 0.0f;
+      const bool whole = seg.kb0 == 0 && seg.kb1 == p.num_kb;
+      int32_t* my_slot = p.sk_partials + ((size_t)(2 * blockIdx.x + (seg.first ? 0 : 1)) * kBM + row_loc) * BN;
       ok = mbar_wait(&tmem_full[buf], bph, abort_flag);
       if (!ok) break;
       tc_fence_after();
@@ -267,63 +391,61 @@ __global__ void __launch_bounds__((A4 || B4) ? 320 : 192, 1)
           tc_fence_before();
           mbar_arrive(&tmem_empty[buf]);
         }
-        const int col0 = n0 + c * 32;
-        if (!row_ok || col0 >= p.N) continue;
         if (kShift) {
 #pragma unroll
           for (int i = 0; i < 32; ++i) acc[i] = (uint32_t)((int)acc[i] >> kShift);
         }
-        if (raw) {
-          int32_t* o = reinterpret_cast<int32_t*>(p.out) + (int64_t)row * p.ldo + col0;
-          if (col0 + 32 <= p.N && (p.ldo & 3) == 0) {
-#pragma unroll
-            for (int i = 0; i < 32; i += 4)
-              *reinterpret_cast<int4*>(o + i) = make_int4((int)acc[i], (int)acc[i + 1], (int)acc[i + 2], (int)acc[i + 3]);
-          } else {
-#pragma unroll
-            for (int i = 0; i < 32; ++i)
-              if (col0 + i < p.N) o[i] = (int)acc[i];
-          }
-          continue;
-        }
-        float f[32];
-#pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const float sb = p.sb_row ? ((col0 + i < p.N) ? p.sb[col0 + i] : 0.0f) : sb0;
-          f[i] = __fmul_rn(__fmul_rn(__fmul_rn((float)(int)acc[i], sa), sb), p.post);
-        }
-        if (p.out_dtype == HOT_F32) {
-          float* o = reinterpret_cast<float*>(p.out) + (int64_t)row * p.ldo + col0;
-          if (col0 + 32 <= p.N && (p.ldo & 3) == 0) {
-#pragma unroll
-            for (int i = 0; i < 32; i += 4) *reinterpret_cast<float4*>(o + i) = make_float4(f[i], f[i + 1], f[i + 2], f[i + 3]);
-          } else {
-#pragma unroll
-            for (int i = 0; i < 32; ++i)
-              if (col0 + i < p.N) o[i] = f[i];
-          }
+        if (whole) {
+          store_chunk(p, row, row_ok, n0 + c * 32, acc, sa, sb0);
         } else {
-          __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(p.out) + (int64_t)row * p.ldo + col0;
-          if (col0 + 32 <= p.N && (p.ldo & 7) == 0) {
+          // partial sum of a tile shared with other CTAs: park the raw accumulators
 #pragma unroll
-            for (int i = 0; i < 32; i += 8) {
-              uint4 w;
-              __nv_bfloat162 t0 = __floats2bfloat162_rn(f[i], f[i + 1]);
-              __nv_bfloat162 t1 = __floats2bfloat162_rn(f[i + 2], f[i + 3]);
-              __nv_bfloat162 t2 = __floats2bfloat162_rn(f[i + 4], f[i + 5]);
-              __nv_bfloat162 t3 = __floats2bfloat162_rn(f[i + 6], f[i + 7]);
-              w.x = *reinterpret_cast<uint32_t*>(&t0);
-              w.y = *reinterpret_cast<uint32_t*>(&t1);
-              w.z = *reinterpret_cast<uint32_t*>(&t2);
-              w.w = *reinterpret_cast<uint32_t*>(&t3);
-              *reinterpret_cast<uint4*>(o + i) = w;
+          for (int i = 0; i < 32; i += 4)
+            *reinterpret_cast<int4*>(my_slot + c * 32 + i) = make_int4((int)acc[i], (int)acc[i + 1], (int)acc[i + 2], (int)acc[i + 3]);
+        }
+      }
+      if (!whole) {
+        // publish, count the k-blocks delivered for this tile; whoever completes the count adds up
+        // every contributor's partial (its own included) and writes the tile
+        __threadfence();
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (threadIdx.x == 64) {
+          const uint32_t mine = (uint32_t)(seg.kb1 - seg.kb0);
+          const uint32_t before = atomicAdd(p.sk_counters + seg.tile, mine);
+          s_finisher = (before + mine == (uint32_t)p.num_kb) ? 1u : 0u;
+          if (s_finisher) p.sk_counters[seg.tile] = 0u;  // leave the counters as they were found
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (s_finisher) {
+          __threadfence();
+          const long long total = (long long)num_tiles * p.num_kb;
+          const long long t_beg = (long long)seg.tile * p.num_kb, t_end = t_beg + p.num_kb;
+          const long long G = gridDim.x;
+          // contributors: the CTAs whose unit range meets [t_beg, t_end)
+          long long c_lo = t_beg * G / total;
+          while (c_lo + 1 < G && total * (c_lo + 1) / G <= t_beg) ++c_lo;
+          while (c_lo > 0 && total * c_lo / G > t_beg) --c_lo;
+#pragma unroll 1
+          for (int c = 0; c < BN / 32; ++c) {
+            int sum[32];
+#pragma unroll
+            for (int i = 0; i < 32; ++i) sum[i] = 0;
+            for (long long cta = c_lo; cta < G && total * cta / G < t_end; ++cta) {
+              const bool cta_first = total * cta / G >= t_beg;  // its range starts inside this tile
+              const int32_t* slot = p.sk_partials + ((size_t)(2 * cta + (cta_first ? 0 : 1)) * kBM + row_loc) * BN + c * 32;
+#pragma unroll
+              for (int i = 0; i < 32; i += 4) {
+                const int4 v = __ldcg(reinterpret_cast<const int4*>(slot + i));
+                sum[i] += v.x; sum[i + 1] += v.y; sum[i + 2] += v.z; sum[i + 3] += v.w;
+              }
             }
-          } else {
+            uint32_t acc[32];
 #pragma unroll
-            for (int i = 0; i < 32; ++i)
-              if (col0 + i < p.N) o[i] = __float2bfloat16_rn(f[i]);
+            for (int i = 0; i < 32; ++i) acc[i] = (uint32_t)sum[i];
+            store_chunk(p, row, row_ok, n0 + c * 32, acc, sa, sb0);
           }
         }
+        asm volatile("bar.sync 1, 128;" ::: "memory");  // s_finisher is reused by the next segment
       }
     }
   } else if (kUnpack) {
@@ -331,8 +453,10 @@ __global__ void __launch_bounds__((A4 || B4) ? 320 : 192, 1)
     const int tid128 = threadIdx.x - 192;
     uint32_t g = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-      for (int kb = 0; kb < p.num_kb; ++kb, ++g) {
+    SegmentIter iter(p, num_tiles);
+    Segment seg;
+    while (ok && iter.next(seg)) {
+      for (int kb = seg.kb0; kb < seg.kb1; ++kb, ++g) {
         const int s = g % STAGES;
         const uint32_t ph = (g / STAGES) & 1u;
         ok = mbar_wait(&full[s], ph, abort_flag);
@@ -362,8 +486,14 @@ __global__ void __launch_bounds__((A4 || B4) ? 320 : 192, 1)
 }
 
 // ---- host side ---------------------------------------------------------------------------
+struct Plan {
+  int bn;
+  bool stream_k;
+  unsigned grid;
+};
+
 template <int BN, bool A4, bool B4>
-int launch_gemm(const void* a, int64_t lda, const void* b, int64_t ldb, const GemmParams& p, cudaStream_t st, int sms) {
+int launch_gemm(const void* a, int64_t lda, const void* b, int64_t ldb, const GemmParams& p, const Plan& plan, cudaStream_t st) {
   using L = SmemLayout<BN, A4, B4>;
   CUtensorMap ma, mb;
   int rc;
@@ -379,52 +509,81 @@ int launch_gemm(const void* a, int64_t lda, const void* b, int64_t ldb, const Ge
     HOT_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kBytes));
     attr_set = true;
   }
-  const int64_t tiles = (int64_t)((p.M + kBM - 1) / kBM) * ((p.N + BN - 1) / BN);
-  const unsigned grid = (unsigned)(tiles < sms ? tiles : sms);
-  kernel<<<grid, (A4 || B4) ? 320 : 192, L::kBytes, st>>>(ma, mb, p);
+  kernel<<<plan.grid, (A4 || B4) ? 320 : 192, L::kBytes, st>>>(ma, mb, p);
   HOT_CUDA(cudaGetLastError());
   return HOT_OK;
 }
 
-// Tile width: fewest waves of the persistent grid, larger tiles preferred at equal cost (the
-// constant stands for per-tile fill/drain).
-int pick_bn(int M, int N, int sms) {
+inline int64_t tiles_for(int M, int N, int bn) { return (int64_t)((M + kBM - 1) / kBM) * ((N + bn - 1) / bn); }
+inline size_t sk_bytes(int sms, int bn, int64_t tiles) {
+  return (size_t)2 * sms * kBM * bn * sizeof(int32_t) + (size_t)((tiles + 63) / 64 * 64) * sizeof(uint32_t);
+}
+
+// Tile width and schedule.  Measured on B200, the time per 128-byte k-block of a CTA grows only
+// mildly with the tile width (~ bn + 400), so what counts is how many k-blocks the busiest CTA
+// runs: whole tiles in waves, or (given a workspace) equal shares of all k-blocks with the cut
+// tiles summed up by their last contributor.  That sum is a latency-bound read of every
+// contributor's 128 x bn int32 partial by one CTA (measured: ~25 us + ~8 us per contributor at
+// bn = 256), charged below in k-block equivalents, so stream-K is picked only for few-tile,
+// very-long-K problems.
+Plan make_plan(int M, int N, int num_kb, int sms, size_t ws_bytes) {
   const int cands[4] = {256, 192, 128, 64};
-  int best = 128;
-  int64_t best_cost = -1;
-  const int64_t mt = (M + kBM - 1) / kBM;
+  Plan best{128, false, 1};
+  double best_cost = -1.0;
+  // HOT_GEMM_SCHEDULE=streamk forces the stream-K schedule wherever it is possible (tests, tuning)
+  const char* env = getenv("HOT_GEMM_SCHEDULE");
+  const bool force_sk = env && env[0] == 's';
   for (int bn : cands) {
-    const int64_t tiles = mt * ((N + bn - 1) / bn);
+    const int64_t tiles = tiles_for(M, N, bn);
     const int64_t waves = (tiles + sms - 1) / sms;
-    const int64_t cost = waves * (bn + 24);
-    if (best_cost < 0 || cost < best_cost) {
-      best_cost = cost;
-      best = bn;
+    const double per_kb = bn + 400.0;
+    const double dp = (double)waves * num_kb * per_kb;
+    if (best_cost < 0 || dp < best_cost) {
+      best_cost = dp;
+      best = Plan{bn, false, (unsigned)(tiles < sms ? tiles : sms)};
+    }
+    const int64_t units = tiles * num_kb;
+    if (ws_bytes >= sk_bytes(sms, bn, tiles) && units >= 2 * (int64_t)sms && tiles % sms != 0) {
+      const double share = (double)units / sms;
+      const double contributors = 1.0 + (double)num_kb / share;
+      const double sk = (share + (60.0 + 18.0 * contributors) * bn / 256.0) * per_kb;
+      if (sk < best_cost || (force_sk && !best.stream_k)) {
+        best_cost = force_sk ? 0.0 : sk;
+        best = Plan{bn, true, (unsigned)sms};
+      }
     }
   }
   return best;
 }
 
 template <bool A4, bool B4>
-int launch_bn(int bn, const void* a, int64_t lda, const void* b, int64_t ldb, const GemmParams& p, cudaStream_t st, int sms) {
-  switch (bn) {
-    case 256: return launch_gemm<256, A4, B4>(a, lda, b, ldb, p, st, sms);
-    case 192: return launch_gemm<192, A4, B4>(a, lda, b, ldb, p, st, sms);
-    case 64: return launch_gemm<64, A4, B4>(a, lda, b, ldb, p, st, sms);
-    default: return launch_gemm<128, A4, B4>(a, lda, b, ldb, p, st, sms);
+int launch_bn(const void* a, int64_t lda, const void* b, int64_t ldb, const GemmParams& p, const Plan& plan, cudaStream_t st) {
+  switch (plan.bn) {
+    case 256: return launch_gemm<256, A4, B4>(a, lda, b, ldb, p, plan, st);
+    case 192: return launch_gemm<192, A4, B4>(a, lda, b, ldb, p, plan, st);
+    case 64: return launch_gemm<64, A4, B4>(a, lda, b, ldb, p, plan, st);
+    default: return launch_gemm<128, A4, B4>(a, lda, b, ldb, p, plan, st);
   }
 }
 
 }  // namespace
-
-int device_sm_count();
-
 }  // namespace hot
 
-extern "C" int hot_gemm_i8(const void* a, int a_storage, int64_t lda, const void* b, int b_storage, int64_t ldb,
-                           int64_t M, int64_t N, int64_t K, const float* scale_a, int scale_a_per_row,
-                           const float* scale_b, int scale_b_per_row, float post, void* out, int out_dtype, int64_t ldo,
-                           uint32_t* status_word, hot_stream_t stream) {
+extern "C" size_t hot_gemm_i8_workspace_bytes(int64_t M, int64_t N) {
+  const int sms = hot::device_sm_count();
+  if (sms <= 0 || M <= 0 || N <= 0) return 0;
+  size_t need = 0;
+  for (int bn : {256, 192, 128, 64}) {
+    const size_t b = hot::sk_bytes(sms, bn, hot::tiles_for((int)M, (int)N, bn));
+    if (b > need) need = b;
+  }
+  return need;
+}
+
+extern "C" int hot_gemm_i8_ws(const void* a, int a_storage, int64_t lda, const void* b, int b_storage, int64_t ldb,
+                              int64_t M, int64_t N, int64_t K, const float* scale_a, int scale_a_per_row,
+                              const float* scale_b, int scale_b_per_row, float post, void* out, int out_dtype, int64_t ldo,
+                              void* workspace, size_t workspace_bytes, uint32_t* status_word, hot_stream_t stream) {
   using namespace hot;
   if (!a || !b || !out) HOT_FAIL(HOT_ERR_ARG, "hot_gemm_i8: null pointer");
   if (M <= 0 || N <= 0 || K <= 0 || M > (1 << 30) || N > (1 << 30) || K > (1 << 30))
@@ -457,9 +616,27 @@ extern "C" int hot_gemm_i8(const void* a, int a_storage, int64_t lda, const void
   cudaStream_t st = (cudaStream_t)stream;
   const int sms = device_sm_count();
   if (sms <= 0) return HOT_ERR_CUDA;
-  const int bn = pick_bn(p.M, p.N, sms);
-  if (!a4 && !b4) return launch_bn<false, false>(bn, a, lda, b, ldb, p, st, sms);
-  if (a4 && !b4) return launch_bn<true, false>(bn, a, lda, b, ldb, p, st, sms);
-  if (!a4 && b4) return launch_bn<false, true>(bn, a, lda, b, ldb, p, st, sms);
-  return launch_bn<true, true>(bn, a, lda, b, ldb, p, st, sms);
+  if (workspace && ((uintptr_t)workspace) % 16 != 0) HOT_FAIL(HOT_ERR_ARG, "hot_gemm_i8_ws: workspace must be 16-byte aligned");
+  const Plan plan = make_plan(p.M, p.N, p.num_kb, sms, workspace ? workspace_bytes : 0);
+  p.stream_k = plan.stream_k ? 1 : 0;
+  p.sk_partials = nullptr;
+  p.sk_counters = nullptr;
+  if (plan.stream_k) {
+    const int64_t tiles = tiles_for(p.M, p.N, plan.bn);
+    p.sk_partials = (int32_t*)workspace;
+    p.sk_counters = (uint32_t*)((uint8_t*)workspace + (size_t)2 * sms * kBM * plan.bn * sizeof(int32_t));
+    HOT_CUDA(cudaMemsetAsync(p.sk_counters, 0, (size_t)tiles * sizeof(uint32_t), st));
+  }
+  if (!a4 && !b4) return launch_bn<false, false>(a, lda, b, ldb, p, plan, st);
+  if (a4 && !b4) return launch_bn<true, false>(a, lda, b, ldb, p, plan, st);
+  if (!a4 && b4) return launch_bn<false, true>(a, lda, b, ldb, p, plan, st);
+  return launch_bn<true, true>(a, lda, b, ldb, p, plan, st);
+}
+
+extern "C" int hot_gemm_i8(const void* a, int a_storage, int64_t lda, const void* b, int b_storage, int64_t ldb,
+                           int64_t M, int64_t N, int64_t K, const float* scale_a, int scale_a_per_row,
+                           const float* scale_b, int scale_b_per_row, float post, void* out, int out_dtype, int64_t ldo,
+                           uint32_t* status_word, hot_stream_t stream) {
+  return hot_gemm_i8_ws(a, a_storage, lda, b, b_storage, ldb, M, N, K, scale_a, scale_a_per_row, scale_b, scale_b_per_row,
+                        post, out, out_dtype, ldo, nullptr, 0, status_word, stream);
 }

@@ -47,7 +47,7 @@ inline size_t up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 inline int64_t code_pitch(int64_t len, int storage) { return (int64_t)up((size_t)(storage == HOT_STORE_INT4 ? (len + 1) / 2 : len), 16); }
 
 struct Workspace {
-  size_t off_qgo, off_sgo, off_qw, off_sw, off_qgw, off_sgw, off_scratch, w_scratch_off, total;
+  size_t off_qgo, off_sgo, off_qw, off_sw, off_qgw, off_sgw, off_scratch, w_scratch_off, off_gemm, gemm_bytes, total;
   int64_t ld_qgo, ld_qw, ld_qgw, lp;
 };
 
@@ -70,6 +70,10 @@ int plan(int64_t L, int64_t O, int64_t I, const hot_linear_cfg_t& c, Workspace& 
   w.w_scratch_off = (size_t)((64 + L + O + 1) / 2 * 2);
   w.off_scratch = o;
   o += up((w.w_scratch_off + hot_col_ht_quant_scratch_words(c.dtype, O, I, c.order_o, c.order_o, c.q_w.scale_mode) + 64) * sizeof(uint32_t), kAlign);
+  // stream-K workspace of the two GEMMs (they run one after the other and share it)
+  const size_t g1 = hot_gemm_i8_workspace_bytes(L, I), g2 = hot_gemm_i8_workspace_bytes(O, I);
+  w.gemm_bytes = g1 > g2 ? g1 : g2;
+  w.off_gemm = o; o += up(w.gemm_bytes, kAlign);
   w.total = o;
   return HOT_OK;
 }
@@ -198,9 +202,9 @@ extern "C" int hot_linear_backward(const void* go, int64_t ldgo, const void* w, 
       }
     }
     rejoin();  // the g_x GEMM needs the quantised weight
-    rc = hot_gemm_i8(base + ws.off_qgo, cfg->q_gx.storage, ws.ld_qgo, base + ws.off_qw, HOT_STORE_INT8, ws.ld_qw, L, I, O,
-                     s_go, cfg->q_gx.scale_mode == HOT_SCALE_ROW, s_w, 0, 1.0f / (float)cfg->order_o, grad_x, cfg->dtype,
-                     ldgx, status_word, stream);
+    rc = hot_gemm_i8_ws(base + ws.off_qgo, cfg->q_gx.storage, ws.ld_qgo, base + ws.off_qw, HOT_STORE_INT8, ws.ld_qw, L, I, O,
+                        s_go, cfg->q_gx.scale_mode == HOT_SCALE_ROW, s_w, 0, 1.0f / (float)cfg->order_o, grad_x, cfg->dtype,
+                        ldgx, ws.gemm_bytes ? base + ws.off_gemm : nullptr, ws.gemm_bytes, status_word, stream);
     if (rc) return rc;
   }
   if (grad_w) {
@@ -209,9 +213,9 @@ extern "C" int hot_linear_backward(const void* go, int64_t ldgo, const void* w, 
                             HOT_LAYOUT_TRANSPOSED, base + ws.off_qgw, ws.ld_qgw, s_gw, scratch + 64 + L, stream);
       if (rc) return rc;
     }
-    rc = hot_gemm_i8(base + ws.off_qgw, cfg->q_gw.storage, ws.ld_qgw, x_q_t, cfg->q_x.storage, hot_abc_pitch(L, cfg), O, I,
-                     ws.lp, s_gw, cfg->q_gw.scale_mode == HOT_SCALE_ROW, scale_x, 0, 1.0f / (float)cfg->order_l, grad_w,
-                     cfg->dtype, ldgw, status_word, stream);
+    rc = hot_gemm_i8_ws(base + ws.off_qgw, cfg->q_gw.storage, ws.ld_qgw, x_q_t, cfg->q_x.storage, hot_abc_pitch(L, cfg), O, I,
+                        ws.lp, s_gw, cfg->q_gw.scale_mode == HOT_SCALE_ROW, scale_x, 0, 1.0f / (float)cfg->order_l, grad_w,
+                        cfg->dtype, ldgw, ws.gemm_bytes ? base + ws.off_gemm : nullptr, ws.gemm_bytes, status_word, stream);
     if (rc) return rc;
   }
   return HOT_OK;

@@ -135,22 +135,29 @@ def col_ht_quant_static(x: torch.Tensor, order: int, sel: Sequence[int], q: Quan
 
 def gemm_i8(a: torch.Tensor, a_storage: str, b: torch.Tensor, b_storage: str, M: int, N: int, K: int,
             scale_a: Optional[torch.Tensor], scale_b: Optional[torch.Tensor], post: float = 1.0,
-            out_dtype: torch.dtype = torch.float32, status: Optional[torch.Tensor] = None) -> torch.Tensor:
+            out_dtype: torch.dtype = torch.float32, status: Optional[torch.Tensor] = None,
+            stream_k: bool = False) -> torch.Tensor:
     """out [M, N] = ((a . b^T) * scale_a[m or 0]) * scale_b[n or 0] * post on the tcgen05 integer path;
     ``a`` [M, pitch] and ``b`` [N, pitch] are uint8/int8 code matrices with K contiguous.
-    ``out_dtype=torch.int32`` returns the raw accumulator."""
+    ``out_dtype=torch.int32`` returns the raw accumulator.  ``stream_k=True`` hands the kernel a
+    workspace so that it may balance k-blocks over the SMs (same results)."""
     _require_cuda(a, b)
     odt = {torch.float32: C.HOT_F32, torch.bfloat16: C.HOT_BF16, torch.int32: C.HOT_I32}[out_dtype]
     out = torch.empty((M, N), dtype=out_dtype, device=a.device)
     sa = scale_a.data_ptr() if scale_a is not None else None
     sb = scale_b.data_ptr() if scale_b is not None else None
     with torch.cuda.device(a.device):
-        C.check(C.lib().hot_gemm_i8(a.data_ptr(), C.STORE_INT4 if a_storage == "int4" else C.STORE_INT8, a.stride(0),
-                                    b.data_ptr(), C.STORE_INT4 if b_storage == "int4" else C.STORE_INT8, b.stride(0),
-                                    M, N, K, sa, int(scale_a is not None and scale_a.numel() > 1), sb,
-                                    int(scale_b is not None and scale_b.numel() > 1), float(post), out.data_ptr(), odt,
-                                    out.stride(0), status.data_ptr() if status is not None else None, _stream(a)),
-                "hot_gemm_i8")
+        ws = None
+        if stream_k:
+            ws = torch.empty((int(C.lib().hot_gemm_i8_workspace_bytes(M, N)),), dtype=torch.uint8, device=a.device)
+        C.check(C.lib().hot_gemm_i8_ws(a.data_ptr(), C.STORE_INT4 if a_storage == "int4" else C.STORE_INT8, a.stride(0),
+                                       b.data_ptr(), C.STORE_INT4 if b_storage == "int4" else C.STORE_INT8, b.stride(0),
+                                       M, N, K, sa, int(scale_a is not None and scale_a.numel() > 1), sb,
+                                       int(scale_b is not None and scale_b.numel() > 1), float(post), out.data_ptr(), odt,
+                                       out.stride(0), ws.data_ptr() if ws is not None else None,
+                                       ws.numel() if ws is not None else 0,
+                                       status.data_ptr() if status is not None else None, _stream(a)),
+                "hot_gemm_i8_ws")
     return out
 
 

@@ -147,6 +147,21 @@ int hot_gemm_i8(const void* a, int a_storage, int64_t lda, const void* b, int b_
                 const float* scale_b, int scale_b_per_row, float post, void* out, int out_dtype,
                 int64_t ldo, uint32_t* status_word, hot_stream_t stream);
 
+/*
+ * hot_gemm_i8 with a caller-owned workspace (hot_gemm_i8_workspace_bytes(M, N) bytes, 16-byte
+ * aligned, contents irrelevant).  With it the kernel may cut the work into equal shares of
+ * (tile, k-block) units per SM ("stream-K") instead of whole tiles: a tile shared by several CTAs
+ * is summed, in exact int32 arithmetic, by the contributor that arrives last.  Results are
+ * identical to hot_gemm_i8; the schedule matters when the tile count is not a multiple of the SM
+ * count (few tiles, or a ragged last wave).  workspace == NULL behaves as hot_gemm_i8.
+ */
+size_t hot_gemm_i8_workspace_bytes(int64_t M, int64_t N);
+int hot_gemm_i8_ws(const void* a, int a_storage, int64_t lda, const void* b, int b_storage, int64_t ldb,
+                   int64_t M, int64_t N, int64_t K, const float* scale_a, int scale_a_per_row,
+                   const float* scale_b, int scale_b_per_row, float post, void* out, int out_dtype,
+                   int64_t ldo, void* workspace, size_t workspace_bytes, uint32_t* status_word,
+                   hot_stream_t stream);
+
 /* Per-layer configuration of the backward pass (scheme gih_gwlr, utils/quant_matmul.py:214-348). */
 typedef struct hot_linear_cfg {
   int32_t dtype;      /* dtype of grad_out, w, x and of the returned gradients                  */

@@ -121,12 +121,16 @@ def test_col_ht_quant(ops, order, sel, dtype, storage, bits, rounding, layout, s
 GEMM_CASES = [
     # M, N, K
     (128, 128, 128), (200, 96, 320), (37, 48, 96), (1000, 768, 3072), (384, 130, 50), (256, 256, 1970),
+    (768, 768, 6304), (2500, 768, 1024), (19000, 256, 384),
 ]
 
 
 @pytest.mark.parametrize("M,N,K", GEMM_CASES)
 @pytest.mark.parametrize("a_storage,b_storage", [("int8", "int8"), ("int4", "int4"), ("int4", "int8"), ("int8", "int4")])
-def test_gemm_i8_accumulators_and_dequant(ops, M, N, K, a_storage, b_storage):
+@pytest.mark.parametrize("stream_k", [False, True])
+def test_gemm_i8_accumulators_and_dequant(ops, M, N, K, a_storage, b_storage, stream_k, monkeypatch):
+    if stream_k:   # the cost model rarely picks stream-K at test sizes: force it wherever it applies
+        monkeypatch.setenv("HOT_GEMM_SCHEDULE", "streamk")
     rng = np.random.default_rng(M + N + K)
 
     def make(rows, storage):
@@ -150,12 +154,14 @@ def test_gemm_i8_accumulators_and_dequant(ops, M, N, K, a_storage, b_storage):
     b, b_dev = make(N, b_storage)
     ref = a.astype(np.int64) @ b.astype(np.int64).T
     status = torch.zeros(1, dtype=torch.int32, device="cuda")
-    acc = ops.gemm_i8(a_dev, a_storage, b_dev, b_storage, M, N, K, None, None, out_dtype=torch.int32, status=status)
+    acc = ops.gemm_i8(a_dev, a_storage, b_dev, b_storage, M, N, K, None, None, out_dtype=torch.int32, status=status,
+                      stream_k=stream_k)
     sa = (rng.random(M, dtype=np.float32) + 0.5) * 1e-4
     sb = np.array([3.3e-3], np.float32)
-    out = ops.gemm_i8(a_dev, a_storage, b_dev, b_storage, M, N, K, _dev(sa), _dev(sb), post=1.0 / 16, status=status)
+    out = ops.gemm_i8(a_dev, a_storage, b_dev, b_storage, M, N, K, _dev(sa), _dev(sb), post=1.0 / 16, status=status,
+                      stream_k=stream_k)
     out_bf = ops.gemm_i8(a_dev, a_storage, b_dev, b_storage, M, N, K, _dev(sa[:1]), _dev(sb), post=0.25,
-                         out_dtype=torch.bfloat16, status=status)
+                         out_dtype=torch.bfloat16, status=status, stream_k=stream_k)
     torch.cuda.synchronize()
     assert int(status.item()) == 0, "a bounded device-side wait ran out"
     assert np.array_equal(acc.cpu().numpy().astype(np.int64), ref)
