@@ -489,8 +489,13 @@ def kernel_legs(ops, layers, a, dtype, device, pk, status):
     in_layer = ["go_dual_quant", "col_ht_quant_w", "gemm_gx_int4xint8", "gemm_gw_int8"]
     top = max(in_layer, key=lambda k: kern[k]["us"])
     tk = kern[top]
-    roof = {"kernel": top, "bound": tk["bound"], "achieved": tk["achieved"], "peak": tk["peak"], "unit": tk["unit"],
-            "frac": tk["frac"], "traffic": None, "launch_us": tk["us"],
+    # DRAM traffic per launch: measured once with ncu (profiles/go_dual_and_gemm_fc1_12608x3072x768_bf16.md):
+    # the grad_out pair moved 167.0 MB (dram read + write) for 96.8 MB of algorithmic bytes at this shape
+    # (two reads of the input, one per pass); scaled here by the algorithmic bytes.  No figure for the others.
+    traffic = round(tk["bytes"] * 167.0 / 96.8) if top == "go_dual_quant" and dtype == torch.bfloat16 else None
+    roof = {"kernel": top + (" (two launches: abs-max pass + quantise pass)" if top == "go_dual_quant" else ""),
+            "bound": tk["bound"], "achieved": tk["achieved"], "peak": tk["peak"], "unit": tk["unit"],
+            "frac": tk["frac"], "traffic": traffic, "launch_us": tk["us"],
             "peak_source": ("%s hbm_gbs" % pk["source"]) if tk["bound"] == "hbm" else
                            ("2 x %s bf16_tflops (no measured INT8 peak; nominal INT8:bf16 = 2)" % pk["source"]),
             "share_of_fc1_layer": round(tk["us"] / t_layer, 3)}
