@@ -490,9 +490,9 @@ def kernel_legs(ops, layers, a, dtype, device, pk, status):
     top = max(in_layer, key=lambda k: kern[k]["us"])
     tk = kern[top]
     # DRAM traffic per launch: measured once with ncu (profiles/go_dual_and_gemm_fc1_12608x3072x768_bf16.md):
-    # the grad_out pair moved 167.0 MB (dram read + write) for 96.8 MB of algorithmic bytes at this shape
+    # the grad_out pair moved 167.0 MB (dram read + write) for 116.2 MB of algorithmic bytes at this shape
     # (two reads of the input, one per pass); scaled here by the algorithmic bytes.  No figure for the others.
-    traffic = round(tk["bytes"] * 167.0 / 96.8) if top == "go_dual_quant" and dtype == torch.bfloat16 else None
+    traffic = round(tk["bytes"] * 167.0 / 116.2) if top == "go_dual_quant" and dtype == torch.bfloat16 else None
     roof = {"kernel": top + (" (two launches: abs-max pass + quantise pass)" if top == "go_dual_quant" else ""),
             "bound": tk["bound"], "achieved": tk["achieved"], "peak": tk["peak"], "unit": tk["unit"],
             "frac": tk["frac"], "traffic": traffic, "launch_us": tk["us"],
@@ -500,8 +500,28 @@ def kernel_legs(ops, layers, a, dtype, device, pk, status):
                            ("2 x %s bf16_tflops (no measured INT8 peak; nominal INT8:bf16 = 2)" % pk["source"]),
             "share_of_fc1_layer": round(tk["us"] / t_layer, 3)}
     fp = {"fc1_hot_us": round(t_layer, 2), "fc1_bf16_matmul_us": round(t_fp, 2), "speedup": round(t_fp / t_layer, 3),
-          "dtype": a.dtype}
+          "dtype": a.dtype, "config1_fp32": config1_leg(ops, device, status)}
     return kern, roof, fp
+
+
+def config1_leg(ops, device, status):
+    """BASELINE config 1: one ViT-B/16 fc1 backward in fp32, X [6304, 768] N(0,1) with 1 % of the
+    channels scaled x20, W kaiming-uniform, grad_out N(0, 1e-3); Hadamard order 16, INT4 g_x with
+    stochastic rounding, 8-of-16 low-rank INT8 g_w; beside the fp32 matmul backward (TF32 off)."""
+    from hot_b200.hadamard_matmul import lowrank_selection
+    g = torch.Generator(device=device).manual_seed(0)
+    L, I, O = 6304, 768, 3072
+    x = torch.randn((L, I), device=device, generator=g)
+    x[:, torch.randperm(I, device=device, generator=g)[:8]] *= 20.0
+    w = (torch.rand((O, I), device=device, generator=g) * 2 - 1) / I ** 0.5
+    gos = [torch.randn((L, O), device=device, generator=g) * 1e-3 for _ in range(4)]   # 4 x 77 MB > L2
+    order_l, sel = lowrank_selection(L, "half16")
+    cfg = ops.LinearConfig(order_o=16, order_l=order_l, sel_l=sel)
+    x_q_t, s_x = ops.abc_compress(x, cfg)
+    t_hot = _graph_time(lambda i: ops.linear_backward(gos[i % 4], w, x_q_t, s_x, cfg, status=status), 4, device)
+    t_fp32 = _graph_time(lambda i: (torch.matmul(gos[i % 4], w), torch.matmul(gos[i % 4].t(), x)), 4, device)
+    return {"hot_us": round(t_hot, 1), "fp32_matmul_us": round(t_fp32, 1), "speedup_vs_fp32": round(t_fp32 / t_hot, 2),
+            "effective_tops": round(4.0 * L * I * O / t_hot / 1e6, 1)}
 
 
 def e2e_leg(layers, a, dtype, device, flops):

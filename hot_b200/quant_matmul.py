@@ -273,6 +273,47 @@ class HQ_Linear(nn.Linear):
         return output
 
 
+class HQ_Conv2d(nn.Conv2d):
+    """Drop-in ``nn.Conv2d`` whose backward is HOT (utils/quant_matmul.py:426-488): the input is
+    unfolded to [B, H'*W', C*kh*kw] (im2col) and goes through the same ``FLinearQ`` as a linear
+    layer, with the kernel viewed as a [C_out, C*kh*kw] weight.  Grouped (depth-wise) convolutions
+    raise ``NotImplementedError``, as in the reference."""
+
+    def __init__(self, in_channels, out_channels, kernel_size, stride=1, padding=0, dilation=1, groups=1, bias=True,
+                 padding_mode="zeros") -> None:
+        super().__init__(in_channels, out_channels, kernel_size, stride, padding, dilation, groups, bias, padding_mode)
+        a = _args()
+        _check_scheme_name(a)
+        self.register_buffer("hadamard_out", torch.tensor(TD.get_or_register("hadamard", self.out_channels),
+                                                          dtype=self.weight.dtype))
+        self.register_buffer("hadamard_bs", torch.zeros((1, 1), dtype=self.weight.dtype))
+        self._bs_tokens = None
+        self.layer_name = " "
+
+    def forward(self, input: Tensor) -> Tensor:
+        if self.groups > 1:
+            raise NotImplementedError
+        a = _args()
+        B = input.shape[0]
+        cols = F.unfold(input, self.kernel_size, dilation=self.dilation, padding=self.padding,
+                        stride=self.stride).transpose(1, 2)                      # [B, H'*W', C*kh*kw]
+        weight = self.weight.view(self.weight.size(0), -1)
+        preset = getattr(a, "lowRankPreset", None)
+        tokens = cols.shape[1] if preset is None else cols.shape[0] * cols.shape[1]
+        if tokens != self._bs_tokens or self.hadamard_bs.device != self.weight.device:
+            from .hadamard_matmul import hadamard
+            n, sel = lowrank_selection(tokens, preset, a.vectorPercentile)
+            self.hadamard_bs = torch.tensor(hadamard(n)[sel], dtype=self.weight.dtype, device=self.weight.device)
+            self._bs_tokens = tokens
+        out = FLinearQ.apply(cols, weight, self.hadamard_out, self.hadamard_bs, self.layer_name)   # [B, H'*W', C_out]
+        h_out = (input.shape[-2] + 2 * self.padding[0] - self.dilation[0] * (self.kernel_size[0] - 1) - 1) // self.stride[0] + 1
+        w_out = (input.shape[-1] + 2 * self.padding[1] - self.dilation[1] * (self.kernel_size[1] - 1) - 1) // self.stride[1] + 1
+        out = out.transpose(1, 2).reshape(B, self.out_channels, h_out, w_out)
+        if self.bias is not None:
+            out = out + self.bias.view(1, -1, 1, 1)
+        return out
+
+
 def _check_scheme_name(a) -> None:
     if a.transform_scheme not in ("hadamard", "low_rank", "gilr_gwh", "gilro_gwh", "gih_gwlr"):
         raise Exception("Transformation method not implemented: " + str(a.transform_scheme))
@@ -301,8 +342,15 @@ def replace_layers(model: nn.Module, old, new) -> None:
             if module.bias is not None:
                 new_layer.bias.data = module.bias.data
             setattr(model, n, new_layer)
-        elif old == nn.Conv2d and isinstance(module, old):
-            raise NotImplementedError("HQ_Conv2d is not built; leave convolutions in full precision")
+        elif old == nn.Conv2d and isinstance(module, old) and not isinstance(module, new) and module.groups == 1:
+            new_layer = new(module.in_channels, module.out_channels, kernel_size=module.kernel_size, stride=module.stride,
+                            padding=module.padding)
+            new_layer = new_layer.to(device=module.weight.device, dtype=module.weight.dtype)
+            new_layer.weight.data = module.weight.data
+            new_layer.weight.requires_grad = module.weight.requires_grad
+            if module.bias is not None:
+                new_layer.bias.data = module.bias.data
+            setattr(model, n, new_layer)
 
 
 def precision_scheduler(current_epoch, max_bit=8, min_bit=4, milestones=()):

@@ -243,3 +243,31 @@ def test_sawb_for_weight_and_activation(hot, golden):
 def hot_ops():
     from hot_b200 import ops
     return ops
+
+
+def test_hq_conv2d_matches_its_linear_form(hot):
+    """HQ_Conv2d is im2col + the same FLinearQ: with nearest rounding its gradients equal those of an
+    HQ_Linear fed the unfolded input, and its forward equals nn.Conv2d."""
+    args, qm = hot
+    args.quantBWDGogi = args.quantBWDWgt = args.quantBWDGogw = args.quantBWDAct = "int"
+    torch.manual_seed(0)
+    conv = qm.HQ_Conv2d(4, 32, kernel_size=4, stride=4).cuda()          # 4*4*4 = 64 input features per patch
+    x = torch.randn(8, 4, 16, 16, device="cuda", requires_grad=True)     # 16 patches per image, 128 tokens
+    y = conv(x)
+    ref = torch.nn.functional.conv2d(x, conv.weight, conv.bias, stride=4)
+    assert y.shape == ref.shape and torch.allclose(y, ref, atol=1e-5)
+    go = torch.randn_like(y) * 1e-3
+    y.backward(go)
+    lin = qm.HQ_Linear(64, 32).cuda()
+    lin.weight.data = conv.weight.data.view(32, 64).clone()
+    lin.bias.data = conv.bias.data.clone()
+    cols = torch.nn.functional.unfold(x.detach(), 4, stride=4).transpose(1, 2).reshape(-1, 64).requires_grad_(True)
+    lin(cols).backward(go.flatten(2).transpose(1, 2).reshape(-1, 32))
+    assert torch.equal(conv.weight.grad.view(32, 64), lin.weight.grad)
+    gx_cols = cols.grad.reshape(8, 16, 64).transpose(1, 2)
+    assert torch.allclose(x.grad, torch.nn.functional.fold(gx_cols, (16, 16), 4, stride=4), atol=1e-7)
+    model = nn.Sequential(nn.Conv2d(3, 16, 3, padding=1), nn.Conv2d(16, 16, 3, groups=16)).cuda()
+    qm.replace_layers(model, nn.Conv2d, qm.HQ_Conv2d)
+    assert isinstance(model[0], qm.HQ_Conv2d) and type(model[1]) is nn.Conv2d      # depth-wise stays as it is
+    with pytest.raises(NotImplementedError):
+        qm.HQ_Conv2d(16, 16, 3, groups=16).cuda()(torch.randn(16, 16, 8, 8, device="cuda"))
