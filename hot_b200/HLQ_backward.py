@@ -60,17 +60,23 @@ def backward(Go: torch.Tensor, W: torch.Tensor, X: torch.Tensor, reorder_idx_go=
         q_w=ops.Quant(4, "int4", rounding, "tensor", seed, base + 2),
         q_gw=ops.Quant(8, "int8", rounding, "tensor", seed, base + 3),
         q_x=ops.Quant(8, "int8", rounding, "tensor", seed, base + 4))
-    n, r = order_l, len(sel)
+    n = order_l
     ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
     status = torch.zeros(1, dtype=torch.int32, device=Go.device)
+    I = W.shape[1]
+    q_w8 = ops.Quant(4, "int8", rounding, "tensor", seed, base + 2)      # weight codes one per byte (B operand)
     ev[0].record()
-    q_go, s_go = ops.row_ht_quant(Go, int(H_size), cfg.q_gx)
-    q_w_t, s_w, _ = ops.col_ht_quant(W, int(H_size), list(range(int(H_size))), cfg.q_w, "natural")
-    q_gw, s_gw, lp = ops.col_ht_quant(Go, n, sel, cfg.q_gw, "transposed")
+    if order_l == 16 and L % 32 == 0 and O % 64 == 0:
+        q_go, s_go, q_gw, s_gw = ops.go_dual_quant(Go, cfg, status)          # both operands from one read per pass
+        lp = L // 2
+    else:
+        q_go, s_go = ops.row_ht_quant(Go, int(H_size), cfg.q_gx)
+        q_gw, s_gw, lp = ops.col_ht_quant(Go, n, sel, cfg.q_gw, "transposed")
+    q_w_t, s_w, _ = ops.col_ht_quant(W, int(H_size), list(range(int(H_size))), q_w8, "natural")
     x_q_t, s_x, _ = ops.col_ht_quant(X, n, sel, cfg.q_x, "natural")
     ev[1].record()
-    gx = ops.gemm_i8(q_go, "int4", q_w_t, "int4", L, W.shape[1], O, s_go, s_w, 1.0 / int(H_size), Go.dtype, status)
-    gw = ops.gemm_i8(q_gw, "int8", x_q_t, "int8", O, W.shape[1], lp, s_gw, s_x, 1.0 / n, Go.dtype, status)
+    gx = ops.gemm_i8(q_go, "int4", q_w_t, "int8", L, I, O, s_go, s_w, 1.0 / int(H_size), Go.dtype, status)
+    gw = ops.gemm_i8(q_gw, "int8", x_q_t, "int8", O, I, lp, s_gw, s_x, 1.0 / n, Go.dtype, status)
     ev[2].record()
     torch.cuda.synchronize(Go.device)
     if int(status.item()) != 0:
