@@ -9,7 +9,7 @@
 //   warps 2..5  epilogue: tcgen05.ld the accumulator (each warp its 32-lane quarter), convert,
 //               apply (acc * sa) * sb * post, store fp32 / bf16 / raw int32; the accumulator is
 //               double-buffered in tensor memory, so this overlaps the next tile's MMAs
-//   warps 6..9  (packed INT4 operands only) TMA lands the packed bytes in a raw stage and these
+//   warps 6..13 (packed INT4 operands only) TMA lands the packed bytes in a raw stage and these
 //               warps expand them to int8 into the swizzled stage before the MMA warp is
 //               signalled (Blackwell has no 4-bit integer MMA kind)
 //
@@ -27,6 +27,7 @@ namespace {
 
 constexpr int kBM = 128;
 constexpr int kBK = 128;  // int8 elements (= bytes) of K per stage: one 128B swizzle span
+constexpr int kUnpackThreads = 256;  // 8 warps expand packed INT4 operands
 
 struct GemmParams {
   int M, N, K, num_kb;
@@ -181,11 +182,11 @@ __device__ __forceinline__ void unpack8_x16(uint32_t w, uint32_t& lo, uint32_t& 
 }
 
 // Expand a raw stage of `rows` rows x 64 packed bytes into the swizzled int8 stage
-// (row r at r * 128, 16-byte chunk c at chunk position c ^ (r & 7)).  128 threads cooperate.
-__device__ __forceinline__ void unpack_stage(const uint8_t* raw, uint8_t* dst, int rows, int tid128) {
+// (row r at r * 128, 16-byte chunk c at chunk position c ^ (r & 7)).  The unpack warps cooperate.
+__device__ __forceinline__ void unpack_stage(const uint8_t* raw, uint8_t* dst, int rows, int tid, int nthreads) {
   const int items = rows * 4;  // 16 packed bytes (32 codes = two output chunks) per item
 #pragma unroll 2
-  for (int it = tid128; it < items; it += 128) {
+  for (int it = tid; it < items; it += nthreads) {
     const int r = it >> 2, qd = it & 3;
     const uint4 w = *reinterpret_cast<const uint4*>(raw + r * 64 + qd * 16);
     uint4 o0, o1;
@@ -262,7 +263,7 @@ __device__ __forceinline__ void store_chunk(const GemmParams& p, int row, bool r
 // accumulator is double-buffered in tensor memory so the epilogue of tile i overlaps the MMAs
 // of tile i + 1.
 template <int BN, bool A4, bool B4>
-__global__ void __launch_bounds__((A4 || B4) ? 320 : 192, 1)
+__global__ void __launch_bounds__((A4 || B4) ? 192 + kUnpackThreads : 192, 1)
     gemm_i8_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b, GemmParams p) {
   using L = SmemLayout<BN, A4, B4>;
   constexpr int STAGES = L::kStages;
@@ -292,7 +293,7 @@ __global__ void __launch_bounds__((A4 || B4) ? 320 : 192, 1)
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(&full[s], 1);
       mbar_init(&empty[s], 1);
-      mbar_init(&ready[s], 128);
+      mbar_init(&ready[s], kUnpackThreads);
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&tmem_full[b], 1);
@@ -450,7 +451,7 @@ __global__ void __launch_bounds__((A4 || B4) ? 320 : 192, 1)
     }
   } else if (kUnpack) {
     // ---- unpack warps (INT4 operands): raw stage -> swizzled int8 stage ----
-    const int tid128 = threadIdx.x - 192;
+    const int utid = threadIdx.x - 192;
     uint32_t g = 0;
     bool ok = true;
     SegmentIter iter(p, num_tiles);
@@ -461,8 +462,8 @@ __global__ void __launch_bounds__((A4 || B4) ? 320 : 192, 1)
         const uint32_t ph = (g / STAGES) & 1u;
         ok = mbar_wait(&full[s], ph, abort_flag);
         if (!ok) break;
-        if (A4) unpack_stage(rawA + s * L::kRawA, sA + s * L::kA, kBM, tid128);
-        if (B4) unpack_stage(rawB + s * L::kRawB, sB + s * L::kB, BN, tid128);
+        if (A4) unpack_stage(rawA + s * L::kRawA, sA + s * L::kA, kBM, utid, kUnpackThreads);
+        if (B4) unpack_stage(rawB + s * L::kRawB, sB + s * L::kB, BN, utid, kUnpackThreads);
         fence_proxy_async_smem();  // generic-proxy writes -> visible to the tensor core (async proxy)
         mbar_arrive(&ready[s]);
       }
@@ -509,7 +510,7 @@ int launch_gemm(const void* a, int64_t lda, const void* b, int64_t ldb, const Ge
     HOT_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kBytes));
     attr_set = true;
   }
-  kernel<<<plan.grid, (A4 || B4) ? 320 : 192, L::kBytes, st>>>(ma, mb, p);
+  kernel<<<plan.grid, (A4 || B4) ? 192 + kUnpackThreads : 192, L::kBytes, st>>>(ma, mb, p);
   HOT_CUDA(cudaGetLastError());
   return HOT_OK;
 }
