@@ -39,6 +39,7 @@ struct GemmParams {
   int64_t ldo;
   int out_dtype;
   uint32_t* status;
+  int tma_store;  // the output qualifies for bulk tensor stores (16-byte aligned base and pitch)
   // stream-K: CTAs take equal contiguous ranges of (tile, k-block) units; a tile cut by a range
   // boundary is finished by whichever contributor arrives last
   int stream_k;
@@ -70,6 +71,7 @@ struct SegmentIter {
     u = total * blockIdx.x / gridDim.x;
     end = total * (blockIdx.x + 1) / gridDim.x;
   }
+  __device__ bool exhausted() const { return stream_k ? u >= end : tile >= num_tiles; }
   __device__ bool next(Segment& s) {
     s.first = first;
     first = false;
@@ -147,7 +149,8 @@ __host__ __device__ constexpr uint32_t instr_desc_i8(int bn) {
   return (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(bn >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
 }
 
-constexpr int kSmemBudget = 225 * 1024;  // of the 227 KB a CTA may use
+constexpr int kSmemMax = 227 * 1024;     // what a CTA may use
+constexpr int kStoreStage = 4 * 2 * 4096;  // per epilogue warp two 32-row x 128-byte output boxes
 
 template <int BN, bool A4, bool B4>
 struct SmemLayout {
@@ -156,14 +159,16 @@ struct SmemLayout {
   static constexpr int kRawA = A4 ? kBM * kBK / 2 : 0;
   static constexpr int kRawB = B4 ? BN * kBK / 2 : 0;
   static constexpr int kStage = kA + kB + kRawA + kRawB;
-  static constexpr int kStagesFit = (kSmemBudget - 2048) / kStage;
+  static constexpr int kStagesFit = (kSmemMax - 1536 - kStoreStage) / kStage;
   static constexpr int kStages = kStagesFit > 8 ? 8 : kStagesFit;
   static constexpr int kOffA = 0;
   static constexpr int kOffB = kOffA + kStages * kA;
   static constexpr int kOffRawA = kOffB + kStages * kB;
   static constexpr int kOffRawB = kOffRawA + kStages * kRawA;
-  static constexpr int kOffBar = kOffRawB + kStages * kRawB;
+  static constexpr int kOffStore = kOffRawB + kStages * kRawB;  // = bytes of the operand ring; 1024-aligned
+  static constexpr int kOffBar = kOffStore + kStoreStage;
   static constexpr int kBytes = kOffBar + 512 + 1024;  // barriers + slack to align the base to 1024
+  static_assert(kOffStore % 1024 == 0 && kBytes <= kSmemMax, "shared-memory plan");
   static_assert(kStages >= 2, "tile too large for shared memory");
 };
 
@@ -198,6 +203,12 @@ __device__ __forceinline__ void unpack_stage(const uint8_t* raw, uint8_t* dst, i
     *reinterpret_cast<uint4*>(dst + r * 128 + ((c0 ^ (r & 7)) << 4)) = o0;
     *reinterpret_cast<uint4*>(dst + r * 128 + ((c1 ^ (r & 7)) << 4)) = o1;
   }
+}
+
+// out = ((float)acc * sa) * sb * post: three roundings, the reference's order
+__device__ __forceinline__ float dequant(const GemmParams& p, uint32_t acc, int col, float sa, float sb0) {
+  const float sb = p.sb_row ? ((col < p.N) ? p.sb[col] : 0.0f) : sb0;
+  return __fmul_rn(__fmul_rn(__fmul_rn((float)(int)acc, sa), sb), p.post);
 }
 
 // Dequantise and store 32 consecutive accumulators of one output row:
@@ -264,7 +275,8 @@ __device__ __forceinline__ void store_chunk(const GemmParams& p, int row, bool r
 // of tile i + 1.
 template <int BN, bool A4, bool B4>
 __global__ void __launch_bounds__((A4 || B4) ? 192 + kUnpackThreads : 192, 1)
-    gemm_i8_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b, GemmParams p) {
+    gemm_i8_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
+                   const __grid_constant__ CUtensorMap tma_out, GemmParams p) {
   using L = SmemLayout<BN, A4, B4>;
   constexpr int STAGES = L::kStages;
   constexpr bool kUnpack = A4 || B4;
@@ -282,7 +294,8 @@ __global__ void __launch_bounds__((A4 || B4) ? 192 + kUnpackThreads : 192, 1)
   uint64_t* ready = empty + STAGES;                                  // unpacked (INT4 operands only)
   uint64_t* tmem_full = ready + STAGES;                              // [2] accumulator complete
   uint64_t* tmem_empty = tmem_full + 2;                              // [2] accumulator drained
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
+  uint64_t* fix_bar = tmem_empty + 2;                                // stream-K fix-up copies landed
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(fix_bar + 1);
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -299,10 +312,12 @@ __global__ void __launch_bounds__((A4 || B4) ? 192 + kUnpackThreads : 192, 1)
       mbar_init(&tmem_full[b], 1);
       mbar_init(&tmem_empty[b], 128);
     }
+    mbar_init(fix_bar, 1);
     *abort_flag = 0u;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     tma_prefetch_desc(&tma_a);
     tma_prefetch_desc(&tma_b);
+    if (p.tma_store) tma_prefetch_desc(&tma_out);
   }
   if (warp == 1) tmem_alloc(tmem_slot, kTmemCols);
   tc_fence_before();
@@ -371,15 +386,75 @@ __global__ void __launch_bounds__((A4 || B4) ? 192 + kUnpackThreads : 192, 1)
     bool ok = true;
     SegmentIter iter(p, num_tiles);
     Segment seg;
+    // Output path: each warp lays its 32 rows x 128 bytes out in a swizzled shared-memory box and one
+    // lane hands the box to a bulk tensor store (full 128-byte lines; rows and columns past the
+    // matrix are clipped by the copy engine).  A bf16 box takes two 32-column chunks.
+    uint8_t* const store_stage = smem + L::kOffStore + q * 8192;
+    const bool out16 = p.out_dtype == HOT_BF16;
+    uint32_t boxes = 0;  // boxes filled by this warp so far (selects the buffer)
+    int m0 = 0, n0 = 0, row = 0;
+    bool row_ok = false;
+    float sa = 0.0f;
+    auto emit = [&](int c, const uint32_t (&acc)[32]) {  // chunk c (32 columns) of the current tile, ascending
+      if (!p.tma_store) {
+        store_chunk(p, row, row_ok, n0 + c * 32, acc, sa, sb0);
+        return;
+      }
+      const int col0 = n0 + c * 32;
+      uint8_t* box = store_stage + (boxes & 1u) * 4096 + lane * 128;
+      const bool opens = !out16 || !(c & 1), closes = !out16 || (c & 1);
+      if (opens) {
+        if (lane == 0) bulk_wait_group_read<1>();  // the store that last read this buffer is done with it
+        __syncwarp();
+      }
+
+      if (out16) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          uint32_t w[4];
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            const int i = 8 * j + 2 * k;
+            __nv_bfloat162 t = __floats2bfloat162_rn(dequant(p, acc[i], col0 + i, sa, sb0), dequant(p, acc[i + 1], col0 + i + 1, sa, sb0));
+            w[k] = *reinterpret_cast<uint32_t*>(&t);
+          }
+          *reinterpret_cast<uint4*>(box + ((((c & 1) * 4 + j) ^ (lane & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+        }
+      } else if (raw) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          *reinterpret_cast<uint4*>(box + ((j ^ (lane & 7)) << 4)) = make_uint4(acc[4 * j], acc[4 * j + 1], acc[4 * j + 2], acc[4 * j + 3]);
+      } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          uint32_t w[4];
+#pragma unroll
+          for (int k = 0; k < 4; ++k) w[k] = __float_as_uint(dequant(p, acc[4 * j + k], col0 + 4 * j + k, sa, sb0));
+          *reinterpret_cast<uint4*>(box + ((j ^ (lane & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+        }
+      }
+      if (closes) {
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+          const int col = n0 + (out16 ? (c & ~1) : c) * 32, y = m0 + q * 32;
+          if (col < p.N && y < p.M) tma_store_2d(&tma_out, box, col << (out16 ? 1 : 2), y);
+          bulk_commit_group();  // always: the buffer rotation counts groups
+        }
+        ++boxes;
+      }
+    };
     for (; ok && iter.next(seg); ++it) {
-      const int m0 = (seg.tile / n_tiles) * kBM, n0 = (seg.tile % n_tiles) * BN;
+      m0 = (seg.tile / n_tiles) * kBM;
+      n0 = (seg.tile % n_tiles) * BN;
       const uint32_t buf = it & 1u, bph = (it >> 1) & 1u;
       const int row_loc = q * 32 + lane;
-      const int row = m0 + row_loc;
-      const bool row_ok = row < p.M;
-      const float sa = (row_ok && !raw) ? (p.sa_row ? p.sa[row] : p.sa[0]) : 0.0f;
+      row = m0 + row_loc;
+      row_ok = row < p.M;
+      sa = (row_ok && !raw) ? (p.sa_row ? p.sa[row] : p.sa[0]) : 0.0f;
       const bool whole = seg.kb0 == 0 && seg.kb1 == p.num_kb;
-      int32_t* my_slot = p.sk_partials + ((size_t)(2 * blockIdx.x + (seg.first ? 0 : 1)) * kBM + row_loc) * BN;
+      // partial slot: [chunk of 32 columns][group of 4 columns][row][4] int32, so that a warp's rows are contiguous
+      int32_t* my_slot = p.sk_partials + (size_t)(2 * blockIdx.x + (seg.first ? 0 : 1)) * kBM * BN + row_loc * 4;
       ok = mbar_wait(&tmem_full[buf], bph, abort_flag);
       if (!ok) break;
       tc_fence_after();
@@ -397,17 +472,19 @@ __global__ void __launch_bounds__((A4 || B4) ? 192 + kUnpackThreads : 192, 1)
           for (int i = 0; i < 32; ++i) acc[i] = (uint32_t)((int)acc[i] >> kShift);
         }
         if (whole) {
-          store_chunk(p, row, row_ok, n0 + c * 32, acc, sa, sb0);
+          emit(c, acc);
         } else {
           // partial sum of a tile shared with other CTAs: park the raw accumulators
 #pragma unroll
           for (int i = 0; i < 32; i += 4)
-            *reinterpret_cast<int4*>(my_slot + c * 32 + i) = make_int4((int)acc[i], (int)acc[i + 1], (int)acc[i + 2], (int)acc[i + 3]);
+            *reinterpret_cast<int4*>(my_slot + c * (32 * kBM) + (i >> 2) * (4 * kBM)) =
+                make_int4((int)acc[i], (int)acc[i + 1], (int)acc[i + 2], (int)acc[i + 3]);
         }
       }
       if (!whole) {
         // publish, count the k-blocks delivered for this tile; whoever completes the count adds up
         // every contributor's partial (its own included) and writes the tile
+        asm volatile("fence.proxy.async.global;" ::: "memory");  // the finisher may read it with bulk copies
         __threadfence();
         asm volatile("bar.sync 1, 128;" ::: "memory");
         if (threadIdx.x == 64) {
@@ -426,29 +503,73 @@ __global__ void __launch_bounds__((A4 || B4) ? 192 + kUnpackThreads : 192, 1)
           long long c_lo = t_beg * G / total;
           while (c_lo + 1 < G && total * (c_lo + 1) / G <= t_beg) ++c_lo;
           while (c_lo > 0 && total * c_lo / G > t_beg) --c_lo;
-#pragma unroll 1
-          for (int c = 0; c < BN / 32; ++c) {
-            int sum[32];
+          long long c_hi = c_lo;
+          while (c_hi + 1 < G && total * (c_hi + 1) / G < t_end) ++c_hi;
+          const int ncontrib = (int)(c_hi - c_lo + 1);
+          auto slot_of = [&](long long cta) {
+            const bool cta_first = total * cta / G >= t_beg;  // its range starts inside this tile
+            return p.sk_partials + (size_t)(2 * cta + (cta_first ? 0 : 1)) * kBM * BN;
+          };
+          // Fast path: this was the CTA's last segment, so the operand ring is idle; bulk copies bring
+          // the partials of a group of chunks into it at full bandwidth and the sum reads shared memory.
+          const int group = iter.exhausted() ? L::kOffStore / (ncontrib * 32 * kBM * 4) : 0;
+          if (group >= 1) {
+            uint32_t fph = 0;
+            for (int c0 = 0; c0 < BN / 32; c0 += group) {
+              const int ng = (BN / 32 - c0) < group ? (BN / 32 - c0) : group;
+              asm volatile("bar.sync 1, 128;" ::: "memory");  // the previous group has been read
+              if (threadIdx.x == 64) {
+                asm volatile("fence.proxy.async;" ::: "memory");
+                mbar_expect_tx(fix_bar, (uint32_t)(ncontrib * ng * 32 * kBM * 4));
+                for (int k = 0; k < ncontrib; ++k)
+                  for (int g = 0; g < ng; ++g)
+                    bulk_load(smem + (size_t)(k * ng + g) * (32 * kBM * 4), slot_of(c_lo + k) + (size_t)(c0 + g) * (32 * kBM), 32 * kBM * 4, fix_bar);
+              }
+              if (!mbar_wait(fix_bar, fph, abort_flag)) break;
+              fph ^= 1u;
+              for (int g = 0; g < ng; ++g) {
+                int sum[32];
 #pragma unroll
-            for (int i = 0; i < 32; ++i) sum[i] = 0;
-            for (long long cta = c_lo; cta < G && total * cta / G < t_end; ++cta) {
-              const bool cta_first = total * cta / G >= t_beg;  // its range starts inside this tile
-              const int32_t* slot = p.sk_partials + ((size_t)(2 * cta + (cta_first ? 0 : 1)) * kBM + row_loc) * BN + c * 32;
+                for (int i = 0; i < 32; ++i) sum[i] = 0;
+                for (int k = 0; k < ncontrib; ++k) {
+                  const int4* src = reinterpret_cast<const int4*>(smem + (size_t)(k * ng + g) * (32 * kBM * 4)) + row_loc;
 #pragma unroll
-              for (int i = 0; i < 32; i += 4) {
-                const int4 v = __ldcg(reinterpret_cast<const int4*>(slot + i));
-                sum[i] += v.x; sum[i + 1] += v.y; sum[i + 2] += v.z; sum[i + 3] += v.w;
+                  for (int i = 0; i < 8; ++i) {
+                    const int4 v = src[i * kBM];
+                    sum[4 * i] += v.x; sum[4 * i + 1] += v.y; sum[4 * i + 2] += v.z; sum[4 * i + 3] += v.w;
+                  }
+                }
+                uint32_t acc[32];
+#pragma unroll
+                for (int i = 0; i < 32; ++i) acc[i] = (uint32_t)sum[i];
+                emit(c0 + g, acc);
               }
             }
-            uint32_t acc[32];
+          } else {
+#pragma unroll 1
+            for (int c = 0; c < BN / 32; ++c) {
+              int sum[32];
 #pragma unroll
-            for (int i = 0; i < 32; ++i) acc[i] = (uint32_t)sum[i];
-            store_chunk(p, row, row_ok, n0 + c * 32, acc, sa, sb0);
+              for (int i = 0; i < 32; ++i) sum[i] = 0;
+              for (int k = 0; k < ncontrib; ++k) {
+                const int4* src = reinterpret_cast<const int4*>(slot_of(c_lo + k) + (size_t)c * (32 * kBM)) + row_loc;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                  const int4 v = __ldcg(src + i * kBM);
+                  sum[4 * i] += v.x; sum[4 * i + 1] += v.y; sum[4 * i + 2] += v.z; sum[4 * i + 3] += v.w;
+                }
+              }
+              uint32_t acc[32];
+#pragma unroll
+              for (int i = 0; i < 32; ++i) acc[i] = (uint32_t)sum[i];
+              emit(c, acc);
+            }
           }
         }
         asm volatile("bar.sync 1, 128;" ::: "memory");  // s_finisher is reused by the next segment
       }
     }
+    if (lane == 0) bulk_wait_group<0>();  // the staged boxes have left shared memory and are written
   } else if (kUnpack) {
     // ---- unpack warps (INT4 operands): raw stage -> swizzled int8 stage ----
     const int utid = threadIdx.x - 192;
@@ -504,13 +625,22 @@ int launch_gemm(const void* a, int64_t lda, const void* b, int64_t ldb, const Ge
   if (B4) rc = make_map(&mb, b, p.N, (p.K + 1) / 2, ldb, kBK / 2, BN, false);
   else rc = make_map(&mb, b, p.N, p.K, ldb, kBK, BN, true);
   if (rc) return rc;
+  // output as a byte matrix for the bulk tensor stores; otherwise the epilogue stores from registers
+  const int64_t esz = p.out_dtype == HOT_BF16 ? 2 : 4;
+  GemmParams pp = p;
+  pp.tma_store = (reinterpret_cast<uintptr_t>(p.out) % 16 == 0 && (p.ldo * esz) % 16 == 0) ? 1 : 0;
+  CUtensorMap mo = ma;
+  if (pp.tma_store) {
+    rc = make_map(&mo, p.out, p.M, (int64_t)p.N * esz, p.ldo * esz, 128, 32, true);
+    if (rc) return rc;
+  }
   auto kernel = gemm_i8_kernel<BN, A4, B4>;
   static bool attr_set = false;  // per instantiation
   if (!attr_set) {
     HOT_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kBytes));
     attr_set = true;
   }
-  kernel<<<plan.grid, (A4 || B4) ? 192 + kUnpackThreads : 192, L::kBytes, st>>>(ma, mb, p);
+  kernel<<<plan.grid, (A4 || B4) ? 192 + kUnpackThreads : 192, L::kBytes, st>>>(ma, mb, mo, pp);
   HOT_CUDA(cudaGetLastError());
   return HOT_OK;
 }
@@ -523,10 +653,8 @@ inline size_t sk_bytes(int sms, int bn, int64_t tiles) {
 // Tile width and schedule.  Measured on B200, the time per 128-byte k-block of a CTA grows only
 // mildly with the tile width (~ bn + 400), so what counts is how many k-blocks the busiest CTA
 // runs: whole tiles in waves, or (given a workspace) equal shares of all k-blocks with the cut
-// tiles summed up by their last contributor.  That sum is a latency-bound read of every
-// contributor's 128 x bn int32 partial by one CTA (measured: ~25 us + ~8 us per contributor at
-// bn = 256), charged below in k-block equivalents, so stream-K is picked only for few-tile,
-// very-long-K problems.
+// tiles summed up by their last contributor (it reads every contributor's 128 x bn int32 partial
+// through bulk copies into the idle operand ring), charged below in k-block equivalents.
 Plan make_plan(int M, int N, int num_kb, int sms, size_t ws_bytes) {
   const int cands[4] = {256, 192, 128, 64};
   Plan best{128, false, 1};
@@ -547,7 +675,7 @@ Plan make_plan(int M, int N, int num_kb, int sms, size_t ws_bytes) {
     if (ws_bytes >= sk_bytes(sms, bn, tiles) && units >= 2 * (int64_t)sms && tiles % sms != 0) {
       const double share = (double)units / sms;
       const double contributors = 1.0 + (double)num_kb / share;
-      const double sk = (share + (60.0 + 18.0 * contributors) * bn / 256.0) * per_kb;
+      const double sk = (share + (6.0 + 4.0 * contributors) * bn / 256.0) * per_kb;
       if (sk < best_cost || (force_sk && !best.stream_k)) {
         best_cost = force_sk ? 0.0 : sk;
         best = Plan{bn, true, (unsigned)sms};
