@@ -60,7 +60,7 @@ EncodeTiledFn encode_fn() {
 }  // namespace
 
 int make_map(CUtensorMap* map, const void* base, int64_t rows, int64_t row_bytes, int64_t ld, int box_bytes,
-             int box_rows, bool swizzle128) {
+             int box_rows, int swizzle_bytes) {
   EncodeTiledFn fn = encode_fn();
   if (!fn) HOT_FAIL(HOT_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
   cuuint64_t dims[2] = {(cuuint64_t)row_bytes, (cuuint64_t)rows};
@@ -68,7 +68,7 @@ int make_map(CUtensorMap* map, const void* base, int64_t rows, int64_t row_bytes
   cuuint32_t box[2] = {(cuuint32_t)box_bytes, (cuuint32_t)box_rows};
   cuuint32_t estr[2] = {1, 1};
   CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
-                  CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle_bytes == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : (swizzle_bytes == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_NONE),
                   CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) HOT_FAIL(HOT_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
   return HOT_OK;

@@ -15,6 +15,7 @@
 //
 // Every wait on an mbarrier is bounded in time; when a wait runs out the CTA ORs a code into
 // the caller's status word, stops issuing work, frees its tensor memory and returns.
+#include <type_traits>
 #include <cstdlib>
 
 #include "tma.cuh"
@@ -39,7 +40,7 @@ struct GemmParams {
   int64_t ldo;
   int out_dtype;
   uint32_t* status;
-  int tma_store;  // the output qualifies for bulk tensor stores (16-byte aligned base and pitch)
+  int staged;  // the output qualifies for bulk tensor stores (16-byte aligned base and pitch)
   // stream-K: CTAs take equal contiguous ranges of (tile, k-block) units; a tile cut by a range
   // boundary is finished by whichever contributor arrives last
   int stream_k;
@@ -150,7 +151,8 @@ __host__ __device__ constexpr uint32_t instr_desc_i8(int bn) {
 }
 
 constexpr int kSmemMax = 227 * 1024;     // what a CTA may use
-constexpr int kStoreStage = 4 * 2 * 4096;  // per epilogue warp two 32-row x 128-byte output boxes
+constexpr int kEpiThreads = 256;          // two teams of four warps; a team covers the 128 accumulator rows
+constexpr int kStoreStage = 8 * 2 * 2048;  // per epilogue warp two 32-row x 64-byte output boxes
 
 template <int BN, bool A4, bool B4>
 struct SmemLayout {
@@ -205,10 +207,15 @@ __device__ __forceinline__ void unpack_stage(const uint8_t* raw, uint8_t* dst, i
   }
 }
 
-// out = ((float)acc * sa) * sb * post: three roundings, the reference's order
-__device__ __forceinline__ float dequant(const GemmParams& p, uint32_t acc, int col, float sa, float sb0) {
-  const float sb = p.sb_row ? ((col < p.N) ? p.sb[col] : 0.0f) : sb0;
-  return __fmul_rn(__fmul_rn(__fmul_rn((float)(int)acc, sa), sb), p.post);
+// out = ((float)(acc >> S) * sa) * sb * post for two neighbouring columns: three roundings, the
+// reference's order.  acc is a multiple of 2^S, so (float)acc * 2^-S equals (float)(acc >> S) and the
+// shift moves from the integer pipe, which this epilogue saturates first, to the FMA pipe.
+template <int S, bool SB_ROW>
+__device__ __forceinline__ float2 dequant2(const GemmParams& p, uint32_t a0, uint32_t a1, int col, float2 sa, float2 sb, float2 post) {
+  float2 f = make_float2((float)(int)a0, (float)(int)a1);
+  if (S) f = __fmul2_rn(f, make_float2(1.0f / (float)(1 << S), 1.0f / (float)(1 << S)));
+  if (SB_ROW) sb = make_float2(col < p.N ? p.sb[col] : 0.0f, col + 1 < p.N ? p.sb[col + 1] : 0.0f);
+  return __fmul2_rn(__fmul2_rn(__fmul2_rn(f, sa), sb), post);
 }
 
 // Dequantise and store 32 consecutive accumulators of one output row:
@@ -274,7 +281,7 @@ __device__ __forceinline__ void store_chunk(const GemmParams& p, int row, bool r
 // accumulator is double-buffered in tensor memory so the epilogue of tile i overlaps the MMAs
 // of tile i + 1.
 template <int BN, bool A4, bool B4>
-__global__ void __launch_bounds__((A4 || B4) ? 192 + kUnpackThreads : 192, 1)
+__global__ void __launch_bounds__(kEpiThreads + 64 + ((A4 || B4) ? kUnpackThreads : 0), 1)
     gemm_i8_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
                    const __grid_constant__ CUtensorMap tma_out, GemmParams p) {
   using L = SmemLayout<BN, A4, B4>;
@@ -298,7 +305,9 @@ __global__ void __launch_bounds__((A4 || B4) ? 192 + kUnpackThreads : 192, 1)
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(fix_bar + 1);
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
+  // warps 0-7: epilogue; INT4 operands: warps 8-15 unpack; then one producer warp and one MMA warp
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  constexpr int kProducerWarp = (kEpiThreads + (kUnpack ? kUnpackThreads : 0)) / 32, kMmaWarp = kProducerWarp + 1;
   const int n_tiles = (p.N + BN - 1) / BN;
   const int num_tiles = ((p.M + kBM - 1) / kBM) * n_tiles;
 
@@ -310,22 +319,22 @@ __global__ void __launch_bounds__((A4 || B4) ? 192 + kUnpackThreads : 192, 1)
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&tmem_full[b], 1);
-      mbar_init(&tmem_empty[b], 128);
+      mbar_init(&tmem_empty[b], kEpiThreads);
     }
     mbar_init(fix_bar, 1);
     *abort_flag = 0u;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     tma_prefetch_desc(&tma_a);
     tma_prefetch_desc(&tma_b);
-    if (p.tma_store) tma_prefetch_desc(&tma_out);
+    if (p.staged) tma_prefetch_desc(&tma_out);
   }
-  if (warp == 1) tmem_alloc(tmem_slot, kTmemCols);
+  if (warp == kMmaWarp) tmem_alloc(tmem_slot, kTmemCols);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  if (warp == 0) {
+  if (warp == kProducerWarp) {
     if (lane == 0) {
       constexpr uint32_t kTx = (A4 ? L::kRawA : L::kA) + (B4 ? L::kRawB : L::kB);
       uint32_t g = 0;  // k-block counter across tiles: ring slot g % STAGES, phase (g / STAGES) & 1
@@ -347,7 +356,7 @@ __global__ void __launch_bounds__((A4 || B4) ? 192 + kUnpackThreads : 192, 1)
         }
       }
     }
-  } else if (warp == 1) {
+  } else if (warp == kMmaWarp) {
     if (lane == 0) {
       constexpr uint32_t idesc = instr_desc_i8(BN);
       uint32_t g = 0, it = 0;
@@ -376,9 +385,13 @@ __global__ void __launch_bounds__((A4 || B4) ? 192 + kUnpackThreads : 192, 1)
         if (ok) umma_commit(&tmem_full[buf]);
       }
     }
-  } else if (warp < 6) {
-    // ---- epilogue warps ----
+  } else if (warp < kEpiThreads / 32) {
+    // ---- epilogue warps: team 0 takes the even output boxes of a tile, team 1 the odd ones ----
+    // With the unpack warps in the CTA every thread starts with few registers; the unpack warp groups
+    // give some back and the two epilogue warp groups take them.
+    if (kUnpack) asm volatile("setmaxnreg.inc.sync.aligned.u32 152;" ::: "memory");
     const int q = warp & 3;  // tensor-memory lane quarter this warp may read
+    const int team = warp >> 2;
     const bool raw = p.out_dtype == HOT_I32;  // raw accumulators: no scales to read
     const float sb0 = (p.sb_row || raw) ? 0.0f : p.sb[0];
     __shared__ uint32_t s_finisher;
@@ -386,62 +399,96 @@ __global__ void __launch_bounds__((A4 || B4) ? 192 + kUnpackThreads : 192, 1)
     bool ok = true;
     SegmentIter iter(p, num_tiles);
     Segment seg;
-    // Output path: each warp lays its 32 rows x 128 bytes out in a swizzled shared-memory box and one
-    // lane hands the box to a bulk tensor store (full 128-byte lines; rows and columns past the
-    // matrix are clipped by the copy engine).  A bf16 box takes two 32-column chunks.
-    uint8_t* const store_stage = smem + L::kOffStore + q * 8192;
-    const bool out16 = p.out_dtype == HOT_BF16;
+    // Output path: a thread holds one row of the accumulator, so stores from registers would touch 32
+    // lines per instruction.  Instead each warp lays 32 rows x 64 bytes out in a swizzled shared-memory
+    // box (two boxes per warp, so that a bulk tensor store is in flight while the next box fills) and
+    // one lane hands it to the copy engine, which clips rows and columns past the matrix.
+    uint8_t* const store_stage = smem + L::kOffStore + warp * 4096;
     uint32_t boxes = 0;  // boxes filled by this warp so far (selects the buffer)
+    const bool out16 = p.out_dtype == HOT_BF16;
+    auto owns = [&](int c) { return (c & 1) == team; };  // chunk c is this team's
     int m0 = 0, n0 = 0, row = 0;
     bool row_ok = false;
     float sa = 0.0f;
-    auto emit = [&](int c, const uint32_t (&acc)[32]) {  // chunk c (32 columns) of the current tile, ascending
-      if (!p.tma_store) {
+    // chunk c (32 columns) of the current tile, ascending; acc = accumulators before the INT4 shift
+    auto emit = [&](int c, uint32_t (&acc)[32]) {
+      if (!p.staged) {
+        if (kShift) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) acc[i] = (uint32_t)((int)acc[i] >> kShift);
+        }
         store_chunk(p, row, row_ok, n0 + c * 32, acc, sa, sb0);
         return;
       }
       const int col0 = n0 + c * 32;
-      uint8_t* box = store_stage + (boxes & 1u) * 4096 + lane * 128;
-      const bool opens = !out16 || !(c & 1), closes = !out16 || (c & 1);
-      if (opens) {
+      const float2 sa2 = make_float2(sa, sa), sb2 = make_float2(sb0, sb0), post2 = make_float2(p.post, p.post);
+      // four 16-byte pieces of this lane's row of a box: the piece index is swizzled like the tensor map
+      auto put = [&](uint8_t* box, int j, uint4 v) {
+        *reinterpret_cast<uint4*>(box + lane * 64 + ((j ^ ((lane >> 1) & 3)) << 4)) = v;
+      };
+      auto open_box = [&]() -> uint8_t* {
         if (lane == 0) bulk_wait_group_read<1>();  // the store that last read this buffer is done with it
         __syncwarp();
-      }
-
-      if (out16) {
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          uint32_t w[4];
-#pragma unroll
-          for (int k = 0; k < 4; ++k) {
-            const int i = 8 * j + 2 * k;
-            __nv_bfloat162 t = __floats2bfloat162_rn(dequant(p, acc[i], col0 + i, sa, sb0), dequant(p, acc[i + 1], col0 + i + 1, sa, sb0));
-            w[k] = *reinterpret_cast<uint32_t*>(&t);
-          }
-          *reinterpret_cast<uint4*>(box + ((((c & 1) * 4 + j) ^ (lane & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
-        }
-      } else if (raw) {
-#pragma unroll
-        for (int j = 0; j < 8; ++j)
-          *reinterpret_cast<uint4*>(box + ((j ^ (lane & 7)) << 4)) = make_uint4(acc[4 * j], acc[4 * j + 1], acc[4 * j + 2], acc[4 * j + 3]);
-      } else {
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          uint32_t w[4];
-#pragma unroll
-          for (int k = 0; k < 4; ++k) w[k] = __float_as_uint(dequant(p, acc[4 * j + k], col0 + 4 * j + k, sa, sb0));
-          *reinterpret_cast<uint4*>(box + ((j ^ (lane & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
-        }
-      }
-      if (closes) {
+        return store_stage + (boxes & 1u) * 2048;
+      };
+      auto close_box = [&](uint8_t* box, int col) {  // col: first column of the box
         fence_proxy_async_smem();
         __syncwarp();
         if (lane == 0) {
-          const int col = n0 + (out16 ? (c & ~1) : c) * 32, y = m0 + q * 32;
+          const int y = m0 + q * 32;
           if (col < p.N && y < p.M) tma_store_2d(&tma_out, box, col << (out16 ? 1 : 2), y);
           bulk_commit_group();  // always: the buffer rotation counts groups
         }
         ++boxes;
+      };
+      auto fill = [&](auto sb_row) {  // one instance per scale layout, so the choice is not made per element
+        constexpr bool kSbRow = decltype(sb_row)::value;
+        if (out16) {
+          uint8_t* box = open_box();
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            uint32_t w[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+              const int i = 8 * j + 2 * k;
+              const float2 f = dequant2<kShift, kSbRow>(p, acc[i], acc[i + 1], col0 + i, sa2, sb2, post2);
+              __nv_bfloat162 t = __floats2bfloat162_rn(f.x, f.y);
+              w[k] = *reinterpret_cast<uint32_t*>(&t);
+            }
+            put(box, j, make_uint4(w[0], w[1], w[2], w[3]));
+          }
+          close_box(box, col0);
+        } else {
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            uint8_t* box = open_box();
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const int i = 16 * h + 4 * j;
+              const float2 f0 = dequant2<kShift, kSbRow>(p, acc[i], acc[i + 1], col0 + i, sa2, sb2, post2);
+              const float2 f1 = dequant2<kShift, kSbRow>(p, acc[i + 2], acc[i + 3], col0 + i + 2, sa2, sb2, post2);
+              put(box, j, make_uint4(__float_as_uint(f0.x), __float_as_uint(f0.y), __float_as_uint(f1.x), __float_as_uint(f1.y)));
+            }
+            close_box(box, col0 + 16 * h);
+          }
+        }
+      };
+      if (raw) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          uint8_t* box = open_box();
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const int i = 16 * h + 4 * j;
+            put(box, j, make_uint4((uint32_t)((int)acc[i] >> kShift), (uint32_t)((int)acc[i + 1] >> kShift),
+                                   (uint32_t)((int)acc[i + 2] >> kShift), (uint32_t)((int)acc[i + 3] >> kShift)));
+          }
+          close_box(box, col0 + 16 * h);
+        }
+      } else if (p.sb_row) {
+        fill(std::true_type{});
+      } else {
+        fill(std::false_type{});
       }
     };
     for (; ok && iter.next(seg); ++it) {
@@ -459,22 +506,25 @@ __global__ void __launch_bounds__((A4 || B4) ? 192 + kUnpackThreads : 192, 1)
       if (!ok) break;
       tc_fence_after();
       const uint32_t t_addr = tmem_base + buf * kBufStride + ((uint32_t)(q * 32) << 16);
+      int c_last = BN / 32 - 1;  // last chunk this team reads
+      while (c_last >= 0 && !owns(c_last)) --c_last;
+      if (c_last < 0) {
+        tc_fence_before();
+        mbar_arrive(&tmem_empty[buf]);
+      }
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
+      for (int c = 0; c <= c_last; ++c) {
+        if (!owns(c)) continue;
         uint32_t acc[32];
         tmem_ld32(t_addr + (uint32_t)(c * 32), acc);
-        if (c == BN / 32 - 1) {  // everything of this buffer is in registers: hand it back
+        if (c == c_last) {  // everything this thread needs of the buffer is in registers: hand it back
           tc_fence_before();
           mbar_arrive(&tmem_empty[buf]);
-        }
-        if (kShift) {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) acc[i] = (uint32_t)((int)acc[i] >> kShift);
         }
         if (whole) {
           emit(c, acc);
         } else {
-          // partial sum of a tile shared with other CTAs: park the raw accumulators
+          // partial sum of a tile shared with other CTAs: park the accumulators as they are
 #pragma unroll
           for (int i = 0; i < 32; i += 4)
             *reinterpret_cast<int4*>(my_slot + c * (32 * kBM) + (i >> 2) * (4 * kBM)) =
@@ -486,14 +536,14 @@ __global__ void __launch_bounds__((A4 || B4) ? 192 + kUnpackThreads : 192, 1)
         // every contributor's partial (its own included) and writes the tile
         asm volatile("fence.proxy.async.global;" ::: "memory");  // the finisher may read it with bulk copies
         __threadfence();
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-        if (threadIdx.x == 64) {
+        asm volatile("bar.sync 1, 256;" ::: "memory");
+        if (threadIdx.x == 0) {
           const uint32_t mine = (uint32_t)(seg.kb1 - seg.kb0);
           const uint32_t before = atomicAdd(p.sk_counters + seg.tile, mine);
           s_finisher = (before + mine == (uint32_t)p.num_kb) ? 1u : 0u;
           if (s_finisher) p.sk_counters[seg.tile] = 0u;  // leave the counters as they were found
         }
-        asm volatile("bar.sync 1, 128;" ::: "memory");
+        asm volatile("bar.sync 1, 256;" ::: "memory");
         if (s_finisher) {
           __threadfence();
           const long long total = (long long)num_tiles * p.num_kb;
@@ -517,8 +567,8 @@ __global__ void __launch_bounds__((A4 || B4) ? 192 + kUnpackThreads : 192, 1)
             uint32_t fph = 0;
             for (int c0 = 0; c0 < BN / 32; c0 += group) {
               const int ng = (BN / 32 - c0) < group ? (BN / 32 - c0) : group;
-              asm volatile("bar.sync 1, 128;" ::: "memory");  // the previous group has been read
-              if (threadIdx.x == 64) {
+              asm volatile("bar.sync 1, 256;" ::: "memory");  // the previous group has been read
+              if (threadIdx.x == 0) {
                 asm volatile("fence.proxy.async;" ::: "memory");
                 mbar_expect_tx(fix_bar, (uint32_t)(ncontrib * ng * 32 * kBM * 4));
                 for (int k = 0; k < ncontrib; ++k)
@@ -528,6 +578,7 @@ __global__ void __launch_bounds__((A4 || B4) ? 192 + kUnpackThreads : 192, 1)
               if (!mbar_wait(fix_bar, fph, abort_flag)) break;
               fph ^= 1u;
               for (int g = 0; g < ng; ++g) {
+                if (!owns(c0 + g)) continue;
                 int sum[32];
 #pragma unroll
                 for (int i = 0; i < 32; ++i) sum[i] = 0;
@@ -548,6 +599,7 @@ __global__ void __launch_bounds__((A4 || B4) ? 192 + kUnpackThreads : 192, 1)
           } else {
 #pragma unroll 1
             for (int c = 0; c < BN / 32; ++c) {
+              if (!owns(c)) continue;
               int sum[32];
 #pragma unroll
               for (int i = 0; i < 32; ++i) sum[i] = 0;
@@ -566,13 +618,14 @@ __global__ void __launch_bounds__((A4 || B4) ? 192 + kUnpackThreads : 192, 1)
             }
           }
         }
-        asm volatile("bar.sync 1, 128;" ::: "memory");  // s_finisher is reused by the next segment
+        asm volatile("bar.sync 1, 256;" ::: "memory");  // s_finisher is reused by the next segment
       }
     }
     if (lane == 0) bulk_wait_group<0>();  // the staged boxes have left shared memory and are written
-  } else if (kUnpack) {
+  } else if (kUnpack && warp < kProducerWarp) {
     // ---- unpack warps (INT4 operands): raw stage -> swizzled int8 stage ----
-    const int utid = threadIdx.x - 192;
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 40;" ::: "memory");
+    const int utid = threadIdx.x - kEpiThreads;
     uint32_t g = 0;
     bool ok = true;
     SegmentIter iter(p, num_tiles);
@@ -593,7 +646,7 @@ __global__ void __launch_bounds__((A4 || B4) ? 192 + kUnpackThreads : 192, 1)
 
   tc_fence_before();
   __syncthreads();
-  if (warp == 1) {
+  if (warp == kMmaWarp) {
     tc_fence_after();
     tmem_dealloc(tmem_base, kTmemCols);
   }
@@ -619,28 +672,35 @@ int launch_gemm(const void* a, int64_t lda, const void* b, int64_t ldb, const Ge
   using L = SmemLayout<BN, A4, B4>;
   CUtensorMap ma, mb;
   int rc;
-  if (A4) rc = make_map(&ma, a, p.M, (p.K + 1) / 2, lda, kBK / 2, kBM, false);
-  else rc = make_map(&ma, a, p.M, p.K, lda, kBK, kBM, true);
+  if (A4) rc = make_map(&ma, a, p.M, (p.K + 1) / 2, lda, kBK / 2, kBM, 0);
+  else rc = make_map(&ma, a, p.M, p.K, lda, kBK, kBM, 128);
   if (rc) return rc;
-  if (B4) rc = make_map(&mb, b, p.N, (p.K + 1) / 2, ldb, kBK / 2, BN, false);
-  else rc = make_map(&mb, b, p.N, p.K, ldb, kBK, BN, true);
+  if (B4) rc = make_map(&mb, b, p.N, (p.K + 1) / 2, ldb, kBK / 2, BN, 0);
+  else rc = make_map(&mb, b, p.N, p.K, ldb, kBK, BN, 128);
   if (rc) return rc;
   // output as a byte matrix for the bulk tensor stores; otherwise the epilogue stores from registers
   const int64_t esz = p.out_dtype == HOT_BF16 ? 2 : 4;
   GemmParams pp = p;
-  pp.tma_store = (reinterpret_cast<uintptr_t>(p.out) % 16 == 0 && (p.ldo * esz) % 16 == 0) ? 1 : 0;
+  pp.staged = (reinterpret_cast<uintptr_t>(p.out) % 16 == 0 && (p.ldo * esz) % 16 == 0) ? 1 : 0;
   CUtensorMap mo = ma;
-  if (pp.tma_store) {
-    rc = make_map(&mo, p.out, p.M, (int64_t)p.N * esz, p.ldo * esz, 128, 32, true);
+  if (pp.staged) {
+    rc = make_map(&mo, p.out, p.M, (int64_t)p.N * esz, p.ldo * esz, 64, 32, 64);
     if (rc) return rc;
   }
   auto kernel = gemm_i8_kernel<BN, A4, B4>;
   static bool attr_set = false;  // per instantiation
   if (!attr_set) {
     HOT_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kBytes));
+    if (A4 || B4) {
+      // the register hand-over (unpack warp groups 96 -> 40, epilogue warp groups 96 -> 152) only balances
+      // when the kernel starts with at least 96 registers per thread
+      cudaFuncAttributes fa;
+      HOT_CUDA(cudaFuncGetAttributes(&fa, kernel));
+      if (fa.numRegs < 96) HOT_FAIL(HOT_ERR_UNSUPPORTED, "gemm_i8: kernel built with %d registers per thread, 96 expected", fa.numRegs);
+    }
     attr_set = true;
   }
-  kernel<<<plan.grid, (A4 || B4) ? 192 + kUnpackThreads : 192, L::kBytes, st>>>(ma, mb, mo, pp);
+  kernel<<<plan.grid, kEpiThreads + 64 + ((A4 || B4) ? kUnpackThreads : 0), L::kBytes, st>>>(ma, mb, mo, pp);
   HOT_CUDA(cudaGetLastError());
   return HOT_OK;
 }
@@ -654,7 +714,9 @@ inline size_t sk_bytes(int sms, int bn, int64_t tiles) {
 // mildly with the tile width (~ bn + 400), so what counts is how many k-blocks the busiest CTA
 // runs: whole tiles in waves, or (given a workspace) equal shares of all k-blocks with the cut
 // tiles summed up by their last contributor (it reads every contributor's 128 x bn int32 partial
-// through bulk copies into the idle operand ring), charged below in k-block equivalents.
+// through bulk copies into the idle operand ring).  Measured, that costs ~14 us + ~3.5 us per
+// contributor at bn = 256, charged below in k-block equivalents, so stream-K is picked only for
+// few-tile, very-long-K problems.
 Plan make_plan(int M, int N, int num_kb, int sms, size_t ws_bytes) {
   const int cands[4] = {256, 192, 128, 64};
   Plan best{128, false, 1};
@@ -675,7 +737,7 @@ Plan make_plan(int M, int N, int num_kb, int sms, size_t ws_bytes) {
     if (ws_bytes >= sk_bytes(sms, bn, tiles) && units >= 2 * (int64_t)sms && tiles % sms != 0) {
       const double share = (double)units / sms;
       const double contributors = 1.0 + (double)num_kb / share;
-      const double sk = (share + (6.0 + 4.0 * contributors) * bn / 256.0) * per_kb;
+      const double sk = (share + (32.0 + 8.0 * contributors) * bn / 256.0) * per_kb;
       if (sk < best_cost || (force_sk && !best.stream_k)) {
         best_cost = force_sk ? 0.0 : sk;
         best = Plan{bn, true, (unsigned)sms};

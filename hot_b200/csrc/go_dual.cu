@@ -345,7 +345,7 @@ int launch_pass(const CUtensorMap& tmap, const DualParams& p, int grid, cudaStre
 template <typename T>
 int launch_dual(const void* go, int64_t ldgo, const DualParams& p, int rx, int rw, int sms, cudaStream_t st) {
   CUtensorMap tmap;
-  if (int rc = make_map(&tmap, go, p.L, (int64_t)p.O * sizeof(T), ldgo * (int64_t)sizeof(T), Tile<T>::kRowBytes, kTT, false))
+  if (int rc = make_map(&tmap, go, p.L, (int64_t)p.O * sizeof(T), ldgo * (int64_t)sizeof(T), Tile<T>::kRowBytes, kTT, 0))
     return rc;
   const int num_tiles = (p.O / kTC) * (int)((p.L + kTT - 1) / kTT);
   const int per_sm = sizeof(T) == 2 ? 3 : 1;  // resident CTAs per SM by shared memory (75 KB / 140 KB each)

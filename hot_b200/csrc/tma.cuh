@@ -10,7 +10,7 @@ namespace hot {
 
 // Tensor map over a [rows, row_bytes] byte matrix with pitch ld, box = box_bytes x box_rows.
 int make_map(CUtensorMap* map, const void* base, int64_t rows, int64_t row_bytes, int64_t ld, int box_bytes,
-             int box_rows, bool swizzle128);
+             int box_rows, int swizzle_bytes);  // swizzle_bytes: 0, 64 or 128
 
 #ifdef __CUDACC__
 
