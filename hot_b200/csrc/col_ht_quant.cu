@@ -27,6 +27,9 @@ struct ColParams {
   int scale_row, store4, noise_transposed;
   int sawb;                   // clip from the second moment and the mean magnitude instead of the abs-max
   signed char pos[64];        // pos[k] = output slot of natural row k, or -1
+  // batched call (blockIdx.z = sample; rows / out_len are per sample, one scale per sample):
+  int batch;                  // 1 in a plain call
+  int64_t sample_pitch;       // bytes from one sample's codes to the next within an output row; 0 in a plain call
 };
 
 template <typename T>
@@ -96,6 +99,8 @@ __global__ void __launch_bounds__(kThreads) col_ht_absmax_kernel(const T* __rest
   constexpr int CPL = ColTraits<T>::kCpl;
   constexpr int CC = 32 * VEC * CPL;
   __shared__ uint32_t s_max[CC];
+  x += (int64_t)blockIdx.z * p.rows * p.ldx;
+  absmax += blockIdx.z;  // batched calls take one abs-max word per sample
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int c0 = blockIdx.x * CC;
   const int64_t nblk = p.rows / N;
@@ -182,6 +187,12 @@ __global__ void __launch_bounds__(kThreads) col_ht_quant_kernel(const T* __restr
   constexpr int CPL = ColTraits<T>::kCpl;
   constexpr int CC = 32 * VEC * CPL;
   extern __shared__ __align__(16) float tile[];  // [CC][pitch]
+  x += (int64_t)blockIdx.z * p.rows * p.ldx;
+  codes += (int64_t)blockIdx.z * p.sample_pitch;
+  absmax += blockIdx.z;
+  scales += blockIdx.z;
+  // the noise / Philox element index runs on from sample to sample
+  const uint64_t e_base = (uint64_t)blockIdx.z * (uint64_t)p.out_len * (uint64_t)p.cols;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int c0 = blockIdx.x * CC;
   const int64_t nblk = p.rows / N;
@@ -275,7 +286,7 @@ __global__ void __launch_bounds__(kThreads) col_ht_quant_kernel(const T* __restr
     int code[8];
     if (ROUND == HOT_ROUND_STOCH_PHILOX) {
       // random byte of stored-layout element e: byte e % 16 of Philox block e / 16
-      const uint64_t e0 = (uint64_t)c * (uint64_t)p.out_len + (uint64_t)l0;
+      const uint64_t e0 = e_base + (uint64_t)c * (uint64_t)p.out_len + (uint64_t)l0;
       if ((e0 & 7u) == 0) {
         // aligned run: its 8 random bytes are one half of a Philox block
         const uint4 blk = philox_block16(q, e0 >> 4);
@@ -309,7 +320,7 @@ __global__ void __launch_bounds__(kThreads) col_ht_quant_kernel(const T* __restr
         if (ROUND == HOT_ROUND_STOCH_NOISE) {
           const int64_t l = l0 + i;
           if (l < p.out_len)
-            un = p.noise_transposed ? q.noise[(int64_t)c * p.out_len + l] : q.noise[l * (int64_t)p.cols + c];
+            un = p.noise_transposed ? q.noise[e_base + (int64_t)c * p.out_len + l] : q.noise[e_base + l * (int64_t)p.cols + c];
         }
         u[i] = un;
       }
@@ -331,6 +342,15 @@ __global__ void __launch_bounds__(kThreads) col_ht_quant_kernel(const T* __restr
       *reinterpret_cast<uint2*>(codes + (int64_t)c * p.ld_codes + l0) = make_uint2(w0, w1);
     }
   }
+  // batched: a sample's codes are padded with zeros up to the next sample (the GEMM contracts over them)
+  if (p.sample_pitch > 0 && blk0 + p.nb >= nblk) {
+    const int64_t from = (p.out_len + 7) & ~(int64_t)7;
+    const int chunks = (int)((p.sample_pitch - from) >> 3);
+    for (int item = threadIdx.x; item < CC * chunks; item += kThreads) {
+      const int cl = item / chunks, ch = item - cl * chunks;
+      if (c0 + cl < p.cols) *reinterpret_cast<uint2*>(codes + (int64_t)(c0 + cl) * p.ld_codes + from + ch * 8) = make_uint2(0u, 0u);
+    }
+  }
 }
 
 template <typename T, int N>
@@ -340,9 +360,9 @@ int launch_n(const T* x, const ColParams& p, const hot_quant_t& hq, uint8_t* cod
   constexpr int CC = 32 * VEC * ColTraits<T>::kCpl;
   const QuantDev q = make_quant_dev(hq);
   const int64_t nblk = p.rows / N;
-  dim3 grid((unsigned)((p.cols + CC - 1) / CC), (unsigned)((nblk + p.nb - 1) / p.nb));
+  dim3 grid((unsigned)((p.cols + CC - 1) / CC), (unsigned)((nblk + p.nb - 1) / p.nb), (unsigned)p.batch);
   const size_t smem = (size_t)CC * p.pitch * sizeof(float);
-  if (!p.sawb) HOT_CUDA(cudaMemsetAsync(ws, 0, sizeof(uint32_t) * (p.scale_row ? p.cols : 1), st));
+  if (!p.sawb) HOT_CUDA(cudaMemsetAsync(ws, 0, sizeof(uint32_t) * (p.scale_row ? p.cols : p.batch), st));
   col_ht_absmax_kernel<T, N><<<grid, kThreads, 0, st>>>(x, p, ws);
   auto launch = [&](auto kernel) -> int {
     HOT_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
@@ -402,10 +422,12 @@ extern "C" size_t hot_col_ht_quant_scratch_words(int dtype, int64_t rows, int64_
   return 4 * (size_t)((cols + cc - 1) / cc) * (size_t)((nblk + nb - 1) / nb) + 4;  // two doubles per CTA
 }
 
-extern "C" int hot_col_ht_quant(const void* x, int dtype, int64_t rows, int64_t cols, int64_t ldx, int order,
-                                const int32_t* sel, int r, const hot_quant_t* q, int logical_layout, void* codes_t,
-                                int64_t ld_codes, float* scales, uint32_t* absmax_ws, hot_stream_t stream) {
-  using namespace hot;
+namespace hot {
+namespace {
+// batch > 1: x holds `batch` samples of `rows` rows each; sample b's codes start sample_pitch * b bytes into each output row
+int col_ht_quant_impl(const void* x, int dtype, int64_t rows, int64_t cols, int64_t ldx, int order, const int32_t* sel, int r,
+                      const hot_quant_t* q, int logical_layout, void* codes_t, int64_t ld_codes, float* scales,
+                      uint32_t* absmax_ws, hot_stream_t stream, int batch, int64_t sample_pitch) {
   if (!x || !q || !codes_t || !scales || !sel || !absmax_ws) HOT_FAIL(HOT_ERR_ARG, "hot_col_ht_quant: null pointer");
   if (rows < 0 || cols <= 0 || cols > (1 << 30)) HOT_FAIL(HOT_ERR_ARG, "hot_col_ht_quant: bad shape");
   if (int rc = validate_quant(q, "hot_col_ht_quant")) return rc;
@@ -431,6 +453,8 @@ extern "C" int hot_col_ht_quant(const void* x, int dtype, int64_t rows, int64_t 
   if (p.sawb && ((uintptr_t)absmax_ws) % 8 != 0) HOT_FAIL(HOT_ERR_ARG, "hot_col_ht_quant: scratch must be 8-byte aligned for HOT_SCALE_SAWB");
   p.store4 = q->storage == HOT_STORE_INT4;
   p.noise_transposed = logical_layout == HOT_LAYOUT_TRANSPOSED;
+  p.batch = batch;
+  p.sample_pitch = sample_pitch;
   for (int k = 0; k < 64; ++k) p.pos[k] = -1;
   for (int j = 0; j < r; ++j) {
     if (sel[j] < 0 || sel[j] >= order || p.pos[sel[j]] >= 0)
@@ -443,6 +467,13 @@ extern "C" int hot_col_ht_quant(const void* x, int dtype, int64_t rows, int64_t 
   p.nb = nb;
   p.pitch = ((nb * r + 31) / 32) * 32 + 4;
   const int64_t row_bytes = p.store4 ? (p.out_len + 1) / 2 : p.out_len;
+  if (sample_pitch > 0) {
+    if (p.scale_row || p.sawb || p.store4)
+      HOT_FAIL(HOT_ERR_UNSUPPORTED, "hot_col_ht_quant_batched: HOT_SCALE_TENSOR (one scale per sample) and HOT_STORE_INT8 only");
+    if (sample_pitch % 16 != 0 || sample_pitch < ((row_bytes + 7) / 8) * 8 || ld_codes < sample_pitch * batch)
+      HOT_FAIL(HOT_ERR_ARG, "hot_col_ht_quant_batched: sample pitch %lld must be a multiple of 16, >= %lld, and fit the row pitch",
+               (long long)sample_pitch, (long long)row_bytes);
+  }
   if (ld_codes % 16 != 0 || ld_codes < ((row_bytes + 7) / 8) * 8 || ((uintptr_t)codes_t) % 16 != 0)
     HOT_FAIL(HOT_ERR_ARG, "hot_col_ht_quant: codes pitch %lld must be a multiple of 16 and >= %lld", (long long)ld_codes,
              (long long)row_bytes);
@@ -450,6 +481,26 @@ extern "C" int hot_col_ht_quant(const void* x, int dtype, int64_t rows, int64_t 
   cudaStream_t st = (cudaStream_t)stream;
   if (dtype == HOT_F32) return launch_t<float>((const float*)x, order, p, *q, (uint8_t*)codes_t, scales, absmax_ws, st);
   return launch_t<__nv_bfloat16>((const __nv_bfloat16*)x, order, p, *q, (uint8_t*)codes_t, scales, absmax_ws, st);
+}
+}  // namespace
+}  // namespace hot
+
+extern "C" int hot_col_ht_quant(const void* x, int dtype, int64_t rows, int64_t cols, int64_t ldx, int order,
+                                const int32_t* sel, int r, const hot_quant_t* q, int logical_layout, void* codes_t,
+                                int64_t ld_codes, float* scales, uint32_t* absmax_ws, hot_stream_t stream) {
+  return hot::col_ht_quant_impl(x, dtype, rows, cols, ldx, order, sel, r, q, logical_layout, codes_t, ld_codes, scales,
+                                absmax_ws, stream, 1, 0);
+}
+
+extern "C" int hot_col_ht_quant_batched(const void* x, int dtype, int64_t batch, int64_t rows, int64_t cols, int64_t ldx,
+                                        int order, const int32_t* sel, int r, const hot_quant_t* q, int logical_layout,
+                                        void* codes_t, int64_t ld_codes, int64_t sample_pitch, float* scales,
+                                        uint32_t* absmax_ws, hot_stream_t stream) {
+  using namespace hot;
+  if (batch < 1 || batch > 65535) HOT_FAIL(HOT_ERR_ARG, "hot_col_ht_quant_batched: batch %lld outside [1, 65535]", (long long)batch);
+  if (sample_pitch <= 0) HOT_FAIL(HOT_ERR_ARG, "hot_col_ht_quant_batched: sample pitch must be positive");
+  return col_ht_quant_impl(x, dtype, rows, cols, ldx, order, sel, r, q, logical_layout, codes_t, ld_codes, scales,
+                           absmax_ws, stream, (int)batch, sample_pitch);
 }
 
 // ---------------------------------------------------------------------------------------

@@ -34,7 +34,12 @@ struct GemmParams {
   int M, N, K, num_kb;
   const float* sa;
   const float* sb;
-  int sa_row, sb_row;
+  int sa_row, sb_row;  // 0: one scale; sa_row = k >= 1: one scale per k consecutive rows of A; sb_row: per row of B
+  // grouped: the K axis is cut into groups of group_kb k-blocks with one scale pair each (a batch of
+  // samples laid side by side along K); out = sum_g ((float)acc_g * ga[g]) * gb[g], then * post
+  int group_kb;
+  const float* ga;
+  const float* gb;
   float post;
   void* out;
   int64_t ldo;
@@ -51,6 +56,7 @@ struct GemmParams {
 // One stretch of k-blocks of one output tile.
 struct Segment {
   int tile, kb0, kb1;
+  int group;   // grouped mode: which group of the K axis
   bool first;  // first segment of this CTA (selects the partial slot)
 };
 
@@ -60,12 +66,15 @@ struct Segment {
 struct SegmentIter {
   bool stream_k, first;
   int tile, stride, num_tiles, num_kb;
+  int group_kb, grp;
   long long u, end;
   __device__ SegmentIter(const GemmParams& p, int num_tiles_) {
     stream_k = p.stream_k != 0;
     first = true;
     num_tiles = num_tiles_;
     num_kb = p.num_kb;
+    group_kb = p.group_kb;
+    grp = 0;
     tile = blockIdx.x;
     stride = gridDim.x;
     const long long total = (long long)num_tiles * num_kb;
@@ -76,6 +85,21 @@ struct SegmentIter {
   __device__ bool next(Segment& s) {
     s.first = first;
     first = false;
+    s.group = 0;
+    if (group_kb) {  // one segment per (tile, group)
+      if (tile >= num_tiles) return false;
+      s.tile = tile;
+      s.group = grp;
+      s.kb0 = grp * group_kb;
+      s.kb1 = s.kb0 + group_kb;
+      if (s.kb1 >= num_kb) {
+        grp = 0;
+        tile += stride;
+      } else {
+        ++grp;
+      }
+      return true;
+    }
     if (!stream_k) {
       if (tile >= num_tiles) return false;
       s.tile = tile;
@@ -290,6 +314,7 @@ __global__ void __launch_bounds__(kEpiThreads + 64 + ((A4 || B4) ? kUnpackThread
   constexpr uint32_t kTmemCols = tmem_cols(BN);
   constexpr uint32_t kBufStride = kTmemCols / 2;
   constexpr int kShift = (A4 ? 4 : 0) + (B4 ? 4 : 0);
+  constexpr bool kGrouped = BN == 128 && !kUnpack;  // the one instance that carries the grouped-scale epilogue
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   uint8_t* sA = smem + L::kOffA;
@@ -393,7 +418,7 @@ __global__ void __launch_bounds__(kEpiThreads + 64 + ((A4 || B4) ? kUnpackThread
     const int q = warp & 3;  // tensor-memory lane quarter this warp may read
     const int team = warp >> 2;
     const bool raw = p.out_dtype == HOT_I32;  // raw accumulators: no scales to read
-    const float sb0 = (p.sb_row || raw) ? 0.0f : p.sb[0];
+    const float sb0 = (p.sb_row || raw || p.group_kb) ? 0.0f : p.sb[0];
     __shared__ uint32_t s_finisher;
     uint32_t it = 0;
     bool ok = true;
@@ -405,11 +430,60 @@ __global__ void __launch_bounds__(kEpiThreads + 64 + ((A4 || B4) ? kUnpackThread
     // one lane hands it to the copy engine, which clips rows and columns past the matrix.
     uint8_t* const store_stage = smem + L::kOffStore + warp * 4096;
     uint32_t boxes = 0;  // boxes filled by this warp so far (selects the buffer)
+    float run[kGrouped ? BN / 64 : 1][32];  // grouped mode only
     const bool out16 = p.out_dtype == HOT_BF16;
     auto owns = [&](int c) { return (c & 1) == team; };  // chunk c is this team's
     int m0 = 0, n0 = 0, row = 0;
     bool row_ok = false;
     float sa = 0.0f;
+    // four 16-byte pieces of this lane's row of a box: the piece index is swizzled like the tensor map
+    auto put = [&](uint8_t* box, int j, uint4 v) {
+      *reinterpret_cast<uint4*>(box + lane * 64 + ((j ^ ((lane >> 1) & 3)) << 4)) = v;
+    };
+    auto open_box = [&]() -> uint8_t* {
+      if (lane == 0) bulk_wait_group_read<1>();  // the store that last read this buffer is done with it
+      __syncwarp();
+      return store_stage + (boxes & 1u) * 2048;
+    };
+    auto close_box = [&](uint8_t* box, int col) {  // col: first column of the box
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) {
+        const int y = m0 + q * 32;
+        if (col < p.N && y < p.M) tma_store_2d(&tma_out, box, col << (out16 ? 1 : 2), y);
+        bulk_commit_group();  // always: the buffer rotation counts groups
+      }
+      ++boxes;
+    };
+    // 32 finished values of this lane's row, columns col0 .. col0 + 31; val(i) gives columns i, i + 1
+    auto store_pairs = [&](int col0, auto&& val) {
+      if (out16) {
+        uint8_t* box = open_box();
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          uint32_t w[4];
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            const float2 f = val(8 * j + 2 * k);
+            __nv_bfloat162 t = __floats2bfloat162_rn(f.x, f.y);
+            w[k] = *reinterpret_cast<uint32_t*>(&t);
+          }
+          put(box, j, make_uint4(w[0], w[1], w[2], w[3]));
+        }
+        close_box(box, col0);
+      } else {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          uint8_t* box = open_box();
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const float2 f0 = val(16 * h + 4 * j), f1 = val(16 * h + 4 * j + 2);
+            put(box, j, make_uint4(__float_as_uint(f0.x), __float_as_uint(f0.y), __float_as_uint(f1.x), __float_as_uint(f1.y)));
+          }
+          close_box(box, col0 + 16 * h);
+        }
+      }
+    };
     // chunk c (32 columns) of the current tile, ascending; acc = accumulators before the INT4 shift
     auto emit = [&](int c, uint32_t (&acc)[32]) {
       if (!p.staged) {
@@ -422,57 +496,6 @@ __global__ void __launch_bounds__(kEpiThreads + 64 + ((A4 || B4) ? kUnpackThread
       }
       const int col0 = n0 + c * 32;
       const float2 sa2 = make_float2(sa, sa), sb2 = make_float2(sb0, sb0), post2 = make_float2(p.post, p.post);
-      // four 16-byte pieces of this lane's row of a box: the piece index is swizzled like the tensor map
-      auto put = [&](uint8_t* box, int j, uint4 v) {
-        *reinterpret_cast<uint4*>(box + lane * 64 + ((j ^ ((lane >> 1) & 3)) << 4)) = v;
-      };
-      auto open_box = [&]() -> uint8_t* {
-        if (lane == 0) bulk_wait_group_read<1>();  // the store that last read this buffer is done with it
-        __syncwarp();
-        return store_stage + (boxes & 1u) * 2048;
-      };
-      auto close_box = [&](uint8_t* box, int col) {  // col: first column of the box
-        fence_proxy_async_smem();
-        __syncwarp();
-        if (lane == 0) {
-          const int y = m0 + q * 32;
-          if (col < p.N && y < p.M) tma_store_2d(&tma_out, box, col << (out16 ? 1 : 2), y);
-          bulk_commit_group();  // always: the buffer rotation counts groups
-        }
-        ++boxes;
-      };
-      auto fill = [&](auto sb_row) {  // one instance per scale layout, so the choice is not made per element
-        constexpr bool kSbRow = decltype(sb_row)::value;
-        if (out16) {
-          uint8_t* box = open_box();
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            uint32_t w[4];
-#pragma unroll
-            for (int k = 0; k < 4; ++k) {
-              const int i = 8 * j + 2 * k;
-              const float2 f = dequant2<kShift, kSbRow>(p, acc[i], acc[i + 1], col0 + i, sa2, sb2, post2);
-              __nv_bfloat162 t = __floats2bfloat162_rn(f.x, f.y);
-              w[k] = *reinterpret_cast<uint32_t*>(&t);
-            }
-            put(box, j, make_uint4(w[0], w[1], w[2], w[3]));
-          }
-          close_box(box, col0);
-        } else {
-#pragma unroll
-          for (int h = 0; h < 2; ++h) {
-            uint8_t* box = open_box();
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              const int i = 16 * h + 4 * j;
-              const float2 f0 = dequant2<kShift, kSbRow>(p, acc[i], acc[i + 1], col0 + i, sa2, sb2, post2);
-              const float2 f1 = dequant2<kShift, kSbRow>(p, acc[i + 2], acc[i + 3], col0 + i + 2, sa2, sb2, post2);
-              put(box, j, make_uint4(__float_as_uint(f0.x), __float_as_uint(f0.y), __float_as_uint(f1.x), __float_as_uint(f1.y)));
-            }
-            close_box(box, col0 + 16 * h);
-          }
-        }
-      };
       if (raw) {
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
@@ -485,10 +508,10 @@ __global__ void __launch_bounds__(kEpiThreads + 64 + ((A4 || B4) ? kUnpackThread
           }
           close_box(box, col0 + 16 * h);
         }
-      } else if (p.sb_row) {
-        fill(std::true_type{});
+      } else if (p.sb_row) {  // one instance per scale layout, so the choice is not made per element
+        store_pairs(col0, [&](int i) { return dequant2<kShift, true>(p, acc[i], acc[i + 1], col0 + i, sa2, sb2, post2); });
       } else {
-        fill(std::false_type{});
+        store_pairs(col0, [&](int i) { return dequant2<kShift, false>(p, acc[i], acc[i + 1], col0 + i, sa2, sb2, post2); });
       }
     };
     for (; ok && iter.next(seg); ++it) {
@@ -498,7 +521,7 @@ __global__ void __launch_bounds__(kEpiThreads + 64 + ((A4 || B4) ? kUnpackThread
       const int row_loc = q * 32 + lane;
       row = m0 + row_loc;
       row_ok = row < p.M;
-      sa = (row_ok && !raw) ? (p.sa_row ? p.sa[row] : p.sa[0]) : 0.0f;
+      sa = (row_ok && !raw && !p.group_kb) ? (p.sa_row ? p.sa[row / p.sa_row] : p.sa[0]) : 0.0f;
       const bool whole = seg.kb0 == 0 && seg.kb1 == p.num_kb;
       // partial slot: [chunk of 32 columns][group of 4 columns][row][4] int32, so that a warp's rows are contiguous
       int32_t* my_slot = p.sk_partials + (size_t)(2 * blockIdx.x + (seg.first ? 0 : 1)) * kBM * BN + row_loc * 4;
@@ -506,6 +529,31 @@ __global__ void __launch_bounds__(kEpiThreads + 64 + ((A4 || B4) ? kUnpackThread
       if (!ok) break;
       tc_fence_after();
       const uint32_t t_addr = tmem_base + buf * kBufStride + ((uint32_t)(q * 32) << 16);
+      if (kGrouped && p.group_kb) {
+        // running fp32 sums of this team's chunks live in registers across the groups of a tile
+        const float ga = p.ga[seg.group], gb = p.gb[seg.group];
+#pragma unroll
+        for (int k = 0; k < BN / 64; ++k) {
+          uint32_t acc[32];
+          tmem_ld32(t_addr + (uint32_t)((2 * k + team) * 32), acc);
+          if (k == BN / 64 - 1) {
+            tc_fence_before();
+            mbar_arrive(&tmem_empty[buf]);
+          }
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const float v = __fmul_rn(__fmul_rn((float)(int)acc[i], ga), gb);
+            run[k][i] = seg.kb0 == 0 ? v : __fadd_rn(run[k][i], v);
+          }
+        }
+        if (seg.kb1 >= p.num_kb) {
+          const float2 post2 = make_float2(p.post, p.post);
+#pragma unroll
+          for (int k = 0; k < BN / 64; ++k)
+            store_pairs(n0 + (2 * k + team) * 32, [&](int i) { return __fmul2_rn(make_float2(run[k][i], run[k][i + 1]), post2); });
+        }
+        continue;
+      }
       int c_last = BN / 32 - 1;  // last chunk this team reads
       while (c_last >= 0 && !owns(c_last)) --c_last;
       if (c_last < 0) {
@@ -797,8 +845,11 @@ extern "C" int hot_gemm_i8_ws(const void* a, int a_storage, int64_t lda, const v
   p.num_kb = (int)((K + kBK - 1) / kBK);
   p.sa = scale_a;
   p.sb = scale_b;
+  if (scale_a_per_row < 0) HOT_FAIL(HOT_ERR_ARG, "hot_gemm_i8: scale_a_per_row must be 0, 1 or a row count");
   p.sa_row = scale_a_per_row;
-  p.sb_row = scale_b_per_row;
+  p.sb_row = scale_b_per_row ? 1 : 0;
+  p.group_kb = 0;
+  p.ga = p.gb = nullptr;
   p.post = post;
   p.out = out;
   p.ldo = ldo;
@@ -830,4 +881,47 @@ extern "C" int hot_gemm_i8(const void* a, int a_storage, int64_t lda, const void
                            uint32_t* status_word, hot_stream_t stream) {
   return hot_gemm_i8_ws(a, a_storage, lda, b, b_storage, ldb, M, N, K, scale_a, scale_a_per_row, scale_b, scale_b_per_row,
                         post, out, out_dtype, ldo, nullptr, 0, status_word, stream);
+}
+
+extern "C" int hot_gemm_i8_grouped(const void* a, int64_t lda, const void* b, int64_t ldb, int64_t M, int64_t N,
+                                   int64_t groups, int64_t group_k, const float* scale_a, const float* scale_b, float post,
+                                   void* out, int out_dtype, int64_t ldo, uint32_t* status_word, hot_stream_t stream) {
+  using namespace hot;
+  if (!a || !b || !out || !scale_a || !scale_b) HOT_FAIL(HOT_ERR_ARG, "hot_gemm_i8_grouped: null pointer");
+  if (M <= 0 || N <= 0 || groups <= 0 || group_k <= 0 || M > (1 << 30) || N > (1 << 30) || groups * group_k > (1 << 30))
+    HOT_FAIL(HOT_ERR_ARG, "hot_gemm_i8_grouped: bad shape M=%lld N=%lld groups=%lld group_k=%lld", (long long)M, (long long)N,
+             (long long)groups, (long long)group_k);
+  if (group_k % kBK != 0)
+    HOT_FAIL(HOT_ERR_UNSUPPORTED, "hot_gemm_i8_grouped: group_k %lld must be a multiple of %d (pad each group with zero codes)",
+             (long long)group_k, kBK);
+  const int64_t K = groups * group_k;
+  if (lda % 16 || ldb % 16 || lda < K || ldb < K || ((uintptr_t)a) % 16 || ((uintptr_t)b) % 16)
+    HOT_FAIL(HOT_ERR_ARG, "hot_gemm_i8_grouped: operand base and pitch must be 16-byte aligned and cover groups * group_k");
+  if (out_dtype != HOT_F32 && out_dtype != HOT_BF16) HOT_FAIL(HOT_ERR_UNSUPPORTED, "hot_gemm_i8_grouped: out dtype %d", out_dtype);
+  const int osz = out_dtype == HOT_BF16 ? 2 : 4;
+  if (ldo < N || ((uintptr_t)out) % 16 != 0 || (ldo * osz) % 16 != 0)
+    HOT_FAIL(HOT_ERR_ARG, "hot_gemm_i8_grouped: out and its pitch must be 16-byte aligned, ldo >= N");
+  GemmParams p;
+  p.M = (int)M;
+  p.N = (int)N;
+  p.K = (int)K;
+  p.num_kb = (int)(K / kBK);
+  p.sa = p.sb = nullptr;
+  p.sa_row = p.sb_row = 0;
+  p.group_kb = (int)(group_k / kBK);
+  p.ga = scale_a;
+  p.gb = scale_b;
+  p.post = post;
+  p.out = out;
+  p.ldo = ldo;
+  p.out_dtype = out_dtype;
+  p.status = status_word;
+  p.stream_k = 0;
+  p.sk_partials = nullptr;
+  p.sk_counters = nullptr;
+  const int sms = device_sm_count();
+  if (sms <= 0) return HOT_ERR_CUDA;
+  const int64_t tiles = tiles_for(p.M, p.N, 128);
+  const Plan plan{128, false, (unsigned)(tiles < sms ? tiles : sms)};
+  return launch_gemm<128, false, false>(a, lda, b, ldb, p, plan, (cudaStream_t)stream);
 }

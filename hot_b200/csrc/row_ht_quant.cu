@@ -104,6 +104,9 @@ __device__ __forceinline__ void locate(int64_t item, int nrun, int64_t ldx, int6
 template <typename T, bool CONTIG>
 __global__ void __launch_bounds__(kThreads) row_ht_absmax_kernel(const T* __restrict__ x, int64_t rows, int cols,
                                                                  int64_t ldx, int n, uint32_t* __restrict__ absmax) {
+  // blockIdx.y: sample of a batched call (rows = rows per sample, one abs-max word per sample)
+  x += (int64_t)blockIdx.y * rows * ldx;
+  absmax += blockIdx.y;
   const int lane = threadIdx.x & 31;
   const int nrun = cols >> 4;
   const int64_t total = rows * nrun;
@@ -137,9 +140,15 @@ template <typename T, int ROUND, int STORE4, bool CONTIG>
 __global__ void __launch_bounds__(kThreads) row_ht_quant_tensorscale_kernel(
     const T* __restrict__ x, int64_t rows, int cols, int64_t ldx, int n, QuantDev q, uint8_t* __restrict__ codes,
     int64_t ld_codes, float* __restrict__ scales, const uint32_t* __restrict__ absmax) {
+  // blockIdx.y: sample of a batched call; the Philox / noise element index runs on across samples
+  x += (int64_t)blockIdx.y * rows * ldx;
+  codes += (int64_t)blockIdx.y * rows * ld_codes;
+  scales += blockIdx.y;
+  absmax += blockIdx.y;
   const int lane = threadIdx.x & 31;
   const int nrun = cols >> 4;
   const int64_t total = rows * nrun;
+  const uint64_t e_base = (uint64_t)blockIdx.y * (uint64_t)total * 16u;
   const int64_t warp_id = ((int64_t)blockIdx.x * kThreads + threadIdx.x) >> 5;
   const int64_t nwarps = ((int64_t)gridDim.x * kThreads) >> 5;
   const ScalePair sp = scale_from_absmax(__uint_as_float(*absmax), q.qmax);
@@ -164,7 +173,7 @@ __global__ void __launch_bounds__(kThreads) row_ht_quant_tensorscale_kernel(
       butterfly16(v[u], n, lane);
       // logical element index of the run: row * cols + col == item * 16 in either layout
       if (coff[u] >= 0)
-        quantise_store16<ROUND, STORE4>(v[u], sp, q, (uint64_t)(base + u * 32 + lane) * 16u, codes + coff[u]);
+        quantise_store16<ROUND, STORE4>(v[u], sp, q, e_base + (uint64_t)(base + u * 32 + lane) * 16u, codes + coff[u]);
     }
   }
 }
@@ -180,7 +189,7 @@ int grid_for(int64_t total_runs, int device_sms) {
 
 template <typename T, int ROUND, int STORE4>
 int launch_typed(const T* x, int64_t rows, int cols, int64_t ldx, int n, const hot_quant_t& hq, uint8_t* codes,
-                 int64_t ld_codes, float* scales, uint32_t* absmax_ws, cudaStream_t st, int sms) {
+                 int64_t ld_codes, float* scales, uint32_t* absmax_ws, cudaStream_t st, int sms, int batch) {
   const QuantDev q = make_quant_dev(hq);
   if (hq.scale_mode == HOT_SCALE_ROW) {
     const int nrun = cols >> 4;
@@ -199,8 +208,8 @@ int launch_typed(const T* x, int64_t rows, int cols, int64_t ldx, int n, const h
     else
       row_ht_quant_rowscale_kernel<T, ROUND, STORE4, 4><<<grid, kThreads, 0, st>>>(x, rows, cols, ldx, n, q, codes, ld_codes, scales, tpr);
   } else {
-    const int grid = grid_for(rows * (cols >> 4), sms);
-    HOT_CUDA(cudaMemsetAsync(absmax_ws, 0, sizeof(uint32_t), st));
+    const dim3 grid((unsigned)grid_for(rows * (cols >> 4), (sms + batch - 1) / batch), (unsigned)batch);
+    HOT_CUDA(cudaMemsetAsync(absmax_ws, 0, sizeof(uint32_t) * (size_t)batch, st));
     const bool contig = ldx == cols && ld_codes == (STORE4 ? cols / 2 : cols);
     if (contig) {
       row_ht_absmax_kernel<T, true><<<grid, kThreads, 0, st>>>(x, rows, cols, ldx, n, absmax_ws);
@@ -218,10 +227,10 @@ int launch_typed(const T* x, int64_t rows, int cols, int64_t ldx, int n, const h
 
 template <typename T>
 int launch_modes(const T* x, int64_t rows, int cols, int64_t ldx, int n, const hot_quant_t& q, uint8_t* codes,
-                 int64_t ld_codes, float* scales, uint32_t* ws, cudaStream_t st, int sms) {
+                 int64_t ld_codes, float* scales, uint32_t* ws, cudaStream_t st, int sms, int batch) {
 #define HOT_CASE(R, S)                                                                              \
   if (q.rounding == (R) && q.storage == (S))                                                        \
-    return launch_typed<T, (R), (S)>(x, rows, cols, ldx, n, q, codes, ld_codes, scales, ws, st, sms);
+    return launch_typed<T, (R), (S)>(x, rows, cols, ldx, n, q, codes, ld_codes, scales, ws, st, sms, batch);
   HOT_CASE(HOT_ROUND_NEAREST, HOT_STORE_INT8)
   HOT_CASE(HOT_ROUND_NEAREST, HOT_STORE_INT4)
   HOT_CASE(HOT_ROUND_STOCH_PHILOX, HOT_STORE_INT8)
@@ -238,10 +247,10 @@ int device_sm_count();
 
 }  // namespace hot
 
-extern "C" int hot_row_ht_quant(const void* x, int dtype, int64_t rows, int64_t cols, int64_t ldx, int order,
-                                const hot_quant_t* q, void* codes, int64_t ld_codes, float* scales,
-                                uint32_t* absmax_ws, hot_stream_t stream) {
-  using namespace hot;
+namespace hot {
+namespace {
+int row_ht_quant_impl(const void* x, int dtype, int64_t rows, int64_t cols, int64_t ldx, int order, const hot_quant_t* q,
+                      void* codes, int64_t ld_codes, float* scales, uint32_t* absmax_ws, hot_stream_t stream, int batch) {
   if (rows == 0 && cols > 0 && q) return HOT_OK;  // nothing to do (and the pointers may be null)
   if (!x || !q || !codes || !scales) HOT_FAIL(HOT_ERR_ARG, "hot_row_ht_quant: null pointer");
   if (rows < 0 || cols <= 0) HOT_FAIL(HOT_ERR_ARG, "hot_row_ht_quant: bad shape %lld x %lld", (long long)rows, (long long)cols);
@@ -267,9 +276,28 @@ extern "C" int hot_row_ht_quant(const void* x, int dtype, int64_t rows, int64_t 
   if (sms <= 0) return HOT_ERR_CUDA;
   if (dtype == HOT_F32)
     return launch_modes<float>((const float*)x, rows, (int)cols, ldx, order, *q, (uint8_t*)codes, ld_codes, scales,
-                               absmax_ws, st, sms);
+                               absmax_ws, st, sms, batch);
   if (dtype == HOT_BF16)
     return launch_modes<__nv_bfloat16>((const __nv_bfloat16*)x, rows, (int)cols, ldx, order, *q, (uint8_t*)codes,
-                                       ld_codes, scales, absmax_ws, st, sms);
+                                       ld_codes, scales, absmax_ws, st, sms, batch);
   HOT_FAIL(HOT_ERR_UNSUPPORTED, "hot_row_ht_quant: dtype %d", dtype);
+}
+}  // namespace
+}  // namespace hot
+
+extern "C" int hot_row_ht_quant(const void* x, int dtype, int64_t rows, int64_t cols, int64_t ldx, int order,
+                                const hot_quant_t* q, void* codes, int64_t ld_codes, float* scales,
+                                uint32_t* absmax_ws, hot_stream_t stream) {
+  return hot::row_ht_quant_impl(x, dtype, rows, cols, ldx, order, q, codes, ld_codes, scales, absmax_ws, stream, 1);
+}
+
+extern "C" int hot_row_ht_quant_batched(const void* x, int dtype, int64_t batch, int64_t rows, int64_t cols, int64_t ldx,
+                                        int order, const hot_quant_t* q, void* codes, int64_t ld_codes, float* scales,
+                                        uint32_t* absmax_ws, hot_stream_t stream) {
+  using namespace hot;
+  if (batch < 1 || batch > 65535) HOT_FAIL(HOT_ERR_ARG, "hot_row_ht_quant_batched: batch %lld outside [1, 65535]", (long long)batch);
+  if (!q) HOT_FAIL(HOT_ERR_ARG, "hot_row_ht_quant_batched: null pointer");
+  if (q->scale_mode != HOT_SCALE_TENSOR)
+    HOT_FAIL(HOT_ERR_UNSUPPORTED, "hot_row_ht_quant_batched: one scale per sample is HOT_SCALE_TENSOR; per-row scales do not depend on the batch");
+  return row_ht_quant_impl(x, dtype, rows, cols, ldx, order, q, codes, ld_codes, scales, absmax_ws, stream, (int)batch);
 }

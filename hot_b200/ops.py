@@ -136,11 +136,12 @@ def col_ht_quant_static(x: torch.Tensor, order: int, sel: Sequence[int], q: Quan
 def gemm_i8(a: torch.Tensor, a_storage: str, b: torch.Tensor, b_storage: str, M: int, N: int, K: int,
             scale_a: Optional[torch.Tensor], scale_b: Optional[torch.Tensor], post: float = 1.0,
             out_dtype: torch.dtype = torch.float32, status: Optional[torch.Tensor] = None,
-            stream_k: bool = False) -> torch.Tensor:
+            stream_k: bool = False, a_rows_per_scale: int = 1) -> torch.Tensor:
     """out [M, N] = ((a . b^T) * scale_a[m or 0]) * scale_b[n or 0] * post on the tcgen05 integer path;
     ``a`` [M, pitch] and ``b`` [N, pitch] are uint8/int8 code matrices with K contiguous.
     ``out_dtype=torch.int32`` returns the raw accumulator.  ``stream_k=True`` hands the kernel a
-    workspace so that it may balance k-blocks over the SMs (same results)."""
+    workspace so that it may balance k-blocks over the SMs (same results).  With
+    ``a_rows_per_scale = k > 1``, ``scale_a`` holds one scale per k consecutive rows of ``a``."""
     _require_cuda(a, b)
     odt = {torch.float32: C.HOT_F32, torch.bfloat16: C.HOT_BF16, torch.int32: C.HOT_I32}[out_dtype]
     out = torch.empty((M, N), dtype=out_dtype, device=a.device)
@@ -152,12 +153,80 @@ def gemm_i8(a: torch.Tensor, a_storage: str, b: torch.Tensor, b_storage: str, M:
             ws = torch.empty((int(C.lib().hot_gemm_i8_workspace_bytes(M, N)),), dtype=torch.uint8, device=a.device)
         C.check(C.lib().hot_gemm_i8_ws(a.data_ptr(), C.STORE_INT4 if a_storage == "int4" else C.STORE_INT8, a.stride(0),
                                        b.data_ptr(), C.STORE_INT4 if b_storage == "int4" else C.STORE_INT8, b.stride(0),
-                                       M, N, K, sa, int(scale_a is not None and scale_a.numel() > 1), sb,
+                                       M, N, K, sa,
+                                       int(a_rows_per_scale) if (scale_a is not None and scale_a.numel() > 1) else 0, sb,
                                        int(scale_b is not None and scale_b.numel() > 1), float(post), out.data_ptr(), odt,
                                        out.stride(0), ws.data_ptr() if ws is not None else None,
                                        ws.numel() if ws is not None else 0,
                                        status.data_ptr() if status is not None else None, _stream(a)),
                 "hot_gemm_i8_ws")
+    return out
+
+
+def row_ht_quant_batched(x: torch.Tensor, order: int, q: Quant):
+    """``row_ht_quant`` on a batch ``x`` [B, rows, cols] with one scale per sample.  Returns (codes
+    uint8 [B*rows, cols] or packed [B*rows, cols/2], scales float32 [B])."""
+    _require_cuda(x)
+    if x.dim() != 3 or not x.is_contiguous():
+        raise ValueError("x must be a contiguous 3-D tensor")
+    B, rows, cols = x.shape
+    row_bytes = cols // 2 if q.storage == "int4" else cols
+    codes = torch.empty((B * rows, _pitch16(row_bytes)), dtype=torch.uint8, device=x.device)[:, :row_bytes]
+    scales = torch.empty((B,), dtype=torch.float32, device=x.device)
+    ws = torch.empty((max(B, 16),), dtype=torch.int32, device=x.device)
+    with torch.cuda.device(x.device):
+        C.check(C.lib().hot_row_ht_quant_batched(x.data_ptr(), _dtype(x), B, rows, cols, cols, order, ctypes.byref(q.to_c()),
+                                                 codes.data_ptr(), codes.stride(0), scales.data_ptr(), ws.data_ptr(),
+                                                 _stream(x)), "hot_row_ht_quant_batched")
+    return codes, scales
+
+
+def sample_pitch(out_len: int) -> int:
+    """Bytes one sample takes along the contraction axis of a batched, transposed INT8 operand:
+    its codes rounded up to whole 128-byte k-blocks of the integer GEMM."""
+    return (out_len + 127) // 128 * 128
+
+
+def col_ht_quant_batched(x: torch.Tensor, order: int, sel: Sequence[int], q: Quant, logical_layout: str = "natural"):
+    """``col_ht_quant`` on a batch ``x`` [B, rows, cols], transform along the rows of each sample, one
+    scale per sample.  Returns (codes_t uint8 [cols, B * pitch] with sample b at byte b * pitch of
+    each row, zero padded, scales float32 [B], out_len per sample, pitch)."""
+    _require_cuda(x)
+    if x.dim() != 3 or not x.is_contiguous():
+        raise ValueError("x must be a contiguous 3-D tensor")
+    B, rows, cols = x.shape
+    r = len(sel)
+    out_len = rows // order * r
+    pitch = sample_pitch(out_len)
+    codes = torch.empty((cols, B * pitch), dtype=torch.uint8, device=x.device)
+    scales = torch.empty((B,), dtype=torch.float32, device=x.device)
+    ws = torch.empty((max(B, 16),), dtype=torch.int32, device=x.device)
+    sel_c = (C.c_i32 * r)(*[int(v) for v in sel])
+    with torch.cuda.device(x.device):
+        C.check(C.lib().hot_col_ht_quant_batched(x.data_ptr(), _dtype(x), B, rows, cols, cols, order, sel_c, r,
+                                                 ctypes.byref(q.to_c()),
+                                                 C.LAYOUT_TRANSPOSED if logical_layout == "transposed" else C.LAYOUT_NATURAL,
+                                                 codes.data_ptr(), codes.stride(0), pitch, scales.data_ptr(), ws.data_ptr(),
+                                                 _stream(x)), "hot_col_ht_quant_batched")
+    return codes, scales, out_len, pitch
+
+
+def gemm_i8_grouped(a: torch.Tensor, b: torch.Tensor, M: int, N: int, groups: int, group_k: int, scale_a: torch.Tensor,
+                    scale_b: torch.Tensor, post: float = 1.0, out_dtype: torch.dtype = torch.float32,
+                    status: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out [M, N] = (sum_g ((a_g . b_g^T) * scale_a[g]) * scale_b[g]) * post, where group g is the
+    columns [g * group_k, (g + 1) * group_k) of the INT8 code matrices ``a`` [M, .] and ``b`` [N, .]
+    (group_k a multiple of 128); the sum over groups runs in fp32, group 0 first."""
+    _require_cuda(a, b, scale_a, scale_b)
+    odt = {torch.float32: C.HOT_F32, torch.bfloat16: C.HOT_BF16}[out_dtype]
+    if out is None:  # the kernel stores through a tensor map: the row pitch must be a multiple of 16 bytes
+        per16 = 16 // torch.empty((), dtype=out_dtype).element_size()
+        out = torch.empty((M, (N + per16 - 1) // per16 * per16), dtype=out_dtype, device=a.device)[:, :N]
+    with torch.cuda.device(a.device):
+        C.check(C.lib().hot_gemm_i8_grouped(a.data_ptr(), a.stride(0), b.data_ptr(), b.stride(0), M, N, groups, group_k,
+                                            scale_a.data_ptr(), scale_b.data_ptr(), float(post), out.data_ptr(), odt,
+                                            out.stride(0), status.data_ptr() if status is not None else None, _stream(a)),
+                "hot_gemm_i8_grouped")
     return out
 
 
@@ -265,4 +334,44 @@ def linear_backward(go: torch.Tensor, w: torch.Tensor, x_q_t: torch.Tensor, scal
                                             gw.data_ptr() if need_gw else None, gw.stride(0) if need_gw else I,
                                             ws.data_ptr(), ws.numel(), status.data_ptr() if status is not None else None,
                                             _stream(go)), "hot_linear_backward")
+    return gx, gw
+
+
+def abc_compress_batched(x: torch.Tensor, cfg: LinearConfig):
+    """Activation buffer of a batch ``x`` [B, L, I] with one scale per sample, as the reference saves
+    it for 3-D inputs: (x_q_t uint8 [I, B * pitch], scale_x float32 [B], pitch)."""
+    codes, scales, _, pitch = col_ht_quant_batched(x, cfg.order_l, cfg.sel_l, _one_per_byte(cfg.q_x), "natural")
+    return codes, scales, pitch
+
+
+def _one_per_byte(q: Quant) -> Quant:
+    """The same quantiser with its codes stored one per byte (the batched operands are INT8-stored)."""
+    return Quant(q.bits, "int8", q.rounding, q.scale, q.seed, q.offset, q.noise)
+
+
+def linear_backward_batched(go: torch.Tensor, w: torch.Tensor, x_q_t: torch.Tensor, scale_x: torch.Tensor,
+                            cfg: LinearConfig, need_gx: bool = True, need_gw: bool = True,
+                            status: Optional[torch.Tensor] = None):
+    """HOT backward of one linear layer on a batch ``go`` [B, L, O] with the reference's 3-D
+    semantics: every quantiser of grad_out and of the activation takes one scale per sample, the
+    low-rank projection runs along the tokens of each sample, and grad_w is the fp32 sum over
+    samples of the dequantised per-sample products (utils/quant_matmul.py:223-225, 288-290,
+    322-324).  ``x_q_t`` / ``scale_x`` come from ``abc_compress_batched``.  Returns
+    (grad_x [B, L, I] or None, grad_w [O, I] or None)."""
+    _require_cuda(go, w, x_q_t)
+    if go.dim() != 3 or not go.is_contiguous():
+        raise ValueError("go must be a contiguous [B, L, O] tensor")
+    B, L, O = go.shape
+    I = w.shape[1]
+    gx = gw = None
+    if need_gx:
+        q_go, s_go = row_ht_quant_batched(go, cfg.order_o, cfg.q_gx)
+        q_w_t, s_w, _ = col_ht_quant(w, cfg.order_o, list(range(cfg.order_o)), _one_per_byte(cfg.q_w), "natural")
+        gx = gemm_i8(q_go, cfg.q_gx.storage, q_w_t, "int8", B * L, I, O, s_go, s_w, 1.0 / cfg.order_o, go.dtype,
+                     status=status, a_rows_per_scale=L).view(B, L, I)
+    if need_gw:
+        q_gw_t, s_gw, out_len, pitch = col_ht_quant_batched(go, cfg.order_l, cfg.sel_l, _one_per_byte(cfg.q_gw), "transposed")
+        if x_q_t.shape[1] != B * pitch:
+            raise ValueError("activation buffer does not match: %d bytes per row, expected %d" % (x_q_t.shape[1], B * pitch))
+        gw = gemm_i8_grouped(q_gw_t, x_q_t, O, I, B, pitch, s_gw, scale_x, 1.0 / cfg.order_l, go.dtype, status=status)
     return gx, gw

@@ -65,39 +65,55 @@ def _quantise_2d(x: Tensor, bits: int, rounding: str, scale: str):
     return codes, scales
 
 
-def _no_batched(name: str, is_batched: bool) -> None:
-    if is_batched:
-        raise NotImplementedError("%s: per-sample (3-D, vmap) scales are not built; flatten tokens to 2-D" % name)
+def _quantise_batched(x: Tensor, bits: int, rounding: str):
+    """One scale per sample of x [B, ...] (what torch.vmap over dim 0 of the reference's quantisers
+    gives, utils/quant_matmul.py:102-106,117-122): (codes like x, scales [B])."""
+    if x.dim() < 2:
+        raise ValueError("a batched quantiser takes a tensor with a batch dim")
+    x3 = x.reshape(x.shape[0], -1, x.shape[-1]) if x.dim() >= 3 else x.reshape(x.shape[0], 1, x.shape[1])
+    x3 = x3.contiguous()
+    pad = (-x3.shape[2]) % 16
+    if pad:
+        x3 = F.pad(x3, (0, pad))
+    q = ops.Quant(bits, "int8", rounding, "tensor", _seed(), _next_offset())
+    codes, scales = ops.row_ht_quant_batched(x3, 1, q)
+    codes = codes.view(torch.int8)[:, :x3.shape[2] - pad].to(x.dtype).reshape(x.shape)
+    return codes, scales
 
 
 def stoch_quantizer(x: Tensor, quantBits: int, is_batched: bool = False):
-    """Per-tensor abs-max scale, stochastic rounding (utils/quant_matmul.py:86-106)."""
-    _no_batched("stoch_quantizer", is_batched)
+    """Abs-max scale (one per tensor, or one per sample when batched), stochastic rounding
+    (utils/quant_matmul.py:86-106)."""
+    if is_batched:
+        return _quantise_batched(x, quantBits, "philox")
     codes, s = _quantise_2d(x, quantBits, "philox", "tensor")
     return codes, s[0]
 
 
 def int_quantizer(x: Tensor, quantBits: int, is_batched: bool = False):
-    """Per-tensor abs-max scale, round half to even (utils/quant_matmul.py:108-122)."""
-    _no_batched("int_quantizer", is_batched)
+    """Abs-max scale (one per tensor, or one per sample when batched), round half to even
+    (utils/quant_matmul.py:108-122)."""
+    if is_batched:
+        return _quantise_batched(x, quantBits, "nearest")
     codes, s = _quantise_2d(x, quantBits, "nearest", "tensor")
     return codes, s[0]
 
 
 def norm_quantizer(x: Tensor, quantBits: int, is_batched: bool = False):
     """Per-row abs-max scale, stochastic rounding; returns the DEQUANTISED tensor and the scale
-    1.0, as the reference does (utils/quant_matmul.py:19-37)."""
-    _no_batched("norm_quantizer", is_batched)
-    if x.dim() != 2:
-        raise NotImplementedError("norm_quantizer takes a 2-D tensor")
+    1.0, as the reference does (utils/quant_matmul.py:19-37).  Batched [B, L, C] input: the rows of
+    every sample are rows of the flattened tensor, so the batch changes nothing."""
+    if x.dim() != (3 if is_batched else 2):
+        raise NotImplementedError("norm_quantizer takes a 2-D tensor, or a 3-D one when batched")
     codes, s = _quantise_2d(x, quantBits, "philox", "row")
-    return codes * s.to(x.dtype).unsqueeze(1), 1.
+    return codes * s.to(x.dtype).reshape(x.shape[:-1]).unsqueeze(-1), 1.
 
 
 def sawb_quantizer(x: Tensor, quantBits: int, is_batched: bool = False):
     """One scale from clip = 12.1*sqrt(mean(x^2)) - 12.2*mean(|x|), values clamped to +-clip, round to
     nearest (utils/quant_matmul.py:40-55).  Returns (codes as float, scale)."""
-    _no_batched("sawb_quantizer", is_batched)
+    if is_batched:
+        raise NotImplementedError("sawb_quantizer: per-sample (3-D, vmap) clip values are not built; flatten tokens to 2-D")
     x2 = x if x.dim() == 2 else x.reshape(-1, x.shape[-1])
     if not x2.is_contiguous():
         x2 = x2.contiguous()
@@ -172,8 +188,11 @@ class FLinearQ(Function):
     Hadamard low-rank projection of ``x`` along tokens, quantised to INT8 (what the reference
     saves), produced by one fused kernel.  backward: grad_input and grad_weight from the
     integer tensor-core path; exactly two real gradients are returned.
-    3-D inputs [B, L, I] are treated as B*L flat tokens with one scale (the reference takes one
-    scale per sample)."""
+    3-D inputs [B, L, I] follow the reference: every quantiser of a batched tensor takes one scale
+    per sample, the low-rank projection runs along the tokens of each sample, grad_weight is the sum
+    over samples (utils/quant_matmul.py:180,223-225,288-290,322-324).  With ``args.lowRankPreset``
+    set (not in the reference) the batch is flattened to B*L tokens with one scale instead, which
+    is the faster path."""
 
     @staticmethod
     def forward(x, w, h_out, h_bs, name):
@@ -184,15 +203,23 @@ class FLinearQ(Function):
         x, w, h_out, h_bs, name = inputs
         a = _args()
         _check_scheme(a)
-        x2 = x.detach().reshape(-1, x.shape[-1])
-        if not x2.is_contiguous():
-            x2 = x2.contiguous()
         n_l, sel = _selection(h_bs)
-        if x2.shape[0] % n_l:
-            raise ValueError("token count %d is not a multiple of the low-rank order %d" % (x2.shape[0], n_l))
         q_x = _operand("x", a.quantBWDAct, a.actQuantBit, "Activation", row_ok=False)
         cfg = ops.LinearConfig(order_o=int(h_out.shape[0]), order_l=n_l, sel_l=sel, q_x=q_x)
-        x_q_t, scale_x = ops.abc_compress(x2, cfg)
+        ctx.per_sample = x.dim() == 3 and getattr(a, "lowRankPreset", None) is None
+        if ctx.per_sample:
+            if x.shape[1] % n_l:
+                raise ValueError("token count %d is not a multiple of the low-rank order %d" % (x.shape[1], n_l))
+            if q_x.scale != "tensor":
+                raise NotImplementedError("Activation rounding scheme %r with per-sample scales is not built" % a.quantBWDAct)
+            x_q_t, scale_x, _ = ops.abc_compress_batched(x.detach().contiguous(), cfg)
+        else:
+            x2 = x.detach().reshape(-1, x.shape[-1])
+            if not x2.is_contiguous():
+                x2 = x2.contiguous()
+            if x2.shape[0] % n_l:
+                raise ValueError("token count %d is not a multiple of the low-rank order %d" % (x2.shape[0], n_l))
+            x_q_t, scale_x = ops.abc_compress(x2, cfg)
         ctx.name = name
         ctx.x_shape = tuple(x.shape)
         ctx.order_o, ctx.order_l, ctx.sel = int(h_out.shape[0]), n_l, sel
@@ -205,7 +232,7 @@ class FLinearQ(Function):
         a = _args()
         _check_scheme(a)
         name = ctx.name
-        go = grad_output.reshape(-1, grad_output.shape[-1])
+        go = grad_output if ctx.per_sample else grad_output.reshape(-1, grad_output.shape[-1])
         if not go.is_contiguous():
             go = go.contiguous()
         if go.dtype != w.dtype:
@@ -229,7 +256,11 @@ class FLinearQ(Function):
                                q_x=ctx.q_x)
         need_gx, need_gw = ctx.needs_input_grad[0], ctx.needs_input_grad[1]
         gx = gw = None
-        if need_gx or need_gw:
+        if (need_gx or need_gw) and ctx.per_sample:
+            if q_gx.scale != "tensor" or q_gw.scale != "tensor":
+                raise NotImplementedError("per-token / per-channel grad_output scales with per-sample (3-D) inputs are not built")
+            gx, gw = ops.linear_backward_batched(go, w.detach(), x_q_t, scale_x, cfg, need_gx=need_gx, need_gw=need_gw)
+        elif need_gx or need_gw:
             gx, gw = ops.linear_backward(go, w.detach(), x_q_t, scale_x, cfg, need_gx=need_gx, need_gw=need_gw)
         if gx is not None:
             gx = gx.reshape(ctx.x_shape)

@@ -77,6 +77,20 @@ int hot_row_ht_quant(const void* x, int dtype, int64_t rows, int64_t cols, int64
                      uint32_t* absmax_ws, hot_stream_t stream);
 
 /*
+ * hot_row_ht_quant on a batch of samples with ONE SCALE PER SAMPLE, in one pair of launches:
+ *   x      [batch, rows, cols] (sample b at row b * rows of a [batch * rows, cols] matrix, pitch ldx)
+ *   codes  same layout as x; scales [batch]; absmax_ws  `batch` 32-bit words of scratch
+ * q->scale_mode must be HOT_SCALE_TENSOR (per-row scales do not depend on the batch: use
+ * hot_row_ht_quant).  noise / Philox element index: (b * rows + row) * cols + col.
+ * Stands in for the vmapped quantisers (torch.vmap(stoch_quantizer_BWD / int_quantizer_BWD),
+ * utils/quant_matmul.py:102-106,117-122) the reference applies to 3-D [B, L, O] tensors after
+ * lowering_matmul_front (utils/hadamard_matmul.py:121-141).
+ */
+int hot_row_ht_quant_batched(const void* x, int dtype, int64_t batch, int64_t rows, int64_t cols, int64_t ldx,
+                             int order, const hot_quant_t* q, void* codes, int64_t ld_codes, float* scales,
+                             uint32_t* absmax_ws, hot_stream_t stream);
+
+/*
  * Fused block Walsh-Hadamard transform along the FIRST dim with row selection (the
  * Hadamard low-rank projection; all rows kept = plain Hadamard) + quantisation, written
  * TRANSPOSED so that the transformed dim becomes the contiguous (contraction) dim.
@@ -103,6 +117,24 @@ int hot_col_ht_quant(const void* x, int dtype, int64_t rows, int64_t cols, int64
                      const int32_t* sel, int r, const hot_quant_t* q, int logical_layout,
                      void* codes_t, int64_t ld_codes, float* scales, uint32_t* absmax_ws,
                      hot_stream_t stream);
+/*
+ * hot_col_ht_quant on a batch of samples with ONE SCALE PER SAMPLE:
+ *   x        [batch, rows, cols]: sample b is rows b * rows .. of a [batch * rows, cols] matrix;
+ *            the transform runs along the rows of each sample (rows % order == 0)
+ *   codes_t  [cols, batch * sample_pitch] INT8: sample b's rows * r / order codes start
+ *            b * sample_pitch bytes into each output row and are followed by zeros up to the next
+ *            sample (sample_pitch a multiple of 16; a multiple of 128 for hot_gemm_i8_grouped)
+ *   scales [batch];  absmax_ws  `batch` words of scratch
+ * HOT_SCALE_TENSOR and HOT_STORE_INT8 only.  noise / Philox element index: b * (rows*r/order * cols)
+ * + the index hot_col_ht_quant would use within the sample.
+ * Stands in for lowering_matmul_back on a 3-D tensor (utils/hadamard_matmul.py:143-161, the
+ * middle-dim case) followed by a vmapped quantiser, as FLinearQ uses them for [B, L, I]
+ * activations and [B, L, O] output gradients (utils/quant_matmul.py:180-204, 300-320).
+ */
+int hot_col_ht_quant_batched(const void* x, int dtype, int64_t batch, int64_t rows, int64_t cols, int64_t ldx,
+                             int order, const int32_t* sel, int r, const hot_quant_t* q, int logical_layout,
+                             void* codes_t, int64_t ld_codes, int64_t sample_pitch, float* scales,
+                             uint32_t* absmax_ws, hot_stream_t stream);
 /* Scratch words hot_col_ht_quant needs for these sizes and this hot_scale_mode (0 on bad arguments). */
 size_t hot_col_ht_quant_scratch_words(int dtype, int64_t rows, int64_t cols, int order, int r, int scale_mode);
 
@@ -134,7 +166,9 @@ int hot_col_ht_quant_static(const void* x, int dtype, int64_t rows, int64_t cols
  *   out[m, n] = ((float)(sum_k a[m,k] * b[n,k]) * sa[m or 0]) * sb[n or 0] * post
  *   a [M, K] and b [N, K]: K contiguous, pitches lda/ldb in BYTES (multiples of 16),
  *       storage HOT_STORE_INT8 or HOT_STORE_INT4 (K even, packed along K)
- *   scale_a / scale_b: device floats, [1] or per row ([M] / [N]) when *_per_row != 0
+ *   scale_a / scale_b: device floats, [1] or per row ([M] / [N]) when *_per_row != 0;
+ *       scale_a_per_row = k > 1: one scale per k consecutive rows of a ([ceil(M / k)]: the per-sample
+ *       scales of a batch of k-row samples)
  *   out: HOT_F32 | HOT_BF16 [M, N] pitch ldo elements, or HOT_I32 for the raw accumulator
  *   status_word: device word the kernel ORs a non-zero code into when a bounded wait runs
  *       out (may be NULL); the caller clears and reads it
@@ -161,6 +195,20 @@ int hot_gemm_i8_ws(const void* a, int a_storage, int64_t lda, const void* b, int
                    const float* scale_b, int scale_b_per_row, float post, void* out, int out_dtype,
                    int64_t ldo, void* workspace, size_t workspace_bytes, uint32_t* status_word,
                    hot_stream_t stream);
+
+/*
+ * Integer GEMM whose contraction axis is a batch of samples laid side by side, each with its own
+ * pair of scales; the dequantised per-sample products are summed in fp32, sample 0 first:
+ *   out[m, n] = (sum_g ((float)(sum_{k in group g} a[m,k] * b[n,k]) * scale_a[g]) * scale_b[g]) * post
+ *   a [M, groups * group_k], b [N, groups * group_k] INT8, K contiguous, pitches in bytes
+ *   group_k a multiple of 128 (pad each sample with zero codes: hot_col_ht_quant_batched does)
+ *   out HOT_F32 | HOT_BF16, base and pitch 16-byte aligned
+ * Stands in for the batched matmul on integer values, the per-sample scales and the sum over
+ * the batch that autograd applies to the [B, O, I] result (utils/quant_matmul.py:322-324).
+ */
+int hot_gemm_i8_grouped(const void* a, int64_t lda, const void* b, int64_t ldb, int64_t M, int64_t N,
+                        int64_t groups, int64_t group_k, const float* scale_a, const float* scale_b, float post,
+                        void* out, int out_dtype, int64_t ldo, uint32_t* status_word, hot_stream_t stream);
 
 /* Per-layer configuration of the backward pass (scheme gih_gwlr, utils/quant_matmul.py:214-348). */
 typedef struct hot_linear_cfg {

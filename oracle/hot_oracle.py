@@ -352,6 +352,59 @@ def linear_backward(go, w, x_q, s_x, *, n_o: int, n_l: int, sel, bits_gx: int = 
 
 
 # ----------------------------------------------------------------------------
+# the same on 3-D tensors [B, L, .]: one scale per sample (torch.vmap over dim 0 of the
+# quantisers, utils/quant_matmul.py:102-106,117-122), grad_w summed over the batch
+# ----------------------------------------------------------------------------
+def _sample(u, b):
+    """Noise of sample b: a slice of a [B, ...] array (keeping the PhiloxBytes marker), or None."""
+    if u is None:
+        return None
+    return u[b].view(type(u)) if isinstance(u, PhiloxBytes) else np.asarray(u)[b]
+
+
+def abc_compress_batched(x: np.ndarray, n_l: int, sel: np.ndarray, bits: int, u, mode: str = "stoch"):
+    """setup_context (:177-212) on x [B, L, I]: HLA along the tokens of each sample, one scale per
+    sample.  Returns (codes int32 [B, L', I], s float32 [B])."""
+    outs = [abc_compress(x[b], n_l, sel, bits, _sample(u, b), mode) for b in range(x.shape[0])]
+    return np.stack([o[0] for o in outs]), np.array([o[1] for o in outs], dtype=F32)
+
+
+def linear_backward_batched(go, w, x_q, s_x, *, n_o: int, n_l: int, sel, bits_gx: int = 4, bits_w: int = 4,
+                            bits_gw: int = 8, u_go=None, u_w=None, u_gw=None, w_mode: str = "stoch",
+                            exact_matmul: bool = True):
+    """FLinearQ.backward (:214-348) for go [B, L, O], x_q [B, L', I], s_x [B].  Every quantiser of a
+    batched tensor takes one scale per sample; the weight is 2-D and keeps one scale.  grad_input[b] =
+    (q_go[b] @ q_w) * s_go[b] * s_w / n_o (:288-290, 342).  grad_w = sum_b (q_gw[b] @ x_q[b]) * s_gw[b]
+    * s_x[b] / n_l (:322-324, 344; the sum over b is the reduction autograd applies to the
+    [B, O, I] result); here it runs in float32 from sample 0 upwards, with the exact division by the
+    power of two n_l after it."""
+    go = np.asarray(go, dtype=F32)
+    w = np.asarray(w, dtype=F32)
+    B = go.shape[0]
+    w_h = fwht_first(w, n_o)
+    if w_mode == "sawb":
+        q_w, s_w = quant_sawb(w_h, bits_w)
+    else:
+        q_w, s_w = quant_tensor(w_h, bits_w, u_w if w_mode == "stoch" else None)
+    q_go, s_go, gx, q_gw, s_gw = [], [], [], [], []
+    run = None
+    for b in range(B):
+        qg, sg = quant_tensor(fwht_last(go[b], n_o), bits_gx, _sample(u_go, b))
+        acc = _int_matmul(qg, q_w, exact_matmul)
+        gx.append(((acc.astype(F32) * F32(sg)) * F32(s_w)) / F32(n_o))
+        q_go.append(qg)
+        s_go.append(sg)
+        qw_, sw_ = quant_tensor(np.ascontiguousarray(hla(go[b], n_l, sel).T), bits_gw, _sample(u_gw, b))
+        v = ((_int_matmul(qw_, np.asarray(x_q[b]), exact_matmul).astype(F32) * F32(sw_)) * F32(s_x[b])).astype(F32)
+        run = v if run is None else (run + v).astype(F32)
+        q_gw.append(qw_)
+        s_gw.append(sw_)
+    return dict(q_go=np.stack(q_go), s_go=np.array(s_go, dtype=F32), q_w=q_w, s_w=s_w,
+                grad_input=np.stack(gx).astype(F32), q_gw=np.stack(q_gw), s_gw=np.array(s_gw, dtype=F32),
+                grad_w=(run / F32(n_l)).astype(F32))
+
+
+# ----------------------------------------------------------------------------
 # layer-wise quantiser selection (ViT_main.py:183-211)
 # ----------------------------------------------------------------------------
 def lqs_select(grad_out: np.ndarray, u_stoch: np.ndarray, u_norm: np.ndarray, bits: int = 4):

@@ -168,7 +168,71 @@ def main(ref_root: str, out_dir: str):
         l[tag + "_errs"] = np.array(errs)
         l[tag + "_gx"] = np.array(choice)
     np.savez_compressed(os.path.join(out_dir, "lqs.npz"), **l)
+    batched(ref_args, hm, qm, out_dir)
     print("golden vectors written to", out_dir)
+
+
+def batched(ref_args, hm, qm, out_dir: str):
+    """FLinearQ on a 3-D input [B, L, I]: the reference quantises every sample with its own scale
+    (torch.vmap over dim 0, utils/quant_matmul.py:102-106) and autograd sums the [B, O, I] weight
+    gradient over the batch.  ``torch.bernoulli`` cannot be fed explicit uniforms inside vmap, so
+    the vmapped wrappers are replaced by a loop that calls the reference's own per-sample
+    ``*_BWD`` function on each sample and stacks the results, which is what vmap computes (checked
+    below on the deterministic quantiser against the real vmap)."""
+    rng = np.random.default_rng(20250322)
+    T = torch.from_numpy
+
+    def per_sample(fn_bwd):
+        def f(x, bits, is_batched):
+            if not is_batched:
+                return fn_bwd(x, bits)
+            outs = [fn_bwd(x[b], bits) for b in range(x.shape[0])]
+            return torch.stack([o[0] for o in outs]), torch.stack([o[1] for o in outs])
+        return f
+
+    probe = T(rng.standard_normal((3, 10, 12)).astype(np.float32))
+    c_v, s_v = qm.int_quantizer(probe, 8, True)                       # the real vmap
+    c_l, s_l = per_sample(qm.int_quantizer_BWD)(probe, 8, True)
+    assert torch.equal(c_v, c_l) and torch.equal(s_v, s_l)
+
+    B, L, O, I = 3, 24, 96, 48
+    ref_args.transform_scheme = "gih_gwlr"
+    ref_args.TransformGogi = ref_args.TransformWgt = ref_args.TransformGogw = ref_args.TransformInput = True
+    ref_args.GogiQuantBit, ref_args.weightQuantBit, ref_args.GogwQuantBit, ref_args.actQuantBit = 4, 4, 8, 8
+    ref_args.quantBWDGogi = ref_args.quantBWDWgt = ref_args.quantBWDGogw = ref_args.quantBWDAct = "stoch"
+    ref_args.quantAuto = False
+    xx = rng.standard_normal((B, L, I)).astype(np.float32)
+    xx[1] *= 3.0                                                       # samples of different magnitude
+    xx[:, :, 3] *= 20.0
+    ww = ((rng.random((O, I)) * 2 - 1) / np.sqrt(I)).astype(np.float32)
+    go = (rng.standard_normal((B, L, O)) * 1e-3).astype(np.float32)
+    go[2] *= 7.0
+    h_out = torch.tensor(hm.make_hadamard(O), dtype=torch.float32)
+    pm = hm.make_WHT(L, 50)
+    h_bs = torch.tensor(pm, dtype=torch.float32)
+    r, n = pm.shape
+    Lp = L * r // n
+    u_x = rng.random((B, Lp, I), dtype=np.float32)
+    u_go = rng.random((B, L, O), dtype=np.float32)
+    u_w = rng.random((O, I), dtype=np.float32)
+    u_gw = rng.random((B, O, Lp), dtype=np.float32)
+    xt = T(xx).requires_grad_(True)
+    wt = T(ww).requires_grad_(True)
+    keep = qm.stoch_quantizer
+    qm.stoch_quantizer = per_sample(qm.stoch_quantizer_BWD)
+    try:
+        with NoiseQueue() as nq:
+            nq.queue += [T(u_x[b]) for b in range(B)] + [T(u_go[b]) for b in range(B)] + [T(u_w)] + \
+                        [T(u_gw[b]) for b in range(B)]
+            y = qm.FLinearQ.apply(xt, wt, h_out, h_bs, "layer")
+            saved = y.grad_fn.saved_tensors
+            y.backward(T(go))
+            assert not nq.queue
+    finally:
+        qm.stoch_quantizer = keep
+    f = dict(x=xx, w=ww, go=go, p=pm.astype(np.int8), u_x=u_x, u_go=u_go, u_w=u_w, u_gw=u_gw, y=y.detach().numpy(),
+             x_q=saved[0].numpy(), scale_x=saved[4].numpy(), grad_input=xt.grad.numpy(), grad_w=wt.grad.numpy())
+    np.savez_compressed(os.path.join(out_dir, "flinearq_batched.npz"), **f)
 
 
 if __name__ == "__main__":

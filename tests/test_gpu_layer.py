@@ -51,7 +51,7 @@ def test_quantiser_callables_follow_the_reference_contract(hot):
     row_err = (d - g).abs().amax(dim=1) / g.abs().amax(dim=1)
     assert float(row_err.max()) < 1.0 / 7 + 1e-3               # error bounded by one per-row step
     with pytest.raises(NotImplementedError):
-        qm.stoch_quantizer(g.reshape(4, 12, 100), 4, True)
+        qm.sawb_quantizer(g.reshape(4, 12, 100), 4, True)       # per-sample clip values are not built
     assert set(qm.quant_scheme_dict) >= {"int_quantizer", "stoch_quantizer", "norm_quantizer"}
 
 
@@ -90,6 +90,37 @@ def test_hq_linear_3d_and_reference_low_rank_basis(hot):
     x2 = torch.randn(3, 197, 64, device="cuda", requires_grad=True)  # ViT token count: identity basis
     lin(x2).sum().backward()
     assert tuple(lin.hadamard_bs.shape) == (1, 1)
+
+
+def test_hq_linear_3d_takes_one_scale_per_sample(hot):
+    """Reference semantics of a [B, L, I] input (no preset): per-sample scales, per-sample low-rank
+    projection, grad_weight summed over the batch; nearest rounding makes it reproducible."""
+    args, qm = hot
+    args.lowRankPreset = None
+    args.quantBWDGogi = args.quantBWDWgt = args.quantBWDGogw = args.quantBWDAct = "int"
+    torch.manual_seed(3)
+    B, L, I, O = 5, 24, 64, 96
+    lin = qm.HQ_Linear(I, O, bias=False).cuda()
+    x = torch.randn(B, L, I, device="cuda") * torch.tensor([1.0, 3.0, 0.5, 8.0, 2.0], device="cuda").view(B, 1, 1)
+    x.requires_grad_(True)
+    go = torch.randn(B, L, O, device="cuda") * 1e-3 * torch.tensor([1.0, 0.2, 6.0, 1.5, 3.0], device="cuda").view(B, 1, 1)
+    lin(x).backward(go)
+    n_l, sel = oc.wht_selection(L, 50)
+    xq, sx = oc.abc_compress_batched(x.detach().cpu().numpy(), n_l, sel, 8, None, "int")
+    ref = oc.linear_backward_batched(go.cpu().numpy(), lin.weight.detach().cpu().numpy(), xq, sx, n_o=16, n_l=n_l, sel=sel,
+                                     w_mode="int")
+    assert np.array_equal(x.grad.cpu().numpy(), ref["grad_input"])
+    assert np.array_equal(lin.weight.grad.cpu().numpy(), ref["grad_w"])
+    # the batched quantiser callables: one scale per sample
+    q, s = qm.int_quantizer(go, 4, True)
+    assert q.shape == go.shape and s.shape == (B,)
+    for b in range(B):
+        rq, rs = oc.quant_tensor(go[b].cpu().numpy(), 4, None)
+        assert np.array_equal(q[b].cpu().numpy(), rq.astype(np.float32)) and float(s[b]) == float(rs)
+    q, s = qm.stoch_quantizer(go, 4, True)
+    assert s.shape == (B,) and float((q * s.view(B, 1, 1) - go).abs().max()) <= float(s.max())
+    d, one = qm.norm_quantizer(go, 4, True)
+    assert one == 1. and d.shape == go.shape
 
 
 def test_stochastic_backward_is_unbiased_enough(hot):

@@ -83,6 +83,31 @@ def test_flinearq_backward(golden, tag):
     assert np.abs(out["q_go"]).max() <= 7 and np.abs(out["q_gw"]).max() <= 127
 
 
+def test_flinearq_backward_batched(golden):
+    """3-D input [B, L, I]: one scale per sample, grad_w summed over the batch (reference run on
+    the same tensors, tests/golden/make_golden.py::batched)."""
+    g = golden("flinearq_batched")
+    n_l, sel = oc.selection_from_matrix(g["p"])
+    x_q, s_x = oc.abc_compress_batched(g["x"], n_l, sel, 8, g["u_x"])
+    assert np.array_equal(x_q, g["x_q"].astype(np.int32))
+    np.testing.assert_allclose(s_x, g["scale_x"], rtol=1e-6)
+    assert len(set(s_x.tolist())) == g["x"].shape[0]          # the samples really have different scales
+    O = g["w"].shape[0]
+    out = oc.linear_backward_batched(g["go"], g["w"], x_q, s_x, n_o=oc.block_order(O), n_l=n_l, sel=sel,
+                                     u_go=g["u_go"], u_w=g["u_w"], u_gw=g["u_gw"])
+    for name in ("grad_input", "grad_w"):
+        ref = g[name]
+        assert out[name].shape == ref.shape
+        rel = np.linalg.norm(out[name] - ref) / np.linalg.norm(ref)
+        assert rel < 1e-3, (name, rel)
+    # what a flat (2-D) treatment of the same tokens would give is measurably different
+    flat = oc.linear_backward(g["go"].reshape(-1, O), g["w"], x_q.reshape(-1, x_q.shape[-1]), s_x[0], n_o=oc.block_order(O),
+                              n_l=n_l, sel=sel, u_go=g["u_go"].reshape(-1, O), u_w=g["u_w"],
+                              u_gw=np.ascontiguousarray(g["u_gw"].transpose(1, 0, 2)).reshape(O, -1))
+    rel_flat = np.linalg.norm(flat["grad_input"].reshape(g["grad_input"].shape) - g["grad_input"]) / np.linalg.norm(g["grad_input"])
+    assert rel_flat > 10 * (np.linalg.norm(out["grad_input"] - g["grad_input"]) / np.linalg.norm(g["grad_input"]) + 1e-7)
+
+
 def test_int4_pack_roundtrip():
     rng = np.random.default_rng(0)
     c = rng.integers(-7, 8, size=(5, 32))
