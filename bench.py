@@ -60,6 +60,8 @@ def parse():
                    help="instead of the step: data-parallel ViT-B/16 training step (forward, HOT backward on the 48 "
                         "block linears, DDP all-reduce, SGD), images/s, beside the same model with plain nn.Linear")
     p.add_argument("--batch", type=int, default=256, help="images per GPU for --vit-train")
+    p.add_argument("--per-sample", action="store_true",
+                   help="the reference's 3-D semantics (one scale per image) on the ViT-B/16 linear shapes")
     p.add_argument("--large-mlp", action="store_true",
                    help="instead of the step: HOT backward vs bf16 matmul on large transformer MLP linears "
                         "(16384 tokens; 4096->11008, 11008->4096, 4096->4096; heavy-tailed outlier channels)")
@@ -342,6 +344,48 @@ def run_large_mlp(a):
     if int(status.item()) != 0:
         raise SystemExit("a bounded device-side wait ran out")
     print(json.dumps({"metric": "hot_backward_large_mlp", "tokens": M, "dtype": "bf16", "layers": out}), flush=True)
+
+
+def run_per_sample(a):
+    """The reference's 3-D semantics (one scale per image, grad_w summed over the batch) on the four
+    linear shapes of ViT-B/16 at 64 images x 197 tokens, bf16, beside the flattened path (one scale for
+    all 12,608 tokens, half16 low-rank) and the bf16 matmul backward.  With 197 tokens per image the
+    reference's own low-rank basis is the identity (197 is odd), so this path carries no low-rank
+    compression: its g_w GEMM contracts over 64 x 256 padded tokens."""
+    from hot_b200 import ops
+    from hot_b200.hadamard_matmul import lowrank_selection
+    device = torch.device("cuda", 0)
+    torch.cuda.set_device(device)
+    torch.manual_seed(0)
+    B, L = 64, 197
+    n_ps, sel_ps = lowrank_selection(L, None, 50)
+    n_fl, sel_fl = lowrank_selection(B * L, "half16")
+    status = torch.zeros(1, dtype=torch.int32, device=device)
+    out = []
+    for i_f, o_f in ((768, 2304), (768, 768), (768, 3072), (3072, 768)):
+        x = torch.randn((B, L, i_f), device=device).to(torch.bfloat16)
+        w = ((torch.rand((o_f, i_f), device=device) * 2 - 1) / i_f ** 0.5).to(torch.bfloat16)
+        go = (torch.randn((B, L, o_f), device=device) * 1e-3).to(torch.bfloat16)
+        cfg_ps = ops.LinearConfig(order_o=16, order_l=n_ps, sel_l=sel_ps)
+        cfg_fl = ops.LinearConfig(order_o=16, order_l=n_fl, sel_l=sel_fl)
+        xq_ps, sx_ps, _ = ops.abc_compress_batched(x, cfg_ps)
+        xq_fl, sx_fl = ops.abc_compress(x.view(B * L, i_f), cfg_fl)
+        go2, x2 = go.view(B * L, o_f), x.view(B * L, i_f)
+        t_ps = _graph_time(lambda i: ops.linear_backward_batched(go, w, xq_ps, sx_ps, cfg_ps, status=status), 5, device, warm=2)
+        t_fl = _graph_time(lambda i: ops.linear_backward(go2, w, xq_fl, sx_fl, cfg_fl, status=status), 5, device, warm=2)
+        t_fp = _graph_time(lambda i: (torch.matmul(go2, w), torch.matmul(go2.t(), x2)), 5, device, warm=2)
+        gx, gw = ops.linear_backward_batched(go, w, xq_ps, sx_ps, cfg_ps, status=status)
+        ex, ew = torch.matmul(go2, w).float(), torch.matmul(go2.t(), x2).float()
+        cos = lambda p_, q_: float(torch.nn.functional.cosine_similarity(p_.float().flatten(), q_.flatten(), dim=0))
+        flops = 4.0 * B * L * i_f * o_f
+        out.append({"in": i_f, "out": o_f, "per_sample_us": round(t_ps, 1), "flattened_us": round(t_fl, 1),
+                    "bf16_matmul_us": round(t_fp, 1), "per_sample_effective_tops": round(flops / t_ps / 1e6, 1),
+                    "cos_gx_vs_fp": round(cos(gx, ex), 4), "cos_gw_vs_fp": round(cos(gw, ew), 4)})
+    torch.cuda.synchronize(device)
+    if int(status.item()) != 0:
+        raise SystemExit("a bounded device-side wait ran out")
+    print(json.dumps({"metric": "hot_backward_per_sample", "images": B, "tokens_per_image": L, "dtype": "bf16",
+                      "layers": out}), flush=True)
 
 
 def run_vit_train(a):
@@ -634,6 +678,8 @@ if __name__ == "__main__":
         run_sweep(args)
     elif args.large_mlp:
         run_large_mlp(args)
+    elif args.per_sample:
+        run_per_sample(args)
     elif args.vit_train:
         run_vit_train(args)
     else:

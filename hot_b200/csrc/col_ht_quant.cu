@@ -49,46 +49,64 @@ struct ColTraits<__nv_bfloat16> {
   }
 };
 
+// A warp handles G consecutive token blocks at a time, G * N = 16 rows for the small orders, so that
+// it always has at least 16 independent rows of loads in flight.
+template <int N>
+__host__ __device__ constexpr int group_for() {
+  return N >= 16 ? 1 : 16 / N;
+}
 // column groups per thread, bounding the register tile at 64 floats (128 for bf16 at n = 64)
 template <typename T, int N>
 __host__ __device__ constexpr int vec_for() {
-  return (64 / (N * ColTraits<T>::kCpl)) >= 4 ? 4 : ((64 / (N * ColTraits<T>::kCpl)) >= 2 ? 2 : 1);
+  constexpr int rows = N * group_for<N>();
+  return (64 / (rows * ColTraits<T>::kCpl)) >= 4 ? 4 : ((64 / (rows * ColTraits<T>::kCpl)) >= 2 ? 2 : 1);
 }
 
-template <int N>
-__device__ __forceinline__ void butterfly_regs(float (&v)[N]) {
+// order-N butterfly on v[OFF .. OFF + N)
+template <int N, int OFF, int LEN>
+__device__ __forceinline__ void butterfly_regs(float (&v)[LEN]) {
 #pragma unroll
   for (int h = 1; h < N; h <<= 1) {
 #pragma unroll
     for (int i = 0; i < N; ++i) {
       if ((i & h) == 0) {
-        const float a = v[i], b = v[i + h];
-        v[i] = a + b;
-        v[i + h] = a - b;
+        const float a = v[OFF + i], b = v[OFF + i + h];
+        v[OFF + i] = a + b;
+        v[OFF + i + h] = a - b;
       }
     }
   }
 }
+template <int N, int G, int LEN>
+__device__ __forceinline__ void butterfly_groups(float (&v)[LEN]) {
+  if constexpr (G >= 1) {
+    butterfly_regs<N, (G - 1) * N, LEN>(v);
+    butterfly_groups<N, G - 1, LEN>(v);
+  }
+}
 
-// Loads the block `blk` (global block index) for this thread's columns and transforms it.
+// Loads the G blocks starting at `blk` (global block index; blocks at or past nblk read as zeros) for
+// this thread's columns and transforms each: v[column][g * N + k] = row k of block blk + g.
 template <typename T, int N, int VEC>
-__device__ __forceinline__ void load_transform(const T* __restrict__ x, const ColParams& p, int64_t blk, int c0, int lane,
-                                               float (&v)[VEC * ColTraits<T>::kCpl][N]) {
+__device__ __forceinline__ void load_transform(const T* __restrict__ x, const ColParams& p, int64_t blk, int64_t nblk, int c0,
+                                               int lane, float (&v)[VEC * ColTraits<T>::kCpl][N * group_for<N>()]) {
   constexpr int CPL = ColTraits<T>::kCpl;
+  constexpr int G = group_for<N>();
   const T* base = x + blk * N * p.ldx;
 #pragma unroll
-  for (int t = 0; t < N; ++t) {
+  for (int t = 0; t < N * G; ++t) {
+    const bool row_ok = blk + t / N < nblk;
 #pragma unroll
     for (int vv = 0; vv < VEC; ++vv) {
       const int c = c0 + (lane + 32 * vv) * CPL;
       float o[CPL];
-      ColTraits<T>::load(base + (int64_t)t * p.ldx + c, c < p.cols, o);
+      ColTraits<T>::load(base + (int64_t)t * p.ldx + c, row_ok && c < p.cols, o);
 #pragma unroll
       for (int q = 0; q < CPL; ++q) v[vv * CPL + q][t] = o[q];
     }
   }
 #pragma unroll
-  for (int i = 0; i < VEC * CPL; ++i) butterfly_regs<N>(v[i]);
+  for (int i = 0; i < VEC * CPL; ++i) butterfly_groups<N, G, N * G>(v[i]);
 }
 
 // ---- pass 1: abs-max of the kept, transformed rows --------------------------------------
@@ -111,24 +129,28 @@ __global__ void __launch_bounds__(kThreads) col_ht_absmax_kernel(const T* __rest
 #pragma unroll
   for (int i = 0; i < VEC * CPL; ++i) cm[i] = 0.0f;
   double sum_sq = 0.0, sum_abs = 0.0;  // SAWB statistics of this thread
-  for (int b = warp; b < p.nb; b += kWarps) {
+  constexpr int G = group_for<N>();
+  for (int b = warp * G; b < p.nb; b += kWarps * G) {
     if (blk0 + b >= nblk) break;
-    float v[VEC * CPL][N];
-    load_transform<T, N, VEC>(x, p, blk0 + b, c0, lane, v);
+    float v[VEC * CPL][N * G];
+    load_transform<T, N, VEC>(x, p, blk0 + b, nblk, c0, lane, v);
 #pragma unroll
-    for (int k = 0; k < N; ++k) {
-      if (p.pos[k] >= 0) {
+    for (int g = 0; g < G; ++g) {
 #pragma unroll
-        for (int i = 0; i < VEC * CPL; ++i) cm[i] = fmaxf(cm[i], fabsf(v[i][k]));
-        if (p.sawb) {
-          float sq = 0.0f, ab = 0.0f;  // columns beyond the matrix were loaded as zeros
+      for (int k = 0; k < N; ++k) {
+        if (p.pos[k] >= 0) {
 #pragma unroll
-          for (int i = 0; i < VEC * CPL; ++i) {
-            sq = fmaf(v[i][k], v[i][k], sq);
-            ab += fabsf(v[i][k]);
+          for (int i = 0; i < VEC * CPL; ++i) cm[i] = fmaxf(cm[i], fabsf(v[i][g * N + k]));
+          if (p.sawb) {
+            float sq = 0.0f, ab = 0.0f;  // columns and blocks beyond the matrix were loaded as zeros
+#pragma unroll
+            for (int i = 0; i < VEC * CPL; ++i) {
+              sq = fmaf(v[i][g * N + k], v[i][g * N + k], sq);
+              ab += fabsf(v[i][g * N + k]);
+            }
+            sum_sq += (double)sq;
+            sum_abs += (double)ab;
           }
-          sum_sq += (double)sq;
-          sum_abs += (double)ab;
         }
       }
     }
@@ -199,23 +221,41 @@ __global__ void __launch_bounds__(kThreads) col_ht_quant_kernel(const T* __restr
   const int64_t blk0 = (int64_t)blockIdx.y * p.nb;
   const int r = p.r;
 
-  for (int b = warp; b < p.nb; b += kWarps) {
+  constexpr int G = group_for<N>();
+  for (int b = warp * G; b < p.nb; b += kWarps * G) {
     if (blk0 + b < nblk) {
-      float v[VEC * CPL][N];
-      load_transform<T, N, VEC>(x, p, blk0 + b, c0, lane, v);
+      // blocks of the group past the end come back as zeros, which is what their tile slots must hold
+      float v[VEC * CPL][N * G];
+      load_transform<T, N, VEC>(x, p, blk0 + b, nblk, c0, lane, v);
+      if constexpr (N == 1) {
+        // no transform: the 16 rows of a column are 16 consecutive tile positions, stored as four float4
 #pragma unroll
-      for (int k = 0; k < N; ++k) {
-        const int j = p.pos[k];
-        if (j >= 0) {
+        for (int vv = 0; vv < VEC; ++vv)
 #pragma unroll
-          for (int vv = 0; vv < VEC; ++vv)
+          for (int qq = 0; qq < CPL; ++qq) {
+            float4* dst = reinterpret_cast<float4*>(tile + ((lane + 32 * vv) * CPL + qq) * p.pitch + b);
+            const float(&c)[G] = v[vv * CPL + qq];
 #pragma unroll
-            for (int qq = 0; qq < CPL; ++qq)
-              tile[((lane + 32 * vv) * CPL + qq) * p.pitch + b * r + j] = v[vv * CPL + qq][k];
+            for (int g4 = 0; g4 < G / 4; ++g4) dst[g4] = make_float4(c[4 * g4], c[4 * g4 + 1], c[4 * g4 + 2], c[4 * g4 + 3]);
+          }
+        continue;
+      }
+#pragma unroll
+      for (int g = 0; g < G; ++g) {
+#pragma unroll
+        for (int k = 0; k < N; ++k) {
+          const int j = p.pos[k];
+          if (j >= 0) {
+#pragma unroll
+            for (int vv = 0; vv < VEC; ++vv)
+#pragma unroll
+              for (int qq = 0; qq < CPL; ++qq)
+                tile[((lane + 32 * vv) * CPL + qq) * p.pitch + (b + g) * r + j] = v[vv * CPL + qq][g * N + k];
+          }
         }
       }
     } else {
-      for (int j = 0; j < r; ++j)
+      for (int j = 0; j < G * r; ++j)
 #pragma unroll
         for (int vv = 0; vv < VEC; ++vv)
 #pragma unroll
@@ -286,7 +326,10 @@ __global__ void __launch_bounds__(kThreads) col_ht_quant_kernel(const T* __restr
     int code[8];
     if (ROUND == HOT_ROUND_STOCH_PHILOX) {
       // random byte of stored-layout element e: byte e % 16 of Philox block e / 16
-      const uint64_t e0 = e_base + (uint64_t)c * (uint64_t)p.out_len + (uint64_t)l0;
+      // batched calls index Philox by the position in the padded output row, so that runs stay aligned
+      const uint64_t e0 = p.sample_pitch > 0
+                              ? (uint64_t)c * (uint64_t)(p.sample_pitch * p.batch) + (uint64_t)blockIdx.z * (uint64_t)p.sample_pitch + (uint64_t)l0
+                              : (uint64_t)c * (uint64_t)p.out_len + (uint64_t)l0;
       if ((e0 & 7u) == 0) {
         // aligned run: its 8 random bytes are one half of a Philox block
         const uint4 blk = philox_block16(q, e0 >> 4);
@@ -403,7 +446,7 @@ namespace {
 // tile geometry shared by the launcher and the scratch-size query
 void col_tile_geometry(int dtype, int order, int r, int* cc, int* nb) {
   const int cpl = dtype == HOT_BF16 ? 2 : 1;
-  const int per = 64 / (order * cpl);
+  const int per = 64 / ((order < 16 ? 16 : order) * cpl);
   const int vec = per >= 4 ? 4 : (per >= 2 ? 2 : 1);
   *cc = 32 * vec * cpl;
   int b = (128 / r) / 8 * 8;

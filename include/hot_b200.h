@@ -125,8 +125,10 @@ int hot_col_ht_quant(const void* x, int dtype, int64_t rows, int64_t cols, int64
  *            b * sample_pitch bytes into each output row and are followed by zeros up to the next
  *            sample (sample_pitch a multiple of 16; a multiple of 128 for hot_gemm_i8_grouped)
  *   scales [batch];  absmax_ws  `batch` words of scratch
- * HOT_SCALE_TENSOR and HOT_STORE_INT8 only.  noise / Philox element index: b * (rows*r/order * cols)
- * + the index hot_col_ht_quant would use within the sample.
+ * HOT_SCALE_TENSOR and HOT_STORE_INT8 only.  noise element index: b * (rows*r/order * cols) + the index
+ * hot_col_ht_quant would use within the sample; Philox element index: the byte position in codes_t
+ * counted with a row pitch of batch * sample_pitch (column c, sample b, code l: (c * batch + b) *
+ * sample_pitch + l).
  * Stands in for lowering_matmul_back on a 3-D tensor (utils/hadamard_matmul.py:143-161, the
  * middle-dim case) followed by a vmapped quantiser, as FLinearQ uses them for [B, L, I]
  * activations and [B, L, O] output gradients (utils/quant_matmul.py:180-204, 300-320).

@@ -98,8 +98,10 @@ def test_col_ht_quant_batched(ops, B, rows, cols, order, sel, dtype, rounding, l
     if rounding == "noise":
         u_t = rng.random((B, cols, out_len), dtype=np.float32)        # as seen in the stored layout
         u_dev = _dev(u_t if layout == "transposed" else np.ascontiguousarray(u_t.transpose(0, 2, 1)))
-    elif rounding == "philox":
-        u_t, u_dev = oc.philox_bytes(seed, offset, (B, cols, out_len)), None
+    elif rounding == "philox":                                        # indexed by the position in the padded output
+        pitch_ = ops.sample_pitch(out_len)
+        u_t = np.ascontiguousarray(oc.philox_bytes(seed, offset, (cols, B, pitch_))[:, :, :out_len].transpose(1, 0, 2))
+        u_t, u_dev = u_t.view(oc.PhiloxBytes), None
     else:
         u_t, u_dev = None, None
     q = ops.Quant(8, "int8", rounding, "tensor", seed, offset, u_dev)
@@ -219,18 +221,20 @@ def test_batched_backward_vs_oracle(ops, B, L, O, I, dtype, rounding):
     def u(shape, off):
         return oc.philox_bytes(seed, off, shape) if rounding == "philox" else None
     xf, wf, gof = _as_f32(x, dtype), _as_f32(w, dtype), _as_f32(go, dtype)
-    # Philox indices follow the stored layout: [B, I, L'] for the activation, [I, O] for the weight
-    u_x = u((B, I, out_len), 1)
-    u_x = None if u_x is None else np.ascontiguousarray(u_x.transpose(0, 2, 1)).view(oc.PhiloxBytes)
+    # Philox indices follow the stored layout: [I, B, pitch] for the activation, [I, O] for the weight
+    u_x = u((I, B, pitch), 1)
+    u_x = None if u_x is None else np.ascontiguousarray(u_x[:, :, :out_len].transpose(1, 2, 0)).view(oc.PhiloxBytes)
     u_w = u((I, O), 3)
     u_w = None if u_w is None else np.ascontiguousarray(u_w.T).view(oc.PhiloxBytes)
+    u_gw = u((O, B, pitch), 4)
+    u_gw = None if u_gw is None else np.ascontiguousarray(u_gw[:, :, :out_len].transpose(1, 0, 2)).view(oc.PhiloxBytes)
     mode = "stoch" if rounding == "philox" else "int"
     x_q, s_xo = oc.abc_compress_batched(xf, n_l, sel, 8, u_x, mode)
     assert np.array_equal(_bits(s_x.cpu().numpy()), _bits(s_xo))
     got_xq = x_q_t.cpu().numpy().view(np.int8).reshape(I, B, pitch)[:, :, :out_len].transpose(1, 2, 0)
     assert np.array_equal(got_xq, x_q)
     ref = oc.linear_backward_batched(gof, wf, x_q, s_xo, n_o=n_o, n_l=n_l, sel=sel, u_go=u((B, L, O), 2), u_w=u_w,
-                                     u_gw=u((B, O, out_len), 4), w_mode=mode)
+                                     u_gw=u_gw, w_mode=mode)
     tdt = dtype
     ref_gx = torch.from_numpy(ref["grad_input"]).to(tdt)
     ref_gw = torch.from_numpy(ref["grad_w"]).to(tdt)
