@@ -60,6 +60,9 @@ def parse():
                    help="instead of the step: data-parallel ViT-B/16 training step (forward, HOT backward on the 48 "
                         "block linears, DDP all-reduce, SGD), images/s, beside the same model with plain nn.Linear")
     p.add_argument("--batch", type=int, default=256, help="images per GPU for --vit-train")
+    p.add_argument("--one-layer", default=None, choices=["qkv", "proj", "fc1", "fc2"],
+                   help="run --calls HOT backward calls of one ViT-B/16 linear shape and nothing else (for ncu captures)")
+    p.add_argument("--calls", type=int, default=3)
     p.add_argument("--per-sample", action="store_true",
                    help="the reference's 3-D semantics (one scale per image) on the ViT-B/16 linear shapes")
     p.add_argument("--large-mlp", action="store_true",
@@ -344,6 +347,33 @@ def run_large_mlp(a):
     if int(status.item()) != 0:
         raise SystemExit("a bounded device-side wait ran out")
     print(json.dumps({"metric": "hot_backward_large_mlp", "tokens": M, "dtype": "bf16", "layers": out}), flush=True)
+
+
+def run_one_layer(a):
+    """--calls HOT backward calls of one ViT-B/16 linear shape at --tokens tokens: a small, fixed
+    launch sequence (per call: grad_out abs-max pass, grad_out quantise pass, weight abs-max and
+    quantise, g_x GEMM, g_w GEMM) for profiler captures."""
+    from hot_b200 import ops
+    from hot_b200.hadamard_matmul import lowrank_selection
+    device = torch.device("cuda", 0)
+    torch.cuda.set_device(device)
+    torch.manual_seed(0)
+    dtype = torch.bfloat16 if a.dtype == "bf16" else torch.float32
+    i_f, o_f = {"qkv": (768, 2304), "proj": (768, 768), "fc1": (768, 3072), "fc2": (3072, 768)}[a.one_layer]
+    L = a.tokens
+    order_l, sel = lowrank_selection(L, "half16")
+    x = torch.randn((L, i_f), device=device).to(dtype)
+    w = ((torch.rand((o_f, i_f), device=device) * 2 - 1) / i_f ** 0.5).to(dtype)
+    go = (torch.randn((L, o_f), device=device) * 1e-3).to(dtype)
+    cfg = ops.LinearConfig(order_o=16, order_l=order_l, sel_l=sel)
+    x_q_t, s_x = ops.abc_compress(x, cfg)
+    status = torch.zeros(1, dtype=torch.int32, device=device)
+    for _ in range(a.calls):
+        ops.linear_backward(go, w, x_q_t, s_x, cfg, status=status)
+    torch.cuda.synchronize(device)
+    if int(status.item()) != 0:
+        raise SystemExit("a bounded device-side wait ran out")
+    print(json.dumps({"one_layer": a.one_layer, "tokens": L, "in": i_f, "out": o_f, "dtype": a.dtype, "calls": a.calls}), flush=True)
 
 
 def run_per_sample(a):
@@ -680,6 +710,8 @@ if __name__ == "__main__":
         run_large_mlp(args)
     elif args.per_sample:
         run_per_sample(args)
+    elif args.one_layer:
+        run_one_layer(args)
     elif args.vit_train:
         run_vit_train(args)
     else:
