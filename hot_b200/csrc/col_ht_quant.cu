@@ -238,8 +238,7 @@ __global__ void __launch_bounds__(kThreads) col_ht_quant_kernel(const T* __restr
 #pragma unroll
             for (int g4 = 0; g4 < G / 4; ++g4) dst[g4] = make_float4(c[4 * g4], c[4 * g4 + 1], c[4 * g4 + 2], c[4 * g4 + 3]);
           }
-        continue;
-      }
+      } else {
 #pragma unroll
       for (int g = 0; g < G; ++g) {
 #pragma unroll
@@ -253,6 +252,7 @@ __global__ void __launch_bounds__(kThreads) col_ht_quant_kernel(const T* __restr
                 tile[((lane + 32 * vv) * CPL + qq) * p.pitch + (b + g) * r + j] = v[vv * CPL + qq][g * N + k];
           }
         }
+      }
       }
     } else {
       for (int j = 0; j < G * r; ++j)

@@ -68,18 +68,19 @@ struct SegmentIter {
   int tile, stride, num_tiles, num_kb;
   int group_kb, grp;
   long long u, end;
-  __device__ SegmentIter(const GemmParams& p, int num_tiles_) {
+  // worker / nworkers: this CTA (or CTA pair) among those that share the tiles
+  __device__ SegmentIter(const GemmParams& p, int num_tiles_, int worker, int nworkers) {
     stream_k = p.stream_k != 0;
     first = true;
     num_tiles = num_tiles_;
     num_kb = p.num_kb;
     group_kb = p.group_kb;
     grp = 0;
-    tile = blockIdx.x;
-    stride = gridDim.x;
+    tile = worker;
+    stride = nworkers;
     const long long total = (long long)num_tiles * num_kb;
-    u = total * blockIdx.x / gridDim.x;
-    end = total * (blockIdx.x + 1) / gridDim.x;
+    u = total * worker / nworkers;
+    end = total * (worker + 1) / nworkers;
   }
   __device__ bool exhausted() const { return stream_k ? u >= end : tile >= num_tiles; }
   __device__ bool next(Segment& s) {
@@ -138,6 +139,58 @@ __device__ __forceinline__ void umma_i8(uint32_t tmem_d, uint64_t adesc, uint64_
       "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+// ---- CTA pairs (cta_group::2): two CTAs of a cluster run one 256 x BN tile; each holds its own 128
+// rows of A and half of the rows of B in shared memory, the MMA is issued by the CTA of rank 0 and
+// accumulates into the tensor memory of both ----
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// shared::cluster address of the same shared-memory location in the CTA of the given rank
+__device__ __forceinline__ uint32_t mapa_rank(uint32_t addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// tile load into this CTA's shared memory whose completion is counted on a barrier of the pair's
+// rank-0 CTA (each CTA fetches only what it holds itself)
+__device__ __forceinline__ void tma_load_2d_pair(void* dst, const CUtensorMap* map, uint32_t bar_cluster_addr, int c0, int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(
+          smem_u32(dst)),
+      "l"(reinterpret_cast<uint64_t>(map)), "r"(bar_cluster_addr), "r"(c0), "r"(c1)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t* slot, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(slot)), "r"(ncols)
+               : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void umma_i8_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::i8 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// arrive on the barrier at this shared-memory offset in BOTH CTAs of the pair once the MMAs issued so far are done
+__device__ __forceinline__ void umma_commit_pair(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(
+                   smem_u32(bar)),
+               "h"((uint16_t)3)
+               : "memory");
+}
 // Arrive on an mbarrier once all MMAs issued so far by this thread have completed.
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
@@ -170,20 +223,22 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t smem_addr) {
   return d;
 }
 // Instruction descriptor: D = S32, A = B = signed 8-bit, both K-major, M = 128, N = BN.
-__host__ __device__ constexpr uint32_t instr_desc_i8(int bn) {
-  return (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(bn >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
+__host__ __device__ constexpr uint32_t instr_desc_i8(int bn, int m = kBM) {
+  return (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(bn >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
 }
 
 constexpr int kSmemMax = 227 * 1024;     // what a CTA may use
 constexpr int kEpiThreads = 256;          // two teams of four warps; a team covers the 128 accumulator rows
 constexpr int kStoreStage = 8 * 2 * 2048;  // per epilogue warp two 32-row x 64-byte output boxes
 
-template <int BN, bool A4, bool B4>
+template <int BN, bool A4, bool B4, bool PAIR = false>
 struct SmemLayout {
+  static_assert(!(PAIR && B4), "CTA pairs take B one code per byte");
+  static constexpr int kBRows = PAIR ? BN / 2 : BN;  // rows of B this CTA holds
   static constexpr int kA = kBM * kBK;       // int8 stage of A
-  static constexpr int kB = BN * kBK;        // int8 stage of B
+  static constexpr int kB = kBRows * kBK;    // int8 stage of B
   static constexpr int kRawA = A4 ? kBM * kBK / 2 : 0;
-  static constexpr int kRawB = B4 ? BN * kBK / 2 : 0;
+  static constexpr int kRawB = B4 ? kBRows * kBK / 2 : 0;
   static constexpr int kStage = kA + kB + kRawA + kRawB;
   static constexpr int kStagesFit = (kSmemMax - 1536 - kStoreStage) / kStage;
   static constexpr int kStages = kStagesFit > 8 ? 8 : kStagesFit;
@@ -304,17 +359,23 @@ __device__ __forceinline__ void store_chunk(const GemmParams& p, int row, bool r
 // share A rows and the whole of B in L2).  The shared-memory ring runs on across tiles; the
 // accumulator is double-buffered in tensor memory so the epilogue of tile i overlaps the MMAs
 // of tile i + 1.
-template <int BN, bool A4, bool B4>
+//
+// PAIR: the kernel is launched in clusters of two CTAs that work on one 256 x BN tile (see the
+// cta_group::2 wrappers above).  Both CTAs run every role on their own half; what differs is that
+// the operand loads of both are counted on barriers of the rank-0 CTA, whose MMA thread issues the
+// instructions for the pair and signals "stage free" / "accumulator complete" into both CTAs, and that
+// the rank-1 CTA reports "accumulator drained" / "operand unpacked" to the rank-0 CTA's barriers.
+template <int BN, bool A4, bool B4, bool PAIR>
 __global__ void __launch_bounds__(kEpiThreads + 64 + ((A4 || B4) ? kUnpackThreads : 0), 1)
     gemm_i8_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
                    const __grid_constant__ CUtensorMap tma_out, GemmParams p) {
-  using L = SmemLayout<BN, A4, B4>;
+  using L = SmemLayout<BN, A4, B4, PAIR>;
   constexpr int STAGES = L::kStages;
   constexpr bool kUnpack = A4 || B4;
   constexpr uint32_t kTmemCols = tmem_cols(BN);
   constexpr uint32_t kBufStride = kTmemCols / 2;
   constexpr int kShift = (A4 ? 4 : 0) + (B4 ? 4 : 0);
-  constexpr bool kGrouped = BN == 128 && !kUnpack;  // the one instance that carries the grouped-scale epilogue
+  constexpr bool kGrouped = BN == 128 && !kUnpack && !PAIR;  // the one instance that carries the grouped-scale epilogue
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   uint8_t* sA = smem + L::kOffA;
@@ -327,24 +388,33 @@ __global__ void __launch_bounds__(kEpiThreads + 64 + ((A4 || B4) ? kUnpackThread
   uint64_t* tmem_full = ready + STAGES;                              // [2] accumulator complete
   uint64_t* tmem_empty = tmem_full + 2;                              // [2] accumulator drained
   uint64_t* fix_bar = tmem_empty + 2;                                // stream-K fix-up copies landed
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(fix_bar + 1);
+  uint64_t* full_a = fix_bar + 1;                                    // PAIR with packed A: this CTA's packed A landed
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(full_a + STAGES);
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
   // warps 0-7: epilogue; INT4 operands: warps 8-15 unpack; then one producer warp and one MMA warp
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   constexpr int kProducerWarp = (kEpiThreads + (kUnpack ? kUnpackThreads : 0)) / 32, kMmaWarp = kProducerWarp + 1;
+  constexpr int kTileM = PAIR ? 2 * kBM : kBM;
   const int n_tiles = (p.N + BN - 1) / BN;
-  const int num_tiles = ((p.M + kBM - 1) / kBM) * n_tiles;
+  const int num_tiles = ((p.M + kTileM - 1) / kTileM) * n_tiles;
+  const uint32_t rank = PAIR ? cluster_ctarank() : 0u;          // 0: the CTA that issues the pair's MMAs
+  const int worker = PAIR ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;
+  const int nworkers = PAIR ? (int)(gridDim.x >> 1) : (int)gridDim.x;
+  // arrivals per phase: per thread in a single CTA; one elected lane per warp of both CTAs in a pair
+  constexpr uint32_t kDrainArrivals = PAIR ? 2 * (kEpiThreads / 32) : kEpiThreads;
+  constexpr uint32_t kUnpackArrivals = PAIR ? 2 * (kUnpackThreads / 32) : kUnpackThreads;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(&full[s], 1);
       mbar_init(&empty[s], 1);
-      mbar_init(&ready[s], kUnpackThreads);
+      mbar_init(&ready[s], kUnpackArrivals);
+      mbar_init(&full_a[s], 1);
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&tmem_full[b], 1);
-      mbar_init(&tmem_empty[b], kEpiThreads);
+      mbar_init(&tmem_empty[b], kDrainArrivals);
     }
     mbar_init(fix_bar, 1);
     *abort_flag = 0u;
@@ -353,9 +423,13 @@ __global__ void __launch_bounds__(kEpiThreads + 64 + ((A4 || B4) ? kUnpackThread
     tma_prefetch_desc(&tma_b);
     if (p.staged) tma_prefetch_desc(&tma_out);
   }
-  if (warp == kMmaWarp) tmem_alloc(tmem_slot, kTmemCols);
+  if (warp == kMmaWarp) {
+    if (PAIR) tmem_alloc_pair(tmem_slot, kTmemCols);
+    else tmem_alloc(tmem_slot, kTmemCols);
+  }
   tc_fence_before();
   __syncthreads();
+  if (PAIR) cluster_sync_all();  // the partner's barriers are initialised before anything signals them
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
@@ -364,15 +438,28 @@ __global__ void __launch_bounds__(kEpiThreads + 64 + ((A4 || B4) ? kUnpackThread
       constexpr uint32_t kTx = (A4 ? L::kRawA : L::kA) + (B4 ? L::kRawB : L::kB);
       uint32_t g = 0;  // k-block counter across tiles: ring slot g % STAGES, phase (g / STAGES) & 1
       bool ok = true;
-      SegmentIter iter(p, num_tiles);
+      SegmentIter iter(p, num_tiles, worker, nworkers);
       Segment seg;
+      const uint32_t full0 = PAIR ? mapa_rank(smem_u32(full), 0) : 0u;  // full[] of the rank-0 CTA
       while (ok && iter.next(seg)) {
-        const int m0 = (seg.tile / n_tiles) * kBM, n0 = (seg.tile % n_tiles) * BN;
+        const int m0 = (seg.tile / n_tiles) * kTileM + (int)rank * kBM, n0 = (seg.tile % n_tiles) * BN;
         for (int kb = seg.kb0; kb < seg.kb1; ++kb, ++g) {
           const int s = g % STAGES;
           const uint32_t ph = (g / STAGES) & 1u;
           ok = mbar_wait(&empty[s], ph ^ 1u, abort_flag);
           if (!ok) break;
+          if (PAIR) {
+            // rank 0 announces the bytes of both CTAs; each CTA loads its rows of A and its half of B
+            if (rank == 0) mbar_expect_tx(&full[s], 2u * ((A4 ? 0u : (uint32_t)L::kA) + (uint32_t)L::kB));
+            if (A4) {
+              mbar_expect_tx(&full_a[s], L::kRawA);
+              tma_load_2d(rawA + s * L::kRawA, &tma_a, &full_a[s], kb * (kBK / 2), m0);
+            } else {
+              tma_load_2d_pair(sA + s * L::kA, &tma_a, full0 + 8u * s, kb * kBK, m0);
+            }
+            tma_load_2d_pair(sB + s * L::kB, &tma_b, full0 + 8u * s, kb * kBK, n0 + (int)rank * (BN / 2));
+            continue;
+          }
           mbar_expect_tx(&full[s], kTx);
           if (A4) tma_load_2d(rawA + s * L::kRawA, &tma_a, &full[s], kb * (kBK / 2), m0);
           else tma_load_2d(sA + s * L::kA, &tma_a, &full[s], kb * kBK, m0);
@@ -382,32 +469,42 @@ __global__ void __launch_bounds__(kEpiThreads + 64 + ((A4 || B4) ? kUnpackThread
       }
     }
   } else if (warp == kMmaWarp) {
-    if (lane == 0) {
-      constexpr uint32_t idesc = instr_desc_i8(BN);
+    if (lane == 0 && rank == 0) {
+      constexpr uint32_t idesc = instr_desc_i8(BN, kTileM);
       uint32_t g = 0, it = 0;
       bool ok = true;
-      SegmentIter iter(p, num_tiles);
+      SegmentIter iter(p, num_tiles, worker, nworkers);
       Segment seg;
       for (; ok && iter.next(seg); ++it) {
         const uint32_t buf = it & 1u, bph = (it >> 1) & 1u;
-        ok = mbar_wait(&tmem_empty[buf], bph ^ 1u, abort_flag);  // epilogue drained this buffer
+        ok = mbar_wait<PAIR>(&tmem_empty[buf], bph ^ 1u, abort_flag);  // epilogue (of both CTAs) drained this buffer
         if (!ok) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + buf * kBufStride;
         for (int kb = seg.kb0; kb < seg.kb1; ++kb, ++g) {
           const int s = g % STAGES;
           const uint32_t ph = (g / STAGES) & 1u;
-          ok = mbar_wait(kUnpack ? &ready[s] : &full[s], ph, abort_flag);
+          ok = kUnpack ? mbar_wait<PAIR>(&ready[s], ph, abort_flag) : mbar_wait(&full[s], ph, abort_flag);
+          if (ok && PAIR && kUnpack) ok = mbar_wait(&full[s], ph, abort_flag);  // B landed in both CTAs
           if (!ok) break;
           tc_fence_after();
           const uint32_t a_addr = smem_u32(sA + s * L::kA), b_addr = smem_u32(sB + s * L::kB);
 #pragma unroll
-          for (int k4 = 0; k4 < kBK / 32; ++k4)
-            umma_i8(d_tmem, smem_desc_sw128(a_addr + k4 * 32), smem_desc_sw128(b_addr + k4 * 32), idesc,
-                    (kb > seg.kb0 || k4 > 0) ? 1u : 0u);
-          umma_commit(&empty[s]);
+          for (int k4 = 0; k4 < kBK / 32; ++k4) {
+            if (PAIR)
+              umma_i8_pair(d_tmem, smem_desc_sw128(a_addr + k4 * 32), smem_desc_sw128(b_addr + k4 * 32), idesc,
+                           (kb > seg.kb0 || k4 > 0) ? 1u : 0u);
+            else
+              umma_i8(d_tmem, smem_desc_sw128(a_addr + k4 * 32), smem_desc_sw128(b_addr + k4 * 32), idesc,
+                      (kb > seg.kb0 || k4 > 0) ? 1u : 0u);
+          }
+          if (PAIR) umma_commit_pair(&empty[s]);
+          else umma_commit(&empty[s]);
         }
-        if (ok) umma_commit(&tmem_full[buf]);
+        if (ok) {
+          if (PAIR) umma_commit_pair(&tmem_full[buf]);
+          else umma_commit(&tmem_full[buf]);
+        }
       }
     }
   } else if (warp < kEpiThreads / 32) {
@@ -422,7 +519,7 @@ __global__ void __launch_bounds__(kEpiThreads + 64 + ((A4 || B4) ? kUnpackThread
     __shared__ uint32_t s_finisher;
     uint32_t it = 0;
     bool ok = true;
-    SegmentIter iter(p, num_tiles);
+    SegmentIter iter(p, num_tiles, worker, nworkers);
     Segment seg;
     // Output path: a thread holds one row of the accumulator, so stores from registers would touch 32
     // lines per instruction.  Instead each warp lays 32 rows x 64 bytes out in a swizzled shared-memory
@@ -433,6 +530,17 @@ __global__ void __launch_bounds__(kEpiThreads + 64 + ((A4 || B4) ? kUnpackThread
     float run[kGrouped ? BN / 64 : 1][32];  // grouped mode only
     const bool out16 = p.out_dtype == HOT_BF16;
     auto owns = [&](int c) { return (c & 1) == team; };  // chunk c is this team's
+    const uint32_t drained0 = PAIR ? mapa_rank(smem_u32(tmem_empty), 0) : 0u;  // tmem_empty[] of the rank-0 CTA
+    // this thread has read all it needs of accumulator buffer `b`
+    auto release_acc = [&](uint32_t b) {
+      tc_fence_before();
+      if (PAIR) {
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(drained0 + 8u * b);
+      } else {
+        mbar_arrive(&tmem_empty[b]);
+      }
+    };
     int m0 = 0, n0 = 0, row = 0;
     bool row_ok = false;
     float sa = 0.0f;
@@ -515,7 +623,7 @@ __global__ void __launch_bounds__(kEpiThreads + 64 + ((A4 || B4) ? kUnpackThread
       }
     };
     for (; ok && iter.next(seg); ++it) {
-      m0 = (seg.tile / n_tiles) * kBM;
+      m0 = (seg.tile / n_tiles) * kTileM + (int)rank * kBM;
       n0 = (seg.tile % n_tiles) * BN;
       const uint32_t buf = it & 1u, bph = (it >> 1) & 1u;
       const int row_loc = q * 32 + lane;
@@ -536,10 +644,7 @@ __global__ void __launch_bounds__(kEpiThreads + 64 + ((A4 || B4) ? kUnpackThread
         for (int k = 0; k < BN / 64; ++k) {
           uint32_t acc[32];
           tmem_ld32(t_addr + (uint32_t)((2 * k + team) * 32), acc);
-          if (k == BN / 64 - 1) {
-            tc_fence_before();
-            mbar_arrive(&tmem_empty[buf]);
-          }
+          if (k == BN / 64 - 1) release_acc(buf);
 #pragma unroll
           for (int i = 0; i < 32; ++i) {
             const float v = __fmul_rn(__fmul_rn((float)(int)acc[i], ga), gb);
@@ -556,19 +661,13 @@ __global__ void __launch_bounds__(kEpiThreads + 64 + ((A4 || B4) ? kUnpackThread
       }
       int c_last = BN / 32 - 1;  // last chunk this team reads
       while (c_last >= 0 && !owns(c_last)) --c_last;
-      if (c_last < 0) {
-        tc_fence_before();
-        mbar_arrive(&tmem_empty[buf]);
-      }
+      if (c_last < 0) release_acc(buf);
 #pragma unroll 1
       for (int c = 0; c <= c_last; ++c) {
         if (!owns(c)) continue;
         uint32_t acc[32];
         tmem_ld32(t_addr + (uint32_t)(c * 32), acc);
-        if (c == c_last) {  // everything this thread needs of the buffer is in registers: hand it back
-          tc_fence_before();
-          mbar_arrive(&tmem_empty[buf]);
-        }
+        if (c == c_last) release_acc(buf);  // everything this thread needs of the buffer is in registers
         if (whole) {
           emit(c, acc);
         } else {
@@ -674,29 +773,37 @@ __global__ void __launch_bounds__(kEpiThreads + 64 + ((A4 || B4) ? kUnpackThread
     // ---- unpack warps (INT4 operands): raw stage -> swizzled int8 stage ----
     asm volatile("setmaxnreg.dec.sync.aligned.u32 40;" ::: "memory");
     const int utid = threadIdx.x - kEpiThreads;
+    const uint32_t ready0 = PAIR ? mapa_rank(smem_u32(ready), 0) : 0u;  // ready[] of the rank-0 CTA
     uint32_t g = 0;
     bool ok = true;
-    SegmentIter iter(p, num_tiles);
+    SegmentIter iter(p, num_tiles, worker, nworkers);
     Segment seg;
     while (ok && iter.next(seg)) {
       for (int kb = seg.kb0; kb < seg.kb1; ++kb, ++g) {
         const int s = g % STAGES;
         const uint32_t ph = (g / STAGES) & 1u;
-        ok = mbar_wait(&full[s], ph, abort_flag);
+        ok = mbar_wait(PAIR ? &full_a[s] : &full[s], ph, abort_flag);
         if (!ok) break;
         if (A4) unpack_stage(rawA + s * L::kRawA, sA + s * L::kA, kBM, utid, kUnpackThreads);
         if (B4) unpack_stage(rawB + s * L::kRawB, sB + s * L::kB, BN, utid, kUnpackThreads);
         fence_proxy_async_smem();  // generic-proxy writes -> visible to the tensor core (async proxy)
-        mbar_arrive(&ready[s]);
+        if (PAIR) {
+          __syncwarp();
+          if (lane == 0) mbar_arrive_cluster(ready0 + 8u * s);
+        } else {
+          mbar_arrive(&ready[s]);
+        }
       }
     }
   }
 
   tc_fence_before();
   __syncthreads();
+  if (PAIR) cluster_sync_all();  // neither CTA leaves, or frees tensor memory, while the other may still use it
   if (warp == kMmaWarp) {
     tc_fence_after();
-    tmem_dealloc(tmem_base, kTmemCols);
+    if (PAIR) tmem_dealloc_pair(tmem_base, kTmemCols);
+    else tmem_dealloc(tmem_base, kTmemCols);
   }
   if (threadIdx.x == 0 && *abort_flag) {
     if (p.status) atomicOr(p.status, 1u);
@@ -713,18 +820,19 @@ struct Plan {
   int bn;
   bool stream_k;
   unsigned grid;
+  bool pair = false;  // clusters of two CTAs per 256 x bn tile
 };
 
-template <int BN, bool A4, bool B4>
+template <int BN, bool A4, bool B4, bool PAIR = false>
 int launch_gemm(const void* a, int64_t lda, const void* b, int64_t ldb, const GemmParams& p, const Plan& plan, cudaStream_t st) {
-  using L = SmemLayout<BN, A4, B4>;
+  using L = SmemLayout<BN, A4, B4, PAIR>;
   CUtensorMap ma, mb;
   int rc;
   if (A4) rc = make_map(&ma, a, p.M, (p.K + 1) / 2, lda, kBK / 2, kBM, 0);
   else rc = make_map(&ma, a, p.M, p.K, lda, kBK, kBM, 128);
   if (rc) return rc;
-  if (B4) rc = make_map(&mb, b, p.N, (p.K + 1) / 2, ldb, kBK / 2, BN, 0);
-  else rc = make_map(&mb, b, p.N, p.K, ldb, kBK, BN, 128);
+  if (B4) rc = make_map(&mb, b, p.N, (p.K + 1) / 2, ldb, kBK / 2, L::kBRows, 0);
+  else rc = make_map(&mb, b, p.N, p.K, ldb, kBK, L::kBRows, 128);
   if (rc) return rc;
   // output as a byte matrix for the bulk tensor stores; otherwise the epilogue stores from registers
   const int64_t esz = p.out_dtype == HOT_BF16 ? 2 : 4;
@@ -735,7 +843,7 @@ int launch_gemm(const void* a, int64_t lda, const void* b, int64_t ldb, const Ge
     rc = make_map(&mo, p.out, p.M, (int64_t)p.N * esz, p.ldo * esz, 64, 32, 64);
     if (rc) return rc;
   }
-  auto kernel = gemm_i8_kernel<BN, A4, B4>;
+  auto kernel = gemm_i8_kernel<BN, A4, B4, PAIR>;
   static bool attr_set = false;  // per instantiation
   if (!attr_set) {
     HOT_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kBytes));
@@ -748,7 +856,24 @@ int launch_gemm(const void* a, int64_t lda, const void* b, int64_t ldb, const Ge
     }
     attr_set = true;
   }
-  kernel<<<plan.grid, kEpiThreads + 64 + ((A4 || B4) ? kUnpackThreads : 0), L::kBytes, st>>>(ma, mb, mo, pp);
+  constexpr unsigned kThreads = kEpiThreads + 64 + ((A4 || B4) ? kUnpackThreads : 0);
+  if (PAIR) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(plan.grid);
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = L::kBytes;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    HOT_CUDA(cudaLaunchKernelEx(&cfg, kernel, ma, mb, mo, pp));
+  } else {
+    kernel<<<plan.grid, kThreads, L::kBytes, st>>>(ma, mb, mo, pp);
+  }
   HOT_CUDA(cudaGetLastError());
   return HOT_OK;
 }
@@ -765,24 +890,44 @@ inline size_t sk_bytes(int sms, int bn, int64_t tiles) {
 // through bulk copies into the idle operand ring).  Measured, that costs ~14 us + ~3.5 us per
 // contributor at bn = 256, charged below in k-block equivalents, so stream-K is picked only for
 // few-tile, very-long-K problems.
-Plan make_plan(int M, int N, int num_kb, int sms, size_t ws_bytes) {
+Plan make_plan(int M, int N, int num_kb, int sms, size_t ws_bytes, bool allow_pair, bool packed) {
   const int cands[4] = {256, 192, 128, 64};
   Plan best{128, false, 1};
   double best_cost = -1.0;
   // HOT_GEMM_SCHEDULE=streamk forces the stream-K schedule wherever it is possible (tests, tuning)
   const char* env = getenv("HOT_GEMM_SCHEDULE");
   const bool force_sk = env && env[0] == 's';
+  // HOT_GEMM_PAIR=0 never uses CTA pairs, =1 always does where the operands allow
+  const char* penv = getenv("HOT_GEMM_PAIR");
+  const int pair_mode = !allow_pair ? 0 : (penv ? (penv[0] == '1' ? 2 : (penv[0] == '0' ? 0 : 1)) : 1);
   for (int bn : cands) {
     const int64_t tiles = tiles_for(M, N, bn);
     const int64_t waves = (tiles + sms - 1) / sms;
     const double per_kb = bn + 400.0;
     const double dp = (double)waves * num_kb * per_kb;
-    if (best_cost < 0 || dp < best_cost) {
+    if (pair_mode != 2 && (best_cost < 0 || dp < best_cost)) {
       best_cost = dp;
       best = Plan{bn, false, (unsigned)(tiles < sms ? tiles : sms)};
     }
+    if (pair_mode != 0) {
+      // A pair of CTAs per 256 x bn tile: each CTA holds half of B.  Measured on B200 (int8 x int8): 8 % faster
+      // than single CTAs at 16384 x 4096 x 11008 (3.18 POP/s), where a CTA runs a dozen long tiles, and
+      // 4-16 % slower at ViT sizes (the hand-shakes between the two CTAs cost more per tile than the
+      // halved B traffic saves); with a packed INT4 operand the partner's "unpacked" signal crosses
+      // the cluster every k-block and the pair is twice as slow.  So pairs are taken for wide tiles of
+      // long, many-tile problems with one-byte codes only, unless forced.
+      const int64_t ptiles = (int64_t)((M + 2 * kBM - 1) / (2 * kBM)) * ((N + bn - 1) / bn);
+      const int64_t pairs = sms / 2;
+      const int64_t pwaves = (ptiles + pairs - 1) / pairs;
+      const bool pays = !packed && bn == 256 && num_kb >= 64 && ptiles >= 4 * pairs;
+      const double pc = (pair_mode == 2 || pays) ? (double)pwaves * num_kb * 0.92 * per_kb : 1e300;
+      if (best_cost < 0 || pc < best_cost) {
+        best_cost = pc;
+        best = Plan{bn, false, (unsigned)(2 * (ptiles < pairs ? ptiles : pairs)), true};
+      }
+    }
     const int64_t units = tiles * num_kb;
-    if (ws_bytes >= sk_bytes(sms, bn, tiles) && units >= 2 * (int64_t)sms && tiles % sms != 0) {
+    if (pair_mode != 2 && ws_bytes >= sk_bytes(sms, bn, tiles) && units >= 2 * (int64_t)sms && tiles % sms != 0) {
       const double share = (double)units / sms;
       const double contributors = 1.0 + (double)num_kb / share;
       const double sk = (share + (32.0 + 8.0 * contributors) * bn / 256.0) * per_kb;
@@ -797,6 +942,16 @@ Plan make_plan(int M, int N, int num_kb, int sms, size_t ws_bytes) {
 
 template <bool A4, bool B4>
 int launch_bn(const void* a, int64_t lda, const void* b, int64_t ldb, const GemmParams& p, const Plan& plan, cudaStream_t st) {
+  if constexpr (!B4) {
+    if (plan.pair) {
+      switch (plan.bn) {
+        case 256: return launch_gemm<256, A4, false, true>(a, lda, b, ldb, p, plan, st);
+        case 192: return launch_gemm<192, A4, false, true>(a, lda, b, ldb, p, plan, st);
+        case 64: return launch_gemm<64, A4, false, true>(a, lda, b, ldb, p, plan, st);
+        default: return launch_gemm<128, A4, false, true>(a, lda, b, ldb, p, plan, st);
+      }
+    }
+  }
   switch (plan.bn) {
     case 256: return launch_gemm<256, A4, B4>(a, lda, b, ldb, p, plan, st);
     case 192: return launch_gemm<192, A4, B4>(a, lda, b, ldb, p, plan, st);
@@ -859,7 +1014,7 @@ extern "C" int hot_gemm_i8_ws(const void* a, int a_storage, int64_t lda, const v
   const int sms = device_sm_count();
   if (sms <= 0) return HOT_ERR_CUDA;
   if (workspace && ((uintptr_t)workspace) % 16 != 0) HOT_FAIL(HOT_ERR_ARG, "hot_gemm_i8_ws: workspace must be 16-byte aligned");
-  const Plan plan = make_plan(p.M, p.N, p.num_kb, sms, workspace ? workspace_bytes : 0);
+  const Plan plan = make_plan(p.M, p.N, p.num_kb, sms, workspace ? workspace_bytes : 0, !b4, a4 || b4);
   p.stream_k = plan.stream_k ? 1 : 0;
   p.sk_partials = nullptr;
   p.sk_counters = nullptr;

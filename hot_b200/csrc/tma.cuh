@@ -28,15 +28,27 @@ __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
+// CLUSTER: acquire at cluster scope, for a barrier that threads of the partner CTA arrive on
+template <bool CLUSTER = false>
 __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok)
-      : "r"(smem_u32(bar)), "r"(parity)
-      : "memory");
+  if (CLUSTER) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+  } else {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+  }
   return ok != 0;
 }
 __device__ __forceinline__ uint64_t global_timer_ns() {
@@ -45,11 +57,12 @@ __device__ __forceinline__ uint64_t global_timer_ns() {
   return t;
 }
 // Bounded wait.  Returns false when it gave up (time limit, or another role already aborted).
+template <bool CLUSTER = false>
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag) {
-  if (mbar_try_wait(bar, parity)) return true;
+  if (mbar_try_wait<CLUSTER>(bar, parity)) return true;
   const uint64_t t0 = global_timer_ns();
   for (uint32_t it = 1;; ++it) {
-    if (mbar_try_wait(bar, parity)) return true;
+    if (mbar_try_wait<CLUSTER>(bar, parity)) return true;
     if ((it & 63u) == 0) {
       if (*abort_flag) return false;
       if (global_timer_ns() - t0 > kWaitLimitNs) {

@@ -127,10 +127,13 @@ GEMM_CASES = [
 
 @pytest.mark.parametrize("M,N,K", GEMM_CASES)
 @pytest.mark.parametrize("a_storage,b_storage", [("int8", "int8"), ("int4", "int4"), ("int4", "int8"), ("int8", "int4")])
-@pytest.mark.parametrize("stream_k", [False, True])
-def test_gemm_i8_accumulators_and_dequant(ops, M, N, K, a_storage, b_storage, stream_k, monkeypatch):
+@pytest.mark.parametrize("schedule", ["tiles", "streamk", "pairs"])
+def test_gemm_i8_accumulators_and_dequant(ops, M, N, K, a_storage, b_storage, schedule, monkeypatch):
+    stream_k = schedule == "streamk"
     if stream_k:   # the cost model rarely picks stream-K at test sizes: force it wherever it applies
         monkeypatch.setenv("HOT_GEMM_SCHEDULE", "streamk")
+    # CTA pairs (two CTAs per 256-row tile) are chosen by cost too: force them on, or off
+    monkeypatch.setenv("HOT_GEMM_PAIR", "1" if schedule == "pairs" else "0")
     rng = np.random.default_rng(M + N + K)
 
     def make(rows, storage):
