@@ -436,16 +436,14 @@ __global__ void __launch_bounds__(kEpiThreads + 64 + ((A4 || B4) ? kUnpackThread
   if (warp == kProducerWarp) {
     if (lane == 0) {
       constexpr uint32_t kTx = (A4 ? L::kRawA : L::kA) + (B4 ? L::kRawB : L::kB);
-      uint32_t g = 0;  // k-block counter across tiles: ring slot g % STAGES, phase (g / STAGES) & 1
+      uint32_t s = 0, ph = 0;  // ring slot and phase, running on across tiles
       bool ok = true;
       SegmentIter iter(p, num_tiles, worker, nworkers);
       Segment seg;
       const uint32_t full0 = PAIR ? mapa_rank(smem_u32(full), 0) : 0u;  // full[] of the rank-0 CTA
       while (ok && iter.next(seg)) {
         const int m0 = (seg.tile / n_tiles) * kTileM + (int)rank * kBM, n0 = (seg.tile % n_tiles) * BN;
-        for (int kb = seg.kb0; kb < seg.kb1; ++kb, ++g) {
-          const int s = g % STAGES;
-          const uint32_t ph = (g / STAGES) & 1u;
+        for (int kb = seg.kb0; kb < seg.kb1; ++kb, s = (s + 1 == STAGES ? 0 : s + 1), ph ^= (s == 0 ? 1u : 0u)) {
           ok = mbar_wait(&empty[s], ph ^ 1u, abort_flag);
           if (!ok) break;
           if (PAIR) {
@@ -471,32 +469,31 @@ __global__ void __launch_bounds__(kEpiThreads + 64 + ((A4 || B4) ? kUnpackThread
   } else if (warp == kMmaWarp) {
     if (lane == 0 && rank == 0) {
       constexpr uint32_t idesc = instr_desc_i8(BN, kTileM);
-      uint32_t g = 0, it = 0;
+      uint32_t s = 0, ph = 0, it = 0;
       bool ok = true;
       SegmentIter iter(p, num_tiles, worker, nworkers);
       Segment seg;
+      // shared-memory descriptors: the high word is the same for every operand slab, the low word is
+      // (address >> 4) | leading-offset field and moves by 2 per 32-byte K step
+      const uint32_t desc_hi = (uint32_t)(smem_desc_sw128(0) >> 32);
+      const uint32_t a_lo0 = (uint32_t)smem_desc_sw128(smem_u32(sA)), b_lo0 = (uint32_t)smem_desc_sw128(smem_u32(sB));
       for (; ok && iter.next(seg); ++it) {
         const uint32_t buf = it & 1u, bph = (it >> 1) & 1u;
         ok = mbar_wait<PAIR>(&tmem_empty[buf], bph ^ 1u, abort_flag);  // epilogue (of both CTAs) drained this buffer
         if (!ok) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + buf * kBufStride;
-        for (int kb = seg.kb0; kb < seg.kb1; ++kb, ++g) {
-          const int s = g % STAGES;
-          const uint32_t ph = (g / STAGES) & 1u;
+        for (int kb = seg.kb0; kb < seg.kb1; ++kb, s = (s + 1 == STAGES ? 0 : s + 1), ph ^= (s == 0 ? 1u : 0u)) {
           ok = kUnpack ? mbar_wait<PAIR>(&ready[s], ph, abort_flag) : mbar_wait(&full[s], ph, abort_flag);
           if (ok && PAIR && kUnpack) ok = mbar_wait(&full[s], ph, abort_flag);  // B landed in both CTAs
           if (!ok) break;
           tc_fence_after();
-          const uint32_t a_addr = smem_u32(sA + s * L::kA), b_addr = smem_u32(sB + s * L::kB);
+          const uint32_t a_lo = a_lo0 + s * (uint32_t)(L::kA >> 4), b_lo = b_lo0 + s * (uint32_t)(L::kB >> 4);
 #pragma unroll
           for (int k4 = 0; k4 < kBK / 32; ++k4) {
-            if (PAIR)
-              umma_i8_pair(d_tmem, smem_desc_sw128(a_addr + k4 * 32), smem_desc_sw128(b_addr + k4 * 32), idesc,
-                           (kb > seg.kb0 || k4 > 0) ? 1u : 0u);
-            else
-              umma_i8(d_tmem, smem_desc_sw128(a_addr + k4 * 32), smem_desc_sw128(b_addr + k4 * 32), idesc,
-                      (kb > seg.kb0 || k4 > 0) ? 1u : 0u);
+            const uint64_t ad = ((uint64_t)desc_hi << 32) | (a_lo + 2u * k4), bd = ((uint64_t)desc_hi << 32) | (b_lo + 2u * k4);
+            if (PAIR) umma_i8_pair(d_tmem, ad, bd, idesc, (kb > seg.kb0 || k4 > 0) ? 1u : 0u);
+            else umma_i8(d_tmem, ad, bd, idesc, (kb > seg.kb0 || k4 > 0) ? 1u : 0u);
           }
           if (PAIR) umma_commit_pair(&empty[s]);
           else umma_commit(&empty[s]);
@@ -774,14 +771,12 @@ __global__ void __launch_bounds__(kEpiThreads + 64 + ((A4 || B4) ? kUnpackThread
     asm volatile("setmaxnreg.dec.sync.aligned.u32 40;" ::: "memory");
     const int utid = threadIdx.x - kEpiThreads;
     const uint32_t ready0 = PAIR ? mapa_rank(smem_u32(ready), 0) : 0u;  // ready[] of the rank-0 CTA
-    uint32_t g = 0;
+    uint32_t s = 0, ph = 0;
     bool ok = true;
     SegmentIter iter(p, num_tiles, worker, nworkers);
     Segment seg;
     while (ok && iter.next(seg)) {
-      for (int kb = seg.kb0; kb < seg.kb1; ++kb, ++g) {
-        const int s = g % STAGES;
-        const uint32_t ph = (g / STAGES) & 1u;
+      for (int kb = seg.kb0; kb < seg.kb1; ++kb, s = (s + 1 == STAGES ? 0 : s + 1), ph ^= (s == 0 ? 1u : 0u)) {
         ok = mbar_wait(PAIR ? &full_a[s] : &full[s], ph, abort_flag);
         if (!ok) break;
         if (A4) unpack_stage(rawA + s * L::kRawA, sA + s * L::kA, kBM, utid, kUnpackThreads);
