@@ -156,11 +156,24 @@ def _operand(kind: str, scheme, bits: int, what: str, row_ok: bool) -> ops.Quant
     return ops.Quant(int(bits), _storage(int(bits)), rounding, scale, _seed(), _next_offset())
 
 
+_BUILT_SCHEMES = ("gih_gwlr", "hadamard")
+
+
+def _token_basis(a, tokens: int, preset):
+    """(n, sel) of the token-side transform of the configured scheme: the low-rank rows of make_WHT
+    (or the preset) for ``gih_gwlr``; every row of the block Hadamard matrix H_n, n = min(16, 2-adic
+    part of the token count), for ``hadamard`` (utils/quant_matmul.py:353-355, make_hadamard)."""
+    if a.transform_scheme == "hadamard":
+        n = biggest_power2_factor_max16(tokens)
+        return n, list(range(n))
+    return lowrank_selection(tokens, preset, a.vectorPercentile)
+
+
 def _check_scheme(a) -> None:
-    if a.transform_scheme != "gih_gwlr":
-        if a.transform_scheme in ("hadamard", "low_rank", "gilr_gwh", "gilro_gwh"):
-            raise NotImplementedError("transform_scheme %r is not built on the native path (only 'gih_gwlr')"
-                                      % a.transform_scheme)
+    if a.transform_scheme not in _BUILT_SCHEMES:
+        if a.transform_scheme in ("low_rank", "gilr_gwh", "gilro_gwh"):
+            raise NotImplementedError("transform_scheme %r is not built on the native path (built: %s)"
+                                      % (a.transform_scheme, ", ".join(_BUILT_SCHEMES)))
         raise Exception("args.transform_scheme not implemented: " + str(a.transform_scheme))
     if not (a.TransformGogi and a.TransformWgt and a.TransformGogw and a.TransformInput):
         raise NotImplementedError("the native path needs TransformGogi/Wgt/Gogw/Input all True")
@@ -278,7 +291,7 @@ class HQ_Linear(nn.Linear):
         _check_scheme_name(a)
         self.register_buffer("hadamard_out", torch.tensor(TD.get_or_register("hadamard", self.out_features),
                                                           dtype=self.weight.dtype))
-        n, sel = lowrank_selection(max(int(a.BATCH_SIZE), 1), None, a.vectorPercentile)
+        n, sel = _token_basis(a, max(int(a.BATCH_SIZE), 1), None)
         self.register_buffer("hadamard_bs", self._basis(n, sel, self.weight.device))
         self._bs_tokens = None
         self.layer_name = " "
@@ -294,10 +307,11 @@ class HQ_Linear(nn.Linear):
         tokens = input.shape[0] if input.dim() == 2 else input.shape[0] * input.shape[1]
         if input.dim() == 3 and getattr(a, "lowRankPreset", None) is None:
             tokens = input.shape[1]   # the reference sizes the basis from the per-sample length
-        if tokens != self._bs_tokens or self.hadamard_bs.device != self.weight.device:
-            n, sel = lowrank_selection(tokens, getattr(a, "lowRankPreset", None), a.vectorPercentile)
+        key = (tokens, a.transform_scheme, getattr(a, "lowRankPreset", None), a.vectorPercentile)
+        if key != self._bs_tokens or self.hadamard_bs.device != self.weight.device:
+            n, sel = _token_basis(a, tokens, getattr(a, "lowRankPreset", None))
             self.hadamard_bs = self._basis(n, sel, self.weight.device)
-            self._bs_tokens = tokens
+            self._bs_tokens = key
         output = FLinearQ.apply(input, self.weight, self.hadamard_out, self.hadamard_bs, self.layer_name)
         if self.bias is not None:
             output += self.bias.to(output.device)
@@ -331,11 +345,12 @@ class HQ_Conv2d(nn.Conv2d):
         weight = self.weight.view(self.weight.size(0), -1)
         preset = getattr(a, "lowRankPreset", None)
         tokens = cols.shape[1] if preset is None else cols.shape[0] * cols.shape[1]
-        if tokens != self._bs_tokens or self.hadamard_bs.device != self.weight.device:
+        key = (tokens, a.transform_scheme, preset, a.vectorPercentile)
+        if key != self._bs_tokens or self.hadamard_bs.device != self.weight.device:
             from .hadamard_matmul import hadamard
-            n, sel = lowrank_selection(tokens, preset, a.vectorPercentile)
+            n, sel = _token_basis(a, tokens, preset)
             self.hadamard_bs = torch.tensor(hadamard(n)[sel], dtype=self.weight.dtype, device=self.weight.device)
-            self._bs_tokens = tokens
+            self._bs_tokens = key
         out = FLinearQ.apply(cols, weight, self.hadamard_out, self.hadamard_bs, self.layer_name)   # [B, H'*W', C_out]
         h_out = (input.shape[-2] + 2 * self.padding[0] - self.dilation[0] * (self.kernel_size[0] - 1) - 1) // self.stride[0] + 1
         w_out = (input.shape[-1] + 2 * self.padding[1] - self.dilation[1] * (self.kernel_size[1] - 1) - 1) // self.stride[1] + 1
@@ -348,9 +363,9 @@ class HQ_Conv2d(nn.Conv2d):
 def _check_scheme_name(a) -> None:
     if a.transform_scheme not in ("hadamard", "low_rank", "gilr_gwh", "gilro_gwh", "gih_gwlr"):
         raise Exception("Transformation method not implemented: " + str(a.transform_scheme))
-    if a.transform_scheme != "gih_gwlr":
-        raise NotImplementedError("transform_scheme %r is not built on the native path (only 'gih_gwlr')"
-                                  % a.transform_scheme)
+    if a.transform_scheme not in _BUILT_SCHEMES:
+        raise NotImplementedError("transform_scheme %r is not built on the native path (built: %s)"
+                                  % (a.transform_scheme, ", ".join(_BUILT_SCHEMES)))
 
 
 def replace_layers(model: nn.Module, old, new) -> None:

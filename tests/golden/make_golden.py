@@ -169,7 +169,46 @@ def main(ref_root: str, out_dir: str):
         l[tag + "_gx"] = np.array(choice)
     np.savez_compressed(os.path.join(out_dir, "lqs.npz"), **l)
     batched(ref_args, hm, qm, out_dir)
+    scheme_hadamard(ref_args, hm, qm, out_dir)
     print("golden vectors written to", out_dir)
+
+
+def scheme_hadamard(ref_args, hm, qm, out_dir: str):
+    """FLinearQ under transform_scheme "hadamard": block Hadamard along the tokens (all rows kept)
+    instead of the low-rank projection (utils/quant_matmul.py:183-184, 229-230, 261-262, 294-295, 330-331)."""
+    rng = np.random.default_rng(20250323)
+    T = torch.from_numpy
+    L, O, I = 48, 96, 32
+    ref_args.transform_scheme = "hadamard"
+    ref_args.TransformGogi = ref_args.TransformWgt = ref_args.TransformGogw = ref_args.TransformInput = True
+    ref_args.GogiQuantBit, ref_args.weightQuantBit, ref_args.GogwQuantBit, ref_args.actQuantBit = 4, 4, 8, 8
+    ref_args.quantBWDGogi = ref_args.quantBWDWgt = ref_args.quantBWDGogw = ref_args.quantBWDAct = "stoch"
+    ref_args.quantAuto = False
+    xx = rng.standard_normal((L, I)).astype(np.float32)
+    xx[:, 5] *= 15.0
+    ww = ((rng.random((O, I)) * 2 - 1) / np.sqrt(I)).astype(np.float32)
+    go = (rng.standard_normal((L, O)) * 1e-3).astype(np.float32)
+    h_out = torch.tensor(hm.make_hadamard(O), dtype=torch.float32)
+    pm = hm.make_hadamard(L)                                           # [16, 16] for 48 tokens
+    h_bs = torch.tensor(pm, dtype=torch.float32)
+    u_x = rng.random((L, I), dtype=np.float32)
+    u_go = rng.random((L, O), dtype=np.float32)
+    u_w = rng.random((O, I), dtype=np.float32)
+    u_gw = rng.random((O, L), dtype=np.float32)
+    xt = T(xx).requires_grad_(True)
+    wt = T(ww).requires_grad_(True)
+    try:
+        with NoiseQueue() as nq:
+            nq.queue += [T(u_x), T(u_go), T(u_w), T(u_gw)]
+            y = qm.FLinearQ.apply(xt, wt, h_out, h_bs, "layer")
+            saved = y.grad_fn.saved_tensors
+            y.backward(T(go))
+            assert not nq.queue
+    finally:
+        ref_args.transform_scheme = "gih_gwlr"
+    f = dict(x=xx, w=ww, go=go, p=pm.astype(np.int8), u_x=u_x, u_go=u_go, u_w=u_w, u_gw=u_gw, y=y.detach().numpy(),
+             x_q=saved[0].numpy(), scale_x=saved[4].numpy(), grad_input=xt.grad.numpy(), grad_w=wt.grad.numpy())
+    np.savez_compressed(os.path.join(out_dir, "flinearq_hadamard.npz"), **f)
 
 
 def batched(ref_args, hm, qm, out_dir: str):

@@ -92,6 +92,41 @@ def test_hq_linear_3d_and_reference_low_rank_basis(hot):
     assert tuple(lin.hadamard_bs.shape) == (1, 1)
 
 
+def test_hq_linear_scheme_hadamard(hot):
+    """transform_scheme "hadamard": full block Hadamard along the tokens; against the oracle bit for
+    bit with nearest rounding, and against the reference's own run (golden, explicit noise)."""
+    args, qm = hot
+    args.transform_scheme = "hadamard"
+    args.lowRankPreset = None
+    args.quantBWDGogi = args.quantBWDWgt = args.quantBWDGogw = args.quantBWDAct = "int"
+    torch.manual_seed(5)
+    L, I, O = 208, 64, 96                                        # 208 = 16 * 13 tokens
+    lin = qm.HQ_Linear(I, O, bias=False).cuda()
+    x = torch.randn(L, I, device="cuda", requires_grad=True)
+    go = torch.randn(L, O, device="cuda") * 1e-3
+    lin(x).backward(go)
+    assert tuple(lin.hadamard_bs.shape) == (16, 16)
+    sel = np.arange(16)
+    xq, sx = oc.abc_compress(x.detach().cpu().numpy(), 16, sel, 8, None, "int")
+    ref = oc.linear_backward(go.cpu().numpy(), lin.weight.detach().cpu().numpy(), xq, sx, n_o=16, n_l=16, sel=sel,
+                             w_mode="int")
+    assert np.array_equal(x.grad.cpu().numpy(), ref["grad_input"])
+    assert np.array_equal(lin.weight.grad.cpu().numpy(), ref["grad_w"])
+    # the reference's run of this scheme
+    import os
+    from hot_b200 import ops
+    g = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "flinearq_hadamard.npz"))
+    dev = lambda a: torch.from_numpy(np.ascontiguousarray(a)).cuda()
+    q = lambda bits, st, u: ops.Quant(bits, st, "noise", "tensor", 0, 0, dev(u))
+    cfg = ops.LinearConfig(order_o=16, order_l=16, sel_l=list(range(16)), q_gx=q(4, "int4", g["u_go"]), q_w=q(4, "int4", g["u_w"]),
+                           q_gw=q(8, "int8", g["u_gw"]), q_x=q(8, "int8", g["u_x"]))
+    x_q_t, s_x = ops.abc_compress(dev(g["x"]), cfg)
+    gx, gw = ops.linear_backward(dev(g["go"]), dev(g["w"]), x_q_t, s_x, cfg)
+    for got, name in ((gx, "grad_input"), (gw, "grad_w")):
+        rel = np.linalg.norm(got.cpu().numpy() - g[name]) / np.linalg.norm(g[name])
+        assert rel < 1e-3, (name, rel)
+
+
 def test_hq_linear_3d_takes_one_scale_per_sample(hot):
     """Reference semantics of a [B, L, I] input (no preset): per-sample scales, per-sample low-rank
     projection, grad_weight summed over the batch; nearest rounding makes it reproducible."""

@@ -83,6 +83,22 @@ def test_flinearq_backward(golden, tag):
     assert np.abs(out["q_go"]).max() <= 7 and np.abs(out["q_gw"]).max() <= 127
 
 
+def test_flinearq_backward_scheme_hadamard(golden):
+    """transform_scheme "hadamard": the token-side transform keeps every row of the block Hadamard matrix."""
+    g = golden("flinearq_hadamard")
+    n_l, sel = oc.selection_from_matrix(g["p"])
+    assert n_l == 16 and list(sel) == list(range(16))
+    x_q, s_x = oc.abc_compress(g["x"], n_l, sel, 8, g["u_x"])
+    assert np.array_equal(x_q, g["x_q"].astype(np.int32))
+    np.testing.assert_allclose(s_x, g["scale_x"], rtol=1e-6)
+    O = g["w"].shape[0]
+    out = oc.linear_backward(g["go"], g["w"], x_q, s_x, n_o=oc.block_order(O), n_l=n_l, sel=sel,
+                             u_go=g["u_go"], u_w=g["u_w"], u_gw=g["u_gw"])
+    for name in ("grad_input", "grad_w"):
+        rel = np.linalg.norm(out[name] - g[name]) / np.linalg.norm(g[name])
+        assert rel < 1e-3, (name, rel)
+
+
 def test_flinearq_backward_batched(golden):
     """3-D input [B, L, I]: one scale per sample, grad_w summed over the batch (reference run on
     the same tensors, tests/golden/make_golden.py::batched)."""
