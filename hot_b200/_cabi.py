@@ -53,6 +53,10 @@ EXPORTS = {
                                                 c_vp, c_i64, c_i64, c_vp, c_vp, c_vp]),
     "hot_gemm_i8_grouped": (ctypes.c_int, [c_vp, c_i64, c_vp, c_i64, c_i64, c_i64, c_i64, c_i64, c_vp, c_vp, ctypes.c_float,
                                            c_vp, ctypes.c_int, c_i64, c_vp, c_vp]),
+    "hot_hla_project": (ctypes.c_int, [c_vp, ctypes.c_int, c_i64, c_i64, c_i64, ctypes.c_int, ctypes.POINTER(c_i32), ctypes.c_int,
+                                       c_vp, c_i64, c_vp]),
+    "hot_hla_expand": (ctypes.c_int, [c_vp, c_i64, c_i64, c_i64, ctypes.c_int, ctypes.POINTER(c_i32), ctypes.c_int,
+                                      ctypes.c_float, c_vp, ctypes.c_int, c_i64, c_vp]),
     "hot_col_ht_quant_scratch_words": (ctypes.c_size_t, [ctypes.c_int, c_i64, c_i64, ctypes.c_int, ctypes.c_int, ctypes.c_int]),
     "hot_col_ht_quant_static": (ctypes.c_int, [c_vp, ctypes.c_int, c_i64, c_i64, c_i64, ctypes.c_int, ctypes.POINTER(c_i32),
                                                ctypes.c_int, ctypes.POINTER(HotQuant), ctypes.c_int, c_vp, c_i64, c_vp,

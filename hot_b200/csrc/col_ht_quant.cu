@@ -396,6 +396,69 @@ __global__ void __launch_bounds__(kThreads) col_ht_quant_kernel(const T* __restr
   }
 }
 
+// ---- un-quantised projection and its transpose (schemes that quantise the projected tensor in its
+// natural layout, or expand a low-rank gradient back to all tokens) --------------------------------
+// out[(b * r + j), c] = sum_t H_N[sel[j], t] * x[b * N + t, c], float32, same butterfly as above
+template <typename T, int N>
+__global__ void __launch_bounds__(kThreads) hla_project_kernel(const T* __restrict__ x, ColParams p, float* __restrict__ out,
+                                                               int64_t ldo) {
+  constexpr int VEC = vec_for<T, N>();
+  constexpr int CPL = ColTraits<T>::kCpl;
+  constexpr int CC = 32 * VEC * CPL;
+  constexpr int G = group_for<N>();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int c0 = blockIdx.x * CC;
+  const int64_t nblk = p.rows / N;
+  const int64_t blk0 = (int64_t)blockIdx.y * p.nb;
+  for (int b = warp * G; b < p.nb; b += kWarps * G) {
+    if (blk0 + b >= nblk) break;
+    float v[VEC * CPL][N * G];
+    load_transform<T, N, VEC>(x, p, blk0 + b, nblk, c0, lane, v);
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+      if (blk0 + b + g >= nblk) break;
+#pragma unroll
+      for (int k = 0; k < N; ++k) {
+        const int j = p.pos[k];
+        if (j < 0) continue;
+        float* row = out + ((blk0 + b + g) * p.r + j) * ldo;
+#pragma unroll
+        for (int vv = 0; vv < VEC; ++vv)
+#pragma unroll
+          for (int qq = 0; qq < CPL; ++qq) {
+            const int c = c0 + (lane + 32 * vv) * CPL + qq;
+            if (c < p.cols) row[c] = v[vv * CPL + qq][g * N + k];
+          }
+      }
+    }
+  }
+}
+
+// out[b * N + t, c] = scale * sum_j H_N[sel[j], t] * in[b * r + j, c]: the kept rows go back to their
+// places in a zero block and the (symmetric) butterfly runs over it, in the same fixed order
+template <typename TO, int N>
+__global__ void __launch_bounds__(kThreads) hla_expand_kernel(const float* __restrict__ in, int64_t ldi, ColParams p, float scale,
+                                                              TO* __restrict__ out, int64_t ldo) {
+  const int c = blockIdx.x * kThreads + threadIdx.x;
+  if (c >= p.cols) return;
+  const int64_t nblk = p.rows / N;
+  for (int64_t blk = blockIdx.y; blk < nblk; blk += gridDim.y) {
+    float v[N];
+#pragma unroll
+    for (int k = 0; k < N; ++k) {
+      const int j = p.pos[k];
+      v[k] = j >= 0 ? in[(blk * p.r + j) * ldi + c] : 0.0f;
+    }
+    butterfly_regs<N, 0, N>(v);
+#pragma unroll
+    for (int t = 0; t < N; ++t) {
+      const float y = __fmul_rn(v[t], scale);
+      if (sizeof(TO) == 2) reinterpret_cast<__nv_bfloat16*>(out)[(blk * N + t) * ldo + c] = __float2bfloat16_rn(y);
+      else reinterpret_cast<float*>(out)[(blk * N + t) * ldo + c] = y;
+    }
+  }
+}
+
 template <typename T, int N>
 int launch_n(const T* x, const ColParams& p, const hot_quant_t& hq, uint8_t* codes, float* scales, uint32_t* ws,
              cudaStream_t st) {
@@ -599,4 +662,105 @@ extern "C" int hot_col_ht_quant_static(const void* x, int dtype, int64_t rows, i
   // so whatever the previous call left in the array does not leak into this one
   return hot_col_ht_quant(x, dtype, rows, cols, ldx, order, sel, r, q, logical_layout, codes_t, ld_codes, scales, scratch,
                           stream);
+}
+
+// ---------------------------------------------------------------------------------------
+// Un-quantised low-rank projection along the first dim, and its transpose.
+// ---------------------------------------------------------------------------------------
+namespace hot {
+namespace {
+int fill_selection(ColParams& p, int order, const int32_t* sel, int r, const char* who) {
+  if (order < 1 || order > 64 || (order & (order - 1))) HOT_FAIL(HOT_ERR_UNSUPPORTED, "%s: order %d not a power of two in [1, 64]", who, order);
+  if (!sel || r < 1 || r > order) HOT_FAIL(HOT_ERR_ARG, "%s: rank %d outside [1, %d] or null selection", who, r, order);
+  for (int k = 0; k < 64; ++k) p.pos[k] = -1;
+  for (int j = 0; j < r; ++j) {
+    if (sel[j] < 0 || sel[j] >= order || p.pos[sel[j]] >= 0) HOT_FAIL(HOT_ERR_ARG, "%s: sel[%d] = %d out of range or repeated", who, j, sel[j]);
+    p.pos[sel[j]] = (signed char)j;
+  }
+  p.r = r;
+  return HOT_OK;
+}
+
+template <typename T, int N>
+int project_n(const T* x, const ColParams& p, float* out, int64_t ldo, cudaStream_t st) {
+  constexpr int CC = 32 * vec_for<T, N>() * ColTraits<T>::kCpl;
+  const int64_t nblk = p.rows / N;
+  dim3 grid((unsigned)((p.cols + CC - 1) / CC), (unsigned)((nblk + p.nb - 1) / p.nb));
+  hla_project_kernel<T, N><<<grid, kThreads, 0, st>>>(x, p, out, ldo);
+  HOT_CUDA(cudaGetLastError());
+  return HOT_OK;
+}
+template <typename T>
+int project_t(const T* x, int n, const ColParams& p, float* out, int64_t ldo, cudaStream_t st) {
+  switch (n) {
+    case 1: return project_n<T, 1>(x, p, out, ldo, st);
+    case 2: return project_n<T, 2>(x, p, out, ldo, st);
+    case 4: return project_n<T, 4>(x, p, out, ldo, st);
+    case 8: return project_n<T, 8>(x, p, out, ldo, st);
+    case 16: return project_n<T, 16>(x, p, out, ldo, st);
+    case 32: return project_n<T, 32>(x, p, out, ldo, st);
+    default: return project_n<T, 64>(x, p, out, ldo, st);
+  }
+}
+template <typename TO, int N>
+int expand_n(const float* in, int64_t ldi, const ColParams& p, float scale, TO* out, int64_t ldo, cudaStream_t st) {
+  const int64_t nblk = p.rows / N;
+  dim3 grid((unsigned)((p.cols + kThreads - 1) / kThreads), (unsigned)(nblk < 4096 ? nblk : 4096));
+  hla_expand_kernel<TO, N><<<grid, kThreads, 0, st>>>(in, ldi, p, scale, out, ldo);
+  HOT_CUDA(cudaGetLastError());
+  return HOT_OK;
+}
+template <typename TO>
+int expand_t(const float* in, int64_t ldi, int n, const ColParams& p, float scale, TO* out, int64_t ldo, cudaStream_t st) {
+  switch (n) {
+    case 1: return expand_n<TO, 1>(in, ldi, p, scale, out, ldo, st);
+    case 2: return expand_n<TO, 2>(in, ldi, p, scale, out, ldo, st);
+    case 4: return expand_n<TO, 4>(in, ldi, p, scale, out, ldo, st);
+    case 8: return expand_n<TO, 8>(in, ldi, p, scale, out, ldo, st);
+    case 16: return expand_n<TO, 16>(in, ldi, p, scale, out, ldo, st);
+    case 32: return expand_n<TO, 32>(in, ldi, p, scale, out, ldo, st);
+    default: return expand_n<TO, 64>(in, ldi, p, scale, out, ldo, st);
+  }
+}
+}  // namespace
+}  // namespace hot
+
+extern "C" int hot_hla_project(const void* x, int dtype, int64_t rows, int64_t cols, int64_t ldx, int order, const int32_t* sel,
+                               int r, float* out, int64_t ldo, hot_stream_t stream) {
+  using namespace hot;
+  if (!x || !out) HOT_FAIL(HOT_ERR_ARG, "hot_hla_project: null pointer");
+  if (rows < 0 || cols <= 0 || cols > (1 << 30)) HOT_FAIL(HOT_ERR_ARG, "hot_hla_project: bad shape");
+  if (dtype != HOT_F32 && dtype != HOT_BF16) HOT_FAIL(HOT_ERR_UNSUPPORTED, "hot_hla_project: dtype %d", dtype);
+  ColParams p = {};
+  if (int rc = fill_selection(p, order, sel, r, "hot_hla_project")) return rc;
+  if (rows % order != 0) HOT_FAIL(HOT_ERR_UNSUPPORTED, "hot_hla_project: rows %lld not a multiple of order %d", (long long)rows, order);
+  const int esz = dtype == HOT_F32 ? 4 : 2;
+  if (ldx < cols || (ldx * esz) % 4 != 0 || ((uintptr_t)x) % 4 != 0 || (dtype == HOT_BF16 && cols % 2 != 0) || ldo < cols)
+    HOT_FAIL(HOT_ERR_ARG, "hot_hla_project: pitches must cover cols; x 4-byte aligned (bf16: even cols)");
+  p.rows = rows;
+  p.cols = (int)cols;
+  p.ldx = ldx;
+  p.nb = 64;
+  p.batch = 1;
+  if (rows == 0) return HOT_OK;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (dtype == HOT_F32) return project_t<float>((const float*)x, order, p, out, ldo, st);
+  return project_t<__nv_bfloat16>((const __nv_bfloat16*)x, order, p, out, ldo, st);
+}
+
+extern "C" int hot_hla_expand(const float* in, int64_t ldi, int64_t rows_out, int64_t cols, int order, const int32_t* sel, int r,
+                              float scale, void* out, int out_dtype, int64_t ldo, hot_stream_t stream) {
+  using namespace hot;
+  if (!in || !out) HOT_FAIL(HOT_ERR_ARG, "hot_hla_expand: null pointer");
+  if (rows_out < 0 || cols <= 0 || cols > (1 << 30) || ldi < cols || ldo < cols) HOT_FAIL(HOT_ERR_ARG, "hot_hla_expand: bad shape or pitch");
+  if (out_dtype != HOT_F32 && out_dtype != HOT_BF16) HOT_FAIL(HOT_ERR_UNSUPPORTED, "hot_hla_expand: out dtype %d", out_dtype);
+  ColParams p = {};
+  if (int rc = fill_selection(p, order, sel, r, "hot_hla_expand")) return rc;
+  if (rows_out % order != 0) HOT_FAIL(HOT_ERR_UNSUPPORTED, "hot_hla_expand: rows %lld not a multiple of order %d", (long long)rows_out, order);
+  p.rows = rows_out;
+  p.cols = (int)cols;
+  if (rows_out == 0) return HOT_OK;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (out_dtype == HOT_F32) return expand_t<float>(in, ldi, order, p, scale, (float*)out, ldo, st);
+  return expand_t<__nv_bfloat16>(in, ldi, order, p, scale, (__nv_bfloat16*)out, ldo, st);
 }

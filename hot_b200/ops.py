@@ -337,6 +337,53 @@ def linear_backward(go: torch.Tensor, w: torch.Tensor, x_q_t: torch.Tensor, scal
     return gx, gw
 
 
+def hla_project(x: torch.Tensor, order: int, sel: Sequence[int]) -> torch.Tensor:
+    """Un-quantised low-rank projection along the first dim: x [rows, cols] -> float32 [rows*r/order, cols]."""
+    _require_cuda(x)
+    if x.dim() != 2 or x.stride(1) != 1:
+        raise ValueError("x must be 2-D with a contiguous last dim")
+    rows, cols = x.shape
+    r = len(sel)
+    out = torch.empty((rows // order * r, cols), dtype=torch.float32, device=x.device)
+    sel_c = (C.c_i32 * r)(*[int(v) for v in sel])
+    with torch.cuda.device(x.device):
+        C.check(C.lib().hot_hla_project(x.data_ptr(), _dtype(x), rows, cols, x.stride(0), order, sel_c, r, out.data_ptr(),
+                                        out.stride(0), _stream(x)), "hot_hla_project")
+    return out
+
+
+def hla_expand(y: torch.Tensor, order: int, sel: Sequence[int], scale: float, out_dtype: torch.dtype) -> torch.Tensor:
+    """Transpose of ``hla_project``: y float32 [rows*r/order, cols] -> [rows, cols] of ``out_dtype``, times ``scale``."""
+    _require_cuda(y)
+    if y.dim() != 2 or y.stride(1) != 1 or y.dtype != torch.float32:
+        raise ValueError("y must be a 2-D float32 tensor with a contiguous last dim")
+    r = len(sel)
+    rows = y.shape[0] // r * order
+    cols = y.shape[1]
+    out = torch.empty((rows, cols), dtype=out_dtype, device=y.device)
+    sel_c = (C.c_i32 * r)(*[int(v) for v in sel])
+    with torch.cuda.device(y.device):
+        C.check(C.lib().hot_hla_expand(y.data_ptr(), y.stride(0), rows, cols, order, sel_c, r, float(scale), out.data_ptr(),
+                                       _DTYPES[out_dtype], out.stride(0), _stream(y)), "hot_hla_expand")
+    return out
+
+
+def linear_backward_lowrank_gx(go: torch.Tensor, w: torch.Tensor, order: int, sel: Sequence[int], q_gx: Quant, q_w: Quant,
+                               status: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """grad_input of the schemes that project grad_output along the TOKENS before the g_x product
+    (transform_scheme low_rank / gilr_gwh, utils/quant_matmul.py:229-234, 261-266, 334-337):
+    grad_x = expand( (Q(HLA(go)) . Q(w)) * s_go * s_w ) / order, the weight left untransformed."""
+    _require_cuda(go, w)
+    L, O = go.shape
+    I = w.shape[1]
+    go_lr = hla_project(go, order, sel)                                     # [L', O] float32, natural layout
+    q_go, s_go = row_ht_quant(go_lr, 1, q_gx)
+    q_w_t, s_w, _ = col_ht_quant(w, 1, [0], _one_per_byte(q_w), "natural")  # [I, O] codes, no transform
+    gi_lr = gemm_i8(q_go, q_gx.storage, q_w_t, "int8", go_lr.shape[0], I, O, s_go, s_w, 1.0, torch.float32, status=status,
+                    a_rows_per_scale=1)
+    return hla_expand(gi_lr, order, sel, 1.0 / order, go.dtype)
+
+
 def abc_compress_batched(x: torch.Tensor, cfg: LinearConfig):
     """Activation buffer of a batch ``x`` [B, L, I] with one scale per sample, as the reference saves
     it for 3-D inputs: (x_q_t uint8 [I, B * pitch], scale_x float32 [B], pitch)."""

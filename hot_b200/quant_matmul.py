@@ -156,22 +156,36 @@ def _operand(kind: str, scheme, bits: int, what: str, row_ok: bool) -> ops.Quant
     return ops.Quant(int(bits), _storage(int(bits)), rounding, scale, _seed(), _next_offset())
 
 
-_BUILT_SCHEMES = ("gih_gwlr", "hadamard")
+_BUILT_SCHEMES = ("gih_gwlr", "hadamard", "low_rank", "gilr_gwh")
+_TOKEN_GX_SCHEMES = ("low_rank", "gilr_gwh")   # grad_output is projected along the tokens for g_x too
 
 
 def _token_basis(a, tokens: int, preset):
     """(n, sel) of the token-side transform of the configured scheme: the low-rank rows of make_WHT
     (or the preset) for ``gih_gwlr``; every row of the block Hadamard matrix H_n, n = min(16, 2-adic
     part of the token count), for ``hadamard`` (utils/quant_matmul.py:353-355, make_hadamard)."""
-    if a.transform_scheme == "hadamard":
+    if a.transform_scheme in ("hadamard", "gilr_gwh"):
         n = biggest_power2_factor_max16(tokens)
         return n, list(range(n))
     return lowrank_selection(tokens, preset, a.vectorPercentile)
 
 
+def _out_matrix(a, out_features: int, tokens: int, preset, dtype, device) -> Tensor:
+    """What ``hadamard_out`` holds per scheme (utils/quant_matmul.py:353-370): the block Hadamard matrix
+    of the output features (gih_gwlr, hadamard), a [1, 1] zero (low_rank) or the low-rank rows of the
+    token count (gilr_gwh)."""
+    from .hadamard_matmul import hadamard
+    if a.transform_scheme == "low_rank":
+        return torch.zeros((1, 1), dtype=dtype, device=device)
+    if a.transform_scheme == "gilr_gwh":
+        n, sel = lowrank_selection(tokens, preset, a.vectorPercentile)
+        return torch.tensor(hadamard(n)[sel], dtype=dtype, device=device)
+    return torch.tensor(TD.get_or_register("hadamard", out_features), dtype=dtype, device=device)
+
+
 def _check_scheme(a) -> None:
     if a.transform_scheme not in _BUILT_SCHEMES:
-        if a.transform_scheme in ("low_rank", "gilr_gwh", "gilro_gwh"):
+        if a.transform_scheme in ("gilro_gwh",):
             raise NotImplementedError("transform_scheme %r is not built on the native path (built: %s)"
                                       % (a.transform_scheme, ", ".join(_BUILT_SCHEMES)))
         raise Exception("args.transform_scheme not implemented: " + str(a.transform_scheme))
@@ -218,8 +232,18 @@ class FLinearQ(Function):
         _check_scheme(a)
         n_l, sel = _selection(h_bs)
         q_x = _operand("x", a.quantBWDAct, a.actQuantBit, "Activation", row_ok=False)
-        cfg = ops.LinearConfig(order_o=int(h_out.shape[0]), order_l=n_l, sel_l=sel, q_x=q_x)
+        ctx.scheme = a.transform_scheme
+        ctx.gx_basis = None
+        if ctx.scheme in _TOKEN_GX_SCHEMES:   # no transform along the output features; g_x takes token rows
+            order_o = 1
+            ctx.gx_basis = (n_l, sel) if ctx.scheme == "low_rank" else _selection(h_out)
+        else:
+            order_o = int(h_out.shape[0])
+        cfg = ops.LinearConfig(order_o=order_o, order_l=n_l, sel_l=sel, q_x=q_x)
         ctx.per_sample = x.dim() == 3 and getattr(a, "lowRankPreset", None) is None
+        if ctx.per_sample and ctx.gx_basis is not None:
+            raise NotImplementedError("transform_scheme %r with per-sample (3-D) inputs is not built; set args.lowRankPreset "
+                                      "to flatten the batch" % ctx.scheme)
         if ctx.per_sample:
             if x.shape[1] % n_l:
                 raise ValueError("token count %d is not a multiple of the low-rank order %d" % (x.shape[1], n_l))
@@ -235,7 +259,7 @@ class FLinearQ(Function):
             x_q_t, scale_x = ops.abc_compress(x2, cfg)
         ctx.name = name
         ctx.x_shape = tuple(x.shape)
-        ctx.order_o, ctx.order_l, ctx.sel = int(h_out.shape[0]), n_l, sel
+        ctx.order_o, ctx.order_l, ctx.sel = order_o, n_l, sel
         ctx.q_x = q_x
         ctx.save_for_backward(x_q_t, w, scale_x)
 
@@ -273,6 +297,14 @@ class FLinearQ(Function):
             if q_gx.scale != "tensor" or q_gw.scale != "tensor":
                 raise NotImplementedError("per-token / per-channel grad_output scales with per-sample (3-D) inputs are not built")
             gx, gw = ops.linear_backward_batched(go, w.detach(), x_q_t, scale_x, cfg, need_gx=need_gx, need_gw=need_gw)
+        elif ctx.gx_basis is not None:
+            if need_gw:
+                _, gw = ops.linear_backward(go, w.detach(), x_q_t, scale_x, cfg, need_gx=False, need_gw=True)
+            if need_gx:
+                n_x, sel_x = ctx.gx_basis
+                if go.shape[0] % n_x:
+                    raise ValueError("token count %d is not a multiple of the low-rank order %d" % (go.shape[0], n_x))
+                gx = ops.linear_backward_lowrank_gx(go, w.detach(), n_x, sel_x, q_gx, q_w)
         elif need_gx or need_gw:
             gx, gw = ops.linear_backward(go, w.detach(), x_q_t, scale_x, cfg, need_gx=need_gx, need_gw=need_gw)
         if gx is not None:
@@ -289,8 +321,8 @@ class HQ_Linear(nn.Linear):
         super().__init__(in_features, out_features, bias)
         a = _args()
         _check_scheme_name(a)
-        self.register_buffer("hadamard_out", torch.tensor(TD.get_or_register("hadamard", self.out_features),
-                                                          dtype=self.weight.dtype))
+        self.register_buffer("hadamard_out", _out_matrix(a, self.out_features, max(int(a.BATCH_SIZE), 1), None,
+                                                         self.weight.dtype, self.weight.device))
         n, sel = _token_basis(a, max(int(a.BATCH_SIZE), 1), None)
         self.register_buffer("hadamard_bs", self._basis(n, sel, self.weight.device))
         self._bs_tokens = None
@@ -311,6 +343,8 @@ class HQ_Linear(nn.Linear):
         if key != self._bs_tokens or self.hadamard_bs.device != self.weight.device:
             n, sel = _token_basis(a, tokens, getattr(a, "lowRankPreset", None))
             self.hadamard_bs = self._basis(n, sel, self.weight.device)
+            self.hadamard_out = _out_matrix(a, self.out_features, tokens, getattr(a, "lowRankPreset", None),
+                                            self.weight.dtype, self.weight.device)
             self._bs_tokens = key
         output = FLinearQ.apply(input, self.weight, self.hadamard_out, self.hadamard_bs, self.layer_name)
         if self.bias is not None:
@@ -329,6 +363,8 @@ class HQ_Conv2d(nn.Conv2d):
         super().__init__(in_channels, out_channels, kernel_size, stride, padding, dilation, groups, bias, padding_mode)
         a = _args()
         _check_scheme_name(a)
+        if a.transform_scheme in _TOKEN_GX_SCHEMES:
+            raise NotImplementedError("HQ_Conv2d with transform_scheme %r is not built" % a.transform_scheme)
         self.register_buffer("hadamard_out", torch.tensor(TD.get_or_register("hadamard", self.out_channels),
                                                           dtype=self.weight.dtype))
         self.register_buffer("hadamard_bs", torch.zeros((1, 1), dtype=self.weight.dtype))

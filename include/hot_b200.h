@@ -164,6 +164,20 @@ int hot_col_ht_quant_static(const void* x, int dtype, int64_t rows, int64_t cols
                             void* codes_t, int64_t ld_codes, float* scales, hot_stream_t stream);
 
 /*
+ * The un-quantised projection of hot_col_ht_quant in the natural layout, and its transpose:
+ *   hot_hla_project: out[b*r + j, c] = sum_t H_n[sel[j], t] * x[b*n + t, c]      x [rows, cols] -> out float32 [rows*r/n, cols]
+ *   hot_hla_expand : out[b*n + t, c] = scale * sum_j H_n[sel[j], t] * in[b*r + j, c]   in float32 [rows_out*r/n, cols] -> out [rows_out, cols]
+ * Same fixed butterfly order as the quantising kernels.  Pitches ldx / ldo / ldi in elements.
+ * Stand in for lowering_matmul_back(h_bs, .) where its result is quantised as it stands
+ * (transform_scheme low_rank / gilr_gwh, utils/quant_matmul.py:229-234) and for
+ * lowering_matmul_back(h_bs.mT, grad_input) / n (utils/quant_matmul.py:334,337).
+ */
+int hot_hla_project(const void* x, int dtype, int64_t rows, int64_t cols, int64_t ldx, int order, const int32_t* sel,
+                    int r, float* out, int64_t ldo, hot_stream_t stream);
+int hot_hla_expand(const float* in, int64_t ldi, int64_t rows_out, int64_t cols, int order, const int32_t* sel, int r,
+                   float scale, void* out, int out_dtype, int64_t ldo, hot_stream_t stream);
+
+/*
  * Integer GEMM on tcgen05 (kind::i8) with fused dequantisation:
  *   out[m, n] = ((float)(sum_k a[m,k] * b[n,k]) * sa[m or 0]) * sb[n or 0] * post
  *   a [M, K] and b [N, K]: K contiguous, pitches lda/ldb in BYTES (multiples of 16),

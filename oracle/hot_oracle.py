@@ -351,6 +351,31 @@ def linear_backward(go, w, x_q, s_x, *, n_o: int, n_l: int, sel, bits_gx: int = 
     return out
 
 
+def hla_expand(y: np.ndarray, n: int, sel: np.ndarray, scale) -> np.ndarray:
+    """lowering_matmul_back(P.mT, y) * scale for P = H_n[sel] (utils/quant_matmul.py:334,337): the kept
+    rows go back to their places in a zero block and the butterfly (H_n is symmetric) runs over it."""
+    y = np.asarray(y, dtype=F32)
+    r = len(sel)
+    nb = y.shape[0] // r
+    full = np.zeros((nb, n, y.shape[1]), dtype=F32)
+    full[:, np.asarray(sel), :] = y.reshape(nb, r, y.shape[1])
+    return (fwht_first(full.reshape(nb * n, y.shape[1]), n) * F32(scale)).astype(F32)
+
+
+def grad_input_lowrank(go, w, *, n: int, sel, bits_gx: int = 4, bits_w: int = 4, u_go=None, u_w=None,
+                       gx_per_token: bool = False, w_mode: str = "stoch", exact_matmul: bool = True):
+    """grad_input of transform_scheme low_rank / gilr_gwh (utils/quant_matmul.py:229-234, 261-266, 288-290,
+    334-337): grad_output is projected along the tokens and quantised as [L', O], the weight is
+    quantised untransformed, and the [L', I] product is expanded back to L tokens and divided by n."""
+    go_lr = hla(np.asarray(go, dtype=F32), n, np.asarray(sel))
+    q_go, s_go = (quant_rows if gx_per_token else quant_tensor)(go_lr, bits_gx, u_go)
+    w = np.asarray(w, dtype=F32)
+    q_w, s_w = quant_sawb(w, bits_w) if w_mode == "sawb" else quant_tensor(w, bits_w, u_w if w_mode == "stoch" else None)
+    acc = _int_matmul(q_go, q_w, exact_matmul)
+    gi_lr = (acc.astype(F32) * (s_go[:, None] if gx_per_token else F32(s_go))) * F32(s_w)
+    return dict(q_go=q_go, s_go=s_go, q_w=q_w, s_w=s_w, grad_input=hla_expand(gi_lr, n, sel, F32(1.0) / F32(n)))
+
+
 # ----------------------------------------------------------------------------
 # the same on 3-D tensors [B, L, .]: one scale per sample (torch.vmap over dim 0 of the
 # quantisers, utils/quant_matmul.py:102-106,117-122), grad_w summed over the batch

@@ -170,7 +170,56 @@ def main(ref_root: str, out_dir: str):
     np.savez_compressed(os.path.join(out_dir, "lqs.npz"), **l)
     batched(ref_args, hm, qm, out_dir)
     scheme_hadamard(ref_args, hm, qm, out_dir)
+    schemes_token_lowrank(ref_args, hm, qm, out_dir)
     print("golden vectors written to", out_dir)
+
+
+def schemes_token_lowrank(ref_args, hm, qm, out_dir: str):
+    """FLinearQ under transform_scheme "low_rank" and "gilr_gwh": grad_output is projected along the
+    tokens for the g_x product too, the weight stays untransformed and grad_input is expanded back
+    (utils/quant_matmul.py:229-234, 261-266, 334-337)."""
+    T = torch.from_numpy
+    L, O, I = 96, 64, 48
+    for scheme, seed in (("low_rank", 20250324), ("gilr_gwh", 20250325)):
+        rng = np.random.default_rng(seed)
+        ref_args.transform_scheme = scheme
+        ref_args.TransformGogi = ref_args.TransformWgt = ref_args.TransformGogw = ref_args.TransformInput = True
+        ref_args.GogiQuantBit, ref_args.weightQuantBit, ref_args.GogwQuantBit, ref_args.actQuantBit = 4, 4, 8, 8
+        ref_args.quantBWDGogi = ref_args.quantBWDWgt = ref_args.quantBWDGogw = ref_args.quantBWDAct = "stoch"
+        ref_args.quantAuto = False
+        xx = rng.standard_normal((L, I)).astype(np.float32)
+        xx[:, 7] *= 12.0
+        ww = ((rng.random((O, I)) * 2 - 1) / np.sqrt(I)).astype(np.float32)
+        go = (rng.standard_normal((L, O)) * 1e-3).astype(np.float32)
+        lr = hm.make_WHT(L, 50)                                        # [r, n] low-rank rows for 96 tokens
+        had = hm.make_hadamard(L)                                      # [16, 16]
+        if scheme == "low_rank":
+            h_out, h_bs = torch.zeros((1, 1)), torch.tensor(lr, dtype=torch.float32)
+            Lx = L * lr.shape[0] // lr.shape[1]                        # tokens of the saved activation
+            Lw = Lx                                                    # and of the g_w operand
+        else:
+            h_out, h_bs = torch.tensor(lr, dtype=torch.float32), torch.tensor(had, dtype=torch.float32)
+            Lx = Lw = L
+        Lg = L * lr.shape[0] // lr.shape[1]                            # tokens of the projected grad_output (g_x side)
+        u_x = rng.random((Lx, I), dtype=np.float32)
+        u_go = rng.random((Lg, O), dtype=np.float32)
+        u_w = rng.random((O, I), dtype=np.float32)
+        u_gw = rng.random((O, Lw), dtype=np.float32)
+        xt = T(xx).requires_grad_(True)
+        wt = T(ww).requires_grad_(True)
+        try:
+            with NoiseQueue() as nq:
+                nq.queue += [T(u_x), T(u_go), T(u_w), T(u_gw)]
+                y = qm.FLinearQ.apply(xt, wt, h_out, h_bs, "layer")
+                saved = y.grad_fn.saved_tensors
+                y.backward(T(go))
+                assert not nq.queue
+        finally:
+            ref_args.transform_scheme = "gih_gwlr"
+        f = dict(x=xx, w=ww, go=go, lowrank=lr.astype(np.int8), hadamard=had.astype(np.int8), u_x=u_x, u_go=u_go, u_w=u_w,
+                 u_gw=u_gw, y=y.detach().numpy(), x_q=saved[0].numpy(), scale_x=saved[4].numpy(),
+                 grad_input=xt.grad.numpy(), grad_w=wt.grad.numpy())
+        np.savez_compressed(os.path.join(out_dir, "flinearq_%s.npz" % scheme), **f)
 
 
 def scheme_hadamard(ref_args, hm, qm, out_dir: str):

@@ -118,6 +118,23 @@ def test_col_ht_quant(ops, order, sel, dtype, storage, bits, rounding, layout, s
     assert np.array_equal(got_c, ref_c), "%d codes differ" % int((got_c != ref_c).sum())
 
 
+@pytest.mark.parametrize("order,sel", _sel_cases())
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_hla_project_and_expand(ops, order, sel, dtype):
+    """The un-quantised projection along the first dim and its transpose, bit for bit."""
+    nblk, cols = 13, 202
+    rng = np.random.default_rng(order + len(sel))
+    x = rng.standard_normal((order * nblk, cols)).astype(np.float32)
+    y = ops.hla_project(_dev(x, dtype), order, sel)
+    torch.cuda.synchronize()
+    ref = oc.hla(_as_f32(x, dtype), order, np.array(sel))
+    assert np.array_equal(y.cpu().numpy().view(np.uint32), ref.view(np.uint32))
+    z = ops.hla_expand(y, order, sel, 1.0 / order, dtype)
+    torch.cuda.synchronize()
+    want = torch.from_numpy(oc.hla_expand(ref, order, np.array(sel), np.float32(1.0 / order))).to(dtype)
+    assert torch.equal(z.cpu(), want)
+
+
 GEMM_CASES = [
     # M, N, K
     (128, 128, 128), (200, 96, 320), (37, 48, 96), (1000, 768, 3072), (384, 130, 50), (256, 256, 1970),

@@ -127,6 +127,47 @@ def test_hq_linear_scheme_hadamard(hot):
         assert rel < 1e-3, (name, rel)
 
 
+@pytest.mark.parametrize("scheme", ["low_rank", "gilr_gwh"])
+def test_hq_linear_token_lowrank_schemes(hot, scheme):
+    """transform_scheme low_rank / gilr_gwh: grad_output projected along the tokens for g_x, weight
+    untransformed, grad_input expanded back; bit for bit against the oracle with nearest rounding, and
+    against the reference's own run (golden, explicit noise)."""
+    import os
+    from hot_b200 import ops
+    args, qm = hot
+    args.transform_scheme = scheme
+    args.lowRankPreset = None
+    args.quantBWDGogi = args.quantBWDWgt = args.quantBWDGogw = args.quantBWDAct = "int"
+    torch.manual_seed(6)
+    L, I, O = 192, 64, 96                                        # 192 tokens: low-rank order 64, block Hadamard order 16
+    lin = qm.HQ_Linear(I, O, bias=False).cuda()
+    x = torch.randn(L, I, device="cuda", requires_grad=True)
+    go = torch.randn(L, O, device="cuda") * 1e-3
+    lin(x).backward(go)
+    n_x, sel_x = oc.wht_selection(L, 50)
+    n_w, sel_w = (n_x, sel_x) if scheme == "low_rank" else (16, np.arange(16))
+    xq, sx = oc.abc_compress(x.detach().cpu().numpy(), n_w, sel_w, 8, None, "int")
+    wn, gon = lin.weight.detach().cpu().numpy(), go.cpu().numpy()
+    ref_gx = oc.grad_input_lowrank(gon, wn, n=n_x, sel=sel_x, w_mode="int")["grad_input"]
+    ref_gw = oc.linear_backward(gon, wn, xq, sx, n_o=1, n_l=n_w, sel=sel_w, w_mode="int")["grad_w"]
+    assert np.array_equal(x.grad.cpu().numpy(), ref_gx)
+    assert np.array_equal(lin.weight.grad.cpu().numpy(), ref_gw)
+    # the reference's run of this scheme
+    g = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "flinearq_%s.npz" % scheme))
+    dev = lambda a: torch.from_numpy(np.ascontiguousarray(a)).cuda()
+    q = lambda bits, st, u: ops.Quant(bits, st, "noise", "tensor", 0, 0, dev(u))
+    n_x, sel_x = oc.selection_from_matrix(g["lowrank"])
+    n_w, sel_w = (n_x, sel_x) if scheme == "low_rank" else oc.selection_from_matrix(g["hadamard"])
+    cfg = ops.LinearConfig(order_o=1, order_l=n_w, sel_l=list(sel_w), q_gw=q(8, "int8", g["u_gw"]), q_x=q(8, "int8", g["u_x"]))
+    x_q_t, s_x = ops.abc_compress(dev(g["x"]), cfg)
+    _, gw = ops.linear_backward(dev(g["go"]), dev(g["w"]), x_q_t, s_x, cfg, need_gx=False)
+    gx = ops.linear_backward_lowrank_gx(dev(g["go"]), dev(g["w"]), n_x, list(sel_x), q(4, "int4", g["u_go"]),
+                                        q(4, "int4", np.ascontiguousarray(g["u_w"])))
+    for got, name in ((gx, "grad_input"), (gw, "grad_w")):
+        rel = np.linalg.norm(got.cpu().numpy() - g[name]) / np.linalg.norm(g[name])
+        assert rel < 1e-3, (name, rel)
+
+
 def test_hq_linear_3d_takes_one_scale_per_sample(hot):
     """Reference semantics of a [B, L, I] input (no preset): per-sample scales, per-sample low-rank
     projection, grad_weight summed over the batch; nearest rounding makes it reproducible."""
@@ -188,7 +229,7 @@ def test_unbuilt_modes_raise(hot):
     with pytest.raises(Exception, match="rounding scheme not implemented"):
         lin(x)
     args.quantBWDAct = "stoch"
-    args.transform_scheme = "low_rank"
+    args.transform_scheme = "gilro_gwh"
     with pytest.raises(NotImplementedError):
         lin(x)
     args.transform_scheme = "nonsense"
