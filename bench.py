@@ -63,6 +63,7 @@ def parse():
     p.add_argument("--one-layer", default=None, choices=["qkv", "proj", "fc1", "fc2"],
                    help="run --calls HOT backward calls of one ViT-B/16 linear shape and nothing else (for ncu captures)")
     p.add_argument("--calls", type=int, default=3)
+    p.add_argument("--schemes", action="store_true", help="one fc1 backward under each built transform_scheme")
     p.add_argument("--per-sample", action="store_true",
                    help="the reference's 3-D semantics (one scale per image) on the ViT-B/16 linear shapes")
     p.add_argument("--large-mlp", action="store_true",
@@ -347,6 +348,46 @@ def run_large_mlp(a):
     if int(status.item()) != 0:
         raise SystemExit("a bounded device-side wait ran out")
     print(json.dumps({"metric": "hot_backward_large_mlp", "tokens": M, "dtype": "bf16", "layers": out}), flush=True)
+
+
+def run_schemes(a):
+    """The four transform schemes built on the native path, on the fc1 shape (768 -> 3072) at --tokens
+    tokens, bf16: time of one layer backward (CUDA graph replay) and agreement with the exact gradients."""
+    from hot_b200 import ops
+    from hot_b200.hadamard_matmul import lowrank_selection
+    device = torch.device("cuda", 0)
+    torch.cuda.set_device(device)
+    torch.manual_seed(0)
+    L, i_f, o_f = a.tokens, 768, 3072
+    x = torch.randn((L, i_f), device=device).to(torch.bfloat16)
+    w = ((torch.rand((o_f, i_f), device=device) * 2 - 1) / i_f ** 0.5).to(torch.bfloat16)
+    go = (torch.randn((L, o_f), device=device) * 1e-3).to(torch.bfloat16)
+    ex, ew = torch.matmul(go, w).float(), torch.matmul(go.t(), x).float()
+    cos = lambda p_, q_: float(torch.nn.functional.cosine_similarity(p_.float().flatten(), q_.flatten(), dim=0))
+    n_lr, sel_lr = lowrank_selection(L, None, 50)          # the reference's make_WHT rows for this token count
+    full16 = (16, list(range(16)))
+    status = torch.zeros(1, dtype=torch.int32, device=device)
+    out = []
+    for scheme, gw_basis, gx_basis in (("gih_gwlr", (n_lr, sel_lr), None), ("hadamard", full16, None),
+                                       ("low_rank", (n_lr, sel_lr), (n_lr, sel_lr)), ("gilr_gwh", full16, (n_lr, sel_lr))):
+        cfg = ops.LinearConfig(order_o=16 if gx_basis is None else 1, order_l=gw_basis[0], sel_l=gw_basis[1])
+        x_q_t, s_x = ops.abc_compress(x, cfg)
+
+        def layer():
+            if gx_basis is None:
+                return ops.linear_backward(go, w, x_q_t, s_x, cfg, status=status)
+            gw_ = ops.linear_backward(go, w, x_q_t, s_x, cfg, need_gx=False, status=status)[1]
+            return ops.linear_backward_lowrank_gx(go, w, gx_basis[0], gx_basis[1], cfg.q_gx, cfg.q_w, status=status), gw_
+        t = _graph_time(lambda i: layer(), 5, device, warm=2)
+        gx, gw = layer()
+        out.append({"scheme": scheme, "token_basis_gw": "%d of %d" % (len(gw_basis[1]), gw_basis[0]),
+                    "token_basis_gx": None if gx_basis is None else "%d of %d" % (len(gx_basis[1]), gx_basis[0]),
+                    "layer_us": round(t, 1), "cos_gx_vs_fp": round(cos(gx, ex), 4), "cos_gw_vs_fp": round(cos(gw, ew), 4)})
+    torch.cuda.synchronize(device)
+    if int(status.item()) != 0:
+        raise SystemExit("a bounded device-side wait ran out")
+    print(json.dumps({"metric": "hot_backward_schemes", "tokens": L, "in": i_f, "out": o_f, "dtype": "bf16", "layers": out}),
+          flush=True)
 
 
 def run_one_layer(a):
@@ -712,6 +753,8 @@ if __name__ == "__main__":
         run_per_sample(args)
     elif args.one_layer:
         run_one_layer(args)
+    elif args.schemes:
+        run_schemes(args)
     elif args.vit_train:
         run_vit_train(args)
     else:
