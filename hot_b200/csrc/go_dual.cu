@@ -351,8 +351,14 @@ int launch_dual(const void* go, int64_t ldgo, const DualParams& p, int rx, int r
   const int per_sm = sizeof(T) == 2 ? 3 : 1;  // resident CTAs per SM by shared memory (75 KB / 140 KB each)
   int grid = sms * per_sm;
   if (grid > num_tiles) grid = num_tiles;
-  HOT_CUDA(cudaMemsetAsync(p.max_x, 0, sizeof(uint32_t) * (p.x_row ? p.L : 1), st));
-  HOT_CUDA(cudaMemsetAsync(p.max_w, 0, sizeof(uint32_t) * (p.w_row ? p.O : 1), st));
+  // one clear when the two abs-max regions lie close together in the caller's scratch (one launch fewer)
+  const size_t nx = p.x_row ? (size_t)p.L : 1, nw = p.w_row ? (size_t)p.O : 1;
+  if (p.max_w >= p.max_x + nx && (size_t)(p.max_w - p.max_x) + nw <= (1u << 18)) {
+    HOT_CUDA(cudaMemsetAsync(p.max_x, 0, sizeof(uint32_t) * ((size_t)(p.max_w - p.max_x) + nw), st));
+  } else {
+    HOT_CUDA(cudaMemsetAsync(p.max_x, 0, sizeof(uint32_t) * nx, st));
+    HOT_CUDA(cudaMemsetAsync(p.max_w, 0, sizeof(uint32_t) * nw, st));
+  }
   if (int rc = launch_pass<T, 0, HOT_ROUND_NEAREST, HOT_ROUND_NEAREST>(tmap, p, grid, st)) return rc;
   const bool px = rx == HOT_ROUND_STOCH_PHILOX, pw = rw == HOT_ROUND_STOCH_PHILOX;
   if (px && pw) return launch_pass<T, 1, HOT_ROUND_STOCH_PHILOX, HOT_ROUND_STOCH_PHILOX>(tmap, p, grid, st);
