@@ -31,6 +31,12 @@ class HotLinearCfg(ctypes.Structure):
                 ("sel_l", c_i32 * 64), ("q_gx", HotQuant), ("q_w", HotQuant), ("q_gw", HotQuant), ("q_x", HotQuant)]
 
 
+class HotGemmProblem(ctypes.Structure):
+    _fields_ = [("a", c_vp), ("a_storage", c_i32), ("lda", c_i64), ("b", c_vp), ("ldb", c_i64), ("M", c_i64), ("N", c_i64),
+                ("K", c_i64), ("scale_a", c_vp), ("scale_a_per_row", c_i32), ("scale_b", c_vp), ("scale_b_per_row", c_i32),
+                ("post", ctypes.c_float), ("out", c_vp), ("out_dtype", c_i32), ("ldo", c_i64)]
+
+
 class HotError(RuntimeError):
     def __init__(self, status: int, where: str, detail: str):
         super().__init__("%s failed: %s%s" % (where, _status_text(status), (" (" + detail + ")") if detail else ""))
@@ -51,6 +57,7 @@ EXPORTS = {
     "hot_col_ht_quant_batched": (ctypes.c_int, [c_vp, ctypes.c_int, c_i64, c_i64, c_i64, c_i64, ctypes.c_int,
                                                 ctypes.POINTER(c_i32), ctypes.c_int, ctypes.POINTER(HotQuant), ctypes.c_int,
                                                 c_vp, c_i64, c_i64, c_vp, c_vp, c_vp]),
+    "hot_gemm_i8_dual": (ctypes.c_int, [ctypes.POINTER(HotGemmProblem), ctypes.POINTER(HotGemmProblem), c_vp, c_vp]),
     "hot_gemm_i8_grouped": (ctypes.c_int, [c_vp, c_i64, c_vp, c_i64, c_i64, c_i64, c_i64, c_i64, c_vp, c_vp, ctypes.c_float,
                                            c_vp, ctypes.c_int, c_i64, c_vp, c_vp]),
     "hot_hla_project": (ctypes.c_int, [c_vp, ctypes.c_int, c_i64, c_i64, c_i64, ctypes.c_int, ctypes.POINTER(c_i32), ctypes.c_int,

@@ -56,6 +56,8 @@ struct GemmParams {
 // One stretch of k-blocks of one output tile.
 struct Segment {
   int tile, kb0, kb1;
+  int prob;    // 0: the kernel's main problem; 1: the rider problem (dual launch)
+  int ltile;   // tile index within its problem
   int group;   // grouped mode: which group of the K axis
   bool first;  // first segment of this CTA (selects the partial slot)
 };
@@ -68,6 +70,12 @@ struct SegmentIter {
   int tile, stride, num_tiles, num_kb;
   int group_kb, grp;
   long long u, end;
+  // dual launch: a second ("rider") problem of few, long tiles shares the launch.  Worker w < riders
+  // takes rider tile w first; the main problem's tiles are then dealt in rounds, in which the workers
+  // that hold a rider tile only join from round `lag` on (lag = rider k-blocks / main k-blocks,
+  // rounded), so that every worker ends up with about the same number of k-blocks.
+  int riders, lag, rider_kb, round, me, nw;
+  bool rider_pending;
   // worker / nworkers: this CTA (or CTA pair) among those that share the tiles
   __device__ SegmentIter(const GemmParams& p, int num_tiles_, int worker, int nworkers) {
     stream_k = p.stream_k != 0;
@@ -81,15 +89,51 @@ struct SegmentIter {
     const long long total = (long long)num_tiles * num_kb;
     u = total * worker / nworkers;
     end = total * (worker + 1) / nworkers;
+    riders = 0;
+    rider_pending = false;
+  }
+  __device__ void add_rider(int rider_tiles, int rider_num_kb, int worker, int nworkers) {
+    riders = rider_tiles;
+    rider_kb = rider_num_kb;
+    lag = (rider_num_kb + num_kb / 2) / num_kb;
+    round = 0;
+    me = worker;
+    nw = nworkers;
+    rider_pending = worker < rider_tiles;
   }
   __device__ bool exhausted() const { return stream_k ? u >= end : tile >= num_tiles; }
   __device__ bool next(Segment& s) {
     s.first = first;
     first = false;
     s.group = 0;
+    s.prob = 0;
+    if (riders) {
+      s.kb0 = 0;
+      if (rider_pending) {
+        rider_pending = false;
+        s.prob = 1;
+        s.ltile = me;
+        s.tile = num_tiles + me;
+        s.kb1 = rider_kb;
+        return true;
+      }
+      const int free_workers = nw - riders;
+      for (;;) {
+        const bool all = round >= lag;
+        const int base = all ? lag * free_workers + (round - lag) * nw : round * free_workers;
+        if (base >= num_tiles) return false;
+        const int rank = all ? me : me - riders;
+        ++round;
+        if (rank < 0) continue;  // this worker sits the round out
+        if (base + rank >= num_tiles) return false;
+        s.tile = s.ltile = base + rank;
+        s.kb1 = num_kb;
+        return true;
+      }
+    }
     if (group_kb) {  // one segment per (tile, group)
       if (tile >= num_tiles) return false;
-      s.tile = tile;
+      s.tile = s.ltile = tile;
       s.group = grp;
       s.kb0 = grp * group_kb;
       s.kb1 = s.kb0 + group_kb;
@@ -103,14 +147,14 @@ struct SegmentIter {
     }
     if (!stream_k) {
       if (tile >= num_tiles) return false;
-      s.tile = tile;
+      s.tile = s.ltile = tile;
       s.kb0 = 0;
       s.kb1 = num_kb;
       tile += stride;
       return true;
     }
     if (u >= end) return false;
-    s.tile = (int)(u / num_kb);
+    s.tile = s.ltile = (int)(u / num_kb);
     s.kb0 = (int)(u - (long long)s.tile * num_kb);
     const long long left = end - u;
     const int room = num_kb - s.kb0;
@@ -287,12 +331,14 @@ __device__ __forceinline__ void unpack_stage(const uint8_t* raw, uint8_t* dst, i
 }
 
 // out = ((float)(acc >> S) * sa) * sb * post for two neighbouring columns: three roundings, the
-// reference's order.  acc is a multiple of 2^S, so (float)acc * 2^-S equals (float)(acc >> S) and the
-// shift moves from the integer pipe, which this epilogue saturates first, to the FMA pipe.
-template <int S, bool SB_ROW>
-__device__ __forceinline__ float2 dequant2(const GemmParams& p, uint32_t a0, uint32_t a1, int col, float2 sa, float2 sb, float2 post) {
+// reference's order.  acc is a multiple of 2^S, so (float)acc * 2^-S (`unshift`) equals
+// (float)(acc >> S) and the shift moves from the integer pipe, which this epilogue saturates first,
+// to the FMA pipe.  SHIFTED: the kernel has a packed operand at all (else unshift is not applied).
+template <bool SHIFTED, bool SB_ROW>
+__device__ __forceinline__ float2 dequant2(const GemmParams& p, uint32_t a0, uint32_t a1, int col, float2 sa, float2 sb, float2 post,
+                                           float2 unshift) {
   float2 f = make_float2((float)(int)a0, (float)(int)a1);
-  if (S) f = __fmul2_rn(f, make_float2(1.0f / (float)(1 << S), 1.0f / (float)(1 << S)));
+  if (SHIFTED) f = __fmul2_rn(f, unshift);
   if (SB_ROW) sb = make_float2(col < p.N ? p.sb[col] : 0.0f, col + 1 < p.N ? p.sb[col + 1] : 0.0f);
   return __fmul2_rn(__fmul2_rn(__fmul2_rn(f, sa), sb), post);
 }
@@ -368,7 +414,11 @@ __device__ __forceinline__ void store_chunk(const GemmParams& p, int row, bool r
 template <int BN, bool A4, bool B4, bool PAIR>
 __global__ void __launch_bounds__(kEpiThreads + 64 + ((A4 || B4) ? kUnpackThreads : 0), 1)
     gemm_i8_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
-                   const __grid_constant__ CUtensorMap tma_out, GemmParams p) {
+                   const __grid_constant__ CUtensorMap tma_out, const __grid_constant__ CUtensorMap tma_a2,
+                   const __grid_constant__ CUtensorMap tma_b2, const __grid_constant__ CUtensorMap tma_out2, GemmParams p,
+                   GemmParams p2) {
+  // p2 (p2.M > 0): the rider problem of a dual launch, INT8 x INT8 with the same tile width; its A
+  // operand goes straight into the int8 stage even in the kernel built for a packed main operand
   using L = SmemLayout<BN, A4, B4, PAIR>;
   constexpr int STAGES = L::kStages;
   constexpr bool kUnpack = A4 || B4;
@@ -404,6 +454,13 @@ __global__ void __launch_bounds__(kEpiThreads + 64 + ((A4 || B4) ? kUnpackThread
   // arrivals per phase: per thread in a single CTA; one elected lane per warp of both CTAs in a pair
   constexpr uint32_t kDrainArrivals = PAIR ? 2 * (kEpiThreads / 32) : kEpiThreads;
   constexpr uint32_t kUnpackArrivals = PAIR ? 2 * (kUnpackThreads / 32) : kUnpackThreads;
+  const int n_tiles2 = (p2.N + BN - 1) / BN;                       // rider problem (dual launch)
+  const int rider_tiles = p2.M > 0 ? ((p2.M + kBM - 1) / kBM) * n_tiles2 : 0;
+  auto make_iter = [&]() {
+    SegmentIter it(p, num_tiles, worker, nworkers);
+    if (rider_tiles) it.add_rider(rider_tiles, p2.num_kb, worker, nworkers);
+    return it;
+  };
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -422,6 +479,11 @@ __global__ void __launch_bounds__(kEpiThreads + 64 + ((A4 || B4) ? kUnpackThread
     tma_prefetch_desc(&tma_a);
     tma_prefetch_desc(&tma_b);
     if (p.staged) tma_prefetch_desc(&tma_out);
+    if (rider_tiles) {
+      tma_prefetch_desc(&tma_a2);
+      tma_prefetch_desc(&tma_b2);
+      if (p2.staged) tma_prefetch_desc(&tma_out2);
+    }
   }
   if (warp == kMmaWarp) {
     if (PAIR) tmem_alloc_pair(tmem_slot, kTmemCols);
@@ -438,14 +500,21 @@ __global__ void __launch_bounds__(kEpiThreads + 64 + ((A4 || B4) ? kUnpackThread
       constexpr uint32_t kTx = (A4 ? L::kRawA : L::kA) + (B4 ? L::kRawB : L::kB);
       uint32_t s = 0, ph = 0;  // ring slot and phase, running on across tiles
       bool ok = true;
-      SegmentIter iter(p, num_tiles, worker, nworkers);
+      SegmentIter iter = make_iter();
       Segment seg;
       const uint32_t full0 = PAIR ? mapa_rank(smem_u32(full), 0) : 0u;  // full[] of the rank-0 CTA
       while (ok && iter.next(seg)) {
-        const int m0 = (seg.tile / n_tiles) * kTileM + (int)rank * kBM, n0 = (seg.tile % n_tiles) * BN;
+        const int nt = seg.prob ? n_tiles2 : n_tiles;
+        const int m0 = (seg.ltile / nt) * kTileM + (int)rank * kBM, n0 = (seg.ltile % nt) * BN;
         for (int kb = seg.kb0; kb < seg.kb1; ++kb, s = (s + 1 == STAGES ? 0 : s + 1), ph ^= (s == 0 ? 1u : 0u)) {
           ok = mbar_wait(&empty[s], ph ^ 1u, abort_flag);
           if (!ok) break;
+          if (seg.prob) {  // rider: both operands one code per byte
+            mbar_expect_tx(&full[s], L::kA + L::kB);
+            tma_load_2d(sA + s * L::kA, &tma_a2, &full[s], kb * kBK, m0);
+            tma_load_2d(sB + s * L::kB, &tma_b2, &full[s], kb * kBK, n0);
+            continue;
+          }
           if (PAIR) {
             // rank 0 announces the bytes of both CTAs; each CTA loads its rows of A and its half of B
             if (rank == 0) mbar_expect_tx(&full[s], 2u * ((A4 ? 0u : (uint32_t)L::kA) + (uint32_t)L::kB));
@@ -471,7 +540,7 @@ __global__ void __launch_bounds__(kEpiThreads + 64 + ((A4 || B4) ? kUnpackThread
       constexpr uint32_t idesc = instr_desc_i8(BN, kTileM);
       uint32_t s = 0, ph = 0, it = 0;
       bool ok = true;
-      SegmentIter iter(p, num_tiles, worker, nworkers);
+      SegmentIter iter = make_iter();
       Segment seg;
       // shared-memory descriptors: the high word is the same for every operand slab, the low word is
       // (address >> 4) | leading-offset field and moves by 2 per 32-byte K step
@@ -511,12 +580,26 @@ __global__ void __launch_bounds__(kEpiThreads + 64 + ((A4 || B4) ? kUnpackThread
     if (kUnpack) asm volatile("setmaxnreg.inc.sync.aligned.u32 152;" ::: "memory");
     const int q = warp & 3;  // tensor-memory lane quarter this warp may read
     const int team = warp >> 2;
-    const bool raw = p.out_dtype == HOT_I32;  // raw accumulators: no scales to read
-    const float sb0 = (p.sb_row || raw || p.group_kb) ? 0.0f : p.sb[0];
+    // the problem the current segment belongs to (the rider of a dual launch has its own output, scales
+    // and no INT4 shift), and what follows from it
+    const GemmParams* cur = &p;
+    const CUtensorMap* omap = &tma_out;
+    bool raw = false, out16 = false;  // raw accumulators wanted (no scales to read); 16-bit output
+    float sb0 = 0.0f;
+    int shift = kShift;
+    auto select_problem = [&](int prob) {
+      cur = prob ? &p2 : &p;
+      omap = prob ? &tma_out2 : &tma_out;
+      raw = cur->out_dtype == HOT_I32;
+      out16 = cur->out_dtype == HOT_BF16;
+      sb0 = (cur->sb_row || raw || cur->group_kb) ? 0.0f : cur->sb[0];
+      shift = prob ? 0 : kShift;
+    };
+    select_problem(0);
     __shared__ uint32_t s_finisher;
     uint32_t it = 0;
     bool ok = true;
-    SegmentIter iter(p, num_tiles, worker, nworkers);
+    SegmentIter iter = make_iter();
     Segment seg;
     // Output path: a thread holds one row of the accumulator, so stores from registers would touch 32
     // lines per instruction.  Instead each warp lays 32 rows x 64 bytes out in a swizzled shared-memory
@@ -525,7 +608,6 @@ __global__ void __launch_bounds__(kEpiThreads + 64 + ((A4 || B4) ? kUnpackThread
     uint8_t* const store_stage = smem + L::kOffStore + warp * 4096;
     uint32_t boxes = 0;  // boxes filled by this warp so far (selects the buffer)
     float run[kGrouped ? BN / 64 : 1][32];  // grouped mode only
-    const bool out16 = p.out_dtype == HOT_BF16;
     auto owns = [&](int c) { return (c & 1) == team; };  // chunk c is this team's
     const uint32_t drained0 = PAIR ? mapa_rank(smem_u32(tmem_empty), 0) : 0u;  // tmem_empty[] of the rank-0 CTA
     // this thread has read all it needs of accumulator buffer `b`
@@ -555,7 +637,7 @@ __global__ void __launch_bounds__(kEpiThreads + 64 + ((A4 || B4) ? kUnpackThread
       __syncwarp();
       if (lane == 0) {
         const int y = m0 + q * 32;
-        if (col < p.N && y < p.M) tma_store_2d(&tma_out, box, col << (out16 ? 1 : 2), y);
+        if (col < cur->N && y < cur->M) tma_store_2d(omap, box, col << (out16 ? 1 : 2), y);
         bulk_commit_group();  // always: the buffer rotation counts groups
       }
       ++boxes;
@@ -591,16 +673,18 @@ __global__ void __launch_bounds__(kEpiThreads + 64 + ((A4 || B4) ? kUnpackThread
     };
     // chunk c (32 columns) of the current tile, ascending; acc = accumulators before the INT4 shift
     auto emit = [&](int c, uint32_t (&acc)[32]) {
-      if (!p.staged) {
+      if (!cur->staged) {
         if (kShift) {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) acc[i] = (uint32_t)((int)acc[i] >> kShift);
+          for (int i = 0; i < 32; ++i) acc[i] = (uint32_t)((int)acc[i] >> shift);
         }
-        store_chunk(p, row, row_ok, n0 + c * 32, acc, sa, sb0);
+        store_chunk(*cur, row, row_ok, n0 + c * 32, acc, sa, sb0);
         return;
       }
       const int col0 = n0 + c * 32;
-      const float2 sa2 = make_float2(sa, sa), sb2 = make_float2(sb0, sb0), post2 = make_float2(p.post, p.post);
+      const float2 sa2 = make_float2(sa, sa), sb2 = make_float2(sb0, sb0), post2 = make_float2(cur->post, cur->post);
+      const float us = shift ? 1.0f / (float)(1 << kShift) : 1.0f;
+      const float2 unshift = make_float2(us, us);
       if (raw) {
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
@@ -608,20 +692,23 @@ __global__ void __launch_bounds__(kEpiThreads + 64 + ((A4 || B4) ? kUnpackThread
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
             const int i = 16 * h + 4 * j;
-            put(box, j, make_uint4((uint32_t)((int)acc[i] >> kShift), (uint32_t)((int)acc[i + 1] >> kShift),
-                                   (uint32_t)((int)acc[i + 2] >> kShift), (uint32_t)((int)acc[i + 3] >> kShift)));
+            put(box, j, make_uint4((uint32_t)((int)acc[i] >> shift), (uint32_t)((int)acc[i + 1] >> shift),
+                                   (uint32_t)((int)acc[i + 2] >> shift), (uint32_t)((int)acc[i + 3] >> shift)));
           }
           close_box(box, col0 + 16 * h);
         }
-      } else if (p.sb_row) {  // one instance per scale layout, so the choice is not made per element
-        store_pairs(col0, [&](int i) { return dequant2<kShift, true>(p, acc[i], acc[i + 1], col0 + i, sa2, sb2, post2); });
+      } else if (cur->sb_row) {  // one instance per scale layout, so the choice is not made per element
+        store_pairs(col0, [&](int i) { return dequant2<kShift != 0, true>(*cur, acc[i], acc[i + 1], col0 + i, sa2, sb2, post2, unshift); });
       } else {
-        store_pairs(col0, [&](int i) { return dequant2<kShift, false>(p, acc[i], acc[i + 1], col0 + i, sa2, sb2, post2); });
+        store_pairs(col0, [&](int i) { return dequant2<kShift != 0, false>(*cur, acc[i], acc[i + 1], col0 + i, sa2, sb2, post2, unshift); });
       }
     };
     for (; ok && iter.next(seg); ++it) {
-      m0 = (seg.tile / n_tiles) * kTileM + (int)rank * kBM;
-      n0 = (seg.tile % n_tiles) * BN;
+      select_problem(seg.prob);
+      const GemmParams& p = *cur;  // from here on `p` is the segment's problem
+      const int nt = seg.prob ? n_tiles2 : n_tiles;
+      m0 = (seg.ltile / nt) * kTileM + (int)rank * kBM;
+      n0 = (seg.ltile % nt) * BN;
       const uint32_t buf = it & 1u, bph = (it >> 1) & 1u;
       const int row_loc = q * 32 + lane;
       row = m0 + row_loc;
@@ -773,14 +860,14 @@ __global__ void __launch_bounds__(kEpiThreads + 64 + ((A4 || B4) ? kUnpackThread
     const uint32_t ready0 = PAIR ? mapa_rank(smem_u32(ready), 0) : 0u;  // ready[] of the rank-0 CTA
     uint32_t s = 0, ph = 0;
     bool ok = true;
-    SegmentIter iter(p, num_tiles, worker, nworkers);
+    SegmentIter iter = make_iter();
     Segment seg;
     while (ok && iter.next(seg)) {
       for (int kb = seg.kb0; kb < seg.kb1; ++kb, s = (s + 1 == STAGES ? 0 : s + 1), ph ^= (s == 0 ? 1u : 0u)) {
         ok = mbar_wait(PAIR ? &full_a[s] : &full[s], ph, abort_flag);
         if (!ok) break;
-        if (A4) unpack_stage(rawA + s * L::kRawA, sA + s * L::kA, kBM, utid, kUnpackThreads);
-        if (B4) unpack_stage(rawB + s * L::kRawB, sB + s * L::kB, BN, utid, kUnpackThreads);
+        if (A4 && !seg.prob) unpack_stage(rawA + s * L::kRawA, sA + s * L::kA, kBM, utid, kUnpackThreads);
+        if (B4 && !seg.prob) unpack_stage(rawB + s * L::kRawB, sB + s * L::kB, BN, utid, kUnpackThreads);
         fence_proxy_async_smem();  // generic-proxy writes -> visible to the tensor core (async proxy)
         if (PAIR) {
           __syncwarp();
@@ -816,10 +903,21 @@ struct Plan {
   bool stream_k;
   unsigned grid;
   bool pair = false;  // clusters of two CTAs per 256 x bn tile
+  double cost = 0.0;  // the model's estimate for this plan (k-block cost units)
+};
+
+// The second problem of a dual launch (INT8 x INT8, one code per byte on both sides).
+struct Rider {
+  const void* a;
+  int64_t lda;
+  const void* b;
+  int64_t ldb;
+  GemmParams p;
 };
 
 template <int BN, bool A4, bool B4, bool PAIR = false>
-int launch_gemm(const void* a, int64_t lda, const void* b, int64_t ldb, const GemmParams& p, const Plan& plan, cudaStream_t st) {
+int launch_gemm(const void* a, int64_t lda, const void* b, int64_t ldb, const GemmParams& p, const Plan& plan, cudaStream_t st,
+                const Rider* rider = nullptr) {
   using L = SmemLayout<BN, A4, B4, PAIR>;
   CUtensorMap ma, mb;
   int rc;
@@ -837,6 +935,21 @@ int launch_gemm(const void* a, int64_t lda, const void* b, int64_t ldb, const Ge
   if (pp.staged) {
     rc = make_map(&mo, p.out, p.M, (int64_t)p.N * esz, p.ldo * esz, 64, 32, 64);
     if (rc) return rc;
+  }
+  GemmParams p2 = {};  // M = 0: no rider
+  CUtensorMap ma2 = ma, mb2 = mb, mo2 = mo;
+  if (rider) {
+    p2 = rider->p;
+    rc = make_map(&ma2, rider->a, p2.M, p2.K, rider->lda, kBK, kBM, 128);
+    if (rc) return rc;
+    rc = make_map(&mb2, rider->b, p2.N, p2.K, rider->ldb, kBK, L::kBRows, 128);
+    if (rc) return rc;
+    const int64_t esz2 = p2.out_dtype == HOT_BF16 ? 2 : 4;
+    p2.staged = (reinterpret_cast<uintptr_t>(p2.out) % 16 == 0 && (p2.ldo * esz2) % 16 == 0) ? 1 : 0;
+    if (p2.staged) {
+      rc = make_map(&mo2, p2.out, p2.M, (int64_t)p2.N * esz2, p2.ldo * esz2, 64, 32, 64);
+      if (rc) return rc;
+    }
   }
   auto kernel = gemm_i8_kernel<BN, A4, B4, PAIR>;
   static bool attr_set = false;  // per instantiation
@@ -865,9 +978,9 @@ int launch_gemm(const void* a, int64_t lda, const void* b, int64_t ldb, const Ge
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    HOT_CUDA(cudaLaunchKernelEx(&cfg, kernel, ma, mb, mo, pp));
+    HOT_CUDA(cudaLaunchKernelEx(&cfg, kernel, ma, mb, mo, ma2, mb2, mo2, pp, p2));
   } else {
-    kernel<<<plan.grid, kThreads, L::kBytes, st>>>(ma, mb, mo, pp);
+    kernel<<<plan.grid, kThreads, L::kBytes, st>>>(ma, mb, mo, ma2, mb2, mo2, pp, p2);
   }
   HOT_CUDA(cudaGetLastError());
   return HOT_OK;
@@ -932,6 +1045,7 @@ Plan make_plan(int M, int N, int num_kb, int sms, size_t ws_bytes, bool allow_pa
       }
     }
   }
+  best.cost = best_cost;
   return best;
 }
 
@@ -1074,4 +1188,96 @@ extern "C" int hot_gemm_i8_grouped(const void* a, int64_t lda, const void* b, in
   const int64_t tiles = tiles_for(p.M, p.N, 128);
   const Plan plan{128, false, (unsigned)(tiles < sms ? tiles : sms)};
   return launch_gemm<128, false, false>(a, lda, b, ldb, p, plan, (cudaStream_t)stream);
+}
+
+namespace hot {
+namespace {
+// Validates one problem of hot_gemm_i8_dual and turns it into kernel parameters.
+int fill_problem(const hot_gemm_problem_t* g, bool allow_packed_a, GemmParams* p, const char* who) {
+  if (!g || !g->a || !g->b || !g->out) HOT_FAIL(HOT_ERR_ARG, "hot_gemm_i8_dual: %s: null pointer", who);
+  if (g->M <= 0 || g->N <= 0 || g->K <= 0 || g->M > (1 << 30) || g->N > (1 << 30) || g->K > (1 << 30))
+    HOT_FAIL(HOT_ERR_ARG, "hot_gemm_i8_dual: %s: bad shape", who);
+  const bool a4 = g->a_storage == HOT_STORE_INT4;
+  if (a4 && !allow_packed_a) HOT_FAIL(HOT_ERR_UNSUPPORTED, "hot_gemm_i8_dual: %s: packed INT4 is taken for the main problem's A only", who);
+  if (a4 && g->K % 2 != 0) HOT_FAIL(HOT_ERR_ARG, "hot_gemm_i8_dual: %s: packed INT4 operands need an even K", who);
+  const int64_t abytes = a4 ? g->K / 2 : g->K;
+  if (g->lda % 16 || g->ldb % 16 || g->lda < abytes || g->ldb < g->K || ((uintptr_t)g->a) % 16 || ((uintptr_t)g->b) % 16)
+    HOT_FAIL(HOT_ERR_ARG, "hot_gemm_i8_dual: %s: operand base and pitch must be 16-byte aligned and cover K", who);
+  if (g->out_dtype != HOT_F32 && g->out_dtype != HOT_BF16 && g->out_dtype != HOT_I32)
+    HOT_FAIL(HOT_ERR_UNSUPPORTED, "hot_gemm_i8_dual: %s: out dtype %d", who, g->out_dtype);
+  if (g->out_dtype != HOT_I32 && (!g->scale_a || !g->scale_b)) HOT_FAIL(HOT_ERR_ARG, "hot_gemm_i8_dual: %s: null scale pointer", who);
+  const int osz = g->out_dtype == HOT_BF16 ? 2 : 4;
+  if (g->ldo < g->N || ((uintptr_t)g->out) % 16 != 0 || (g->ldo * osz) % 4 != 0 || g->scale_a_per_row < 0)
+    HOT_FAIL(HOT_ERR_ARG, "hot_gemm_i8_dual: %s: bad output pitch / alignment / scale layout", who);
+  *p = GemmParams{};
+  p->M = (int)g->M;
+  p->N = (int)g->N;
+  p->K = (int)g->K;
+  p->num_kb = (int)((g->K + kBK - 1) / kBK);
+  p->sa = g->scale_a;
+  p->sb = g->scale_b;
+  p->sa_row = g->scale_a_per_row;
+  p->sb_row = g->scale_b_per_row ? 1 : 0;
+  p->post = g->post;
+  p->out = g->out;
+  p->ldo = g->ldo;
+  p->out_dtype = g->out_dtype;
+  return HOT_OK;
+}
+
+// k-blocks of the busiest worker under the dual schedule of SegmentIter (same rules, on the host)
+int64_t dual_max_load(int64_t t0, int kb0, int64_t t1, int kb1, int workers) {
+  const int lag = (kb1 + kb0 / 2) / kb0;
+  const int64_t free_w = workers - t1;
+  int64_t worst = 0;
+  for (int w = 0; w < workers; ++w) {
+    int64_t load = w < t1 ? kb1 : 0;
+    for (int round = 0;; ++round) {
+      const bool all = round >= lag;
+      const int64_t base = all ? lag * free_w + (round - lag) * (int64_t)workers : round * free_w;
+      if (base >= t0) break;
+      const int64_t rank = all ? w : w - t1;
+      if (rank < 0) continue;
+      if (base + rank >= t0) break;
+      load += kb0;
+    }
+    if (load > worst) worst = load;
+  }
+  return worst;
+}
+}  // namespace
+}  // namespace hot
+
+extern "C" int hot_gemm_i8_dual(const hot_gemm_problem_t* main_problem, const hot_gemm_problem_t* rider_problem,
+                                uint32_t* status_word, hot_stream_t stream) {
+  using namespace hot;
+  GemmParams p0, p1;
+  if (int rc = fill_problem(main_problem, true, &p0, "main problem")) return rc;
+  if (int rc = fill_problem(rider_problem, false, &p1, "rider problem")) return rc;
+  p0.status = p1.status = status_word;
+  cudaStream_t st = (cudaStream_t)stream;
+  const int sms = device_sm_count();
+  if (sms <= 0) return HOT_ERR_CUDA;
+  const bool a4 = main_problem->a_storage == HOT_STORE_INT4;
+  // One launch pays when the rider's few long tiles fit beside the main problem's last, partly empty
+  // wave; otherwise (or with HOT_GEMM_DUAL=0) the two problems run one after the other.
+  const int64_t t0 = tiles_for(p0.M, p0.N, 256), t1 = tiles_for(p1.M, p1.N, 256);
+  const Plan s0 = make_plan(p0.M, p0.N, p0.num_kb, sms, 0, !a4, a4), s1 = make_plan(p1.M, p1.N, p1.num_kb, sms, 0, true, false);
+  const char* env = getenv("HOT_GEMM_DUAL");
+  bool dual = t1 <= sms && t0 >= sms && t1 >= 1 && !(env && env[0] == '0');
+  if (dual && !(env && env[0] == '1')) {
+    const double together = (double)dual_max_load(t0, p0.num_kb, t1, p1.num_kb, sms) * (256 + 400.0);
+    // a second launch costs about 3 us of ramp-down and ramp-up, some 4000 units of this model
+    dual = together < s0.cost + s1.cost + 4000.0;
+  }
+  if (dual) {
+    Rider r{rider_problem->a, rider_problem->lda, rider_problem->b, rider_problem->ldb, p1};
+    const Plan plan{256, false, (unsigned)sms};
+    if (a4) return launch_gemm<256, true, false>(main_problem->a, main_problem->lda, main_problem->b, main_problem->ldb, p0, plan, st, &r);
+    return launch_gemm<256, false, false>(main_problem->a, main_problem->lda, main_problem->b, main_problem->ldb, p0, plan, st, &r);
+  }
+  int rc = a4 ? launch_bn<true, false>(main_problem->a, main_problem->lda, main_problem->b, main_problem->ldb, p0, s0, st)
+              : launch_bn<false, false>(main_problem->a, main_problem->lda, main_problem->b, main_problem->ldb, p0, s0, st);
+  if (rc) return rc;
+  return launch_bn<false, false>(rider_problem->a, rider_problem->lda, rider_problem->b, rider_problem->ldb, p1, s1, st);
 }

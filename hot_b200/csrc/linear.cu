@@ -192,30 +192,43 @@ extern "C" int hot_linear_backward(const void* go, int64_t ldgo, const void* w, 
       return rc;
     }
   }
-  if (grad_x) {
-    if (!dual) {
-      rc = hot_row_ht_quant(go, cfg->dtype, L, O, ldgo, cfg->order_o, &cfg->q_gx, base + ws.off_qgo, ws.ld_qgo, s_go, scratch,
-                            stream);
-      if (rc) {
-        rejoin();
-        return rc;
-      }
+  if (grad_x && !dual) {
+    rc = hot_row_ht_quant(go, cfg->dtype, L, O, ldgo, cfg->order_o, &cfg->q_gx, base + ws.off_qgo, ws.ld_qgo, s_go, scratch,
+                          stream);
+    if (rc) {
+      rejoin();
+      return rc;
     }
-    rejoin();  // the g_x GEMM needs the quantised weight
+  }
+  if (grad_w && !dual) {
+    rc = hot_col_ht_quant(go, cfg->dtype, L, O, ldgo, cfg->order_l, cfg->sel_l, cfg->rank_l, &cfg->q_gw,
+                          HOT_LAYOUT_TRANSPOSED, base + ws.off_qgw, ws.ld_qgw, s_gw, scratch + 64 + L, stream);
+    if (rc) {
+      rejoin();
+      return rc;
+    }
+  }
+  rejoin();  // the g_x GEMM needs the quantised weight
+  const float post_x = 1.0f / (float)cfg->order_o, post_w = 1.0f / (float)cfg->order_l;
+  const int gx_row = cfg->q_gx.scale_mode == HOT_SCALE_ROW, gw_row = cfg->q_gw.scale_mode == HOT_SCALE_ROW;
+  if (grad_x && grad_w && cfg->q_gw.storage == HOT_STORE_INT8 && cfg->q_x.storage == HOT_STORE_INT8) {
+    // both products in one launch: the few long g_w tiles run in the SMs that the last wave of g_x tiles leaves idle
+    hot_gemm_problem_t gx = {base + ws.off_qgo, cfg->q_gx.storage, ws.ld_qgo, base + ws.off_qw, ws.ld_qw, L, I, O, s_go, gx_row,
+                             s_w, 0, post_x, grad_x, cfg->dtype, ldgx};
+    hot_gemm_problem_t gw = {base + ws.off_qgw, HOT_STORE_INT8, ws.ld_qgw, x_q_t, hot_abc_pitch(L, cfg), O, I, ws.lp, s_gw, gw_row,
+                             scale_x, 0, post_w, grad_w, cfg->dtype, ldgw};
+    return hot_gemm_i8_dual(&gx, &gw, status_word, stream);
+  }
+  if (grad_x) {
     rc = hot_gemm_i8_ws(base + ws.off_qgo, cfg->q_gx.storage, ws.ld_qgo, base + ws.off_qw, HOT_STORE_INT8, ws.ld_qw, L, I, O,
-                        s_go, cfg->q_gx.scale_mode == HOT_SCALE_ROW, s_w, 0, 1.0f / (float)cfg->order_o, grad_x, cfg->dtype,
-                        ldgx, ws.gemm_bytes ? base + ws.off_gemm : nullptr, ws.gemm_bytes, status_word, stream);
+                        s_go, gx_row, s_w, 0, post_x, grad_x, cfg->dtype, ldgx, ws.gemm_bytes ? base + ws.off_gemm : nullptr,
+                        ws.gemm_bytes, status_word, stream);
     if (rc) return rc;
   }
   if (grad_w) {
-    if (!dual) {
-      rc = hot_col_ht_quant(go, cfg->dtype, L, O, ldgo, cfg->order_l, cfg->sel_l, cfg->rank_l, &cfg->q_gw,
-                            HOT_LAYOUT_TRANSPOSED, base + ws.off_qgw, ws.ld_qgw, s_gw, scratch + 64 + L, stream);
-      if (rc) return rc;
-    }
     rc = hot_gemm_i8_ws(base + ws.off_qgw, cfg->q_gw.storage, ws.ld_qgw, x_q_t, cfg->q_x.storage, hot_abc_pitch(L, cfg), O, I,
-                        ws.lp, s_gw, cfg->q_gw.scale_mode == HOT_SCALE_ROW, scale_x, 0, 1.0f / (float)cfg->order_l, grad_w,
-                        cfg->dtype, ldgw, ws.gemm_bytes ? base + ws.off_gemm : nullptr, ws.gemm_bytes, status_word, stream);
+                        ws.lp, s_gw, gw_row, scale_x, 0, post_w, grad_w, cfg->dtype, ldgw,
+                        ws.gemm_bytes ? base + ws.off_gemm : nullptr, ws.gemm_bytes, status_word, stream);
     if (rc) return rc;
   }
   return HOT_OK;

@@ -163,6 +163,36 @@ def gemm_i8(a: torch.Tensor, a_storage: str, b: torch.Tensor, b_storage: str, M:
     return out
 
 
+def gemm_i8_dual(main: dict, rider: dict, status: Optional[torch.Tensor] = None):
+    """Two ``gemm_i8`` problems in one launch (the rider's tiles fill the SMs the main problem's last
+    wave leaves idle); each dict holds a, a_storage ("int8" | "int4"; rider: "int8"), b, M, N, K,
+    scale_a, scale_b, post, out_dtype and optionally a_rows_per_scale.  Returns (out_main, out_rider)."""
+    outs, probs = [], []
+    odts = {torch.float32: C.HOT_F32, torch.bfloat16: C.HOT_BF16, torch.int32: C.HOT_I32}
+    for g in (main, rider):
+        a, b = g["a"], g["b"]
+        _require_cuda(a, b)
+        out = torch.empty((g["M"], g["N"]), dtype=g.get("out_dtype", torch.float32), device=a.device)
+        sa, sb = g.get("scale_a"), g.get("scale_b")
+        pr = C.HotGemmProblem()
+        pr.a, pr.a_storage, pr.lda = a.data_ptr(), C.STORE_INT4 if g.get("a_storage", "int8") == "int4" else C.STORE_INT8, a.stride(0)
+        pr.b, pr.ldb = b.data_ptr(), b.stride(0)
+        pr.M, pr.N, pr.K = g["M"], g["N"], g["K"]
+        pr.scale_a = sa.data_ptr() if sa is not None else None
+        pr.scale_a_per_row = int(g.get("a_rows_per_scale", 1)) if (sa is not None and sa.numel() > 1) else 0
+        pr.scale_b = sb.data_ptr() if sb is not None else None
+        pr.scale_b_per_row = int(sb is not None and sb.numel() > 1)
+        pr.post = float(g.get("post", 1.0))
+        pr.out, pr.out_dtype, pr.ldo = out.data_ptr(), odts[out.dtype], out.stride(0)
+        outs.append(out)
+        probs.append(pr)
+    with torch.cuda.device(main["a"].device):
+        C.check(C.lib().hot_gemm_i8_dual(ctypes.byref(probs[0]), ctypes.byref(probs[1]),
+                                         status.data_ptr() if status is not None else None, _stream(main["a"])),
+                "hot_gemm_i8_dual")
+    return outs[0], outs[1]
+
+
 def row_ht_quant_batched(x: torch.Tensor, order: int, q: Quant):
     """``row_ht_quant`` on a batch ``x`` [B, rows, cols] with one scale per sample.  Returns (codes
     uint8 [B*rows, cols] or packed [B*rows, cols/2], scales float32 [B])."""

@@ -226,6 +226,34 @@ int hot_gemm_i8_grouped(const void* a, int64_t lda, const void* b, int64_t ldb, 
                         int64_t groups, int64_t group_k, const float* scale_a, const float* scale_b, float post,
                         void* out, int out_dtype, int64_t ldo, uint32_t* status_word, hot_stream_t stream);
 
+/*
+ * Two integer GEMMs in one launch.  The g_x product of a layer leaves its last wave of tiles nearly
+ * empty at ViT sizes (297 tiles of 128 x 256 on 148 SMs) and the g_w product is a few long tiles:
+ * run together, the g_w tiles ride in the SMs that wave leaves idle.  Each problem is what
+ * hot_gemm_i8 computes; results are identical to two hot_gemm_i8 calls, and when the shapes do not
+ * suit one launch (rider tiles of 128 x 256 more than SMs, or no gain by the cost model) that is
+ * what happens internally.
+ *   main:  a INT8 or packed INT4, b INT8;   rider: a and b INT8.
+ */
+typedef struct hot_gemm_problem {
+  const void* a;
+  int32_t a_storage;        /* hot_storage of a (b is HOT_STORE_INT8) */
+  int64_t lda;              /* bytes */
+  const void* b;
+  int64_t ldb;              /* bytes */
+  int64_t M, N, K;
+  const float* scale_a;
+  int32_t scale_a_per_row;  /* as in hot_gemm_i8 */
+  const float* scale_b;
+  int32_t scale_b_per_row;
+  float post;
+  void* out;
+  int32_t out_dtype;        /* hot_dtype */
+  int64_t ldo;              /* elements */
+} hot_gemm_problem_t;
+int hot_gemm_i8_dual(const hot_gemm_problem_t* main_problem, const hot_gemm_problem_t* rider_problem,
+                     uint32_t* status_word, hot_stream_t stream);
+
 /* Per-layer configuration of the backward pass (scheme gih_gwlr, utils/quant_matmul.py:214-348). */
 typedef struct hot_linear_cfg {
   int32_t dtype;      /* dtype of grad_out, w, x and of the returned gradients                  */

@@ -191,6 +191,52 @@ def test_gemm_i8_accumulators_and_dequant(ops, M, N, K, a_storage, b_storage, sc
     assert torch.equal(out_bf.cpu(), want_bf)
 
 
+@pytest.mark.parametrize("main_shape,rider_shape", [
+    ((12608, 768, 3072), (3072, 768, 6304)),     # fc1: g_x and g_w
+    ((12608, 768, 2304), (2304, 768, 6304)),     # qkv
+    ((12608, 3072, 768), (768, 3072, 6304)),     # fc2
+    ((19000, 256, 384), (256, 256, 1000)),       # ragged last row tile; rider K not a multiple of 128
+    ((300, 100, 256), (128, 128, 128)),          # too few main tiles: falls back to two launches
+])
+@pytest.mark.parametrize("a_storage", ["int8", "int4"])
+@pytest.mark.parametrize("force", ["1", None])
+def test_gemm_i8_dual(ops, main_shape, rider_shape, a_storage, force, monkeypatch):
+    """Two problems in one launch equal the two problems run separately, bit for bit."""
+    if force:
+        monkeypatch.setenv("HOT_GEMM_DUAL", force)
+    rng = np.random.default_rng(sum(main_shape) + sum(rider_shape))
+
+    def operand(rows, K, storage):
+        lim = 7 if storage == "int4" else 127
+        c = rng.integers(-lim, lim + 1, size=(rows, K)).astype(np.int32)
+        packed = oc.pack_int4(c) if storage == "int4" else c.astype(np.int8).view(np.uint8)
+        pitch = (packed.shape[1] + 15) // 16 * 16
+        buf = np.zeros((rows, pitch), np.uint8)
+        buf[:, :packed.shape[1]] = packed
+        return c, _dev(buf)
+    (M0, N0, K0), (M1, N1, K1) = main_shape, rider_shape
+    a0, a0d = operand(M0, K0, a_storage)
+    b0, b0d = operand(N0, K0, "int8")
+    a1, a1d = operand(M1, K1, "int8")
+    b1, b1d = operand(N1, K1, "int8")
+    sa0 = (rng.random(M0, dtype=np.float32) + 0.5) * 1e-4
+    sb0, sa1, sb1 = np.array([3.3e-3], np.float32), np.array([7.1e-5], np.float32), np.array([2.2e-2], np.float32)
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    main = dict(a=a0d, a_storage=a_storage, b=b0d, M=M0, N=N0, K=K0, scale_a=_dev(sa0), scale_b=_dev(sb0), post=1.0 / 16,
+                out_dtype=torch.bfloat16)
+    rider = dict(a=a1d, b=b1d, M=M1, N=N1, K=K1, scale_a=_dev(sa1), scale_b=_dev(sb1), post=1.0 / 16, out_dtype=torch.float32)
+    o0, o1 = ops.gemm_i8_dual(main, rider, status=status)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0, "a bounded device-side wait ran out"
+    # float64 BLAS is exact for these integer products (|acc| < 2^53) and far quicker than int64 matmul
+    r0 = (a0.astype(np.float64) @ b0.astype(np.float64).T).astype(np.float32)
+    r1 = (a1.astype(np.float64) @ b1.astype(np.float64).T).astype(np.float32)
+    want0 = torch.from_numpy(((r0 * sa0[:, None]) * sb0[0]) * np.float32(1.0 / 16)).to(torch.bfloat16)
+    want1 = ((r1 * sa1[0]) * sb1[0]) * np.float32(1.0 / 16)
+    assert torch.equal(o0.cpu(), want0)
+    assert np.array_equal(o1.cpu().numpy(), want1)
+
+
 def _run_backward(ops, x, w, go, order_l, sel, dtype, *, gx_row=False, gw_row=False, rounding="noise", rng=None,
                   storage4="int4"):
     L, I = x.shape
