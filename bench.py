@@ -651,7 +651,8 @@ def config1_leg(ops, device, status):
 
 def e2e_leg(layers, a, dtype, device, flops):
     """The same step through HLQ_backward.backward with Go and X in pinned host memory and both
-    gradients copied back, every layer, every step."""
+    gradients copied back, every layer, every step; the copies of neighbouring layers overlap the
+    call (two copy streams), as a caller streaming a model through the plugin would arrange it."""
     import HLQ_backward
     shapes = {}
     for name, i_f, o_f in LAYERS:
@@ -668,16 +669,37 @@ def e2e_leg(layers, a, dtype, device, flops):
     h2d *= a.blocks
     d2h *= a.blocks
 
+    # The caller's side of the pipeline: while layer k runs, the inputs of layer k + 1 come up on one
+    # copy stream and the gradients of layer k - 1 go down on another (PCIe carries both directions).
+    comp = torch.cuda.current_stream(device)
+    s_in, s_out = torch.cuda.Stream(device), torch.cuda.Stream(device)
+    order = [(b, li) for b in reversed(range(a.blocks)) for li in reversed(range(len(LAYERS)))]
+
+    def upload(k):
+        l = layers[order[k][0]][order[k][1]]
+        s = shapes[l["name"]]
+        with torch.cuda.stream(s_in):
+            go = s["go"].to(device, non_blocking=True)
+            x = s["x"].to(device, non_blocking=True)
+            ev = torch.cuda.Event()
+            ev.record(s_in)
+        return l, s, go, x, ev
+
     def step():
-        for b in reversed(range(a.blocks)):
-            for li in reversed(range(len(LAYERS))):
-                l = layers[b][li]
-                s = shapes[l["name"]]
-                go = s["go"].to(device, non_blocking=True)
-                x = s["x"].to(device, non_blocking=True)
-                gx, gw, _ = HLQ_backward.backward(go, l["w"], x, 0, 0, 16, False)
+        nxt = upload(0)
+        for k in range(len(order)):
+            l, s, go, x, ev = nxt
+            if k + 1 < len(order):
+                nxt = upload(k + 1)
+            comp.wait_event(ev)
+            go.record_stream(comp)
+            x.record_stream(comp)
+            gx, gw, _ = HLQ_backward.backward(go, l["w"], x, 0, 0, 16, False)   # returns with gx, gw complete
+            with torch.cuda.stream(s_out):
                 s["gx"].copy_(gx, non_blocking=True)
                 s["gw"].copy_(gw, non_blocking=True)
+            gx.record_stream(s_out)
+            gw.record_stream(s_out)
         torch.cuda.synchronize(device)
 
     step()

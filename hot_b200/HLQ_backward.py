@@ -10,8 +10,8 @@ g_x, Hadamard-low-rank-INT8 g_w (the prototype multiplied zero dummies with scal
 
 Stage times: the transform and the quantiser are one fused kernel here, and so are the
 integer GEMM and its dequantisation, so entries 0 and 2 carry the fused times and entries 1
-and 3 are 0.0.  They are CUDA-event times, and like the prototype the call synchronises the
-device before returning.
+and 3 are 0.0.  They are CUDA-event times, and the call returns when its
+results are complete (it waits for its own stream; the prototype synchronises the whole device).
 """
 from __future__ import annotations
 
@@ -75,10 +75,15 @@ def backward(Go: torch.Tensor, W: torch.Tensor, X: torch.Tensor, reorder_idx_go=
     q_w_t, s_w, _ = ops.col_ht_quant(W, int(H_size), list(range(int(H_size))), q_w8, "natural")
     x_q_t, s_x, _ = ops.col_ht_quant(X, n, sel, cfg.q_x, "natural")
     ev[1].record()
-    gx = ops.gemm_i8(q_go, "int4", q_w_t, "int8", L, I, O, s_go, s_w, 1.0 / int(H_size), Go.dtype, status)
-    gw = ops.gemm_i8(q_gw, "int8", x_q_t, "int8", O, I, lp, s_gw, s_x, 1.0 / n, Go.dtype, status)
+    # both products in one launch where the shapes suit it (else two launches, decided inside)
+    gx, gw = ops.gemm_i8_dual(
+        dict(a=q_go, a_storage="int4", b=q_w_t, M=L, N=I, K=O, scale_a=s_go, scale_b=s_w, post=1.0 / int(H_size),
+             out_dtype=Go.dtype, a_rows_per_scale=1),
+        dict(a=q_gw, b=x_q_t, M=O, N=I, K=lp, scale_a=s_gw, scale_b=s_x, post=1.0 / n, out_dtype=Go.dtype), status)
     ev[2].record()
-    torch.cuda.synchronize(Go.device)
+    # the prototype synchronises the device; here the call waits for its own stream, which gives the
+    # caller the same guarantee (results complete on return) without stalling copies on other streams
+    torch.cuda.current_stream(Go.device).synchronize()
     if int(status.item()) != 0:
         raise RuntimeError("HLQ_backward: a bounded device-side wait ran out (status %d)" % int(status.item()))
     return gx, gw, [ev[0].elapsed_time(ev[1]) * 1e-3, 0.0, ev[1].elapsed_time(ev[2]) * 1e-3, 0.0]
