@@ -493,6 +493,9 @@ __global__ void __launch_bounds__(kEpiThreads + 64 + ((A4 || B4) ? kUnpackThread
   __syncthreads();
   if (PAIR) cluster_sync_all();  // the partner's barriers are initialised before anything signals them
   tc_fence_after();
+  // Launched as a programmatic dependent of the kernel before it on the stream: the set-up above ran
+  // while that kernel drained; its results (the operands, the scales) are visible once this returns.
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   const uint32_t tmem_base = *tmem_slot;
 
   if (warp == kProducerWarp) {
@@ -965,23 +968,24 @@ int launch_gemm(const void* a, int64_t lda, const void* b, int64_t ldb, const Ge
     attr_set = true;
   }
   constexpr unsigned kThreads = kEpiThreads + 64 + ((A4 || B4) ? kUnpackThreads : 0);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(plan.grid);
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = L::kBytes;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;  // may start while its predecessor drains
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.numAttrs = 1;
   if (PAIR) {
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(plan.grid);
-    cfg.blockDim = dim3(kThreads);
-    cfg.dynamicSmemBytes = L::kBytes;
-    cfg.stream = st;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = 2;
-    attr[0].val.clusterDim.y = 1;
-    attr[0].val.clusterDim.z = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
-    HOT_CUDA(cudaLaunchKernelEx(&cfg, kernel, ma, mb, mo, ma2, mb2, mo2, pp, p2));
-  } else {
-    kernel<<<plan.grid, kThreads, L::kBytes, st>>>(ma, mb, mo, ma2, mb2, mo2, pp, p2);
+    attr[1].id = cudaLaunchAttributeClusterDimension;
+    attr[1].val.clusterDim.x = 2;
+    attr[1].val.clusterDim.y = 1;
+    attr[1].val.clusterDim.z = 1;
+    cfg.numAttrs = 2;
   }
+  cfg.attrs = attr;
+  HOT_CUDA(cudaLaunchKernelEx(&cfg, kernel, ma, mb, mo, ma2, mb2, mo2, pp, p2));
   HOT_CUDA(cudaGetLastError());
   return HOT_OK;
 }

@@ -174,6 +174,10 @@ __global__ void __launch_bounds__(kThreads, sizeof(T) == 2 ? 3 : 1) go_dual_kern
 
   ScalePair sp_x = scale_from_absmax(0.0f, p.qx.qmax), sp_w = scale_from_absmax(0.0f, p.qw.qmax);
   if (PASS == 1) {
+    // launched as a programmatic dependent of the statistics pass: everything above (barriers, the
+    // first tile's load of grad_out, which that pass does not write) ran while it drained; its
+    // abs-maxima are visible once this returns
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     if (!p.x_row) sp_x = scale_from_absmax(__uint_as_float(p.max_x[0]), p.qx.qmax);
     if (!p.w_row) sp_w = scale_from_absmax(__uint_as_float(p.max_w[0]), p.qw.qmax);
     if (blockIdx.x == 0 && tid == 0) {
@@ -307,6 +311,7 @@ __global__ void __launch_bounds__(kThreads, sizeof(T) == 2 ? 3 : 1) go_dual_kern
     __syncthreads();  // staging / column maxima free for the next tile
   }
 
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");  // the next kernel on the stream may begin to launch
   if (PASS == 0) {
     if (!p.x_row) {
       tmax_x = warp_max(tmax_x);
@@ -337,7 +342,22 @@ int launch_pass(const CUtensorMap& tmap, const DualParams& p, int grid, cudaStre
     HOT_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes<T>()));
     attr_set = true;
   }
-  kernel<<<grid, kThreads, smem_bytes<T>(), st>>>(tmap, p);
+  if (PASS == 1) {
+    // may start while the statistics pass (the launch before it on this stream) is still draining
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = smem_bytes<T>();
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    HOT_CUDA(cudaLaunchKernelEx(&cfg, kernel, tmap, p));
+  } else {
+    kernel<<<grid, kThreads, smem_bytes<T>(), st>>>(tmap, p);
+  }
   HOT_CUDA(cudaGetLastError());
   return HOT_OK;
 }
