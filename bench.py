@@ -270,7 +270,7 @@ def run_hot(a):
 
 
 def run_sweep(a):
-    """BASELINE config 2: the fused transform + quantise kernel alone.  Algorithmic bytes per launch:
+    """Benchmark configuration 2 of the target: the fused transform + quantise kernel alone.  Algorithmic bytes per launch:
     M*K*sizeof(in) + M*K*bits/8 + 4 (per tensor) or + 4*M (per token), over the CUDA-event time."""
     from hot_b200 import ops
     device = torch.device("cuda", 0)
@@ -318,7 +318,7 @@ def run_sweep(a):
 
 
 def run_large_mlp(a):
-    """BASELINE config 4: large MLP linears in bf16 at 16384 tokens, activations with heavy-tailed
+    """Benchmark configuration 4 of the target: large MLP linears in bf16 at 16384 tokens, activations with heavy-tailed
     outlier channels (1 % of channels scaled by |Student-t(3)| draws), compressed activation buffer."""
     from hot_b200 import ops
     from hot_b200.hadamard_matmul import lowrank_selection
@@ -465,7 +465,7 @@ def run_per_sample(a):
 
 
 def run_vit_train(a):
-    """BASELINE config 5: synthetic 224x224x3 images N(0,1), 100 random classes, random-init ViT-B/16
+    """Benchmark configuration 5 of the target: synthetic 224x224x3 images N(0,1), 100 random classes, random-init ViT-B/16
     in bf16, cross-entropy, SGD; per GPU `--batch` images (256 -> 50,432 tokens).  One process per
     GPU, gradients all-reduced by DistributedDataParallel over NCCL as in the reference."""
     import torch.distributed as dist
@@ -630,7 +630,7 @@ def kernel_legs(ops, layers, a, dtype, device, pk, status):
 
 
 def config1_leg(ops, device, status):
-    """BASELINE config 1: one ViT-B/16 fc1 backward in fp32, X [6304, 768] N(0,1) with 1 % of the
+    """Benchmark configuration 1 of the target: one ViT-B/16 fc1 backward in fp32, X [6304, 768] N(0,1) with 1 % of the
     channels scaled x20, W kaiming-uniform, grad_out N(0, 1e-3); Hadamard order 16, INT4 g_x with
     stochastic rounding, 8-of-16 low-rank INT8 g_w; beside the fp32 matmul backward (TF32 off)."""
     from hot_b200.hadamard_matmul import lowrank_selection
