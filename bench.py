@@ -51,6 +51,9 @@ def parse():
     p.add_argument("--blocks", type=int, default=12)
     p.add_argument("--dtype", default="bf16", choices=["bf16", "fp32"])
     p.add_argument("--e2e-steps", type=int, default=2)
+    p.add_argument("--gx-storage", default="int4", choices=["int4", "int8"],
+                   help="how the 4-bit g_x codes of grad_out are stored between the quantiser and the GEMM: packed two per "
+                        "byte and expanded in shared memory (default, what the target asks for), or one per byte")
     p.add_argument("--no-cpu-baseline", action="store_true")
     p.add_argument("--no-kernels", action="store_true", help="skip the per-kernel roofline legs")
     p.add_argument("--sweep", action="store_true",
@@ -139,7 +142,7 @@ class ClockSampler:
 # ---------------------------------------------------------------------------------------------
 # the hot arm
 # ---------------------------------------------------------------------------------------------
-def build_layers(ops, tokens, blocks, dtype, device, rank):
+def build_layers(ops, tokens, blocks, dtype, device, rank, gx_storage="int4"):
     """Per block and layer: weight, grad_out, compressed activation, config."""
     from hot_b200.hadamard_matmul import biggest_power2_factor_max16, lowrank_selection
     gw_seed = torch.Generator(device=device).manual_seed(0)            # same weights on every rank
@@ -156,7 +159,7 @@ def build_layers(ops, tokens, blocks, dtype, device, rank):
             x = torch.randn((tokens, i_f), device=device, generator=gd).to(dtype)
             call += 4
             cfg = ops.LinearConfig(order_o=biggest_power2_factor_max16(o_f), order_l=order_l, sel_l=sel,
-                                   q_gx=ops.Quant(4, "int4", "philox", "tensor", 0, call + 1),
+                                   q_gx=ops.Quant(4, gx_storage, "philox", "tensor", 0, call + 1),
                                    q_w=ops.Quant(4, "int4", "philox", "tensor", 0, call + 2),
                                    q_gw=ops.Quant(8, "int8", "philox", "tensor", 0, call + 3),
                                    q_x=ops.Quant(8, "int8", "philox", "tensor", 0, call + 4))
@@ -182,7 +185,7 @@ def run_hot(a):
         dist.init_process_group("nccl", device_id=device)
     dtype = torch.bfloat16 if a.dtype == "bf16" else torch.float32
     pk = peaks()
-    layers = build_layers(ops, a.tokens, a.blocks, dtype, device, rank)
+    layers = build_layers(ops, a.tokens, a.blocks, dtype, device, rank, a.gx_storage)
     status = torch.zeros(1, dtype=torch.int32, device=device)
     # gradient buffers: grad_x is consumed by the layer below (one reusable buffer per width);
     # grad_w lands in one flat bucket per block, the unit of the all-reduce
@@ -249,7 +252,7 @@ def run_hot(a):
            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8/int4 codes, int32 accumulate",
            "data": "synthetic", "gpu_launches": n_layers * KERNELS_PER_LAYER * a.steps,
            "config": {"workload": WORKLOAD, "tokens_per_gpu": a.tokens, "layers": n_layers, "tensor_dtype": a.dtype,
-                      "hadamard_order": 16, "low_rank": "8 of 16 (lowest sequency)", "g_x": "INT4 x INT4, per-tensor, Philox stochastic",
+                      "hadamard_order": 16, "low_rank": "8 of 16 (lowest sequency)", "g_x": "INT4 x INT4, per-tensor, Philox stochastic" + ("" if a.gx_storage == "int4" else "; grad_out codes stored one per byte"),
                       "g_w": "INT8 x INT8, per-tensor, Philox stochastic", "activation_buffer": "compressed in forward (not timed)",
                       "cache": "inputs 2.1 GB per GPU, distinct per layer (> 126 MB L2)",
                       "parallelism": "dp%d, grad_w all-reduce (NCCL) per block" % world if world > 1 else "single GPU"}}
