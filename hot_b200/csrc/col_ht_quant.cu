@@ -304,11 +304,15 @@ __global__ void __launch_bounds__(kThreads) col_ht_quant_kernel(const T* __restr
   const int qmax = (int)q.qmax;
   const int cpr = (p.nb * r) >> 3;  // 8-code chunks per tile row
   const int64_t pos0 = blk0 * r;    // first stored position of this tile within an output row
-  for (int item = threadIdx.x; item < CC * cpr; item += kThreads) {
-    const int cl = item / cpr, ch = item - cl * cpr;
+  // the eight codes of chunk `ch` of tile row `cl` (column c = c0 + cl); zeros past the end of the row
+  auto quantise8 = [&](int cl, int ch, int (&code)[8]) {
     const int c = c0 + cl;
     const int64_t l0 = pos0 + (int64_t)ch * 8;
-    if (c >= p.cols || l0 >= p.out_len) continue;
+    if (l0 >= p.out_len) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) code[i] = 0;
+      return;
+    }
     float v[8];
     const float4 a = *reinterpret_cast<const float4*>(tile + cl * p.pitch + ch * 8);
     const float4 b = *reinterpret_cast<const float4*>(tile + cl * p.pitch + ch * 8 + 4);
@@ -321,9 +325,8 @@ __global__ void __launch_bounds__(kThreads) col_ht_quant_kernel(const T* __restr
     ScalePair sp = sp_t;
     if (p.scale_row) {
       sp = scale_from_absmax(__uint_as_float(absmax[c]), q.qmax);
-      if (blockIdx.y == 0 && ch == 0) scales[c] = sp.s;
+      if (blockIdx.y == 0 && ch == 0 && c < p.cols) scales[c] = sp.s;
     }
-    int code[8];
     if (ROUND == HOT_ROUND_STOCH_PHILOX) {
       // random byte of stored-layout element e: byte e % 16 of Philox block e / 16
       // batched calls index Philox by the position in the padded output row, so that runs stay aligned
@@ -370,12 +373,34 @@ __global__ void __launch_bounds__(kThreads) col_ht_quant_kernel(const T* __restr
 #pragma unroll
       for (int i = 0; i < 8; ++i) code[i] = quantise_one<ROUND>(v[i], sp, u[i], qmax);
     }
-    if (p.store4) {
-      uint32_t w = 0;
+  };
+  if (p.store4) {
+    // packed INT4: a run of 16 codes per item; byte j = code j | code (j + 8) << 4 (nb * r is a multiple of 16)
+    const int rpr = cpr >> 1;  // runs per tile row
+    for (int item = threadIdx.x; item < CC * rpr; item += kThreads) {
+      const int cl = item / rpr, run = item - cl * rpr;
+      const int c = c0 + cl;
+      const int64_t l0 = pos0 + (int64_t)run * 16;
+      if (c >= p.cols || l0 >= p.out_len) continue;
+      int lo[8], hi[8];
+      quantise8(cl, 2 * run, lo);
+      quantise8(cl, 2 * run + 1, hi);
+      uint32_t w0 = 0, w1 = 0;
 #pragma unroll
-      for (int i = 0; i < 8; ++i) w |= (uint32_t)(code[i] & 0xF) << (4 * i);
-      *reinterpret_cast<uint32_t*>(codes + (int64_t)c * p.ld_codes + (l0 >> 1)) = w;
-    } else {
+      for (int i = 0; i < 4; ++i) {
+        w0 |= (uint32_t)((lo[i] & 0xF) | ((hi[i] & 0xF) << 4)) << (8 * i);
+        w1 |= (uint32_t)((lo[i + 4] & 0xF) | ((hi[i + 4] & 0xF) << 4)) << (8 * i);
+      }
+      *reinterpret_cast<uint2*>(codes + (int64_t)c * p.ld_codes + (l0 >> 1)) = make_uint2(w0, w1);
+    }
+  } else {
+    for (int item = threadIdx.x; item < CC * cpr; item += kThreads) {
+      const int cl = item / cpr, ch = item - cl * cpr;
+      const int c = c0 + cl;
+      const int64_t l0 = pos0 + (int64_t)ch * 8;
+      if (c >= p.cols || l0 >= p.out_len) continue;
+      int code[8];
+      quantise8(cl, ch, code);
       uint32_t w0 = 0, w1 = 0;
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
@@ -512,8 +537,11 @@ void col_tile_geometry(int dtype, int order, int r, int* cc, int* nb) {
   const int per = 64 / ((order < 16 ? 16 : order) * cpl);
   const int vec = per >= 4 ? 4 : (per >= 2 ? 2 : 1);
   *cc = 32 * vec * cpl;
-  int b = (128 / r) / 8 * 8;
-  *nb = b < 8 ? 8 : b;
+  // the smaller of the two tile heights the launcher may use (INT8 / packed INT4 output): an upper bound on CTAs
+  int b8 = (128 / r) / 8 * 8, b16 = (128 / r) / 16 * 16;
+  if (b8 < 8) b8 = 8;
+  if (b16 < 16) b16 = 16;
+  *nb = b8 < b16 ? b8 : b16;
 }
 }  // namespace
 }  // namespace hot
@@ -568,8 +596,10 @@ int col_ht_quant_impl(const void* x, int dtype, int64_t rows, int64_t cols, int6
     p.pos[sel[j]] = (signed char)j;
   }
   // blocks per tile: a multiple of 8 (so that nb * r is a multiple of 8 codes) near 128 / r
-  int nb = (128 / r) / 8 * 8;
-  if (nb < 8) nb = 8;
+  // (packed INT4 output: a multiple of 16, so that nb * r is whole runs of 16 codes)
+  const int step = p.store4 ? 16 : 8;
+  int nb = (128 / r) / step * step;
+  if (nb < step) nb = step;
   p.nb = nb;
   p.pitch = ((nb * r + 31) / 32) * 32 + 4;
   const int64_t row_bytes = p.store4 ? (p.out_len + 1) / 2 : p.out_len;

@@ -152,10 +152,9 @@ __device__ __forceinline__ float2 philox_offset_bits2(float2 x, const ScalePair&
 __device__ __forceinline__ uint32_t gather_low_bytes(uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
   return __byte_perm(__byte_perm(a, b, 0x0040u), __byte_perm(c, d, 0x0040u), 0x5410u);
 }
-// eight byte-wide codes (each < 16; lo = codes 0..3, hi = codes 4..7) -> eight nibbles
-__device__ __forceinline__ uint32_t squeeze_nibbles(uint32_t lo, uint32_t hi) {
-  return __byte_perm(lo | (lo >> 4), hi | (hi >> 4), 0x6420u);
-}
+// Packed INT4 layout: a run of 16 codes takes 8 bytes; byte j holds code j in its low nibble and code
+// j + 8 in its high nibble.  lo / hi: four byte-wide codes (each < 16) of the first / second half.
+__device__ __forceinline__ uint32_t pack_nibbles(uint32_t lo, uint32_t hi) { return lo | (hi << 4); }
 // Remove the offset 2^(bits-1) from packed offset codes (a flip of that bit per lane) and
 // sign-extend codes narrower than their lane.  lanes: 0x11111111 (nibbles) or 0x01010101 (bytes).
 __device__ __forceinline__ uint32_t remove_offset(uint32_t w, uint32_t off, uint32_t lanes, uint32_t lane_span) {

@@ -300,16 +300,14 @@ struct SmemLayout {
 // Tensor-memory columns: two accumulator buffers of BN columns, rounded up to a power of two.
 __host__ __device__ constexpr uint32_t tmem_cols(int bn) { return 2 * bn <= 128 ? 128u : (2 * bn <= 256 ? 256u : 512u); }
 
-// A packed byte holds code 2j in its low nibble and code 2j+1 in its high nibble.  Moving a
-// nibble into the HIGH half of a byte gives 16 * code as a signed int8 with no sign-extension
-// arithmetic, so operands unpacked this way are 16x too large and the accumulator is shifted
-// right by 4 bits per packed operand in the epilogue (exact: it is a multiple of 16).
-__device__ __forceinline__ void unpack8_x16(uint32_t w, uint32_t& lo, uint32_t& hi) {
-  const uint32_t e = (w << 4) & 0xF0F0F0F0u;  // codes 0, 2, 4, 6 (x16) in bytes 0..3
-  const uint32_t o = w & 0xF0F0F0F0u;         // codes 1, 3, 5, 7 (x16)
-  lo = __byte_perm(e, o, 0x5140);             // e0 o0 e1 o1
-  hi = __byte_perm(e, o, 0x7362);             // e2 o2 e3 o3
-}
+// Packed INT4: a run of 16 codes is 8 bytes, byte j holding code j in its low nibble and code j + 8 in
+// its high nibble.  Moving a nibble into the HIGH half of a byte gives 16 * code as a signed int8 with
+// no sign-extension arithmetic, so operands unpacked this way are 16x too large and the accumulator
+// is scaled back by 2^-4 per packed operand in the epilogue (exact: it is a multiple of 16).  With this
+// layout four packed bytes turn into codes j..j+3 with one multiply (a shift, on the FMA pipe) and one
+// mask, and into codes j+8..j+11 with one mask: no byte permutes.
+__device__ __forceinline__ uint32_t nib_lo_x16(uint32_t w) { return (w * 16u) & 0xF0F0F0F0u; }
+__device__ __forceinline__ uint32_t nib_hi_x16(uint32_t w) { return w & 0xF0F0F0F0u; }
 
 // Expand a raw stage of `rows` rows x 64 packed bytes into the swizzled int8 stage
 // (row r at r * 128, 16-byte chunk c at chunk position c ^ (r & 7)).  The unpack warps cooperate.
@@ -319,11 +317,9 @@ __device__ __forceinline__ void unpack_stage(const uint8_t* raw, uint8_t* dst, i
   for (int it = tid; it < items; it += nthreads) {
     const int r = it >> 2, qd = it & 3;
     const uint4 w = *reinterpret_cast<const uint4*>(raw + r * 64 + qd * 16);
-    uint4 o0, o1;
-    unpack8_x16(w.x, o0.x, o0.y);
-    unpack8_x16(w.y, o0.z, o0.w);
-    unpack8_x16(w.z, o1.x, o1.y);
-    unpack8_x16(w.w, o1.z, o1.w);
+    // (w.x, w.y) is one run of 16 codes, (w.z, w.w) the next
+    const uint4 o0 = make_uint4(nib_lo_x16(w.x), nib_lo_x16(w.y), nib_hi_x16(w.x), nib_hi_x16(w.y));
+    const uint4 o1 = make_uint4(nib_lo_x16(w.z), nib_lo_x16(w.w), nib_hi_x16(w.z), nib_hi_x16(w.w));
     const int c0 = qd * 2, c1 = qd * 2 + 1;
     *reinterpret_cast<uint4*>(dst + r * 128 + ((c0 ^ (r & 7)) << 4)) = o0;
     *reinterpret_cast<uint4*>(dst + r * 128 + ((c1 ^ (r & 7)) << 4)) = o1;
@@ -924,10 +920,10 @@ int launch_gemm(const void* a, int64_t lda, const void* b, int64_t ldb, const Ge
   using L = SmemLayout<BN, A4, B4, PAIR>;
   CUtensorMap ma, mb;
   int rc;
-  if (A4) rc = make_map(&ma, a, p.M, (p.K + 1) / 2, lda, kBK / 2, kBM, 0);
+  if (A4) rc = make_map(&ma, a, p.M, (p.K + 15) / 16 * 8, lda, kBK / 2, kBM, 0);  // whole runs of 16 codes
   else rc = make_map(&ma, a, p.M, p.K, lda, kBK, kBM, 128);
   if (rc) return rc;
-  if (B4) rc = make_map(&mb, b, p.N, (p.K + 1) / 2, ldb, kBK / 2, L::kBRows, 0);
+  if (B4) rc = make_map(&mb, b, p.N, (p.K + 15) / 16 * 8, ldb, kBK / 2, L::kBRows, 0);
   else rc = make_map(&mb, b, p.N, p.K, ldb, kBK, L::kBRows, 128);
   if (rc) return rc;
   // output as a byte matrix for the bulk tensor stores; otherwise the epilogue stores from registers
@@ -1098,7 +1094,7 @@ extern "C" int hot_gemm_i8_ws(const void* a, int a_storage, int64_t lda, const v
   if (out_dtype != HOT_I32 && (!scale_a || !scale_b)) HOT_FAIL(HOT_ERR_ARG, "hot_gemm_i8: null scale pointer");
   const bool a4 = a_storage == HOT_STORE_INT4, b4 = b_storage == HOT_STORE_INT4;
   if ((a4 || b4) && (K % 2 != 0)) HOT_FAIL(HOT_ERR_ARG, "hot_gemm_i8: packed INT4 operands need an even K");
-  const int64_t abytes = a4 ? K / 2 : K, bbytes = b4 ? K / 2 : K;
+  const int64_t abytes = a4 ? (K + 15) / 16 * 8 : K, bbytes = b4 ? (K + 15) / 16 * 8 : K;  // packed: whole runs of 16 codes
   if (lda % 16 || ldb % 16 || lda < abytes || ldb < bbytes || ((uintptr_t)a) % 16 || ((uintptr_t)b) % 16)
     HOT_FAIL(HOT_ERR_ARG, "hot_gemm_i8: operand base and pitch must be 16-byte aligned and cover K");
   if (ldo < N) HOT_FAIL(HOT_ERR_ARG, "hot_gemm_i8: ldo < N");
@@ -1204,7 +1200,7 @@ int fill_problem(const hot_gemm_problem_t* g, bool allow_packed_a, GemmParams* p
   const bool a4 = g->a_storage == HOT_STORE_INT4;
   if (a4 && !allow_packed_a) HOT_FAIL(HOT_ERR_UNSUPPORTED, "hot_gemm_i8_dual: %s: packed INT4 is taken for the main problem's A only", who);
   if (a4 && g->K % 2 != 0) HOT_FAIL(HOT_ERR_ARG, "hot_gemm_i8_dual: %s: packed INT4 operands need an even K", who);
-  const int64_t abytes = a4 ? g->K / 2 : g->K;
+  const int64_t abytes = a4 ? (g->K + 15) / 16 * 8 : g->K;
   if (g->lda % 16 || g->ldb % 16 || g->lda < abytes || g->ldb < g->K || ((uintptr_t)g->a) % 16 || ((uintptr_t)g->b) % 16)
     HOT_FAIL(HOT_ERR_ARG, "hot_gemm_i8_dual: %s: operand base and pitch must be 16-byte aligned and cover K", who);
   if (g->out_dtype != HOT_F32 && g->out_dtype != HOT_BF16 && g->out_dtype != HOT_I32)

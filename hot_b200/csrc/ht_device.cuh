@@ -114,9 +114,11 @@ __device__ __forceinline__ void quantise_store16(const float2 (&v)[8], const Sca
     wb0 = gather_low_bytes(bb[0], bb[1], bb[2], bb[3]);
     wb1 = gather_low_bytes(bb[4], bb[5], bb[6], bb[7]);
     const uint32_t off = (uint32_t)(q.qmax + 1.0f);
-    if (STORE4) {
-      wa0 = remove_offset(squeeze_nibbles(wa0, wa1), off, 0x11111111u, 0x10u);
-      wb0 = remove_offset(squeeze_nibbles(wb0, wb1), off, 0x11111111u, 0x10u);
+    if (STORE4) {  // A_i is code i, B_i is code i + 8: byte i = A_i | B_i << 4
+      const uint32_t p0 = remove_offset(pack_nibbles(wa0, wb0), off, 0x11111111u, 0x10u);
+      const uint32_t p1 = remove_offset(pack_nibbles(wa1, wb1), off, 0x11111111u, 0x10u);
+      wa0 = p0;
+      wb0 = p1;
     } else {
       wa0 = remove_offset(wa0, off, 0x01010101u, 0x100u);
       wa1 = remove_offset(wa1, off, 0x01010101u, 0x100u);
@@ -134,9 +136,10 @@ __device__ __forceinline__ void quantise_store16(const float2 (&v)[8], const Sca
     for (int i = 0; i < 8; ++i) {
       const int ca = quantise_one<ROUND>(v[i].x, sp, ROUND == HOT_ROUND_STOCH_NOISE ? ua[i] : 0.0f, qmax);
       const int cb = quantise_one<ROUND>(v[i].y, sp, ROUND == HOT_ROUND_STOCH_NOISE ? ub[i] : 0.0f, qmax);
-      if (STORE4) {
-        wa0 |= (uint32_t)(ca & 0xF) << (4 * i);
-        wb0 |= (uint32_t)(cb & 0xF) << (4 * i);
+      if (STORE4) {  // byte i = code i | code (i + 8) << 4; bytes 0..3 in wa0, 4..7 in wb0
+        const uint32_t byte = (uint32_t)(ca & 0xF) | ((uint32_t)(cb & 0xF) << 4);
+        if (i < 4) wa0 |= byte << (8 * i);
+        else wb0 |= byte << (8 * (i - 4));
       } else {
         if (i < 4) { wa0 |= (uint32_t)(ca & 0xFF) << (8 * i); wb0 |= (uint32_t)(cb & 0xFF) << (8 * i); }
         else { wa1 |= (uint32_t)(ca & 0xFF) << (8 * (i - 4)); wb1 |= (uint32_t)(cb & 0xFF) << (8 * (i - 4)); }

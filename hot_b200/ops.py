@@ -20,7 +20,7 @@ _ROUNDING = {"nearest": C.ROUND_NEAREST, "philox": C.ROUND_STOCH_PHILOX, "noise"
 class Quant:
     """How one operand is quantised (mirrors ``hot_quant_t``)."""
     bits: int = 8
-    storage: str = "int8"            # "int8" | "int4" (two codes per byte, low nibble = even index)
+    storage: str = "int8"            # "int8" | "int4" (two codes per byte, in runs of 16: byte j = codes j and j + 8)
     rounding: str = "philox"         # "nearest" | "philox" | "noise"
     scale: str = "tensor"            # "tensor" | "row" | "sawb" (column kernel only, nearest rounding)
     seed: int = 0

@@ -37,7 +37,10 @@ enum hot_rounding { HOT_ROUND_NEAREST = 0, HOT_ROUND_STOCH_PHILOX = 1, HOT_ROUND
  * rounding): one scale from clip = 12.1 * sqrt(mean(y^2)) - 12.2 * mean(|y|), values clamped to
  * +-clip first (sawb_quantizer, utils/quant_matmul.py:40-55). */
 enum hot_scale_mode { HOT_SCALE_TENSOR = 0, HOT_SCALE_ROW = 1, HOT_SCALE_SAWB = 2 };
-enum hot_storage { HOT_STORE_INT8 = 0, HOT_STORE_INT4 = 1 }; /* INT4: two codes per byte, low nibble = even index */
+/* INT4: two codes per byte.  The packed dim is cut into runs of 16 codes (8 bytes; a last partial run is
+ * zero-filled): byte j of a run holds code j in its low nibble and code j + 8 in its high nibble, so each
+ * half of a run expands to consecutive int8 codes with one shift or mask. */
+enum hot_storage { HOT_STORE_INT8 = 0, HOT_STORE_INT4 = 1 };
 enum hot_layout { HOT_LAYOUT_NATURAL = 0, HOT_LAYOUT_TRANSPOSED = 1 };
 
 /* How one operand is quantised.  Codes lie in [-(2^(bits-1)-1), 2^(bits-1)-1]. */
@@ -63,7 +66,7 @@ int hot_abi_version(void);
  *   x      [rows, cols] row-major, pitch ldx elements, dtype HOT_F32 | HOT_BF16
  *   order  Hadamard block order: 1, 2, 4, ..., 64; cols % max(order, 16) == 0
  *   codes  HOT_STORE_INT8: [rows, cols] int8, pitch ld_codes bytes
- *          HOT_STORE_INT4: [rows, cols/2] bytes, pitch ld_codes bytes
+ *          HOT_STORE_INT4: [rows, cols/2] bytes (cols is a multiple of 16: whole runs), pitch ld_codes bytes
  *   scales [1] (HOT_SCALE_TENSOR) or [rows] (HOT_SCALE_ROW): s = absmax / (2^(bits-1)-1)
  *   absmax_ws  one 32-bit word of scratch, used in HOT_SCALE_TENSOR mode only
  * noise / Philox element index: row * cols + col.

@@ -272,20 +272,28 @@ def philox_bytes(seed: int, offset: int, shape) -> np.ndarray:
 # int4 packing (cuda_measure/HLQ_backward_kernel.cu:140: low nibble = even element)
 # ----------------------------------------------------------------------------
 def pack_int4(codes: np.ndarray) -> np.ndarray:
+    """The kernels' packed INT4 layout: the last dim is cut into runs of 16 codes (zero-padded), and
+    byte j (0..7) of a run holds code j in its low nibble and code j + 8 in its high nibble, so that
+    both halves of a run expand to consecutive int8 codes with one shift / mask each."""
     c = np.asarray(codes).astype(np.int32)
-    lo = c[..., 0::2] & 0xF
-    hi = c[..., 1::2] & 0xF
-    return (lo | (hi << 4)).astype(np.uint8)
+    n = c.shape[-1]
+    pad = (-n) % 16
+    if pad:
+        c = np.concatenate([c, np.zeros(c.shape[:-1] + (pad,), np.int32)], axis=-1)
+    g = c.reshape(c.shape[:-1] + (-1, 2, 8)) & 0xF                     # [..., run, half, 8]
+    return (g[..., 0, :] | (g[..., 1, :] << 4)).astype(np.uint8).reshape(c.shape[:-1] + (-1,))
 
 
 def unpack_int4(packed: np.ndarray) -> np.ndarray:
+    """Inverse of ``pack_int4`` (the byte count of the last dim must be a multiple of 8): two codes
+    per byte, sign-extended; callers slice off the zero padding of the last run."""
     p = np.asarray(packed).astype(np.int32)
-    lo = ((p & 0xF) ^ 8) - 8
-    hi = (((p >> 4) & 0xF) ^ 8) - 8
-    out = np.empty(p.shape[:-1] + (p.shape[-1] * 2,), np.int32)
-    out[..., 0::2] = lo
-    out[..., 1::2] = hi
-    return out
+    if p.shape[-1] % 8:
+        p = np.concatenate([p, np.zeros(p.shape[:-1] + ((-p.shape[-1]) % 8,), np.int32)], axis=-1)
+    g = p.reshape(p.shape[:-1] + (-1, 8))
+    lo = ((g & 0xF) ^ 8) - 8
+    hi = (((g >> 4) & 0xF) ^ 8) - 8
+    return np.concatenate([lo, hi], axis=-1).reshape(p.shape[:-1] + (-1,))
 
 
 # ----------------------------------------------------------------------------

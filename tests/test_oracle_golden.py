@@ -149,7 +149,8 @@ def test_int4_pack_roundtrip():
     c = rng.integers(-7, 8, size=(5, 32))
     p = oc.pack_int4(c)
     assert p.shape == (5, 16) and p.dtype == np.uint8
-    assert (p[0, 0] & 0xF) == (c[0, 0] & 0xF) and (p[0, 0] >> 4) == (c[0, 1] & 0xF)
+    assert (p[0, 0] & 0xF) == (c[0, 0] & 0xF) and (p[0, 0] >> 4) == (c[0, 8] & 0xF)     # byte j: codes j and j + 8 of a run
+    assert (p[0, 9] & 0xF) == (c[0, 17] & 0xF) and (p[0, 9] >> 4) == (c[0, 25] & 0xF)
     assert np.array_equal(oc.unpack_int4(p), c)
 
 
