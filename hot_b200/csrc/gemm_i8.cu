@@ -1260,21 +1260,36 @@ extern "C" int hot_gemm_i8_dual(const hot_gemm_problem_t* main_problem, const ho
   if (sms <= 0) return HOT_ERR_CUDA;
   const bool a4 = main_problem->a_storage == HOT_STORE_INT4;
   // One launch pays when the rider's few long tiles fit beside the main problem's last, partly empty
-  // wave; otherwise (or with HOT_GEMM_DUAL=0) the two problems run one after the other.
-  const int64_t t0 = tiles_for(p0.M, p0.N, 256), t1 = tiles_for(p1.M, p1.N, 256);
+  // wave; otherwise (or with HOT_GEMM_DUAL=0) the two problems run one after the other.  The tile
+  // width is the one whose busiest worker, replayed on the host, has the least to do.
   const Plan s0 = make_plan(p0.M, p0.N, p0.num_kb, sms, 0, !a4, a4), s1 = make_plan(p1.M, p1.N, p1.num_kb, sms, 0, true, false);
   const char* env = getenv("HOT_GEMM_DUAL");
-  bool dual = t1 <= sms && t0 >= sms && t1 >= 1 && !(env && env[0] == '0');
-  if (dual && !(env && env[0] == '1')) {
-    const double together = (double)dual_max_load(t0, p0.num_kb, t1, p1.num_kb, sms) * (256 + 400.0);
-    // a second launch costs about 3 us of ramp-down and ramp-up, some 4000 units of this model
-    dual = together < s0.cost + s1.cost + 4000.0;
+  int dual_bn = 0;
+  double together = 0.0;
+  for (int bn : {256, 192}) {
+    const int64_t t0 = tiles_for(p0.M, p0.N, bn), t1 = tiles_for(p1.M, p1.N, bn);
+    if (t1 > sms || t0 < sms || t1 < 1) continue;
+    const double c = (double)dual_max_load(t0, p0.num_kb, t1, p1.num_kb, sms) * (bn + 400.0);
+    if (!dual_bn || c < together) {
+      dual_bn = bn;
+      together = c;
+    }
   }
+  bool dual = dual_bn != 0 && !(env && env[0] == '0');
+  // a second launch costs about 3 us of ramp-down and ramp-up, some 4000 units of this model
+  if (dual && !(env && env[0] == '1')) dual = together < s0.cost + s1.cost + 4000.0;
   if (dual) {
     Rider r{rider_problem->a, rider_problem->lda, rider_problem->b, rider_problem->ldb, p1};
-    const Plan plan{256, false, (unsigned)sms};
-    if (a4) return launch_gemm<256, true, false>(main_problem->a, main_problem->lda, main_problem->b, main_problem->ldb, p0, plan, st, &r);
-    return launch_gemm<256, false, false>(main_problem->a, main_problem->lda, main_problem->b, main_problem->ldb, p0, plan, st, &r);
+    const Plan plan{dual_bn, false, (unsigned)sms};
+    const void* a = main_problem->a;
+    const void* b = main_problem->b;
+    const int64_t lda = main_problem->lda, ldb = main_problem->ldb;
+    if (dual_bn == 256) {
+      if (a4) return launch_gemm<256, true, false>(a, lda, b, ldb, p0, plan, st, &r);
+      return launch_gemm<256, false, false>(a, lda, b, ldb, p0, plan, st, &r);
+    }
+    if (a4) return launch_gemm<192, true, false>(a, lda, b, ldb, p0, plan, st, &r);
+    return launch_gemm<192, false, false>(a, lda, b, ldb, p0, plan, st, &r);
   }
   int rc = a4 ? launch_bn<true, false>(main_problem->a, main_problem->lda, main_problem->b, main_problem->ldb, p0, s0, st)
               : launch_bn<false, false>(main_problem->a, main_problem->lda, main_problem->b, main_problem->ldb, p0, s0, st);
