@@ -281,16 +281,15 @@ struct SmemLayout {
   static constexpr int kBRows = PAIR ? BN / 2 : BN;  // rows of B this CTA holds
   static constexpr int kA = kBM * kBK;       // int8 stage of A
   static constexpr int kB = kBRows * kBK;    // int8 stage of B
-  static constexpr int kRawA = A4 ? kBM * kBK / 2 : 0;
+  // a packed operand lands in the upper half of its own int8 stage and is expanded in place
+  static constexpr int kRawA = A4 ? kBM * kBK / 2 : 0;       // bytes of packed A per stage
   static constexpr int kRawB = B4 ? kBRows * kBK / 2 : 0;
-  static constexpr int kStage = kA + kB + kRawA + kRawB;
+  static constexpr int kStage = kA + kB;
   static constexpr int kStagesFit = (kSmemMax - 1536 - kStoreStage) / kStage;
   static constexpr int kStages = kStagesFit > 8 ? 8 : kStagesFit;
   static constexpr int kOffA = 0;
   static constexpr int kOffB = kOffA + kStages * kA;
-  static constexpr int kOffRawA = kOffB + kStages * kB;
-  static constexpr int kOffRawB = kOffRawA + kStages * kRawA;
-  static constexpr int kOffStore = kOffRawB + kStages * kRawB;  // = bytes of the operand ring; 1024-aligned
+  static constexpr int kOffStore = kOffB + kStages * kB;  // = bytes of the operand ring; 1024-aligned
   static constexpr int kOffBar = kOffStore + kStoreStage;
   static constexpr int kBytes = kOffBar + 512 + 1024;  // barriers + slack to align the base to 1024
   static_assert(kOffStore % 1024 == 0 && kBytes <= kSmemMax, "shared-memory plan");
@@ -309,20 +308,29 @@ __host__ __device__ constexpr uint32_t tmem_cols(int bn) { return 2 * bn <= 128 
 __device__ __forceinline__ uint32_t nib_lo_x16(uint32_t w) { return (w * 16u) & 0xF0F0F0F0u; }
 __device__ __forceinline__ uint32_t nib_hi_x16(uint32_t w) { return w & 0xF0F0F0F0u; }
 
-// Expand a raw stage of `rows` rows x 64 packed bytes into the swizzled int8 stage
-// (row r at r * 128, 16-byte chunk c at chunk position c ^ (r & 7)).  The unpack warps cooperate.
-__device__ __forceinline__ void unpack_stage(const uint8_t* raw, uint8_t* dst, int rows, int tid, int nthreads) {
-  const int items = rows * 4;  // 16 packed bytes (32 codes = two output chunks) per item
-#pragma unroll 2
-  for (int it = tid; it < items; it += nthreads) {
+// Expand a stage in place: its upper half holds ROWS rows x 64 packed bytes, as TMA delivered them; the
+// whole stage becomes ROWS rows x 128 int8 codes in the 128-byte-swizzled layout (row r at r * 128,
+// 16-byte chunk c at chunk position c ^ (r & 7)).  All unpack threads read their share into registers,
+// meet at a barrier of their own (the output overwrites the packed bytes), then write.
+template <int ROWS>
+__device__ __forceinline__ void unpack_stage(uint8_t* stage, int tid) {
+  constexpr int kItems = ROWS * 4 / kUnpackThreads;  // 16 packed bytes (32 codes = two output chunks) per item
+  static_assert(ROWS * 4 % kUnpackThreads == 0, "rows per stage must be a multiple of 64");
+  const uint8_t* raw = stage + ROWS * 64;
+  uint4 w[kItems];
+#pragma unroll
+  for (int k = 0; k < kItems; ++k) w[k] = *reinterpret_cast<const uint4*>(raw + (tid + k * kUnpackThreads) * 16);
+  asm volatile("bar.sync 2, %0;" ::"n"(kUnpackThreads) : "memory");
+#pragma unroll
+  for (int k = 0; k < kItems; ++k) {
+    const int it = tid + k * kUnpackThreads;
     const int r = it >> 2, qd = it & 3;
-    const uint4 w = *reinterpret_cast<const uint4*>(raw + r * 64 + qd * 16);
     // (w.x, w.y) is one run of 16 codes, (w.z, w.w) the next
-    const uint4 o0 = make_uint4(nib_lo_x16(w.x), nib_lo_x16(w.y), nib_hi_x16(w.x), nib_hi_x16(w.y));
-    const uint4 o1 = make_uint4(nib_lo_x16(w.z), nib_lo_x16(w.w), nib_hi_x16(w.z), nib_hi_x16(w.w));
+    const uint4 o0 = make_uint4(nib_lo_x16(w[k].x), nib_lo_x16(w[k].y), nib_hi_x16(w[k].x), nib_hi_x16(w[k].y));
+    const uint4 o1 = make_uint4(nib_lo_x16(w[k].z), nib_lo_x16(w[k].w), nib_hi_x16(w[k].z), nib_hi_x16(w[k].w));
     const int c0 = qd * 2, c1 = qd * 2 + 1;
-    *reinterpret_cast<uint4*>(dst + r * 128 + ((c0 ^ (r & 7)) << 4)) = o0;
-    *reinterpret_cast<uint4*>(dst + r * 128 + ((c1 ^ (r & 7)) << 4)) = o1;
+    *reinterpret_cast<uint4*>(stage + r * 128 + ((c0 ^ (r & 7)) << 4)) = o0;
+    *reinterpret_cast<uint4*>(stage + r * 128 + ((c1 ^ (r & 7)) << 4)) = o1;
   }
 }
 
@@ -426,8 +434,6 @@ __global__ void __launch_bounds__(kEpiThreads + 64 + ((A4 || B4) ? kUnpackThread
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   uint8_t* sA = smem + L::kOffA;
   uint8_t* sB = smem + L::kOffB;
-  uint8_t* rawA = smem + L::kOffRawA;
-  uint8_t* rawB = smem + L::kOffRawB;
   uint64_t* full = reinterpret_cast<uint64_t*>(smem + L::kOffBar);  // TMA landed
   uint64_t* empty = full + STAGES;                                   // MMAs of the stage retired
   uint64_t* ready = empty + STAGES;                                  // unpacked (INT4 operands only)
@@ -519,7 +525,7 @@ __global__ void __launch_bounds__(kEpiThreads + 64 + ((A4 || B4) ? kUnpackThread
             if (rank == 0) mbar_expect_tx(&full[s], 2u * ((A4 ? 0u : (uint32_t)L::kA) + (uint32_t)L::kB));
             if (A4) {
               mbar_expect_tx(&full_a[s], L::kRawA);
-              tma_load_2d(rawA + s * L::kRawA, &tma_a, &full_a[s], kb * (kBK / 2), m0);
+              tma_load_2d(sA + s * L::kA + L::kRawA, &tma_a, &full_a[s], kb * (kBK / 2), m0);
             } else {
               tma_load_2d_pair(sA + s * L::kA, &tma_a, full0 + 8u * s, kb * kBK, m0);
             }
@@ -527,9 +533,9 @@ __global__ void __launch_bounds__(kEpiThreads + 64 + ((A4 || B4) ? kUnpackThread
             continue;
           }
           mbar_expect_tx(&full[s], kTx);
-          if (A4) tma_load_2d(rawA + s * L::kRawA, &tma_a, &full[s], kb * (kBK / 2), m0);
+          if (A4) tma_load_2d(sA + s * L::kA + L::kRawA, &tma_a, &full[s], kb * (kBK / 2), m0);
           else tma_load_2d(sA + s * L::kA, &tma_a, &full[s], kb * kBK, m0);
-          if (B4) tma_load_2d(rawB + s * L::kRawB, &tma_b, &full[s], kb * (kBK / 2), n0);
+          if (B4) tma_load_2d(sB + s * L::kB + L::kRawB, &tma_b, &full[s], kb * (kBK / 2), n0);
           else tma_load_2d(sB + s * L::kB, &tma_b, &full[s], kb * kBK, n0);
         }
       }
@@ -865,8 +871,12 @@ __global__ void __launch_bounds__(kEpiThreads + 64 + ((A4 || B4) ? kUnpackThread
       for (int kb = seg.kb0; kb < seg.kb1; ++kb, s = (s + 1 == STAGES ? 0 : s + 1), ph ^= (s == 0 ? 1u : 0u)) {
         ok = mbar_wait(PAIR ? &full_a[s] : &full[s], ph, abort_flag);
         if (!ok) break;
-        if (A4 && !seg.prob) unpack_stage(rawA + s * L::kRawA, sA + s * L::kA, kBM, utid, kUnpackThreads);
-        if (B4 && !seg.prob) unpack_stage(rawB + s * L::kRawB, sB + s * L::kB, BN, utid, kUnpackThreads);
+        if constexpr (A4) {
+          if (!seg.prob) unpack_stage<kBM>(sA + s * L::kA, utid);
+        }
+        if constexpr (B4) {
+          if (!seg.prob) unpack_stage<L::kBRows>(sB + s * L::kB, utid);
+        }
         fence_proxy_async_smem();  // generic-proxy writes -> visible to the tensor core (async proxy)
         if (PAIR) {
           __syncwarp();
