@@ -140,8 +140,15 @@ __device__ __forceinline__ uint4 quantise16_int8(const float (&y)[16], const Sca
 }
 
 // PASS 0: statistics.  PASS 1: quantise (RX / RW: rounding of the g_x / g_w side).
-template <typename T, int PASS, int RX, int RW>
+// FAST: the configuration of the training path (channel order 16, one scale per tensor on both
+// sides, g_x codes packed INT4) with those four choices folded at compile time; otherwise they
+// are read from the parameters.
+template <typename T, int PASS, int RX, int RW, bool FAST>
 __global__ void __launch_bounds__(kThreads, sizeof(T) == 2 ? 3 : 1) go_dual_kernel(const __grid_constant__ CUtensorMap tmap, DualParams p) {
+  const int n_o = FAST ? 16 : p.n_o;
+  const bool x_row = FAST ? false : p.x_row != 0;
+  const bool w_row = FAST ? false : p.w_row != 0;
+  const bool x_store4 = FAST ? true : p.x_store4 != 0;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~(uintptr_t)127);
   uint8_t* tile[2] = {smem, smem + Tile<T>::kBytes};
@@ -178,11 +185,11 @@ __global__ void __launch_bounds__(kThreads, sizeof(T) == 2 ? 3 : 1) go_dual_kern
     // first tile's load of grad_out, which that pass does not write) ran while it drained; its
     // abs-maxima are visible once this returns
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    if (!p.x_row) sp_x = scale_from_absmax(__uint_as_float(p.max_x[0]), p.qx.qmax);
-    if (!p.w_row) sp_w = scale_from_absmax(__uint_as_float(p.max_w[0]), p.qw.qmax);
+    if (!x_row) sp_x = scale_from_absmax(__uint_as_float(p.max_x[0]), p.qx.qmax);
+    if (!w_row) sp_w = scale_from_absmax(__uint_as_float(p.max_w[0]), p.qw.qmax);
     if (blockIdx.x == 0 && tid == 0) {
-      if (!p.x_row) p.s_x[0] = sp_x.s;
-      if (!p.w_row) p.s_w[0] = sp_w.s;
+      if (!x_row) p.s_x[0] = sp_x.s;
+      if (!w_row) p.s_w[0] = sp_w.s;
     }
   }
   float tmax_x = 0.0f, tmax_w = 0.0f;  // per-tensor maxima of this thread (PASS 0)
@@ -200,7 +207,7 @@ __global__ void __launch_bounds__(kThreads, sizeof(T) == 2 ? 3 : 1) go_dual_kern
     const int64_t tok0 = (int64_t)tt * kTT;
     const int ch0 = tc * kTC;
 
-    if (PASS == 0 && p.w_row) {
+    if (PASS == 0 && w_row) {
       if (tid < kTC) s_colmax[tid] = 0u;
       __syncthreads();
     }
@@ -219,10 +226,10 @@ __global__ void __launch_bounds__(kThreads, sizeof(T) == 2 ? 3 : 1) go_dual_kern
         const int item = tid + (half * 2 + u) * kThreads;
         const int64_t tok = tok0 + (item >> 2);
         const int ch = ch0 + (item & 3) * 16;
-        butterfly16(v[u], p.n_o, lane);
+        butterfly16(v[u], n_o, lane);
         if (PASS == 0) {
           float m = absmax16(v[u]);
-          if (p.x_row) {
+          if (x_row) {
             m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, 1));
             m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, 2));
             if ((lane & 3) == 0 && tok < p.L) atomic_absmax(p.max_x + tok, m);
@@ -231,13 +238,13 @@ __global__ void __launch_bounds__(kThreads, sizeof(T) == 2 ? 3 : 1) go_dual_kern
           }
         } else if (tok < p.L) {
           ScalePair sp = sp_x;
-          if (p.x_row) {
+          if (x_row) {
             sp = scale_from_absmax(__uint_as_float(p.max_x[tok]), p.qx.qmax);
             if (tc == 0 && (item & 3) == 0) p.s_x[tok] = sp.s;
           }
           const uint64_t e0 = (uint64_t)tok * (uint64_t)p.O + (uint64_t)ch;
-          uint8_t* dst = p.q_go + tok * p.ld_qgo + (p.x_store4 ? (ch >> 1) : ch);
-          if (p.x_store4) quantise_store16<RX, 1>(v[u], sp, p.qx, e0, dst);
+          uint8_t* dst = p.q_go + tok * p.ld_qgo + (x_store4 ? (ch >> 1) : ch);
+          if (x_store4) quantise_store16<RX, 1>(v[u], sp, p.qx, e0, dst);
           else quantise_store16<RX, 0>(v[u], sp, p.qx, e0, dst);
         }
       }
@@ -270,7 +277,7 @@ __global__ void __launch_bounds__(kThreads, sizeof(T) == 2 ? 3 : 1) go_dual_kern
       const int64_t blk_pair = tok0 / 32 + bp;           // global index of this pair of token blocks
       const bool pair_ok = tok0 + bp * 32 < p.L;          // tokens are a multiple of 32: all or nothing
       if (PASS == 0) {
-        if (p.w_row) {
+        if (w_row) {
           atomicMax(&s_colmax[c_loc], __float_as_uint(cmax0));
           atomicMax(&s_colmax[c_loc + 1], __float_as_uint(cmax1));
         } else {
@@ -282,7 +289,7 @@ __global__ void __launch_bounds__(kThreads, sizeof(T) == 2 ? 3 : 1) go_dual_kern
         for (int cc = 0; cc < 2; ++cc) {
           const int ch = ch0 + c_loc + cc;
           ScalePair sp = sp_w;
-          if (p.w_row) {
+          if (w_row) {
             sp = scale_from_absmax(__uint_as_float(p.max_w[ch]), p.qw.qmax);
             if (tt == 0 && bp == 0) p.s_w[ch] = sp.s;
           }
@@ -294,7 +301,7 @@ __global__ void __launch_bounds__(kThreads, sizeof(T) == 2 ? 3 : 1) go_dual_kern
     }
     __syncthreads();  // tile consumed; staging complete
     if (PASS == 0) {
-      if (p.w_row && tid < kTC) atomicMax(p.max_w + ch0 + tid, s_colmax[tid]);
+      if (w_row && tid < kTC) atomicMax(p.max_w + ch0 + tid, s_colmax[tid]);
     } else {
       // transposed g_w codes of this tile: kTC rows x 128 bytes, written in 16-byte pieces
       const int64_t pos0 = tok0 / 2;                       // first stored position of the tile in a row
@@ -313,11 +320,11 @@ __global__ void __launch_bounds__(kThreads, sizeof(T) == 2 ? 3 : 1) go_dual_kern
 
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");  // the next kernel on the stream may begin to launch
   if (PASS == 0) {
-    if (!p.x_row) {
+    if (!x_row) {
       tmax_x = warp_max(tmax_x);
       if (lane == 0) atomic_absmax(p.max_x, tmax_x);
     }
-    if (!p.w_row) {
+    if (!w_row) {
       tmax_w = warp_max(tmax_w);
       if (lane == 0) atomic_absmax(p.max_w, tmax_w);
     }
@@ -334,9 +341,9 @@ __global__ void __launch_bounds__(kThreads, sizeof(T) == 2 ? 3 : 1) go_dual_kern
 template <typename T>
 constexpr int smem_bytes() { return 2 * Tile<T>::kBytes + kTC * kStagePitch + 64 + 128; }
 
-template <typename T, int PASS, int RX, int RW>
-int launch_pass(const CUtensorMap& tmap, const DualParams& p, int grid, cudaStream_t st) {
-  auto kernel = go_dual_kernel<T, PASS, RX, RW>;
+template <typename T, int PASS, int RX, int RW, bool FAST>
+int launch_pass_as(const CUtensorMap& tmap, const DualParams& p, int grid, cudaStream_t st) {
+  auto kernel = go_dual_kernel<T, PASS, RX, RW, FAST>;
   static bool attr_set = false;
   if (!attr_set) {
     HOT_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes<T>()));
@@ -360,6 +367,12 @@ int launch_pass(const CUtensorMap& tmap, const DualParams& p, int grid, cudaStre
   }
   HOT_CUDA(cudaGetLastError());
   return HOT_OK;
+}
+
+template <typename T, int PASS, int RX, int RW>
+int launch_pass(const CUtensorMap& tmap, const DualParams& p, int grid, cudaStream_t st) {
+  if (p.n_o == 16 && !p.x_row && !p.w_row && p.x_store4) return launch_pass_as<T, PASS, RX, RW, true>(tmap, p, grid, st);
+  return launch_pass_as<T, PASS, RX, RW, false>(tmap, p, grid, st);
 }
 
 template <typename T>
