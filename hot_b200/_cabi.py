@@ -58,8 +58,8 @@ EXPORTS = {
                                                 ctypes.POINTER(c_i32), ctypes.c_int, ctypes.POINTER(HotQuant), ctypes.c_int,
                                                 c_vp, c_i64, c_i64, c_vp, c_vp, c_vp]),
     "hot_gemm_i8_dual": (ctypes.c_int, [ctypes.POINTER(HotGemmProblem), ctypes.POINTER(HotGemmProblem), c_vp, c_vp]),
-    "hot_gemm_i8_grouped": (ctypes.c_int, [c_vp, c_i64, c_vp, c_i64, c_i64, c_i64, c_i64, c_i64, c_vp, c_vp, ctypes.c_float,
-                                           c_vp, ctypes.c_int, c_i64, c_vp, c_vp]),
+    "hot_gemm_i8_grouped": (ctypes.c_int, [c_vp, c_i64, c_vp, c_i64, c_i64, c_i64, c_i64, c_i64, c_vp, ctypes.c_int, c_vp,
+                                           ctypes.c_float, c_vp, ctypes.c_int, c_i64, c_vp, c_vp]),
     "hot_hla_project": (ctypes.c_int, [c_vp, ctypes.c_int, c_i64, c_i64, c_i64, ctypes.c_int, ctypes.POINTER(c_i32), ctypes.c_int,
                                        c_vp, c_i64, c_vp]),
     "hot_hla_expand": (ctypes.c_int, [c_vp, c_i64, c_i64, c_i64, ctypes.c_int, ctypes.POINTER(c_i32), ctypes.c_int,

@@ -118,7 +118,9 @@ __global__ void __launch_bounds__(kThreads) col_ht_absmax_kernel(const T* __rest
   constexpr int CC = 32 * VEC * CPL;
   __shared__ uint32_t s_max[CC];
   x += (int64_t)blockIdx.z * p.rows * p.ldx;
-  absmax += blockIdx.z;  // batched calls take one abs-max word per sample
+  // SAWB: two doubles per CTA, the CTAs of sample z at (z * gridDim.y + y) * gridDim.x + x
+  double* sawb_part = reinterpret_cast<double*>(absmax) + 2 * (((size_t)blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x);
+  absmax += (size_t)blockIdx.z * (p.scale_row ? (size_t)p.cols : 1);  // batched: one abs-max word (or one row of them) per sample
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int c0 = blockIdx.x * CC;
   const int64_t nblk = p.rows / N;
@@ -142,14 +144,14 @@ __global__ void __launch_bounds__(kThreads) col_ht_absmax_kernel(const T* __rest
 #pragma unroll
           for (int i = 0; i < VEC * CPL; ++i) cm[i] = fmaxf(cm[i], fabsf(v[i][g * N + k]));
           if (p.sawb) {
-            float sq = 0.0f, ab = 0.0f;  // columns and blocks beyond the matrix were loaded as zeros
+            // in double throughout (the squares are exact there), so that the two means round to
+            // float once, as a float64 mean does; columns and blocks beyond the matrix were loaded as zeros
 #pragma unroll
             for (int i = 0; i < VEC * CPL; ++i) {
-              sq = fmaf(v[i][g * N + k], v[i][g * N + k], sq);
-              ab += fabsf(v[i][g * N + k]);
+              const double d = (double)v[i][g * N + k];
+              sum_sq = fma(d, d, sum_sq);
+              sum_abs += fabs(d);
             }
-            sum_sq += (double)sq;
-            sum_abs += (double)ab;
           }
         }
       }
@@ -175,9 +177,8 @@ __global__ void __launch_bounds__(kThreads) col_ht_absmax_kernel(const T* __rest
         a += s_sum[0][w];
         b += s_sum[1][w];
       }
-      double* part = reinterpret_cast<double*>(absmax) + 2 * ((size_t)blockIdx.y * gridDim.x + blockIdx.x);
-      part[0] = a;
-      part[1] = b;
+      sawb_part[0] = a;
+      sawb_part[1] = b;
     }
     return;
   }
@@ -211,8 +212,9 @@ __global__ void __launch_bounds__(kThreads) col_ht_quant_kernel(const T* __restr
   extern __shared__ __align__(16) float tile[];  // [CC][pitch]
   x += (int64_t)blockIdx.z * p.rows * p.ldx;
   codes += (int64_t)blockIdx.z * p.sample_pitch;
-  absmax += blockIdx.z;
-  scales += blockIdx.z;
+  const double* sawb_parts = reinterpret_cast<const double*>(absmax) + 2 * ((size_t)blockIdx.z * gridDim.y * gridDim.x);
+  absmax += (size_t)blockIdx.z * (p.scale_row ? (size_t)p.cols : 1);
+  scales += (size_t)blockIdx.z * (p.scale_row ? (size_t)p.cols : 1);
   // the noise / Philox element index runs on from sample to sample
   const uint64_t e_base = (uint64_t)blockIdx.z * (uint64_t)p.out_len * (uint64_t)p.cols;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -266,10 +268,10 @@ __global__ void __launch_bounds__(kThreads) col_ht_quant_kernel(const T* __restr
 
   float clip = 0.0f;  // SAWB clamp bound
   if (p.sawb) {
-    // clip = 12.1 * sqrt(mean(y^2)) - 12.2 * mean(|y|) over the whole transformed tensor
+    // clip = 12.1 * sqrt(mean(y^2)) - 12.2 * mean(|y|) over the whole transformed tensor (of this sample)
     __shared__ double s_tot[2][kWarps];
     __shared__ float s_clip;
-    const double* part = reinterpret_cast<const double*>(absmax);
+    const double* part = sawb_parts;
     const int nparts = (int)(gridDim.x * gridDim.y);
     double a = 0.0, b = 0.0;
     for (int i = threadIdx.x; i < nparts; i += kThreads) {
@@ -493,7 +495,7 @@ int launch_n(const T* x, const ColParams& p, const hot_quant_t& hq, uint8_t* cod
   const int64_t nblk = p.rows / N;
   dim3 grid((unsigned)((p.cols + CC - 1) / CC), (unsigned)((nblk + p.nb - 1) / p.nb), (unsigned)p.batch);
   const size_t smem = (size_t)CC * p.pitch * sizeof(float);
-  if (!p.sawb) HOT_CUDA(cudaMemsetAsync(ws, 0, sizeof(uint32_t) * (p.scale_row ? p.cols : p.batch), st));
+  if (!p.sawb) HOT_CUDA(cudaMemsetAsync(ws, 0, sizeof(uint32_t) * (p.scale_row ? (size_t)p.cols * p.batch : (size_t)p.batch), st));
   col_ht_absmax_kernel<T, N><<<grid, kThreads, 0, st>>>(x, p, ws);
   auto launch = [&](auto kernel) -> int {
     HOT_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
@@ -604,8 +606,7 @@ int col_ht_quant_impl(const void* x, int dtype, int64_t rows, int64_t cols, int6
   p.pitch = ((nb * r + 31) / 32) * 32 + 4;
   const int64_t row_bytes = p.store4 ? (p.out_len + 1) / 2 : p.out_len;
   if (sample_pitch > 0) {
-    if (p.scale_row || p.sawb || p.store4)
-      HOT_FAIL(HOT_ERR_UNSUPPORTED, "hot_col_ht_quant_batched: HOT_SCALE_TENSOR (one scale per sample) and HOT_STORE_INT8 only");
+    if (p.store4) HOT_FAIL(HOT_ERR_UNSUPPORTED, "hot_col_ht_quant_batched: HOT_STORE_INT8 only");
     if (sample_pitch % 16 != 0 || sample_pitch < ((row_bytes + 7) / 8) * 8 || ld_codes < sample_pitch * batch)
       HOT_FAIL(HOT_ERR_ARG, "hot_col_ht_quant_batched: sample pitch %lld must be a multiple of 16, >= %lld, and fit the row pitch",
                (long long)sample_pitch, (long long)row_bytes);

@@ -31,6 +31,7 @@ struct QuantDev {
   const float* noise;  // explicit uniforms (ROUND_NOISE)
   uint32_t k0, k1;     // Philox key   = seed
   uint32_t o0, o1;     // Philox c2,c3 = offset
+  uint32_t rk0[10], rk1[10];  // the key of each round (the key schedule is the same for every block)
 };
 
 inline QuantDev make_quant_dev(const hot_quant_t& q) {
@@ -41,6 +42,10 @@ inline QuantDev make_quant_dev(const hot_quant_t& q) {
   d.k1 = (uint32_t)(q.seed >> 32);
   d.o0 = (uint32_t)q.offset;
   d.o1 = (uint32_t)(q.offset >> 32);
+  for (int r = 0; r < 10; ++r) {
+    d.rk0[r] = d.k0 + (uint32_t)r * 0x9E3779B9u;
+    d.rk1[r] = d.k1 + (uint32_t)r * 0xBB67AE85u;
+  }
   return d;
 }
 
@@ -49,18 +54,18 @@ inline QuantDev make_quant_dev(const hot_quant_t& q) {
 constexpr float kEps = 1e-11f;  // the reference's args.eps, added to the scale before dividing
 
 // Philox4x32-10 (Salmon et al., "Parallel random numbers: as easy as 1, 2, 3").
+// rk0 / rk1: the ten round keys (key + r * Weyl constant), precomputed by the host so that they
+// reach the XORs as kernel-parameter operands; each round is two 32 x 32 -> 64 bit products.
 __device__ __forceinline__ uint4 philox4x32_10(uint32_t c0, uint32_t c1, uint32_t c2, uint32_t c3,
-                                               uint32_t k0, uint32_t k1) {
+                                               const uint32_t (&rk0)[10], const uint32_t (&rk1)[10]) {
 #pragma unroll
   for (int r = 0; r < 10; ++r) {
-    const uint32_t hi0 = __umulhi(0xD2511F53u, c0), lo0 = 0xD2511F53u * c0;
-    const uint32_t hi1 = __umulhi(0xCD9E8D57u, c2), lo1 = 0xCD9E8D57u * c2;
-    c0 = hi1 ^ c1 ^ k0;
-    c1 = lo1;
-    c2 = hi0 ^ c3 ^ k1;
-    c3 = lo0;
-    k0 += 0x9E3779B9u;
-    k1 += 0xBB67AE85u;
+    const uint64_t p0 = (uint64_t)0xD2511F53u * (uint64_t)c0;
+    const uint64_t p1 = (uint64_t)0xCD9E8D57u * (uint64_t)c2;
+    c0 = (uint32_t)(p1 >> 32) ^ c1 ^ rk0[r];
+    c1 = (uint32_t)p1;
+    c2 = (uint32_t)(p0 >> 32) ^ c3 ^ rk1[r];
+    c3 = (uint32_t)p0;
   }
   return make_uint4(c0, c1, c2, c3);
 }
@@ -68,7 +73,7 @@ __device__ __forceinline__ uint4 philox4x32_10(uint32_t c0, uint32_t c1, uint32_
 // The 16 random bytes of Philox block g: the stochastic-rounding bits of elements 16g .. 16g+15
 // (element 16g + j takes byte j, little-endian within the words x, y, z, w).
 __device__ __forceinline__ uint4 philox_block16(const QuantDev& q, uint64_t g) {
-  return philox4x32_10((uint32_t)g, (uint32_t)(g >> 32), q.o0, q.o1, q.k0, q.k1);
+  return philox4x32_10((uint32_t)g, (uint32_t)(g >> 32), q.o0, q.o1, q.rk0, q.rk1);
 }
 __device__ __forceinline__ uint32_t philox_byte(const uint4& r, int j) {
   const uint32_t w = j < 4 ? r.x : (j < 8 ? r.y : (j < 12 ? r.z : r.w));

@@ -728,7 +728,9 @@ __global__ void __launch_bounds__(kEpiThreads + 64 + ((A4 || B4) ? kUnpackThread
       const uint32_t t_addr = tmem_base + buf * kBufStride + ((uint32_t)(q * 32) << 16);
       if (kGrouped && p.group_kb) {
         // running fp32 sums of this team's chunks live in registers across the groups of a tile
-        const float ga = p.ga[seg.group], gb = p.gb[seg.group];
+        // sa_row: one scale per (group, row) of A instead of one per group
+        const float ga = p.sa_row ? (row_ok ? p.ga[(size_t)seg.group * (size_t)p.M + (size_t)row] : 0.0f) : p.ga[seg.group];
+        const float gb = p.gb[seg.group];
 #pragma unroll
         for (int k = 0; k < BN / 64; ++k) {
           uint32_t acc[32];
@@ -1158,8 +1160,9 @@ extern "C" int hot_gemm_i8(const void* a, int a_storage, int64_t lda, const void
 }
 
 extern "C" int hot_gemm_i8_grouped(const void* a, int64_t lda, const void* b, int64_t ldb, int64_t M, int64_t N,
-                                   int64_t groups, int64_t group_k, const float* scale_a, const float* scale_b, float post,
-                                   void* out, int out_dtype, int64_t ldo, uint32_t* status_word, hot_stream_t stream) {
+                                   int64_t groups, int64_t group_k, const float* scale_a, int scale_a_per_row,
+                                   const float* scale_b, float post, void* out, int out_dtype, int64_t ldo,
+                                   uint32_t* status_word, hot_stream_t stream) {
   using namespace hot;
   if (!a || !b || !out || !scale_a || !scale_b) HOT_FAIL(HOT_ERR_ARG, "hot_gemm_i8_grouped: null pointer");
   if (M <= 0 || N <= 0 || groups <= 0 || group_k <= 0 || M > (1 << 30) || N > (1 << 30) || groups * group_k > (1 << 30))
@@ -1181,7 +1184,8 @@ extern "C" int hot_gemm_i8_grouped(const void* a, int64_t lda, const void* b, in
   p.K = (int)K;
   p.num_kb = (int)(K / kBK);
   p.sa = p.sb = nullptr;
-  p.sa_row = p.sb_row = 0;
+  p.sa_row = scale_a_per_row ? 1 : 0;
+  p.sb_row = 0;
   p.group_kb = (int)(group_k / kBK);
   p.ga = scale_a;
   p.gb = scale_b;

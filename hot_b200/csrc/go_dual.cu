@@ -111,32 +111,46 @@ __device__ __forceinline__ void butterfly_tokens16_even(const float2 (&u)[16], f
   }
 }
 
-// Quantise 16 consecutive codes of one row of the transposed g_w operand (stored-layout element
-// index e0, a multiple of 16) into 16 bytes.
+// Quantise 16 consecutive codes of two neighbouring rows (channels c, c + 1) of the transposed g_w
+// operand into 16 bytes each.  y[i] = (value i of channel c, value i of channel c + 1): the packed
+// fp32 operations run across the channel pair, so the transform's outputs are used where they are.
+// e_a / e_b: stored-layout element index of the first code of each row (multiples of 16).
 template <int ROUND>
-__device__ __forceinline__ uint4 quantise16_int8(const float (&y)[16], const ScalePair& sp, const QuantDev& q, uint64_t e0) {
-  uint32_t w[4] = {0, 0, 0, 0};
+__device__ __forceinline__ void quantise16_int8_pair(const float2 (&y)[16], const ScalePair& sa, const ScalePair& sb,
+                                                     const QuantDev& q, uint64_t e_a, uint64_t e_b, uint4& out_a, uint4& out_b) {
+  uint32_t wa[4] = {0, 0, 0, 0}, wb[4] = {0, 0, 0, 0};
   if (ROUND == HOT_ROUND_STOCH_PHILOX) {
-    const uint4 r = philox_block16(q, e0 >> 4);
-    const uint32_t rr[4] = {r.x, r.y, r.z, r.w};
-    uint32_t bits[16];
+    const uint4 r_a = philox_block16(q, e_a >> 4), r_b = philox_block16(q, e_b >> 4);
+    const uint32_t ra[4] = {r_a.x, r_a.y, r_a.z, r_a.w}, rb[4] = {r_b.x, r_b.y, r_b.z, r_b.w};
+    const float2 r2 = make_float2(sa.dv.r, sb.dv.r), nd2 = make_float2(-sa.dv.d, -sb.dv.d);
+    const float2 c2 = make_float2(sa.c0, sa.c0), magic2 = make_float2(kFloorMagic, kFloorMagic);
+    uint32_t ba[16], bb[16];
 #pragma unroll
-    for (int i = 0; i < 16; i += 2) {
-      const float2 t = philox_offset_bits2(make_float2(y[i], y[i + 1]), sp,
-                                           make_float2(philox_u128(rr[i >> 2], i & 3), philox_u128(rr[i >> 2], (i + 1) & 3)));
-      bits[i] = __float_as_uint(t.x);
-      bits[i + 1] = __float_as_uint(t.y);
+    for (int i = 0; i < 16; ++i) {
+      const float2 q0 = __fmul2_rn(y[i], r2);                    // the exact division of div2_exact,
+      const float2 e = __ffma2_rn(q0, nd2, y[i]);                // with one divisor per channel
+      const float2 d = __ffma2_rn(e, r2, q0);
+      const float2 u = make_float2(philox_u128(ra[i >> 2], i & 3), philox_u128(rb[i >> 2], i & 3));
+      const float2 t = __fadd2_rd(add2(add2(d, c2), u), magic2);
+      ba[i] = __float_as_uint(t.x);
+      bb[i] = __float_as_uint(t.y);
     }
     const uint32_t off = (uint32_t)(q.qmax + 1.0f);
 #pragma unroll
-    for (int k = 0; k < 4; ++k)
-      w[k] = remove_offset(gather_low_bytes(bits[4 * k], bits[4 * k + 1], bits[4 * k + 2], bits[4 * k + 3]), off, 0x01010101u, 0x100u);
+    for (int k = 0; k < 4; ++k) {
+      wa[k] = remove_offset(gather_low_bytes(ba[4 * k], ba[4 * k + 1], ba[4 * k + 2], ba[4 * k + 3]), off, 0x01010101u, 0x100u);
+      wb[k] = remove_offset(gather_low_bytes(bb[4 * k], bb[4 * k + 1], bb[4 * k + 2], bb[4 * k + 3]), off, 0x01010101u, 0x100u);
+    }
   } else {
     const int qmax = (int)q.qmax;
 #pragma unroll
-    for (int i = 0; i < 16; ++i) w[i >> 2] |= (uint32_t)(quantise_one<ROUND>(y[i], sp, 0.0f, qmax) & 0xFF) << (8 * (i & 3));
+    for (int i = 0; i < 16; ++i) {
+      wa[i >> 2] |= (uint32_t)(quantise_one<ROUND>(y[i].x, sa, 0.0f, qmax) & 0xFF) << (8 * (i & 3));
+      wb[i >> 2] |= (uint32_t)(quantise_one<ROUND>(y[i].y, sb, 0.0f, qmax) & 0xFF) << (8 * (i & 3));
+    }
   }
-  return make_uint4(w[0], w[1], w[2], w[3]);
+  out_a = make_uint4(wa[0], wa[1], wa[2], wa[3]);
+  out_b = make_uint4(wb[0], wb[1], wb[2], wb[3]);
 }
 
 // PASS 0: statistics.  PASS 1: quantise (RX / RW: rounding of the g_x / g_w side).
@@ -150,8 +164,9 @@ __global__ void __launch_bounds__(kThreads, sizeof(T) == 2 ? 3 : 1) go_dual_kern
   const bool w_row = FAST ? false : p.w_row != 0;
   const bool x_store4 = FAST ? true : p.x_store4 != 0;
   extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~(uintptr_t)127);
-  uint8_t* tile[2] = {smem, smem + Tile<T>::kBytes};
+  // rounded up to 128 bytes by an offset, so that every pointer below is still visibly derived from
+  // the shared array and its loads and stores compile to shared-memory instructions
+  uint8_t* smem = smem_raw + ((128u - ((uint32_t)__cvta_generic_to_shared(smem_raw) & 127u)) & 127u);
   uint8_t* stage_out = smem + 2 * Tile<T>::kBytes;                       // [kTC][kStagePitch] (PASS 1)
   uint32_t* s_colmax = reinterpret_cast<uint32_t*>(stage_out);          // [kTC]             (PASS 0)
   uint64_t* full = reinterpret_cast<uint64_t*>(smem + 2 * Tile<T>::kBytes + kTC * kStagePitch);
@@ -175,7 +190,7 @@ __global__ void __launch_bounds__(kThreads, sizeof(T) == 2 ? 3 : 1) go_dual_kern
   auto issue = [&](int tile_idx, int s) {
     const int tt = tile_idx / tiles_c, tc = tile_idx % tiles_c;
     mbar_expect_tx(&full[s], Tile<T>::kBytes);
-    tma_load_2d(tile[s], &tmap, &full[s], tc * Tile<T>::kRowBytes, tt * kTT);
+    tma_load_2d(smem + s * Tile<T>::kBytes, &tmap, &full[s], tc * Tile<T>::kRowBytes, tt * kTT);
   };
   if (tid == 0 && (int)blockIdx.x < num_tiles) issue(blockIdx.x, 0);
 
@@ -202,7 +217,7 @@ __global__ void __launch_bounds__(kThreads, sizeof(T) == 2 ? 3 : 1) go_dual_kern
     if (tid == 0 && next < num_tiles) issue(next, s ^ 1);  // stage s^1 was released by the barrier below
     ok = mbar_wait(&full[s], (it >> 1) & 1u, abort_flag);
     if (!ok) break;
-    const uint8_t* tl = tile[s];
+    const uint8_t* tl = smem + s * Tile<T>::kBytes;
     const int tt = t_idx / tiles_c, tc = t_idx % tiles_c;
     const int64_t tok0 = (int64_t)tt * kTT;
     const int ch0 = tc * kTC;
@@ -254,7 +269,7 @@ __global__ void __launch_bounds__(kThreads, sizeof(T) == 2 ? 3 : 1) go_dual_kern
     {
       const int cp = tid & 31, bp = tid >> 5;
       const int c_loc = cp * 2;
-      float y[2][16];  // kept rows of [channel][block A slots 0..7 | block B slots 0..7]
+      float2 y[16];  // kept rows of the channel pair: block A slots 0..7 | block B slots 0..7
       float cmax0 = 0.0f, cmax1 = 0.0f;
 #pragma unroll
       for (int blk = 0; blk < 2; ++blk) {
@@ -269,8 +284,7 @@ __global__ void __launch_bounds__(kThreads, sizeof(T) == 2 ? 3 : 1) go_dual_kern
             cmax0 = fmaxf(cmax0, fabsf(e[i].x));
             cmax1 = fmaxf(cmax1, fabsf(e[i].y));
           } else {
-            y[0][blk * 8 + kSlotOfEvenRow[i]] = e[i].x;
-            y[1][blk * 8 + kSlotOfEvenRow[i]] = e[i].y;
+            y[blk * 8 + kSlotOfEvenRow[i]] = e[i];
           }
         }
       }
@@ -285,18 +299,23 @@ __global__ void __launch_bounds__(kThreads, sizeof(T) == 2 ? 3 : 1) go_dual_kern
         }
       } else {
         const int64_t out_len = p.L / 2;
-#pragma unroll
-        for (int cc = 0; cc < 2; ++cc) {
-          const int ch = ch0 + c_loc + cc;
-          ScalePair sp = sp_w;
-          if (w_row) {
-            sp = scale_from_absmax(__uint_as_float(p.max_w[ch]), p.qw.qmax);
-            if (tt == 0 && bp == 0) p.s_w[ch] = sp.s;
+        const int ch = ch0 + c_loc;
+        ScalePair sa = sp_w, sb = sp_w;
+        if (w_row) {
+          sa = scale_from_absmax(__uint_as_float(p.max_w[ch]), p.qw.qmax);
+          sb = scale_from_absmax(__uint_as_float(p.max_w[ch + 1]), p.qw.qmax);
+          if (tt == 0 && bp == 0) {
+            p.s_w[ch] = sa.s;
+            p.s_w[ch + 1] = sb.s;
           }
-          uint4 codes = make_uint4(0, 0, 0, 0);
-          if (pair_ok) codes = quantise16_int8<RW>(y[cc], sp, p.qw, (uint64_t)ch * (uint64_t)out_len + (uint64_t)blk_pair * 16u);
-          *reinterpret_cast<uint4*>(stage_out + (c_loc + cc) * kStagePitch + bp * 16) = codes;
         }
+        uint4 codes_a = make_uint4(0, 0, 0, 0), codes_b = make_uint4(0, 0, 0, 0);
+        if (pair_ok) {
+          const uint64_t e_a = (uint64_t)ch * (uint64_t)out_len + (uint64_t)blk_pair * 16u;
+          quantise16_int8_pair<RW>(y, sa, sb, p.qw, e_a, e_a + (uint64_t)out_len, codes_a, codes_b);
+        }
+        *reinterpret_cast<uint4*>(stage_out + c_loc * kStagePitch + bp * 16) = codes_a;
+        *reinterpret_cast<uint4*>(stage_out + (c_loc + 1) * kStagePitch + bp * 16) = codes_b;
       }
     }
     __syncthreads();  // tile consumed; staging complete

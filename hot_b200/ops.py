@@ -219,8 +219,9 @@ def sample_pitch(out_len: int) -> int:
 
 def col_ht_quant_batched(x: torch.Tensor, order: int, sel: Sequence[int], q: Quant, logical_layout: str = "natural"):
     """``col_ht_quant`` on a batch ``x`` [B, rows, cols], transform along the rows of each sample, one
-    scale per sample.  Returns (codes_t uint8 [cols, B * pitch] with sample b at byte b * pitch of
-    each row, zero padded, scales float32 [B], out_len per sample, pitch)."""
+    scale per sample (``q.scale`` "tensor" or "sawb") or one per sample and output row ("row").
+    Returns (codes_t uint8 [cols, B * pitch] with sample b at byte b * pitch of each row, zero
+    padded, scales float32 [B] or [B, cols], out_len per sample, pitch)."""
     _require_cuda(x)
     if x.dim() != 3 or not x.is_contiguous():
         raise ValueError("x must be a contiguous 3-D tensor")
@@ -229,8 +230,11 @@ def col_ht_quant_batched(x: torch.Tensor, order: int, sel: Sequence[int], q: Qua
     out_len = rows // order * r
     pitch = sample_pitch(out_len)
     codes = torch.empty((cols, B * pitch), dtype=torch.uint8, device=x.device)
-    scales = torch.empty((B,), dtype=torch.float32, device=x.device)
-    ws = torch.empty((max(B, 16),), dtype=torch.int32, device=x.device)
+    scales = torch.empty((B, cols) if q.scale == "row" else (B,), dtype=torch.float32, device=x.device)
+    words = B * cols if q.scale == "row" else B
+    if q.scale == "sawb":
+        words = B * int(C.lib().hot_col_ht_quant_scratch_words(_dtype(x), rows, cols, order, r, q.to_c().scale_mode))
+    ws = torch.empty((max(words, 16) + 1) // 2, dtype=torch.int64, device=x.device)   # 8-byte aligned
     sel_c = (C.c_i32 * r)(*[int(v) for v in sel])
     with torch.cuda.device(x.device):
         C.check(C.lib().hot_col_ht_quant_batched(x.data_ptr(), _dtype(x), B, rows, cols, cols, order, sel_c, r,
@@ -246,15 +250,20 @@ def gemm_i8_grouped(a: torch.Tensor, b: torch.Tensor, M: int, N: int, groups: in
                     status: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """out [M, N] = (sum_g ((a_g . b_g^T) * scale_a[g]) * scale_b[g]) * post, where group g is the
     columns [g * group_k, (g + 1) * group_k) of the INT8 code matrices ``a`` [M, .] and ``b`` [N, .]
-    (group_k a multiple of 128); the sum over groups runs in fp32, group 0 first."""
+    (group_k a multiple of 128); the sum over groups runs in fp32, group 0 first.  ``scale_a`` of
+    shape [groups, M] gives every row of ``a`` its own scale within each group."""
     _require_cuda(a, b, scale_a, scale_b)
     odt = {torch.float32: C.HOT_F32, torch.bfloat16: C.HOT_BF16}[out_dtype]
     if out is None:  # the kernel stores through a tensor map: the row pitch must be a multiple of 16 bytes
         per16 = 16 // torch.empty((), dtype=out_dtype).element_size()
         out = torch.empty((M, (N + per16 - 1) // per16 * per16), dtype=out_dtype, device=a.device)[:, :N]
     with torch.cuda.device(a.device):
+        per_row = scale_a.dim() == 2
+        if per_row and (tuple(scale_a.shape) != (groups, M) or not scale_a.is_contiguous()):
+            raise ValueError("per-row scale_a must be a contiguous [groups, M] tensor")
         C.check(C.lib().hot_gemm_i8_grouped(a.data_ptr(), a.stride(0), b.data_ptr(), b.stride(0), M, N, groups, group_k,
-                                            scale_a.data_ptr(), scale_b.data_ptr(), float(post), out.data_ptr(), odt,
+                                            scale_a.data_ptr(), 1 if per_row else 0, scale_b.data_ptr(), float(post),
+                                            out.data_ptr(), odt,
                                             out.stride(0), status.data_ptr() if status is not None else None, _stream(a)),
                 "hot_gemm_i8_grouped")
     return out
@@ -433,7 +442,9 @@ def linear_backward_batched(go: torch.Tensor, w: torch.Tensor, x_q_t: torch.Tens
     semantics: every quantiser of grad_out and of the activation takes one scale per sample, the
     low-rank projection runs along the tokens of each sample, and grad_w is the fp32 sum over
     samples of the dequantised per-sample products (utils/quant_matmul.py:223-225, 288-290,
-    322-324).  ``x_q_t`` / ``scale_x`` come from ``abc_compress_batched``.  Returns
+    322-324).  With ``scale="row"`` (the reference's norm_quantizer) the g_x side takes one scale per
+    token and the g_w side one per sample and output channel.  ``x_q_t`` / ``scale_x`` come from
+    ``abc_compress_batched``.  Returns
     (grad_x [B, L, I] or None, grad_w [O, I] or None)."""
     _require_cuda(go, w, x_q_t)
     if go.dim() != 3 or not go.is_contiguous():
@@ -442,10 +453,15 @@ def linear_backward_batched(go: torch.Tensor, w: torch.Tensor, x_q_t: torch.Tens
     I = w.shape[1]
     gx = gw = None
     if need_gx:
-        q_go, s_go = row_ht_quant_batched(go, cfg.order_o, cfg.q_gx)
+        if cfg.q_gx.scale == "row":   # one scale per token: the samples' rows are the rows of the flattened tensor
+            q_go, s_go = row_ht_quant(go.view(B * L, O), cfg.order_o, cfg.q_gx)
+            rows_per_scale = 1
+        else:
+            q_go, s_go = row_ht_quant_batched(go, cfg.order_o, cfg.q_gx)
+            rows_per_scale = L
         q_w_t, s_w, _ = col_ht_quant(w, cfg.order_o, list(range(cfg.order_o)), _one_per_byte(cfg.q_w), "natural")
         gx = gemm_i8(q_go, cfg.q_gx.storage, q_w_t, "int8", B * L, I, O, s_go, s_w, 1.0 / cfg.order_o, go.dtype,
-                     status=status, a_rows_per_scale=L).view(B, L, I)
+                     status=status, a_rows_per_scale=rows_per_scale).view(B, L, I)
     if need_gw:
         q_gw_t, s_gw, out_len, pitch = col_ht_quant_batched(go, cfg.order_l, cfg.sel_l, _one_per_byte(cfg.q_gw), "transposed")
         if x_q_t.shape[1] != B * pitch:

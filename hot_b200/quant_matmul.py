@@ -112,8 +112,14 @@ def norm_quantizer(x: Tensor, quantBits: int, is_batched: bool = False):
 def sawb_quantizer(x: Tensor, quantBits: int, is_batched: bool = False):
     """One scale from clip = 12.1*sqrt(mean(x^2)) - 12.2*mean(|x|), values clamped to +-clip, round to
     nearest (utils/quant_matmul.py:40-55).  Returns (codes as float, scale)."""
-    if is_batched:
-        raise NotImplementedError("sawb_quantizer: per-sample (3-D, vmap) clip values are not built; flatten tokens to 2-D")
+    if is_batched:   # one clip per sample of x [B, ...] (torch.vmap over dim 0, utils/quant_matmul.py:51-55)
+        if x.dim() < 2:
+            raise ValueError("a batched quantiser takes a tensor with a batch dim")
+        x3 = (x.reshape(x.shape[0], -1, x.shape[-1]) if x.dim() >= 3 else x.reshape(x.shape[0], 1, x.shape[1])).contiguous()
+        q = ops.Quant(quantBits, "int8", "nearest", "sawb")
+        codes_t, s, n, pitch = ops.col_ht_quant_batched(x3, 1, [0], q, "natural")
+        codes = codes_t.view(torch.int8).view(x3.shape[2], x3.shape[0], pitch)[:, :, :n].permute(1, 2, 0)
+        return codes.to(x.dtype).reshape(x.shape), s
     x2 = x if x.dim() == 2 else x.reshape(-1, x.shape[-1])
     if not x2.is_contiguous():
         x2 = x2.contiguous()
@@ -247,8 +253,6 @@ class FLinearQ(Function):
         if ctx.per_sample:
             if x.shape[1] % n_l:
                 raise ValueError("token count %d is not a multiple of the low-rank order %d" % (x.shape[1], n_l))
-            if q_x.scale != "tensor":
-                raise NotImplementedError("Activation rounding scheme %r with per-sample scales is not built" % a.quantBWDAct)
             x_q_t, scale_x, _ = ops.abc_compress_batched(x.detach().contiguous(), cfg)
         else:
             x2 = x.detach().reshape(-1, x.shape[-1])
@@ -294,8 +298,6 @@ class FLinearQ(Function):
         need_gx, need_gw = ctx.needs_input_grad[0], ctx.needs_input_grad[1]
         gx = gw = None
         if (need_gx or need_gw) and ctx.per_sample:
-            if q_gx.scale != "tensor" or q_gw.scale != "tensor":
-                raise NotImplementedError("per-token / per-channel grad_output scales with per-sample (3-D) inputs are not built")
             gx, gw = ops.linear_backward_batched(go, w.detach(), x_q_t, scale_x, cfg, need_gx=need_gx, need_gw=need_gw)
         elif ctx.gx_basis is not None:
             if need_gw:

@@ -127,8 +127,11 @@ int hot_col_ht_quant(const void* x, int dtype, int64_t rows, int64_t cols, int64
  *   codes_t  [cols, batch * sample_pitch] INT8: sample b's rows * r / order codes start
  *            b * sample_pitch bytes into each output row and are followed by zeros up to the next
  *            sample (sample_pitch a multiple of 16; a multiple of 128 for hot_gemm_i8_grouped)
- *   scales [batch];  absmax_ws  `batch` words of scratch
- * HOT_SCALE_TENSOR and HOT_STORE_INT8 only.  noise element index: b * (rows*r/order * cols) + the index
+ *   scales [batch];  absmax_ws  `batch` words of scratch (HOT_SCALE_SAWB: batch times the words
+ *            hot_col_ht_quant_scratch_words gives for one sample, 8-byte aligned)
+ * HOT_SCALE_TENSOR, HOT_SCALE_SAWB (the clip of each sample from its own moments, as the vmapped
+ * sawb_quantizer gives, utils/quant_matmul.py:51-55) or HOT_SCALE_ROW (scales [batch, cols]: one per
+ * sample and output row, the vmapped norm_quantizer; batch * cols words of scratch); HOT_STORE_INT8 only.  noise element index: b * (rows*r/order * cols) + the index
  * hot_col_ht_quant would use within the sample; Philox element index: the byte position in codes_t
  * counted with a row pitch of batch * sample_pitch (column c, sample b, code l: (c * batch + b) *
  * sample_pitch + l).
@@ -221,13 +224,16 @@ int hot_gemm_i8_ws(const void* a, int a_storage, int64_t lda, const void* b, int
  *   out[m, n] = (sum_g ((float)(sum_{k in group g} a[m,k] * b[n,k]) * scale_a[g]) * scale_b[g]) * post
  *   a [M, groups * group_k], b [N, groups * group_k] INT8, K contiguous, pitches in bytes
  *   group_k a multiple of 128 (pad each sample with zero codes: hot_col_ht_quant_batched does)
+ *   scale_a [groups], or with scale_a_per_row != 0 [groups, M]: scale_a[g * M + m] (one scale per
+ *   sample and row, what the vmapped norm_quantizer gives, utils/quant_matmul.py:19-37);  scale_b [groups]
  *   out HOT_F32 | HOT_BF16, base and pitch 16-byte aligned
  * Stands in for the batched matmul on integer values, the per-sample scales and the sum over
  * the batch that autograd applies to the [B, O, I] result (utils/quant_matmul.py:322-324).
  */
 int hot_gemm_i8_grouped(const void* a, int64_t lda, const void* b, int64_t ldb, int64_t M, int64_t N,
-                        int64_t groups, int64_t group_k, const float* scale_a, const float* scale_b, float post,
-                        void* out, int out_dtype, int64_t ldo, uint32_t* status_word, hot_stream_t stream);
+                        int64_t groups, int64_t group_k, const float* scale_a, int scale_a_per_row,
+                        const float* scale_b, float post, void* out, int out_dtype, int64_t ldo,
+                        uint32_t* status_word, hot_stream_t stream);
 
 /*
  * Two integer GEMMs in one launch.  The g_x product of a layer leaves its last wave of tiles nearly

@@ -404,13 +404,15 @@ def abc_compress_batched(x: np.ndarray, n_l: int, sel: np.ndarray, bits: int, u,
 
 def linear_backward_batched(go, w, x_q, s_x, *, n_o: int, n_l: int, sel, bits_gx: int = 4, bits_w: int = 4,
                             bits_gw: int = 8, u_go=None, u_w=None, u_gw=None, w_mode: str = "stoch",
-                            exact_matmul: bool = True):
+                            gx_per_token: bool = False, gw_per_channel: bool = False, exact_matmul: bool = True):
     """FLinearQ.backward (:214-348) for go [B, L, O], x_q [B, L', I], s_x [B].  Every quantiser of a
     batched tensor takes one scale per sample; the weight is 2-D and keeps one scale.  grad_input[b] =
     (q_go[b] @ q_w) * s_go[b] * s_w / n_o (:288-290, 342).  grad_w = sum_b (q_gw[b] @ x_q[b]) * s_gw[b]
     * s_x[b] / n_l (:322-324, 344; the sum over b is the reduction autograd applies to the
     [B, O, I] result); here it runs in float32 from sample 0 upwards, with the exact division by the
-    power of two n_l after it."""
+    power of two n_l after it.  gx_per_token / gw_per_channel: the vmapped norm_quantizer (:19-37) on
+    that side, i.e. one scale per row of each sample's [L, O] / [O, L'] operand, applied to the
+    integer product (the reference multiplies the scales in before its float matmul)."""
     go = np.asarray(go, dtype=F32)
     w = np.asarray(w, dtype=F32)
     B = go.shape[0]
@@ -422,13 +424,16 @@ def linear_backward_batched(go, w, x_q, s_x, *, n_o: int, n_l: int, sel, bits_gx
     q_go, s_go, gx, q_gw, s_gw = [], [], [], [], []
     run = None
     for b in range(B):
-        qg, sg = quant_tensor(fwht_last(go[b], n_o), bits_gx, _sample(u_go, b))
+        qg, sg = (quant_rows if gx_per_token else quant_tensor)(fwht_last(go[b], n_o), bits_gx, _sample(u_go, b))
         acc = _int_matmul(qg, q_w, exact_matmul)
-        gx.append(((acc.astype(F32) * F32(sg)) * F32(s_w)) / F32(n_o))
+        sg_b = sg[:, None] if gx_per_token else F32(sg)
+        gx.append(((acc.astype(F32) * sg_b) * F32(s_w)) / F32(n_o))
         q_go.append(qg)
         s_go.append(sg)
-        qw_, sw_ = quant_tensor(np.ascontiguousarray(hla(go[b], n_l, sel).T), bits_gw, _sample(u_gw, b))
-        v = ((_int_matmul(qw_, np.asarray(x_q[b]), exact_matmul).astype(F32) * F32(sw_)) * F32(s_x[b])).astype(F32)
+        qw_, sw_ = (quant_rows if gw_per_channel else quant_tensor)(np.ascontiguousarray(hla(go[b], n_l, sel).T), bits_gw,
+                                                                    _sample(u_gw, b))
+        sw_b = sw_[:, None] if gw_per_channel else F32(sw_)
+        v = ((_int_matmul(qw_, np.asarray(x_q[b]), exact_matmul).astype(F32) * sw_b) * F32(s_x[b])).astype(F32)
         run = v if run is None else (run + v).astype(F32)
         q_gw.append(qw_)
         s_gw.append(sw_)

@@ -322,6 +322,55 @@ def batched(ref_args, hm, qm, out_dir: str):
              x_q=saved[0].numpy(), scale_x=saved[4].numpy(), grad_input=xt.grad.numpy(), grad_w=wt.grad.numpy())
     np.savez_compressed(os.path.join(out_dir, "flinearq_batched.npz"), **f)
 
+    # the same call with the training script's defaults for the weight and the activation buffer
+    # (sawb, ViT_main.py:102,104): the activation's clip is per sample through the reference's own
+    # vmap (sawb draws no random numbers), the weight is 2-D and keeps one clip
+    ref_args.quantBWDWgt = ref_args.quantBWDAct = "sawb"
+    xt = T(xx).requires_grad_(True)
+    wt = T(ww).requires_grad_(True)
+    qm.stoch_quantizer = per_sample(qm.stoch_quantizer_BWD)
+    try:
+        with NoiseQueue() as nq:
+            nq.queue += [T(u_go[b]) for b in range(B)] + [T(u_gw[b]) for b in range(B)]
+            y = qm.FLinearQ.apply(xt, wt, h_out, h_bs, "layer")
+            saved = y.grad_fn.saved_tensors
+            y.backward(T(go))
+            assert not nq.queue
+    finally:
+        qm.stoch_quantizer = keep
+        ref_args.quantBWDWgt = ref_args.quantBWDAct = "stoch"
+    f = dict(x=xx, w=ww, go=go, p=pm.astype(np.int8), u_go=u_go, u_gw=u_gw, y=y.detach().numpy(),
+             x_q=saved[0].numpy(), scale_x=saved[4].numpy(), grad_input=xt.grad.numpy(), grad_w=wt.grad.numpy())
+    np.savez_compressed(os.path.join(out_dir, "flinearq_batched_sawb.npz"), **f)
+
+    # and with the training script's defaults on all four operands (ViT_main.py:101-104: nq, sawb, nq,
+    # sawb), which is what runs while layer_quant_dict is still empty: the vmapped norm_quantizer takes
+    # one scale per token of each sample on the g_x side and one per sample and output channel on the
+    # g_w side, and returns dequantised values with scale 1
+    def per_sample_nq(x, bits, is_batched):
+        if not is_batched:
+            return qm.norm_quantizer_BWD(x, bits), 1.
+        return torch.stack([qm.norm_quantizer_BWD(x[b], bits) for b in range(x.shape[0])]), 1.
+
+    ref_args.quantBWDWgt = ref_args.quantBWDAct = "sawb"
+    ref_args.quantBWDGogi = ref_args.quantBWDGogw = "nq"
+    xt = T(xx).requires_grad_(True)
+    wt = T(ww).requires_grad_(True)
+    keep_nq = qm.norm_quantizer
+    qm.norm_quantizer = per_sample_nq
+    try:
+        with NoiseQueue() as nq:
+            nq.queue += [T(u_go[b]) for b in range(B)] + [T(u_gw[b]) for b in range(B)]
+            y = qm.FLinearQ.apply(xt, wt, h_out, h_bs, "layer")
+            y.backward(T(go))
+            assert not nq.queue
+    finally:
+        qm.norm_quantizer = keep_nq
+        ref_args.quantBWDWgt = ref_args.quantBWDAct = ref_args.quantBWDGogi = ref_args.quantBWDGogw = "stoch"
+    f = dict(x=xx, w=ww, go=go, p=pm.astype(np.int8), u_go=u_go, u_gw=u_gw, grad_input=xt.grad.numpy(),
+             grad_w=wt.grad.numpy())
+    np.savez_compressed(os.path.join(out_dir, "flinearq_batched_nq.npz"), **f)
+
 
 if __name__ == "__main__":
     main(sys.argv[1], os.path.dirname(os.path.abspath(__file__)))

@@ -122,14 +122,15 @@ def test_col_ht_quant_batched(ops, B, rows, cols, order, sel, dtype, rounding, l
 @pytest.mark.parametrize("M,N,groups,glen", [(96, 48, 3, 9), (300, 130, 5, 197), (3072, 768, 64, 197), (128, 128, 1, 128),
                                              (257, 96, 7, 300)])
 @pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
-def test_gemm_i8_grouped(ops, M, N, groups, glen, out_dtype):
+@pytest.mark.parametrize("per_row", [False, True])
+def test_gemm_i8_grouped(ops, M, N, groups, glen, out_dtype, per_row):
     rng = np.random.default_rng(M + N + groups)
     pitch = ops.sample_pitch(glen)
     a = np.zeros((M, groups, pitch), dtype=np.int8)
     b = np.zeros((N, groups, pitch), dtype=np.int8)
     a[:, :, :glen] = rng.integers(-127, 128, size=(M, groups, glen))
     b[:, :, :glen] = rng.integers(-127, 128, size=(N, groups, glen))
-    sa = (rng.random(groups) * 1e-3 + 1e-4).astype(np.float32)
+    sa = (rng.random((groups, M) if per_row else groups) * 1e-3 + 1e-4).astype(np.float32)   # [groups, M]: one per row too
     sb = (rng.random(groups) * 1e-2 + 1e-3).astype(np.float32)
     post = 0.125
     status = torch.zeros(1, dtype=torch.int32, device="cuda")
@@ -140,7 +141,7 @@ def test_gemm_i8_grouped(ops, M, N, groups, glen, out_dtype):
     run = None
     for g in range(groups):
         acc = a[:, g].astype(np.int64) @ b[:, g].astype(np.int64).T
-        v = ((acc.astype(np.float32) * sa[g]) * sb[g]).astype(np.float32)
+        v = ((acc.astype(np.float32) * (sa[g][:, None] if per_row else sa[g])) * sb[g]).astype(np.float32)
         run = v if run is None else (run + v).astype(np.float32)
     ref = torch.from_numpy((run * np.float32(post)).astype(np.float32)).to(out_dtype)
     assert torch.equal(out.cpu(), ref)
@@ -200,6 +201,134 @@ def test_batched_backward_golden(ops):
     x_q, s_xo = oc.abc_compress_batched(g["x"], n_l, sel, 8, g["u_x"])
     ref = oc.linear_backward_batched(g["go"], g["w"], x_q, s_xo, n_o=oc.block_order(O), n_l=n_l, sel=sel, u_go=g["u_go"],
                                      u_w=g["u_w"], u_gw=g["u_gw"])
+    assert np.array_equal(_bits(gx.cpu().numpy()), _bits(ref["grad_input"]))
+    assert np.array_equal(_bits(gw.cpu().numpy()), _bits(ref["grad_w"]))
+
+
+@pytest.mark.parametrize("B,rows,cols,order,sel", [
+    (3, 24, 96, 8, list(oc.wht_selection(24, 50)[1])),
+    (4, 197, 200, 1, [0]),
+    (64, 32, 128, 16, list(oc.lowrank_preset(16, 8))),
+    (5, 256, 768, 16, list(oc.lowrank_preset(16, 8))),                # several CTAs per sample
+])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_col_ht_quant_batched_sawb(ops, B, rows, cols, order, sel, dtype):
+    """One SAWB clip per sample (the vmapped sawb_quantizer), nearest rounding."""
+    r = len(sel)
+    out_len = rows // order * r
+    rng = np.random.default_rng(B * 7 + rows + cols)
+    x = rng.standard_normal((B, rows, cols)).astype(np.float32)
+    x *= (1.0 + 5.0 * rng.random((B, 1, 1))).astype(np.float32)
+    q = ops.Quant(8, "int8", "nearest", "sawb")
+    codes, scales, got_len, pitch = ops.col_ht_quant_batched(_dev(x, dtype), order, sel, q, "natural")
+    torch.cuda.synchronize()
+    c = codes.cpu().numpy().view(np.int8).astype(np.int32).reshape(cols, B, pitch)
+    got_s = scales.cpu().numpy()
+    xf = _as_f32(x, dtype)
+    for b in range(B):
+        y_t = np.ascontiguousarray(oc.hla(xf[b], order, np.array(sel)).T)
+        ref_c, ref_s = oc.quant_sawb(y_t, 8)
+        assert _bits(ref_s) == _bits(got_s[b]), (b, ref_s, got_s[b])
+        assert np.array_equal(c[:, b, :out_len], ref_c), (b, int((c[:, b, :out_len] != ref_c).sum()))
+        assert not c[:, b, out_len:].any()
+    assert len(set(got_s.tolist())) == B
+
+
+@pytest.mark.parametrize("B,rows,cols,order,sel", [
+    (3, 24, 96, 8, list(oc.wht_selection(24, 50)[1])),
+    (4, 197, 200, 1, [0]),
+    (64, 32, 128, 16, list(oc.lowrank_preset(16, 8))),
+])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("rounding", ["nearest", "noise", "philox"])
+def test_col_ht_quant_batched_row_scales(ops, B, rows, cols, order, sel, dtype, rounding):
+    """One scale per sample and output row (the vmapped norm_quantizer on [B, O, L'])."""
+    r = len(sel)
+    out_len = rows // order * r
+    rng = np.random.default_rng(B * 11 + rows + cols)
+    x = rng.standard_normal((B, rows, cols)).astype(np.float32)
+    x *= (1.0 + 5.0 * rng.random((B, 1, cols))).astype(np.float32)
+    seed, offset = 17, 5
+    if rounding == "noise":
+        u_t = rng.random((B, cols, out_len), dtype=np.float32)
+        u_dev = _dev(u_t)
+    elif rounding == "philox":
+        pitch_ = ops.sample_pitch(out_len)
+        u_t = np.ascontiguousarray(oc.philox_bytes(seed, offset, (cols, B, pitch_))[:, :, :out_len].transpose(1, 0, 2))
+        u_t, u_dev = u_t.view(oc.PhiloxBytes), None
+    else:
+        u_t, u_dev = None, None
+    q = ops.Quant(8, "int8", rounding, "row", seed, offset, u_dev)
+    codes, scales, got_len, pitch = ops.col_ht_quant_batched(_dev(x, dtype), order, sel, q, "transposed")
+    torch.cuda.synchronize()
+    assert tuple(scales.shape) == (B, cols)
+    c = codes.cpu().numpy().view(np.int8).astype(np.int32).reshape(cols, B, pitch)
+    got_s = scales.cpu().numpy()
+    xf = _as_f32(x, dtype)
+    for b in range(B):
+        y_t = np.ascontiguousarray(oc.hla(xf[b], order, np.array(sel)).T)
+        ref_c, ref_s = oc.quant_rows(y_t, 8, _slice(u_t, b))
+        assert np.array_equal(_bits(ref_s), _bits(got_s[b])), b
+        assert np.array_equal(c[:, b, :out_len], ref_c), (b, int((c[:, b, :out_len] != ref_c).sum()))
+        assert not c[:, b, out_len:].any()
+
+
+def test_batched_backward_nq_golden(ops):
+    """The reference's 3-D run with its default quantisers on all four operands (nq, sawb, nq, sawb):
+    both gradients against its output, and bit for bit against the oracle on the same noise."""
+    g = np.load(os.path.join(GOLDEN, "flinearq_batched_nq.npz"))
+    n_l, sel = oc.selection_from_matrix(g["p"])
+    B, L, O = g["go"].shape
+    cfg = ops.LinearConfig(order_o=oc.block_order(O), order_l=n_l, sel_l=list(sel),
+                           q_gx=ops.Quant(4, "int4", "noise", "row", 0, 0, _dev(g["u_go"])),
+                           q_w=ops.Quant(4, "int4", "nearest", "sawb"),
+                           q_gw=ops.Quant(8, "int8", "noise", "row", 0, 0, _dev(g["u_gw"])),
+                           q_x=ops.Quant(8, "int8", "nearest", "sawb"))
+    x_q_t, s_x, pitch = ops.abc_compress_batched(_dev(g["x"]), cfg)
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    gx, gw = ops.linear_backward_batched(_dev(g["go"]), _dev(g["w"]), x_q_t, s_x, cfg, status=status)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    for got, name in ((gx, "grad_input"), (gw, "grad_w")):
+        ref = g[name]
+        rel = np.linalg.norm(got.cpu().numpy() - ref) / np.linalg.norm(ref)
+        assert rel < 1e-3, (name, rel)
+    x_q, s_xo = oc.abc_compress_batched(g["x"], n_l, sel, 8, None, "sawb")
+    ref = oc.linear_backward_batched(g["go"], g["w"], x_q, s_xo, n_o=oc.block_order(O), n_l=n_l, sel=sel, u_go=g["u_go"],
+                                     u_gw=g["u_gw"], w_mode="sawb", gx_per_token=True, gw_per_channel=True)
+    assert np.array_equal(_bits(gx.cpu().numpy()), _bits(ref["grad_input"]))
+    assert np.array_equal(_bits(gw.cpu().numpy()), _bits(ref["grad_w"]))
+
+
+def test_batched_backward_sawb_golden(ops):
+    """The reference's 3-D run with sawb on the weight and the activation buffer (its training
+    defaults): saved codes, per-sample scales, both gradients; and bit for bit against the oracle."""
+    g = np.load(os.path.join(GOLDEN, "flinearq_batched_sawb.npz"))
+    n_l, sel = oc.selection_from_matrix(g["p"])
+    B, L, O = g["go"].shape
+    I = g["w"].shape[1]
+    sawb = ops.Quant(8, "int8", "nearest", "sawb")
+    cfg = ops.LinearConfig(order_o=oc.block_order(O), order_l=n_l, sel_l=list(sel),
+                           q_gx=ops.Quant(4, "int4", "noise", "tensor", 0, 0, _dev(g["u_go"])),
+                           q_w=ops.Quant(4, "int4", "nearest", "sawb"),
+                           q_gw=ops.Quant(8, "int8", "noise", "tensor", 0, 0, _dev(g["u_gw"])), q_x=sawb)
+    x_q_t, s_x, pitch = ops.abc_compress_batched(_dev(g["x"]), cfg)
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    gx, gw = ops.linear_backward_batched(_dev(g["go"]), _dev(g["w"]), x_q_t, s_x, cfg, status=status)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    out_len = L // n_l * len(sel)
+    xq = x_q_t.cpu().numpy().view(np.int8).reshape(I, B, pitch)[:, :, :out_len].transpose(1, 2, 0)
+    assert np.mean(xq != g["x_q"]) < 1e-3                              # float32 mean order differs in the reference
+    np.testing.assert_allclose(s_x.cpu().numpy(), g["scale_x"], rtol=1e-5)
+    for got, name in ((gx, "grad_input"), (gw, "grad_w")):
+        ref = g[name]
+        rel = np.linalg.norm(got.cpu().numpy() - ref) / np.linalg.norm(ref)
+        assert rel < 1e-3, (name, rel)
+    x_q, s_xo = oc.abc_compress_batched(g["x"], n_l, sel, 8, None, "sawb")
+    assert np.array_equal(xq, x_q) and np.array_equal(_bits(s_x.cpu().numpy()), _bits(s_xo))
+    ref = oc.linear_backward_batched(g["go"], g["w"], x_q, s_xo, n_o=oc.block_order(O), n_l=n_l, sel=sel, u_go=g["u_go"],
+                                     u_gw=g["u_gw"], w_mode="sawb")
     assert np.array_equal(_bits(gx.cpu().numpy()), _bits(ref["grad_input"]))
     assert np.array_equal(_bits(gw.cpu().numpy()), _bits(ref["grad_w"]))
 

@@ -50,8 +50,11 @@ def test_quantiser_callables_follow_the_reference_contract(hot):
     assert one == 1.0 and d.shape == g.shape
     row_err = (d - g).abs().amax(dim=1) / g.abs().amax(dim=1)
     assert float(row_err.max()) < 1.0 / 7 + 1e-3               # error bounded by one per-row step
-    with pytest.raises(NotImplementedError):
-        qm.sawb_quantizer(g.reshape(4, 12, 100), 4, True)       # per-sample clip values are not built
+    q, s = qm.sawb_quantizer(g.reshape(4, 12, 100), 4, True)   # one clip per sample
+    assert q.shape == (4, 12, 100) and s.shape == (4,)
+    for b in range(4):
+        rq, rs = oc.quant_sawb(gn.reshape(4, 12, 100)[b], 4)
+        assert np.float32(s[b].item()) == rs and np.array_equal(q[b].cpu().numpy().astype(np.int32), rq)
     assert set(qm.quant_scheme_dict) >= {"int_quantizer", "stoch_quantizer", "norm_quantizer"}
 
 
@@ -187,6 +190,25 @@ def test_hq_linear_3d_takes_one_scale_per_sample(hot):
                                      w_mode="int")
     assert np.array_equal(x.grad.cpu().numpy(), ref["grad_input"])
     assert np.array_equal(lin.weight.grad.cpu().numpy(), ref["grad_w"])
+    # the training script's defaults for the weight and the activation buffer (sawb), same 3-D call
+    args.quantBWDWgt = args.quantBWDAct = "sawb"
+    x.grad = None
+    lin.weight.grad = None
+    lin(x).backward(go)
+    xq, sx = oc.abc_compress_batched(x.detach().cpu().numpy(), n_l, sel, 8, None, "sawb")
+    ref = oc.linear_backward_batched(go.cpu().numpy(), lin.weight.detach().cpu().numpy(), xq, sx, n_o=16, n_l=n_l, sel=sel,
+                                     w_mode="sawb")
+    assert np.array_equal(x.grad.cpu().numpy(), ref["grad_input"])
+    assert np.array_equal(lin.weight.grad.cpu().numpy(), ref["grad_w"])
+    # all four of the training script's defaults (nq, sawb, nq, sawb): per-token / per-channel scales
+    # within each sample, stochastic rounding; the gradients stay close to the exact ones
+    args.quantBWDGogi = args.quantBWDGogw = "nq"
+    x.grad = None
+    lin.weight.grad = None
+    lin(x).backward(go)
+    exact_gx = go @ lin.weight.detach()
+    cos = torch.nn.functional.cosine_similarity(x.grad.flatten(), exact_gx.flatten(), dim=0)
+    assert torch.isfinite(lin.weight.grad).all() and float(cos) > 0.95, float(cos)
     # the batched quantiser callables: one scale per sample
     q, s = qm.int_quantizer(go, 4, True)
     assert q.shape == go.shape and s.shape == (B,)

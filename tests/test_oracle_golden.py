@@ -144,6 +144,45 @@ def test_flinearq_backward_batched(golden):
     assert rel_flat > 10 * (np.linalg.norm(out["grad_input"] - g["grad_input"]) / np.linalg.norm(g["grad_input"]) + 1e-7)
 
 
+def test_flinearq_backward_batched_sawb(golden):
+    """3-D input with the training script's weight / activation quantiser (sawb): the activation's
+    clip is per sample (the reference's own vmap), the weight's per tensor
+    (tests/golden/make_golden.py::batched, second fixture)."""
+    g = golden("flinearq_batched_sawb")
+    n_l, sel = oc.selection_from_matrix(g["p"])
+    x_q, s_x = oc.abc_compress_batched(g["x"], n_l, sel, 8, None, "sawb")
+    assert np.mean(x_q != g["x_q"].astype(np.int32)) < 1e-3           # float32 mean order differs
+    np.testing.assert_allclose(s_x, g["scale_x"], rtol=1e-5)
+    assert len(set(s_x.tolist())) == g["x"].shape[0]
+    O = g["w"].shape[0]
+    out = oc.linear_backward_batched(g["go"], g["w"], x_q, s_x, n_o=oc.block_order(O), n_l=n_l, sel=sel,
+                                     u_go=g["u_go"], u_gw=g["u_gw"], w_mode="sawb")
+    for name in ("grad_input", "grad_w"):
+        ref = g[name]
+        rel = np.linalg.norm(out[name] - ref) / np.linalg.norm(ref)
+        assert rel < 1e-3, (name, rel)
+
+
+def test_flinearq_backward_batched_nq(golden):
+    """3-D input with the training script's defaults on all four operands (nq, sawb, nq, sawb): one
+    scale per token of each sample for g_x, one per sample and output channel for g_w."""
+    g = golden("flinearq_batched_nq")
+    n_l, sel = oc.selection_from_matrix(g["p"])
+    x_q, s_x = oc.abc_compress_batched(g["x"], n_l, sel, 8, None, "sawb")
+    O = g["w"].shape[0]
+    out = oc.linear_backward_batched(g["go"], g["w"], x_q, s_x, n_o=oc.block_order(O), n_l=n_l, sel=sel,
+                                     u_go=g["u_go"], u_gw=g["u_gw"], w_mode="sawb", gx_per_token=True, gw_per_channel=True)
+    assert out["s_go"].shape == g["go"].shape[:2] and out["s_gw"].shape == (g["go"].shape[0], O)
+    for name in ("grad_input", "grad_w"):
+        ref = g[name]
+        rel = np.linalg.norm(out[name] - ref) / np.linalg.norm(ref)
+        assert rel < 1e-3, (name, rel)
+    # per-tensor scales on the same noise give a measurably different result
+    flat = oc.linear_backward_batched(g["go"], g["w"], x_q, s_x, n_o=oc.block_order(O), n_l=n_l, sel=sel,
+                                      u_go=g["u_go"], u_gw=g["u_gw"], w_mode="sawb")
+    assert np.linalg.norm(flat["grad_input"] - g["grad_input"]) > 10 * np.linalg.norm(out["grad_input"] - g["grad_input"])
+
+
 def test_int4_pack_roundtrip():
     rng = np.random.default_rng(0)
     c = rng.integers(-7, 8, size=(5, 32))
