@@ -408,18 +408,27 @@ def hla_expand(y: torch.Tensor, order: int, sel: Sequence[int], scale: float, ou
 
 
 def linear_backward_lowrank_gx(go: torch.Tensor, w: torch.Tensor, order: int, sel: Sequence[int], q_gx: Quant, q_w: Quant,
-                               status: Optional[torch.Tensor] = None) -> torch.Tensor:
+                               status: Optional[torch.Tensor] = None, batch: int = 1) -> torch.Tensor:
     """grad_input of the schemes that project grad_output along the TOKENS before the g_x product
     (transform_scheme low_rank / gilr_gwh, utils/quant_matmul.py:229-234, 261-266, 334-337):
-    grad_x = expand( (Q(HLA(go)) . Q(w)) * s_go * s_w ) / order, the weight left untransformed."""
+    grad_x = expand( (Q(HLA(go)) . Q(w)) * s_go * s_w ) / order, the weight left untransformed.
+    ``batch`` > 1: ``go`` holds that many samples of L / batch tokens each (a multiple of ``order``, so
+    the projection blocks stay within a sample) and the quantiser takes one scale per sample."""
     _require_cuda(go, w)
     L, O = go.shape
     I = w.shape[1]
+    if batch > 1 and (L % batch or (L // batch) % order):
+        raise ValueError("tokens per sample must be a multiple of the low-rank order %d" % order)
     go_lr = hla_project(go, order, sel)                                     # [L', O] float32, natural layout
-    q_go, s_go = row_ht_quant(go_lr, 1, q_gx)
+    rows_per_scale = 1
+    if batch > 1 and q_gx.scale == "tensor":
+        q_go, s_go = row_ht_quant_batched(go_lr.view(batch, -1, O), 1, q_gx)
+        rows_per_scale = go_lr.shape[0] // batch
+    else:
+        q_go, s_go = row_ht_quant(go_lr, 1, q_gx)
     q_w_t, s_w, _ = col_ht_quant(w, 1, [0], _one_per_byte(q_w), "natural")  # [I, O] codes, no transform
     gi_lr = gemm_i8(q_go, q_gx.storage, q_w_t, "int8", go_lr.shape[0], I, O, s_go, s_w, 1.0, torch.float32, status=status,
-                    a_rows_per_scale=1)
+                    a_rows_per_scale=rows_per_scale)
     return hla_expand(gi_lr, order, sel, 1.0 / order, go.dtype)
 
 

@@ -247,9 +247,8 @@ class FLinearQ(Function):
             order_o = int(h_out.shape[0])
         cfg = ops.LinearConfig(order_o=order_o, order_l=n_l, sel_l=sel, q_x=q_x)
         ctx.per_sample = x.dim() == 3 and getattr(a, "lowRankPreset", None) is None
-        if ctx.per_sample and ctx.gx_basis is not None:
-            raise NotImplementedError("transform_scheme %r with per-sample (3-D) inputs is not built; set args.lowRankPreset "
-                                      "to flatten the batch" % ctx.scheme)
+        if ctx.per_sample and ctx.gx_basis is not None and x.shape[1] % ctx.gx_basis[0]:
+            raise ValueError("token count %d is not a multiple of the low-rank order %d" % (x.shape[1], ctx.gx_basis[0]))
         if ctx.per_sample:
             if x.shape[1] % n_l:
                 raise ValueError("token count %d is not a multiple of the low-rank order %d" % (x.shape[1], n_l))
@@ -297,7 +296,15 @@ class FLinearQ(Function):
                                q_x=ctx.q_x)
         need_gx, need_gw = ctx.needs_input_grad[0], ctx.needs_input_grad[1]
         gx = gw = None
-        if (need_gx or need_gw) and ctx.per_sample:
+        if (need_gx or need_gw) and ctx.per_sample and ctx.gx_basis is not None:
+            if need_gw:
+                _, gw = ops.linear_backward_batched(go, w.detach(), x_q_t, scale_x, cfg, need_gx=False, need_gw=True)
+            if need_gx:
+                n_x, sel_x = ctx.gx_basis
+                B, L, O = go.shape
+                gx = ops.linear_backward_lowrank_gx(go.view(B * L, O), w.detach(), n_x, sel_x, q_gx, q_w, batch=B)
+                gx = gx.view(B, L, -1)
+        elif (need_gx or need_gw) and ctx.per_sample:
             gx, gw = ops.linear_backward_batched(go, w.detach(), x_q_t, scale_x, cfg, need_gx=need_gx, need_gw=need_gw)
         elif ctx.gx_basis is not None:
             if need_gw:

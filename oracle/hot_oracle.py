@@ -402,6 +402,17 @@ def abc_compress_batched(x: np.ndarray, n_l: int, sel: np.ndarray, bits: int, u,
     return np.stack([o[0] for o in outs]), np.array([o[1] for o in outs], dtype=F32)
 
 
+def grad_input_lowrank_batched(go, w, *, n: int, sel, bits_gx: int = 4, bits_w: int = 4, u_go=None, u_w=None,
+                               gx_per_token: bool = False, w_mode: str = "stoch", exact_matmul: bool = True):
+    """grad_input_lowrank on go [B, L, O]: projection, quantiser (one scale per sample) and expansion
+    run per sample; the weight is 2-D and is quantised once.  Returns grad_input [B, L, I]."""
+    go = np.asarray(go, dtype=F32)
+    outs = [grad_input_lowrank(go[b], w, n=n, sel=sel, bits_gx=bits_gx, bits_w=bits_w, u_go=_sample(u_go, b), u_w=u_w,
+                               gx_per_token=gx_per_token, w_mode=w_mode, exact_matmul=exact_matmul)["grad_input"]
+            for b in range(go.shape[0])]
+    return np.stack(outs).astype(F32)
+
+
 def linear_backward_batched(go, w, x_q, s_x, *, n_o: int, n_l: int, sel, bits_gx: int = 4, bits_w: int = 4,
                             bits_gw: int = 8, u_go=None, u_w=None, u_gw=None, w_mode: str = "stoch",
                             gx_per_token: bool = False, gw_per_channel: bool = False, exact_matmul: bool = True):

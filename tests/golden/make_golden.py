@@ -171,7 +171,70 @@ def main(ref_root: str, out_dir: str):
     batched(ref_args, hm, qm, out_dir)
     scheme_hadamard(ref_args, hm, qm, out_dir)
     schemes_token_lowrank(ref_args, hm, qm, out_dir)
+    schemes_token_lowrank_batched(ref_args, hm, qm, out_dir)
     print("golden vectors written to", out_dir)
+
+
+def _per_sample(fn_bwd):
+    """What torch.vmap over dim 0 of a reference ``*_BWD`` quantiser computes, as a loop (the explicit
+    uniforms cannot be fed to torch.bernoulli inside vmap): per-sample results stacked."""
+    def f(x, bits, is_batched):
+        if not is_batched:
+            return fn_bwd(x, bits)
+        outs = [fn_bwd(x[b], bits) for b in range(x.shape[0])]
+        return torch.stack([o[0] for o in outs]), torch.stack([o[1] for o in outs])
+    return f
+
+
+def schemes_token_lowrank_batched(ref_args, hm, qm, out_dir: str):
+    """The token-low-rank schemes on a 3-D input [B, L, I]: projection and expansion run along the
+    tokens of each sample, every quantiser of a batched tensor takes one scale per sample."""
+    T = torch.from_numpy
+    B, L, O, I = 2, 96, 64, 48
+    for scheme, seed in (("low_rank", 20250326), ("gilr_gwh", 20250327)):
+        rng = np.random.default_rng(seed)
+        ref_args.transform_scheme = scheme
+        ref_args.TransformGogi = ref_args.TransformWgt = ref_args.TransformGogw = ref_args.TransformInput = True
+        ref_args.GogiQuantBit, ref_args.weightQuantBit, ref_args.GogwQuantBit, ref_args.actQuantBit = 4, 4, 8, 8
+        ref_args.quantBWDGogi = ref_args.quantBWDWgt = ref_args.quantBWDGogw = ref_args.quantBWDAct = "stoch"
+        ref_args.quantAuto = False
+        xx = rng.standard_normal((B, L, I)).astype(np.float32)
+        xx[1] *= 4.0
+        ww = ((rng.random((O, I)) * 2 - 1) / np.sqrt(I)).astype(np.float32)
+        go = (rng.standard_normal((B, L, O)) * 1e-3).astype(np.float32)
+        go[0] *= 5.0
+        lr = hm.make_WHT(L, 50)
+        had = hm.make_hadamard(L)
+        if scheme == "low_rank":
+            h_out, h_bs = torch.zeros((1, 1)), torch.tensor(lr, dtype=torch.float32)
+            Lx = Lw = L * lr.shape[0] // lr.shape[1]
+        else:
+            h_out, h_bs = torch.tensor(lr, dtype=torch.float32), torch.tensor(had, dtype=torch.float32)
+            Lx = Lw = L
+        Lg = L * lr.shape[0] // lr.shape[1]
+        u_x = rng.random((B, Lx, I), dtype=np.float32)
+        u_go = rng.random((B, Lg, O), dtype=np.float32)
+        u_w = rng.random((O, I), dtype=np.float32)
+        u_gw = rng.random((B, O, Lw), dtype=np.float32)
+        xt = T(xx).requires_grad_(True)
+        wt = T(ww).requires_grad_(True)
+        keep = qm.stoch_quantizer
+        qm.stoch_quantizer = _per_sample(qm.stoch_quantizer_BWD)
+        try:
+            with NoiseQueue() as nq:
+                nq.queue += [T(u_x[b]) for b in range(B)] + [T(u_go[b]) for b in range(B)] + [T(u_w)] + \
+                            [T(u_gw[b]) for b in range(B)]
+                y = qm.FLinearQ.apply(xt, wt, h_out, h_bs, "layer")
+                saved = y.grad_fn.saved_tensors
+                y.backward(T(go))
+                assert not nq.queue
+        finally:
+            qm.stoch_quantizer = keep
+            ref_args.transform_scheme = "gih_gwlr"
+        f = dict(x=xx, w=ww, go=go, lowrank=lr.astype(np.int8), hadamard=had.astype(np.int8), u_x=u_x, u_go=u_go, u_w=u_w,
+                 u_gw=u_gw, x_q=saved[0].numpy(), scale_x=saved[4].numpy(), grad_input=xt.grad.numpy(),
+                 grad_w=wt.grad.numpy())
+        np.savez_compressed(os.path.join(out_dir, "flinearq_%s_batched.npz" % scheme), **f)
 
 
 def schemes_token_lowrank(ref_args, hm, qm, out_dir: str):

@@ -171,6 +171,51 @@ def test_hq_linear_token_lowrank_schemes(hot, scheme):
         assert rel < 1e-3, (name, rel)
 
 
+@pytest.mark.parametrize("scheme", ["low_rank", "gilr_gwh"])
+def test_hq_linear_token_lowrank_schemes_3d(hot, scheme):
+    """The token-low-rank schemes on a [B, L, I] input: projection, scales and expansion per sample;
+    bit for bit against the oracle with nearest rounding, and against the reference's own 3-D run."""
+    import os
+    from hot_b200 import ops
+    args, qm = hot
+    args.transform_scheme = scheme
+    args.lowRankPreset = None
+    args.quantBWDGogi = args.quantBWDWgt = args.quantBWDGogw = args.quantBWDAct = "int"
+    torch.manual_seed(8)
+    B, L, I, O = 3, 192, 64, 96
+    lin = qm.HQ_Linear(I, O, bias=False).cuda()
+    x = torch.randn(B, L, I, device="cuda") * torch.tensor([1.0, 4.0, 0.3], device="cuda").view(B, 1, 1)
+    x.requires_grad_(True)
+    go = torch.randn(B, L, O, device="cuda") * 1e-3 * torch.tensor([2.0, 0.5, 6.0], device="cuda").view(B, 1, 1)
+    lin(x).backward(go)
+    n_x, sel_x = oc.wht_selection(L, 50)
+    n_w, sel_w = (n_x, sel_x) if scheme == "low_rank" else (16, np.arange(16))
+    xq, sx = oc.abc_compress_batched(x.detach().cpu().numpy(), n_w, sel_w, 8, None, "int")
+    wn, gon = lin.weight.detach().cpu().numpy(), go.cpu().numpy()
+    ref_gx = oc.grad_input_lowrank_batched(gon, wn, n=n_x, sel=sel_x, w_mode="int")
+    ref_gw = oc.linear_backward_batched(gon, wn, xq, sx, n_o=1, n_l=n_w, sel=sel_w, w_mode="int")["grad_w"]
+    assert np.array_equal(x.grad.cpu().numpy(), ref_gx)
+    assert np.array_equal(lin.weight.grad.cpu().numpy(), ref_gw)
+    # the reference's 3-D run of this scheme (explicit noise)
+    g = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "flinearq_%s_batched.npz" % scheme))
+    dev = lambda a: torch.from_numpy(np.ascontiguousarray(a)).cuda()
+    q = lambda bits, st, u: ops.Quant(bits, st, "noise", "tensor", 0, 0, dev(u))
+    n_x, sel_x = oc.selection_from_matrix(g["lowrank"])
+    n_w, sel_w = (n_x, sel_x) if scheme == "low_rank" else oc.selection_from_matrix(g["hadamard"])
+    Bg, Lg, Og = g["go"].shape
+    cfg = ops.LinearConfig(order_o=1, order_l=n_w, sel_l=list(sel_w), q_gw=q(8, "int8", g["u_gw"]), q_x=q(8, "int8", g["u_x"]))
+    x_q_t, s_x, _ = ops.abc_compress_batched(dev(g["x"]), cfg)
+    np.testing.assert_allclose(s_x.cpu().numpy(), g["scale_x"], rtol=1e-6)
+    _, gw = ops.linear_backward_batched(dev(g["go"]), dev(g["w"]), x_q_t, s_x, cfg, need_gx=False)
+    gx = ops.linear_backward_lowrank_gx(dev(g["go"]).view(Bg * Lg, Og), dev(g["w"]), n_x, list(sel_x), q(4, "int4", g["u_go"]),
+                                        q(4, "int4", np.ascontiguousarray(g["u_w"])), batch=Bg).view(Bg, Lg, -1)
+    for got, name in ((gx, "grad_input"), (gw, "grad_w")):
+        rel = np.linalg.norm(got.cpu().numpy() - g[name]) / np.linalg.norm(g[name])
+        assert rel < 1e-3, (name, rel)
+    ref_gx = oc.grad_input_lowrank_batched(g["go"], g["w"], n=n_x, sel=sel_x, u_go=g["u_go"], u_w=g["u_w"])
+    assert np.array_equal(gx.cpu().numpy(), ref_gx)
+
+
 def test_hq_linear_3d_takes_one_scale_per_sample(hot):
     """Reference semantics of a [B, L, I] input (no preset): per-sample scales, per-sample low-rank
     projection, grad_weight summed over the batch; nearest rounding makes it reproducible."""

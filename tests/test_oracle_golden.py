@@ -119,6 +119,24 @@ def test_flinearq_backward_token_lowrank_schemes(golden, scheme):
         assert rel < 1e-3, (name, rel)
 
 
+@pytest.mark.parametrize("scheme", ["low_rank", "gilr_gwh"])
+def test_flinearq_backward_token_lowrank_schemes_batched(golden, scheme):
+    """The token-low-rank schemes on a 3-D input: per-sample projection, scales and expansion."""
+    g = golden("flinearq_%s_batched" % scheme)
+    n_x, sel_x = oc.selection_from_matrix(g["lowrank"])
+    n_w, sel_w = (n_x, sel_x) if scheme == "low_rank" else oc.selection_from_matrix(g["hadamard"])
+    x_q, s_x = oc.abc_compress_batched(g["x"], n_w, sel_w, 8, g["u_x"])
+    assert np.array_equal(x_q, g["x_q"].astype(np.int32))
+    np.testing.assert_allclose(s_x, g["scale_x"], rtol=1e-6)
+    gx = oc.grad_input_lowrank_batched(g["go"], g["w"], n=n_x, sel=sel_x, u_go=g["u_go"], u_w=g["u_w"])
+    gw = oc.linear_backward_batched(g["go"], g["w"], x_q, s_x, n_o=1, n_l=n_w, sel=sel_w, u_go=None, u_w=None,
+                                    u_gw=g["u_gw"])["grad_w"]
+    for got, name in ((gx, "grad_input"), (gw, "grad_w")):
+        assert got.shape == g[name].shape
+        rel = np.linalg.norm(got - g[name]) / np.linalg.norm(g[name])
+        assert rel < 1e-3, (name, rel)
+
+
 def test_flinearq_backward_batched(golden):
     """3-D input [B, L, I]: one scale per sample, grad_w summed over the batch (reference run on
     the same tensors, tests/golden/make_golden.py::batched)."""
