@@ -261,11 +261,9 @@ def run_hot(a):
     if rank == 0 and world == 1:
         if not a.no_kernels:
             out["kernels"], out["roofline"], out["fp_backward_bf16_cublas"] = kernel_legs(ops, layers, a, dtype, device, pk, status)
-        out["e2e"] = e2e_leg(layers, a, dtype, device, flops) if a.e2e_steps > 0 else None
         if not a.no_cpu_baseline:
             out["cpu_baseline"] = cpu_baseline(threads=1)
-    elif rank == 0:
-        out["e2e"] = None
+    out["e2e"] = e2e_leg(layers, a, dtype, device, flops, world) if a.e2e_steps > 0 else None   # every rank takes part
     if rank == 0:
         print(json.dumps(out), flush=True)
     if world > 1:
@@ -652,10 +650,11 @@ def config1_leg(ops, device, status):
             "effective_tops": round(4.0 * L * I * O / t_hot / 1e6, 1)}
 
 
-def e2e_leg(layers, a, dtype, device, flops):
+def e2e_leg(layers, a, dtype, device, flops, world=1):
     """The same step through HLQ_backward.backward with Go and X in pinned host memory and both
     gradients copied back, every layer, every step; the copies of neighbouring layers overlap the
     call (two copy streams), as a caller streaming a model through the plugin would arrange it."""
+    import torch.distributed as dist
     import HLQ_backward
     shapes = {}
     for name, i_f, o_f in LAYERS:
@@ -706,12 +705,26 @@ def e2e_leg(layers, a, dtype, device, flops):
         torch.cuda.synchronize(device)
 
     step()
-    t0 = time.perf_counter()
+    # timed on the device: the events sit on the compute stream, which joins both copy streams before
+    # the closing one; with several ranks every rank streams its own shard and the slowest one counts
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize(device)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(comp)
     for _ in range(a.e2e_steps):
         step()
-    dt = (time.perf_counter() - t0) / a.e2e_steps
-    return {"value": round(flops / dt / 1e12, 3), "unit": UNIT, "ms_per_step": round(dt * 1e3, 3),
-            "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h), "api": "HLQ_backward.backward(Go, W, X, 0, 0, 16, False)"}
+    comp.wait_stream(s_in)
+    comp.wait_stream(s_out)
+    e1.record(comp)
+    torch.cuda.synchronize(device)
+    ms = torch.tensor([e0.elapsed_time(e1) / a.e2e_steps], device=device)
+    if world > 1:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    dt = float(ms.item()) * 1e-3
+    return {"value": round(flops * world / dt / 1e12, 3), "unit": UNIT, "ms_per_step": round(dt * 1e3, 3),
+            "h2d_bytes_per_step": int(h2d) * world, "d2h_bytes_per_step": int(d2h) * world,
+            "api": "HLQ_backward.backward(Go, W, X, 0, 0, 16, False)"}
 
 
 # ---------------------------------------------------------------------------------------------
