@@ -51,9 +51,10 @@ def parse():
     p.add_argument("--blocks", type=int, default=12)
     p.add_argument("--dtype", default="bf16", choices=["bf16", "fp32"])
     p.add_argument("--e2e-steps", type=int, default=2)
-    p.add_argument("--gx-storage", default="int4", choices=["int4", "int8"],
+    p.add_argument("--gx-storage", default="auto", choices=["int4", "int8", "auto"],
                    help="how the 4-bit g_x codes of grad_out are stored between the quantiser and the GEMM: packed two per "
-                        "byte and expanded in shared memory (default, what the target asks for), or one per byte")
+                        "byte and expanded in shared memory, one per byte, or (default) the library's policy "
+                        "ops.gx_code_storage: packed where the contraction is longer than 1024")
     p.add_argument("--no-cpu-baseline", action="store_true")
     p.add_argument("--no-kernels", action="store_true", help="skip the per-kernel roofline legs")
     p.add_argument("--sweep", action="store_true",
@@ -159,7 +160,8 @@ def build_layers(ops, tokens, blocks, dtype, device, rank, gx_storage="int4"):
             x = torch.randn((tokens, i_f), device=device, generator=gd).to(dtype)
             call += 4
             cfg = ops.LinearConfig(order_o=biggest_power2_factor_max16(o_f), order_l=order_l, sel_l=sel,
-                                   q_gx=ops.Quant(4, gx_storage, "philox", "tensor", 0, call + 1),
+                                   q_gx=ops.Quant(4, ops.gx_code_storage(4, o_f) if gx_storage == "auto" else gx_storage,
+                                                  "philox", "tensor", 0, call + 1),
                                    q_w=ops.Quant(4, "int4", "philox", "tensor", 0, call + 2),
                                    q_gw=ops.Quant(8, "int8", "philox", "tensor", 0, call + 3),
                                    q_x=ops.Quant(8, "int8", "philox", "tensor", 0, call + 4))
@@ -252,7 +254,7 @@ def run_hot(a):
            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8/int4 codes, int32 accumulate",
            "data": "synthetic", "gpu_launches": n_layers * KERNELS_PER_LAYER * a.steps,
            "config": {"workload": WORKLOAD, "tokens_per_gpu": a.tokens, "layers": n_layers, "tensor_dtype": a.dtype,
-                      "hadamard_order": 16, "low_rank": "8 of 16 (lowest sequency)", "g_x": "INT4 x INT4, per-tensor, Philox stochastic" + ("" if a.gx_storage == "int4" else "; grad_out codes stored one per byte"),
+                      "hadamard_order": 16, "low_rank": "8 of 16 (lowest sequency)", "g_x": "INT4 x INT4, per-tensor, Philox stochastic" + {"int4": "; grad_out codes packed", "int8": "; grad_out codes stored one per byte", "auto": "; grad_out codes packed for qkv and fc1 (contraction > 1024), one per byte for proj and fc2"}[a.gx_storage],
                       "g_w": "INT8 x INT8, per-tensor, Philox stochastic", "activation_buffer": "compressed in forward (not timed)",
                       "cache": "inputs 2.1 GB per GPU, distinct per layer (> 126 MB L2)",
                       "parallelism": "dp%d, grad_w all-reduce (NCCL) per block" % world if world > 1 else "single GPU"}}

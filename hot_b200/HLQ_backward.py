@@ -56,7 +56,7 @@ def backward(Go: torch.Tensor, W: torch.Tensor, X: torch.Tensor, reorder_idx_go=
     rounding = "philox" if stochastic else "nearest"
     cfg = ops.LinearConfig(
         order_o=int(H_size), order_l=order_l, sel_l=sel,
-        q_gx=ops.Quant(4, "int4", rounding, "row" if per_token else "tensor", seed, base + 1),
+        q_gx=ops.Quant(4, ops.gx_code_storage(4, O), rounding, "row" if per_token else "tensor", seed, base + 1),
         q_w=ops.Quant(4, "int4", rounding, "tensor", seed, base + 2),
         q_gw=ops.Quant(8, "int8", rounding, "tensor", seed, base + 3),
         q_x=ops.Quant(8, "int8", rounding, "tensor", seed, base + 4))
@@ -77,7 +77,7 @@ def backward(Go: torch.Tensor, W: torch.Tensor, X: torch.Tensor, reorder_idx_go=
     ev[1].record()
     # both products in one launch where the shapes suit it (else two launches, decided inside)
     gx, gw = ops.gemm_i8_dual(
-        dict(a=q_go, a_storage="int4", b=q_w_t, M=L, N=I, K=O, scale_a=s_go, scale_b=s_w, post=1.0 / int(H_size),
+        dict(a=q_go, a_storage=cfg.q_gx.storage, b=q_w_t, M=L, N=I, K=O, scale_a=s_go, scale_b=s_w, post=1.0 / int(H_size),
              out_dtype=Go.dtype, a_rows_per_scale=1),
         dict(a=q_gw, b=x_q_t, M=O, N=I, K=lp, scale_a=s_gw, scale_b=s_x, post=1.0 / n, out_dtype=Go.dtype), status)
     ev[2].record()

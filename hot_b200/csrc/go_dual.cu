@@ -155,14 +155,14 @@ __device__ __forceinline__ void quantise16_int8_pair(const float2 (&y)[16], cons
 
 // PASS 0: statistics.  PASS 1: quantise (RX / RW: rounding of the g_x / g_w side).
 // FAST: the configuration of the training path (channel order 16, one scale per tensor on both
-// sides, g_x codes packed INT4) with those four choices folded at compile time; otherwise they
-// are read from the parameters.
-template <typename T, int PASS, int RX, int RW, bool FAST>
+// sides; X4: g_x codes packed INT4 or one per byte) with those choices folded at compile time;
+// otherwise they are read from the parameters.
+template <typename T, int PASS, int RX, int RW, bool FAST, bool X4>
 __global__ void __launch_bounds__(kThreads, sizeof(T) == 2 ? 3 : 1) go_dual_kernel(const __grid_constant__ CUtensorMap tmap, DualParams p) {
   const int n_o = FAST ? 16 : p.n_o;
   const bool x_row = FAST ? false : p.x_row != 0;
   const bool w_row = FAST ? false : p.w_row != 0;
-  const bool x_store4 = FAST ? true : p.x_store4 != 0;
+  const bool x_store4 = FAST ? X4 : p.x_store4 != 0;
   extern __shared__ uint8_t smem_raw[];
   // rounded up to 128 bytes by an offset, so that every pointer below is still visibly derived from
   // the shared array and its loads and stores compile to shared-memory instructions
@@ -360,9 +360,9 @@ __global__ void __launch_bounds__(kThreads, sizeof(T) == 2 ? 3 : 1) go_dual_kern
 template <typename T>
 constexpr int smem_bytes() { return 2 * Tile<T>::kBytes + kTC * kStagePitch + 64 + 128; }
 
-template <typename T, int PASS, int RX, int RW, bool FAST>
+template <typename T, int PASS, int RX, int RW, bool FAST, bool X4>
 int launch_pass_as(const CUtensorMap& tmap, const DualParams& p, int grid, cudaStream_t st) {
-  auto kernel = go_dual_kernel<T, PASS, RX, RW, FAST>;
+  auto kernel = go_dual_kernel<T, PASS, RX, RW, FAST, X4>;
   static bool attr_set = false;
   if (!attr_set) {
     HOT_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes<T>()));
@@ -390,8 +390,11 @@ int launch_pass_as(const CUtensorMap& tmap, const DualParams& p, int grid, cudaS
 
 template <typename T, int PASS, int RX, int RW>
 int launch_pass(const CUtensorMap& tmap, const DualParams& p, int grid, cudaStream_t st) {
-  if (p.n_o == 16 && !p.x_row && !p.w_row && p.x_store4) return launch_pass_as<T, PASS, RX, RW, true>(tmap, p, grid, st);
-  return launch_pass_as<T, PASS, RX, RW, false>(tmap, p, grid, st);
+  if (p.n_o == 16 && !p.x_row && !p.w_row) {
+    if (p.x_store4 || PASS == 0) return launch_pass_as<T, PASS, RX, RW, true, true>(tmap, p, grid, st);  // the statistics pass stores no codes
+    return launch_pass_as<T, PASS, RX, RW, true, PASS == 1 ? false : true>(tmap, p, grid, st);
+  }
+  return launch_pass_as<T, PASS, RX, RW, false, true>(tmap, p, grid, st);
 }
 
 template <typename T>

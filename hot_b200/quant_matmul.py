@@ -144,7 +144,7 @@ def _storage(bits: int) -> str:
     return "int4" if bits <= 4 else "int8"
 
 
-def _operand(kind: str, scheme, bits: int, what: str, row_ok: bool) -> ops.Quant:
+def _operand(kind: str, scheme, bits: int, what: str, row_ok: bool, k: int = 1 << 30) -> ops.Quant:
     if scheme == "stoch":
         rounding, scale = "philox", "tensor"
     elif scheme == "int":
@@ -159,7 +159,8 @@ def _operand(kind: str, scheme, bits: int, what: str, row_ok: bool) -> ops.Quant
         raise Exception("%s rounding scheme not implemented: %s" % (what, scheme))
     if not 2 <= int(bits) <= 8:
         raise ValueError("%s: quantBits %r outside [2, 8]" % (what, bits))
-    return ops.Quant(int(bits), _storage(int(bits)), rounding, scale, _seed(), _next_offset())
+    storage = ops.gx_code_storage(int(bits), k) if kind == "gx" else _storage(int(bits))
+    return ops.Quant(int(bits), storage, rounding, scale, _seed(), _next_offset())
 
 
 _BUILT_SCHEMES = ("gih_gwlr", "hadamard", "low_rank", "gilr_gwh")
@@ -286,10 +287,10 @@ class FLinearQ(Function):
                 gw_scheme = pick[a.layer_quant_dict[name + "_gw"]]
             except KeyError as e:
                 raise NotImplementedError("layer_quant_dict entry %s is not built on the native path" % e) from None
-            q_gx = _operand("gx", gx_scheme, a.GogiQuantBit, "GradHo", row_ok=True)
+            q_gx = _operand("gx", gx_scheme, a.GogiQuantBit, "GradHo", row_ok=True, k=go.shape[-1])
             q_gw = _operand("gw", gw_scheme, a.GogiQuantBit, "GradHb", row_ok=True)
         else:
-            q_gx = _operand("gx", a.quantBWDGogi, a.GogiQuantBit, "GradHo", row_ok=True)
+            q_gx = _operand("gx", a.quantBWDGogi, a.GogiQuantBit, "GradHo", row_ok=True, k=go.shape[-1])
             q_gw = _operand("gw", a.quantBWDGogw, a.GogwQuantBit, "GradHb", row_ok=True)
         q_w = _operand("w", a.quantBWDWgt, a.weightQuantBit, "Weight", row_ok=False)
         cfg = ops.LinearConfig(order_o=ctx.order_o, order_l=ctx.order_l, sel_l=ctx.sel, q_gx=q_gx, q_w=q_w, q_gw=q_gw,
