@@ -414,7 +414,8 @@ def run_one_layer(a):
     x = torch.randn((L, i_f), device=device).to(dtype)
     w = ((torch.rand((o_f, i_f), device=device) * 2 - 1) / i_f ** 0.5).to(dtype)
     go = (torch.randn((L, o_f), device=device) * 1e-3).to(dtype)
-    cfg = ops.LinearConfig(order_o=16, order_l=order_l, sel_l=sel)
+    storage = ops.gx_code_storage(4, o_f) if a.gx_storage == "auto" else a.gx_storage   # as the benchmark step stores them
+    cfg = ops.LinearConfig(order_o=16, order_l=order_l, sel_l=sel, q_gx=ops.Quant(4, storage))
     x_q_t, s_x = ops.abc_compress(x, cfg)
     status = torch.zeros(1, dtype=torch.int32, device=device)
     for _ in range(a.calls):
