@@ -415,7 +415,9 @@ __device__ __forceinline__ void store_chunk(const GemmParams& p, int row, bool r
 // the operand loads of both are counted on barriers of the rank-0 CTA, whose MMA thread issues the
 // instructions for the pair and signals "stage free" / "accumulator complete" into both CTAs, and that
 // the rank-1 CTA reports "accumulator drained" / "operand unpacked" to the rank-0 CTA's barriers.
-template <int BN, bool A4, bool B4, bool PAIR>
+// GROUPED: the grouped-scale epilogue (hot_gemm_i8_grouped) as an instantiation of its own, so that the
+// running sums a thread keeps across the groups of a tile share the register file with that epilogue only.
+template <int BN, bool A4, bool B4, bool PAIR, bool GROUPED>
 __global__ void __launch_bounds__(kEpiThreads + 64 + ((A4 || B4) ? kUnpackThreads : 0), 1)
     gemm_i8_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
                    const __grid_constant__ CUtensorMap tma_out, const __grid_constant__ CUtensorMap tma_a2,
@@ -429,7 +431,8 @@ __global__ void __launch_bounds__(kEpiThreads + 64 + ((A4 || B4) ? kUnpackThread
   constexpr uint32_t kTmemCols = tmem_cols(BN);
   constexpr uint32_t kBufStride = kTmemCols / 2;
   constexpr int kShift = (A4 ? 4 : 0) + (B4 ? 4 : 0);
-  constexpr bool kGrouped = BN == 128 && !kUnpack && !PAIR;  // the one instance that carries the grouped-scale epilogue
+  constexpr bool kGrouped = GROUPED;
+  static_assert(!GROUPED || (!kUnpack && !PAIR), "the grouped-scale epilogue takes INT8 operands on single CTAs");
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   uint8_t* sA = smem + L::kOffA;
@@ -726,7 +729,7 @@ __global__ void __launch_bounds__(kEpiThreads + 64 + ((A4 || B4) ? kUnpackThread
       if (!ok) break;
       tc_fence_after();
       const uint32_t t_addr = tmem_base + buf * kBufStride + ((uint32_t)(q * 32) << 16);
-      if (kGrouped && p.group_kb) {
+      if constexpr (kGrouped) {
         // running fp32 sums of this team's chunks live in registers across the groups of a tile
         // sa_row: one scale per (group, row) of A instead of one per group
         const float ga = p.sa_row ? (row_ok ? p.ga[(size_t)seg.group * (size_t)p.M + (size_t)row] : 0.0f) : p.ga[seg.group];
@@ -926,7 +929,7 @@ struct Rider {
   GemmParams p;
 };
 
-template <int BN, bool A4, bool B4, bool PAIR = false>
+template <int BN, bool A4, bool B4, bool PAIR = false, bool GROUPED = false>
 int launch_gemm(const void* a, int64_t lda, const void* b, int64_t ldb, const GemmParams& p, const Plan& plan, cudaStream_t st,
                 const Rider* rider = nullptr) {
   using L = SmemLayout<BN, A4, B4, PAIR>;
@@ -962,7 +965,7 @@ int launch_gemm(const void* a, int64_t lda, const void* b, int64_t ldb, const Ge
       if (rc) return rc;
     }
   }
-  auto kernel = gemm_i8_kernel<BN, A4, B4, PAIR>;
+  auto kernel = gemm_i8_kernel<BN, A4, B4, PAIR, GROUPED>;
   static bool attr_set = false;  // per instantiation
   if (!attr_set) {
     HOT_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kBytes));
@@ -1201,7 +1204,7 @@ extern "C" int hot_gemm_i8_grouped(const void* a, int64_t lda, const void* b, in
   if (sms <= 0) return HOT_ERR_CUDA;
   const int64_t tiles = tiles_for(p.M, p.N, 128);
   const Plan plan{128, false, (unsigned)(tiles < sms ? tiles : sms)};
-  return launch_gemm<128, false, false>(a, lda, b, ldb, p, plan, (cudaStream_t)stream);
+  return launch_gemm<128, false, false, false, true>(a, lda, b, ldb, p, plan, (cudaStream_t)stream);
 }
 
 namespace hot {
