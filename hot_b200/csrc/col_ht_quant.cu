@@ -652,7 +652,6 @@ constexpr int kStaticScratchWords = 16384;  // 64 KiB, resident on every GPU tha
 // code this name is only a handle for cudaGetSymbolAddress; it is not a device address.
 static __device__ __align__(256) uint32_t g_static_scratch[kStaticScratchWords];
 
-constexpr int kMaxDevices = 64;
 uint32_t* g_static_scratch_ptr[kMaxDevices] = {};  // device address per device ordinal, filled on first use
 
 // Device address of g_static_scratch on the CURRENT device.  The first call on a device asks
@@ -689,8 +688,10 @@ extern "C" int hot_col_ht_quant_static(const void* x, int dtype, int64_t rows, i
              (long long)cols, (long long)words, kStaticScratchWords);
   uint32_t* scratch = nullptr;
   if (int rc = static_scratch_for_current_device(&scratch)) return rc;
-  // hot_col_ht_quant zeroes the words it uses (a memset on the stream) before its first kernel,
-  // so whatever the previous call left in the array does not leak into this one
+  // What the previous call left in the array does not leak into this one: in the abs-max modes
+  // (HOT_SCALE_TENSOR, HOT_SCALE_ROW) hot_col_ht_quant zeroes the words it uses with a memset on
+  // the stream before its first kernel; in HOT_SCALE_SAWB mode there is no memset, and every CTA
+  // of the statistics kernel overwrites its own four words before the second kernel reads them
   return hot_col_ht_quant(x, dtype, rows, cols, ldx, order, sel, r, q, logical_layout, codes_t, ld_codes, scales, scratch,
                           stream);
 }

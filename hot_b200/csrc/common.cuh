@@ -6,6 +6,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <atomic>
+
 #include "hot_b200.h"
 
 namespace hot {
@@ -24,6 +26,22 @@ void set_error(const char* fmt, ...);
   } while (0)
 
 int validate_quant(const hot_quant_t* q, const char* who);
+
+// Function attributes (the dynamic shared-memory limit) belong to a device, and host threads may
+// reach a launcher's first call together: one flag per device ordinal per kernel instantiation.
+// Setting an attribute twice is harmless, so the flag only has to be published after the call.
+constexpr int kMaxDevices = 64;
+struct PerDeviceOnce {
+  std::atomic<unsigned char> done[kMaxDevices];
+  // Returns the current device ordinal (or -1 on error) and whether it was already marked.
+  int current(bool* was_done) {
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return -1;
+    *was_done = done[dev].load(std::memory_order_acquire) != 0;
+    return dev;
+  }
+  void mark(int dev) { done[dev].store(1, std::memory_order_release); }
+};
 
 // ---- quantiser parameters as the kernels see them -------------------------------------
 struct QuantDev {

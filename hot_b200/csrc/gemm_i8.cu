@@ -966,8 +966,11 @@ int launch_gemm(const void* a, int64_t lda, const void* b, int64_t ldb, const Ge
     }
   }
   auto kernel = gemm_i8_kernel<BN, A4, B4, PAIR, GROUPED>;
-  static bool attr_set = false;  // per instantiation
-  if (!attr_set) {
+  static PerDeviceOnce attr_set;  // per instantiation and device
+  bool have_attr = false;
+  const int dev = attr_set.current(&have_attr);
+  if (dev < 0) HOT_FAIL(HOT_ERR_CUDA, "gemm_i8: cannot query the current CUDA device");
+  if (!have_attr) {
     HOT_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kBytes));
     if (A4 || B4) {
       // the register hand-over (unpack warp groups 96 -> 40, epilogue warp groups 96 -> 152) only balances
@@ -976,7 +979,7 @@ int launch_gemm(const void* a, int64_t lda, const void* b, int64_t ldb, const Ge
       HOT_CUDA(cudaFuncGetAttributes(&fa, kernel));
       if (fa.numRegs < 96) HOT_FAIL(HOT_ERR_UNSUPPORTED, "gemm_i8: kernel built with %d registers per thread, 96 expected", fa.numRegs);
     }
-    attr_set = true;
+    attr_set.mark(dev);
   }
   constexpr unsigned kThreads = kEpiThreads + 64 + ((A4 || B4) ? kUnpackThreads : 0);
   cudaLaunchConfig_t cfg = {};

@@ -363,10 +363,13 @@ constexpr int smem_bytes() { return 2 * Tile<T>::kBytes + kTC * kStagePitch + 64
 template <typename T, int PASS, int RX, int RW, bool FAST, bool X4>
 int launch_pass_as(const CUtensorMap& tmap, const DualParams& p, int grid, cudaStream_t st) {
   auto kernel = go_dual_kernel<T, PASS, RX, RW, FAST, X4>;
-  static bool attr_set = false;
-  if (!attr_set) {
+  static PerDeviceOnce attr_set;  // per instantiation and device
+  bool have_attr = false;
+  const int dev = attr_set.current(&have_attr);
+  if (dev < 0) HOT_FAIL(HOT_ERR_CUDA, "go_dual_quant: cannot query the current CUDA device");
+  if (!have_attr) {
     HOT_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes<T>()));
-    attr_set = true;
+    attr_set.mark(dev);
   }
   if (PASS == 1) {
     // may start while the statistics pass (the launch before it on this stream) is still draining

@@ -1,6 +1,8 @@
 // The HOT backward of one linear layer as a sequence of the three kernels, plus the
 // forward-side activation-buffer compression.  All intermediates live in a caller-owned
 // workspace; nothing here allocates or synchronises.
+#include <mutex>
+
 #include "common.cuh"
 
 namespace hot {
@@ -20,12 +22,14 @@ struct SideStream {
   cudaStream_t stream = nullptr;
   cudaEvent_t fork = nullptr, join = nullptr;
 };
-SideStream g_side[64];
+SideStream g_side[kMaxDevices];
+std::mutex g_side_mutex;  // guards creation only; the streams and events themselves are used by one caller at a time
 
 int side_stream(SideStream** out) {
   int dev = -1;
   HOT_CUDA(cudaGetDevice(&dev));
-  if (dev < 0 || dev >= 64) HOT_FAIL(HOT_ERR_UNSUPPORTED, "hot_linear_backward: device ordinal %d", dev);
+  if (dev < 0 || dev >= kMaxDevices) HOT_FAIL(HOT_ERR_UNSUPPORTED, "hot_linear_backward: device ordinal %d", dev);
+  std::lock_guard<std::mutex> lock(g_side_mutex);
   SideStream& s = g_side[dev];
   if (!s.stream) {
     cudaStream_t st;
@@ -142,6 +146,10 @@ extern "C" int hot_linear_backward(const void* go, int64_t ldgo, const void* w, 
   if (((uintptr_t)workspace) % kAlign != 0) HOT_FAIL(HOT_ERR_ARG, "hot_linear_backward: workspace must be 256-byte aligned");
   if (cfg->order_o < 1 || cfg->order_o > 16 || O % cfg->order_o != 0)
     HOT_FAIL(HOT_ERR_ARG, "hot_linear_backward: order_o %d does not divide O = %lld", cfg->order_o, (long long)O);
+  // the scratch plan reserves abs-max words for the two grad_out quantisers; the two-moment clip needs
+  // words per CTA instead and is what the reference offers for the weight and the activation only
+  if (cfg->q_gx.scale_mode == HOT_SCALE_SAWB || cfg->q_gw.scale_mode == HOT_SCALE_SAWB)
+    HOT_FAIL(HOT_ERR_UNSUPPORTED, "hot_linear_backward: HOT_SCALE_SAWB is for the weight and the activation buffer, not for grad_out");
   uint8_t* base = (uint8_t*)workspace;
   // scratch words: [0, 64) per-tensor maxima of the three quantiser calls and the weight's,
   // then per-token (L) and per-channel (O) maxima

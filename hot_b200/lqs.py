@@ -4,7 +4,9 @@ grad_output is quantised with one scale per tensor or one per token on the g_x p
 
 The rule, unchanged: quantise the UN-transformed first-batch grad_output to 4 bits with the
 per-tensor stochastic quantiser and with the per-token one; per-token wins for g_x only if it
-cuts the L2 error by more than half; g_w always keeps the per-tensor quantiser.
+cuts the L2 error by more than half; g_w always keeps the per-tensor quantiser.  A 3-D
+grad_output [B, L, O] (every linear of a ViT block) is quantised "batched", as the reference
+calls it there (ViT_main.py:190-201): the per-tensor quantiser then takes one scale per sample.
 """
 from __future__ import annotations
 
@@ -13,7 +15,7 @@ from typing import Callable, Dict, Iterable, Optional
 import torch
 import torch.nn as nn
 
-from .quant_matmul import HQ_Linear, _args, norm_quantizer, stoch_quantizer
+from .quant_matmul import HQ_Conv2d, HQ_Linear, _args, norm_quantizer, stoch_quantizer
 
 quantScheme_gx = ["stoch_quantizer", "norm_quantizer"]
 
@@ -28,7 +30,7 @@ class FirstBatchCapture:
 
     def attach(self, model: nn.Module) -> "FirstBatchCapture":
         for name, layer in model.named_modules():
-            if isinstance(layer, HQ_Linear):
+            if isinstance(layer, (HQ_Linear, HQ_Conv2d)):   # the reference hooks both (ViT_main.py:51-56)
                 self._handles.append(layer.register_full_backward_hook(self._hook(name)))
         return self
 
@@ -45,16 +47,28 @@ class FirstBatchCapture:
 
 
 def select_quantizer(grad_out: torch.Tensor, bits: int = 4):
-    """(gx_name, gw_name, err_stoch, err_norm) for one layer's captured grad_output."""
-    g = grad_out.reshape(-1, grad_out.shape[-1]).float().contiguous()
+    """(gx_name, gw_name, err_stoch, err_norm) for one layer's captured grad_output
+    (ViT_main.py:183-211).  3-D [B, L, O]: batched quantisers, one scale per sample for the
+    per-tensor one, error against q * s[:, None, None].  2-D: one scale.  4-D [B, C, H, W] (a
+    convolution's gradient, which the reference does not treat as batched): one scale for the
+    per-tensor quantiser and one per position (b, h, w) over the channels for the per-token one."""
+    g = grad_out.float()
+    if g.dim() == 4:
+        g = g.permute(0, 2, 3, 1).reshape(-1, g.shape[1])
+    elif g.dim() not in (2, 3):
+        g = g.reshape(-1, g.shape[-1])
+    g = g.contiguous()
+    is_batched = g.dim() == 3
     choice_gx = choice_gw = None
     min_qerror = 9999.0
     errs = []
     for q_func in quantScheme_gx:
         if q_func == "stoch_quantizer":
-            q_grad, s_grad = stoch_quantizer(g, bits, False)
+            q_grad, s_grad = stoch_quantizer(g, bits, is_batched)
+            if is_batched:
+                s_grad = s_grad.unsqueeze(1).unsqueeze(2)
         else:
-            q_grad, s_grad = norm_quantizer(g, bits, False)
+            q_grad, s_grad = norm_quantizer(g, bits, is_batched)
         qerror = float(torch.dist(g, q_grad * s_grad))
         errs.append(qerror)
         if qerror < min_qerror and q_func != "norm_quantizer":
@@ -96,13 +110,16 @@ def calibrate(model: nn.Module, batches: Iterable, loss_fn: Callable, optimizer:
 
 
 def _plain_linear_mode(model: nn.Module, on: bool, saved=None):
-    """Temporarily route HQ_Linear.forward through nn.Linear.forward (full precision)."""
+    """Temporarily route HQ_Linear / HQ_Conv2d forward through nn.Linear / nn.Conv2d (full precision)."""
     if on:
         saved = []
         for m in model.modules():
             if isinstance(m, HQ_Linear):
                 saved.append(m)
                 m.forward = nn.Linear.forward.__get__(m, nn.Linear)
+            elif isinstance(m, HQ_Conv2d):
+                saved.append(m)
+                m.forward = nn.Conv2d.forward.__get__(m, nn.Conv2d)
         return saved
     for m in saved or []:
         m.__dict__.pop("forward", None)

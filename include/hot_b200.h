@@ -154,15 +154,21 @@ size_t hot_col_ht_quant_scratch_words(int dtype, int64_t rows, int64_t cols, int
  * The abs-max words live in a 64 KiB array inside the library's device image instead, which
  * every GPU that loads the library carries until the process exits.
  *   - Same arguments, results and errors as hot_col_ht_quant, minus absmax_ws.
- *   - Limit: HOT_SCALE_ROW needs one word per column, so cols <= 16384 in that mode (any cols in
- *     HOT_SCALE_TENSOR mode); beyond it the call fails with HOT_ERR_UNSUPPORTED and says so.
+ *   - Limit: the array holds 16384 words.  HOT_SCALE_TENSOR needs one (any size goes);
+ *     HOT_SCALE_ROW needs one per column, so cols <= 16384; HOT_SCALE_SAWB needs four per CTA of
+ *     the statistics kernel plus four, i.e. hot_col_ht_quant_scratch_words(...) <= 16384 (about
+ *     4095 CTAs: in bf16 with order 16, 12608 x 3072 fits and 50432 x 3072 does not).  Beyond the limit the call
+ *     fails with HOT_ERR_UNSUPPORTED and says so.
  *   - It allocates nothing (no cudaMalloc / cudaFree / allocating library call).  The first call
  *     on each device looks up the array's device address; make that first call outside any
- *     stream capture, with the target device current.
- *   - All calls on a device share the one array.  Each call clears the words it uses on its
- *     stream before using them, so calls that run one after another are independent; calls
- *     that can overlap on the GPU (different streams, no ordering between them) race on it and
- *     must be serialised by the caller.
+ *     stream capture.  The device of `stream` must be the current device on EVERY call: the
+ *     address is chosen by the current device.
+ *   - All calls on a device share the one array, which keeps the last call's contents.  In the
+ *     abs-max modes each call clears the words it uses on its stream before using them; in
+ *     HOT_SCALE_SAWB mode every word that is read was written by the same call's first kernel.
+ *     So calls that run one after another are independent; calls that can overlap on the GPU
+ *     (different streams, no ordering between them) race on it and must be serialised by the
+ *     caller.
  * This entry point has no counterpart in the reference.
  */
 int hot_col_ht_quant_static(const void* x, int dtype, int64_t rows, int64_t cols, int64_t ldx, int order,
@@ -312,6 +318,10 @@ int hot_go_dual_quant(const void* go, int64_t L, int64_t O, int64_t ldgo, const 
  *   grad_w [O, I] = (Q(HLA(go))^T . x_q) * s_gw * s_x / order_l
  * go [L, O] pitch ldgo, w [O, I] pitch ldw (elements); x_q_t / scale_x from hot_abc_compress.
  * status_word: device word, non-zero after the call completes if a device-side wait ran out.
+ * cfg->q_gx / q_gw take HOT_SCALE_TENSOR or HOT_SCALE_ROW (HOT_SCALE_SAWB is for q_w and q_x).
+ * The weight is quantised on a helper stream the library keeps per device (one stream and one
+ * fork/join event pair): calls on one device must come from one host thread and one stream at a
+ * time; the first call on a device creates them and should be made outside stream capture.
  * Stands in for FLinearQ.backward (utils/quant_matmul.py:214-348) and for backward_cuda
  * (cuda_measure/HLQ_backward_kernel.cu:457-737).
  */

@@ -460,12 +460,22 @@ def lqs_select(grad_out: np.ndarray, u_stoch: np.ndarray, u_norm: np.ndarray, bi
     """Per-layer choice between per-tensor ('stoch_quantizer') and per-token
     ('norm_quantizer') quantisation of grad_out: the per-token quantiser is taken for
     g_x only when it cuts the per-tensor L2 error by more than half; g_w always keeps
-    'stoch_quantizer'.  Returns (gx_name, gw_name, err_stoch, err_norm)."""
+    'stoch_quantizer'.  A 3-D grad_out [B, L, O] is quantised "batched", as the
+    calibration loop does (ViT_main.py:190-201): the per-tensor quantiser takes one scale
+    per sample and the error is the distance to q * s[:, None, None]; the per-token
+    quantiser's rows are the tokens of every sample either way.  Returns (gx_name,
+    gw_name, err_stoch, err_norm)."""
     g = np.asarray(grad_out, dtype=F32)
-    q, s = quant_tensor(g, bits, u_stoch)
-    e_st = float(np.sqrt(np.sum((g.astype(np.float64) - (q.astype(F32) * s).astype(np.float64)) ** 2)))
-    qn, sn = quant_rows(g, bits, u_norm)
-    e_nq = float(np.sqrt(np.sum((g.astype(np.float64) - (qn.astype(F32) * sn[:, None]).astype(np.float64)) ** 2)))
+    if g.ndim == 3:
+        deq = np.stack([(lambda q, s: q.astype(F32) * s)(*quant_tensor(g[b], bits, _sample(u_stoch, b)))
+                        for b in range(g.shape[0])])
+    else:
+        q, s = quant_tensor(g, bits, u_stoch)
+        deq = q.astype(F32) * s
+    e_st = float(np.sqrt(np.sum((g.astype(np.float64) - deq.astype(np.float64)) ** 2)))
+    g2 = g.reshape(-1, g.shape[-1])
+    qn, sn = quant_rows(g2, bits, None if u_norm is None else np.asarray(u_norm).reshape(g2.shape))
+    e_nq = float(np.sqrt(np.sum((g2.astype(np.float64) - (qn.astype(F32) * sn[:, None]).astype(np.float64)) ** 2)))
     gx = "stoch_quantizer"
     if e_nq < e_st and (e_st - e_nq) > e_st * 0.5:
         gx = "norm_quantizer"

@@ -2,7 +2,10 @@
 
 Usage (in a container where the reference checkout is mounted):
 
-    python tests/golden/make_golden.py /path/to/reference
+    python tests/golden/make_golden.py /path/to/reference [section ...]
+
+With section names (``core``, ``lqs_batched``, ``precision``, ``conv``) only those files are
+rewritten; without, all of them.
 
 The reference's ``args.py`` imports ``utils/plot.py`` which needs matplotlib; three
 empty stand-in modules are registered before the import so that ``args``,
@@ -56,8 +59,15 @@ class NoiseQueue:
         return (u < p).to(p.dtype)
 
 
-def main(ref_root: str, out_dir: str):
+def main(ref_root: str, out_dir: str, only=()):
     ref_args, hm, qm = _import_reference(ref_root)
+    extra = {"lqs_batched": lqs_batched, "precision": precision_schedule, "conv": conv2d}
+    for name, fn in extra.items():
+        if not only or name in only:
+            fn(ref_args, hm, qm, out_dir)
+    if only and "core" not in only:
+        print("golden vectors written to", out_dir, "(sections: %s)" % ", ".join(only))
+        return
     rng = np.random.default_rng(20250321)
     T = torch.from_numpy
 
@@ -435,5 +445,98 @@ def batched(ref_args, hm, qm, out_dir: str):
     np.savez_compressed(os.path.join(out_dir, "flinearq_batched_nq.npz"), **f)
 
 
+def _gih_gwlr(ref_args, scheme="stoch"):
+    ref_args.transform_scheme = "gih_gwlr"
+    ref_args.TransformGogi = ref_args.TransformWgt = ref_args.TransformGogw = ref_args.TransformInput = True
+    ref_args.GogiQuantBit, ref_args.weightQuantBit, ref_args.GogwQuantBit, ref_args.actQuantBit = 4, 4, 8, 8
+    ref_args.quantBWDGogi = ref_args.quantBWDWgt = ref_args.quantBWDGogw = ref_args.quantBWDAct = scheme
+    ref_args.quantAuto = False
+
+
+def lqs_batched(ref_args, hm, qm, out_dir: str):
+    """The selection rule on 3-D first-batch gradients [B, L, O], as the calibration loop applies it
+    (ViT_main.py:190-211): both quantisers are called with is_batched=True, so the per-tensor
+    quantiser takes one scale per SAMPLE and the error is torch.dist against q * s[:, None, None].
+    Case "spread": samples of very different magnitude, where one scale for the whole batch would be
+    poor but one per sample is not, so the per-token quantiser must not win.  Case "outlier": one
+    outlier token in every sample, where it does."""
+    rng = np.random.default_rng(20250328)
+    T = torch.from_numpy
+    out = {}
+    for tag in ("spread", "outlier"):
+        g = (rng.standard_normal((6, 24, 48)) * 1e-3).astype(np.float32)
+        if tag == "spread":
+            g *= np.array([1.0, 1.0, 1.0, 1.0, 1.0, 8.0], dtype=np.float32)[:, None, None]
+        else:
+            g[:, 5] *= 40.0
+        u1 = rng.random(g.shape, dtype=np.float32)
+        u2 = rng.random(g.shape, dtype=np.float32)
+        errs = []
+        with NoiseQueue() as nq:
+            nq.queue += [T(u1[b]) for b in range(g.shape[0])] + [T(u2[b]) for b in range(g.shape[0])]
+            qg, sg = _per_sample(qm.stoch_quantizer_BWD)(T(g), 4, True)
+            errs.append(float(torch.dist(T(g), qg * sg.unsqueeze(1).unsqueeze(2))))
+            qg = torch.stack([qm.norm_quantizer_BWD(T(g)[b], 4) for b in range(g.shape[0])])
+            errs.append(float(torch.dist(T(g), qg * 1.)))
+            assert not nq.queue
+        choice = "stoch_quantizer"
+        if errs[1] < errs[0] and (errs[0] - errs[1]) > errs[0] * 0.5:
+            choice = "norm_quantizer"
+        out[tag + "_g"], out[tag + "_u1"], out[tag + "_u2"] = g, u1, u2
+        out[tag + "_errs"] = np.array(errs)
+        out[tag + "_gx"] = np.array(choice)
+    np.savez_compressed(os.path.join(out_dir, "lqs_batched.npz"), **out)
+
+
+def precision_schedule(ref_args, hm, qm, out_dir: str):
+    """utils/utils.py:149-159 run over epochs 0..11 for several flag settings: the four bit widths
+    after each call."""
+    import utils.utils as uu
+    cases = [  # (quantBWDGogi, quantBWDWgt, max_bit, min_bit, milestones)
+        ("stoch", "stoch", 8, 4, (3, 6)), ("int", "sawb", 8, 4, (2, 4, 5)), ("nq", "int", 8, 2, (1, 2, 3, 9)),
+        ("nq", "sawb", 8, 4, (5,)), ("stoch", "int", 6, 3, (4, 8)), ("stoch", "stoch", 8, 4, ())]
+    keep = {k: getattr(ref_args, k) for k in ("GogiQuantBit", "weightQuantBit", "GogwQuantBit", "actQuantBit",
+                                              "quantBWDGogi", "quantBWDWgt")}
+    table = np.zeros((len(cases), 12, 4), dtype=np.int32)
+    for ci, (gogi, wgt, mx, mn, ms) in enumerate(cases):
+        ref_args.quantBWDGogi, ref_args.quantBWDWgt = gogi, wgt
+        ref_args.GogiQuantBit, ref_args.weightQuantBit, ref_args.GogwQuantBit, ref_args.actQuantBit = 4, 4, 8, 8
+        for epoch in range(12):
+            uu.precision_scheduler(epoch, mx, mn, list(ms))
+            table[ci, epoch] = (ref_args.GogiQuantBit, ref_args.weightQuantBit, ref_args.GogwQuantBit, ref_args.actQuantBit)
+    for k, v in keep.items():
+        setattr(ref_args, k, v)
+    np.savez_compressed(os.path.join(out_dir, "precision_scheduler.npz"), bits=table,
+                        cases=np.array([("%s,%s,%d,%d,%s" % (c[0], c[1], c[2], c[3], " ".join(map(str, c[4])))) for c in cases]))
+
+
+def conv2d(ref_args, hm, qm, out_dir: str):
+    """HQ_Conv2d forward + backward (utils/quant_matmul.py:426-488) with the deterministic quantiser
+    on all four operands (int_quantizer, vmapped per sample by the reference itself, so no random
+    draws are involved): a stride-16 patch embedding (16 tokens per image, basis 10 of 16) and a 3x3
+    convolution with padding 1 (64 positions per image, basis 36 of 64)."""
+    T = torch.from_numpy
+    out = {}
+    for tag, (B, cin, cout, hw, k, stride, pad, seed) in {"patch": (4, 3, 64, 64, 16, 16, 0, 20250329),
+                                                          "c3x3": (3, 8, 32, 8, 3, 1, 1, 20250330)}.items():
+        rng = np.random.default_rng(seed)
+        _gih_gwlr(ref_args, "int")
+        torch.manual_seed(seed)
+        conv = qm.HQ_Conv2d(cin, cout, k, stride=stride, padding=pad)
+        x = rng.standard_normal((B, cin, hw, hw)).astype(np.float32)
+        x[:, 1] *= 6.0
+        xt = T(x).requires_grad_(True)
+        y = conv(xt)
+        go = (rng.standard_normal(tuple(y.shape)) * 1e-3).astype(np.float32)
+        y.backward(T(go))
+        out.update({tag + "_x": x, tag + "_w": conv.weight.detach().numpy(), tag + "_b": conv.bias.detach().numpy(),
+                    tag + "_go": go, tag + "_y": y.detach().numpy(), tag + "_gx": xt.grad.numpy(),
+                    tag + "_gw": conv.weight.grad.numpy(), tag + "_gb": conv.bias.grad.numpy(),
+                    tag + "_p": conv.hadamard_bs.numpy().astype(np.int8),
+                    tag + "_cfg": np.array([B, cin, cout, hw, k, stride, pad])})
+    _gih_gwlr(ref_args, "stoch")
+    np.savez_compressed(os.path.join(out_dir, "conv2d.npz"), **out)
+
+
 if __name__ == "__main__":
-    main(sys.argv[1], os.path.dirname(os.path.abspath(__file__)))
+    main(sys.argv[1], os.path.dirname(os.path.abspath(__file__)), tuple(sys.argv[2:]))

@@ -335,6 +335,61 @@ def test_linear_backward_vs_reference_golden(ops, golden, tag):
         assert rel < 1e-3, (name, rel)
 
 
+@pytest.mark.parametrize("basis", ["half16", "ref_10_of_32"])
+def test_config1_fc1_full_size(ops, basis):
+    """The single-layer configuration the targets are stated on, at its real size: ViT-B/16 fc1,
+    X [6304, 768] ~ N(0, 1) with 8 of 768 channels scaled by 20, W [3072, 768] kaiming-uniform,
+    grad_out [6304, 3072] ~ N(0, 1e-3), fp32, seed 0, explicit rounding noise; Hadamard order 16 +
+    INT4 for g_x, low-rank (8 lowest-sequency rows of H_16, and the reference's own make_WHT(6304)
+    rows) + INT8 for g_w.  Codes, scales, int32 accumulators and fp32 gradients are bit-exact
+    against the oracle."""
+    import math
+    gen = torch.Generator().manual_seed(0)
+    L, I, O = 6304, 768, 3072
+    x = torch.randn(L, I, generator=gen)
+    x[:, torch.randperm(I, generator=gen)[:8]] *= 20.0
+    bound = 1.0 / math.sqrt(I)                                    # kaiming_uniform_(a=sqrt(5)) on [O, I]
+    w = (torch.rand(O, I, generator=gen) * 2 - 1) * bound
+    go = torch.randn(L, O, generator=gen) * 1e-3
+    x, w, go = x.numpy(), w.numpy(), go.numpy()
+    order_l, sel = (16, oc.lowrank_preset(16, 8)) if basis == "half16" else oc.wht_selection(L, 50)
+    assert (order_l, len(sel)) == ((16, 8) if basis == "half16" else (32, 10))
+    Lp = L // order_l * len(sel)
+    rng = np.random.default_rng(0)
+    u = {k: rng.random(shp, dtype=np.float32) for k, shp in dict(x=(Lp, I), go=(L, O), w=(O, I), gw=(O, Lp)).items()}
+    mk = lambda k, bits, storage: ops.Quant(bits, storage, "noise", "tensor", 0, 0, _dev(u[k]))
+    cfg = ops.LinearConfig(order_o=16, order_l=order_l, sel_l=[int(v) for v in sel], q_gx=mk("go", 4, "int4"),
+                           q_w=mk("w", 4, "int4"), q_gw=mk("gw", 8, "int8"), q_x=mk("x", 8, "int8"))
+    xd, wd, god = _dev(x), _dev(w), _dev(go)
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    x_q_t, s_x = ops.abc_compress(xd, cfg)
+    gx, gw = ops.linear_backward(god, wd, x_q_t, s_x, cfg, status=status)
+    # the operands one by one, for the integer artefacts
+    q_go, s_go = ops.row_ht_quant(god, 16, cfg.q_gx)
+    q_w_t, s_w, _ = ops.col_ht_quant(wd, 16, list(range(16)), mk("w", 4, "int8"), "natural")      # [I, O] codes
+    q_gw_t, s_gw, lp = ops.col_ht_quant(god, order_l, [int(v) for v in sel], cfg.q_gw, "transposed")  # [O, L'] codes
+    acc_x = ops.gemm_i8(q_go, "int4", q_w_t, "int8", L, I, O, None, None, out_dtype=torch.int32, status=status)
+    acc_w = ops.gemm_i8(q_gw_t, "int8", x_q_t, "int8", O, I, Lp, None, None, out_dtype=torch.int32, status=status)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0 and lp == Lp
+    xq_ref, sx_ref = oc.abc_compress(x, order_l, np.array(sel), 8, u["x"])
+    ref = oc.linear_backward(go, w, xq_ref, sx_ref, n_o=16, n_l=order_l, sel=np.array(sel), u_go=u["go"], u_w=u["w"],
+                             u_gw=u["gw"], exact_matmul=False)   # float32 BLAS on integer values: exact below 2^24
+    bits32 = lambda a: np.atleast_1d(np.asarray(a, dtype=np.float32)).view(np.uint32)
+    assert np.array_equal(x_q_t.cpu().numpy().view(np.int8).astype(np.int32)[:, :Lp].T, xq_ref)
+    assert np.array_equal(bits32(sx_ref), s_x.cpu().numpy().view(np.uint32))
+    assert np.array_equal(_codes_from(q_go, "int4", O), ref["q_go"])
+    assert np.array_equal(_codes_from(q_w_t, "int8", O).T, ref["q_w"])
+    assert np.array_equal(_codes_from(q_gw_t, "int8", Lp), ref["q_gw"])
+    for got, want in ((s_go, ref["s_go"]), (s_w, ref["s_w"]), (s_gw, ref["s_gw"])):
+        assert np.array_equal(got.cpu().numpy().view(np.uint32), bits32(want))
+    assert np.abs(ref["acc_x"]).max() < 2 ** 24 and np.abs(ref["acc_w"]).max() < 2 ** 24
+    assert np.array_equal(acc_x.cpu().numpy(), ref["acc_x"].astype(np.int32))
+    assert np.array_equal(acc_w.cpu().numpy(), ref["acc_w"].astype(np.int32))
+    assert np.array_equal(gx.cpu().numpy(), ref["grad_input"])
+    assert np.array_equal(gw.cpu().numpy(), ref["grad_w"])
+
+
 def test_errors_are_reported(ops):
     x = torch.zeros((4, 24), device="cuda")
     with pytest.raises(RuntimeError, match="multiple of 16"):

@@ -358,6 +358,85 @@ def test_hlq_backward_plugin_call(hot):
         HLQ_backward.backward(go[None], w, x, 0, 0, 16, False)
 
 
+@pytest.mark.parametrize("per_token", [False, True])
+@pytest.mark.parametrize("stochastic", [False, True])
+@pytest.mark.parametrize("L", [16 * 27, 32 * 14])       # separate grad_out kernels / the fused pair
+def test_hlq_backward_plugin_call_matches_the_oracle(hot, per_token, stochastic, L):
+    """The plugin call composes its own launches, Philox offsets, post factors and low-rank preset:
+    its fp32 gradients must equal the oracle's bit for bit, with nearest rounding and with the
+    Philox streams at the offsets the call uses (8 * call number + 1..4 for grad_out/g_x, the
+    weight, grad_out/g_w, the activation; weight and activation streams indexed in their stored,
+    transposed layout)."""
+    import HLQ_backward
+    from hot_b200 import HLQ_backward as plugin
+    rng = np.random.default_rng(7)
+    O, I = 256, 96
+    go = (rng.standard_normal((L, O)) * 1e-3).astype(np.float32)
+    go[11] *= 25.0
+    w = ((rng.random((O, I)) * 2 - 1) / np.sqrt(I)).astype(np.float32)
+    x = rng.standard_normal((L, I)).astype(np.float32)
+    x[:, 9] *= 15.0
+    seed = 5
+    base = (plugin._call_counter + 1) * 8
+    gx, gw, times = HLQ_backward.backward(torch.from_numpy(go).cuda(), torch.from_numpy(w).cuda(), torch.from_numpy(x).cuda(),
+                                          0, 0, 16, per_token, seed=seed, stochastic=stochastic)
+    sel = np.array(oc.lowrank_preset(16, 8))
+    Lp = L // 2
+    if stochastic:
+        u_go = oc.philox_bytes(seed, base + 1, (L, O))
+        u_w = np.ascontiguousarray(oc.philox_bytes(seed, base + 2, (I, O)).T).view(oc.PhiloxBytes)
+        u_gw = oc.philox_bytes(seed, base + 3, (O, Lp))
+        u_x = np.ascontiguousarray(oc.philox_bytes(seed, base + 4, (I, Lp)).T).view(oc.PhiloxBytes)
+        mode = "stoch"
+    else:
+        u_go = u_w = u_gw = u_x = None
+        mode = "int"
+    xq, sx = oc.abc_compress(x, 16, sel, 8, u_x, mode)
+    ref = oc.linear_backward(go, w, xq, sx, n_o=16, n_l=16, sel=sel, u_go=u_go, u_w=u_w, u_gw=u_gw,
+                             gx_per_token=per_token, w_mode=mode)
+    assert np.array_equal(gx.cpu().numpy(), ref["grad_input"])
+    assert np.array_equal(gw.cpu().numpy(), ref["grad_w"])
+
+
+@pytest.mark.parametrize("fixture,tags", [("lqs", ("flat", "outlier")), ("lqs_batched", ("spread", "outlier"))])
+def test_lqs_select_quantizer_on_the_reference_cases(hot, golden, fixture, tags):
+    """The product's selection on the first-batch gradients of the reference-generated cases: the same
+    choice as the reference, and quantisation errors within 4 % of its (the rounding noise is another
+    draw; 3-7 thousand elements put the spread of the error near 1 %).  "spread" is the case where one
+    scale for the whole batch would give g_x to the per-token quantiser and the reference, with one
+    scale per sample, does not."""
+    from hot_b200 import lqs
+    g = golden(fixture)
+    for tag in tags:
+        gx, gw, e_st, e_nq = lqs.select_quantizer(torch.from_numpy(g[tag + "_g"]).cuda())
+        assert (gx, gw) == (str(g[tag + "_gx"]), "stoch_quantizer"), (tag, gx, e_st, e_nq)
+        np.testing.assert_allclose([e_st, e_nq], g[tag + "_errs"], rtol=0.04)
+
+
+@pytest.mark.parametrize("tag", ["patch", "c3x3"])
+def test_hq_conv2d_against_the_reference(hot, golden, tag):
+    """HQ_Conv2d forward + backward against the reference's own run (a stride-16 patch embedding and
+    a padded 3x3 convolution, deterministic quantisers on all four operands, per-sample scales): the
+    reference's transforms are BLAS matmuls, so the bound is the 1e-3 relative Frobenius error."""
+    args, qm = hot
+    args.lowRankPreset = None
+    args.quantBWDGogi = args.quantBWDWgt = args.quantBWDGogw = args.quantBWDAct = "int"
+    g = golden("conv2d")
+    B, cin, cout, hw, k, stride, pad = (int(v) for v in g[tag + "_cfg"])
+    conv = qm.HQ_Conv2d(cin, cout, k, stride=stride, padding=pad).cuda()
+    conv.weight.data = torch.from_numpy(g[tag + "_w"]).cuda()
+    conv.bias.data = torch.from_numpy(g[tag + "_b"]).cuda()
+    x = torch.from_numpy(g[tag + "_x"]).cuda().requires_grad_(True)
+    y = conv(x)
+    assert tuple(conv.hadamard_bs.shape) == tuple(g[tag + "_p"].shape)
+    assert np.array_equal(conv.hadamard_bs.cpu().numpy().astype(np.int8), g[tag + "_p"])
+    y.backward(torch.from_numpy(g[tag + "_go"]).cuda())
+    for got, name in ((y.detach(), "y"), (x.grad, "gx"), (conv.weight.grad, "gw"), (conv.bias.grad, "gb")):
+        want = g[tag + "_" + name]
+        rel = np.linalg.norm(got.cpu().numpy() - want) / np.linalg.norm(want)
+        assert rel < 1e-3, (name, rel)
+
+
 def test_vit_with_hot_linears_trains(hot):
     """A small ViT of the benchmark's architecture: apply_hot swaps exactly the block linears, a few
     SGD steps on a fixed batch reduce the loss, and gradients reach every parameter."""

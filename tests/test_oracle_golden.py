@@ -220,6 +220,42 @@ def test_lqs_rule(golden):
     assert str(g["flat_gx"]) == "stoch_quantizer" and str(g["outlier_gx"]) == "norm_quantizer"
 
 
+def test_lqs_rule_batched(golden):
+    """3-D gradients: one scale per sample for the per-tensor quantiser, as the calibration loop
+    calls it.  On the "spread" case one scale for the whole batch would hand g_x to the per-token
+    quantiser; the reference keeps the per-tensor one."""
+    g = golden("lqs_batched")
+    for tag in ("spread", "outlier"):
+        gx, gw, e_st, e_nq = oc.lqs_select(g[tag + "_g"], g[tag + "_u1"], g[tag + "_u2"])
+        np.testing.assert_allclose([e_st, e_nq], g[tag + "_errs"], rtol=1e-4)
+        assert gx == str(g[tag + "_gx"]) and gw == "stoch_quantizer"
+    assert str(g["spread_gx"]) == "stoch_quantizer" and str(g["outlier_gx"]) == "norm_quantizer"
+    flat = g["spread_g"].reshape(-1, g["spread_g"].shape[-1])
+    assert oc.lqs_select(flat, g["spread_u1"].reshape(flat.shape), g["spread_u2"].reshape(flat.shape))[0] == "norm_quantizer"
+
+
+def test_precision_scheduler_follows_the_reference(golden):
+    """hot_b200.quant_matmul.precision_scheduler against the reference's run (utils/utils.py:149-159)
+    over epochs 0..11 for six flag settings; host logic only, no device needed."""
+    import hot_b200.args as args
+    from hot_b200.quant_matmul import precision_scheduler
+    g = golden("precision_scheduler")
+    keep = {k: getattr(args, k) for k in ("GogiQuantBit", "weightQuantBit", "GogwQuantBit", "actQuantBit", "quantBWDGogi",
+                                          "quantBWDWgt")}
+    try:
+        for ci, case in enumerate(g["cases"]):
+            gogi, wgt, mx, mn, ms = str(case).split(",")
+            args.quantBWDGogi, args.quantBWDWgt = gogi, wgt
+            args.GogiQuantBit, args.weightQuantBit, args.GogwQuantBit, args.actQuantBit = 4, 4, 8, 8
+            for epoch in range(12):
+                precision_scheduler(epoch, int(mx), int(mn), [int(v) for v in ms.split()])
+                got = (args.GogiQuantBit, args.weightQuantBit, args.GogwQuantBit, args.actQuantBit)
+                assert got == tuple(int(v) for v in g["bits"][ci, epoch]), (str(case), epoch, got)
+    finally:
+        for k, v in keep.items():
+            setattr(args, k, v)
+
+
 def test_philox_known_answer():
     # Random123 known-answer vectors for philox4x32-10
     out = oc.philox4x32_10(0, 0, 0, 0, 0, 0)

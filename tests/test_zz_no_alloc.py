@@ -52,11 +52,31 @@ def test_static_scratch_matches_caller_scratch_twice_in_a_row(ops, scale, dtype)
     _pair(ops, big[:, :64].contiguous(), 16, sel, q8, "natural")
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_static_scratch_sawb_mode_twice_in_a_row(ops, dtype):
+    """The two-moment clip keeps four words per CTA in the array and clears nothing: every word the
+    second kernel reads was written by the first kernel of the same call, so a call after a larger
+    one (more CTAs, larger sums) must still agree with the caller-scratch variant bit for bit."""
+    torch.manual_seed(9)
+    q = ops.Quant(8, "int8", "nearest", "sawb")
+    big = (torch.randn(16 * 40, 768, device="cuda") * 30.0).to(dtype)
+    small = (torch.randn(16 * 6, 96, device="cuda") * 1e-2).to(dtype)
+    sel = [0, 8, 12, 4, 6, 14, 10, 2]
+    s_big = _pair(ops, big, 16, sel, q, "natural")
+    s_small = _pair(ops, small, 16, sel, q, "natural")
+    assert float(s_small[0]) < float(s_big[0])
+    _pair(ops, small, 1, [0], ops.Quant(4, "int8", "nearest", "sawb"), "natural")   # the weight's form: no transform
+
+
 def test_static_scratch_rejects_what_does_not_fit(ops):
     x = torch.zeros((16, 16400), device="cuda")             # one scratch word per column needed: 16400 > 16384
     sel = list(range(16))
     with pytest.raises(RuntimeError, match="built-in scratch holds 16384"):
         ops.col_ht_quant_static(x, 16, sel, ops.Quant(8, "int8", "nearest", "row"))
+    big = torch.zeros((50432, 3072), device="cuda", dtype=torch.bfloat16)   # the clip needs four words per CTA: 18916 here
+    with pytest.raises(RuntimeError, match="built-in scratch holds 16384"):
+        ops.col_ht_quant_static(big, 16, [0, 8, 12, 4, 6, 14, 10, 2], ops.Quant(8, "int8", "nearest", "sawb"))
+    del big
     codes, scales, n = ops.col_ht_quant_static(x, 16, sel, ops.Quant(8, "int8", "nearest", "tensor"))
     torch.cuda.synchronize()
     assert n == 16 and float(scales[0]) == 0.0 and int(codes[:, :16].max()) == 0
