@@ -330,35 +330,25 @@ __global__ void __launch_bounds__(kThreads) col_ht_quant_kernel(const T* __restr
       if (blockIdx.y == 0 && ch == 0 && c < p.cols) scales[c] = sp.s;
     }
     if (ROUND == HOT_ROUND_STOCH_PHILOX) {
-      // random byte of stored-layout element e: byte e % 16 of Philox block e / 16
+      // the random number of a code is indexed by its position e in the stored layout
       // batched calls index Philox by the position in the padded output row, so that runs stay aligned
       const uint64_t e0 = p.sample_pitch > 0
                               ? (uint64_t)c * (uint64_t)(p.sample_pitch * p.batch) + (uint64_t)blockIdx.z * (uint64_t)p.sample_pitch + (uint64_t)l0
                               : (uint64_t)c * (uint64_t)p.out_len + (uint64_t)l0;
-      if ((e0 & 7u) == 0) {
-        // aligned run: its 8 random bytes are one half of a Philox block
-        const uint4 blk = philox_block16(q, e0 >> 4);
-        const bool hi = (e0 & 8u) != 0;
-        const uint32_t rw[2] = {hi ? blk.z : blk.x, hi ? blk.w : blk.y};
+      // (one block serves 16 elements with 8 random bits each, or 32 with 4 bits each)
+      const int rb = rand_bits(q.qmax);
+      const int shift = rb == 4 ? 5 : 4;
+      uint64_t g = e0 >> shift;
+      uint4 blk = philox_block(q, g);
 #pragma unroll
-        for (int i = 0; i < 8; i += 2) {
-          const float2 t = philox_offset_bits2(make_float2(v[i], v[i + 1]), sp,
-                                               make_float2(philox_u128(rw[i >> 2], i & 3), philox_u128(rw[i >> 2], (i + 1) & 3)));
-          code[i] = (int)(__float_as_uint(t.x) & 0xFFu) - (qmax + 1);
-          code[i + 1] = (int)(__float_as_uint(t.y) & 0xFFu) - (qmax + 1);
+      for (int i = 0; i < 8; ++i) {
+        const uint64_t e = e0 + (uint64_t)i;
+        if ((e >> shift) != g) {  // the run crossed into the next block (unaligned row starts only)
+          g = e >> shift;
+          blk = philox_block(q, g);
         }
-      } else {
-        uint4 blk = philox_block16(q, e0 >> 4);
-        int j = (int)(e0 & 15u);
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          if (j == 16) {  // the run crossed into the next block (unaligned row starts only)
-            blk = philox_block16(q, (e0 >> 4) + 1);
-            j = 0;
-          }
-          code[i] = (int)philox_offset_code(v[i], sp, __uint_as_float(0x43000000u | (philox_byte(blk, j) << 8))) - (qmax + 1);
-          ++j;
-        }
+        const uint32_t r = rb == 4 ? philox_r4(blk, e) : philox_r8(blk, e);
+        code[i] = (int)philox_offset_code(v[i], sp, r, rb) - (qmax + 1);
       }
     } else {
       float u[8];

@@ -43,13 +43,18 @@ struct PerDeviceOnce {
   void mark(int dev) { done[dev].store(1, std::memory_order_release); }
 };
 
+// Philox4x32 rounds.  Salmon et al. ("Parallel random numbers: as easy as 1, 2, 3") give 10 as the
+// default and 7 as the fewest rounds that pass BigCrush; the rounding bits of a quantiser need no
+// more than that, and three rounds fewer are a third of the generator's integer work.
+constexpr int kPhiloxRounds = 7;
+
 // ---- quantiser parameters as the kernels see them -------------------------------------
 struct QuantDev {
   float qmax;          // 2^(bits-1) - 1
   const float* noise;  // explicit uniforms (ROUND_NOISE)
   uint32_t k0, k1;     // Philox key   = seed
   uint32_t o0, o1;     // Philox c2,c3 = offset
-  uint32_t rk0[10], rk1[10];  // the key of each round (the key schedule is the same for every block)
+  uint32_t rk0[kPhiloxRounds], rk1[kPhiloxRounds];  // the key of each round (the key schedule is the same for every block)
 };
 
 inline QuantDev make_quant_dev(const hot_quant_t& q) {
@@ -60,7 +65,7 @@ inline QuantDev make_quant_dev(const hot_quant_t& q) {
   d.k1 = (uint32_t)(q.seed >> 32);
   d.o0 = (uint32_t)q.offset;
   d.o1 = (uint32_t)(q.offset >> 32);
-  for (int r = 0; r < 10; ++r) {
+  for (int r = 0; r < kPhiloxRounds; ++r) {
     d.rk0[r] = d.k0 + (uint32_t)r * 0x9E3779B9u;
     d.rk1[r] = d.k1 + (uint32_t)r * 0xBB67AE85u;
   }
@@ -71,13 +76,13 @@ inline QuantDev make_quant_dev(const hot_quant_t& q) {
 
 constexpr float kEps = 1e-11f;  // the reference's args.eps, added to the scale before dividing
 
-// Philox4x32-10 (Salmon et al., "Parallel random numbers: as easy as 1, 2, 3").
-// rk0 / rk1: the ten round keys (key + r * Weyl constant), precomputed by the host so that they
+// Philox4x32 (Salmon et al., "Parallel random numbers: as easy as 1, 2, 3"), kPhiloxRounds rounds.
+// rk0 / rk1: the round keys (key + r * Weyl constant), precomputed by the host so that they
 // reach the XORs as kernel-parameter operands; each round is two 32 x 32 -> 64 bit products.
-__device__ __forceinline__ uint4 philox4x32_10(uint32_t c0, uint32_t c1, uint32_t c2, uint32_t c3,
-                                               const uint32_t (&rk0)[10], const uint32_t (&rk1)[10]) {
+__device__ __forceinline__ uint4 philox4x32(uint32_t c0, uint32_t c1, uint32_t c2, uint32_t c3,
+                                            const uint32_t (&rk0)[kPhiloxRounds], const uint32_t (&rk1)[kPhiloxRounds]) {
 #pragma unroll
-  for (int r = 0; r < 10; ++r) {
+  for (int r = 0; r < kPhiloxRounds; ++r) {
     const uint64_t p0 = (uint64_t)0xD2511F53u * (uint64_t)c0;
     const uint64_t p1 = (uint64_t)0xCD9E8D57u * (uint64_t)c2;
     c0 = (uint32_t)(p1 >> 32) ^ c1 ^ rk0[r];
@@ -88,14 +93,33 @@ __device__ __forceinline__ uint4 philox4x32_10(uint32_t c0, uint32_t c1, uint32_
   return make_uint4(c0, c1, c2, c3);
 }
 
-// The 16 random bytes of Philox block g: the stochastic-rounding bits of elements 16g .. 16g+15
-// (element 16g + j takes byte j, little-endian within the words x, y, z, w).
-__device__ __forceinline__ uint4 philox_block16(const QuantDev& q, uint64_t g) {
-  return philox4x32_10((uint32_t)g, (uint32_t)(g >> 32), q.o0, q.o1, q.rk0, q.rk1);
+// Philox block g: counter (g_lo, g_hi, offset_lo, offset_hi), key = seed.  Which elements a block
+// serves depends on the random bits a code takes (rand_bits below):
+//   8 bits: elements 16g .. 16g+15; element 16g + j takes byte j % 4 (little-endian) of word j / 4
+//   4 bits: elements 32g .. 32g+31; with j = e % 32, run h = j / 16, i = j % 16, element e takes
+//           nibble i / 8 of byte i % 4 of word 2h + (i % 8) / 4, so that one word serves elements
+//           i..i+3 of a run with its low nibbles and i+8..i+11 with its high ones
+__device__ __forceinline__ uint4 philox_block(const QuantDev& q, uint64_t g) {
+  return philox4x32((uint32_t)g, (uint32_t)(g >> 32), q.o0, q.o1, q.rk0, q.rk1);
 }
-__device__ __forceinline__ uint32_t philox_byte(const uint4& r, int j) {
-  const uint32_t w = j < 4 ? r.x : (j < 8 ? r.y : (j < 12 ? r.z : r.w));
-  return (w >> (8 * (j & 3))) & 0xFFu;
+__device__ __forceinline__ uint32_t philox_word(const uint4& r, int w) {
+  return w == 0 ? r.x : (w == 1 ? r.y : (w == 2 ? r.z : r.w));
+}
+// the 8-bit / 4-bit random number of stored-layout element e, from the block that serves it
+__device__ __forceinline__ uint32_t philox_r8(const uint4& blk, uint64_t e) {
+  const int j = (int)(e & 15u);
+  return (philox_word(blk, j >> 2) >> (8 * (j & 3))) & 0xFFu;
+}
+__device__ __forceinline__ uint32_t philox_r4(const uint4& blk, uint64_t e) {
+  const int i = (int)(e & 15u), h = (int)((e >> 4) & 1u);
+  return (philox_word(blk, 2 * h + ((i & 7) >> 2)) >> (8 * (i & 3) + 4 * (i >> 3))) & 0xFu;
+}
+// the two words of the 16-element run that starts at element e0 (a multiple of 16), 4-bit numbers
+__device__ __forceinline__ void philox_run_words4(const QuantDev& q, uint64_t e0, uint32_t& r0, uint32_t& r1) {
+  const uint4 b = philox_block(q, e0 >> 5);
+  const bool hi = (e0 & 16u) != 0;
+  r0 = hi ? b.z : b.x;
+  r1 = hi ? b.w : b.y;
 }
 
 // ---- packed fp32 (two IEEE round-to-nearest operations per instruction on sm_100) -------
@@ -135,45 +159,58 @@ __device__ __forceinline__ float2 div2_exact(float2 x, const Divisor& v) {
 
 // Everything a quantiser derives from an abs-max: the scale s = mx / qmax the caller gets back,
 // the divisor s + eps (fp32, round-to-nearest: the reference divides, it does not multiply by
-// a reciprocal), and the constant of the Philox rounding path.
+// a reciprocal), and the constants of the Philox rounding path.
 struct ScalePair {
   float s;
   Divisor dv;  // divide by s + eps
-  float c0;    // (qmax + 1) - 128 + 1/512, see philox_offset_code
+  float mk;    // RN(2^RB / (s + eps)), RB = rand_bits(qmax)
+  float ck;    // 1.5 * 2^23 + 2^RB * (qmax + 1)
 };
+
+// Random bits per code on the Philox path: 4 for codes of up to 4 bits, else 8.
+__host__ __device__ __forceinline__ int rand_bits(float qmax) { return qmax <= 7.0f ? 4 : 8; }
+constexpr float kKMagic = 12582912.0f;  // 1.5 * 2^23 = 0x4B400000: the low mantissa bits of RN(t + this) are RN(t) as an integer
 
 __device__ __forceinline__ ScalePair scale_from_absmax(float mx, float qmax) {
   ScalePair p;
   p.s = __fdiv_rn(mx, qmax);
   p.dv = make_divisor(__fadd_rn(p.s, kEps));
-  p.c0 = (qmax + 1.0f) - 128.0f + 0.001953125f;  // exact in fp32
+  const float two_rb = qmax <= 7.0f ? 16.0f : 256.0f;
+  p.mk = __fdiv_rn(two_rb, p.dv.d);
+  p.ck = kKMagic + two_rb * (qmax + 1.0f);  // exact in fp32
   return p;
 }
 
-// Philox-path stochastic rounding.  With y = x / d, B = qmax + 1 and R the element's random byte,
-//     offset code = floor( y + B + (R + 0.5) / 256 )        (code = offset code - B)
-// evaluated as  t1 = RN(y + c0),  t2 = t1 + u  (exact),  floor(t2),  where u = 128 + R / 256 is built
-// by dropping R into the mantissa of 128.0f and c0 = B - 128 + 1/512.  The value is shifted to be
-// positive so that floor is the rounding for both signs; adding a uniform in (0, 1) and flooring
-// rounds up with probability frac(y) to within 1/256, and the +0.5 centres it (no bias).  Since
-// |y| <= qmax * (1 + 2^-22), the offset code stays in [1, 2 * qmax + 1]: no clamp needed.
-__device__ __forceinline__ float philox_u128(uint32_t word, int byte) {
-  return __uint_as_float(__byte_perm(word, 0x43000000u, 0x7404u | ((uint32_t)byte << 4)));
+// Philox-path stochastic rounding.  With RB random bits per code, R the element's RB-bit random
+// number, B = qmax + 1 and m = RN(2^RB / d):
+//     K = round_half_even(x * m) + 2^RB * B,      offset code = (K + R) >> RB      (code = offset code - B)
+// K comes out of ONE fused multiply-add: RN(x * m + (1.5 * 2^23 + 2^RB * B)) lies in [2^23, 2^24), where
+// fp32 has unit spacing, so its low mantissa bits are K (x * m enters the rounding exactly).  The
+// quotient is thereby rounded to RB fractional bits; adding a uniform RB-bit integer and dropping
+// RB bits rounds up with probability round(2^RB * frac) / 2^RB: unbiased.  Since |x * m| <=
+// 2^RB * qmax * (1 + 2^-22), K + R stays within [2^RB, 2^RB * (2 * qmax + 2)): no clamp, and for
+// RB = 4 / 8 the sum fits an 8- / 16-bit lane, so the random numbers are added to packed lanes.
+__device__ __forceinline__ uint32_t philox_kbits(float x, const ScalePair& sp) {
+  return __float_as_uint(__fmaf_rn(x, sp.mk, sp.ck));
 }
-constexpr float kFloorMagic = 8388608.0f;  // 2^23: RD(t + 2^23) keeps floor(t) in the low mantissa bits
-
-__device__ __forceinline__ uint32_t philox_offset_code(float x, const ScalePair& sp, float u128) {
-  const float t2 = __fadd_rn(__fadd_rn(div_exact(x, sp.dv), sp.c0), u128);
-  return __float_as_uint(__fadd_rd(t2, kFloorMagic)) & 0xFFu;
-}
-// two values at once; returns the raw bits whose low bytes are the offset codes
-__device__ __forceinline__ float2 philox_offset_bits2(float2 x, const ScalePair& sp, float2 u128) {
-  const float2 t2 = add2(add2(div2_exact(x, sp.dv), make_float2(sp.c0, sp.c0)), u128);
-  return __fadd2_rd(t2, make_float2(kFloorMagic, kFloorMagic));
+__device__ __forceinline__ uint32_t philox_offset_code(float x, const ScalePair& sp, uint32_t r, int rb) {
+  return ((philox_kbits(x, sp) & 0xFFFFu) + r) >> rb;
 }
 // low bytes of four words -> one word
 __device__ __forceinline__ uint32_t gather_low_bytes(uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
   return __byte_perm(__byte_perm(a, b, 0x0040u), __byte_perm(c, d, 0x0040u), 0x5410u);
+}
+// Four offset codes (one per byte) of the K words k0..k3 of elements j..j+3 with 8 random bits each:
+// rw = the word whose bytes are their random numbers.  Two K values share a 32-bit word in 16-bit lanes.
+__device__ __forceinline__ uint32_t offset_codes4_rb8(uint32_t k0, uint32_t k1, uint32_t k2, uint32_t k3, uint32_t rw) {
+  const uint32_t s02 = __byte_perm(k0, k2, 0x5410u) + (rw & 0x00FF00FFu);
+  const uint32_t s13 = __byte_perm(k1, k3, 0x5410u) + __byte_perm(rw, 0u, 0x4341u);
+  return __byte_perm(s02, s13, 0x7351u);
+}
+// Four sums K + R (one per byte; the offset code is the high nibble) with 4 random bits each:
+// rn = the four random nibbles, one per byte, already masked
+__device__ __forceinline__ uint32_t offset_sums4_rb4(uint32_t k0, uint32_t k1, uint32_t k2, uint32_t k3, uint32_t rn) {
+  return gather_low_bytes(k0, k1, k2, k3) + rn;
 }
 // Packed INT4 layout: a run of 16 codes takes 8 bytes; byte j holds code j in its low nibble and code
 // j + 8 in its high nibble.  lo / hi: four byte-wide codes (each < 16) of the first / second half.
@@ -185,6 +222,38 @@ __device__ __forceinline__ uint32_t remove_offset(uint32_t w, uint32_t off, uint
   const uint32_t ext = lane_span - 2u * off;  // the bits above the sign bit (0 if the code fills its lane)
   if (ext) w |= ((w & (off * lanes)) / off) * ext;
   return w;
+}
+
+// The 16 offset codes of a run whose K words are ka[0..7] (elements 0..7) and kb[0..7] (elements
+// 8..15), Philox rounding; e0 = stored-layout index of element 0 (a multiple of 16).
+//   RB = 4: wa0 / wb0 / wa1 / wb1 hold the sums of elements 0-3 / 8-11 / 4-7 / 12-15 (code = high nibble)
+//   RB = 8: they hold the offset codes of those elements, one per byte
+__device__ __forceinline__ void philox_run16_words(const uint32_t* ka, const uint32_t* kb, bool rb4, uint32_t r0, uint32_t r1,
+                                                   uint32_t r2, uint32_t r3, uint32_t& wa0, uint32_t& wa1, uint32_t& wb0,
+                                                   uint32_t& wb1) {
+  // rb4: (r0, r1) are the run's two words; else (r0, r1, r2, r3) are the four words of its block
+  if (rb4) {
+    wa0 = offset_sums4_rb4(ka[0], ka[1], ka[2], ka[3], r0 & 0x0F0F0F0Fu);
+    wb0 = offset_sums4_rb4(kb[0], kb[1], kb[2], kb[3], (r0 >> 4) & 0x0F0F0F0Fu);
+    wa1 = offset_sums4_rb4(ka[4], ka[5], ka[6], ka[7], r1 & 0x0F0F0F0Fu);
+    wb1 = offset_sums4_rb4(kb[4], kb[5], kb[6], kb[7], (r1 >> 4) & 0x0F0F0F0Fu);
+  } else {
+    wa0 = offset_codes4_rb8(ka[0], ka[1], ka[2], ka[3], r0);
+    wa1 = offset_codes4_rb8(ka[4], ka[5], ka[6], ka[7], r1);
+    wb0 = offset_codes4_rb8(kb[0], kb[1], kb[2], kb[3], r2);
+    wb1 = offset_codes4_rb8(kb[4], kb[5], kb[6], kb[7], r3);
+  }
+}
+__device__ __forceinline__ void philox_run16(const uint32_t* ka, const uint32_t* kb, const QuantDev& q, uint64_t e0,
+                                             bool rb4, uint32_t& wa0, uint32_t& wa1, uint32_t& wb0, uint32_t& wb1) {
+  if (rb4) {
+    uint32_t r0, r1;
+    philox_run_words4(q, e0, r0, r1);
+    philox_run16_words(ka, kb, true, r0, r1, 0u, 0u, wa0, wa1, wb0, wb1);
+  } else {
+    const uint4 r = philox_block(q, e0 >> 4);
+    philox_run16_words(ka, kb, false, r.x, r.y, r.z, r.w, wa0, wa1, wb0, wb1);
+  }
 }
 
 // One code for the deterministic and the explicit-noise modes, |code| <= qmax.

@@ -120,26 +120,26 @@ __device__ __forceinline__ void quantise16_int8_pair(const float2 (&y)[16], cons
                                                      const QuantDev& q, uint64_t e_a, uint64_t e_b, uint4& out_a, uint4& out_b) {
   uint32_t wa[4] = {0, 0, 0, 0}, wb[4] = {0, 0, 0, 0};
   if (ROUND == HOT_ROUND_STOCH_PHILOX) {
-    const uint4 r_a = philox_block16(q, e_a >> 4), r_b = philox_block16(q, e_b >> 4);
-    const uint32_t ra[4] = {r_a.x, r_a.y, r_a.z, r_a.w}, rb[4] = {r_b.x, r_b.y, r_b.z, r_b.w};
-    const float2 r2 = make_float2(sa.dv.r, sb.dv.r), nd2 = make_float2(-sa.dv.d, -sb.dv.d);
-    const float2 c2 = make_float2(sa.c0, sa.c0), magic2 = make_float2(kFloorMagic, kFloorMagic);
-    uint32_t ba[16], bb[16];
+    const bool rb4 = rand_bits(q.qmax) == 4;
+    const float2 mk2 = make_float2(sa.mk, sb.mk), ck2 = make_float2(sa.ck, sb.ck);  // one divisor per channel
+    uint32_t ka[2][8], kb[2][8];  // [first / second eight codes][i]: K bits of channel c / c + 1
 #pragma unroll
     for (int i = 0; i < 16; ++i) {
-      const float2 q0 = __fmul2_rn(y[i], r2);                    // the exact division of div2_exact,
-      const float2 e = __ffma2_rn(q0, nd2, y[i]);                // with one divisor per channel
-      const float2 d = __ffma2_rn(e, r2, q0);
-      const float2 u = make_float2(philox_u128(ra[i >> 2], i & 3), philox_u128(rb[i >> 2], i & 3));
-      const float2 t = __fadd2_rd(add2(add2(d, c2), u), magic2);
-      ba[i] = __float_as_uint(t.x);
-      bb[i] = __float_as_uint(t.y);
+      const float2 t = __ffma2_rn(y[i], mk2, ck2);
+      ka[i >> 3][i & 7] = __float_as_uint(t.x);
+      kb[i >> 3][i & 7] = __float_as_uint(t.y);
     }
+    philox_run16(ka[0], ka[1], q, e_a, rb4, wa[0], wa[1], wa[2], wa[3]);
+    philox_run16(kb[0], kb[1], q, e_b, rb4, wb[0], wb[1], wb[2], wb[3]);
     const uint32_t off = (uint32_t)(q.qmax + 1.0f);
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
-      wa[k] = remove_offset(gather_low_bytes(ba[4 * k], ba[4 * k + 1], ba[4 * k + 2], ba[4 * k + 3]), off, 0x01010101u, 0x100u);
-      wb[k] = remove_offset(gather_low_bytes(bb[4 * k], bb[4 * k + 1], bb[4 * k + 2], bb[4 * k + 3]), off, 0x01010101u, 0x100u);
+      if (rb4) {
+        wa[k] = (wa[k] >> 4) & 0x0F0F0F0Fu;
+        wb[k] = (wb[k] >> 4) & 0x0F0F0F0Fu;
+      }
+      wa[k] = remove_offset(wa[k], off, 0x01010101u, 0x100u);
+      wb[k] = remove_offset(wb[k], off, 0x01010101u, 0x100u);
     }
   } else {
     const int qmax = (int)q.qmax;

@@ -1,0 +1,487 @@
+// grad_output (bf16) -> both quantised operands of the backward, with the two +-1 transforms run on
+// the tensor cores: the Hadamard transform of order 16 along the channels (g_x side) and the
+// low-rank Walsh-Hadamard projection along the tokens (g_w side, 8 lowest-sequency rows of H_16)
+// are small matrix products against +-1 matrices, so a tile of grad_output that TMA laid in shared
+// memory is multiplied, as it lies there, once as a K-major operand (rows = tokens) and once as an
+// MN-major operand (rows = channels) by tcgen05.mma.kind::f16.  The products of bf16 values with +-1
+// are exact and are summed in fp32 in tensor memory; the CUDA cores are left with what cannot be a
+// matrix product: abs-max (pass 0), scaling, Philox rounding and packing (pass 1).
+//
+// One persistent CTA per SM walks 128-token x 128-channel tiles.  Warp roles:
+//   warp 0      TMA producer: two 128-token x 64-channel boxes (128-byte swizzle) per tile
+//   warp 1      allocates tensor memory and issues, from one lane, 8 MMAs (M 128 tokens, N 16, K 16
+//               channels) for the channel transform and 8 (M 128 channels, N 16 = two token blocks x
+//               8 kept rows, K 16 tokens) for the token projection; accumulators are double-buffered
+//   warps 2-5   g_x side: a lane owns a token, reads its 128 transformed channels from tensor memory,
+//               quantises and hands 32-token x 64-byte boxes to the copy engine
+//   warps 6-9   g_w side: a lane owns a channel, reads its 64 projected positions, quantises, and
+//               stores them as a row piece of the transposed operand the same way
+//
+// The fp32 sums differ from the fixed-order butterflies of row_ht_quant / col_ht_quant only where a
+// sum of 16 bf16 values is not exact in fp32 (operands more than ~2^13 apart in magnitude); there the
+// last bit of a transformed value may differ, and with it, rarely, a code.  The kernels therefore serve
+// the nearest and Philox modes; the explicit-noise mode (bit-exact parity with the reference's
+// quantisers) stays on the butterfly kernels.
+// Every wait on an mbarrier is bounded in time (see gemm_i8.cu for the abort protocol).
+#include "tc.cuh"
+
+namespace hot {
+namespace {
+
+constexpr int kTok = 128;                  // tokens per tile
+constexpr int kCh = 128;                   // channels per tile
+constexpr int kBoxBytes = kTok * 128;      // one TMA box: 128 tokens x 64 bf16 channels
+constexpr int kStageBytes = 2 * kBoxBytes; // 32 KB
+constexpr int kStages = 4;
+constexpr int kEpiWarps = 8;
+constexpr int kThreadsTc = (2 + kEpiWarps) * 32;
+constexpr uint32_t kTmemColsTc = 512;      // two buffers of 128 (channel transform) + 64 (token projection) columns
+constexpr uint32_t kBufCols = 192;
+constexpr int kOffOperands = kStages * kStageBytes;      // H16 | P (first block) | P (second block): 512 bytes each
+constexpr int kOffStoreStage = kOffOperands + 2048;      // per epilogue warp two 32-row x 64-byte boxes
+constexpr int kOffBarriers = kOffStoreStage + kEpiWarps * 4096;
+constexpr int kSmemTc = kOffBarriers + 256 + 1024;       // barriers + slack to align the base to 1024
+
+// natural row of H_16 of output slot j of the token projection (the 8 lowest-sequency rows)
+__device__ constexpr int kSlotRow[8] = {0, 8, 12, 4, 6, 14, 10, 2};
+constexpr int kSlotRowHost[8] = {0, 8, 12, 4, 6, 14, 10, 2};
+
+struct TcParams {
+  int64_t L;
+  int O;
+  int x_row, w_row;        // per-token scale on the g_x side, per-channel scale on the g_w side
+  QuantDev qx, qw;
+  float* s_x;              // [1] or [L]
+  float* s_w;              // [1] or [O]
+  uint32_t* max_x;         // [1] or [L]
+  uint32_t* max_w;         // [1] or [O]
+  uint32_t* status;
+};
+
+// Instruction descriptor: D = F32, A = B = BF16, B K-major, A K-major or MN-major, M = 128, N = 16.
+__host__ __device__ constexpr uint32_t instr_desc_bf16(bool a_mn_major) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((a_mn_major ? 1u : 0u) << 15) | ((16u >> 3) << 17) | ((128u >> 4) << 24);
+}
+
+// byte offset of element (n, k) of a 16 x 16 bf16 K-major operand without swizzle: 8 x 16-byte core
+// matrices, the two K halves 128 bytes apart (leading offset), the two row groups 256 bytes apart (stride offset)
+__device__ __forceinline__ int operand_offset(int n, int k) { return (n >> 3) * 256 + (k >> 3) * 128 + (n & 7) * 16 + (k & 7) * 2; }
+
+__device__ __forceinline__ uint16_t pm_one_bf16(int negative) { return negative ? 0xBF80u : 0x3F80u; }
+
+// 32 consecutive values of this lane's row of the accumulator -> K bits (RN(x * mk + ck)) of Philox rounding
+__device__ __forceinline__ void kbits32(const uint32_t (&f)[32], const ScalePair& sp, uint32_t (&k)[32]) {
+  const float2 mk2 = make_float2(sp.mk, sp.mk), ck2 = make_float2(sp.ck, sp.ck);
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    const float2 t = __ffma2_rn(make_float2(__uint_as_float(f[2 * i]), __uint_as_float(f[2 * i + 1])), mk2, ck2);
+    k[2 * i] = __float_as_uint(t.x);
+    k[2 * i + 1] = __float_as_uint(t.y);
+  }
+}
+
+// The 32 codes of elements e0 .. e0+31 (e0 a multiple of 16; of 32 when the codes take 4 random bits and
+// `aligned32` is set, so that one Philox block serves both runs).  Output: INT4 packed (STORE4: 16 bytes in
+// out[0..3]) or one code per byte (32 bytes in out[0..7]): run 0 first, within a run the stored order.
+template <int ROUND, bool STORE4>
+__device__ __forceinline__ void quantise32(const uint32_t (&f)[32], const ScalePair& sp, const QuantDev& q, uint64_t e0,
+                                           bool aligned32, uint32_t (&out)[8]) {
+  const uint32_t off = (uint32_t)(q.qmax + 1.0f);
+  if (ROUND == HOT_ROUND_STOCH_PHILOX) {
+    const bool rb4 = rand_bits(q.qmax) == 4;
+    uint32_t k[32];
+    kbits32(f, sp, k);
+    uint4 b0, b1;
+    if (rb4 && aligned32) {
+      b0 = philox_block(q, e0 >> 5);
+      b1 = b0;
+    } else if (rb4) {
+      b0 = philox_block(q, e0 >> 5);
+      b1 = philox_block(q, (e0 + 16) >> 5);
+    } else {
+      b0 = philox_block(q, e0 >> 4);
+      b1 = philox_block(q, (e0 >> 4) + 1);
+    }
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      const uint4 b = r ? b1 : b0;
+      const bool hi = ((e0 + 16 * r) & 16u) != 0;  // rb4: which half of the block this run takes
+      uint32_t wa0, wa1, wb0, wb1;
+      philox_run16_words(k + 16 * r, k + 16 * r + 8, rb4, rb4 ? (hi ? b.z : b.x) : b.x, rb4 ? (hi ? b.w : b.y) : b.y, b.z, b.w,
+                         wa0, wa1, wb0, wb1);
+      if (STORE4) {
+        out[2 * r] = remove_offset(((wa0 >> 4) & 0x0F0F0F0Fu) | (wb0 & 0xF0F0F0F0u), off, 0x11111111u, 0x10u);
+        out[2 * r + 1] = remove_offset(((wa1 >> 4) & 0x0F0F0F0Fu) | (wb1 & 0xF0F0F0F0u), off, 0x11111111u, 0x10u);
+      } else {
+        if (rb4) {
+          wa0 = (wa0 >> 4) & 0x0F0F0F0Fu; wa1 = (wa1 >> 4) & 0x0F0F0F0Fu;
+          wb0 = (wb0 >> 4) & 0x0F0F0F0Fu; wb1 = (wb1 >> 4) & 0x0F0F0F0Fu;
+        }
+        out[4 * r] = remove_offset(wa0, off, 0x01010101u, 0x100u);
+        out[4 * r + 1] = remove_offset(wa1, off, 0x01010101u, 0x100u);
+        out[4 * r + 2] = remove_offset(wb0, off, 0x01010101u, 0x100u);
+        out[4 * r + 3] = remove_offset(wb1, off, 0x01010101u, 0x100u);
+      }
+    }
+  } else {
+    const int qmax = (int)q.qmax;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) out[i] = 0u;
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        const int c = quantise_one<HOT_ROUND_NEAREST>(__uint_as_float(f[16 * r + i]), sp, 0.0f, qmax);
+        if (STORE4) out[2 * r + ((i & 7) >> 2)] |= (uint32_t)(c & 0xF) << (8 * (i & 3) + 4 * (i >> 3));
+        else out[4 * r + (i >> 2)] |= (uint32_t)(c & 0xFF) << (8 * (i & 3));
+      }
+    }
+  }
+}
+
+// PASS 0: abs-max of both transformed tensors.  PASS 1: quantise against them (RX / RW: rounding of the
+// g_x / g_w side; X4: g_x codes packed INT4, else one per byte).  Pass 1 walks the tiles in the reverse
+// order of pass 0, so that it starts on the part of grad_output that is most likely still in L2.
+template <int PASS, int RX, int RW, bool X4>
+__global__ void __launch_bounds__(kThreadsTc, 1)
+    go_dual_tc_kernel(const __grid_constant__ CUtensorMap tmap_in, const __grid_constant__ CUtensorMap tmap_qgo,
+                      const __grid_constant__ CUtensorMap tmap_qgw, TcParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + kOffBarriers);   // tile landed
+  uint64_t* empty = full + kStages;                                    // the tile's MMAs retired
+  uint64_t* tmem_full = empty + kStages;                               // [2] both accumulators of a tile complete
+  uint64_t* tmem_empty = tmem_full + 2;                                // [2] drained by the epilogue warps
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
+  volatile uint32_t* abort_flag = tmem_slot + 1;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tiles_c = p.O / kCh;
+  const int tiles_t = (int)((p.L + kTok - 1) / kTok);
+  const int num_tiles = tiles_c * tiles_t;
+  // tile sequence of this CTA: blockIdx.x, + gridDim.x, ...; pass 1 mirrors the index
+  auto tile_of = [&](int seq) { return PASS == 0 ? seq : num_tiles - 1 - seq; };
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&tmem_full[b], 1);
+      mbar_init(&tmem_empty[b], kEpiWarps * 32);
+    }
+    *abort_flag = 0u;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    tma_prefetch_desc(&tmap_in);
+    if (PASS == 1) {
+      tma_prefetch_desc(&tmap_qgo);
+      tma_prefetch_desc(&tmap_qgw);
+    }
+  }
+  // the three +-1 operands: H_16, and the kept rows of H_16 placed for the first / second token block of a pair
+  if (threadIdx.x < 256) {
+    const int n = threadIdx.x >> 4, k = threadIdx.x & 15;
+    uint8_t* ops = smem + kOffOperands;
+    *reinterpret_cast<uint16_t*>(ops + operand_offset(n, k)) = pm_one_bf16(__popc(n & k) & 1);
+    const uint16_t pv = pm_one_bf16(__popc(kSlotRow[n & 7] & k) & 1);
+    *reinterpret_cast<uint16_t*>(ops + 512 + operand_offset(n, k)) = n < 8 ? pv : (uint16_t)0;
+    *reinterpret_cast<uint16_t*>(ops + 1024 + operand_offset(n, k)) = n < 8 ? (uint16_t)0 : pv;
+  }
+  fence_proxy_async_smem();  // generic-proxy writes -> visible to the tensor core
+  if (warp == 1) tmem_alloc(tmem_slot, kTmemColsTc);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ---- TMA producer (grad_out is not written by the kernel before this one: no dependency wait) ----
+    if (lane == 0) {
+      uint32_t s = 0, ph = 0;
+      for (int seq = blockIdx.x; seq < num_tiles; seq += gridDim.x, s = (s + 1 == kStages ? 0 : s + 1), ph ^= (s == 0 ? 1u : 0u)) {
+        if (!mbar_wait(&empty[s], ph ^ 1u, abort_flag)) break;
+        const int t = tile_of(seq);
+        const int tt = t / tiles_c, tc = t % tiles_c;
+        mbar_expect_tx(&full[s], kStageBytes);
+        tma_load_2d(smem + s * kStageBytes, &tmap_in, &full[s], tc * (kCh * 2), tt * kTok);
+        tma_load_2d(smem + s * kStageBytes + kBoxBytes, &tmap_in, &full[s], tc * (kCh * 2) + 128, tt * kTok);
+      }
+    }
+  } else if (warp == 1) {
+    // ---- MMA issue ----
+    if (lane == 0) {
+      constexpr uint32_t idesc_row = instr_desc_bf16(false), idesc_col = instr_desc_bf16(true);
+      const uint32_t ops = smem_u32(smem + kOffOperands);
+      const uint64_t b_h = smem_desc(ops, 128, 256, 0);
+      const uint64_t b_p0 = smem_desc(ops + 512, 128, 256, 0), b_p1 = smem_desc(ops + 1024, 128, 256, 0);
+      uint32_t s = 0, ph = 0, it = 0;
+      for (int seq = blockIdx.x; seq < num_tiles; seq += gridDim.x, ++it, s = (s + 1 == kStages ? 0 : s + 1), ph ^= (s == 0 ? 1u : 0u)) {
+        const uint32_t buf = it & 1u, bph = (it >> 1) & 1u;
+        if (!mbar_wait(&tmem_empty[buf], bph ^ 1u, abort_flag)) break;
+        if (!mbar_wait(&full[s], ph, abort_flag)) break;
+        tc_fence_after();
+        const uint32_t stage = smem_u32(smem + s * kStageBytes);
+        const uint32_t d_row = tmem_base + buf * kBufCols, d_col = d_row + 128;
+        // channel transform: tokens are the rows of a K-major operand (128 bytes per token, 8-token groups 1024
+        // bytes apart); 16 channels = 32 bytes of K per MMA
+#pragma unroll
+        for (int g = 0; g < 8; ++g) {
+          const uint64_t a = smem_desc(stage + (g >> 2) * kBoxBytes + (g & 3) * 32, 16, 1024, 2);
+          umma_bf16(d_row + 16 * g, a, b_h, idesc_row, 0u);
+        }
+        // token projection: channels are the rows of an MN-major operand (64 channels contiguous, the next 64 in the
+        // second box = leading offset; 8-token groups 1024 bytes apart = stride offset); a pair of 16-token blocks per
+        // 16 output columns, one block per MMA
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const uint64_t a0 = smem_desc(stage + (32 * j) * 128, kBoxBytes, 1024, 2);
+          const uint64_t a1 = smem_desc(stage + (32 * j + 16) * 128, kBoxBytes, 1024, 2);
+          umma_bf16(d_col + 16 * j, a0, b_p0, idesc_col, 0u);
+          umma_bf16(d_col + 16 * j, a1, b_p1, idesc_col, 1u);
+        }
+        umma_commit(&empty[s]);
+        umma_commit(&tmem_full[buf]);
+      }
+    }
+  } else {
+    // ---- epilogue: warps 2-5 g_x side (lane = token), warps 6-9 g_w side (lane = channel) ----
+    const int q = warp & 3;                 // tensor-memory lane quarter this warp may read
+    const bool col_side = warp >= 6;
+    uint8_t* const store_stage = smem + kOffStoreStage + (warp - 2) * 4096;
+    uint32_t boxes = 0;
+    auto put = [&](uint8_t* box, int j, uint4 v) {  // 16-byte piece j of this lane's 64-byte row, swizzled like the tensor map
+      *reinterpret_cast<uint4*>(box + lane * 64 + ((j ^ ((lane >> 1) & 3)) << 4)) = v;
+    };
+    auto open_box = [&]() -> uint8_t* {
+      if (lane == 0) bulk_wait_group_read<1>();  // the store that last read this buffer is done with it
+      __syncwarp();
+      return store_stage + (boxes & 1u) * 2048;
+    };
+    auto close_box = [&](const CUtensorMap* map, uint8_t* box, int x, int y, bool inside) {
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) {
+        if (inside) tma_store_2d(map, box, x, y);  // rows past the end of a partly covered box are clipped
+        bulk_commit_group();                        // always: the buffer rotation counts groups
+      }
+      ++boxes;
+    };
+    ScalePair sp_x = scale_from_absmax(0.0f, p.qx.qmax), sp_w = scale_from_absmax(0.0f, p.qw.qmax);
+    if (PASS == 1) {
+      // launched as a programmatic dependent of pass 0: its abs-maxima are visible once this returns
+      asm volatile("griddepcontrol.wait;" ::: "memory");
+      if (!p.x_row) sp_x = scale_from_absmax(__uint_as_float(p.max_x[0]), p.qx.qmax);
+      if (!p.w_row) sp_w = scale_from_absmax(__uint_as_float(p.max_w[0]), p.qw.qmax);
+      if (blockIdx.x == 0 && warp == 2 && lane == 0) {
+        if (!p.x_row) p.s_x[0] = sp_x.s;
+        if (!p.w_row) p.s_w[0] = sp_w.s;
+      }
+    }
+    float tmax = 0.0f;  // pass 0: this thread's maximum for the per-tensor scale of its side
+    const int64_t out_len = p.L / 2;
+    uint32_t it = 0;
+    bool ok = true;
+    for (int seq = blockIdx.x; seq < num_tiles; seq += gridDim.x, ++it) {
+      const uint32_t buf = it & 1u, bph = (it >> 1) & 1u;
+      ok = __all_sync(0xFFFFFFFFu, mbar_wait(&tmem_full[buf], bph, abort_flag));  // a warp leaves together
+      if (!ok) break;
+      tc_fence_after();
+      const int t = tile_of(seq);
+      const int tt = t / tiles_c, tc = t % tiles_c;
+      const int64_t tok0 = (int64_t)tt * kTok;
+      const int ch0 = tc * kCh;
+      const uint32_t taddr = tmem_base + buf * kBufCols + ((uint32_t)(q * 32) << 16);
+      uint32_t f[32];
+      if (!col_side) {
+        const int64_t tok = tok0 + q * 32 + lane;
+        const bool tok_ok = tok < p.L;
+        if (PASS == 0) {
+          float m = 0.0f;
+#pragma unroll 1
+          for (int c = 0; c < 4; ++c) {
+            tmem_ld32(taddr + 32 * c, f);
+#pragma unroll
+            for (int i = 0; i < 32; ++i) m = fmaxf(m, fabsf(__uint_as_float(f[i])));
+          }
+          if (p.x_row) {
+            if (tok_ok) atomic_absmax(p.max_x + tok, m);
+          } else {
+            tmax = fmaxf(tmax, m);
+          }
+        } else {
+          ScalePair sp = sp_x;
+          if (p.x_row) {
+            sp = scale_from_absmax(tok_ok ? __uint_as_float(p.max_x[tok]) : 0.0f, p.qx.qmax);
+            if (tc == 0 && tok_ok) p.s_x[tok] = sp.s;
+          }
+          const uint64_t e_row = (uint64_t)tok * (uint64_t)p.O + (uint64_t)ch0;
+          uint8_t* box = open_box();
+#pragma unroll 1
+          for (int c = 0; c < 4; ++c) {
+            tmem_ld32(taddr + 32 * c, f);
+            uint32_t out[8];
+            quantise32<RX, X4>(f, sp, p.qx, e_row + 32 * c, true, out);
+            if (X4) {
+              put(box, c, make_uint4(out[0], out[1], out[2], out[3]));
+            } else {
+              // element order of a run is 0-3, 4-7, 8-11, 12-15 = out[0], out[1], out[2], out[3]
+              put(box, 2 * (c & 1), make_uint4(out[0], out[1], out[2], out[3]));
+              put(box, 2 * (c & 1) + 1, make_uint4(out[4], out[5], out[6], out[7]));
+              if (c & 1) {
+                close_box(&tmap_qgo, box, ch0 + 64 * (c >> 1), (int)tok0 + q * 32, tok0 + q * 32 < p.L);
+                if (c == 1) box = open_box();
+              }
+            }
+          }
+          if (X4) close_box(&tmap_qgo, box, ch0 / 2, (int)tok0 + q * 32, tok0 + q * 32 < p.L);
+        }
+      } else {
+        const int ch = ch0 + q * 32 + lane;
+        if (PASS == 0) {
+          float m = 0.0f;
+#pragma unroll 1
+          for (int c = 0; c < 2; ++c) {
+            tmem_ld32(taddr + 128 + 32 * c, f);
+#pragma unroll
+            for (int i = 0; i < 32; ++i) m = fmaxf(m, fabsf(__uint_as_float(f[i])));
+          }
+          if (p.w_row) atomic_absmax(p.max_w + ch, m);
+          else tmax = fmaxf(tmax, m);
+        } else {
+          ScalePair sp = sp_w;
+          if (p.w_row) {
+            sp = scale_from_absmax(__uint_as_float(p.max_w[ch]), p.qw.qmax);
+            if (tt == 0) p.s_w[ch] = sp.s;
+          }
+          const int64_t pos0 = tok0 / 2;  // first stored position of the tile within a row of the transposed operand
+          const uint64_t e_row = (uint64_t)ch * (uint64_t)out_len + (uint64_t)pos0;
+          uint8_t* box = open_box();
+#pragma unroll 1
+          for (int c = 0; c < 2; ++c) {
+            tmem_ld32(taddr + 128 + 32 * c, f);
+            uint32_t out[8];
+            quantise32<RW, false>(f, sp, p.qw, e_row + 32 * c, false, out);
+            put(box, 2 * c, make_uint4(out[0], out[1], out[2], out[3]));
+            put(box, 2 * c + 1, make_uint4(out[4], out[5], out[6], out[7]));
+          }
+          close_box(&tmap_qgw, box, (int)pos0, ch0 + q * 32, true);
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(&tmem_empty[buf]);  // this thread has read all it needs of the accumulator buffer
+    }
+    if (PASS == 0) {
+      tmax = warp_max(tmax);
+      if (lane == 0) {
+        if (!col_side && !p.x_row) atomic_absmax(p.max_x, tmax);
+        if (col_side && !p.w_row) atomic_absmax(p.max_w, tmax);
+      }
+    } else if (lane == 0) {
+      bulk_wait_group<0>();  // the staged boxes have left shared memory and are written
+    }
+  }
+
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");  // the next kernel on the stream may begin to launch
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, kTmemColsTc);
+  }
+  if (threadIdx.x == 0 && *abort_flag) {
+    if (p.status) atomicOr(p.status, 4u);
+    const uint64_t t0 = global_timer_ns();  // let bulk copies already issued land before exit
+    while (global_timer_ns() - t0 < 100000ull) {
+    }
+  }
+}
+
+template <int PASS, int RX, int RW, bool X4>
+int launch_tc_pass(const CUtensorMap& m_in, const CUtensorMap& m_qgo, const CUtensorMap& m_qgw, const TcParams& p, int grid,
+                   cudaStream_t st) {
+  auto kernel = go_dual_tc_kernel<PASS, RX, RW, X4>;
+  static PerDeviceOnce attr_set;  // per instantiation and device
+  bool have_attr = false;
+  const int dev = attr_set.current(&have_attr);
+  if (dev < 0) HOT_FAIL(HOT_ERR_CUDA, "go_dual_quant: cannot query the current CUDA device");
+  if (!have_attr) {
+    HOT_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemTc));
+    attr_set.mark(dev);
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(kThreadsTc);
+  cfg.dynamicSmemBytes = kSmemTc;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = PASS == 1 ? 1 : 0;  // pass 1 may start while pass 0 (the launch before it on this stream) drains
+  HOT_CUDA(cudaLaunchKernelEx(&cfg, kernel, m_in, m_qgo, m_qgw, p));
+  HOT_CUDA(cudaGetLastError());
+  return HOT_OK;
+}
+
+}  // namespace
+
+int device_sm_count();
+
+// Whether the tensor-core kernels cover this configuration (else the caller takes the butterfly kernels).
+bool go_dual_tc_supported(int64_t L, int64_t O, int64_t ldgo, int dtype, int order_o, int order_l, int rank_l,
+                          const int32_t* sel_l, const hot_quant_t& q_gx, const hot_quant_t& q_gw) {
+  if (dtype != HOT_BF16 || order_o != 16 || order_l != 16 || rank_l != 8) return false;
+  for (int j = 0; j < 8; ++j)
+    if (sel_l[j] != kSlotRowHost[j]) return false;
+  return L % 32 == 0 && L < (1ll << 31) && O % kCh == 0 && O <= (1 << 24) && (ldgo * 2) % 16 == 0 &&
+         q_gw.storage == HOT_STORE_INT8 && q_gx.rounding != HOT_ROUND_STOCH_NOISE && q_gw.rounding != HOT_ROUND_STOCH_NOISE;
+}
+
+int go_dual_quant_tc(const void* go, int64_t L, int64_t O, int64_t ldgo, const hot_quant_t& q_gx, const hot_quant_t& q_gw,
+                     void* q_go, int64_t ld_qgo, float* s_gx, void* q_gw_t, int64_t ld_qgw, float* s_gw, uint32_t* max_x,
+                     uint32_t* max_w, uint32_t* status, cudaStream_t st) {
+  TcParams p;
+  p.L = L;
+  p.O = (int)O;
+  p.x_row = q_gx.scale_mode == HOT_SCALE_ROW;
+  p.w_row = q_gw.scale_mode == HOT_SCALE_ROW;
+  p.qx = make_quant_dev(q_gx);
+  p.qw = make_quant_dev(q_gw);
+  p.s_x = s_gx;
+  p.s_w = s_gw;
+  p.max_x = max_x;
+  p.max_w = max_w;
+  p.status = status;
+  const bool x4 = q_gx.storage == HOT_STORE_INT4;
+  CUtensorMap m_in, m_qgo, m_qgw;
+  if (int rc = make_map(&m_in, go, L, O * 2, ldgo * 2, 128, kTok, 128)) return rc;
+  if (int rc = make_map(&m_qgo, q_go, L, x4 ? O / 2 : O, ld_qgo, 64, 32, 64)) return rc;
+  if (int rc = make_map(&m_qgw, q_gw_t, O, L / 2, ld_qgw, 64, 32, 64)) return rc;
+  const int sms = device_sm_count();
+  if (sms <= 0) return HOT_ERR_CUDA;
+  const int num_tiles = (int)(O / kCh) * (int)((L + kTok - 1) / kTok);
+  const int grid = sms < num_tiles ? sms : num_tiles;
+  const size_t nx = p.x_row ? (size_t)L : 1, nw = p.w_row ? (size_t)O : 1;
+  if (max_w >= max_x + nx && (size_t)(max_w - max_x) + nw <= (1u << 18)) {
+    HOT_CUDA(cudaMemsetAsync(max_x, 0, sizeof(uint32_t) * ((size_t)(max_w - max_x) + nw), st));
+  } else {
+    HOT_CUDA(cudaMemsetAsync(max_x, 0, sizeof(uint32_t) * nx, st));
+    HOT_CUDA(cudaMemsetAsync(max_w, 0, sizeof(uint32_t) * nw, st));
+  }
+  if (int rc = launch_tc_pass<0, HOT_ROUND_NEAREST, HOT_ROUND_NEAREST, true>(m_in, m_qgo, m_qgw, p, grid, st)) return rc;
+  const bool px = q_gx.rounding == HOT_ROUND_STOCH_PHILOX, pw = q_gw.rounding == HOT_ROUND_STOCH_PHILOX;
+  constexpr int N = HOT_ROUND_NEAREST, P = HOT_ROUND_STOCH_PHILOX;
+  if (x4) {
+    if (px && pw) return launch_tc_pass<1, P, P, true>(m_in, m_qgo, m_qgw, p, grid, st);
+    if (px) return launch_tc_pass<1, P, N, true>(m_in, m_qgo, m_qgw, p, grid, st);
+    if (pw) return launch_tc_pass<1, N, P, true>(m_in, m_qgo, m_qgw, p, grid, st);
+    return launch_tc_pass<1, N, N, true>(m_in, m_qgo, m_qgw, p, grid, st);
+  }
+  if (px && pw) return launch_tc_pass<1, P, P, false>(m_in, m_qgo, m_qgw, p, grid, st);
+  if (px) return launch_tc_pass<1, P, N, false>(m_in, m_qgo, m_qgw, p, grid, st);
+  if (pw) return launch_tc_pass<1, N, P, false>(m_in, m_qgo, m_qgw, p, grid, st);
+  return launch_tc_pass<1, N, N, false>(m_in, m_qgo, m_qgw, p, grid, st);
+}
+
+}  // namespace hot

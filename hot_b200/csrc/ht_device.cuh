@@ -100,26 +100,27 @@ __device__ __forceinline__ void quantise_store16(const float2 (&v)[8], const Sca
                                                  uint8_t* dst) {
   uint32_t wa0 = 0, wa1 = 0, wb0 = 0, wb1 = 0;  // INT4: wa0 = A, wb0 = B; INT8: (wa0, wa1) = A, (wb0, wb1) = B
   if (ROUND == HOT_ROUND_STOCH_PHILOX) {
-    const uint4 r = philox_block16(q, e0 >> 4);
-    const uint32_t ra[2] = {r.x, r.y}, rb[2] = {r.z, r.w};
-    uint32_t ba[8], bb[8];  // raw bits; the low byte of each is an offset code
+    const bool rb4 = rand_bits(q.qmax) == 4;
+    const float2 mk2 = make_float2(sp.mk, sp.mk), ck2 = make_float2(sp.ck, sp.ck);
+    uint32_t ka[8], kb[8];  // raw bits of RN(x * mk + ck); the low mantissa bits are K
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
-      const float2 t = philox_offset_bits2(v[i], sp, make_float2(philox_u128(ra[i >> 2], i & 3), philox_u128(rb[i >> 2], i & 3)));
-      ba[i] = __float_as_uint(t.x);
-      bb[i] = __float_as_uint(t.y);
+      const float2 t = __ffma2_rn(v[i], mk2, ck2);
+      ka[i] = __float_as_uint(t.x);
+      kb[i] = __float_as_uint(t.y);
     }
-    wa0 = gather_low_bytes(ba[0], ba[1], ba[2], ba[3]);
-    wa1 = gather_low_bytes(ba[4], ba[5], ba[6], ba[7]);
-    wb0 = gather_low_bytes(bb[0], bb[1], bb[2], bb[3]);
-    wb1 = gather_low_bytes(bb[4], bb[5], bb[6], bb[7]);
+    philox_run16(ka, kb, q, e0, rb4, wa0, wa1, wb0, wb1);
     const uint32_t off = (uint32_t)(q.qmax + 1.0f);
-    if (STORE4) {  // A_i is code i, B_i is code i + 8: byte i = A_i | B_i << 4
-      const uint32_t p0 = remove_offset(pack_nibbles(wa0, wb0), off, 0x11111111u, 0x10u);
-      const uint32_t p1 = remove_offset(pack_nibbles(wa1, wb1), off, 0x11111111u, 0x10u);
+    if (STORE4) {  // (always 4 random bits) element i is code i, element i + 8 code i + 8: byte i = code i | code (i + 8) << 4
+      const uint32_t p0 = remove_offset(((wa0 >> 4) & 0x0F0F0F0Fu) | (wb0 & 0xF0F0F0F0u), off, 0x11111111u, 0x10u);
+      const uint32_t p1 = remove_offset(((wa1 >> 4) & 0x0F0F0F0Fu) | (wb1 & 0xF0F0F0F0u), off, 0x11111111u, 0x10u);
       wa0 = p0;
       wb0 = p1;
     } else {
+      if (rb4) {
+        wa0 = (wa0 >> 4) & 0x0F0F0F0Fu; wa1 = (wa1 >> 4) & 0x0F0F0F0Fu;
+        wb0 = (wb0 >> 4) & 0x0F0F0F0Fu; wb1 = (wb1 >> 4) & 0x0F0F0F0Fu;
+      }
       wa0 = remove_offset(wa0, off, 0x01010101u, 0x100u);
       wa1 = remove_offset(wa1, off, 0x01010101u, 0x100u);
       wb0 = remove_offset(wb0, off, 0x01010101u, 0x100u);

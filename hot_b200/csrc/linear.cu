@@ -1,6 +1,7 @@
 // The HOT backward of one linear layer as a sequence of the three kernels, plus the
 // forward-side activation-buffer compression.  All intermediates live in a caller-owned
 // workspace; nothing here allocates or synchronises.
+#include <cstdlib>
 #include <mutex>
 
 #include "common.cuh"
@@ -13,7 +14,31 @@ int go_dual_quant(const void* go, int dtype, int64_t L, int64_t O, int64_t ldgo,
                   const hot_quant_t& q_gx, const hot_quant_t& q_gw, void* q_go, int64_t ld_qgo, float* s_gx, void* q_gw_t,
                   int64_t ld_qgw, float* s_gw, uint32_t* max_x, uint32_t* max_w, uint32_t* status, cudaStream_t st);
 
+bool go_dual_tc_supported(int64_t L, int64_t O, int64_t ldgo, int dtype, int order_o, int order_l, int rank_l,
+                          const int32_t* sel_l, const hot_quant_t& q_gx, const hot_quant_t& q_gw);
+int go_dual_quant_tc(const void* go, int64_t L, int64_t O, int64_t ldgo, const hot_quant_t& q_gx, const hot_quant_t& q_gw,
+                     void* q_go, int64_t ld_qgo, float* s_gx, void* q_gw_t, int64_t ld_qgw, float* s_gw, uint32_t* max_x,
+                     uint32_t* max_w, uint32_t* status, cudaStream_t st);
+
 namespace {
+
+// Which fused grad_out kernels serve a call: the tensor-core pair where it covers the configuration,
+// else the butterfly pair.  HOT_GO_DUAL=butterfly keeps the tensor-core pair out (the parity tests
+// compare the two).
+bool use_tc(int64_t L, int64_t O, int64_t ldgo, const hot_linear_cfg_t& c) {
+  const char* env = getenv("HOT_GO_DUAL");
+  if (env && env[0] == 'b') return false;
+  return go_dual_tc_supported(L, O, ldgo, c.dtype, c.order_o, c.order_l, c.rank_l, c.sel_l, c.q_gx, c.q_gw);
+}
+
+int go_dual_any(const void* go, int64_t L, int64_t O, int64_t ldgo, const hot_linear_cfg_t& c, void* q_go, int64_t ld_qgo,
+                float* s_gx, void* q_gw_t, int64_t ld_qgw, float* s_gw, uint32_t* max_x, uint32_t* max_w, uint32_t* status,
+                cudaStream_t st) {
+  if (use_tc(L, O, ldgo, c))
+    return go_dual_quant_tc(go, L, O, ldgo, c.q_gx, c.q_gw, q_go, ld_qgo, s_gx, q_gw_t, ld_qgw, s_gw, max_x, max_w, status, st);
+  return go_dual_quant(go, c.dtype, L, O, ldgo, c.order_o, c.sel_l, c.q_gx, c.q_gw, q_go, ld_qgo, s_gx, q_gw_t, ld_qgw, s_gw,
+                       max_x, max_w, status, st);
+}
 
 // A helper stream per device, so that the weight quantisation (independent of grad_out) runs
 // beside the grad_out kernels.  Created on first use: make the first call on a device outside
@@ -127,8 +152,8 @@ extern "C" int hot_go_dual_quant(const void* go, int64_t L, int64_t O, int64_t l
   if (ld_qgo < need_x || ld_qgo % 16 || ld_qgw < L / 2 || ld_qgw % 16 || ((uintptr_t)q_go) % 16 || ((uintptr_t)q_gw_t) % 16 ||
       ((uintptr_t)go) % 16)
     HOT_FAIL(HOT_ERR_ARG, "hot_go_dual_quant: buffers and pitches must be 16-byte aligned and cover the codes");
-  return go_dual_quant(go, cfg->dtype, L, O, ldgo, cfg->order_o, cfg->sel_l, cfg->q_gx, cfg->q_gw, q_go, ld_qgo, s_gx, q_gw_t,
-                       ld_qgw, s_gw, scratch, scratch + L, status_word, (cudaStream_t)stream);
+  return go_dual_any(go, L, O, ldgo, *cfg, q_go, ld_qgo, s_gx, q_gw_t, ld_qgw, s_gw, scratch, scratch + L, status_word,
+                     (cudaStream_t)stream);
 }
 
 extern "C" int hot_linear_backward(const void* go, int64_t ldgo, const void* w, int64_t ldw, const void* x_q_t,
@@ -192,9 +217,8 @@ extern "C" int hot_linear_backward(const void* go, int64_t ldgo, const void* w, 
     joined = true;
   };
   if (dual) {
-    rc = go_dual_quant(go, cfg->dtype, L, O, ldgo, cfg->order_o, cfg->sel_l, cfg->q_gx, cfg->q_gw, base + ws.off_qgo,
-                       ws.ld_qgo, s_go, base + ws.off_qgw, ws.ld_qgw, s_gw, scratch + 64, scratch + 64 + L, status_word,
-                       (cudaStream_t)stream);
+    rc = go_dual_any(go, L, O, ldgo, *cfg, base + ws.off_qgo, ws.ld_qgo, s_go, base + ws.off_qgw, ws.ld_qgw, s_gw, scratch + 64,
+                     scratch + 64 + L, status_word, (cudaStream_t)stream);
     if (rc) {
       rejoin();
       return rc;

@@ -177,23 +177,43 @@ def _qmax(bits: int) -> F32:
     return F32(2 ** (bits - 1) - 1)
 
 
+PHILOX_ROUNDS = 7
+_K_MAGIC = 12582912  # 1.5 * 2^23: a float32 in [2^23, 2^24) holds an integer in its low mantissa bits
+
+
+def rand_bits(bits: int) -> int:
+    """Random bits per code of the kernels' production rounding: 4 for codes of up to 4 bits, else 8."""
+    return 4 if bits <= 4 else 8
+
+
 class PhiloxBytes(np.ndarray):
-    """Marker type: one random byte R per element, for the kernels' production rounding path:
-    code = floor(y + B + (R + 0.5) / 256) - B with B = qmax + 1, evaluated in float32 as
-    t1 = fl(y + (B - 128 + 1/512)); t2 = t1 + (128 + R/256) (exact); floor(t2).
-    Plain float arrays keep the reference's predicate  u < frac."""
+    """Marker type (uint16 per element) for the kernels' production rounding path.  The low byte
+    is the element's 8-bit random number R8, the high byte its 4-bit one R4 (see ``philox_bytes``).
+    With RB = rand_bits(bits), R the RB-bit random number, B = qmax + 1, d = s + eps and
+    m = fl(2^RB / d) (one float32 division per scale):
+        K = round_half_even(x * m) + 2^RB * B        (x * m exact: what fl(fma(x, m, 1.5 * 2^23 + 2^RB * B)) leaves
+                                                      in the low mantissa bits)
+        code = ((K + R) >> RB) - B
+    i.e. x / d is rounded to RB fractional bits, a uniform RB-bit integer is added and the sum is
+    floored: it rounds up with probability round(2^RB * frac) / 2^RB, unbiased.  |code| <= qmax holds
+    without a clamp.  Plain float arrays keep the reference's predicate  u < frac."""
 
 
-def _round_codes(y: np.ndarray, u: np.ndarray | None, qmax: F32 = F32(0)) -> np.ndarray:
+def _codes(xc: np.ndarray, d, u, qmax: F32) -> np.ndarray:
+    """Codes of the clamped values ``xc`` for the divisor ``d`` = s + eps (scalar or broadcastable)."""
+    d = np.asarray(d, dtype=F32)
+    if isinstance(u, PhiloxBytes):
+        bits = int(qmax).bit_length() + 1
+        rb = rand_bits(bits)
+        off = int(qmax) + 1
+        m = (F32(1 << rb) / d).astype(F32)
+        k = np.rint(xc.astype(np.float64) * m.astype(np.float64)).astype(np.int64) + (off << rb)
+        r = np.asarray(u).astype(np.int64)
+        r = (r >> 8) & 0xF if rb == 4 else r & 0xFF
+        return (((k + r) >> rb) - off).astype(np.int32)
+    y = (xc / d).astype(F32)
     if u is None:  # torch.round: half to even (utils/quant_matmul.py:47,115)
         return np.rint(y).astype(np.int32)
-    if isinstance(u, PhiloxBytes):
-        off = int(qmax) + 1
-        c0 = F32(F32(off) - F32(128.0) + F32(1.0 / 512.0))
-        t1 = (y.astype(F32) + c0).astype(F32)
-        u128 = (F32(128.0) + np.asarray(u).astype(F32) / F32(256.0)).astype(F32)
-        t2 = (t1 + u128).astype(F32)
-        return (np.floor(t2).astype(np.int64) - off).astype(np.int32)
     a = np.abs(y)
     f = np.floor(a)
     frac = a - f
@@ -207,8 +227,7 @@ def quant_tensor(x: np.ndarray, bits: int, u: np.ndarray | None):
     x = np.asarray(x, dtype=F32)
     mx = np.max(np.abs(x)) if x.size else F32(0)
     s = F32(mx / _qmax(bits))
-    y = np.clip(x, -mx, mx) / F32(s + EPS)
-    return _round_codes(y, u, _qmax(bits)), s
+    return _codes(np.clip(x, -mx, mx), F32(s + EPS), u, _qmax(bits)), s
 
 
 def quant_rows(x: np.ndarray, bits: int, u: np.ndarray | None):
@@ -217,8 +236,7 @@ def quant_rows(x: np.ndarray, bits: int, u: np.ndarray | None):
     x = np.asarray(x, dtype=F32)
     mx = np.max(np.abs(x), axis=1, keepdims=True)
     s = (mx / _qmax(bits)).astype(F32)
-    y = np.clip(x, -mx, mx) / (s + EPS).astype(F32)
-    return _round_codes(y, u, _qmax(bits)), s[:, 0]
+    return _codes(np.clip(x, -mx, mx), (s + EPS).astype(F32), u, _qmax(bits)), s[:, 0]
 
 
 def quant_sawb(x: np.ndarray, bits: int):
@@ -234,16 +252,18 @@ def quant_sawb(x: np.ndarray, bits: int):
 
 
 # ----------------------------------------------------------------------------
-# counter-based uniforms (Philox4x32-10); mirrored bit for bit by the CUDA kernels
+# counter-based random numbers (Philox4x32-7); mirrored bit for bit by the CUDA kernels
 # ----------------------------------------------------------------------------
 _M0, _M1 = np.uint64(0xD2511F53), np.uint64(0xCD9E8D57)
 _W0, _W1 = 0x9E3779B9, 0xBB67AE85
 _MASK = np.uint64(0xFFFFFFFF)
 
 
-def philox4x32_10(c0, c1, c2, c3, k0: int, k1: int):
+def philox4x32(c0, c1, c2, c3, k0: int, k1: int, rounds: int = PHILOX_ROUNDS):
+    """Philox4x32 with ``rounds`` rounds (Salmon et al., "Parallel random numbers: as easy as 1, 2, 3";
+    10 rounds is the paper's default, 7 the fewest it reports as passing BigCrush)."""
     c0, c1, c2, c3 = (np.asarray(c, dtype=np.uint64) for c in (c0, c1, c2, c3))
-    for _ in range(10):
+    for _ in range(rounds):
         p0 = _M0 * c0
         p1 = _M1 * c2
         hi0, lo0 = p0 >> np.uint64(32), p0 & _MASK
@@ -254,18 +274,36 @@ def philox4x32_10(c0, c1, c2, c3, k0: int, k1: int):
     return c0, c1, c2, c3
 
 
+def philox4x32_10(c0, c1, c2, c3, k0: int, k1: int):
+    return philox4x32(c0, c1, c2, c3, k0, k1, 10)
+
+
+def _philox_words(n_blocks: int, seed: int, offset: int) -> np.ndarray:
+    """[n_blocks, 4] output words of the blocks with counter (g_lo, g_hi, offset_lo, offset_hi), key = seed."""
+    g = np.arange(n_blocks, dtype=np.uint64)
+    w = philox4x32(g & _MASK, g >> np.uint64(32), np.uint64(offset & 0xFFFFFFFF), np.uint64((offset >> 32) & 0xFFFFFFFF),
+                   seed & 0xFFFFFFFF, (seed >> 32) & 0xFFFFFFFF)
+    return np.stack(w, axis=1).astype(np.uint64)
+
+
 def philox_bytes(seed: int, offset: int, shape) -> np.ndarray:
-    """The stochastic-rounding byte of every element 0..N-1 of a tensor in row-major order, as a
-    ``PhiloxBytes`` array.  Elements 16g..16g+15 share the Philox block with counter
-    (g_lo, g_hi, offset_lo, offset_hi) and key (seed_lo, seed_hi); element 16g+j takes byte
-    j % 4 (little-endian) of output word j // 4."""
+    """The stochastic-rounding numbers of every element 0..N-1 of a tensor in row-major order, as a
+    ``PhiloxBytes`` array: R8 | R4 << 8 per element.
+    R8 (codes wider than 4 bits): elements 16g..16g+15 share Philox block g; element 16g + j takes
+    byte j % 4 (little-endian) of output word j // 4.
+    R4 (codes of up to 4 bits): elements 32g..32g+31 share block g; with j = e % 32, run h = j // 16
+    and i = j % 16, element e takes nibble i // 8 of byte i % 4 of word 2h + (i % 8) // 4 -- so one
+    word serves elements i..i+3 with its low nibbles and i+8..i+11 with its high ones."""
     n = int(np.prod(shape))
-    g = np.arange((n + 15) // 16, dtype=np.uint64)
-    w = philox4x32_10(g & _MASK, g >> np.uint64(32), np.uint64(offset & 0xFFFFFFFF),
-                      np.uint64((offset >> 32) & 0xFFFFFFFF), seed & 0xFFFFFFFF, (seed >> 32) & 0xFFFFFFFF)
-    words = np.stack(w, axis=1).astype(np.uint64)                                    # [G, 4]
-    by = np.stack([(words >> np.uint64(8 * k)) & np.uint64(0xFF) for k in range(4)], axis=2)   # [G, 4, 4]
-    return by.reshape(-1)[:n].astype(np.uint8).reshape(shape).view(PhiloxBytes)
+    e = np.arange(n, dtype=np.int64)
+    w8 = _philox_words((n + 15) // 16, seed, offset)
+    j = e & 15
+    r8 = (w8[e >> 4, j >> 2] >> (8 * (j & 3)).astype(np.uint64)) & np.uint64(0xFF)
+    w4 = w8[:(n + 31) // 32]
+    i = e & 15
+    word = 2 * ((e >> 4) & 1) + ((i & 7) >> 2)
+    r4 = (w4[e >> 5, word] >> (8 * (i & 3) + 4 * (i >> 3)).astype(np.uint64)) & np.uint64(0xF)
+    return (r8 | (r4 << np.uint64(8))).astype(np.uint16).reshape(shape).view(PhiloxBytes)
 
 
 # ----------------------------------------------------------------------------

@@ -433,6 +433,47 @@ def test_go_dual_quant_matches_the_separate_kernels(ops, dtype, rounding, gx_sca
     assert torch.equal(q_gw[:, :lp], ref_gw[:, :lp])
 
 
+@pytest.mark.parametrize("rounding", ["philox", "nearest"])
+@pytest.mark.parametrize("gx_scale,gw_scale", [("tensor", "tensor"), ("row", "row")])
+@pytest.mark.parametrize("L,O,gx_storage,bits_x,bits_w", [(32 * 21, 384, "int4", 4, 8), (128 * 3 + 96, 128, "int8", 4, 8),
+                                                          (256, 256, "int8", 8, 4), (32, 128, "int4", 3, 6),
+                                                          (128 * 40, 768, "int4", 4, 8)])
+def test_go_dual_quant_tensor_core_transforms(ops, rounding, gx_scale, gw_scale, L, O, gx_storage, bits_x, bits_w):
+    """bf16 grad_out with channel order 16 takes the kernels that run both +-1 transforms on the tensor
+    cores.  Their fp32 sums equal the butterflies' wherever a 16-term sum is exact in fp32; elsewhere a
+    transformed value may differ in its last bit.  So: scales equal to the butterfly kernels' to within
+    one ulp, and where they are bit-equal (the rule) at most a few codes in a million differ, by one."""
+    torch.manual_seed(L * 7 + O)
+    go = (torch.randn(L, O, device="cuda") * 1e-3).to(torch.bfloat16)
+    go[5] *= 30.0
+    go[:, 3] *= 10.0
+    sel = [int(v) for v in oc.lowrank_preset(16, 8)]
+    cfg = ops.LinearConfig(order_o=16, order_l=16, sel_l=sel,
+                           q_gx=ops.Quant(bits_x, gx_storage, rounding, gx_scale, 21, 5),
+                           q_gw=ops.Quant(bits_w, "int8", rounding, gw_scale, 21, 6))
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    q_go, s_gx, q_gw, s_gw = ops.go_dual_quant(go, cfg, status)
+    ref_go, ref_sx = ops.row_ht_quant(go, 16, cfg.q_gx)
+    ref_gw, ref_sw, lp = ops.col_ht_quant(go, 16, sel, cfg.q_gw, "transposed")
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    for got_s, ref_s in ((s_gx, ref_sx), (s_gw, ref_sw)):
+        ulps = (got_s.view(torch.int32).long() - ref_s.view(torch.int32).long()).abs()
+        assert int(ulps.max()) <= 1, "a scale is more than one ulp from the butterfly kernels'"
+    same_x = (s_gx.view(torch.int32) == ref_sx.view(torch.int32))
+    same_w = (s_gw.view(torch.int32) == ref_sw.view(torch.int32))
+    got_x, want_x = _codes_from(q_go, gx_storage, O), _codes_from(ref_go, gx_storage, O)
+    got_w, want_w = _codes_from(q_gw, "int8", lp), _codes_from(ref_gw, "int8", lp)
+    rows_x = same_x.cpu().numpy() if gx_scale == "row" else np.full(L, bool(same_x[0]))
+    rows_w = same_w.cpu().numpy() if gw_scale == "row" else np.full(O, bool(same_w[0]))
+    for got, want, rows in ((got_x, want_x, rows_x), (got_w, want_w, rows_w)):
+        d = np.abs(got[rows] - want[rows])
+        assert d.size == 0 or d.max() <= 1
+        assert d.sum() <= max(2, 1e-5 * d.size), "%d of %d codes differ" % (int(d.sum()), d.size)
+        assert np.abs(got - want).max() <= 1       # rows whose scale moved by an ulp: still neighbours
+    assert rows_x.mean() > 0.99 and rows_w.mean() > 0.99
+
+
 def test_go_dual_quant_rejects_what_it_does_not_cover(ops):
     go = torch.zeros((64, 64), device="cuda")
     cfg = ops.LinearConfig(order_o=16, order_l=32, sel_l=list(oc.wht_selection(6304, 50)[1]))

@@ -257,16 +257,30 @@ def test_precision_scheduler_follows_the_reference(golden):
 
 
 def test_philox_known_answer():
-    # Random123 known-answer vectors for philox4x32-10
+    # Random123 known-answer vectors for philox4x32-10 and philox4x32-7 (the kernels run 7 rounds)
     out = oc.philox4x32_10(0, 0, 0, 0, 0, 0)
     assert [int(v) for v in out] == [0x6627E8D5, 0xE169C58D, 0xBC57AC4C, 0x9B00DBD8]
     out = oc.philox4x32_10(0xFFFFFFFF, 0xFFFFFFFF, 0xFFFFFFFF, 0xFFFFFFFF, 0xFFFFFFFF, 0xFFFFFFFF)
     assert [int(v) for v in out] == [0x408F276D, 0x41C83B0E, 0xA20BC7C6, 0x6D5451FD]
-    r = oc.philox_bytes(1, 2, (3, 7))
-    assert r.shape == (3, 7) and r.dtype == np.uint8 and isinstance(r, oc.PhiloxBytes)
-    first = oc.philox4x32_10(0, 0, 2, 0, 1, 0)
-    assert int(r[0, 0]) == int(first[0]) & 0xFF and int(r[0, 5]) == (int(first[1]) >> 8) & 0xFF
-    # the fixed-point rounding is unbiased: mean code == mean of y to within noise
+    assert oc.PHILOX_ROUNDS == 7
+    out = oc.philox4x32(0, 0, 0, 0, 0, 0)
+    assert [int(v) for v in out] == [0x5F6FB709, 0x0D893F64, 0x4F121F81, 0x4F730A48]
+    out = oc.philox4x32(0xFFFFFFFF, 0xFFFFFFFF, 0xFFFFFFFF, 0xFFFFFFFF, 0xFFFFFFFF, 0xFFFFFFFF)
+    assert [int(v) for v in out] == [0x5207DDC2, 0x45165E59, 0x4D8EE751, 0x8C52F662]
+    out = oc.philox4x32(0x243F6A88, 0x85A308D3, 0x13198A2E, 0x03707344, 0xA4093822, 0x299F31D0)
+    assert [int(v) for v in out] == [0x4DFCCABA, 0x190A87F0, 0xC47362BA, 0xB6B5242A]
+    r = oc.philox_bytes(1, 2, (3, 40))
+    assert r.shape == (3, 40) and r.dtype == np.uint16 and isinstance(r, oc.PhiloxBytes)
+    first = oc.philox4x32(0, 0, 2, 0, 1, 0)
+    flat = np.asarray(r).reshape(-1)
+    assert int(flat[0]) & 0xFF == int(first[0]) & 0xFF and int(flat[5]) & 0xFF == (int(first[1]) >> 8) & 0xFF
+    # 4-bit numbers: elements 0..3 / 8..11 of a run take the low / high nibbles of the bytes of one word
+    assert int(flat[2]) >> 8 == (int(first[0]) >> 16) & 0xF and int(flat[10]) >> 8 == (int(first[0]) >> 20) & 0xF
+    assert int(flat[5]) >> 8 == (int(first[1]) >> 8) & 0xF and int(flat[16 + 13]) >> 8 == (int(first[3]) >> 12) & 0xF
+    # the fixed-point rounding is unbiased: mean code == mean of y to within noise, for both widths
     y = np.random.default_rng(0).uniform(-7, 7, 200000).astype(np.float32)
-    c, s = oc.quant_tensor(y, 4, oc.philox_bytes(3, 4, y.shape))
-    assert abs(float(np.mean(c - y / (s + oc.EPS)))) < 5e-3 and np.abs(c).max() <= 7
+    for bits in (4, 8):
+        c, s = oc.quant_tensor(y, bits, oc.philox_bytes(3, 4, y.shape))
+        q = y / (s + oc.EPS)
+        assert abs(float(np.mean(c - q))) < 5e-3 and np.abs(c).max() <= 2 ** (bits - 1) - 1
+        assert np.all(np.abs(c - q) < 1.0 + 2.0 ** -oc.rand_bits(bits))       # floor or ceil of the quotient
