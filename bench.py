@@ -264,7 +264,7 @@ def run_hot(a):
         if not a.no_kernels:
             out["kernels"], out["roofline"], out["fp_backward_bf16_cublas"] = kernel_legs(ops, layers, a, dtype, device, pk, status)
         if not a.no_cpu_baseline:
-            out["cpu_baseline"] = cpu_baseline(threads=1)
+            out["cpu_baseline"] = cpu_baseline(threads=os.cpu_count() or 1)
     out["e2e"] = e2e_leg(layers, a, dtype, device, flops, world) if a.e2e_steps > 0 else None   # every rank takes part
     if rank == 0:
         print(json.dumps(out), flush=True)
@@ -751,10 +751,26 @@ def cpu_layer_seconds(tokens, i_f, o_f, seed=0):
 
 
 def cpu_baseline(threads):
-    """Oracle port of the reference's fake-quant backward on a bounded sample: one fc1 layer
-    (768 -> 3072) at 6,304 tokens, float32."""
-    from threadpoolctl import threadpool_limits
+    """The reference's own fake-quant backward on the host cores, on a bounded sample: one fc1 layer
+    (768 -> 3072) at 6,304 tokens, float32 (the single-layer configuration).  Runs
+    ``oracle/reference_arm.py`` as a child process (the reference's top-level ``args`` / ``utils``
+    modules stay out of this interpreter); falls back to the numpy port when ``oracle/_ref`` is absent."""
+    import subprocess
     tokens, (name, i_f, o_f) = 6304, LAYERS[2]
+    root = os.path.dirname(os.path.abspath(__file__))
+    if os.path.isfile(os.path.join(root, "oracle", "_ref", "utils", "quant_matmul.py")):
+        r = subprocess.run([sys.executable, os.path.join(root, "oracle", "reference_arm.py"), "--tokens", str(tokens), "--layers",
+                            "fc1", "--steps", "5", "--warmup", "1", "--threads", str(threads)], capture_output=True, text=True,
+                           timeout=600)
+        try:
+            d = json.loads(r.stdout.strip().splitlines()[-1])
+            return {"value": round(d["effective_tops"], 5), "unit": UNIT, "cores": d["threads"], "kind": "reference",
+                    "seconds": round(d["seconds_per_step"], 3),
+                    "sample": "one fc1 (768->3072) backward at 6304 tokens, fp32: the reference's HQ_Linear (utils/quant_matmul.py) "
+                              "with its own low-rank basis (10 of 32 rows), stoch quantisers, median of 5 after 1 warm-up"}
+        except Exception:                                 # fall through to the port, and say so
+            pass
+    from threadpoolctl import threadpool_limits
     with threadpool_limits(limits=threads):
         cpu_layer_seconds(256, i_f, o_f)
         sec = cpu_layer_seconds(tokens, i_f, o_f)
@@ -765,30 +781,51 @@ def cpu_baseline(threads):
 
 
 def run_reference(a):
-    """The reference arm: the CPU restatement of the reference's own implementation of the path,
-    all host threads, on a bounded sample of the workload; rank 0 only."""
+    """The reference arm: the reference's own CPU implementation of the path (``HQ_Linear`` of
+    utils/quant_matmul.py, imported unmodified from ``oracle/_ref``) on all host threads; a step is one
+    backward of each of the four layer shapes at the workload's token count, i.e. one of the 12
+    transformer blocks (the token count is halved until a run of steps + warm-up fits a few minutes).
+    Falls back to the numpy port where ``oracle/_ref`` is absent.  Rank 0 only."""
     if int(os.environ.get("RANK", 0)) != 0:
         return
     threads = os.cpu_count() or 1
-    tokens = 1600                                     # about 1/8 of the workload's tokens per layer shape
-    for _, i_f, o_f in LAYERS:
-        cpu_layer_seconds(64, i_f, o_f)
-    for _ in range(max(a.warmup, 0)):
+    root = os.path.dirname(os.path.abspath(__file__))
+    sys.path.insert(0, root)
+    kind = "port"
+    names = [n for n, _, _ in LAYERS]
+    tokens = a.tokens
+    if os.path.isfile(os.path.join(root, "oracle", "_ref", "utils", "quant_matmul.py")):
+        from oracle import reference_arm
+        kind = "reference"
+        probe = reference_arm.run(1576, names, 1, 1, threads)["seconds_per_step"]       # 1/8 of the tokens
+        budget = 200.0 / max(a.steps + max(a.warmup, 1), 1)
+        while tokens > 1576 and probe * (tokens / 1576.0) > budget:
+            tokens //= 2
+        res = reference_arm.run(tokens, names, a.steps, a.warmup, threads)
+        sec = res["seconds_per_step"]
+        how = "the reference's HQ_Linear (utils/quant_matmul.py, unmodified, from oracle/_ref), its own low-rank basis"
+    else:
+        tokens = 1600
         for _, i_f, o_f in LAYERS:
-            cpu_layer_seconds(tokens, i_f, o_f)
-    t0 = time.perf_counter()
-    for _ in range(a.steps):
-        for _, i_f, o_f in LAYERS:
-            cpu_layer_seconds(tokens, i_f, o_f)
-    sec = (time.perf_counter() - t0) / a.steps
+            cpu_layer_seconds(64, i_f, o_f)
+        for _ in range(max(a.warmup, 0)):
+            for _, i_f, o_f in LAYERS:
+                cpu_layer_seconds(tokens, i_f, o_f)
+        t0 = time.perf_counter()
+        for _ in range(a.steps):
+            for _, i_f, o_f in LAYERS:
+                cpu_layer_seconds(tokens, i_f, o_f)
+        sec = (time.perf_counter() - t0) / a.steps
+        how = "oracle/hot_oracle.py (numpy restatement; oracle/_ref absent)"
     flops = float(sum(4 * tokens * o * i for _, i, o in LAYERS))
     value = round(flops / sec / 1e12, 5)
-    sample = "per step: one layer of each of the 4 shapes at 1600 tokens (about 1/8 of the tokens, 1/12 of the blocks), fp32"
+    sample = ("per step: one backward of each of the 4 layer shapes (one of the 12 blocks) at %d tokens, fp32, %s"
+              % (tokens, how))
     print(json.dumps({"impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": a.gpus,
                       "steps": a.steps, "warmup": a.warmup, "ms_per_step": round(sec * 1e3, 3), "higher_is_better": True,
                       "scaling": "weak", "vs_baseline": None, "dtype": "f32 holding integer codes", "data": "synthetic",
                       "config": {"workload": WORKLOAD, "sample": sample},
-                      "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample},
+                      "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": kind, "sample": sample},
                       "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}), flush=True)
 
 
