@@ -56,6 +56,11 @@ def parse():
                         "byte and expanded in shared memory, one per byte, or (default) the library's policy "
                         "ops.gx_code_storage: packed where the contraction is longer than 1024")
     p.add_argument("--no-cpu-baseline", action="store_true")
+    p.add_argument("--sm-margin", type=int, default=-1,
+                   help="SMs left out of the persistent kernels' grids for the all-reduce kernels (multi-GPU; -1: 8 when N > 1)")
+    p.add_argument("--bucket-blocks", type=int, default=3, help="transformer blocks per all-reduce bucket (multi-GPU)")
+    p.add_argument("--dp-breakdown", action="store_true",
+                   help="multi-GPU: also time the step without the all-reduces and the all-reduces alone")
     p.add_argument("--no-kernels", action="store_true", help="skip the per-kernel roofline legs")
     p.add_argument("--sweep", action="store_true",
                    help="instead of the step: the stand-alone fused Hadamard+quantise sweep (M x K x order x "
@@ -183,8 +188,12 @@ def run_hot(a):
         raise SystemExit("bench.py needs a CUDA device: the HOT kernels have no CPU path")
     torch.cuda.set_device(local)
     device = torch.device("cuda", local)
+    margin = (8 if world > 1 else 0) if a.sm_margin < 0 else a.sm_margin
     if world > 1:
+        if margin > 0:
+            os.environ.setdefault("NCCL_MAX_CTAS", str(margin))   # the collective's kernels fit the SMs left free for them
         dist.init_process_group("nccl", device_id=device)
+    ops.set_sm_margin(margin)
     dtype = torch.bfloat16 if a.dtype == "bf16" else torch.float32
     pk = peaks()
     layers = build_layers(ops, a.tokens, a.blocks, dtype, device, rank, a.gx_storage)
@@ -193,13 +202,17 @@ def run_hot(a):
     # grad_w lands in one flat bucket per block, the unit of the all-reduce
     from hot_b200.dp import GradBuckets
     gx_buf = {i_f: torch.empty((a.tokens, i_f), dtype=dtype, device=device) for _, i_f, _ in LAYERS}
-    grads = GradBuckets([[(o_f, i_f) for _, i_f, o_f in LAYERS] for _ in range(a.blocks)], dtype, device)
+    # a bucket holds the grad_w of `per` consecutive blocks: fewer, larger collectives
+    per = max(1, min(a.bucket_blocks, a.blocks))
+    n_buckets = (a.blocks + per - 1) // per
+    grads = GradBuckets([[(o_f, i_f) for b in range(j * per, min((j + 1) * per, a.blocks)) for _, i_f, o_f in LAYERS]
+                         for j in range(n_buckets)], dtype, device)
 
     def block_backward(b):
         for li in reversed(range(len(LAYERS))):
             l = layers[b][li]
             ops.linear_backward(l["go"], l["w"], l["x_q_t"], l["s_x"], l["cfg"], status=status,
-                                gx_out=gx_buf[l["I"]], gw_out=grads.view(b, li))
+                                gx_out=gx_buf[l["I"]], gw_out=grads.view(b // per, (b % per) * len(LAYERS) + li))
 
     # one CUDA graph per transformer block: launch overhead off the critical path, and the
     # all-reduce of a block's bucket can be enqueued between graph launches
@@ -216,10 +229,16 @@ def run_hot(a):
             graphs.append(g)
     torch.cuda.synchronize(device)
 
-    def step():
+    def step(reduce=True):
         for b in reversed(range(a.blocks)):
             graphs[b].replay()
-            grads.reduce_async(b)
+            if reduce and b % per == 0:            # the bucket's last block (blocks run from the top down) is enqueued
+                grads.reduce_async(b // per)
+        grads.wait_all()
+
+    def reduce_only():
+        for j in reversed(range(n_buckets)):
+            grads.reduce_async(j)
         grads.wait_all()
 
     def sync_all():
@@ -243,6 +262,21 @@ def run_hot(a):
         dist.all_reduce(ms, op=dist.ReduceOp.MAX)
     clocks = sampler.stop() if sampler else None
     ms_step = float(ms.item()) / a.steps
+    breakdown = None
+    if world > 1 and a.dp_breakdown:
+        def timed(fn):
+            sync_all()
+            t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            t0.record()
+            for _ in range(a.steps):
+                fn()
+            t1.record()
+            sync_all()
+            v = torch.tensor([t0.elapsed_time(t1)], device=device)
+            dist.all_reduce(v, op=dist.ReduceOp.MAX)
+            return round(float(v.item()) / a.steps, 4)
+        breakdown = {"ms_step_without_all_reduce": timed(lambda: step(False)), "ms_all_reduce_alone": timed(reduce_only),
+                     "ms_step": round(ms_step, 4)}
     if int(status.item()) != 0:
         raise SystemExit("a bounded device-side wait ran out during the benchmark (status %d)" % int(status.item()))
     flops = step_flops(a.tokens, a.blocks)
@@ -257,7 +291,11 @@ def run_hot(a):
                       "hadamard_order": 16, "low_rank": "8 of 16 (lowest sequency)", "g_x": "INT4 x INT4, per-tensor, Philox stochastic" + {"int4": "; grad_out codes packed", "int8": "; grad_out codes stored one per byte", "auto": "; grad_out codes packed for qkv and fc1 (contraction > 1024), one per byte for proj and fc2"}[a.gx_storage],
                       "g_w": "INT8 x INT8, per-tensor, Philox stochastic", "activation_buffer": "compressed in forward (not timed)",
                       "cache": "inputs 2.1 GB per GPU, distinct per layer (> 126 MB L2)",
-                      "parallelism": "dp%d, grad_w all-reduce (NCCL) per block" % world if world > 1 else "single GPU"}}
+                      "parallelism": ("dp%d, grad_w all-reduce (NCCL) in %d buckets of %d blocks (%.1f MB each), %d SMs left to "
+                                      "the collective" % (world, n_buckets, per, grads.message_bytes() / n_buckets / 1e6, margin))
+                      if world > 1 else "single GPU"}}
+    if breakdown:
+        out["dp_breakdown"] = breakdown
     if clocks:
         out["clocks"] = clocks
     if rank == 0 and world == 1:
@@ -607,7 +645,10 @@ def kernel_legs(ops, layers, a, dtype, device, pk, status):
     t_layer = _graph_time(lambda i: ops.linear_backward(fc1[i % n]["go"], fc1[i % n]["w"], fc1[i % n]["x_q_t"], fc1[i % n]["s_x"], cfg, status=status), n, device)
     xs = [torch.randn((L, I), device=device).to(dtype) for _ in range(2)]
     t_fp = _graph_time(lambda i: (torch.matmul(fc1[i % n]["go"], fc1[i % n]["w"]), torch.matmul(fc1[i % n]["go"].t(), xs[i % 2])), n, device)
-    int8_peak = 2.0 * pk["bf16"]   # no measured INT8 figure: nominal INT8 is twice the bf16 rate
+    # the INT8 ceiling the GEMM fractions are quoted against: measured here, in this run, on a square 8192^3
+    # problem by the library GEMM (torch._int_mm) and by this repo's kernel; the larger of the two
+    int8 = int8_ceiling(ops, device, status)
+    int8_peak = max(int8["torch_int_mm_tops"] or 0.0, int8["hot_gemm_i8_tops"] or 0.0) or 2.0 * pk["bf16"]
     for k, v in kern.items():
         v["us"] = round(v["us"], 2)
         if v["bound"] == "hbm":
@@ -626,11 +667,31 @@ def kernel_legs(ops, layers, a, dtype, device, pk, status):
             "bound": tk["bound"], "achieved": tk["achieved"], "peak": tk["peak"], "unit": tk["unit"],
             "frac": tk["frac"], "traffic": traffic, "launch_us": tk["us"],
             "peak_source": ("%s hbm_gbs" % pk["source"]) if tk["bound"] == "hbm" else
-                           ("2 x %s bf16_tflops (no measured INT8 peak; nominal INT8:bf16 = 2)" % pk["source"]),
+                           "INT8 ceiling measured in this run at 8192^3 (max of torch._int_mm and hot_gemm_i8)",
             "share_of_fc1_layer": round(tk["us"] / t_layer, 3)}
+    kern["int8_ceiling_8192"] = int8
     fp = {"fc1_hot_us": round(t_layer, 2), "fc1_bf16_matmul_us": round(t_fp, 2), "speedup": round(t_fp / t_layer, 3),
           "dtype": a.dtype, "config1_fp32": config1_leg(ops, device, status)}
     return kern, roof, fp
+
+
+def int8_ceiling(ops, device, status):
+    """Dense INT8 throughput on an 8192 x 8192 x 8192 problem: torch._int_mm (the library GEMM) and this
+    repo's hot_gemm_i8 (raw int32 output), TOP/s each (None where a path is not available)."""
+    n = 8192
+    a = torch.randint(-8, 8, (n, n), device=device, dtype=torch.int8)
+    b = torch.randint(-8, 8, (n, n), device=device, dtype=torch.int8)
+    out = {"torch_int_mm_tops": None, "hot_gemm_i8_tops": None, "ops": 2 * n ** 3}
+    try:
+        bt = b.t()                                                       # column-major second operand
+        t = _graph_time(lambda i: torch._int_mm(a, bt), 4, device)
+        out["torch_int_mm_tops"] = round(2.0 * n ** 3 / t / 1e6, 1)
+    except Exception as e:                                               # pragma: no cover
+        out["torch_int_mm_error"] = str(e)[:120]
+    au, bu = a.view(torch.uint8), b.view(torch.uint8)
+    t = _graph_time(lambda i: ops.gemm_i8(au, "int8", bu, "int8", n, n, n, None, None, out_dtype=torch.int32, status=status), 4, device)
+    out["hot_gemm_i8_tops"] = round(2.0 * n ** 3 / t / 1e6, 1)
+    return out
 
 
 def config1_leg(ops, device, status):

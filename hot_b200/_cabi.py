@@ -47,6 +47,11 @@ EXPORTS = {
     "hot_status_string": (ctypes.c_char_p, [ctypes.c_int]),
     "hot_last_error": (ctypes.c_char_p, []),
     "hot_abi_version": (ctypes.c_int, []),
+    "hot_set_sm_margin": (None, [ctypes.c_int]),
+    "hot_set_wait_limit_ns": (None, [ctypes.c_uint64]),
+    "hot_get_wait_limit_ns": (ctypes.c_uint64, []),
+    "hot_wait_probe": (ctypes.c_int, [c_vp, c_vp]),
+    "hot_check_status": (ctypes.c_int, [ctypes.c_uint32]),
     "hot_row_ht_quant": (ctypes.c_int, [c_vp, ctypes.c_int, c_i64, c_i64, c_i64, ctypes.c_int, ctypes.POINTER(HotQuant),
                                         c_vp, c_i64, c_vp, c_vp, c_vp]),
     "hot_col_ht_quant": (ctypes.c_int, [c_vp, ctypes.c_int, c_i64, c_i64, c_i64, ctypes.c_int, ctypes.POINTER(c_i32),

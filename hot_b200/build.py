@@ -19,7 +19,7 @@ ROOT = os.path.dirname(HERE)
 CSRC = os.path.join(HERE, "csrc")
 LIB_DIR = os.path.join(HERE, "lib")
 LIB_PATH = os.path.join(LIB_DIR, "libhot_b200.so")
-SOURCES = ["common.cu", "row_ht_quant.cu", "col_ht_quant.cu", "go_dual.cu", "go_dual_tc.cu", "gemm_i8.cu", "linear.cu"]
+SOURCES = ["common.cu", "status.cu", "row_ht_quant.cu", "col_ht_quant.cu", "go_dual.cu", "go_dual_tc.cu", "gemm_i8.cu", "linear.cu"]
 NVCC_FLAGS = ["-std=c++17", "-O3", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo",
               "-Xcompiler", "-fPIC", "--cudart", "static"]
 

@@ -338,17 +338,43 @@ __global__ void __launch_bounds__(kThreads) col_ht_quant_kernel(const T* __restr
       // (one block serves 16 elements with 8 random bits each, or 32 with 4 bits each)
       const int rb = rand_bits(q.qmax);
       const int shift = rb == 4 ? 5 : 4;
-      uint64_t g = e0 >> shift;
-      uint4 blk = philox_block(q, g);
+      if ((e0 & 7u) == 0) {
+        // aligned run of 8: its random numbers are the bytes (or the low / high nibbles of the bytes) of two
+        // words of one block, so they are added to the K values four at a time in packed lanes
+        const uint4 blk = philox_block(q, e0 >> shift);
+        uint32_t kk[8];
 #pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const uint64_t e = e0 + (uint64_t)i;
-        if ((e >> shift) != g) {  // the run crossed into the next block (unaligned row starts only)
-          g = e >> shift;
-          blk = philox_block(q, g);
+        for (int i = 0; i < 8; ++i) kk[i] = philox_kbits(v[i], sp);
+        uint32_t c0, c1;  // four offset codes each, one per byte
+        if (rb == 4) {
+          const bool hi = (e0 & 16u) != 0;
+          const int nib = (int)((e0 >> 3) & 1u) * 4;
+          const uint32_t r0 = ((hi ? blk.z : blk.x) >> nib) & 0x0F0F0F0Fu, r1 = ((hi ? blk.w : blk.y) >> nib) & 0x0F0F0F0Fu;
+          c0 = (offset_sums4_rb4(kk[0], kk[1], kk[2], kk[3], r0) >> 4) & 0x0F0F0F0Fu;
+          c1 = (offset_sums4_rb4(kk[4], kk[5], kk[6], kk[7], r1) >> 4) & 0x0F0F0F0Fu;
+        } else {
+          const bool hi = (e0 & 8u) != 0;
+          c0 = offset_codes4_rb8(kk[0], kk[1], kk[2], kk[3], hi ? blk.z : blk.x);
+          c1 = offset_codes4_rb8(kk[4], kk[5], kk[6], kk[7], hi ? blk.w : blk.y);
         }
-        const uint32_t r = rb == 4 ? philox_r4(blk, e) : philox_r8(blk, e);
-        code[i] = (int)philox_offset_code(v[i], sp, r, rb) - (qmax + 1);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          code[i] = (int)((c0 >> (8 * i)) & 0xFFu) - (qmax + 1);
+          code[i + 4] = (int)((c1 >> (8 * i)) & 0xFFu) - (qmax + 1);
+        }
+      } else {
+        uint64_t g = e0 >> shift;
+        uint4 blk = philox_block(q, g);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const uint64_t e = e0 + (uint64_t)i;
+          if ((e >> shift) != g) {  // the run crossed into the next block (unaligned row starts only)
+            g = e >> shift;
+            blk = philox_block(q, g);
+          }
+          const uint32_t r = rb == 4 ? philox_r4(blk, e) : philox_r8(blk, e);
+          code[i] = (int)philox_offset_code(v[i], sp, r, rb) - (qmax + 1);
+        }
       }
     } else {
       float u[8];

@@ -28,13 +28,27 @@ int validate_quant(const hot_quant_t* q, const char* who) {
   return HOT_OK;
 }
 
+namespace {
+std::atomic<uint64_t> g_wait_limit_ns{1500ull * 1000ull * 1000ull};
+}
+uint64_t wait_limit_ns() { return g_wait_limit_ns.load(std::memory_order_relaxed); }
+void set_wait_limit_ns(uint64_t ns) { g_wait_limit_ns.store(ns, std::memory_order_relaxed); }
+
+namespace {
+std::atomic<int> g_sm_margin{0};
+}
+void set_sm_margin(int sms) { g_sm_margin.store(sms < 0 ? 0 : sms, std::memory_order_relaxed); }
+
+// SMs the persistent kernels size their grids to: those of the current device, less the margin a caller
+// asked to be left free (for a communication library's kernels that run beside them).
 int device_sm_count() {
   int dev = 0, sms = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) {
     set_error("cannot query the current CUDA device");
     return -1;
   }
-  return sms;
+  const int left = sms - g_sm_margin.load(std::memory_order_relaxed);
+  return left < 1 ? 1 : left;
 }
 
 namespace {

@@ -45,6 +45,7 @@ struct GemmParams {
   int64_t ldo;
   int out_dtype;
   uint32_t* status;
+  uint64_t wait_ns;  // time limit of a device-side wait
   int staged;  // the output qualifies for bulk tensor stores (16-byte aligned base and pitch)
   // stream-K: CTAs take equal contiguous ranges of (tile, k-block) units; a tile cut by a range
   // boundary is finished by whichever contributor arrives last
@@ -476,7 +477,7 @@ __global__ void __launch_bounds__(kEpiThreads + 64 + ((A4 || B4) ? kUnpackThread
         const int nt = seg.prob ? n_tiles2 : n_tiles;
         const int m0 = (seg.ltile / nt) * kTileM + (int)rank * kBM, n0 = (seg.ltile % nt) * BN;
         for (int kb = seg.kb0; kb < seg.kb1; ++kb, s = (s + 1 == STAGES ? 0 : s + 1), ph ^= (s == 0 ? 1u : 0u)) {
-          ok = mbar_wait(&empty[s], ph ^ 1u, abort_flag);
+          ok = mbar_wait(&empty[s], ph ^ 1u, abort_flag, p.wait_ns);
           if (!ok) break;
           if (seg.prob) {  // rider: both operands one code per byte
             mbar_expect_tx(&full[s], L::kA + L::kB);
@@ -517,13 +518,13 @@ __global__ void __launch_bounds__(kEpiThreads + 64 + ((A4 || B4) ? kUnpackThread
       const uint32_t a_lo0 = (uint32_t)smem_desc_sw128(smem_u32(sA)), b_lo0 = (uint32_t)smem_desc_sw128(smem_u32(sB));
       for (; ok && iter.next(seg); ++it) {
         const uint32_t buf = it & 1u, bph = (it >> 1) & 1u;
-        ok = mbar_wait<PAIR>(&tmem_empty[buf], bph ^ 1u, abort_flag);  // epilogue (of both CTAs) drained this buffer
+        ok = mbar_wait<PAIR>(&tmem_empty[buf], bph ^ 1u, abort_flag, p.wait_ns);  // epilogue (of both CTAs) drained this buffer
         if (!ok) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + buf * kBufStride;
         for (int kb = seg.kb0; kb < seg.kb1; ++kb, s = (s + 1 == STAGES ? 0 : s + 1), ph ^= (s == 0 ? 1u : 0u)) {
-          ok = kUnpack ? mbar_wait<PAIR>(&ready[s], ph, abort_flag) : mbar_wait(&full[s], ph, abort_flag);
-          if (ok && PAIR && kUnpack) ok = mbar_wait(&full[s], ph, abort_flag);  // B landed in both CTAs
+          ok = kUnpack ? mbar_wait<PAIR>(&ready[s], ph, abort_flag, p.wait_ns) : mbar_wait(&full[s], ph, abort_flag, p.wait_ns);
+          if (ok && PAIR && kUnpack) ok = mbar_wait(&full[s], ph, abort_flag, p.wait_ns);  // B landed in both CTAs
           if (!ok) break;
           tc_fence_after();
           const uint32_t a_lo = a_lo0 + s * (uint32_t)(L::kA >> 4), b_lo = b_lo0 + s * (uint32_t)(L::kB >> 4);
@@ -686,7 +687,7 @@ __global__ void __launch_bounds__(kEpiThreads + 64 + ((A4 || B4) ? kUnpackThread
       const bool whole = seg.kb0 == 0 && seg.kb1 == p.num_kb;
       // partial slot: [chunk of 32 columns][group of 4 columns][row][4] int32, so that a warp's rows are contiguous
       int32_t* my_slot = p.sk_partials + (size_t)(2 * blockIdx.x + (seg.first ? 0 : 1)) * kBM * BN + row_loc * 4;
-      ok = mbar_wait(&tmem_full[buf], bph, abort_flag);
+      ok = mbar_wait(&tmem_full[buf], bph, abort_flag, p.wait_ns);
       if (!ok) break;
       tc_fence_after();
       const uint32_t t_addr = tmem_base + buf * kBufStride + ((uint32_t)(q * 32) << 16);
@@ -777,7 +778,7 @@ __global__ void __launch_bounds__(kEpiThreads + 64 + ((A4 || B4) ? kUnpackThread
                   for (int g = 0; g < ng; ++g)
                     bulk_load(smem + (size_t)(k * ng + g) * (32 * kBM * 4), slot_of(c_lo + k) + (size_t)(c0 + g) * (32 * kBM), 32 * kBM * 4, fix_bar);
               }
-              if (!mbar_wait(fix_bar, fph, abort_flag)) break;
+              if (!mbar_wait(fix_bar, fph, abort_flag, p.wait_ns)) break;
               fph ^= 1u;
               for (int g = 0; g < ng; ++g) {
                 if (!owns(c0 + g)) continue;
@@ -835,7 +836,7 @@ __global__ void __launch_bounds__(kEpiThreads + 64 + ((A4 || B4) ? kUnpackThread
     Segment seg;
     while (ok && iter.next(seg)) {
       for (int kb = seg.kb0; kb < seg.kb1; ++kb, s = (s + 1 == STAGES ? 0 : s + 1), ph ^= (s == 0 ? 1u : 0u)) {
-        ok = mbar_wait(PAIR ? &full_a[s] : &full[s], ph, abort_flag);
+        ok = mbar_wait(PAIR ? &full_a[s] : &full[s], ph, abort_flag, p.wait_ns);
         if (!ok) break;
         if constexpr (A4) {
           if (!seg.prob) unpack_stage<kBM>(sA + s * L::kA, utid);
@@ -863,7 +864,7 @@ __global__ void __launch_bounds__(kEpiThreads + 64 + ((A4 || B4) ? kUnpackThread
     else tmem_dealloc(tmem_base, kTmemCols);
   }
   if (threadIdx.x == 0 && *abort_flag) {
-    if (p.status) atomicOr(p.status, 1u);
+    if (p.status) atomicOr(p.status, (uint32_t)HOT_STATUS_GEMM);
     // bulk copies issued before the abort land within microseconds; give them time before the
     // shared memory of this CTA is released
     const uint64_t t0 = global_timer_ns();
@@ -1098,6 +1099,7 @@ extern "C" int hot_gemm_i8_ws(const void* a, int a_storage, int64_t lda, const v
   p.ldo = ldo;
   p.out_dtype = out_dtype;
   p.status = status_word;
+  p.wait_ns = wait_limit_ns();
   cudaStream_t st = (cudaStream_t)stream;
   const int sms = device_sm_count();
   if (sms <= 0) return HOT_ERR_CUDA;
@@ -1161,6 +1163,7 @@ extern "C" int hot_gemm_i8_grouped(const void* a, int64_t lda, const void* b, in
   p.ldo = ldo;
   p.out_dtype = out_dtype;
   p.status = status_word;
+  p.wait_ns = wait_limit_ns();
   p.stream_k = 0;
   p.sk_partials = nullptr;
   p.sk_counters = nullptr;
@@ -1236,6 +1239,7 @@ extern "C" int hot_gemm_i8_dual(const hot_gemm_problem_t* main_problem, const ho
   if (int rc = fill_problem(main_problem, true, &p0, "main problem")) return rc;
   if (int rc = fill_problem(rider_problem, false, &p1, "rider problem")) return rc;
   p0.status = p1.status = status_word;
+  p0.wait_ns = p1.wait_ns = wait_limit_ns();
   cudaStream_t st = (cudaStream_t)stream;
   const int sms = device_sm_count();
   if (sms <= 0) return HOT_ERR_CUDA;

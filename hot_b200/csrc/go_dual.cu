@@ -41,6 +41,7 @@ struct DualParams {
   uint32_t* max_x;         // [1] or [L]
   uint32_t* max_w;         // [1] or [O]
   uint32_t* status;
+  uint64_t wait_ns;        // time limit of a device-side wait
 };
 
 template <typename T>
@@ -215,7 +216,9 @@ __global__ void __launch_bounds__(kThreads, sizeof(T) == 2 ? 3 : 1) go_dual_kern
     const int s = it & 1;
     const int next = t_idx + gridDim.x;
     if (tid == 0 && next < num_tiles) issue(next, s ^ 1);  // stage s^1 was released by the barrier below
-    ok = mbar_wait(&full[s], (it >> 1) & 1u, abort_flag);
+    // the whole CTA leaves the tile loop together when a wait ran out (a thread that saw the barrier complete
+    // in time must not go on to the __syncthreads below while others have left)
+    ok = __syncthreads_and(mbar_wait(&full[s], (it >> 1) & 1u, abort_flag, p.wait_ns)) != 0;
     if (!ok) break;
     const uint8_t* tl = smem + s * Tile<T>::kBytes;
     const int tt = t_idx / tiles_c, tc = t_idx % tiles_c;
@@ -348,7 +351,7 @@ __global__ void __launch_bounds__(kThreads, sizeof(T) == 2 ? 3 : 1) go_dual_kern
       if (lane == 0) atomic_absmax(p.max_w, tmax_w);
     }
   }
-  if (!ok && tid == 0 && p.status) atomicOr(p.status, 2u);
+  if (!ok && tid == 0 && p.status) atomicOr(p.status, (uint32_t)HOT_STATUS_GO_DUAL);
   __syncthreads();
   if (tid == 0 && *abort_flag) {
     const uint64_t t0 = global_timer_ns();  // let bulk copies already issued land before exit
@@ -464,6 +467,7 @@ int go_dual_quant(const void* go, int dtype, int64_t L, int64_t O, int64_t ldgo,
   p.max_x = max_x;
   p.max_w = max_w;
   p.status = status;
+  p.wait_ns = wait_limit_ns();
   const int sms = device_sm_count();
   if (sms <= 0) return HOT_ERR_CUDA;
   if (dtype == HOT_F32) return launch_dual<float>(go, ldgo, p, q_gx.rounding, q_gw.rounding, sms, st);

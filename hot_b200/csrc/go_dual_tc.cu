@@ -12,10 +12,18 @@
 //   warp 1      allocates tensor memory and issues, from one lane, 8 MMAs (M 128 tokens, N 16, K 16
 //               channels) for the channel transform and 8 (M 128 channels, N 16 = two token blocks x
 //               8 kept rows, K 16 tokens) for the token projection; accumulators are double-buffered
-//   warps 2-5   g_x side: a lane owns a token, reads its 128 transformed channels from tensor memory,
-//               quantises and hands 32-token x 64-byte boxes to the copy engine
-//   warps 6-9   g_w side: a lane owns a channel, reads its 64 projected positions, quantises, and
-//               stores them as a row piece of the transposed operand the same way
+//   warps 2-17  g_x side: a lane owns a token; each warp reads one 32-channel chunk of the lane's 128
+//               transformed channels from tensor memory, quantises it and hands a 32-token box of
+//               codes to the copy engine
+//   warps 18-25 g_w side: a lane owns a channel; each warp reads one 32-position chunk of the lane's 64
+//               projected positions, quantises it and stores it as a row piece of the transposed
+//               operand the same way
+//   All 24 epilogue warps work on the same tile and hand its accumulator buffer back as soon as the
+//   values are in registers.  The four warps with the same chunk index wait as a group: one polls the
+//   accumulator's barrier, the others sit at a named barrier.
+// Measured on the ViT-B/16 fc1 gradient (12,608 x 3,072, bf16): the 16 small MMAs of a tile cost about as
+// much as the tile's share of HBM time, so pass 0 runs at the tensor core's issue rate for 128 x 16 x 16
+// products, and pass 1 is bound by the instruction issue of the rounding and packing arithmetic.
 //
 // The fp32 sums differ from the fixed-order butterflies of row_ht_quant / col_ht_quant only where a
 // sum of 16 bf16 values is not exact in fp32 (operands more than ~2^13 apart in magnitude); there the
@@ -33,13 +41,17 @@ constexpr int kCh = 128;                   // channels per tile
 constexpr int kBoxBytes = kTok * 128;      // one TMA box: 128 tokens x 64 bf16 channels
 constexpr int kStageBytes = 2 * kBoxBytes; // 32 KB
 constexpr int kStages = 4;
-constexpr int kEpiWarps = 8;
+constexpr uint32_t kBufCols = 192;         // an accumulator buffer: 128 (channel transform) + 64 (token projection) columns
+constexpr uint32_t kTmemColsTc = 512;      // two buffers (384 columns), rounded up to a power of two
+// Epilogue warps: the work on a tile is cut into 32-value chunks of a lane's accumulator row, one per warp,
+// so that all of them work on the same tile at once: 16 on the g_x side (4 lane quarters x 4 chunks of 32
+// channels) and 8 on the g_w side (4 lane quarters x 2 chunks of 32 positions).
+constexpr int kRowWarps = 16, kColWarps = 8;
+constexpr int kEpiWarps = kRowWarps + kColWarps;
 constexpr int kThreadsTc = (2 + kEpiWarps) * 32;
-constexpr uint32_t kTmemColsTc = 512;      // two buffers of 128 (channel transform) + 64 (token projection) columns
-constexpr uint32_t kBufCols = 192;
 constexpr int kOffOperands = kStages * kStageBytes;      // H16 | P (first block) | P (second block): 512 bytes each
-constexpr int kOffStoreStage = kOffOperands + 2048;      // per epilogue warp two 32-row x 64-byte boxes
-constexpr int kOffBarriers = kOffStoreStage + kEpiWarps * 4096;
+constexpr int kOffStoreStage = kOffOperands + 2048;      // per epilogue warp two boxes of 32 rows x 32 bytes
+constexpr int kOffBarriers = kOffStoreStage + kEpiWarps * 2048;
 constexpr int kSmemTc = kOffBarriers + 256 + 1024;       // barriers + slack to align the base to 1024
 
 // natural row of H_16 of output slot j of the token projection (the 8 lowest-sequency rows)
@@ -56,6 +68,7 @@ struct TcParams {
   uint32_t* max_x;         // [1] or [L]
   uint32_t* max_w;         // [1] or [O]
   uint32_t* status;
+  uint64_t wait_ns;        // time limit of a device-side wait
 };
 
 // Instruction descriptor: D = F32, A = B = BF16, B K-major, A K-major or MN-major, M = 128, N = 16.
@@ -83,12 +96,14 @@ __device__ __forceinline__ void kbits32(const uint32_t (&f)[32], const ScalePair
 // The 32 codes of elements e0 .. e0+31 (e0 a multiple of 16; of 32 when the codes take 4 random bits and
 // `aligned32` is set, so that one Philox block serves both runs).  Output: INT4 packed (STORE4: 16 bytes in
 // out[0..3]) or one code per byte (32 bytes in out[0..7]): run 0 first, within a run the stored order.
-template <int ROUND, bool STORE4>
+// BITS: the code width when it is known at compile time (4 or 8: everything that depends on it folds to
+// immediates and the width-dependent choices disappear from the instruction stream), 0: read from q.
+template <int ROUND, bool STORE4, int BITS>
 __device__ __forceinline__ void quantise32(const uint32_t (&f)[32], const ScalePair& sp, const QuantDev& q, uint64_t e0,
                                            bool aligned32, uint32_t (&out)[8]) {
-  const uint32_t off = (uint32_t)(q.qmax + 1.0f);
+  const uint32_t off = BITS ? (1u << (BITS - 1)) : (uint32_t)(q.qmax + 1.0f);
   if (ROUND == HOT_ROUND_STOCH_PHILOX) {
-    const bool rb4 = rand_bits(q.qmax) == 4;
+    const bool rb4 = BITS ? BITS <= 4 : rand_bits(q.qmax) == 4;
     uint32_t k[32];
     kbits32(f, sp, k);
     uint4 b0, b1;
@@ -105,7 +120,8 @@ __device__ __forceinline__ void quantise32(const uint32_t (&f)[32], const ScaleP
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
       const uint4 b = r ? b1 : b0;
-      const bool hi = ((e0 + 16 * r) & 16u) != 0;  // rb4: which half of the block this run takes
+      // rb4: which half of the block this run takes (known at compile time when both runs share an aligned block)
+      const bool hi = aligned32 ? r == 1 : ((e0 + 16 * r) & 16u) != 0;
       uint32_t wa0, wa1, wb0, wb1;
       philox_run16_words(k + 16 * r, k + 16 * r + 8, rb4, rb4 ? (hi ? b.z : b.x) : b.x, rb4 ? (hi ? b.w : b.y) : b.y, b.z, b.w,
                          wa0, wa1, wb0, wb1);
@@ -124,7 +140,7 @@ __device__ __forceinline__ void quantise32(const uint32_t (&f)[32], const ScaleP
       }
     }
   } else {
-    const int qmax = (int)q.qmax;
+    const int qmax = BITS ? (1 << (BITS - 1)) - 1 : (int)q.qmax;
 #pragma unroll
     for (int i = 0; i < 8; ++i) out[i] = 0u;
 #pragma unroll
@@ -142,7 +158,9 @@ __device__ __forceinline__ void quantise32(const uint32_t (&f)[32], const ScaleP
 // PASS 0: abs-max of both transformed tensors.  PASS 1: quantise against them (RX / RW: rounding of the
 // g_x / g_w side; X4: g_x codes packed INT4, else one per byte).  Pass 1 walks the tiles in the reverse
 // order of pass 0, so that it starts on the part of grad_output that is most likely still in L2.
-template <int PASS, int RX, int RW, bool X4>
+// FAST: the widths of the training configuration (4-bit codes on the g_x side, 8-bit on the g_w side) and one
+// scale per tensor on both sides, folded at compile time.
+template <int PASS, int RX, int RW, bool X4, bool FAST>
 __global__ void __launch_bounds__(kThreadsTc, 1)
     go_dual_tc_kernel(const __grid_constant__ CUtensorMap tmap_in, const __grid_constant__ CUtensorMap tmap_qgo,
                       const __grid_constant__ CUtensorMap tmap_qgw, TcParams p) {
@@ -156,6 +174,7 @@ __global__ void __launch_bounds__(kThreadsTc, 1)
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const bool x_row = FAST ? false : p.x_row != 0, w_row = FAST ? false : p.w_row != 0;
   const int tiles_c = p.O / kCh;
   const int tiles_t = (int)((p.L + kTok - 1) / kTok);
   const int num_tiles = tiles_c * tiles_t;
@@ -169,7 +188,7 @@ __global__ void __launch_bounds__(kThreadsTc, 1)
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&tmem_full[b], 1);
-      mbar_init(&tmem_empty[b], kEpiWarps * 32);
+      mbar_init(&tmem_empty[b], kEpiWarps);  // one elected lane per epilogue warp
     }
     *abort_flag = 0u;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -200,7 +219,7 @@ __global__ void __launch_bounds__(kThreadsTc, 1)
     if (lane == 0) {
       uint32_t s = 0, ph = 0;
       for (int seq = blockIdx.x; seq < num_tiles; seq += gridDim.x, s = (s + 1 == kStages ? 0 : s + 1), ph ^= (s == 0 ? 1u : 0u)) {
-        if (!mbar_wait(&empty[s], ph ^ 1u, abort_flag)) break;
+        if (!mbar_wait_parked(&empty[s], ph ^ 1u, abort_flag, p.wait_ns)) break;
         const int t = tile_of(seq);
         const int tt = t / tiles_c, tc = t % tiles_c;
         mbar_expect_tx(&full[s], kStageBytes);
@@ -218,8 +237,8 @@ __global__ void __launch_bounds__(kThreadsTc, 1)
       uint32_t s = 0, ph = 0, it = 0;
       for (int seq = blockIdx.x; seq < num_tiles; seq += gridDim.x, ++it, s = (s + 1 == kStages ? 0 : s + 1), ph ^= (s == 0 ? 1u : 0u)) {
         const uint32_t buf = it & 1u, bph = (it >> 1) & 1u;
-        if (!mbar_wait(&tmem_empty[buf], bph ^ 1u, abort_flag)) break;
-        if (!mbar_wait(&full[s], ph, abort_flag)) break;
+        if (!mbar_wait_parked(&tmem_empty[buf], bph ^ 1u, abort_flag, p.wait_ns)) break;
+        if (!mbar_wait_parked(&full[s], ph, abort_flag, p.wait_ns)) break;
         tc_fence_after();
         const uint32_t stage = smem_u32(smem + s * kStageBytes);
         const uint32_t d_row = tmem_base + buf * kBufCols, d_col = d_row + 128;
@@ -245,137 +264,139 @@ __global__ void __launch_bounds__(kThreadsTc, 1)
       }
     }
   } else {
-    // ---- epilogue: warps 2-5 g_x side (lane = token), warps 6-9 g_w side (lane = channel) ----
+    // ---- epilogue: one 32-value chunk of the tile per warp ----
+    const int e = warp - 2;
     const int q = warp & 3;                 // tensor-memory lane quarter this warp may read
-    const bool col_side = warp >= 6;
-    uint8_t* const store_stage = smem + kOffStoreStage + (warp - 2) * 4096;
+    const bool col_side = e >= kRowWarps;
+    const int chunk = col_side ? (e - kRowWarps) >> 2 : e >> 2;  // 32 channels (of 128) / 32 positions (of 64)
+    uint8_t* const store_stage = smem + kOffStoreStage + e * 2048;
     uint32_t boxes = 0;
-    auto put = [&](uint8_t* box, int j, uint4 v) {  // 16-byte piece j of this lane's 64-byte row, swizzled like the tensor map
-      *reinterpret_cast<uint4*>(box + lane * 64 + ((j ^ ((lane >> 1) & 3)) << 4)) = v;
-    };
-    auto open_box = [&]() -> uint8_t* {
-      if (lane == 0) bulk_wait_group_read<1>();  // the store that last read this buffer is done with it
-      __syncwarp();
-      return store_stage + (boxes & 1u) * 2048;
-    };
-    auto close_box = [&](const CUtensorMap* map, uint8_t* box, int x, int y, bool inside) {
-      fence_proxy_async_smem();
-      __syncwarp();
-      if (lane == 0) {
-        if (inside) tma_store_2d(map, box, x, y);  // rows past the end of a partly covered box are clipped
-        bulk_commit_group();                        // always: the buffer rotation counts groups
-      }
-      ++boxes;
-    };
     ScalePair sp_x = scale_from_absmax(0.0f, p.qx.qmax), sp_w = scale_from_absmax(0.0f, p.qw.qmax);
     if (PASS == 1) {
       // launched as a programmatic dependent of pass 0: its abs-maxima are visible once this returns
       asm volatile("griddepcontrol.wait;" ::: "memory");
-      if (!p.x_row) sp_x = scale_from_absmax(__uint_as_float(p.max_x[0]), p.qx.qmax);
-      if (!p.w_row) sp_w = scale_from_absmax(__uint_as_float(p.max_w[0]), p.qw.qmax);
+      if (!x_row) sp_x = scale_from_absmax(__uint_as_float(p.max_x[0]), p.qx.qmax);
+      if (!w_row) sp_w = scale_from_absmax(__uint_as_float(p.max_w[0]), p.qw.qmax);
       if (blockIdx.x == 0 && warp == 2 && lane == 0) {
-        if (!p.x_row) p.s_x[0] = sp_x.s;
-        if (!p.w_row) p.s_w[0] = sp_w.s;
+        if (!x_row) p.s_x[0] = sp_x.s;
+        if (!w_row) p.s_w[0] = sp_w.s;
       }
     }
     float tmax = 0.0f;  // pass 0: this thread's maximum for the per-tensor scale of its side
     const int64_t out_len = p.L / 2;
+    // tile coordinates advance without divisions: the sequence moves by gridDim.x tiles per step (pass 1: backwards)
+    const int step_t = (int)gridDim.x / tiles_c, step_c = (int)gridDim.x % tiles_c;
+    int tt = tile_of(blockIdx.x) / tiles_c, tc = tile_of(blockIdx.x) % tiles_c;
+    auto advance = [&]() {
+      if (PASS == 0) {
+        tt += step_t;
+        tc += step_c;
+        if (tc >= tiles_c) {
+          tc -= tiles_c;
+          ++tt;
+        }
+      } else {
+        tt -= step_t;
+        tc -= step_c;
+        if (tc < 0) {
+          tc += tiles_c;
+          --tt;
+        }
+      }
+    };
     uint32_t it = 0;
-    bool ok = true;
     for (int seq = blockIdx.x; seq < num_tiles; seq += gridDim.x, ++it) {
       const uint32_t buf = it & 1u, bph = (it >> 1) & 1u;
-      ok = __all_sync(0xFFFFFFFFu, mbar_wait(&tmem_full[buf], bph, abort_flag));  // a warp leaves together
-      if (!ok) break;
+      // The four warps that share a chunk index (one per lane quarter, equal work) wait as a group: one of them
+      // polls the accumulator's barrier, the other three sit at a named barrier, which costs them no issue slots.
+      if ((e & 3) == 0) mbar_wait_parked(&tmem_full[buf], bph, abort_flag, p.wait_ns);
+      asm volatile("bar.sync %0, 128;" ::"r"(1 + (e >> 2)) : "memory");
+      if (*abort_flag) break;  // set by whichever wait ran out; every warp of the group sees it after the barrier
       tc_fence_after();
-      const int t = tile_of(seq);
-      const int tt = t / tiles_c, tc = t % tiles_c;
       const int64_t tok0 = (int64_t)tt * kTok;
       const int ch0 = tc * kCh;
-      const uint32_t taddr = tmem_base + buf * kBufCols + ((uint32_t)(q * 32) << 16);
       uint32_t f[32];
-      if (!col_side) {
-        const int64_t tok = tok0 + q * 32 + lane;
-        const bool tok_ok = tok < p.L;
-        if (PASS == 0) {
-          float m = 0.0f;
-#pragma unroll 1
-          for (int c = 0; c < 4; ++c) {
-            tmem_ld32(taddr + 32 * c, f);
+      tmem_ld32(tmem_base + buf * kBufCols + ((uint32_t)(q * 32) << 16) + (col_side ? 128u : 0u) + 32u * chunk, f);
+      // the accumulator values are in registers: hand the buffer back before working on them
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tmem_empty[buf]);
+      if (PASS == 0) {
+        float m4[4] = {0.0f, 0.0f, 0.0f, 0.0f};  // four chains
 #pragma unroll
-            for (int i = 0; i < 32; ++i) m = fmaxf(m, fabsf(__uint_as_float(f[i])));
-          }
-          if (p.x_row) {
-            if (tok_ok) atomic_absmax(p.max_x + tok, m);
+        for (int i = 0; i < 32; ++i) m4[i & 3] = fmaxf(m4[i & 3], fabsf(__uint_as_float(f[i])));
+        const float m = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
+        if (!col_side) {
+          const int64_t tok = tok0 + q * 32 + lane;
+          if (x_row) {
+            if (tok < p.L) atomic_absmax(p.max_x + tok, m);
           } else {
             tmax = fmaxf(tmax, m);
           }
         } else {
-          ScalePair sp = sp_x;
-          if (p.x_row) {
-            sp = scale_from_absmax(tok_ok ? __uint_as_float(p.max_x[tok]) : 0.0f, p.qx.qmax);
-            if (tc == 0 && tok_ok) p.s_x[tok] = sp.s;
-          }
-          const uint64_t e_row = (uint64_t)tok * (uint64_t)p.O + (uint64_t)ch0;
-          uint8_t* box = open_box();
-#pragma unroll 1
-          for (int c = 0; c < 4; ++c) {
-            tmem_ld32(taddr + 32 * c, f);
-            uint32_t out[8];
-            quantise32<RX, X4>(f, sp, p.qx, e_row + 32 * c, true, out);
-            if (X4) {
-              put(box, c, make_uint4(out[0], out[1], out[2], out[3]));
-            } else {
-              // element order of a run is 0-3, 4-7, 8-11, 12-15 = out[0], out[1], out[2], out[3]
-              put(box, 2 * (c & 1), make_uint4(out[0], out[1], out[2], out[3]));
-              put(box, 2 * (c & 1) + 1, make_uint4(out[4], out[5], out[6], out[7]));
-              if (c & 1) {
-                close_box(&tmap_qgo, box, ch0 + 64 * (c >> 1), (int)tok0 + q * 32, tok0 + q * 32 < p.L);
-                if (c == 1) box = open_box();
-              }
-            }
-          }
-          if (X4) close_box(&tmap_qgo, box, ch0 / 2, (int)tok0 + q * 32, tok0 + q * 32 < p.L);
+          if (w_row) atomic_absmax(p.max_w + ch0 + q * 32 + lane, m);
+          else tmax = fmaxf(tmax, m);
+        }
+        advance();
+        continue;
+      }
+      // ---- pass 1: quantise the chunk, stage it as 32 rows of 16 or 32 bytes, hand the box to the copy engine ----
+      if (lane == 0) bulk_wait_group_read<1>();  // the store that last read this staging buffer is done with it
+      __syncwarp();
+      uint8_t* box = store_stage + (boxes & 1u) * 1024;
+      ++boxes;
+      uint32_t out[8];
+      const CUtensorMap* map;
+      int x, y;
+      bool inside = true;
+      if (!col_side) {
+        const int64_t tok = tok0 + q * 32 + lane;
+        const bool tok_ok = tok < p.L;
+        ScalePair sp = sp_x;
+        if (x_row) {
+          sp = scale_from_absmax(tok_ok ? __uint_as_float(p.max_x[tok]) : 0.0f, p.qx.qmax);
+          if (tc == 0 && chunk == 0 && tok_ok) p.s_x[tok] = sp.s;
+        }
+        quantise32<RX, X4, FAST ? 4 : 0>(f, sp, p.qx, (uint64_t)tok * (uint64_t)p.O + (uint64_t)(ch0 + 32 * chunk), true, out);
+        map = &tmap_qgo;
+        x = X4 ? (ch0 + 32 * chunk) / 2 : ch0 + 32 * chunk;
+        y = (int)tok0 + q * 32;
+        inside = tok0 + q * 32 < p.L;  // rows past the end of a partly covered box are clipped by the copy engine
+        if (X4) {
+          *reinterpret_cast<uint4*>(box + lane * 16) = make_uint4(out[0], out[1], out[2], out[3]);
+        } else {
+          *reinterpret_cast<uint4*>(box + lane * 32) = make_uint4(out[0], out[1], out[2], out[3]);
+          *reinterpret_cast<uint4*>(box + lane * 32 + 16) = make_uint4(out[4], out[5], out[6], out[7]);
         }
       } else {
         const int ch = ch0 + q * 32 + lane;
-        if (PASS == 0) {
-          float m = 0.0f;
-#pragma unroll 1
-          for (int c = 0; c < 2; ++c) {
-            tmem_ld32(taddr + 128 + 32 * c, f);
-#pragma unroll
-            for (int i = 0; i < 32; ++i) m = fmaxf(m, fabsf(__uint_as_float(f[i])));
-          }
-          if (p.w_row) atomic_absmax(p.max_w + ch, m);
-          else tmax = fmaxf(tmax, m);
-        } else {
-          ScalePair sp = sp_w;
-          if (p.w_row) {
-            sp = scale_from_absmax(__uint_as_float(p.max_w[ch]), p.qw.qmax);
-            if (tt == 0) p.s_w[ch] = sp.s;
-          }
-          const int64_t pos0 = tok0 / 2;  // first stored position of the tile within a row of the transposed operand
-          const uint64_t e_row = (uint64_t)ch * (uint64_t)out_len + (uint64_t)pos0;
-          uint8_t* box = open_box();
-#pragma unroll 1
-          for (int c = 0; c < 2; ++c) {
-            tmem_ld32(taddr + 128 + 32 * c, f);
-            uint32_t out[8];
-            quantise32<RW, false>(f, sp, p.qw, e_row + 32 * c, false, out);
-            put(box, 2 * c, make_uint4(out[0], out[1], out[2], out[3]));
-            put(box, 2 * c + 1, make_uint4(out[4], out[5], out[6], out[7]));
-          }
-          close_box(&tmap_qgw, box, (int)pos0, ch0 + q * 32, true);
+        ScalePair sp = sp_w;
+        if (w_row) {
+          sp = scale_from_absmax(__uint_as_float(p.max_w[ch]), p.qw.qmax);
+          if (tt == 0 && chunk == 0) p.s_w[ch] = sp.s;
         }
+        const int64_t pos0 = tok0 / 2 + 32 * chunk;  // first stored position of the chunk within a row of the transposed operand
+        quantise32<RW, false, FAST ? 8 : 0>(f, sp, p.qw, (uint64_t)ch * (uint64_t)out_len + (uint64_t)pos0, false, out);
+        map = &tmap_qgw;
+        x = (int)pos0;
+        y = ch0 + q * 32;
+        inside = pos0 < out_len;
+        *reinterpret_cast<uint4*>(box + lane * 32) = make_uint4(out[0], out[1], out[2], out[3]);
+        *reinterpret_cast<uint4*>(box + lane * 32 + 16) = make_uint4(out[4], out[5], out[6], out[7]);
       }
-      tc_fence_before();
-      mbar_arrive(&tmem_empty[buf]);  // this thread has read all it needs of the accumulator buffer
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) {
+        if (inside) tma_store_2d(map, box, x, y);
+        bulk_commit_group();  // always: the buffer rotation counts groups
+      }
+      advance();
     }
     if (PASS == 0) {
       tmax = warp_max(tmax);
       if (lane == 0) {
-        if (!col_side && !p.x_row) atomic_absmax(p.max_x, tmax);
-        if (col_side && !p.w_row) atomic_absmax(p.max_w, tmax);
+        if (!col_side && !x_row) atomic_absmax(p.max_x, tmax);
+        if (col_side && !w_row) atomic_absmax(p.max_w, tmax);
       }
     } else if (lane == 0) {
       bulk_wait_group<0>();  // the staged boxes have left shared memory and are written
@@ -390,17 +411,17 @@ __global__ void __launch_bounds__(kThreadsTc, 1)
     tmem_dealloc(tmem_base, kTmemColsTc);
   }
   if (threadIdx.x == 0 && *abort_flag) {
-    if (p.status) atomicOr(p.status, 4u);
+    if (p.status) atomicOr(p.status, (uint32_t)HOT_STATUS_GO_DUAL_TC);
     const uint64_t t0 = global_timer_ns();  // let bulk copies already issued land before exit
     while (global_timer_ns() - t0 < 100000ull) {
     }
   }
 }
 
-template <int PASS, int RX, int RW, bool X4>
-int launch_tc_pass(const CUtensorMap& m_in, const CUtensorMap& m_qgo, const CUtensorMap& m_qgw, const TcParams& p, int grid,
-                   cudaStream_t st) {
-  auto kernel = go_dual_tc_kernel<PASS, RX, RW, X4>;
+template <int PASS, int RX, int RW, bool X4, bool FAST>
+int launch_tc_pass_as(const CUtensorMap& m_in, const CUtensorMap& m_qgo, const CUtensorMap& m_qgw, const TcParams& p, int grid,
+                      cudaStream_t st) {
+  auto kernel = go_dual_tc_kernel<PASS, RX, RW, X4, FAST>;
   static PerDeviceOnce attr_set;  // per instantiation and device
   bool have_attr = false;
   const int dev = attr_set.current(&have_attr);
@@ -422,6 +443,15 @@ int launch_tc_pass(const CUtensorMap& m_in, const CUtensorMap& m_qgo, const CUte
   HOT_CUDA(cudaLaunchKernelEx(&cfg, kernel, m_in, m_qgo, m_qgw, p));
   HOT_CUDA(cudaGetLastError());
   return HOT_OK;
+}
+
+template <int PASS, int RX, int RW, bool X4>
+int launch_tc_pass(const CUtensorMap& m_in, const CUtensorMap& m_qgo, const CUtensorMap& m_qgw, const TcParams& p, int grid,
+                   cudaStream_t st) {
+  const bool fast = !p.x_row && !p.w_row && p.qx.qmax == 7.0f && p.qw.qmax == 127.0f;
+  if (PASS == 0) return launch_tc_pass_as<PASS, RX, RW, X4, false>(m_in, m_qgo, m_qgw, p, grid, st);  // nothing of it depends on the widths
+  if (fast) return launch_tc_pass_as<PASS, RX, RW, X4, true>(m_in, m_qgo, m_qgw, p, grid, st);
+  return launch_tc_pass_as<PASS, RX, RW, X4, false>(m_in, m_qgo, m_qgw, p, grid, st);
 }
 
 }  // namespace
@@ -453,11 +483,12 @@ int go_dual_quant_tc(const void* go, int64_t L, int64_t O, int64_t ldgo, const h
   p.max_x = max_x;
   p.max_w = max_w;
   p.status = status;
+  p.wait_ns = wait_limit_ns();
   const bool x4 = q_gx.storage == HOT_STORE_INT4;
   CUtensorMap m_in, m_qgo, m_qgw;
   if (int rc = make_map(&m_in, go, L, O * 2, ldgo * 2, 128, kTok, 128)) return rc;
-  if (int rc = make_map(&m_qgo, q_go, L, x4 ? O / 2 : O, ld_qgo, 64, 32, 64)) return rc;
-  if (int rc = make_map(&m_qgw, q_gw_t, O, L / 2, ld_qgw, 64, 32, 64)) return rc;
+  if (int rc = make_map(&m_qgo, q_go, L, x4 ? O / 2 : O, ld_qgo, x4 ? 16 : 32, 32, 0)) return rc;
+  if (int rc = make_map(&m_qgw, q_gw_t, O, L / 2, ld_qgw, 32, 32, 0)) return rc;
   const int sms = device_sm_count();
   if (sms <= 0) return HOT_ERR_CUDA;
   const int num_tiles = (int)(O / kCh) * (int)((L + kTok - 1) / kTok);

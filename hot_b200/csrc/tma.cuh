@@ -12,9 +12,11 @@ namespace hot {
 int make_map(CUtensorMap* map, const void* base, int64_t rows, int64_t row_bytes, int64_t ld, int box_bytes,
              int box_rows, int swizzle_bytes);  // swizzle_bytes: 0, 64 or 128
 
-#ifdef __CUDACC__
+// The time limit of every device-side wait: 1.5 s unless hot_set_wait_limit_ns changed it; the launchers copy it
+// into the kernel parameters (host side: common.cu).
+uint64_t wait_limit_ns();
 
-constexpr uint64_t kWaitLimitNs = 1500ull * 1000ull * 1000ull;
+#ifdef __CUDACC__
 
 // ---- PTX wrappers ------------------------------------------------------------------------
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -51,6 +53,19 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   }
   return ok != 0;
 }
+// try_wait that lets the hardware park the thread for up to `hint_ns` while the phase is incomplete (it is
+// woken as soon as the phase completes), so that a waiting warp does not spend issue slots on polling
+__device__ __forceinline__ bool mbar_try_wait_parked(uint64_t* bar, uint32_t parity, uint32_t hint_ns) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity), "r"(hint_ns)
+      : "memory");
+  return ok != 0;
+}
 __device__ __forceinline__ uint64_t global_timer_ns() {
   uint64_t t;
   asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
@@ -58,14 +73,31 @@ __device__ __forceinline__ uint64_t global_timer_ns() {
 }
 // Bounded wait.  Returns false when it gave up (time limit, or another role already aborted).
 template <bool CLUSTER = false>
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag) {
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag, uint64_t limit_ns) {
   if (mbar_try_wait<CLUSTER>(bar, parity)) return true;
   const uint64_t t0 = global_timer_ns();
   for (uint32_t it = 1;; ++it) {
     if (mbar_try_wait<CLUSTER>(bar, parity)) return true;
     if ((it & 63u) == 0) {
       if (*abort_flag) return false;
-      if (global_timer_ns() - t0 > kWaitLimitNs) {
+      if (global_timer_ns() - t0 > limit_ns) {
+        *abort_flag = 1u;
+        return false;
+      }
+    }
+  }
+}
+
+// The same bounded wait for roles that wait long and often (a whole tile's worth of work by another role):
+// each poll parks the thread for up to 2 us, so a waiting warp issues a handful of instructions per wait.
+__device__ __forceinline__ bool mbar_wait_parked(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag, uint64_t limit_ns) {
+  if (mbar_try_wait<false>(bar, parity)) return true;
+  const uint64_t t0 = global_timer_ns();
+  for (uint32_t it = 1;; ++it) {
+    if (mbar_try_wait_parked(bar, parity, 2000u)) return true;
+    if ((it & 7u) == 0) {
+      if (*abort_flag) return false;
+      if (global_timer_ns() - t0 > limit_ns) {
         *abort_flag = 1u;
         return false;
       }

@@ -46,12 +46,35 @@ class FirstBatchCapture:
         self._handles = []
 
 
-def select_quantizer(grad_out: torch.Tensor, bits: int = 4):
+def _with_noise(g: torch.Tensor, bits: int, scale: str, u: torch.Tensor, is_batched: bool):
+    """The quantiser call of the rule with caller-supplied uniforms instead of the Philox stream (the
+    reference's predicate u < frac): dequantised values.  For reproducing a recorded calibration."""
+    from . import ops
+    g2 = g.reshape(-1, g.shape[-1])
+    pad = (-g2.shape[1]) % 16
+    un = u.reshape(g2.shape).float()
+    if pad:
+        g2, un = torch.nn.functional.pad(g2, (0, pad)), torch.nn.functional.pad(un, (0, pad))
+    q = lambda noise: ops.Quant(bits, "int8", "noise", scale, 0, 0, noise.contiguous())
+    if scale == "tensor" and is_batched:
+        B = g.shape[0]
+        codes, s = ops.row_ht_quant_batched(g2.view(B, -1, g2.shape[1]).contiguous(), 1, q(un))
+        s = s.repeat_interleave(g2.shape[0] // B).unsqueeze(1)
+    else:
+        codes, s = ops.row_ht_quant(g2.contiguous(), 1, q(un))
+        s = s.unsqueeze(1) if scale == "row" else s
+    deq = codes.view(torch.int8)[:, :g2.shape[1] - pad].float() * s
+    return deq.reshape(g.shape)
+
+
+def select_quantizer(grad_out: torch.Tensor, bits: int = 4, noise=None):
     """(gx_name, gw_name, err_stoch, err_norm) for one layer's captured grad_output
     (ViT_main.py:183-211).  3-D [B, L, O]: batched quantisers, one scale per sample for the
     per-tensor one, error against q * s[:, None, None].  2-D: one scale.  4-D [B, C, H, W] (a
     convolution's gradient, which the reference does not treat as batched): one scale for the
-    per-tensor quantiser and one per position (b, h, w) over the channels for the per-token one."""
+    per-tensor quantiser and one per position (b, h, w) over the channels for the per-token one.
+    ``noise`` = (u_stoch, u_norm), two float32 tensors of grad_out's shape with uniforms in [0, 1):
+    round with them (u < frac, as torch.bernoulli does) instead of the Philox stream."""
     g = grad_out.float()
     if g.dim() == 4:
         g = g.permute(0, 2, 3, 1).reshape(-1, g.shape[1])
@@ -63,7 +86,13 @@ def select_quantizer(grad_out: torch.Tensor, bits: int = 4):
     min_qerror = 9999.0
     errs = []
     for q_func in quantScheme_gx:
-        if q_func == "stoch_quantizer":
+        if noise is not None:
+            if g.shape != grad_out.shape:
+                raise ValueError("explicit noise is taken for 2-D and 3-D gradients")
+            q_grad = _with_noise(g, bits, "tensor" if q_func == "stoch_quantizer" else "row",
+                                 noise[0 if q_func == "stoch_quantizer" else 1].to(g.device), is_batched)
+            s_grad = 1.0
+        elif q_func == "stoch_quantizer":
             q_grad, s_grad = stoch_quantizer(g, bits, is_batched)
             if is_batched:
                 s_grad = s_grad.unsqueeze(1).unsqueeze(2)

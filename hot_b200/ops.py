@@ -43,6 +43,29 @@ class Quant:
         return q
 
 
+def check_status(status: torch.Tensor) -> None:
+    """Reads a status word back (this synchronises with the stream that wrote it) and raises
+    ``HotError`` (HOT_ERR_TIMEOUT) if a bounded device-side wait ran out in a launch that was given it."""
+    C.check(C.lib().hot_check_status(int(status.item()) & 0xFFFFFFFF), "status word")
+
+
+def set_wait_limit_ns(limit_ns: int) -> None:
+    """Time limit of every device-side wait in launches made from now on (0 restores the default 1.5 s)."""
+    C.lib().hot_set_wait_limit_ns(int(limit_ns))
+
+
+def set_sm_margin(sms: int) -> None:
+    """Leave ``sms`` SMs out of the persistent kernels' grids from now on (room for a collective's kernels)."""
+    C.lib().hot_set_sm_margin(int(sms))
+
+
+def wait_probe(status: torch.Tensor) -> None:
+    """Launch the probe whose wait runs out (needs a limit of at most 100 ms): it ORs its bit into ``status``."""
+    _require_cuda(status)
+    with torch.cuda.device(status.device):
+        C.check(C.lib().hot_wait_probe(status.data_ptr(), torch.cuda.current_stream(status.device).cuda_stream), "hot_wait_probe")
+
+
 def _require_cuda(*tensors: torch.Tensor) -> None:
     for t in tensors:
         if not t.is_cuda:

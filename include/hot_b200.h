@@ -56,6 +56,34 @@ typedef struct hot_quant {
 } hot_quant_t;
 
 const char* hot_status_string(int status);
+
+/*
+ * Bounded waits.  Every wait inside a kernel (on an mbarrier that a bulk copy, the tensor core or
+ * another warp completes) gives up after a time limit: the kernel then ORs one of the bits below
+ * into the caller's status word, stops issuing work, releases what it holds and returns normally;
+ * the context stays usable and the outputs of that launch are incomplete.  The status word is a
+ * device uint32 the caller zeroes and reads back; hot_check_status turns a value read back into a
+ * hot_status (HOT_OK for 0, else HOT_ERR_TIMEOUT with the kernels named in hot_last_error()).
+ * hot_set_wait_limit_ns sets the limit for launches made after it (process-wide; 0 restores the
+ * default of 1.5 s).  hot_wait_probe launches one warp that waits on a barrier nothing arrives on,
+ * so that the give-up path can be exercised: it needs a limit of at most 100 ms.
+ * The reference has no counterpart (its kernels have no waits: cuda_measure/HLQ_backward_kernel.cu
+ * synchronises the device between stages, :525-552).
+ */
+/*
+ * The GEMM and the fused grad_out kernels are persistent: one CTA per SM of the device.  A caller whose
+ * communication library runs kernels beside them (the grad_w all-reduce of a data-parallel step) can ask
+ * for `sms` SMs to be left out of those grids, so that the collective's CTAs find room at once instead of
+ * queueing behind a persistent CTA; 0 (the default) uses every SM.  Process-wide, for launches made after it.
+ * The reference has no counterpart (DistributedDataParallel schedules its own kernels, ViT_main.py:284-286).
+ */
+void hot_set_sm_margin(int sms);
+
+enum hot_status_bits { HOT_STATUS_GEMM = 1, HOT_STATUS_GO_DUAL = 2, HOT_STATUS_GO_DUAL_TC = 4, HOT_STATUS_PROBE = 8 };
+void hot_set_wait_limit_ns(uint64_t limit_ns);
+uint64_t hot_get_wait_limit_ns(void);
+int hot_wait_probe(uint32_t* status_word, hot_stream_t stream);
+int hot_check_status(uint32_t status_value);
 /* Text of the most recent failure on the calling thread ("" if none). */
 const char* hot_last_error(void);
 /* Library ABI version (bumped on any signature change). */

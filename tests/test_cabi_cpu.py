@@ -54,6 +54,26 @@ def test_argument_errors_need_no_device(cabi):
     assert lib.hot_abc_pitch(6304, ctypes.byref(cfg)) == 3152
 
 
+def test_status_word_and_wait_limit(cabi):
+    """The status word's host side needs no device: 0 is HOT_OK, any bit is HOT_ERR_TIMEOUT and the message
+    names the kernels; the wait limit has a setter, and the probe refuses to run with a long limit."""
+    C, lib = cabi, cabi.lib()
+    assert lib.hot_check_status(0) == C.HOT_OK
+    assert lib.hot_check_status(1 | 4) == C.HOT_ERR_TIMEOUT
+    msg = lib.hot_last_error().decode()
+    assert "integer GEMM" in msg and "tensor-core grad_out" in msg and "0x5" in msg and "wait probe" not in msg
+    assert lib.hot_check_status(8) == C.HOT_ERR_TIMEOUT and "wait probe" in lib.hot_last_error().decode()
+    assert lib.hot_get_wait_limit_ns() == 1500 * 1000 * 1000
+    lib.hot_set_wait_limit_ns(2_000_000)
+    assert lib.hot_get_wait_limit_ns() == 2_000_000
+    lib.hot_set_wait_limit_ns(0)
+    assert lib.hot_get_wait_limit_ns() == 1500 * 1000 * 1000
+    import ctypes
+    word = ctypes.c_uint32(0)
+    assert lib.hot_wait_probe(ctypes.byref(word), None) == C.HOT_ERR_ARG        # limit too long for a probe
+    assert "at most 100 ms" in lib.hot_last_error().decode()
+
+
 def test_host_modules_without_a_device():
     import hot_b200.hadamard_matmul as hm
     g = np.load(os.path.join(ROOT, "tests", "golden", "transforms.npz"))

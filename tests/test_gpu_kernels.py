@@ -390,6 +390,43 @@ def test_config1_fc1_full_size(ops, basis):
     assert np.array_equal(gw.cpu().numpy(), ref["grad_w"])
 
 
+def test_a_bounded_wait_that_runs_out_is_reported_and_leaves_the_device_usable(ops):
+    """One warp waits, with the kernels' own wait routine, on a barrier nothing ever arrives on, with the
+    limit set to 2 ms: the kernel returns by itself, its bit is in the status word, the host side turns
+    the word into HOT_ERR_TIMEOUT, and the next ordinary launch on the same stream is correct."""
+    from hot_b200 import _cabi as C
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    ops.set_wait_limit_ns(2_000_000)
+    try:
+        t0 = torch.cuda.Event(enable_timing=True)
+        t1 = torch.cuda.Event(enable_timing=True)
+        t0.record()
+        ops.wait_probe(status)
+        t1.record()
+        torch.cuda.synchronize()
+        assert 1.5 < t0.elapsed_time(t1) < 200.0                    # it waited about the limit, then gave up
+        assert int(status.item()) == 8                               # HOT_STATUS_PROBE
+        with pytest.raises(C.HotError, match="bounded device-side wait ran out.*wait probe") as err:
+            ops.check_status(status)
+        assert err.value.status == C.HOT_ERR_TIMEOUT
+    finally:
+        ops.set_wait_limit_ns(0)
+    # the context is intact: a real launch with a clean status word right after
+    status.zero_()
+    rng = np.random.default_rng(3)
+    x = (rng.standard_normal((64, 128)) * 1e-3).astype(np.float32)
+    codes, scales = ops.row_ht_quant(_dev(x), 16, ops.Quant(8, "int8", "nearest", "tensor"))
+    a = torch.randint(-7, 8, (128, 256), device="cuda", dtype=torch.int8)
+    b = torch.randint(-7, 8, (64, 256), device="cuda", dtype=torch.int8)
+    acc = ops.gemm_i8(a.view(torch.uint8), "int8", b.view(torch.uint8), "int8", 128, 64, 256, None, None,
+                      out_dtype=torch.int32, status=status)
+    torch.cuda.synchronize()
+    ops.check_status(status)                                         # 0: nothing ran out
+    ref_c, ref_s = oc.quant_tensor(oc.fwht_last(x, 16), 8, None)
+    assert np.array_equal(_codes_from(codes, "int8", 128), ref_c)
+    assert torch.equal(acc.cpu(), (a.cpu().int() @ b.cpu().int().t()))
+
+
 def test_errors_are_reported(ops):
     x = torch.zeros((4, 24), device="cuda")
     with pytest.raises(RuntimeError, match="multiple of 16"):
