@@ -102,13 +102,25 @@ def selection_from_matrix(p) -> tuple:
     if p.ndim != 2 or p.shape[1] < 1 or (p.shape[1] & (p.shape[1] - 1)):
         raise ValueError("expected an [r, n] matrix with n a power of two, got %s" % (p.shape,))
     r, n = p.shape
-    h = hadamard(n)
+    signs = np.rint(p).astype(np.int64)
+    # row i of the Sylvester matrix is t -> (-1)^popcount(i & t): bit k of i is the sign at t = 2^k
     sel = []
+    t = np.arange(n)
     for j in range(r):
-        hit = np.nonzero((h == np.rint(p[j]).astype(np.int64)[None, :]).all(axis=1))[0]
-        if hit.size != 1:
+        i = 0
+        k = 1
+        while k < n:
+            if signs[j, k] < 0:
+                i |= k
+            k <<= 1
+        par = np.zeros(n, dtype=np.int64)
+        both = i & t
+        while both.any():
+            par ^= both & 1
+            both = both >> 1
+        if not np.array_equal(signs[j], 1 - 2 * par):
             raise ValueError("row %d is not a row of the order-%d Hadamard matrix" % (j, n))
-        sel.append(int(hit[0]))
+        sel.append(int(i))
     return n, sel
 
 

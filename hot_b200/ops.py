@@ -319,6 +319,8 @@ class LinearConfig:
 def abc_compress(x: torch.Tensor, cfg: LinearConfig):
     """Activation-buffer compression: x [L, I] -> (x_q_t uint8 [I, pitch], scale_x float32 [1])."""
     _require_cuda(x)
+    if cfg.order_l > MAX_KERNEL_ORDER:   # project in two passes, then quantise the projected rows as they are
+        return abc_compress(hla_project_any(x, cfg.order_l, cfg.sel_l), _identity_tokens(cfg))
     L, I = x.shape
     cc = cfg.to_c(x.dtype)
     pitch = C.lib().hot_abc_pitch(L, ctypes.byref(cc))
@@ -332,6 +334,11 @@ def abc_compress(x: torch.Tensor, cfg: LinearConfig):
         C.check(C.lib().hot_abc_compress(x.data_ptr(), L, I, x.stride(0), ctypes.byref(cc), x_q_t.data_ptr(),
                                          scale.data_ptr(), ws.data_ptr(), ws.numel(), _stream(x)), "hot_abc_compress")
     return x_q_t, scale
+
+
+def _identity_tokens(cfg: "LinearConfig") -> "LinearConfig":
+    """The same configuration with no transform along the tokens (order 1): for operands projected beforehand."""
+    return LinearConfig(order_o=cfg.order_o, order_l=1, sel_l=[0], q_gx=cfg.q_gx, q_w=cfg.q_w, q_gw=cfg.q_gw, q_x=cfg.q_x)
 
 
 def gx_code_storage(bits: int, k: int) -> str:
@@ -389,6 +396,20 @@ def linear_backward(go: torch.Tensor, w: torch.Tensor, x_q_t: torch.Tensor, scal
     _require_cuda(go, w, x_q_t)
     L, O = go.shape
     I = w.shape[1]
+    if cfg.order_l > MAX_KERNEL_ORDER:
+        # token basis of order above 64: grad_x does not involve it; for grad_w grad_out is projected in two passes
+        # and quantised as it is (the activation buffer was made the same way by abc_compress)
+        gx = gw = None
+        if need_gx:
+            gx, _ = linear_backward(go, w, x_q_t, scale_x, _identity_tokens(cfg), True, False, status, gx_out, None)
+        if need_gw:
+            go_lr = hla_project_any(go, cfg.order_l, cfg.sel_l)
+            q_gw_t, s_gw, lp = col_ht_quant(go_lr, 1, [0], _one_per_byte(cfg.q_gw), "transposed")
+            gw = gemm_i8(q_gw_t, "int8", x_q_t, "int8", O, I, lp, s_gw, scale_x, 1.0 / cfg.order_l, go.dtype, status=status)
+            if gw_out is not None:
+                gw_out.copy_(gw)
+                gw = gw_out
+        return gx, gw
     cc = cfg.to_c(go.dtype)
     nbytes = C.lib().hot_linear_workspace_bytes(L, O, I, ctypes.byref(cc))
     if nbytes == 0:
@@ -422,6 +443,30 @@ def hla_project(x: torch.Tensor, order: int, sel: Sequence[int]) -> torch.Tensor
         C.check(C.lib().hot_hla_project(x.data_ptr(), _dtype(x), rows, cols, x.stride(0), order, sel_c, r, out.data_ptr(),
                                         out.stride(0), _stream(x)), "hot_hla_project")
     return out
+
+
+MAX_KERNEL_ORDER = 64   # largest transform order a single kernel launch takes
+
+
+def hla_project_any(x: torch.Tensor, order: int, sel: Sequence[int]) -> torch.Tensor:
+    """``hla_project`` for any power-of-two order up to 4096.  Orders above 64 (a token count such as 128
+    or 1024 under the reference's uncapped make_WHT, or the output-feature basis of ``gilro_gwh``) run as two
+    passes of the order-<=64 kernel: H_(a*64) = H_a (x) H_64, so the 64-point butterflies run first on
+    groups of 64 rows and the a-point ones then on rows 64 apart -- the same stage order h = 1, 2, 4, ... as a
+    single butterfly, hence the same float32 results -- and the kept rows are gathered at the end."""
+    if order <= MAX_KERNEL_ORDER:
+        return hla_project(x, order, sel)
+    if order & (order - 1) or order > MAX_KERNEL_ORDER ** 2:
+        raise ValueError("transform order %d is not a power of two <= %d" % (order, MAX_KERNEL_ORDER ** 2))
+    rows, cols = x.shape
+    if rows % order:
+        raise ValueError("rows %d not a multiple of order %d" % (rows, order))
+    b, a = MAX_KERNEL_ORDER, order // MAX_KERNEL_ORDER
+    y = hla_project(x, b, list(range(b)))                                   # [rows, cols]: index (blk, t_a, i_b)
+    y = hla_project(y.view(rows // b, b * cols), a, list(range(a)))         # rows (blk, t_a) -> (blk, i_a)
+    full = y.view(rows // order, order, cols)                               # natural row index i_a * 64 + i_b
+    idx = torch.as_tensor([int(v) for v in sel], device=x.device, dtype=torch.long)
+    return full.index_select(1, idx).reshape(-1, cols)
 
 
 def hla_expand(y: torch.Tensor, order: int, sel: Sequence[int], scale: float, out_dtype: torch.dtype) -> torch.Tensor:
@@ -465,9 +510,42 @@ def linear_backward_lowrank_gx(go: torch.Tensor, w: torch.Tensor, order: int, se
     return hla_expand(gi_lr, order, sel, 1.0 / order, go.dtype)
 
 
+def linear_backward_gilro_gx(go: torch.Tensor, w: torch.Tensor, order: int, sel: Sequence[int], q_gx: Quant, q_w: Quant,
+                             status: Optional[torch.Tensor] = None, batch: int = 1) -> torch.Tensor:
+    """grad_input of transform_scheme ``gilro_gwh`` (utils/quant_matmul.py:235-236, 267-268, 288-290, 339-340):
+    grad_output [L, O] and the weight [O, I] are both projected along the OUTPUT FEATURES onto the kept rows of
+    H_order (order = the whole 2-adic part of O, up to 1024 for ViT widths), quantised, and multiplied over the
+    shortened feature axis: grad_x = (Q(go . P^T) . Q(P w)) * s_go * s_w / order.  ``batch`` > 1: one scale per
+    sample for grad_output, as the reference's batched quantiser gives."""
+    import torch.nn.functional as F
+    _require_cuda(go, w)
+    L, O = go.shape
+    I = w.shape[1]
+    go_lr = hla_project_any(go.t().contiguous(), order, sel).t().contiguous()       # [L, O'] float32
+    w_lr = hla_project_any(w, order, sel)                                            # [O', I] float32
+    pad = (-go_lr.shape[1]) % 16      # the quantiser works on runs of 16; zero features add nothing to the product
+    if pad:
+        go_lr = F.pad(go_lr, (0, pad))
+        w_lr = F.pad(w_lr, (0, 0, 0, pad))
+    K = go_lr.shape[1]
+    rows_per_scale = 1
+    if batch > 1 and q_gx.scale == "tensor":
+        q_go, s_go = row_ht_quant_batched(go_lr.view(batch, L // batch, K), 1, q_gx)
+        rows_per_scale = L // batch
+    else:
+        q_go, s_go = row_ht_quant(go_lr, 1, q_gx)
+    q_w_t, s_w, _ = col_ht_quant(w_lr, 1, [0], _one_per_byte(q_w), "natural")        # [I, O'] codes
+    return gemm_i8(q_go, q_gx.storage, q_w_t, "int8", L, I, K, s_go, s_w, 1.0 / order, go.dtype, status=status,
+                   a_rows_per_scale=rows_per_scale)
+
+
 def abc_compress_batched(x: torch.Tensor, cfg: LinearConfig):
     """Activation buffer of a batch ``x`` [B, L, I] with one scale per sample, as the reference saves
     it for 3-D inputs: (x_q_t uint8 [I, B * pitch], scale_x float32 [B], pitch)."""
+    if cfg.order_l > MAX_KERNEL_ORDER:   # projection blocks never straddle samples: project the flattened batch
+        B, L, I = x.shape
+        x_lr = hla_project_any(x.reshape(B * L, I), cfg.order_l, cfg.sel_l).view(B, -1, I)
+        return abc_compress_batched(x_lr, _identity_tokens(cfg))
     codes, scales, _, pitch = col_ht_quant_batched(x, cfg.order_l, cfg.sel_l, _one_per_byte(cfg.q_x), "natural")
     return codes, scales, pitch
 
@@ -505,7 +583,10 @@ def linear_backward_batched(go: torch.Tensor, w: torch.Tensor, x_q_t: torch.Tens
         gx = gemm_i8(q_go, cfg.q_gx.storage, q_w_t, "int8", B * L, I, O, s_go, s_w, 1.0 / cfg.order_o, go.dtype,
                      status=status, a_rows_per_scale=rows_per_scale).view(B, L, I)
     if need_gw:
-        q_gw_t, s_gw, out_len, pitch = col_ht_quant_batched(go, cfg.order_l, cfg.sel_l, _one_per_byte(cfg.q_gw), "transposed")
+        go_w, order_w, sel_w = go, cfg.order_l, cfg.sel_l
+        if cfg.order_l > MAX_KERNEL_ORDER:
+            go_w, order_w, sel_w = hla_project_any(go.view(B * L, O), cfg.order_l, cfg.sel_l).view(B, -1, O), 1, [0]
+        q_gw_t, s_gw, out_len, pitch = col_ht_quant_batched(go_w, order_w, sel_w, _one_per_byte(cfg.q_gw), "transposed")
         if x_q_t.shape[1] != B * pitch:
             raise ValueError("activation buffer does not match: %d bytes per row, expected %d" % (x_q_t.shape[1], B * pitch))
         gw = gemm_i8_grouped(q_gw_t, x_q_t, O, I, B, pitch, s_gw, scale_x, 1.0 / cfg.order_l, go.dtype, status=status)

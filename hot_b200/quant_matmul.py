@@ -163,7 +163,7 @@ def _operand(kind: str, scheme, bits: int, what: str, row_ok: bool, k: int = 1 <
     return ops.Quant(int(bits), storage, rounding, scale, _seed(), _next_offset())
 
 
-_BUILT_SCHEMES = ("gih_gwlr", "hadamard", "low_rank", "gilr_gwh")
+_BUILT_SCHEMES = ("gih_gwlr", "hadamard", "low_rank", "gilr_gwh", "gilro_gwh")
 _TOKEN_GX_SCHEMES = ("low_rank", "gilr_gwh")   # grad_output is projected along the tokens for g_x too
 
 
@@ -171,7 +171,7 @@ def _token_basis(a, tokens: int, preset):
     """(n, sel) of the token-side transform of the configured scheme: the low-rank rows of make_WHT
     (or the preset) for ``gih_gwlr``; every row of the block Hadamard matrix H_n, n = min(16, 2-adic
     part of the token count), for ``hadamard`` (utils/quant_matmul.py:353-355, make_hadamard)."""
-    if a.transform_scheme in ("hadamard", "gilr_gwh"):
+    if a.transform_scheme in ("hadamard", "gilr_gwh", "gilro_gwh"):
         n = biggest_power2_factor_max16(tokens)
         return n, list(range(n))
     return lowrank_selection(tokens, preset, a.vectorPercentile)
@@ -187,15 +187,24 @@ def _out_matrix(a, out_features: int, tokens: int, preset, dtype, device) -> Ten
     if a.transform_scheme == "gilr_gwh":
         n, sel = lowrank_selection(tokens, preset, a.vectorPercentile)
         return torch.tensor(hadamard(n)[sel], dtype=dtype, device=device)
+    if a.transform_scheme == "gilro_gwh":   # low-rank rows over the OUTPUT FEATURES, order = their whole 2-adic part (:365)
+        return torch.tensor(TD.get_or_register("low_rank", out_features, a.vectorPercentile), dtype=dtype, device=device)
     return torch.tensor(TD.get_or_register("hadamard", out_features), dtype=dtype, device=device)
 
 
 def _check_scheme(a) -> None:
     if a.transform_scheme not in _BUILT_SCHEMES:
-        if a.transform_scheme in ("gilro_gwh",):
-            raise NotImplementedError("transform_scheme %r is not built on the native path (built: %s)"
-                                      % (a.transform_scheme, ", ".join(_BUILT_SCHEMES)))
         raise Exception("args.transform_scheme not implemented: " + str(a.transform_scheme))
+    if a.transform_scheme == "gilro_gwh":
+        # the reference has no activation / grad_out(g_w) transform for this scheme: it raises with them switched on
+        # (utils/quant_matmul.py:192, 303), so the scheme runs with the g_w side untransformed
+        if a.TransformInput:
+            raise Exception("Activation transform scheme not implemented: gilro_gwh")
+        if a.TransformGogw:
+            raise Exception("GradHb transform scheme not implemented: gilro_gwh")
+        if not (a.TransformGogi and a.TransformWgt):
+            raise NotImplementedError("gilro_gwh on the native path needs TransformGogi and TransformWgt True")
+        return
     if not (a.TransformGogi and a.TransformWgt and a.TransformGogw and a.TransformInput):
         raise NotImplementedError("the native path needs TransformGogi/Wgt/Gogw/Input all True")
 
@@ -244,11 +253,15 @@ class FLinearQ(Function):
         if ctx.scheme in _TOKEN_GX_SCHEMES:   # no transform along the output features; g_x takes token rows
             order_o = 1
             ctx.gx_basis = (n_l, sel) if ctx.scheme == "low_rank" else _selection(h_out)
+        elif ctx.scheme == "gilro_gwh":       # low-rank rows over the output features for g_x; g_w untransformed
+            order_o = 1
+            ctx.gx_basis = _selection(h_out)
+            n_l, sel = 1, [0]
         else:
             order_o = int(h_out.shape[0])
         cfg = ops.LinearConfig(order_o=order_o, order_l=n_l, sel_l=sel, q_x=q_x)
         ctx.per_sample = x.dim() == 3 and getattr(a, "lowRankPreset", None) is None
-        if ctx.per_sample and ctx.gx_basis is not None and x.shape[1] % ctx.gx_basis[0]:
+        if ctx.per_sample and ctx.scheme in _TOKEN_GX_SCHEMES and x.shape[1] % ctx.gx_basis[0]:
             raise ValueError("token count %d is not a multiple of the low-rank order %d" % (x.shape[1], ctx.gx_basis[0]))
         if ctx.per_sample:
             if x.shape[1] % n_l:
@@ -297,7 +310,17 @@ class FLinearQ(Function):
                                q_x=ctx.q_x)
         need_gx, need_gw = ctx.needs_input_grad[0], ctx.needs_input_grad[1]
         gx = gw = None
-        if (need_gx or need_gw) and ctx.per_sample and ctx.gx_basis is not None:
+        if ctx.scheme == "gilro_gwh":
+            n_x, sel_x = ctx.gx_basis
+            if need_gw:
+                if ctx.per_sample:
+                    _, gw = ops.linear_backward_batched(go, w.detach(), x_q_t, scale_x, cfg, need_gx=False, need_gw=True)
+                else:
+                    _, gw = ops.linear_backward(go, w.detach(), x_q_t, scale_x, cfg, need_gx=False, need_gw=True)
+            if need_gx:
+                B = go.shape[0] if ctx.per_sample else 1
+                gx = ops.linear_backward_gilro_gx(go.reshape(-1, go.shape[-1]), w.detach(), n_x, sel_x, q_gx, q_w, batch=B)
+        elif (need_gx or need_gw) and ctx.per_sample and ctx.gx_basis is not None:
             if need_gw:
                 _, gw = ops.linear_backward_batched(go, w.detach(), x_q_t, scale_x, cfg, need_gx=False, need_gw=True)
             if need_gx:
@@ -375,8 +398,7 @@ class HQ_Conv2d(nn.Conv2d):
         _check_scheme_name(a)
         if a.transform_scheme in _TOKEN_GX_SCHEMES:
             raise NotImplementedError("HQ_Conv2d with transform_scheme %r is not built" % a.transform_scheme)
-        self.register_buffer("hadamard_out", torch.tensor(TD.get_or_register("hadamard", self.out_channels),
-                                                          dtype=self.weight.dtype))
+        self.register_buffer("hadamard_out", _out_matrix(a, self.out_channels, 1, None, self.weight.dtype, self.weight.device))
         self.register_buffer("hadamard_bs", torch.zeros((1, 1), dtype=self.weight.dtype))
         self._bs_tokens = None
         self.layer_name = " "
@@ -409,9 +431,6 @@ class HQ_Conv2d(nn.Conv2d):
 def _check_scheme_name(a) -> None:
     if a.transform_scheme not in ("hadamard", "low_rank", "gilr_gwh", "gilro_gwh", "gih_gwlr"):
         raise Exception("Transformation method not implemented: " + str(a.transform_scheme))
-    if a.transform_scheme not in _BUILT_SCHEMES:
-        raise NotImplementedError("transform_scheme %r is not built on the native path (built: %s)"
-                                  % (a.transform_scheme, ", ".join(_BUILT_SCHEMES)))
 
 
 def replace_layers(model: nn.Module, old, new) -> None:

@@ -422,6 +422,24 @@ def grad_input_lowrank(go, w, *, n: int, sel, bits_gx: int = 4, bits_w: int = 4,
     return dict(q_go=q_go, s_go=s_go, q_w=q_w, s_w=s_w, grad_input=hla_expand(gi_lr, n, sel, F32(1.0) / F32(n)))
 
 
+def grad_input_gilro(go, w, *, n: int, sel, bits_gx: int = 4, bits_w: int = 4, u_go=None, u_w=None,
+                     w_mode: str = "stoch", exact_matmul: bool = True):
+    """grad_input of transform_scheme gilro_gwh (utils/quant_matmul.py:235-236, 267-268, 288-290, 339-340):
+    grad_output [L, O] and the weight [O, I] are projected along the output features onto the kept rows P of
+    H_n (n = the whole 2-adic part of O): go_lr = go . P^T blockwise [L, O r/n], w_lr = P w blockwise
+    [O r/n, I]; both quantised with one scale; grad_input = (q_go @ q_w) * s_go * s_w / n."""
+    go = np.asarray(go, dtype=F32)
+    w = np.asarray(w, dtype=F32)
+    sel = np.asarray(sel)
+    go_lr = np.ascontiguousarray(hla(np.ascontiguousarray(go.T), n, sel).T)
+    w_lr = hla(w, n, sel)
+    q_go, s_go = quant_tensor(go_lr, bits_gx, u_go)
+    q_w, s_w = quant_sawb(w_lr, bits_w) if w_mode == "sawb" else quant_tensor(w_lr, bits_w, u_w if w_mode == "stoch" else None)
+    acc = _int_matmul(q_go, q_w, exact_matmul)
+    gi = ((acc.astype(F32) * F32(s_go)) * F32(s_w)) / F32(n)
+    return dict(q_go=q_go, s_go=s_go, q_w=q_w, s_w=s_w, grad_input=gi.astype(F32))
+
+
 # ----------------------------------------------------------------------------
 # the same on 3-D tensors [B, L, .]: one scale per sample (torch.vmap over dim 0 of the
 # quantisers, utils/quant_matmul.py:102-106,117-122), grad_w summed over the batch

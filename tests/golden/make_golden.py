@@ -4,7 +4,7 @@ Usage (in a container where the reference checkout is mounted):
 
     python tests/golden/make_golden.py /path/to/reference [section ...]
 
-With section names (``core``, ``lqs_batched``, ``precision``, ``conv``) only those files are
+With section names (``core``, ``lqs_batched``, ``precision``, ``conv``, ``gilro``) only those files are
 rewritten; without, all of them.
 
 The reference's ``args.py`` imports ``utils/plot.py`` which needs matplotlib; three
@@ -61,7 +61,7 @@ class NoiseQueue:
 
 def main(ref_root: str, out_dir: str, only=()):
     ref_args, hm, qm = _import_reference(ref_root)
-    extra = {"lqs_batched": lqs_batched, "precision": precision_schedule, "conv": conv2d}
+    extra = {"lqs_batched": lqs_batched, "precision": precision_schedule, "conv": conv2d, "gilro": gilro_and_big_order}
     for name, fn in extra.items():
         if not only or name in only:
             fn(ref_args, hm, qm, out_dir)
@@ -536,6 +536,69 @@ def conv2d(ref_args, hm, qm, out_dir: str):
                     tag + "_cfg": np.array([B, cin, cout, hw, k, stride, pad])})
     _gih_gwlr(ref_args, "stoch")
     np.savez_compressed(os.path.join(out_dir, "conv2d.npz"), **out)
+
+
+def gilro_and_big_order(ref_args, hm, qm, out_dir: str):
+    """(1) transform_scheme "gilro_gwh" as the reference can run it: TransformGogi / TransformWgt on (grad_output and
+    the weight projected along the output features onto make_WHT(O), whose order is the whole 2-adic part of O),
+    TransformInput / TransformGogw off (the reference has no branch for them and raises with them on).  Two widths:
+    O = 96 (order 32, 10 rows) and O = 256 (order 256, 136 rows: above what one kernel launch takes).
+    (2) gih_gwlr on 384 tokens: make_WHT gives an order-128 token basis (36 rows)."""
+    T = torch.from_numpy
+    for tag, (L, O, I, seed) in {"o96": (48, 96, 32, 20250331), "o256": (32, 256, 48, 20250401)}.items():
+        rng = np.random.default_rng(seed)
+        _gih_gwlr(ref_args, "stoch")
+        ref_args.transform_scheme = "gilro_gwh"
+        ref_args.TransformInput = ref_args.TransformGogw = False
+        xx = rng.standard_normal((L, I)).astype(np.float32)
+        xx[:, 2] *= 9.0
+        ww = ((rng.random((O, I)) * 2 - 1) / np.sqrt(I)).astype(np.float32)
+        go = (rng.standard_normal((L, O)) * 1e-3).astype(np.float32)
+        lr = hm.make_WHT(O, 50)
+        h_out = torch.tensor(lr, dtype=torch.float32)
+        h_bs = torch.tensor(hm.make_hadamard(L), dtype=torch.float32)
+        Op = O * lr.shape[0] // lr.shape[1]
+        u_x = rng.random((L, I), dtype=np.float32)
+        u_go = rng.random((L, Op), dtype=np.float32)
+        u_w = rng.random((Op, I), dtype=np.float32)
+        u_gw = rng.random((O, L), dtype=np.float32)
+        xt = T(xx).requires_grad_(True)
+        wt = T(ww).requires_grad_(True)
+        try:
+            with NoiseQueue() as nq:
+                nq.queue += [T(u_x), T(u_go), T(u_w), T(u_gw)]
+                y = qm.FLinearQ.apply(xt, wt, h_out, h_bs, "layer")
+                saved = y.grad_fn.saved_tensors
+                y.backward(T(go))
+                assert not nq.queue
+        finally:
+            _gih_gwlr(ref_args, "stoch")
+        np.savez_compressed(os.path.join(out_dir, "flinearq_gilro_%s.npz" % tag), x=xx, w=ww, go=go, lowrank=lr.astype(np.int8),
+                            u_x=u_x, u_go=u_go, u_w=u_w, u_gw=u_gw, x_q=saved[0].numpy(), scale_x=saved[4].numpy(),
+                            grad_input=xt.grad.numpy(), grad_w=wt.grad.numpy())
+    rng = np.random.default_rng(20250402)
+    _gih_gwlr(ref_args, "stoch")
+    L, O, I = 384, 64, 32
+    xx = rng.standard_normal((L, I)).astype(np.float32)
+    xx[:, 4] *= 11.0
+    ww = ((rng.random((O, I)) * 2 - 1) / np.sqrt(I)).astype(np.float32)
+    go = (rng.standard_normal((L, O)) * 1e-3).astype(np.float32)
+    pm = hm.make_WHT(L, 50)
+    assert pm.shape[1] == 128
+    Lp = L * pm.shape[0] // pm.shape[1]
+    u_x, u_go = rng.random((Lp, I), dtype=np.float32), rng.random((L, O), dtype=np.float32)
+    u_w, u_gw = rng.random((O, I), dtype=np.float32), rng.random((O, Lp), dtype=np.float32)
+    xt = T(xx).requires_grad_(True)
+    wt = T(ww).requires_grad_(True)
+    with NoiseQueue() as nq:
+        nq.queue += [T(u_x), T(u_go), T(u_w), T(u_gw)]
+        y = qm.FLinearQ.apply(xt, wt, torch.tensor(hm.make_hadamard(O), dtype=torch.float32), torch.tensor(pm, dtype=torch.float32), "layer")
+        saved = y.grad_fn.saved_tensors
+        y.backward(T(go))
+        assert not nq.queue
+    np.savez_compressed(os.path.join(out_dir, "flinearq_lr_ref128.npz"), x=xx, w=ww, go=go, p=pm.astype(np.int8), u_x=u_x, u_go=u_go,
+                        u_w=u_w, u_gw=u_gw, x_q=saved[0].numpy(), scale_x=saved[4].numpy(), grad_input=xt.grad.numpy(),
+                        grad_w=wt.grad.numpy())
 
 
 if __name__ == "__main__":

@@ -296,8 +296,8 @@ def test_unbuilt_modes_raise(hot):
     with pytest.raises(Exception, match="rounding scheme not implemented"):
         lin(x)
     args.quantBWDAct = "stoch"
-    args.transform_scheme = "gilro_gwh"
-    with pytest.raises(NotImplementedError):
+    args.transform_scheme = "gilro_gwh"                          # runs only with the g_w side untransformed, as in the reference
+    with pytest.raises(Exception, match="Activation transform scheme not implemented: gilro_gwh"):
         lin(x)
     args.transform_scheme = "nonsense"
     with pytest.raises(Exception, match="not implemented"):
@@ -403,9 +403,9 @@ def test_lqs_select_quantizer_on_the_reference_cases(hot, golden, fixture, tags)
     """The product's selection on the first-batch gradients of the reference-generated cases.  With the
     recorded rounding noise: the reference's choice and its two quantisation errors to 1e-5 (the
     quantisers are bit-exact, the norm is summed in another order).  With the Philox stream: the same
-    choice, and errors within the spread another draw of the noise has (a single outlier row of 48
-    values carries the per-token error of the "outlier" cases: 4 % for the per-tensor error, 35 % for
-    that one).  "spread" is the case where one scale for the whole batch would give g_x to the
+    choice, and errors within the spread another draw of the noise has (one sample of 1,152 values, or a
+    single outlier row of 48, carries most of an error: 10 % for the per-tensor error, 35 % for the
+    per-token one).  "spread" is the case where one scale for the whole batch would give g_x to the
     per-token quantiser and the reference, with one scale per sample, does not."""
     from hot_b200 import lqs
     g = golden(fixture)
@@ -417,7 +417,7 @@ def test_lqs_select_quantizer_on_the_reference_cases(hot, golden, fixture, tags)
         np.testing.assert_allclose([e_st, e_nq], g[tag + "_errs"], rtol=1e-5)
         gx, gw, e_st, e_nq = lqs.select_quantizer(grad)
         assert (gx, gw) == (str(g[tag + "_gx"]), "stoch_quantizer"), (tag, gx, e_st, e_nq)
-        np.testing.assert_allclose(e_st, g[tag + "_errs"][0], rtol=0.04)
+        np.testing.assert_allclose(e_st, g[tag + "_errs"][0], rtol=0.10)
         np.testing.assert_allclose(e_nq, g[tag + "_errs"][1], rtol=0.35)
 
 
@@ -443,6 +443,96 @@ def test_hq_conv2d_against_the_reference(hot, golden, tag):
         want = g[tag + "_" + name]
         rel = np.linalg.norm(got.cpu().numpy() - want) / np.linalg.norm(want)
         assert rel < 1e-3, (name, rel)
+
+
+@pytest.mark.parametrize("tag", ["o96", "o256"])
+def test_scheme_gilro_gwh(hot, golden, tag):
+    """transform_scheme "gilro_gwh": grad_input from grad_output and the weight projected along the output
+    features (order 32, and order 256 = two passes of the order-64 kernel).  With the reference's recorded
+    noise: bit-identical to the oracle, within 1e-3 of the reference's own run.  Through HQ_Linear with nearest
+    rounding: bit-identical to the oracle; with the transforms the reference cannot run switched on, the
+    reference's own exceptions."""
+    args, qm = hot
+    from hot_b200 import ops
+    g = golden("flinearq_gilro_" + tag)
+    n, sel = oc.selection_from_matrix(g["lowrank"])
+    go, w, x = g["go"], g["w"], g["x"]
+    L, O = go.shape
+    Op = O * len(sel) // n
+    pad = (-Op) % 16
+    dev = lambda a: torch.from_numpy(np.ascontiguousarray(a)).cuda()
+    u_go = np.pad(g["u_go"], ((0, 0), (0, pad)), constant_values=0.5)
+    u_w = np.pad(g["u_w"], ((0, pad), (0, 0)), constant_values=0.5)
+    q_gx = ops.Quant(4, "int4", "noise", "tensor", 0, 0, dev(u_go))
+    q_w = ops.Quant(4, "int8", "noise", "tensor", 0, 0, dev(u_w))
+    gx = ops.linear_backward_gilro_gx(dev(go), dev(w), n, [int(v) for v in sel], q_gx, q_w)
+    ref = oc.grad_input_gilro(go, w, n=n, sel=sel, u_go=g["u_go"], u_w=g["u_w"])
+    assert np.array_equal(gx.cpu().numpy(), ref["grad_input"])
+    assert np.linalg.norm(gx.cpu().numpy() - g["grad_input"]) / np.linalg.norm(g["grad_input"]) < 1e-3
+    # the layer
+    args.transform_scheme = "gilro_gwh"
+    args.lowRankPreset = None
+    args.quantBWDGogi = args.quantBWDWgt = args.quantBWDGogw = args.quantBWDAct = "int"
+    lin = qm.HQ_Linear(w.shape[1], O, bias=False).cuda()
+    lin.weight.data = dev(w)
+    xin = dev(x).requires_grad_(True)
+    with pytest.raises(Exception, match="Activation transform scheme not implemented: gilro_gwh"):
+        lin(xin)
+    args.TransformInput = False
+    with pytest.raises(Exception, match="GradHb transform scheme not implemented: gilro_gwh"):
+        lin(xin).backward(dev(go))
+    args.TransformGogw = False
+    lin.weight.grad = None
+    xin.grad = None
+    lin(xin).backward(dev(go))
+    assert tuple(lin.hadamard_out.shape) == tuple(g["lowrank"].shape)
+    xq, sx = oc.abc_compress(x, 1, np.array([0]), 8, None, "int")
+    want_gx = oc.grad_input_gilro(go, w, n=n, sel=sel, w_mode="int")["grad_input"]
+    want_gw = oc.linear_backward(go, w, xq, sx, n_o=1, n_l=1, sel=np.array([0]), w_mode="int")["grad_w"]
+    assert np.array_equal(xin.grad.cpu().numpy(), want_gx)
+    assert np.array_equal(lin.weight.grad.cpu().numpy(), want_gw)
+
+
+def test_token_basis_of_order_128(hot, golden):
+    """384 tokens give make_WHT an order-128 basis (36 rows): above what one kernel launch transforms, so
+    the projection runs as two passes (64-point, then 2-point butterflies on rows 64 apart) and the projected
+    rows are quantised as they are.  Bit-identical to the oracle with the recorded noise, within 1e-3 of the
+    reference's run; and through HQ_Linear, which derives the basis from the live token count."""
+    args, qm = hot
+    from hot_b200 import ops
+    g = golden("flinearq_lr_ref128")
+    n_l, sel = oc.selection_from_matrix(g["p"])
+    x, w, go = g["x"], g["w"], g["go"]
+    L, I = x.shape
+    O = w.shape[0]
+    Lp = L // n_l * len(sel)
+    dev = lambda a: torch.from_numpy(np.ascontiguousarray(a)).cuda()
+    q = lambda bits, storage, u: ops.Quant(bits, storage, "noise", "tensor", 0, 0, dev(u))
+    cfg = ops.LinearConfig(order_o=16, order_l=n_l, sel_l=[int(v) for v in sel], q_gx=q(4, "int4", g["u_go"]),
+                           q_w=q(4, "int4", g["u_w"]), q_gw=q(8, "int8", g["u_gw"]), q_x=q(8, "int8", g["u_x"]))
+    x_q_t, s_x = ops.abc_compress(dev(x), cfg)
+    gx, gw = ops.linear_backward(dev(go), dev(w), x_q_t, s_x, cfg)
+    xq_ref, sx_ref = oc.abc_compress(x, n_l, sel, 8, g["u_x"])
+    ref = oc.linear_backward(go, w, xq_ref, sx_ref, n_o=16, n_l=n_l, sel=sel, u_go=g["u_go"], u_w=g["u_w"], u_gw=g["u_gw"])
+    assert np.array_equal(x_q_t.cpu().numpy().view(np.int8).astype(np.int32)[:, :Lp].T, xq_ref)
+    assert np.array_equal(gx.cpu().numpy(), ref["grad_input"]) and np.array_equal(gw.cpu().numpy(), ref["grad_w"])
+    for got, name in ((gx, "grad_input"), (gw, "grad_w")):
+        assert np.linalg.norm(got.cpu().numpy() - g[name]) / np.linalg.norm(g[name]) < 1e-3, name
+    args.lowRankPreset = None
+    args.quantBWDGogi = args.quantBWDWgt = args.quantBWDGogw = args.quantBWDAct = "int"
+    lin = qm.HQ_Linear(I, O, bias=False).cuda()
+    lin.weight.data = dev(w)
+    xin = dev(x).requires_grad_(True)
+    lin(xin).backward(dev(go))
+    assert tuple(lin.hadamard_bs.shape) == (36, 128)
+    xq_i, sx_i = oc.abc_compress(x, n_l, sel, 8, None, "int")
+    ref_i = oc.linear_backward(go, w, xq_i, sx_i, n_o=16, n_l=n_l, sel=sel, w_mode="int")
+    assert np.array_equal(xin.grad.cpu().numpy(), ref_i["grad_input"])
+    assert np.array_equal(lin.weight.grad.cpu().numpy(), ref_i["grad_w"])
+    # a 3-D input whose per-sample length has a 2-adic part above 64: one scale per sample, same projection
+    x3 = torch.randn(2, 256, I, device="cuda", requires_grad=True)
+    lin(x3).backward(torch.randn(2, 256, O, device="cuda") * 1e-3)
+    assert tuple(lin.hadamard_bs.shape)[1] == 256 and torch.isfinite(x3.grad).all() and torch.isfinite(lin.weight.grad).all()
 
 
 def test_vit_with_hot_linears_trains(hot):

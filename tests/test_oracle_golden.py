@@ -201,6 +201,32 @@ def test_flinearq_backward_batched_nq(golden):
     assert np.linalg.norm(flat["grad_input"] - g["grad_input"]) > 10 * np.linalg.norm(out["grad_input"] - g["grad_input"])
 
 
+@pytest.mark.parametrize("tag", ["o96", "o256"])
+def test_flinearq_backward_scheme_gilro(golden, tag):
+    """transform_scheme "gilro_gwh" with the g_w side untransformed (the only form the reference can run):
+    grad_output and the weight projected along the output features (order 32 of 96; order 256 of 256)."""
+    g = golden("flinearq_gilro_" + tag)
+    n, sel = oc.selection_from_matrix(g["lowrank"])
+    xq, sx = oc.abc_compress(g["x"], 1, np.array([0]), 8, g["u_x"])          # no transform along the tokens
+    assert np.array_equal(xq, g["x_q"].astype(np.int32)) and np.float32(sx) == g["scale_x"]
+    gi = oc.grad_input_gilro(g["go"], g["w"], n=n, sel=sel, u_go=g["u_go"], u_w=g["u_w"])["grad_input"]
+    gw = oc.linear_backward(g["go"], g["w"], xq, sx, n_o=1, n_l=1, sel=np.array([0]), u_go=None, u_w=None, u_gw=g["u_gw"])["grad_w"]
+    for got, want in ((gi, g["grad_input"]), (gw, g["grad_w"])):
+        assert np.linalg.norm(got - want) / np.linalg.norm(want) < 1e-3
+
+
+def test_flinearq_backward_order_128_token_basis(golden):
+    """384 tokens: make_WHT keeps 36 rows of H_128 (the order is the whole 2-adic part of the token count)."""
+    g = golden("flinearq_lr_ref128")
+    n_l, sel = oc.selection_from_matrix(g["p"])
+    assert (n_l, len(sel)) == (128, 36)
+    xq, sx = oc.abc_compress(g["x"], n_l, sel, 8, g["u_x"])
+    assert np.mean(xq != g["x_q"].astype(np.int32)) < 1e-3
+    out = oc.linear_backward(g["go"], g["w"], xq, sx, n_o=16, n_l=n_l, sel=sel, u_go=g["u_go"], u_w=g["u_w"], u_gw=g["u_gw"])
+    for name in ("grad_input", "grad_w"):
+        assert np.linalg.norm(out[name] - g[name]) / np.linalg.norm(g[name]) < 1e-3, name
+
+
 def test_int4_pack_roundtrip():
     rng = np.random.default_rng(0)
     c = rng.integers(-7, 8, size=(5, 32))
