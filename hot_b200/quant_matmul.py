@@ -129,7 +129,42 @@ def sawb_quantizer(x: Tensor, quantBits: int, is_batched: bool = False):
     return codes, s[0]
 
 
+def _luq_one(x: Tensor, quantBits: int, u_prune: Optional[Tensor] = None, u_round: Optional[Tensor] = None):
+    """luq_quantizer_BWD (utils/quant_matmul.py:58-76), expression by expression, on the tensor's device.
+    ``u_prune`` / ``u_round``: uniforms in [0, 1) to use instead of fresh draws (the reference draws torch.rand for
+    the stochastic pruning below the smallest level and uniform_(-0.5, 0.5) for the rounding between powers of two)."""
+    mx = torch.max(x)                                   # the signed maximum, as the reference takes it
+    s = mx / (2 ** (2 ** (quantBits - 1) - 1))
+    s_eps = s * (torch.rand(x.shape, device=x.device) if u_prune is None else u_prune)
+    x_abs = x.abs()
+    zero = torch.zeros((), dtype=torch.float32, device=x.device)
+    out = torch.where(x_abs < s, s * torch.sign(x), x)
+    out = torch.where(x_abs < s_eps, zero, out)
+    half = (torch.rand(x.shape, device=x.device) if u_round is None else u_round) - 0.5
+    level = 2 ** torch.floor(torch.log2(out.abs() / s))
+    out_q = 2 ** torch.floor(torch.log2((out.abs() / s + level * half) * 4 / 3))
+    out_q = torch.sign(out) * torch.where(out_q < level, level, out_q)
+    out_q = torch.where(out == 0, zero, out_q)
+    return out_q, s
+
+
+def luq_quantizer(x: Tensor, quantBits: int, is_batched: bool = False, noise=None):
+    """Logarithmic stochastic quantiser (utils/quant_matmul.py:58-83): values are sign * 2^k * s with
+    k in [0, 2^(bits-1) - 1], those below the smallest level pruned stochastically.  Returns (levels as float:
+    0 or +-2^k, s); batched: one s per sample.  The levels are not an integer code of ``quantBits`` bits, so this
+    quantiser is a composition of elementwise device operations and its product is a float matmul
+    (``FLinearQ`` does that when a grad_output side is set to 'luq'); ``noise`` = (u_prune, u_round)."""
+    if x.dtype != torch.float32:
+        x = x.float()
+    if is_batched:
+        outs = [_luq_one(x[b], quantBits, None if noise is None else noise[0][b], None if noise is None else noise[1][b])
+                for b in range(x.shape[0])]
+        return torch.stack([o[0] for o in outs]), torch.stack([o[1] for o in outs])
+    return _luq_one(x, quantBits, None if noise is None else noise[0], None if noise is None else noise[1])
+
+
 quant_scheme_dict = {
+    "luq_quantizer": luq_quantizer,
     "sawb_quantizer": sawb_quantizer,
     "int_quantizer": int_quantizer,
     "stoch_quantizer": stoch_quantizer,
@@ -153,6 +188,8 @@ def _operand(kind: str, scheme, bits: int, what: str, row_ok: bool, k: int = 1 <
         rounding, scale = "philox", "row"
     elif scheme == "sawb" and kind in ("w", "x"):
         rounding, scale = "nearest", "sawb"
+    elif scheme == "luq" and kind in ("gx", "gw"):
+        return "luq"                                    # not an integer format: FLinearQ takes the float path for this side
     elif scheme in ("sawb", "luq", "no", False):
         raise NotImplementedError("%s rounding scheme %r is not built on the native path" % (what, scheme))
     else:
@@ -294,7 +331,7 @@ class FLinearQ(Function):
         if a.quantAuto and len(a.layer_quant_dict) > 0:
             # layer-wise quantiser selection; both sides take GogiQuantBit here, as the reference
             # does (utils/quant_matmul.py:244-245, 307-308)
-            pick = {"stoch_quantizer": "stoch", "norm_quantizer": "nq", "int_quantizer": "int"}
+            pick = {"stoch_quantizer": "stoch", "norm_quantizer": "nq", "int_quantizer": "int", "luq_quantizer": "luq"}
             try:
                 gx_scheme = pick[a.layer_quant_dict[name + "_gx"]]
                 gw_scheme = pick[a.layer_quant_dict[name + "_gw"]]
@@ -306,10 +343,26 @@ class FLinearQ(Function):
             q_gx = _operand("gx", a.quantBWDGogi, a.GogiQuantBit, "GradHo", row_ok=True, k=go.shape[-1])
             q_gw = _operand("gw", a.quantBWDGogw, a.GogwQuantBit, "GradHb", row_ok=True)
         q_w = _operand("w", a.quantBWDWgt, a.weightQuantBit, "Weight", row_ok=False)
-        cfg = ops.LinearConfig(order_o=ctx.order_o, order_l=ctx.order_l, sel_l=ctx.sel, q_gx=q_gx, q_w=q_w, q_gw=q_gw,
-                               q_x=ctx.q_x)
         need_gx, need_gw = ctx.needs_input_grad[0], ctx.needs_input_grad[1]
         gx = gw = None
+        # a grad_output side set to the logarithmic quantiser leaves the integer path: its product is a float matmul
+        luq_gx, luq_gw = q_gx == "luq", q_gw == "luq"
+        if luq_gx or luq_gw:
+            if ctx.scheme not in ("gih_gwlr", "hadamard"):
+                raise NotImplementedError("the logarithmic quantiser is built for transform_scheme gih_gwlr / hadamard")
+            bits_gw = a.GogiQuantBit if (a.quantAuto and len(a.layer_quant_dict) > 0) else a.GogwQuantBit
+            if luq_gx and need_gx:
+                gx = _luq_grad_input(go, w.detach(), ctx.order_o, q_w, a.GogiQuantBit, ctx.per_sample)
+            if luq_gw and need_gw:
+                gw = _luq_grad_weight(go, x_q_t, scale_x, ctx.order_l, ctx.sel, bits_gw, ctx.per_sample, w.dtype)
+            need_gx, need_gw = need_gx and not luq_gx, need_gw and not luq_gw
+            if luq_gx:
+                q_gx = _operand("gx", "stoch", a.GogiQuantBit, "GradHo", row_ok=True, k=go.shape[-1])   # placeholder, unused
+            if luq_gw:
+                q_gw = _operand("gw", "stoch", a.GogwQuantBit, "GradHb", row_ok=True)
+        cfg = ops.LinearConfig(order_o=ctx.order_o, order_l=ctx.order_l, sel_l=ctx.sel, q_gx=q_gx, q_w=q_w, q_gw=q_gw,
+                               q_x=ctx.q_x)
+        gx_luq, gw_luq = gx, gw
         if ctx.scheme == "gilro_gwh":
             n_x, sel_x = ctx.gx_basis
             if need_gw:
@@ -340,9 +393,48 @@ class FLinearQ(Function):
                 gx = ops.linear_backward_lowrank_gx(go, w.detach(), n_x, sel_x, q_gx, q_w)
         elif need_gx or need_gw:
             gx, gw = ops.linear_backward(go, w.detach(), x_q_t, scale_x, cfg, need_gx=need_gx, need_gw=need_gw)
+        gx = gx_luq if gx_luq is not None else gx
+        gw = gw_luq if gw_luq is not None else gw
         if gx is not None:
             gx = gx.reshape(ctx.x_shape)
         return gx, gw, None, None, None
+
+
+def _luq_grad_input(go: Tensor, w: Tensor, order_o: int, q_w, bits: int, per_sample: bool, noise=None) -> Tensor:
+    """grad_input with the logarithmic quantiser on grad_output (utils/quant_matmul.py:237-238, 250-251, 288-290, 342):
+    block Hadamard of grad_output along the output features in float, luq levels, a float32 product with the
+    weight's integer codes (which the integer kernel makes as usual), scales and the 1 / order factor."""
+    from .hadamard_matmul import hadamard, lowering_matmul_front
+    O = go.shape[-1]
+    h = torch.tensor(hadamard(order_o), dtype=torch.float32, device=go.device)
+    levels, s = luq_quantizer(lowering_matmul_front(go.float(), h), bits, per_sample, noise)
+    q_w_t, s_w, _ = ops.col_ht_quant(w, order_o, list(range(order_o)), ops._one_per_byte(q_w), "natural")   # [I, O] codes
+    wq = q_w_t.view(torch.int8)[:, :O].float()
+    gi = torch.matmul(levels, wq.t()) * (s.view(-1, 1, 1) if per_sample else s) * s_w[0] / order_o
+    return gi.to(go.dtype)
+
+
+def _luq_grad_weight(go: Tensor, x_q_t: Tensor, scale_x: Tensor, order_l: int, sel, bits: int, per_sample: bool, dtype,
+                     noise=None) -> Tensor:
+    """grad_weight with the logarithmic quantiser on the projected grad_output (utils/quant_matmul.py:300-301, 313-314,
+    322-324, 344): low-rank projection along the tokens in float, transposed, luq levels, a float32 product with the
+    saved activation codes; per sample and summed over the batch for 3-D inputs."""
+    O = go.shape[-1]
+    go2 = go.reshape(-1, O)
+    go_lr = ops.hla_project_any(go2, order_l, sel)                                   # [L', O] (all samples one after the other)
+    if per_sample:
+        B = go.shape[0]
+        lp = go_lr.shape[0] // B
+        levels, s = luq_quantizer(go_lr.view(B, lp, O).transpose(1, 2).contiguous(), bits, True, noise)     # [B, O, L']
+        pitch = x_q_t.shape[1] // B
+        xq = x_q_t.view(torch.int8).view(-1, B, pitch)[:, :, :lp].permute(1, 2, 0).float()                 # [B, L', I]
+        gw = (torch.bmm(levels, xq) * (s * scale_x).view(-1, 1, 1)).sum(0) / order_l
+    else:
+        lp = go_lr.shape[0]
+        levels, s = luq_quantizer(go_lr.t().contiguous(), bits, False, noise)                               # [O, L']
+        xq = x_q_t.view(torch.int8)[:, :lp].t().float()                                                      # [L', I]
+        gw = torch.matmul(levels, xq) * s * scale_x[0] / order_l
+    return gw.to(dtype)
 
 
 class HQ_Linear(nn.Linear):

@@ -4,7 +4,7 @@ Usage (in a container where the reference checkout is mounted):
 
     python tests/golden/make_golden.py /path/to/reference [section ...]
 
-With section names (``core``, ``lqs_batched``, ``precision``, ``conv``, ``gilro``) only those files are
+With section names (``core``, ``lqs_batched``, ``precision``, ``conv``, ``gilro``, ``luq``) only those files are
 rewritten; without, all of them.
 
 The reference's ``args.py`` imports ``utils/plot.py`` which needs matplotlib; three
@@ -61,7 +61,7 @@ class NoiseQueue:
 
 def main(ref_root: str, out_dir: str, only=()):
     ref_args, hm, qm = _import_reference(ref_root)
-    extra = {"lqs_batched": lqs_batched, "precision": precision_schedule, "conv": conv2d, "gilro": gilro_and_big_order}
+    extra = {"lqs_batched": lqs_batched, "precision": precision_schedule, "conv": conv2d, "gilro": gilro_and_big_order, "luq": luq}
     for name, fn in extra.items():
         if not only or name in only:
             fn(ref_args, hm, qm, out_dir)
@@ -599,6 +599,79 @@ def gilro_and_big_order(ref_args, hm, qm, out_dir: str):
     np.savez_compressed(os.path.join(out_dir, "flinearq_lr_ref128.npz"), x=xx, w=ww, go=go, p=pm.astype(np.int8), u_x=u_x, u_go=u_go,
                         u_w=u_w, u_gw=u_gw, x_q=saved[0].numpy(), scale_x=saved[4].numpy(), grad_input=xt.grad.numpy(),
                         grad_w=wt.grad.numpy())
+
+
+class UniformQueue:
+    """Stand-ins for ``torch.rand`` and ``Tensor.uniform_`` that consume supplied uniforms in [0, 1) in call order
+    (the two random draws of the reference's luq_quantizer_BWD)."""
+
+    def __init__(self):
+        self.queue: list[torch.Tensor] = []
+        self._rand, self._uniform_ = torch.rand, torch.Tensor.uniform_
+
+    def __enter__(self):
+        q = self.queue
+
+        def rand(*shape, **kw):
+            u = q.pop(0)
+            assert tuple(u.shape) == tuple(shape[0] if len(shape) == 1 and not isinstance(shape[0], int) else shape)
+            return u.clone()
+
+        def uniform_(t, a=0.0, b=1.0):
+            u = q.pop(0)
+            assert u.shape == t.shape
+            return t.copy_(u * (b - a) + a)
+
+        torch.rand, torch.Tensor.uniform_ = rand, uniform_
+        return self
+
+    def __exit__(self, *exc):
+        torch.rand, torch.Tensor.uniform_ = self._rand, self._uniform_
+
+
+def luq(ref_args, hm, qm, out_dir: str):
+    """The logarithmic quantiser (utils/quant_matmul.py:58-83) alone, and FLinearQ with it on both grad_output
+    sides (quantBWDGogi = quantBWDGogw = 'luq'; weight and activation keep the stochastic integer quantiser)."""
+    T = torch.from_numpy
+    rng = np.random.default_rng(20250403)
+    out = {}
+    x = (rng.standard_normal((40, 64)) * 1e-3).astype(np.float32)
+    x[3] *= 25.0
+    u1, u2 = rng.random(x.shape, dtype=np.float32), rng.random(x.shape, dtype=np.float32)
+    for bits in (3, 4):
+        with UniformQueue() as uq:
+            uq.queue += [T(u1), T(u2)]
+            q, s = qm.luq_quantizer(T(x), bits, False)
+            assert not uq.queue
+        out["luq%d_levels" % bits], out["luq%d_scale" % bits] = q.numpy(), s.numpy()
+    out.update(x=x, u_prune=u1, u_round=u2)
+    L, O, I = 64, 96, 32
+    _gih_gwlr(ref_args, "stoch")
+    ref_args.quantBWDGogi = ref_args.quantBWDGogw = "luq"
+    ref_args.GogwQuantBit = 4      # the scale is mx / 2^(2^(bits-1)-1): at 8 bits the reference's own expression overflows
+    xx = rng.standard_normal((L, I)).astype(np.float32)
+    ww = ((rng.random((O, I)) * 2 - 1) / np.sqrt(I)).astype(np.float32)
+    go = (rng.standard_normal((L, O)) * 1e-3).astype(np.float32)
+    h = hm.hadamard(16)
+    seq = [int(np.sum(r[:-1] != r[1:])) for r in h]
+    pm = h[np.argsort(seq, kind="stable")[:8]]
+    Lp = L // 2
+    u_x, u_w = rng.random((Lp, I), dtype=np.float32), rng.random((O, I), dtype=np.float32)
+    ug1, ug2 = rng.random((L, O), dtype=np.float32), rng.random((L, O), dtype=np.float32)
+    uw1, uw2 = rng.random((O, Lp), dtype=np.float32), rng.random((O, Lp), dtype=np.float32)
+    xt, wt = T(xx).requires_grad_(True), T(ww).requires_grad_(True)
+    try:
+        with NoiseQueue() as nq, UniformQueue() as uq:
+            nq.queue += [T(u_x), T(u_w)]
+            uq.queue += [T(ug1), T(ug2), T(uw1), T(uw2)]
+            y = qm.FLinearQ.apply(xt, wt, torch.tensor(hm.make_hadamard(O), dtype=torch.float32), torch.tensor(pm, dtype=torch.float32), "layer")
+            y.backward(T(go))
+            assert not nq.queue and not uq.queue
+    finally:
+        _gih_gwlr(ref_args, "stoch")
+    out.update(l_x=xx, l_w=ww, l_go=go, l_p=pm.astype(np.int8), l_u_x=u_x, l_u_w=u_w, l_ug1=ug1, l_ug2=ug2, l_uw1=uw1, l_uw2=uw2,
+               l_grad_input=xt.grad.numpy(), l_grad_w=wt.grad.numpy())
+    np.savez_compressed(os.path.join(out_dir, "luq.npz"), **out)
 
 
 if __name__ == "__main__":

@@ -285,7 +285,7 @@ def test_unbuilt_modes_raise(hot):
     args, qm = hot
     lin = qm.HQ_Linear(64, 64).cuda()
     x = torch.randn(32, 64, device="cuda", requires_grad=True)
-    args.quantBWDAct = "luq"
+    args.quantBWDAct = "luq"                                       # the logarithmic quantiser is for the grad_output sides
     with pytest.raises(NotImplementedError):
         lin(x)
     args.quantBWDAct, args.quantBWDGogi = "stoch", "sawb"       # sawb exists for W and X only
@@ -533,6 +533,53 @@ def test_token_basis_of_order_128(hot, golden):
     x3 = torch.randn(2, 256, I, device="cuda", requires_grad=True)
     lin(x3).backward(torch.randn(2, 256, O, device="cuda") * 1e-3)
     assert tuple(lin.hadamard_bs.shape)[1] == 256 and torch.isfinite(x3.grad).all() and torch.isfinite(lin.weight.grad).all()
+
+
+def test_luq_quantizer_and_layer(hot, golden):
+    """The logarithmic quantiser against the reference's own run with the same two uniform draws (levels and
+    scale; a level can differ where log2 lands on a power of two, hence the 1e-3 allowance), and FLinearQ with it
+    on both grad_output sides (4-bit: at 8 bits the reference's scale expression overflows, and so does this one)."""
+    args, qm = hot
+    g = golden("luq")
+    dev = lambda a: torch.from_numpy(np.ascontiguousarray(a)).cuda()
+    for bits in (3, 4):
+        lv, s = qm.luq_quantizer(dev(g["x"]), bits, False, noise=(dev(g["u_prune"]), dev(g["u_round"])))
+        np.testing.assert_allclose(float(s), float(g["luq%d_scale" % bits]), rtol=1e-6)
+        assert np.mean(lv.cpu().numpy() != g["luq%d_levels" % bits]) < 1e-3
+    lv, s = qm.luq_quantizer(dev(g["x"]).reshape(4, 10, 64), 4, True)                   # batched: one scale per sample
+    assert lv.shape == (4, 10, 64) and s.shape == (4,)
+    assert set(np.unique(np.abs(lv.cpu().numpy()))) <= {0.0} | {2.0 ** k for k in range(0, 12)}
+    with pytest.raises(OverflowError):
+        qm.luq_quantizer(dev(g["x"]), 8, False)
+    assert qm.quant_scheme_dict["luq_quantizer"] is qm.luq_quantizer
+    # the layer: explicit draws through the two helpers the backward uses
+    from hot_b200 import ops
+    x, w, go = g["l_x"], g["l_w"], g["l_go"]
+    n_l, sel = oc.selection_from_matrix(g["l_p"])
+    q = lambda bits, storage, u: ops.Quant(bits, storage, "noise", "tensor", 0, 0, dev(u))
+    cfg = ops.LinearConfig(order_o=16, order_l=n_l, sel_l=[int(v) for v in sel], q_x=q(8, "int8", g["l_u_x"]))
+    x_q_t, s_x = ops.abc_compress(dev(x), cfg)
+    gx = qm._luq_grad_input(dev(go), dev(w), 16, q(4, "int8", g["l_u_w"]), 4, False, noise=(dev(g["l_ug1"]), dev(g["l_ug2"])))
+    gw = qm._luq_grad_weight(dev(go), x_q_t, s_x, n_l, [int(v) for v in sel], 4, False, torch.float32,
+                             noise=(dev(g["l_uw1"]), dev(g["l_uw2"])))
+    for got, name in ((gx, "l_grad_input"), (gw, "l_grad_w")):
+        rel = np.linalg.norm(got.cpu().numpy() - g[name]) / np.linalg.norm(g[name])
+        assert rel < 2e-3, (name, rel)
+    # and through the module, 2-D and 3-D, with its own draws
+    args.quantBWDGogi = args.quantBWDGogw = "luq"
+    args.GogwQuantBit = 4
+    lin = qm.HQ_Linear(w.shape[1], w.shape[0], bias=False).cuda()
+    lin.weight.data = dev(w)
+    xin = dev(x).requires_grad_(True)
+    lin(xin).backward(dev(go))
+    fp_gx, fp_gw = dev(go) @ dev(w), dev(go).t() @ dev(x)
+    assert float(torch.nn.functional.cosine_similarity(xin.grad.flatten(), fp_gx.flatten(), dim=0)) > 0.8
+    assert float(torch.nn.functional.cosine_similarity(lin.weight.grad.flatten(), fp_gw.flatten(), dim=0)) > 0.5
+    args.lowRankPreset = None
+    x3 = torch.randn(3, 32, w.shape[1], device="cuda", requires_grad=True)
+    lin.weight.grad = None
+    lin(x3).backward(torch.randn(3, 32, w.shape[0], device="cuda") * 1e-3)
+    assert torch.isfinite(x3.grad).all() and torch.isfinite(lin.weight.grad).all()
 
 
 def test_vit_with_hot_linears_trains(hot):
