@@ -57,7 +57,7 @@ def parse():
                         "ops.gx_code_storage: packed where the contraction is longer than 1024")
     p.add_argument("--no-cpu-baseline", action="store_true")
     p.add_argument("--sm-margin", type=int, default=-1,
-                   help="SMs left out of the persistent kernels' grids for the all-reduce kernels (multi-GPU; -1: 8 when N > 1)")
+                   help="SMs left out of the persistent kernels' grids for the all-reduce kernels (multi-GPU; default 0)")
     p.add_argument("--bucket-blocks", type=int, default=3, help="transformer blocks per all-reduce bucket (multi-GPU)")
     p.add_argument("--dp-breakdown", action="store_true",
                    help="multi-GPU: also time the step without the all-reduces and the all-reduces alone")
@@ -188,7 +188,7 @@ def run_hot(a):
         raise SystemExit("bench.py needs a CUDA device: the HOT kernels have no CPU path")
     torch.cuda.set_device(local)
     device = torch.device("cuda", local)
-    margin = (8 if world > 1 else 0) if a.sm_margin < 0 else a.sm_margin
+    margin = 0 if a.sm_margin < 0 else a.sm_margin   # measured on 2 GPUs: leaving SMs to the collective costs more than it saves
     if world > 1:
         if margin > 0:
             os.environ.setdefault("NCCL_MAX_CTAS", str(margin))   # the collective's kernels fit the SMs left free for them
@@ -202,17 +202,28 @@ def run_hot(a):
     # grad_w lands in one flat bucket per block, the unit of the all-reduce
     from hot_b200.dp import GradBuckets
     gx_buf = {i_f: torch.empty((a.tokens, i_f), dtype=dtype, device=device) for _, i_f, _ in LAYERS}
-    # a bucket holds the grad_w of `per` consecutive blocks: fewer, larger collectives
+    # a bucket holds the grad_w of `per` consecutive blocks (fewer, larger collectives); the blocks run from the top
+    # down, so the bucket that ends the step is cut down to block 0 alone: its all-reduce has nothing to hide behind
     per = max(1, min(a.bucket_blocks, a.blocks))
-    n_buckets = (a.blocks + per - 1) // per
-    grads = GradBuckets([[(o_f, i_f) for b in range(j * per, min((j + 1) * per, a.blocks)) for _, i_f, o_f in LAYERS]
-                         for j in range(n_buckets)], dtype, device)
+    bounds = list(range(a.blocks, 0, -per))[::-1]            # upper ends, ascending: e.g. 3, 6, 9, 12
+    lows = [max(hi - per, 0) for hi in bounds]
+    if lows[0] == 0 and bounds[0] > 1:
+        lows, bounds = [0, 1] + lows[1:], [1] + bounds       # [0, 1) and [1, first upper end)
+    bucket_of, first_of = {}, {}
+    for j, (lo, hi) in enumerate(zip(lows, bounds)):
+        for b in range(lo, hi):
+            bucket_of[b] = (j, b - lo)
+        first_of[lo] = j
+    n_buckets = len(bounds)
+    grads = GradBuckets([[(o_f, i_f) for b in range(lo, hi) for _, i_f, o_f in LAYERS] for lo, hi in zip(lows, bounds)],
+                        dtype, device)
 
     def block_backward(b):
+        j, k = bucket_of[b]
         for li in reversed(range(len(LAYERS))):
             l = layers[b][li]
             ops.linear_backward(l["go"], l["w"], l["x_q_t"], l["s_x"], l["cfg"], status=status,
-                                gx_out=gx_buf[l["I"]], gw_out=grads.view(b // per, (b % per) * len(LAYERS) + li))
+                                gx_out=gx_buf[l["I"]], gw_out=grads.view(j, k * len(LAYERS) + li))
 
     # one CUDA graph per transformer block: launch overhead off the critical path, and the
     # all-reduce of a block's bucket can be enqueued between graph launches
@@ -232,8 +243,8 @@ def run_hot(a):
     def step(reduce=True):
         for b in reversed(range(a.blocks)):
             graphs[b].replay()
-            if reduce and b % per == 0:            # the bucket's last block (blocks run from the top down) is enqueued
-                grads.reduce_async(b // per)
+            if reduce and b in first_of:           # the bucket's last block (blocks run from the top down) is enqueued
+                grads.reduce_async(first_of[b])
         grads.wait_all()
 
     def reduce_only():
@@ -291,8 +302,9 @@ def run_hot(a):
                       "hadamard_order": 16, "low_rank": "8 of 16 (lowest sequency)", "g_x": "INT4 x INT4, per-tensor, Philox stochastic" + {"int4": "; grad_out codes packed", "int8": "; grad_out codes stored one per byte", "auto": "; grad_out codes packed for qkv and fc1 (contraction > 1024), one per byte for proj and fc2"}[a.gx_storage],
                       "g_w": "INT8 x INT8, per-tensor, Philox stochastic", "activation_buffer": "compressed in forward (not timed)",
                       "cache": "inputs 2.1 GB per GPU, distinct per layer (> 126 MB L2)",
-                      "parallelism": ("dp%d, grad_w all-reduce (NCCL) in %d buckets of %d blocks (%.1f MB each), %d SMs left to "
-                                      "the collective" % (world, n_buckets, per, grads.message_bytes() / n_buckets / 1e6, margin))
+                      "parallelism": ("dp%d, grad_w all-reduce (NCCL) in %d buckets of up to %d blocks (%.1f MB per block; the last one holds "
+                                      "block 0 alone), %d SMs left to the collective"
+                                      % (world, n_buckets, per, grads.message_bytes() / a.blocks / 1e6, margin))
                       if world > 1 else "single GPU"}}
     if breakdown:
         out["dp_breakdown"] = breakdown
@@ -517,8 +529,13 @@ def run_vit_train(a):
     rank, world, local = (int(os.environ.get(k, d)) for k, d in (("RANK", 0), ("WORLD_SIZE", 1), ("LOCAL_RANK", 0)))
     torch.cuda.set_device(local)
     device = torch.device("cuda", local)
+    margin = 0 if a.sm_margin < 0 else a.sm_margin
     if world > 1:
+        if margin > 0:
+            os.environ.setdefault("NCCL_MAX_CTAS", str(margin))
         dist.init_process_group("nccl", device_id=device)
+    from hot_b200 import ops as _ops
+    _ops.set_sm_margin(margin)
     hargs.transform_scheme = "gih_gwlr"
     hargs.TransformGogi = hargs.TransformWgt = hargs.TransformGogw = hargs.TransformInput = True
     hargs.GogiQuantBit, hargs.weightQuantBit, hargs.GogwQuantBit, hargs.actQuantBit = 4, 4, 8, 8
