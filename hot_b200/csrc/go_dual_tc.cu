@@ -31,6 +31,7 @@
 // the nearest and Philox modes; the explicit-noise mode (bit-exact parity with the reference's
 // quantisers) stays on the butterfly kernels.
 // Every wait on an mbarrier is bounded in time (see gemm_i8.cu for the abort protocol).
+#include "ht_device.cuh"
 #include "tc.cuh"
 
 namespace hot {
@@ -184,11 +185,11 @@ __global__ void __launch_bounds__(kThreadsTc, 1)
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
       mbar_init(&full[s], 1);
-      mbar_init(&empty[s], 1);
+      mbar_init(&empty[s], PASS == 0 ? 1 + kColWarps : 1);  // pass 0: the g_w side reads the tile itself (below)
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&tmem_full[b], 1);
-      mbar_init(&tmem_empty[b], kEpiWarps);  // one elected lane per epilogue warp
+      mbar_init(&tmem_empty[b], PASS == 0 ? kRowWarps : kEpiWarps);  // one elected lane per warp that reads it
     }
     *abort_flag = 0u;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -253,7 +254,7 @@ __global__ void __launch_bounds__(kThreadsTc, 1)
         // second box = leading offset; 8-token groups 1024 bytes apart = stride offset); a pair of 16-token blocks per
         // 16 output columns, one block per MMA
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
+        for (int j = 0; j < (PASS == 0 ? 0 : 4); ++j) {
           const uint64_t a0 = smem_desc(stage + (32 * j) * 128, kBoxBytes, 1024, 2);
           const uint64_t a1 = smem_desc(stage + (32 * j + 16) * 128, kBoxBytes, 1024, 2);
           umma_bf16(d_col + 16 * j, a0, b_p0, idesc_col, 0u);
@@ -307,6 +308,46 @@ __global__ void __launch_bounds__(kThreadsTc, 1)
     uint32_t it = 0;
     for (int seq = blockIdx.x; seq < num_tiles; seq += gridDim.x, ++it) {
       const uint32_t buf = it & 1u, bph = (it >> 1) & 1u;
+      if (PASS == 0 && col_side) {
+        // Pass 0, g_w side: the abs-max of the token projection comes from the CUDA cores, straight from the tile in
+        // shared memory (the butterfly of the separate kernels), so that the tensor core has the eight MMAs of the
+        // channel transform left per tile; 16 would bound the pass, eight stay under its HBM time.  A warp takes one
+        // box (64 channels: lane = channel pair, i.e. one 128-byte row per load, conflict-free under the swizzle) and
+        // two 16-token blocks.
+        const uint32_t s = it % kStages, ph = (it / kStages) & 1u;
+        if ((e & 3) == 0) mbar_wait_parked(&full[s], ph, abort_flag, p.wait_ns);
+        asm volatile("bar.sync %0, 128;" ::"r"(1 + (e >> 2)) : "memory");
+        if (*abort_flag) break;
+        const int cw = e - kRowWarps;
+        const uint8_t* tile = smem + s * kStageBytes + (cw & 1) * kBoxBytes + (32 * (cw >> 1)) * 128 + (lane & 3) * 4;
+        float cmax0 = 0.0f, cmax1 = 0.0f;
+#pragma unroll
+        for (int b = 0; b < 2; ++b) {
+          float2 u[16], ev[8];
+#pragma unroll
+          for (int t = 0; t < 16; ++t) {
+            const uint32_t w = *reinterpret_cast<const uint32_t*>(tile + (16 * b + t) * 128 + (((lane >> 2) ^ (t & 7)) << 4));
+            u[t] = make_float2(__uint_as_float(w << 16), __uint_as_float(w & 0xFFFF0000u));
+          }
+          butterfly_tokens16_even(u, ev);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            cmax0 = fmaxf(cmax0, fabsf(ev[i].x));
+            cmax1 = fmaxf(cmax1, fabsf(ev[i].y));
+          }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&empty[s]);  // this warp has read all it needs of the stage
+        if (w_row) {
+          const int ch = tc * kCh + (cw & 1) * 64 + 2 * lane;
+          atomic_absmax(p.max_w + ch, cmax0);
+          atomic_absmax(p.max_w + ch + 1, cmax1);
+        } else {
+          tmax = fmaxf(tmax, fmaxf(cmax0, cmax1));
+        }
+        advance();
+        continue;
+      }
       // The four warps that share a chunk index (one per lane quarter, equal work) wait as a group: one of them
       // polls the accumulator's barrier, the other three sit at a named barrier, which costs them no issue slots.
       if ((e & 3) == 0) mbar_wait_parked(&tmem_full[buf], bph, abort_flag, p.wait_ns);

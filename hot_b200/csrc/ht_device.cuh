@@ -86,6 +86,26 @@ __device__ __forceinline__ void butterfly16(float2 (&v)[8], int n, int lane) {
   }
 }
 
+// Even rows of the order-16 butterfly over tokens for a channel pair: u[t] = (x[t][c], x[t][c+1]).
+// Stage h = 1 leaves the sums x[2i] + x[2i+1] at the even positions, and the later stages only
+// ever combine positions of equal parity, so the even outputs need the sums alone: e[i] is
+// natural row 2i.  Same operations, in the same order, as the full butterfly computes for them.
+__device__ __forceinline__ void butterfly_tokens16_even(const float2 (&u)[16], float2 (&e)[8]) {
+#pragma unroll
+  for (int i = 0; i < 8; ++i) e[i] = add2(u[2 * i], u[2 * i + 1]);
+#pragma unroll
+  for (int h = 1; h < 8; h <<= 1) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      if ((i & h) == 0) {
+        const float2 a = e[i], b = e[i + h];
+        e[i] = add2(a, b);
+        e[i + h] = sub2(a, b);
+      }
+    }
+  }
+}
+
 __device__ __forceinline__ float absmax16(const float2 (&v)[8]) {
   float m = 0.0f;
 #pragma unroll
