@@ -676,10 +676,11 @@ def kernel_legs(ops, layers, a, dtype, device, pk, status):
     in_layer = ["go_dual_quant", "col_ht_quant_w", "gemm_gx_gw_one_launch"]
     top = max(in_layer, key=lambda k: kern[k]["us"])
     tk = kern[top]
-    # DRAM traffic per launch: measured once with ncu (profiles/go_dual_and_gemm_fc1_12608x3072x768_bf16.md):
-    # the grad_out pair moved 167.0 MB (dram read + write) for 116.2 MB of algorithmic bytes at this shape
-    # (two reads of the input, one per pass); scaled here by the algorithmic bytes.  No figure for the others.
-    traffic = round(tk["bytes"] * 167.0 / 116.2) if top == "go_dual_quant" and dtype == torch.bfloat16 else None
+    # DRAM traffic per launch pair, from an ncu capture of this very workload (fc1 gradient, 12,608 x 3,072 bf16,
+    # `bench.py --one-layer fc1`): pass 0 read 77.5 MB + wrote 1.7 MB, pass 1 read 77.5 MB + wrote 5.3 MB (most of its
+    # 38.7 MB of codes were still in L2 when it ended) = 162.0 MB for 116.2 MB of algorithmic bytes; scaled by the
+    # algorithmic bytes for other token counts.  No figure for the other kernels.
+    traffic = round(tk["bytes"] * 162.0 / 116.2) if top == "go_dual_quant" and dtype == torch.bfloat16 else None
     roof = {"kernel": top + (" (two launches: abs-max pass + quantise pass)" if top == "go_dual_quant" else ""),
             "bound": tk["bound"], "achieved": tk["achieved"], "peak": tk["peak"], "unit": tk["unit"],
             "frac": tk["frac"], "traffic": traffic, "launch_us": tk["us"],
