@@ -48,6 +48,19 @@ struct PerDeviceOnce {
 // more than that, and three rounds fewer are a third of the generator's integer work.
 constexpr int kPhiloxRounds = 7;
 
+// The layer's weight [O, I] (dtype, O and transform order of the grad_out it goes with), transformed along O and
+// quantised with one scale by the tensor-core grad_out kernels on the side: codes [I, O] one per byte at pitch
+// ld_qw, scale to s_w[0]; max_w is one scratch word (cleared by the call).
+struct TcWeightJob {
+  const void* w;
+  int64_t ldw, I;
+  hot_quant_t q;
+  void* q_w;
+  int64_t ld_qw;
+  float* s_w;
+  uint32_t* max_w;
+};
+
 // ---- quantiser parameters as the kernels see them -------------------------------------
 struct QuantDev {
   float qmax;          // 2^(bits-1) - 1

@@ -30,6 +30,13 @@
 // last bit of a transformed value may differ, and with it, rarely, a code.  The kernels therefore serve
 // the nearest and Philox modes; the explicit-noise mode (bit-exact parity with the reference's
 // quantisers) stays on the butterfly kernels.
+//
+// The layer's weight rides along (TcWeightJob): its Hadamard transform along the output features and its
+// quantisation are independent of grad_output and tiny (a few MB), but as kernels of their own they cost
+// three launches whose CTAs cannot share an SM with these (measured: 18 us of a 102 us fc1 backward).  Here the
+// epilogue warps each take at most a few 32 x 32 pieces of the weight before their tile loop: abs-max in
+// pass 0, codes in pass 1 (measured: 5 us for the 3,072 x 768 weight, most of it in pass 1, whose warps are
+// the busy ones).
 // Every wait on an mbarrier is bounded in time (see gemm_i8.cu for the abort protocol).
 #include "ht_device.cuh"
 #include "tc.cuh"
@@ -70,6 +77,15 @@ struct TcParams {
   uint32_t* max_w;         // [1] or [O]
   uint32_t* status;
   uint64_t wait_ns;        // time limit of a device-side wait
+  // the weight that rides along (wt == nullptr: none): [O, wt_cols] bf16 -> codes [wt_cols, O], one per byte
+  const uint16_t* wt;
+  int64_t ld_wt, ld_qwt;
+  int wt_cols;             // a multiple of 32
+  int wt_philox;           // Philox rounding, else to nearest
+  uint8_t* q_wt;
+  float* s_wt;             // [1]
+  uint32_t* max_wt;        // [1]
+  QuantDev qwt;
 };
 
 // Instruction descriptor: D = F32, A = B = BF16, B K-major, A K-major or MN-major, M = 128, N = 16.
@@ -154,6 +170,60 @@ __device__ __forceinline__ void quantise32(const uint32_t (&f)[32], const ScaleP
       }
     }
   }
+}
+
+// The weight pieces of one epilogue warp.  A piece is 32 rows (two blocks of the order-16 transform along the
+// output features) x 32 columns (lane = column, i.e. input feature); consecutive pieces go to consecutive
+// CTAs, so the CTAs that run side by side read neighbouring 64-byte stretches of the same rows.  The
+// butterfly is the one of col_ht_quant (stages 1, 2, 4, 8 in place), so the transformed values and the codes
+// are bit-identical to that kernel's; a lane's 32 codes are one aligned run of the stored row of its column
+// (element index = column * O + position), i.e. exactly one Philox block of 4-bit draws or two of 8-bit draws.
+// The pieces go to the CTAs that have one tile less than the others (all of them when the tiles divide evenly):
+// those would otherwise idle for a tile's time at the end of the pass.
+struct WeightWalk {
+  int pieces, col_groups, first, step;  // this warp's pieces: first, first + step, ... < pieces
+};
+__device__ __forceinline__ WeightWalk weight_walk(const TcParams& p, int e, int num_tiles) {
+  WeightWalk w;
+  w.col_groups = p.wt_cols >> 5;
+  w.pieces = (p.O >> 5) * w.col_groups;
+  const int extra = num_tiles % (int)gridDim.x;  // CTAs 0 .. extra-1 walk one tile more
+  const int workers = (int)gridDim.x - extra;
+  w.step = kEpiWarps * workers;
+  w.first = (int)blockIdx.x < extra ? w.pieces : e * workers + ((int)blockIdx.x - extra);
+  return w;
+}
+// loads piece u and transforms it: v[16 * b + k] = row k of H_16 applied to rows 16 * b .. 16 * b + 15 of the piece
+__device__ __forceinline__ void weight_piece_load(const TcParams& p, const WeightWalk& w, int u, int lane, float (&v)[32]) {
+  const int rb = u / w.col_groups, c = (u - rb * w.col_groups) * 32 + lane;
+  const uint16_t* src = p.wt + (int64_t)(rb * 32) * p.ld_wt + c;
+#pragma unroll
+  for (int r = 0; r < 32; ++r) v[r] = __uint_as_float((uint32_t)__ldg(src + (int64_t)r * p.ld_wt) << 16);
+#pragma unroll
+  for (int b = 0; b < 2; ++b)
+#pragma unroll
+    for (int h = 1; h < 16; h <<= 1)
+#pragma unroll
+      for (int i = 0; i < 16; ++i)
+        if ((i & h) == 0) {
+          const float a = v[16 * b + i], d = v[16 * b + i + h];
+          v[16 * b + i] = a + d;
+          v[16 * b + i + h] = a - d;
+        }
+}
+__device__ __forceinline__ void weight_piece_quant(const TcParams& p, const WeightWalk& w, int u, int lane, const float (&v)[32],
+                                                   const ScalePair& sp) {
+  const int rb = u / w.col_groups, c = (u - rb * w.col_groups) * 32 + lane;
+  uint32_t f[32], out[8];
+#pragma unroll
+  for (int i = 0; i < 32; ++i) f[i] = __float_as_uint(v[i]);
+  const uint64_t e0 = (uint64_t)c * (uint64_t)p.O + (uint64_t)(rb * 32);
+  if (!p.wt_philox) quantise32<HOT_ROUND_NEAREST, false, 0>(f, sp, p.qwt, e0, true, out);
+  else if (p.qwt.qmax == 7.0f) quantise32<HOT_ROUND_STOCH_PHILOX, false, 4>(f, sp, p.qwt, e0, true, out);  // the usual width, folded
+  else quantise32<HOT_ROUND_STOCH_PHILOX, false, 0>(f, sp, p.qwt, e0, true, out);
+  uint4* dst = reinterpret_cast<uint4*>(p.q_wt + (int64_t)c * p.ld_qwt + rb * 32);
+  dst[0] = make_uint4(out[0], out[1], out[2], out[3]);
+  dst[1] = make_uint4(out[4], out[5], out[6], out[7]);
 }
 
 // PASS 0: abs-max of both transformed tensors.  PASS 1: quantise against them (RX / RW: rounding of the
@@ -273,6 +343,14 @@ __global__ void __launch_bounds__(kThreadsTc, 1)
     uint8_t* const store_stage = smem + kOffStoreStage + e * 2048;
     uint32_t boxes = 0;
     ScalePair sp_x = scale_from_absmax(0.0f, p.qx.qmax), sp_w = scale_from_absmax(0.0f, p.qw.qmax);
+    // the weight that rides along: in pass 1 this warp's first piece is loaded and transformed before the wait for
+    // pass 0 (the weight is an input of the layer, complete before pass 0 began), so only the scaling waits
+    WeightWalk ww = {0, 1, 0, 1};
+    float wv[32];
+    if (p.wt != nullptr) {
+      ww = weight_walk(p, e, num_tiles);
+      if (PASS == 1 && ww.first < ww.pieces) weight_piece_load(p, ww, ww.first, lane, wv);
+    }
     if (PASS == 1) {
       // launched as a programmatic dependent of pass 0: its abs-maxima are visible once this returns
       asm volatile("griddepcontrol.wait;" ::: "memory");
@@ -281,6 +359,29 @@ __global__ void __launch_bounds__(kThreadsTc, 1)
       if (blockIdx.x == 0 && warp == 2 && lane == 0) {
         if (!x_row) p.s_x[0] = sp_x.s;
         if (!w_row) p.s_w[0] = sp_w.s;
+      }
+    }
+    if (p.wt != nullptr) {
+      if (PASS == 0) {
+        float m = 0.0f;
+        for (int u = ww.first; u < ww.pieces; u += ww.step) {
+          weight_piece_load(p, ww, u, lane, wv);
+          float m4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+          for (int i = 0; i < 32; ++i) m4[i & 3] = fmaxf(m4[i & 3], fabsf(wv[i]));
+          m = fmaxf(m, fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3])));
+        }
+        if (ww.first < ww.pieces) {
+          m = warp_max(m);
+          if (lane == 0) atomic_absmax(p.max_wt, m);
+        }
+      } else {
+        const ScalePair sp_wt = scale_from_absmax(__uint_as_float(p.max_wt[0]), p.qwt.qmax);
+        if (blockIdx.x == 0 && warp == 2 && lane == 0) p.s_wt[0] = sp_wt.s;
+        for (int u = ww.first; u < ww.pieces; u += ww.step) {
+          if (u != ww.first) weight_piece_load(p, ww, u, lane, wv);
+          weight_piece_quant(p, ww, u, lane, wv, sp_wt);
+        }
       }
     }
     float tmax = 0.0f;  // pass 0: this thread's maximum for the per-tensor scale of its side
@@ -509,10 +610,31 @@ bool go_dual_tc_supported(int64_t L, int64_t O, int64_t ldgo, int dtype, int ord
          q_gw.storage == HOT_STORE_INT8 && q_gx.rounding != HOT_ROUND_STOCH_NOISE && q_gw.rounding != HOT_ROUND_STOCH_NOISE;
 }
 
+// Whether the layer's weight [O, I] (same dtype and transform order as grad_out) can ride along.
+bool tc_weight_job_supported(int64_t O, int64_t I, int64_t ldw, const hot_quant_t& q_w) {
+  return I > 0 && I % 32 == 0 && I <= (1 << 24) && O % 32 == 0 && ldw >= I && q_w.scale_mode == HOT_SCALE_TENSOR &&
+         (q_w.rounding == HOT_ROUND_STOCH_PHILOX || q_w.rounding == HOT_ROUND_NEAREST) && q_w.bits >= 2 && q_w.bits <= 8;
+}
+
 int go_dual_quant_tc(const void* go, int64_t L, int64_t O, int64_t ldgo, const hot_quant_t& q_gx, const hot_quant_t& q_gw,
                      void* q_go, int64_t ld_qgo, float* s_gx, void* q_gw_t, int64_t ld_qgw, float* s_gw, uint32_t* max_x,
-                     uint32_t* max_w, uint32_t* status, cudaStream_t st) {
+                     uint32_t* max_w, uint32_t* status, cudaStream_t st, const TcWeightJob* wj) {
   TcParams p;
+  p.wt = nullptr;
+  if (wj) {
+    if (!tc_weight_job_supported(O, wj->I, wj->ldw, wj->q) || wj->ld_qw % 16 != 0 || wj->ld_qw < O || ((uintptr_t)wj->q_w) % 16 != 0 ||
+        ((uintptr_t)wj->w) % 2 != 0)
+      HOT_FAIL(HOT_ERR_ARG, "go_dual_quant: the weight cannot ride along (shape, pitch or quantiser)");
+    p.wt = (const uint16_t*)wj->w;
+    p.ld_wt = wj->ldw;
+    p.ld_qwt = wj->ld_qw;
+    p.wt_cols = (int)wj->I;
+    p.wt_philox = wj->q.rounding == HOT_ROUND_STOCH_PHILOX;
+    p.q_wt = (uint8_t*)wj->q_w;
+    p.s_wt = wj->s_w;
+    p.max_wt = wj->max_w;
+    p.qwt = make_quant_dev(wj->q);
+  }
   p.L = L;
   p.O = (int)O;
   p.x_row = q_gx.scale_mode == HOT_SCALE_ROW;
@@ -535,11 +657,16 @@ int go_dual_quant_tc(const void* go, int64_t L, int64_t O, int64_t ldgo, const h
   const int num_tiles = (int)(O / kCh) * (int)((L + kTok - 1) / kTok);
   const int grid = sms < num_tiles ? sms : num_tiles;
   const size_t nx = p.x_row ? (size_t)L : 1, nw = p.w_row ? (size_t)O : 1;
-  if (max_w >= max_x + nx && (size_t)(max_w - max_x) + nw <= (1u << 18)) {
-    HOT_CUDA(cudaMemsetAsync(max_x, 0, sizeof(uint32_t) * ((size_t)(max_w - max_x) + nw), st));
+  // one clear where the abs-max words lie close together in the order x, w, weight; else one each
+  uint32_t* last = max_w + nw;  // end of the span that starts at max_x
+  if (wj && wj->max_w >= last) last = wj->max_w + 1;
+  const bool one_span = max_w >= max_x + nx && (!wj || wj->max_w >= max_w + nw) && (size_t)(last - max_x) <= (1u << 18);
+  if (one_span) {
+    HOT_CUDA(cudaMemsetAsync(max_x, 0, sizeof(uint32_t) * (size_t)(last - max_x), st));
   } else {
     HOT_CUDA(cudaMemsetAsync(max_x, 0, sizeof(uint32_t) * nx, st));
     HOT_CUDA(cudaMemsetAsync(max_w, 0, sizeof(uint32_t) * nw, st));
+    if (wj) HOT_CUDA(cudaMemsetAsync(wj->max_w, 0, sizeof(uint32_t), st));
   }
   if (int rc = launch_tc_pass<0, HOT_ROUND_NEAREST, HOT_ROUND_NEAREST, true>(m_in, m_qgo, m_qgw, p, grid, st)) return rc;
   const bool px = q_gx.rounding == HOT_ROUND_STOCH_PHILOX, pw = q_gw.rounding == HOT_ROUND_STOCH_PHILOX;

@@ -16,9 +16,10 @@ int go_dual_quant(const void* go, int dtype, int64_t L, int64_t O, int64_t ldgo,
 
 bool go_dual_tc_supported(int64_t L, int64_t O, int64_t ldgo, int dtype, int order_o, int order_l, int rank_l,
                           const int32_t* sel_l, const hot_quant_t& q_gx, const hot_quant_t& q_gw);
+bool tc_weight_job_supported(int64_t O, int64_t I, int64_t ldw, const hot_quant_t& q_w);
 int go_dual_quant_tc(const void* go, int64_t L, int64_t O, int64_t ldgo, const hot_quant_t& q_gx, const hot_quant_t& q_gw,
                      void* q_go, int64_t ld_qgo, float* s_gx, void* q_gw_t, int64_t ld_qgw, float* s_gw, uint32_t* max_x,
-                     uint32_t* max_w, uint32_t* status, cudaStream_t st);
+                     uint32_t* max_w, uint32_t* status, cudaStream_t st, const TcWeightJob* wj);
 
 namespace {
 
@@ -31,11 +32,13 @@ bool use_tc(int64_t L, int64_t O, int64_t ldgo, const hot_linear_cfg_t& c) {
   return go_dual_tc_supported(L, O, ldgo, c.dtype, c.order_o, c.order_l, c.rank_l, c.sel_l, c.q_gx, c.q_gw);
 }
 
+// wj: the weight that rides along; only with the tensor-core pair (see weight_rides)
 int go_dual_any(const void* go, int64_t L, int64_t O, int64_t ldgo, const hot_linear_cfg_t& c, void* q_go, int64_t ld_qgo,
                 float* s_gx, void* q_gw_t, int64_t ld_qgw, float* s_gw, uint32_t* max_x, uint32_t* max_w, uint32_t* status,
-                cudaStream_t st) {
+                cudaStream_t st, const TcWeightJob* wj = nullptr) {
   if (use_tc(L, O, ldgo, c))
-    return go_dual_quant_tc(go, L, O, ldgo, c.q_gx, c.q_gw, q_go, ld_qgo, s_gx, q_gw_t, ld_qgw, s_gw, max_x, max_w, status, st);
+    return go_dual_quant_tc(go, L, O, ldgo, c.q_gx, c.q_gw, q_go, ld_qgo, s_gx, q_gw_t, ld_qgw, s_gw, max_x, max_w, status, st, wj);
+  if (wj) HOT_FAIL(HOT_ERR_ARG, "go_dual_quant: the weight rides along with the tensor-core kernels only");
   return go_dual_quant(go, c.dtype, L, O, ldgo, c.order_o, c.sel_l, c.q_gx, c.q_gw, q_go, ld_qgo, s_gx, q_gw_t, ld_qgw, s_gw,
                        max_x, max_w, status, st);
 }
@@ -188,10 +191,18 @@ extern "C" int hot_linear_backward(const void* go, int64_t ldgo, const void* w, 
   const bool dual = grad_x && grad_w &&
                     go_dual_supported(L, O, ldgo, cfg->dtype, cfg->order_o, cfg->order_l, cfg->rank_l, cfg->sel_l, cfg->q_gx,
                                       cfg->q_gw);
-  // the weight side starts first, on the helper stream
+  // The weight: where the tensor-core grad_out kernels run, they transform and quantise it on the side (no launch
+  // of its own); else it starts first, on the helper stream.  HOT_WEIGHT_QUANT=separate keeps it apart (the parity
+  // tests compare the two).
   SideStream* side = nullptr;
   cudaStream_t main_st = (cudaStream_t)stream;
-  if (grad_x) {
+  hot_quant_t q_w8 = cfg->q_w;
+  q_w8.storage = HOT_STORE_INT8;
+  const char* wq_env = getenv("HOT_WEIGHT_QUANT");
+  const bool weight_rides = grad_x && dual && use_tc(L, O, ldgo, *cfg) && cfg->q_w.scale_mode == HOT_SCALE_TENSOR &&
+                            tc_weight_job_supported(O, I, ldw, q_w8) && !(wq_env && wq_env[0] == 's');
+  const TcWeightJob wj = {w, ldw, I, q_w8, base + ws.off_qw, ws.ld_qw, s_w, scratch + ws.w_scratch_off};
+  if (grad_x && !weight_rides) {
     if (cfg->q_w.scale_mode == HOT_SCALE_ROW) HOT_FAIL(HOT_ERR_UNSUPPORTED, "hot_linear_backward: the weight takes one scale");
     if ((rc = side_stream(&side))) return rc;
     HOT_CUDA(cudaEventRecord(side->fork, main_st));
@@ -201,9 +212,7 @@ extern "C" int hot_linear_backward(const void* go, int64_t ldgo, const void* w, 
     // The quantised weight is the B operand of every CTA of the g_x GEMM and is tiny (O * I bytes):
     // it is stored one code per byte whatever its bit width, so that it reaches the tensor core by
     // TMA alone and only grad_out (the large, streamed operand) is expanded in shared memory.
-    hot_quant_t q_w = cfg->q_w;
-    q_w.storage = HOT_STORE_INT8;
-    rc = hot_col_ht_quant(w, cfg->dtype, O, I, ldw, cfg->order_o, ident, cfg->order_o, &q_w, HOT_LAYOUT_NATURAL,
+    rc = hot_col_ht_quant(w, cfg->dtype, O, I, ldw, cfg->order_o, ident, cfg->order_o, &q_w8, HOT_LAYOUT_NATURAL,
                           base + ws.off_qw, ws.ld_qw, s_w, scratch + ws.w_scratch_off, (hot_stream_t)side->stream);
     cudaEventRecord(side->join, side->stream);
     if (rc) {
@@ -218,7 +227,7 @@ extern "C" int hot_linear_backward(const void* go, int64_t ldgo, const void* w, 
   };
   if (dual) {
     rc = go_dual_any(go, L, O, ldgo, *cfg, base + ws.off_qgo, ws.ld_qgo, s_go, base + ws.off_qgw, ws.ld_qgw, s_gw, scratch + 64,
-                     scratch + 64 + L, status_word, (cudaStream_t)stream);
+                     scratch + 64 + L, status_word, (cudaStream_t)stream, weight_rides ? &wj : nullptr);
     if (rc) {
       rejoin();
       return rc;

@@ -286,9 +286,10 @@ def _run_backward(ops, x, w, go, order_l, sel, dtype, *, gx_row=False, gw_row=Fa
 @pytest.mark.parametrize("rounding", ["noise", "philox", "nearest"])
 @pytest.mark.parametrize("gx_row,gw_row", [(False, False), (True, True)])
 @pytest.mark.parametrize("preset", ["half16", "ref32"])
-def test_linear_backward_vs_oracle(ops, dtype, rounding, gx_row, gw_row, preset):
+@pytest.mark.parametrize("I", [136, 160])   # 160: a multiple of 32, so that in bf16 the weight is quantised by the grad_out kernels
+def test_linear_backward_vs_oracle(ops, dtype, rounding, gx_row, gw_row, preset, I):
     rng = np.random.default_rng(5)
-    L, O, I = 32 * 13, 384, 136
+    L, O = 32 * 13, 384
     order_l, sel = (16, oc.lowrank_preset(16, 8)) if preset == "half16" else (32, oc.wht_selection(6304, 50)[1])
     x = rng.standard_normal((L, I)).astype(np.float32)
     x[:, 5] *= 20.0
@@ -509,6 +510,39 @@ def test_go_dual_quant_tensor_core_transforms(ops, rounding, gx_scale, gw_scale,
         assert d.sum() <= max(2, 1e-5 * d.size), "%d of %d codes differ" % (int(d.sum()), d.size)
         assert np.abs(got - want).max() <= 1       # rows whose scale moved by an ulp: still neighbours
     assert rows_x.mean() > 0.99 and rows_w.mean() > 0.99
+
+
+@pytest.mark.parametrize("rounding", ["philox", "nearest"])
+@pytest.mark.parametrize("w_bits", [4, 8, 3])
+@pytest.mark.parametrize("L,O,I", [(32 * 13, 384, 160), (256, 128, 32), (640, 256, 768), (128 * 150, 128, 64)])
+def test_weight_quantised_by_the_grad_out_kernels_matches_its_own_kernels(ops, monkeypatch, rounding, w_bits, L, O, I):
+    """In bf16 with the order-16 bases the weight is transformed and quantised inside the two grad_out kernels;
+    HOT_WEIGHT_QUANT=separate sends it through hot_col_ht_quant instead.  Same codes and scale, hence the same
+    accumulators: both gradients must be bit-identical."""
+    rng = np.random.default_rng(L + O + I + w_bits)
+    x = torch.from_numpy(rng.standard_normal((L, I)).astype(np.float32)).cuda().bfloat16()
+    w = torch.from_numpy(((rng.random((O, I)) * 2 - 1) / np.sqrt(I)).astype(np.float32)).cuda().bfloat16()
+    w[5, 3] = 1.5   # one large entry decides the scale
+    go = torch.from_numpy((rng.standard_normal((L, O)) * 1e-3).astype(np.float32)).cuda().bfloat16()
+    sel = [int(v) for v in oc.lowrank_preset(16, 8)]
+    cfg = ops.LinearConfig(order_o=16, order_l=16, sel_l=sel, q_gx=ops.Quant(4, "int4", rounding, "tensor", 3, 1),
+                           q_w=ops.Quant(w_bits, "int4" if w_bits <= 4 else "int8", rounding, "tensor", 7, 2),
+                           q_gw=ops.Quant(8, "int8", rounding, "tensor", 11, 3), q_x=ops.Quant(8, "int8", rounding, "tensor", 13, 4))
+    x_q_t, s_x = ops.abc_compress(x, cfg)
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    out = {}
+    for mode in ("rides", "separate"):
+        if mode == "separate":
+            monkeypatch.setenv("HOT_WEIGHT_QUANT", "separate")
+        else:
+            monkeypatch.delenv("HOT_WEIGHT_QUANT", raising=False)
+        gx, gw = ops.linear_backward(go, w, x_q_t, s_x, cfg, status=status)
+        torch.cuda.synchronize()
+        out[mode] = (gx.clone(), gw.clone())
+    assert int(status.item()) == 0
+    assert float(out["rides"][0].float().abs().max()) > 0
+    assert torch.equal(out["rides"][0], out["separate"][0])
+    assert torch.equal(out["rides"][1], out["separate"][1])
 
 
 def test_go_dual_quant_rejects_what_it_does_not_cover(ops):
