@@ -81,9 +81,10 @@ def parse():
     return p.parse_args()
 
 
-# kernels one layer backward launches: grad_out abs-max pass + quantise pass, weight abs-max + quantise
-# (helper stream), and one persistent kernel for both integer GEMMs (memset nodes are not kernels)
-KERNELS_PER_LAYER = 5
+# kernels one layer backward launches: grad_out abs-max pass + quantise pass (the weight's abs-max and codes come
+# out of the same two launches) and one persistent kernel for both integer GEMMs (memset nodes are not kernels);
+# in fp32 the weight has two kernels of its own on the helper stream
+KERNELS_PER_LAYER = {"bf16": 3, "fp32": 5}
 
 
 def step_flops(tokens: int, blocks: int) -> float:
@@ -297,7 +298,7 @@ def run_hot(a):
     out = {"metric": METRIC, "value": round(value, 2), "unit": UNIT, "n_gpus": world, "steps": a.steps,
            "warmup": max(a.warmup, 3), "ms_per_step": round(ms_step, 4), "ms_per_layer": round(ms_step / n_layers, 5),
            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8/int4 codes, int32 accumulate",
-           "data": "synthetic", "gpu_launches": n_layers * KERNELS_PER_LAYER * a.steps,
+           "data": "synthetic", "gpu_launches": n_layers * KERNELS_PER_LAYER[a.dtype] * a.steps,
            "config": {"workload": WORKLOAD, "tokens_per_gpu": a.tokens, "layers": n_layers, "tensor_dtype": a.dtype,
                       "hadamard_order": 16, "low_rank": "8 of 16 (lowest sequency)", "g_x": "INT4 x INT4, per-tensor, Philox stochastic" + {"int4": "; grad_out codes packed", "int8": "; grad_out codes stored one per byte", "auto": "; grad_out codes packed for qkv and fc1 (contraction > 1024), one per byte for proj and fc2"}[a.gx_storage],
                       "g_w": "INT8 x INT8, per-tensor, Philox stochastic", "activation_buffer": "compressed in forward (not timed)",

@@ -36,7 +36,7 @@
 // three launches whose CTAs cannot share an SM with these (measured: 18 us of a 102 us fc1 backward).  Here the
 // epilogue warps each take at most a few 32 x 32 pieces of the weight before their tile loop: abs-max in
 // pass 0, codes in pass 1 (measured: 5 us for the 3,072 x 768 weight, most of it in pass 1, whose warps are
-// the busy ones).
+// the busy ones; the CTAs whose warps had pieces then simply draw fewer tiles).
 // Every wait on an mbarrier is bounded in time (see gemm_i8.cu for the abort protocol).
 #include "ht_device.cuh"
 #include "tc.cuh"
@@ -60,7 +60,15 @@ constexpr int kThreadsTc = (2 + kEpiWarps) * 32;
 constexpr int kOffOperands = kStages * kStageBytes;      // H16 | P (first block) | P (second block): 512 bytes each
 constexpr int kOffStoreStage = kOffOperands + 2048;      // per epilogue warp two boxes of 32 rows x 32 bytes
 constexpr int kOffBarriers = kOffStoreStage + kEpiWarps * 2048;
-constexpr int kSmemTc = kOffBarriers + 256 + 1024;       // barriers + slack to align the base to 1024
+constexpr int kSmemTc = kOffBarriers + 512 + 1024;       // barriers and tile descriptors + slack to align the base to 1024
+// Tiles are handed out at run time: the producer thread draws the next tile from a counter in global memory and
+// leaves its coordinates in a ring of descriptors in shared memory, where every role reads them once the tile's
+// data barrier has let it through.  A descriptor is written after the wait for its stage, i.e. when the
+// epilogue of the tile six places back (four stages, two accumulator buffers) has its values in registers, so
+// eight slots cannot be overrun.  After the last tile the producer writes a descriptor that says so and completes
+// the stage's barrier by hand; the MMA thread passes that on through the accumulator's barrier.  A CTA that starts
+// late, or not at all while another kernel holds its SM, therefore costs the others only the tiles it does not take.
+constexpr int kSched = 8;
 
 // natural row of H_16 of output slot j of the token projection (the 8 lowest-sequency rows)
 __device__ constexpr int kSlotRow[8] = {0, 8, 12, 4, 6, 14, 10, 2};
@@ -76,6 +84,7 @@ struct TcParams {
   uint32_t* max_x;         // [1] or [L]
   uint32_t* max_w;         // [1] or [O]
   uint32_t* status;
+  uint32_t* counters;      // [2], zero before pass 0: tiles drawn in pass 0 / in pass 1
   uint64_t wait_ns;        // time limit of a device-side wait
   // the weight that rides along (wt == nullptr: none): [O, wt_cols] bf16 -> codes [wt_cols, O], one per byte
   const uint16_t* wt;
@@ -178,19 +187,16 @@ __device__ __forceinline__ void quantise32(const uint32_t (&f)[32], const ScaleP
 // butterfly is the one of col_ht_quant (stages 1, 2, 4, 8 in place), so the transformed values and the codes
 // are bit-identical to that kernel's; a lane's 32 codes are one aligned run of the stored row of its column
 // (element index = column * O + position), i.e. exactly one Philox block of 4-bit draws or two of 8-bit draws.
-// The pieces go to the CTAs that have one tile less than the others (all of them when the tiles divide evenly):
-// those would otherwise idle for a tile's time at the end of the pass.
+// Warp e of CTA b takes pieces e * gridDim.x + b, + kEpiWarps * gridDim.x, ...
 struct WeightWalk {
-  int pieces, col_groups, first, step;  // this warp's pieces: first, first + step, ... < pieces
+  int pieces, col_groups, first, step;
 };
-__device__ __forceinline__ WeightWalk weight_walk(const TcParams& p, int e, int num_tiles) {
+__device__ __forceinline__ WeightWalk weight_walk(const TcParams& p, int e) {
   WeightWalk w;
   w.col_groups = p.wt_cols >> 5;
   w.pieces = (p.O >> 5) * w.col_groups;
-  const int extra = num_tiles % (int)gridDim.x;  // CTAs 0 .. extra-1 walk one tile more
-  const int workers = (int)gridDim.x - extra;
-  w.step = kEpiWarps * workers;
-  w.first = (int)blockIdx.x < extra ? w.pieces : e * workers + ((int)blockIdx.x - extra);
+  w.first = e * (int)gridDim.x + (int)blockIdx.x;
+  w.step = kEpiWarps * (int)gridDim.x;
   return w;
 }
 // loads piece u and transforms it: v[16 * b + k] = row k of H_16 applied to rows 16 * b .. 16 * b + 15 of the piece
@@ -241,7 +247,8 @@ __global__ void __launch_bounds__(kThreadsTc, 1)
   uint64_t* empty = full + kStages;                                    // the tile's MMAs retired
   uint64_t* tmem_full = empty + kStages;                               // [2] both accumulators of a tile complete
   uint64_t* tmem_empty = tmem_full + 2;                                // [2] drained by the epilogue warps
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
+  volatile int2* sched_tile = reinterpret_cast<volatile int2*>(tmem_empty + 2);  // [kSched] (token tile, channel tile); x < 0: no more tiles
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(const_cast<int2*>(sched_tile + kSched));
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -249,8 +256,6 @@ __global__ void __launch_bounds__(kThreadsTc, 1)
   const int tiles_c = p.O / kCh;
   const int tiles_t = (int)((p.L + kTok - 1) / kTok);
   const int num_tiles = tiles_c * tiles_t;
-  // tile sequence of this CTA: blockIdx.x, + gridDim.x, ...; pass 1 mirrors the index
-  auto tile_of = [&](int seq) { return PASS == 0 ? seq : num_tiles - 1 - seq; };
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
@@ -289,11 +294,25 @@ __global__ void __launch_bounds__(kThreadsTc, 1)
     // ---- TMA producer (grad_out is not written by the kernel before this one: no dependency wait) ----
     if (lane == 0) {
       uint32_t s = 0, ph = 0;
-      for (int seq = blockIdx.x; seq < num_tiles; seq += gridDim.x, s = (s + 1 == kStages ? 0 : s + 1), ph ^= (s == 0 ? 1u : 0u)) {
+      // A CTA's first tile is its own index, so that the first copy does not wait for a round trip to the counter;
+      // after that the draw for the next tile is in flight while this one's waits and copies are issued (a CTA ends
+      // up drawing one number more than it uses).
+      int next = (int)blockIdx.x;
+      for (uint32_t it = 0;; ++it, s = (s + 1 == kStages ? 0 : s + 1), ph ^= (s == 0 ? 1u : 0u)) {
+        const int seq = next;
+        if (seq < num_tiles) next = (int)(gridDim.x + atomicAdd(p.counters + PASS, 1u));
         if (!mbar_wait_parked(&empty[s], ph ^ 1u, abort_flag, p.wait_ns)) break;
-        const int t = tile_of(seq);
+        volatile int2* desc = sched_tile + (it % kSched);
+        if (seq >= num_tiles) {
+          desc->x = -1;
+          mbar_arrive(&full[s]);  // no data: the phase completes on this arrival alone
+          break;
+        }
+        const int t = PASS == 0 ? seq : num_tiles - 1 - seq;  // pass 1 takes the tiles in the reverse order of pass 0 (see above)
         const int tt = t / tiles_c, tc = t % tiles_c;
-        mbar_expect_tx(&full[s], kStageBytes);
+        desc->x = tt;
+        desc->y = tc;
+        mbar_expect_tx(&full[s], kStageBytes);  // (release: the descriptor is visible to whoever sees this phase complete)
         tma_load_2d(smem + s * kStageBytes, &tmap_in, &full[s], tc * (kCh * 2), tt * kTok);
         tma_load_2d(smem + s * kStageBytes + kBoxBytes, &tmap_in, &full[s], tc * (kCh * 2) + 128, tt * kTok);
       }
@@ -305,11 +324,15 @@ __global__ void __launch_bounds__(kThreadsTc, 1)
       const uint32_t ops = smem_u32(smem + kOffOperands);
       const uint64_t b_h = smem_desc(ops, 128, 256, 0);
       const uint64_t b_p0 = smem_desc(ops + 512, 128, 256, 0), b_p1 = smem_desc(ops + 1024, 128, 256, 0);
-      uint32_t s = 0, ph = 0, it = 0;
-      for (int seq = blockIdx.x; seq < num_tiles; seq += gridDim.x, ++it, s = (s + 1 == kStages ? 0 : s + 1), ph ^= (s == 0 ? 1u : 0u)) {
+      uint32_t s = 0, ph = 0;
+      for (uint32_t it = 0;; ++it, s = (s + 1 == kStages ? 0 : s + 1), ph ^= (s == 0 ? 1u : 0u)) {
         const uint32_t buf = it & 1u, bph = (it >> 1) & 1u;
         if (!mbar_wait_parked(&tmem_empty[buf], bph ^ 1u, abort_flag, p.wait_ns)) break;
         if (!mbar_wait_parked(&full[s], ph, abort_flag, p.wait_ns)) break;
+        if (sched_tile[it % kSched].x < 0) {
+          mbar_arrive(&tmem_full[buf]);  // no more tiles: let the epilogue warps through to see it too
+          break;
+        }
         tc_fence_after();
         const uint32_t stage = smem_u32(smem + s * kStageBytes);
         const uint32_t d_row = tmem_base + buf * kBufCols, d_col = d_row + 128;
@@ -348,7 +371,7 @@ __global__ void __launch_bounds__(kThreadsTc, 1)
     WeightWalk ww = {0, 1, 0, 1};
     float wv[32];
     if (p.wt != nullptr) {
-      ww = weight_walk(p, e, num_tiles);
+      ww = weight_walk(p, e);
       if (PASS == 1 && ww.first < ww.pieces) weight_piece_load(p, ww, ww.first, lane, wv);
     }
     if (PASS == 1) {
@@ -386,39 +409,23 @@ __global__ void __launch_bounds__(kThreadsTc, 1)
     }
     float tmax = 0.0f;  // pass 0: this thread's maximum for the per-tensor scale of its side
     const int64_t out_len = p.L / 2;
-    // tile coordinates advance without divisions: the sequence moves by gridDim.x tiles per step (pass 1: backwards)
-    const int step_t = (int)gridDim.x / tiles_c, step_c = (int)gridDim.x % tiles_c;
-    int tt = tile_of(blockIdx.x) / tiles_c, tc = tile_of(blockIdx.x) % tiles_c;
-    auto advance = [&]() {
-      if (PASS == 0) {
-        tt += step_t;
-        tc += step_c;
-        if (tc >= tiles_c) {
-          tc -= tiles_c;
-          ++tt;
-        }
-      } else {
-        tt -= step_t;
-        tc -= step_c;
-        if (tc < 0) {
-          tc += tiles_c;
-          --tt;
-        }
-      }
-    };
-    uint32_t it = 0;
-    for (int seq = blockIdx.x; seq < num_tiles; seq += gridDim.x, ++it) {
+    const int grp = e >> 2;  // four warps (one per lane quarter) with the same chunk index
+    for (uint32_t it = 0;; ++it) {
       const uint32_t buf = it & 1u, bph = (it >> 1) & 1u;
+      const uint32_t s = it % kStages, ph = (it / kStages) & 1u;
+      // The four warps of a group wait as one: the first polls the barrier of the tile's data (the accumulators; in
+      // pass 0 on the g_w side the tile itself), the others sit at a named barrier, which costs them no issue slots.
+      if ((e & 3) == 0)
+        mbar_wait_parked(PASS == 0 && col_side ? &full[s] : &tmem_full[buf], PASS == 0 && col_side ? ph : bph, abort_flag, p.wait_ns);
+      asm volatile("bar.sync %0, 128;" ::"r"(1 + grp) : "memory");
+      const int tt = sched_tile[it % kSched].x, tc = sched_tile[it % kSched].y;
+      if (tt < 0 || *abort_flag) break;  // no more tiles, or a wait ran out somewhere (every warp of the group sees it after the barrier)
       if (PASS == 0 && col_side) {
         // Pass 0, g_w side: the abs-max of the token projection comes from the CUDA cores, straight from the tile in
         // shared memory (the butterfly of the separate kernels), so that the tensor core has the eight MMAs of the
         // channel transform left per tile; 16 would bound the pass, eight stay under its HBM time.  A warp takes one
         // box (64 channels: lane = channel pair, i.e. one 128-byte row per load, conflict-free under the swizzle) and
         // two 16-token blocks.
-        const uint32_t s = it % kStages, ph = (it / kStages) & 1u;
-        if ((e & 3) == 0) mbar_wait_parked(&full[s], ph, abort_flag, p.wait_ns);
-        asm volatile("bar.sync %0, 128;" ::"r"(1 + (e >> 2)) : "memory");
-        if (*abort_flag) break;
         const int cw = e - kRowWarps;
         const uint8_t* tile = smem + s * kStageBytes + (cw & 1) * kBoxBytes + (32 * (cw >> 1)) * 128 + (lane & 3) * 4;
         float cmax0 = 0.0f, cmax1 = 0.0f;
@@ -446,14 +453,8 @@ __global__ void __launch_bounds__(kThreadsTc, 1)
         } else {
           tmax = fmaxf(tmax, fmaxf(cmax0, cmax1));
         }
-        advance();
         continue;
       }
-      // The four warps that share a chunk index (one per lane quarter, equal work) wait as a group: one of them
-      // polls the accumulator's barrier, the other three sit at a named barrier, which costs them no issue slots.
-      if ((e & 3) == 0) mbar_wait_parked(&tmem_full[buf], bph, abort_flag, p.wait_ns);
-      asm volatile("bar.sync %0, 128;" ::"r"(1 + (e >> 2)) : "memory");
-      if (*abort_flag) break;  // set by whichever wait ran out; every warp of the group sees it after the barrier
       tc_fence_after();
       const int64_t tok0 = (int64_t)tt * kTok;
       const int ch0 = tc * kCh;
@@ -479,7 +480,6 @@ __global__ void __launch_bounds__(kThreadsTc, 1)
           if (w_row) atomic_absmax(p.max_w + ch0 + q * 32 + lane, m);
           else tmax = fmaxf(tmax, m);
         }
-        advance();
         continue;
       }
       // ---- pass 1: quantise the chunk, stage it as 32 rows of 16 or 32 bytes, hand the box to the copy engine ----
@@ -532,7 +532,6 @@ __global__ void __launch_bounds__(kThreadsTc, 1)
         if (inside) tma_store_2d(map, box, x, y);
         bulk_commit_group();  // always: the buffer rotation counts groups
       }
-      advance();
     }
     if (PASS == 0) {
       tmax = warp_max(tmax);
@@ -618,8 +617,9 @@ bool tc_weight_job_supported(int64_t O, int64_t I, int64_t ldw, const hot_quant_
 
 int go_dual_quant_tc(const void* go, int64_t L, int64_t O, int64_t ldgo, const hot_quant_t& q_gx, const hot_quant_t& q_gw,
                      void* q_go, int64_t ld_qgo, float* s_gx, void* q_gw_t, int64_t ld_qgw, float* s_gw, uint32_t* max_x,
-                     uint32_t* max_w, uint32_t* status, cudaStream_t st, const TcWeightJob* wj) {
+                     uint32_t* max_w, uint32_t* counters, uint32_t* status, cudaStream_t st, const TcWeightJob* wj) {
   TcParams p;
+  p.counters = counters;  // two words: tiles drawn by each pass
   p.wt = nullptr;
   if (wj) {
     if (!tc_weight_job_supported(O, wj->I, wj->ldw, wj->q) || wj->ld_qw % 16 != 0 || wj->ld_qw < O || ((uintptr_t)wj->q_w) % 16 != 0 ||
@@ -657,16 +657,24 @@ int go_dual_quant_tc(const void* go, int64_t L, int64_t O, int64_t ldgo, const h
   const int num_tiles = (int)(O / kCh) * (int)((L + kTok - 1) / kTok);
   const int grid = sms < num_tiles ? sms : num_tiles;
   const size_t nx = p.x_row ? (size_t)L : 1, nw = p.w_row ? (size_t)O : 1;
-  // one clear where the abs-max words lie close together in the order x, w, weight; else one each
-  uint32_t* last = max_w + nw;  // end of the span that starts at max_x
-  if (wj && wj->max_w >= last) last = wj->max_w + 1;
-  const bool one_span = max_w >= max_x + nx && (!wj || wj->max_w >= max_w + nw) && (size_t)(last - max_x) <= (1u << 18);
-  if (one_span) {
-    HOT_CUDA(cudaMemsetAsync(max_x, 0, sizeof(uint32_t) * (size_t)(last - max_x), st));
+  // one clear where the scratch words lie close together (they do in every caller of this library), else one each
+  struct Span {
+    uint32_t* p;
+    size_t n;
+  } spans[4] = {{max_x, nx}, {max_w, nw}, {counters, 2}, {wj ? wj->max_w : max_x, wj ? (size_t)1 : (size_t)0}};
+  uint32_t *lo = max_x, *hi = max_x;
+  for (const Span& sp : spans) {
+    if (sp.n == 0) continue;
+    if (sp.p < lo) lo = sp.p;
+    if (sp.p + sp.n > hi) hi = sp.p + sp.n;
+  }
+  size_t used = 0;
+  for (const Span& sp : spans) used += sp.n;
+  if ((size_t)(hi - lo) <= (1u << 18) || (size_t)(hi - lo) <= 2 * used) {
+    HOT_CUDA(cudaMemsetAsync(lo, 0, sizeof(uint32_t) * (size_t)(hi - lo), st));
   } else {
-    HOT_CUDA(cudaMemsetAsync(max_x, 0, sizeof(uint32_t) * nx, st));
-    HOT_CUDA(cudaMemsetAsync(max_w, 0, sizeof(uint32_t) * nw, st));
-    if (wj) HOT_CUDA(cudaMemsetAsync(wj->max_w, 0, sizeof(uint32_t), st));
+    for (const Span& sp : spans)
+      if (sp.n) HOT_CUDA(cudaMemsetAsync(sp.p, 0, sizeof(uint32_t) * sp.n, st));
   }
   if (int rc = launch_tc_pass<0, HOT_ROUND_NEAREST, HOT_ROUND_NEAREST, true>(m_in, m_qgo, m_qgw, p, grid, st)) return rc;
   const bool px = q_gx.rounding == HOT_ROUND_STOCH_PHILOX, pw = q_gw.rounding == HOT_ROUND_STOCH_PHILOX;

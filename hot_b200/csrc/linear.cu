@@ -19,7 +19,7 @@ bool go_dual_tc_supported(int64_t L, int64_t O, int64_t ldgo, int dtype, int ord
 bool tc_weight_job_supported(int64_t O, int64_t I, int64_t ldw, const hot_quant_t& q_w);
 int go_dual_quant_tc(const void* go, int64_t L, int64_t O, int64_t ldgo, const hot_quant_t& q_gx, const hot_quant_t& q_gw,
                      void* q_go, int64_t ld_qgo, float* s_gx, void* q_gw_t, int64_t ld_qgw, float* s_gw, uint32_t* max_x,
-                     uint32_t* max_w, uint32_t* status, cudaStream_t st, const TcWeightJob* wj);
+                     uint32_t* max_w, uint32_t* counters, uint32_t* status, cudaStream_t st, const TcWeightJob* wj);
 
 namespace {
 
@@ -32,12 +32,14 @@ bool use_tc(int64_t L, int64_t O, int64_t ldgo, const hot_linear_cfg_t& c) {
   return go_dual_tc_supported(L, O, ldgo, c.dtype, c.order_o, c.order_l, c.rank_l, c.sel_l, c.q_gx, c.q_gw);
 }
 
+// counters: two scratch words behind the abs-max words, for the tensor-core pair's tile hand-out
 // wj: the weight that rides along; only with the tensor-core pair (see weight_rides)
 int go_dual_any(const void* go, int64_t L, int64_t O, int64_t ldgo, const hot_linear_cfg_t& c, void* q_go, int64_t ld_qgo,
-                float* s_gx, void* q_gw_t, int64_t ld_qgw, float* s_gw, uint32_t* max_x, uint32_t* max_w, uint32_t* status,
-                cudaStream_t st, const TcWeightJob* wj = nullptr) {
+                float* s_gx, void* q_gw_t, int64_t ld_qgw, float* s_gw, uint32_t* max_x, uint32_t* max_w, uint32_t* counters,
+                uint32_t* status, cudaStream_t st, const TcWeightJob* wj = nullptr) {
   if (use_tc(L, O, ldgo, c))
-    return go_dual_quant_tc(go, L, O, ldgo, c.q_gx, c.q_gw, q_go, ld_qgo, s_gx, q_gw_t, ld_qgw, s_gw, max_x, max_w, status, st, wj);
+    return go_dual_quant_tc(go, L, O, ldgo, c.q_gx, c.q_gw, q_go, ld_qgo, s_gx, q_gw_t, ld_qgw, s_gw, max_x, max_w, counters, status, st,
+                            wj);
   if (wj) HOT_FAIL(HOT_ERR_ARG, "go_dual_quant: the weight rides along with the tensor-core kernels only");
   return go_dual_quant(go, c.dtype, L, O, ldgo, c.order_o, c.sel_l, c.q_gx, c.q_gw, q_go, ld_qgo, s_gx, q_gw_t, ld_qgw, s_gw,
                        max_x, max_w, status, st);
@@ -98,8 +100,8 @@ int plan(int64_t L, int64_t O, int64_t I, const hot_linear_cfg_t& c, Workspace& 
   w.off_sw = o;  o += kAlign;
   w.off_qgw = o; o += up((size_t)O * w.ld_qgw, kAlign);
   w.off_sgw = o; o += up((size_t)O * sizeof(float), kAlign);
-  // scratch words: 64 fixed + per-token (L) + per-channel (O) maxima + the weight quantiser's own
-  w.w_scratch_off = (size_t)((64 + L + O + 1) / 2 * 2);
+  // scratch words: 64 fixed + per-token (L) + per-channel (O) maxima + 2 counters + the weight quantiser's own
+  w.w_scratch_off = (size_t)((64 + L + O + 2 + 1) / 2 * 2);
   w.off_scratch = o;
   o += up((w.w_scratch_off + hot_col_ht_quant_scratch_words(c.dtype, O, I, c.order_o, c.order_o, c.q_w.scale_mode) + 64) * sizeof(uint32_t), kAlign);
   // stream-K workspace of the two GEMMs (they run one after the other and share it)
@@ -155,7 +157,7 @@ extern "C" int hot_go_dual_quant(const void* go, int64_t L, int64_t O, int64_t l
   if (ld_qgo < need_x || ld_qgo % 16 || ld_qgw < L / 2 || ld_qgw % 16 || ((uintptr_t)q_go) % 16 || ((uintptr_t)q_gw_t) % 16 ||
       ((uintptr_t)go) % 16)
     HOT_FAIL(HOT_ERR_ARG, "hot_go_dual_quant: buffers and pitches must be 16-byte aligned and cover the codes");
-  return go_dual_any(go, L, O, ldgo, *cfg, q_go, ld_qgo, s_gx, q_gw_t, ld_qgw, s_gw, scratch, scratch + L, status_word,
+  return go_dual_any(go, L, O, ldgo, *cfg, q_go, ld_qgo, s_gx, q_gw_t, ld_qgw, s_gw, scratch, scratch + L, scratch + L + O, status_word,
                      (cudaStream_t)stream);
 }
 
@@ -227,7 +229,7 @@ extern "C" int hot_linear_backward(const void* go, int64_t ldgo, const void* w, 
   };
   if (dual) {
     rc = go_dual_any(go, L, O, ldgo, *cfg, base + ws.off_qgo, ws.ld_qgo, s_go, base + ws.off_qgw, ws.ld_qgw, s_gw, scratch + 64,
-                     scratch + 64 + L, status_word, (cudaStream_t)stream, weight_rides ? &wj : nullptr);
+                     scratch + 64 + L, scratch + 64 + L + O, status_word, (cudaStream_t)stream, weight_rides ? &wj : nullptr);
     if (rc) {
       rejoin();
       return rc;
