@@ -52,6 +52,10 @@ struct GemmParams {
   int stream_k;
   int32_t* sk_partials;    // [2 * gridDim.x][128][BN] int32
   uint32_t* sk_counters;   // [num_tiles] k-blocks delivered so far (zero before launch; left zero)
+  // rider of a dual launch: each of its (few, long) tiles is cut into `split` stretches of k-blocks that go to
+  // different workers; their partial sums meet like those of a stream-K tile (sk_partials: one slot per
+  // worker that holds a stretch, sk_counters: one word per rider tile).  0 or 1: whole tiles.
+  int split;
 };
 
 // One stretch of k-blocks of one output tile.
@@ -72,10 +76,11 @@ struct SegmentIter {
   int group_kb, grp;
   long long u, end;
   // dual launch: a second ("rider") problem of few, long tiles shares the launch.  Worker w < riders
-  // takes rider tile w first; the main problem's tiles are then dealt in rounds, in which the workers
-  // that hold a rider tile only join from round `lag` on (lag = rider k-blocks / main k-blocks,
-  // rounded), so that every worker ends up with about the same number of k-blocks.
-  int riders, lag, rider_kb, round, me, nw;
+  // takes rider piece w first (a whole tile, or one of `split` stretches of its k-blocks); the main problem's
+  // tiles are then dealt in rounds, in which the workers that hold a rider piece only join from round `lag`
+  // on (lag = k-blocks of a piece / main k-blocks, rounded), so that every worker ends up with about the
+  // same number of k-blocks.
+  int riders, lag, rider_kb, rider_piece_kb, rider_split, round, me, nw;
   bool rider_pending;
   // worker / nworkers: this CTA (or CTA pair) among those that share the tiles
   __device__ SegmentIter(const GemmParams& p, int num_tiles_, int worker, int nworkers) {
@@ -93,14 +98,16 @@ struct SegmentIter {
     riders = 0;
     rider_pending = false;
   }
-  __device__ void add_rider(int rider_tiles, int rider_num_kb, int worker, int nworkers) {
-    riders = rider_tiles;
+  __device__ void add_rider(int rider_tiles, int rider_num_kb, int worker, int nworkers, int split) {
+    rider_split = split < 1 ? 1 : split;
+    riders = rider_tiles * rider_split;
     rider_kb = rider_num_kb;
-    lag = (rider_num_kb + num_kb / 2) / num_kb;
+    rider_piece_kb = (rider_num_kb + rider_split - 1) / rider_split;
+    lag = (rider_piece_kb + num_kb / 2) / num_kb;
     round = 0;
     me = worker;
     nw = nworkers;
-    rider_pending = worker < rider_tiles;
+    rider_pending = worker < riders;
   }
   __device__ bool exhausted() const { return stream_k ? u >= end : tile >= num_tiles; }
   __device__ bool next(Segment& s) {
@@ -113,9 +120,10 @@ struct SegmentIter {
       if (rider_pending) {
         rider_pending = false;
         s.prob = 1;
-        s.ltile = me;
-        s.tile = num_tiles + me;
-        s.kb1 = rider_kb;
+        s.ltile = me / rider_split;
+        s.tile = num_tiles + s.ltile;
+        s.kb0 = (me % rider_split) * rider_piece_kb;
+        s.kb1 = s.kb0 + rider_piece_kb < rider_kb ? s.kb0 + rider_piece_kb : rider_kb;
         return true;
       }
       const int free_workers = nw - riders;
@@ -425,7 +433,7 @@ __global__ void __launch_bounds__(kEpiThreads + 64 + ((A4 || B4) ? kUnpackThread
   const int rider_tiles = p2.M > 0 ? ((p2.M + kBM - 1) / kBM) * n_tiles2 : 0;
   auto make_iter = [&]() {
     SegmentIter it(p, num_tiles, worker, nworkers);
-    if (rider_tiles) it.add_rider(rider_tiles, p2.num_kb, worker, nworkers);
+    if (rider_tiles) it.add_rider(rider_tiles, p2.num_kb, worker, nworkers, p2.split);
     return it;
   };
 
@@ -686,7 +694,8 @@ __global__ void __launch_bounds__(kEpiThreads + 64 + ((A4 || B4) ? kUnpackThread
       sa = (row_ok && !raw && !p.group_kb) ? (p.sa_row ? p.sa[row / p.sa_row] : p.sa[0]) : 0.0f;
       const bool whole = seg.kb0 == 0 && seg.kb1 == p.num_kb;
       // partial slot: [chunk of 32 columns][group of 4 columns][row][4] int32, so that a warp's rows are contiguous
-      int32_t* my_slot = p.sk_partials + (size_t)(2 * blockIdx.x + (seg.first ? 0 : 1)) * kBM * BN + row_loc * 4;
+      // (a stretch of a rider tile: the slot of this worker)
+      int32_t* my_slot = p.sk_partials + (size_t)(seg.prob ? worker : 2 * blockIdx.x + (seg.first ? 0 : 1)) * kBM * BN + row_loc * 4;
       ok = mbar_wait(&tmem_full[buf], bph, abort_flag, p.wait_ns);
       if (!ok) break;
       tc_fence_after();
@@ -742,9 +751,10 @@ __global__ void __launch_bounds__(kEpiThreads + 64 + ((A4 || B4) ? kUnpackThread
         asm volatile("bar.sync 1, 256;" ::: "memory");
         if (threadIdx.x == 0) {
           const uint32_t mine = (uint32_t)(seg.kb1 - seg.kb0);
-          const uint32_t before = atomicAdd(p.sk_counters + seg.tile, mine);
+          uint32_t* counter = p.sk_counters + (seg.prob ? seg.ltile : seg.tile);
+          const uint32_t before = atomicAdd(counter, mine);
           s_finisher = (before + mine == (uint32_t)p.num_kb) ? 1u : 0u;
-          if (s_finisher) p.sk_counters[seg.tile] = 0u;  // leave the counters as they were found
+          if (s_finisher) *counter = 0u;  // leave the counters as they were found
         }
         asm volatile("bar.sync 1, 256;" ::: "memory");
         if (s_finisher) {
@@ -752,20 +762,28 @@ __global__ void __launch_bounds__(kEpiThreads + 64 + ((A4 || B4) ? kUnpackThread
           const long long total = (long long)num_tiles * p.num_kb;
           const long long t_beg = (long long)seg.tile * p.num_kb, t_end = t_beg + p.num_kb;
           const long long G = gridDim.x;
-          // contributors: the CTAs whose unit range meets [t_beg, t_end)
-          long long c_lo = t_beg * G / total;
-          while (c_lo + 1 < G && total * (c_lo + 1) / G <= t_beg) ++c_lo;
-          while (c_lo > 0 && total * c_lo / G > t_beg) --c_lo;
+          // contributors: the CTAs whose unit range meets [t_beg, t_end); for a rider tile the workers
+          // that hold its stretches
+          long long c_lo = seg.prob ? (long long)seg.ltile * p.split : t_beg * G / total;
           long long c_hi = c_lo;
-          while (c_hi + 1 < G && total * (c_hi + 1) / G < t_end) ++c_hi;
+          if (seg.prob) {
+            c_hi = c_lo + p.split - 1;
+          } else {
+            while (c_lo + 1 < G && total * (c_lo + 1) / G <= t_beg) ++c_lo;
+            while (c_lo > 0 && total * c_lo / G > t_beg) --c_lo;
+            c_hi = c_lo;
+            while (c_hi + 1 < G && total * (c_hi + 1) / G < t_end) ++c_hi;
+          }
           const int ncontrib = (int)(c_hi - c_lo + 1);
+          const bool rider_seg = seg.prob != 0;
           auto slot_of = [&](long long cta) {
+            if (rider_seg) return p.sk_partials + (size_t)cta * kBM * BN;
             const bool cta_first = total * cta / G >= t_beg;  // its range starts inside this tile
             return p.sk_partials + (size_t)(2 * cta + (cta_first ? 0 : 1)) * kBM * BN;
           };
           // Fast path: this was the CTA's last segment, so the operand ring is idle; bulk copies bring
           // the partials of a group of chunks into it at full bandwidth and the sum reads shared memory.
-          const int group = iter.exhausted() ? L::kOffStore / (ncontrib * 32 * kBM * 4) : 0;
+          const int group = (!rider_seg && iter.exhausted()) ? L::kOffStore / (ncontrib * 32 * kBM * 4) : 0;
           if (group >= 1) {
             uint32_t fph = 0;
             for (int c0 = 0; c0 < BN / 32; c0 += group) {
@@ -1209,7 +1227,8 @@ int fill_problem(const hot_gemm_problem_t* g, bool allow_packed_a, GemmParams* p
   return HOT_OK;
 }
 
-// k-blocks of the busiest worker under the dual schedule of SegmentIter (same rules, on the host)
+// k-blocks of the busiest worker under the dual schedule of SegmentIter (same rules, on the host); t1 rider
+// pieces of kb1 k-blocks each
 int64_t dual_max_load(int64_t t0, int kb0, int64_t t1, int kb1, int workers) {
   const int lag = (kb1 + kb0 / 2) / kb0;
   const int64_t free_w = workers - t1;
@@ -1232,9 +1251,11 @@ int64_t dual_max_load(int64_t t0, int kb0, int64_t t1, int kb1, int workers) {
 }  // namespace
 }  // namespace hot
 
-extern "C" int hot_gemm_i8_dual(const hot_gemm_problem_t* main_problem, const hot_gemm_problem_t* rider_problem,
-                                uint32_t* status_word, hot_stream_t stream) {
-  using namespace hot;
+namespace hot {
+// hot_gemm_i8_dual with scratch: `workspace` (256-byte aligned) for the partial sums of rider tiles that are cut
+// along K, `counters` = 160 zeroed words (left zero).  Without them rider tiles stay whole.
+int gemm_i8_dual_ws(const hot_gemm_problem_t* main_problem, const hot_gemm_problem_t* rider_problem, void* workspace,
+                    size_t workspace_bytes, uint32_t* counters, uint32_t* status_word, hot_stream_t stream) {
   GemmParams p0, p1;
   if (int rc = fill_problem(main_problem, true, &p0, "main problem")) return rc;
   if (int rc = fill_problem(rider_problem, false, &p1, "rider problem")) return rc;
@@ -1246,24 +1267,46 @@ extern "C" int hot_gemm_i8_dual(const hot_gemm_problem_t* main_problem, const ho
   const bool a4 = main_problem->a_storage == HOT_STORE_INT4;
   // One launch pays when the rider's few long tiles fit beside the main problem's last, partly empty
   // wave; otherwise (or with HOT_GEMM_DUAL=0) the two problems run one after the other.  The tile
-  // width is the one whose busiest worker, replayed on the host, has the least to do.
+  // width, and into how many stretches of k-blocks a rider tile is cut, are those whose busiest worker,
+  // replayed on the host, has the least to do.
   const Plan s0 = make_plan(p0.M, p0.N, p0.num_kb, sms, 0, !a4, a4), s1 = make_plan(p1.M, p1.N, p1.num_kb, sms, 0, true, false);
   const char* env = getenv("HOT_GEMM_DUAL");
-  int dual_bn = 0;
+  const char* senv = getenv("HOT_GEMM_RIDER_SPLIT");  // 1: rider tiles stay whole; n: cut into n where possible
+  const int force_split = senv ? atoi(senv) : 0;
+  int dual_bn = 0, dual_split = 1;
   double together = 0.0;
   for (int bn : {256, 192}) {
     const int64_t t0 = tiles_for(p0.M, p0.N, bn), t1 = tiles_for(p1.M, p1.N, bn);
     if (t1 > sms || t0 < sms || t1 < 1) continue;
-    const double c = (double)dual_max_load(t0, p0.num_kb, t1, p1.num_kb, sms) * (bn + 400.0);
-    if (!dual_bn || c < together) {
-      dual_bn = bn;
-      together = c;
+    for (int split = 1; split <= 4; ++split) {
+      if (force_split > 0 && split != force_split) continue;
+      const int piece = (p1.num_kb + split - 1) / split;
+      if (split > 1) {
+        // every stretch non-empty, a slot per worker with a stretch, a counter per rider tile
+        if (!workspace || !counters || t1 * split > sms || (int64_t)(split - 1) * piece >= p1.num_kb || t1 > 160 ||
+            (size_t)(t1 * split) * kBM * bn * sizeof(int32_t) > workspace_bytes || ((uintptr_t)workspace) % 16 != 0)
+          continue;
+      }
+      // Whoever completes a cut tile reads every stretch's sums back from L2, chunk by chunk, and adds them; with the
+      // parking of the sums before it that is about 7 us on the busiest worker (measured on B200 at ViT-B sizes:
+      // 768 x 768 x 6304 beside 12608 x 768 x 768 gains 2 us from a cut in two, larger riders lose), some 10000
+      // units of this model.
+      const double fix = split > 1 ? 8000.0 + 1000.0 * split : 0.0;
+      const double c = (double)dual_max_load(t0, p0.num_kb, t1 * split, piece, sms) * (bn + 400.0) + fix;
+      if (!dual_bn || c < together) {
+        dual_bn = bn;
+        dual_split = split;
+        together = c;
+      }
     }
   }
   bool dual = dual_bn != 0 && !(env && env[0] == '0');
   // a second launch costs about 3 us of ramp-down and ramp-up, some 4000 units of this model
   if (dual && !(env && env[0] == '1')) dual = together < s0.cost + s1.cost + 4000.0;
   if (dual) {
+    p1.split = dual_split;
+    p1.sk_partials = (int32_t*)workspace;
+    p1.sk_counters = counters;
     Rider r{rider_problem->a, rider_problem->lda, rider_problem->b, rider_problem->ldb, p1};
     const Plan plan{dual_bn, false, (unsigned)sms};
     const void* a = main_problem->a;
@@ -1280,4 +1323,10 @@ extern "C" int hot_gemm_i8_dual(const hot_gemm_problem_t* main_problem, const ho
               : launch_bn<false, false>(main_problem->a, main_problem->lda, main_problem->b, main_problem->ldb, p0, s0, st);
   if (rc) return rc;
   return launch_bn<false, false>(rider_problem->a, rider_problem->lda, rider_problem->b, rider_problem->ldb, p1, s1, st);
+}
+}  // namespace hot
+
+extern "C" int hot_gemm_i8_dual(const hot_gemm_problem_t* main_problem, const hot_gemm_problem_t* rider_problem,
+                                uint32_t* status_word, hot_stream_t stream) {
+  return hot::gemm_i8_dual_ws(main_problem, rider_problem, nullptr, 0, nullptr, status_word, stream);
 }

@@ -617,9 +617,10 @@ bool tc_weight_job_supported(int64_t O, int64_t I, int64_t ldw, const hot_quant_
 
 int go_dual_quant_tc(const void* go, int64_t L, int64_t O, int64_t ldgo, const hot_quant_t& q_gx, const hot_quant_t& q_gw,
                      void* q_go, int64_t ld_qgo, float* s_gx, void* q_gw_t, int64_t ld_qgw, float* s_gw, uint32_t* max_x,
-                     uint32_t* max_w, uint32_t* counters, uint32_t* status, cudaStream_t st, const TcWeightJob* wj) {
+                     uint32_t* max_w, uint32_t* counters, size_t counter_words, uint32_t* status, cudaStream_t st,
+                     const TcWeightJob* wj) {
   TcParams p;
-  p.counters = counters;  // two words: tiles drawn by each pass
+  p.counters = counters;  // two words: tiles drawn by each pass (the caller may have more words behind them cleared along)
   p.wt = nullptr;
   if (wj) {
     if (!tc_weight_job_supported(O, wj->I, wj->ldw, wj->q) || wj->ld_qw % 16 != 0 || wj->ld_qw < O || ((uintptr_t)wj->q_w) % 16 != 0 ||
@@ -661,7 +662,7 @@ int go_dual_quant_tc(const void* go, int64_t L, int64_t O, int64_t ldgo, const h
   struct Span {
     uint32_t* p;
     size_t n;
-  } spans[4] = {{max_x, nx}, {max_w, nw}, {counters, 2}, {wj ? wj->max_w : max_x, wj ? (size_t)1 : (size_t)0}};
+  } spans[4] = {{max_x, nx}, {max_w, nw}, {counters, counter_words < 2 ? (size_t)2 : counter_words}, {wj ? wj->max_w : max_x, wj ? (size_t)1 : (size_t)0}};
   uint32_t *lo = max_x, *hi = max_x;
   for (const Span& sp : spans) {
     if (sp.n == 0) continue;

@@ -19,7 +19,10 @@ bool go_dual_tc_supported(int64_t L, int64_t O, int64_t ldgo, int dtype, int ord
 bool tc_weight_job_supported(int64_t O, int64_t I, int64_t ldw, const hot_quant_t& q_w);
 int go_dual_quant_tc(const void* go, int64_t L, int64_t O, int64_t ldgo, const hot_quant_t& q_gx, const hot_quant_t& q_gw,
                      void* q_go, int64_t ld_qgo, float* s_gx, void* q_gw_t, int64_t ld_qgw, float* s_gw, uint32_t* max_x,
-                     uint32_t* max_w, uint32_t* counters, uint32_t* status, cudaStream_t st, const TcWeightJob* wj);
+                     uint32_t* max_w, uint32_t* counters, size_t counter_words, uint32_t* status, cudaStream_t st,
+                     const TcWeightJob* wj);
+int gemm_i8_dual_ws(const hot_gemm_problem_t* main_problem, const hot_gemm_problem_t* rider_problem, void* workspace,
+                    size_t workspace_bytes, uint32_t* counters, uint32_t* status_word, hot_stream_t stream);
 
 namespace {
 
@@ -32,14 +35,15 @@ bool use_tc(int64_t L, int64_t O, int64_t ldgo, const hot_linear_cfg_t& c) {
   return go_dual_tc_supported(L, O, ldgo, c.dtype, c.order_o, c.order_l, c.rank_l, c.sel_l, c.q_gx, c.q_gw);
 }
 
-// counters: two scratch words behind the abs-max words, for the tensor-core pair's tile hand-out
+// counters: scratch words behind the abs-max words: two for the tensor-core pair's tile hand-out, and whatever else
+// of the caller's lies behind them and is to be cleared along (counter_words in all; tensor-core pair only)
 // wj: the weight that rides along; only with the tensor-core pair (see weight_rides)
 int go_dual_any(const void* go, int64_t L, int64_t O, int64_t ldgo, const hot_linear_cfg_t& c, void* q_go, int64_t ld_qgo,
                 float* s_gx, void* q_gw_t, int64_t ld_qgw, float* s_gw, uint32_t* max_x, uint32_t* max_w, uint32_t* counters,
-                uint32_t* status, cudaStream_t st, const TcWeightJob* wj = nullptr) {
+                size_t counter_words, uint32_t* status, cudaStream_t st, const TcWeightJob* wj = nullptr) {
   if (use_tc(L, O, ldgo, c))
-    return go_dual_quant_tc(go, L, O, ldgo, c.q_gx, c.q_gw, q_go, ld_qgo, s_gx, q_gw_t, ld_qgw, s_gw, max_x, max_w, counters, status, st,
-                            wj);
+    return go_dual_quant_tc(go, L, O, ldgo, c.q_gx, c.q_gw, q_go, ld_qgo, s_gx, q_gw_t, ld_qgw, s_gw, max_x, max_w, counters,
+                            counter_words, status, st, wj);
   if (wj) HOT_FAIL(HOT_ERR_ARG, "go_dual_quant: the weight rides along with the tensor-core kernels only");
   return go_dual_quant(go, c.dtype, L, O, ldgo, c.order_o, c.sel_l, c.q_gx, c.q_gw, q_go, ld_qgo, s_gx, q_gw_t, ld_qgw, s_gw,
                        max_x, max_w, status, st);
@@ -76,6 +80,7 @@ int side_stream(SideStream** out) {
 }
 
 constexpr size_t kAlign = 256;
+constexpr int kRiderCounters = 160;  // one word per g_w tile that the dual GEMM may cut along K
 inline size_t up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
 inline int64_t code_pitch(int64_t len, int storage) { return (int64_t)up((size_t)(storage == HOT_STORE_INT4 ? (len + 1) / 2 : len), 16); }
@@ -100,8 +105,9 @@ int plan(int64_t L, int64_t O, int64_t I, const hot_linear_cfg_t& c, Workspace& 
   w.off_sw = o;  o += kAlign;
   w.off_qgw = o; o += up((size_t)O * w.ld_qgw, kAlign);
   w.off_sgw = o; o += up((size_t)O * sizeof(float), kAlign);
-  // scratch words: 64 fixed + per-token (L) + per-channel (O) maxima + 2 counters + the weight quantiser's own
-  w.w_scratch_off = (size_t)((64 + L + O + 2 + 1) / 2 * 2);
+  // scratch words: 64 fixed + per-token (L) + per-channel (O) maxima + 2 tile counters + kRiderCounters of the
+  // GEMM + the weight quantiser's own
+  w.w_scratch_off = (size_t)((64 + L + O + 2 + kRiderCounters + 1) / 2 * 2);
   w.off_scratch = o;
   o += up((w.w_scratch_off + hot_col_ht_quant_scratch_words(c.dtype, O, I, c.order_o, c.order_o, c.q_w.scale_mode) + 64) * sizeof(uint32_t), kAlign);
   // stream-K workspace of the two GEMMs (they run one after the other and share it)
@@ -157,7 +163,7 @@ extern "C" int hot_go_dual_quant(const void* go, int64_t L, int64_t O, int64_t l
   if (ld_qgo < need_x || ld_qgo % 16 || ld_qgw < L / 2 || ld_qgw % 16 || ((uintptr_t)q_go) % 16 || ((uintptr_t)q_gw_t) % 16 ||
       ((uintptr_t)go) % 16)
     HOT_FAIL(HOT_ERR_ARG, "hot_go_dual_quant: buffers and pitches must be 16-byte aligned and cover the codes");
-  return go_dual_any(go, L, O, ldgo, *cfg, q_go, ld_qgo, s_gx, q_gw_t, ld_qgw, s_gw, scratch, scratch + L, scratch + L + O, status_word,
+  return go_dual_any(go, L, O, ldgo, *cfg, q_go, ld_qgo, s_gx, q_gw_t, ld_qgw, s_gw, scratch, scratch + L, scratch + L + O, 2, status_word,
                      (cudaStream_t)stream);
 }
 
@@ -229,7 +235,8 @@ extern "C" int hot_linear_backward(const void* go, int64_t ldgo, const void* w, 
   };
   if (dual) {
     rc = go_dual_any(go, L, O, ldgo, *cfg, base + ws.off_qgo, ws.ld_qgo, s_go, base + ws.off_qgw, ws.ld_qgw, s_gw, scratch + 64,
-                     scratch + 64 + L, scratch + 64 + L + O, status_word, (cudaStream_t)stream, weight_rides ? &wj : nullptr);
+                     scratch + 64 + L, scratch + 64 + L + O, 2 + kRiderCounters, status_word, (cudaStream_t)stream,
+                     weight_rides ? &wj : nullptr);
     if (rc) {
       rejoin();
       return rc;
@@ -260,7 +267,10 @@ extern "C" int hot_linear_backward(const void* go, int64_t ldgo, const void* w, 
                              s_w, 0, post_x, grad_x, cfg->dtype, ldgx};
     hot_gemm_problem_t gw = {base + ws.off_qgw, HOT_STORE_INT8, ws.ld_qgw, x_q_t, hot_abc_pitch(L, cfg), O, I, ws.lp, s_gw, gw_row,
                              scale_x, 0, post_w, grad_w, cfg->dtype, ldgw};
-    return hot_gemm_i8_dual(&gx, &gw, status_word, stream);
+    // the GEMM's counters lie behind the tile counters of the tensor-core grad_out kernels, which clear them along
+    uint32_t* rider_counters = scratch + 64 + L + O + 2;
+    if (!(dual && use_tc(L, O, ldgo, *cfg))) HOT_CUDA(cudaMemsetAsync(rider_counters, 0, kRiderCounters * sizeof(uint32_t), main_st));
+    return gemm_i8_dual_ws(&gx, &gw, ws.gemm_bytes ? base + ws.off_gemm : nullptr, ws.gemm_bytes, rider_counters, status_word, stream);
   }
   if (grad_x) {
     rc = hot_gemm_i8_ws(base + ws.off_qgo, cfg->q_gx.storage, ws.ld_qgo, base + ws.off_qw, HOT_STORE_INT8, ws.ld_qw, L, I, O,

@@ -545,6 +545,34 @@ def test_weight_quantised_by_the_grad_out_kernels_matches_its_own_kernels(ops, m
     assert torch.equal(out["rides"][1], out["separate"][1])
 
 
+@pytest.mark.parametrize("L,O,I", [(128 * 50, 256, 768), (12608, 768, 768)])
+def test_dual_gemm_with_g_w_tiles_cut_along_the_tokens(ops, monkeypatch, L, O, I):
+    """The layer's GEMM launch may cut the few, long tiles of the g_w product into stretches of k-blocks that run on
+    different SMs and are summed by whichever finishes last.  Integer sums: the gradients must be bit-identical to
+    those of whole tiles, whatever the cut."""
+    rng = np.random.default_rng(L + O)
+    x = torch.from_numpy(rng.standard_normal((L, I)).astype(np.float32)).cuda().bfloat16()
+    w = torch.from_numpy(((rng.random((O, I)) * 2 - 1) / np.sqrt(I)).astype(np.float32)).cuda().bfloat16()
+    go = torch.from_numpy((rng.standard_normal((L, O)) * 1e-3).astype(np.float32)).cuda().bfloat16()
+    sel = [int(v) for v in oc.lowrank_preset(16, 8)]
+    cfg = ops.LinearConfig(order_o=16, order_l=16, sel_l=sel, q_gx=ops.Quant(4, "int8", "philox", "tensor", 3, 1))
+    x_q_t, s_x = ops.abc_compress(x, cfg)
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    monkeypatch.setenv("HOT_GEMM_DUAL", "1")
+    out = {}
+    for split in ("1", "2", "3", "4"):
+        monkeypatch.setenv("HOT_GEMM_RIDER_SPLIT", split)
+        for rep in range(2):   # twice: the counters must come back to zero
+            gx, gw = ops.linear_backward(go, w, x_q_t, s_x, cfg, status=status)
+        torch.cuda.synchronize()
+        out[split] = (gx.clone(), gw.clone())
+    assert int(status.item()) == 0
+    assert float(out["1"][1].float().abs().max()) > 0
+    for split in ("2", "3", "4"):
+        assert torch.equal(out[split][0], out["1"][0]), split
+        assert torch.equal(out[split][1], out["1"][1]), split
+
+
 def test_go_dual_quant_rejects_what_it_does_not_cover(ops):
     go = torch.zeros((64, 64), device="cuda")
     cfg = ops.LinearConfig(order_o=16, order_l=32, sel_l=list(oc.wht_selection(6304, 50)[1]))
