@@ -592,30 +592,29 @@ def run_vit_train(a):
         dist.destroy_process_group()
 
 
-def _graph_time(fn, iters, device, warm=3):
-    """Average device time of fn() in microseconds: captured once per distinct call, replayed."""
+def _graph_time(fn, iters, device, warm=3, replays=3):
+    """Average device time of fn(i) in microseconds: the calls fn(0) .. fn(iters - 1) captured back to back in one
+    CUDA graph (so that what is timed is the kernels as they follow one another in a step, not a graph launch per
+    call), replayed `replays` times after `warm` warm-up replays."""
     side = torch.cuda.Stream(device)
+    keep = []
     with torch.cuda.stream(side):
         fn(0)
         torch.cuda.synchronize(device)
-        gs = []
-        for i in range(iters):
-            g = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(g, stream=side):
-                fn(i)
-            gs.append(g)
-    torch.cuda.synchronize(device)
-    for _ in range(warm):
-        for g in gs:
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=side):
+            for i in range(iters):
+                keep.append(fn(i))
+        for _ in range(warm):
             g.replay()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    torch.cuda.synchronize(device)
-    e0.record()
-    for g in gs:
-        g.replay()
-    e1.record()
-    torch.cuda.synchronize(device)
-    return e0.elapsed_time(e1) * 1e3 / iters
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize(device)
+        e0.record(side)
+        for _ in range(replays):
+            g.replay()
+        e1.record(side)
+        torch.cuda.synchronize(device)
+    return e0.elapsed_time(e1) * 1e3 / (iters * replays)
 
 
 def kernel_legs(ops, layers, a, dtype, device, pk, status):
@@ -674,7 +673,9 @@ def kernel_legs(ops, layers, a, dtype, device, pk, status):
         else:
             v["achieved"], v["unit"], v["peak"] = round(v["ops"] / v["us"] / 1e6, 1), "TOP/s", int8_peak
         v["frac"] = round(v["achieved"] / v["peak"], 4)
-    in_layer = ["go_dual_quant", "col_ht_quant_w", "gemm_gx_gw_one_launch"]
+    # what a layer backward launches (in fp32 the weight has kernels of its own; in bf16 it is quantised inside the
+    # two grad_out launches)
+    in_layer = ["go_dual_quant", "gemm_gx_gw_one_launch"] + ([] if dtype == torch.bfloat16 else ["col_ht_quant_w"])
     top = max(in_layer, key=lambda k: kern[k]["us"])
     tk = kern[top]
     # DRAM traffic per launch pair, from an ncu capture of this very workload (fc1 gradient, 12,608 x 3,072 bf16,
@@ -689,8 +690,21 @@ def kernel_legs(ops, layers, a, dtype, device, pk, status):
                            "INT8 ceiling measured in this run at 8192^3 (max of torch._int_mm and hot_gemm_i8)",
             "share_of_fc1_layer": round(tk["us"] / t_layer, 3)}
     kern["int8_ceiling_8192"] = int8
+    # the other three linears of a block, and the block as a whole, against the same two cuBLAS products
+    shapes = {"fc1": {"hot_us": round(t_layer, 2), "matmul_us": round(t_fp, 2)}}
+    for li, name in ((0, "qkv"), (1, "proj"), (3, "fc2")):
+        ls = [blk[li] for blk in layers]
+        xs_l = [torch.randn((L, ls[0]["I"]), device=device).to(dtype) for _ in range(2)]
+        th = _graph_time(lambda i: ops.linear_backward(ls[i % n]["go"], ls[i % n]["w"], ls[i % n]["x_q_t"], ls[i % n]["s_x"], ls[i % n]["cfg"], status=status), n, device)
+        tf = _graph_time(lambda i: (torch.matmul(ls[i % n]["go"], ls[i % n]["w"]), torch.matmul(ls[i % n]["go"].t(), xs_l[i % 2])), n, device)
+        shapes[name] = {"hot_us": round(th, 2), "matmul_us": round(tf, 2)}
+        del xs_l
+    blk_hot = sum(v["hot_us"] for v in shapes.values())
+    blk_fp = sum(v["matmul_us"] for v in shapes.values())
     fp = {"fc1_hot_us": round(t_layer, 2), "fc1_bf16_matmul_us": round(t_fp, 2), "speedup": round(t_fp / t_layer, 3),
-          "dtype": a.dtype, "config1_fp32": config1_leg(ops, device, status)}
+          "dtype": a.dtype, "per_linear": shapes,
+          "block_hot_us": round(blk_hot, 1), "block_matmul_us": round(blk_fp, 1), "block_speedup": round(blk_fp / blk_hot, 3),
+          "config1_fp32": config1_leg(ops, device, status)}
     return kern, roof, fp
 
 
