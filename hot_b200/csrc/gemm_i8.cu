@@ -1279,7 +1279,7 @@ int gemm_i8_dual_ws(const hot_gemm_problem_t* main_problem, const hot_gemm_probl
     const int64_t t0 = tiles_for(p0.M, p0.N, bn), t1 = tiles_for(p1.M, p1.N, bn);
     if (t1 > sms || t0 < sms || t1 < 1) continue;
     for (int split = 1; split <= 4; ++split) {
-      if (force_split > 0 && split != force_split) continue;
+      if (force_split > 0 ? split != force_split : split > 2) continue;  // more than two stretches only when asked (tests)
       const int piece = (p1.num_kb + split - 1) / split;
       if (split > 1) {
         // every stretch non-empty, a slot per worker with a stretch, a counter per rider tile
@@ -1288,10 +1288,10 @@ int gemm_i8_dual_ws(const hot_gemm_problem_t* main_problem, const hot_gemm_probl
           continue;
       }
       // Whoever completes a cut tile reads every stretch's sums back from L2, chunk by chunk, and adds them; with the
-      // parking of the sums before it that is about 7 us on the busiest worker (measured on B200 at ViT-B sizes:
-      // 768 x 768 x 6304 beside 12608 x 768 x 768 gains 2 us from a cut in two, larger riders lose), some 10000
-      // units of this model.
-      const double fix = split > 1 ? 8000.0 + 1000.0 * split : 0.0;
+      // parking of the sums before it that costs the busiest worker about 10 us for two stretches and more for
+      // three or four (measured on B200 at ViT-B sizes: 768 x 768 x 6304 beside 12608 x 768 x 768 gains 2 us from
+      // a cut in two and loses with three or four; larger riders lose with two), some 14000 units of this model.
+      const double fix = split > 1 ? 14000.0 + 4000.0 * (split - 2) : 0.0;
       const double c = (double)dual_max_load(t0, p0.num_kb, t1 * split, piece, sms) * (bn + 400.0) + fix;
       if (!dual_bn || c < together) {
         dual_bn = bn;
