@@ -86,6 +86,9 @@ struct TcParams {
   uint32_t* status;
   uint32_t* counters;      // [2], zero before pass 0: tiles drawn in pass 0 / in pass 1
   uint64_t wait_ns;        // time limit of a device-side wait
+  // the token side alone (the activation buffer of the forward pass: x -> INT8 codes of its low-rank projection,
+  // transposed): no channel transform is issued and the g_x-side warps only keep the barriers' counts
+  int col_only;
   // the weight that rides along (wt == nullptr: none): [O, wt_cols] bf16 -> codes [wt_cols, O], one per byte
   const uint16_t* wt;
   int64_t ld_wt, ld_qwt;
@@ -338,10 +341,12 @@ __global__ void __launch_bounds__(kThreadsTc, 1)
         const uint32_t d_row = tmem_base + buf * kBufCols, d_col = d_row + 128;
         // channel transform: tokens are the rows of a K-major operand (128 bytes per token, 8-token groups 1024
         // bytes apart); 16 channels = 32 bytes of K per MMA
+        if (!p.col_only) {
 #pragma unroll
-        for (int g = 0; g < 8; ++g) {
-          const uint64_t a = smem_desc(stage + (g >> 2) * kBoxBytes + (g & 3) * 32, 16, 1024, 2);
-          umma_bf16(d_row + 16 * g, a, b_h, idesc_row, 0u);
+          for (int g = 0; g < 8; ++g) {
+            const uint64_t a = smem_desc(stage + (g >> 2) * kBoxBytes + (g & 3) * 32, 16, 1024, 2);
+            umma_bf16(d_row + 16 * g, a, b_h, idesc_row, 0u);
+          }
         }
         // token projection: channels are the rows of an MN-major operand (64 channels contiguous, the next 64 in the
         // second box = leading offset; 8-token groups 1024 bytes apart = stride offset); a pair of 16-token blocks per
@@ -353,8 +358,13 @@ __global__ void __launch_bounds__(kThreadsTc, 1)
           umma_bf16(d_col + 16 * j, a0, b_p0, idesc_col, 0u);
           umma_bf16(d_col + 16 * j, a1, b_p1, idesc_col, 1u);
         }
-        umma_commit(&empty[s]);
-        umma_commit(&tmem_full[buf]);
+        if (PASS == 0 && p.col_only) {  // nothing was issued: the two barriers take plain arrivals
+          mbar_arrive(&empty[s]);
+          mbar_arrive(&tmem_full[buf]);
+        } else {
+          umma_commit(&empty[s]);
+          umma_commit(&tmem_full[buf]);
+        }
       }
     }
   } else {
@@ -377,10 +387,10 @@ __global__ void __launch_bounds__(kThreadsTc, 1)
     if (PASS == 1) {
       // launched as a programmatic dependent of pass 0: its abs-maxima are visible once this returns
       asm volatile("griddepcontrol.wait;" ::: "memory");
-      if (!x_row) sp_x = scale_from_absmax(__uint_as_float(p.max_x[0]), p.qx.qmax);
+      if (!x_row && !p.col_only) sp_x = scale_from_absmax(__uint_as_float(p.max_x[0]), p.qx.qmax);
       if (!w_row) sp_w = scale_from_absmax(__uint_as_float(p.max_w[0]), p.qw.qmax);
       if (blockIdx.x == 0 && warp == 2 && lane == 0) {
-        if (!x_row) p.s_x[0] = sp_x.s;
+        if (!x_row && !p.col_only) p.s_x[0] = sp_x.s;
         if (!w_row) p.s_w[0] = sp_w.s;
       }
     }
@@ -420,6 +430,10 @@ __global__ void __launch_bounds__(kThreadsTc, 1)
       asm volatile("bar.sync %0, 128;" ::"r"(1 + grp) : "memory");
       const int tt = sched_tile[it % kSched].x, tc = sched_tile[it % kSched].y;
       if (tt < 0 || *abort_flag) break;  // no more tiles, or a wait ran out somewhere (every warp of the group sees it after the barrier)
+      if (p.col_only && !col_side) {
+        if (lane == 0) mbar_arrive(&tmem_empty[buf]);  // nothing of this tile is this warp's: keep the count
+        continue;
+      }
       if (PASS == 0 && col_side) {
         // Pass 0, g_w side: the abs-max of the token projection comes from the CUDA cores, straight from the tile in
         // shared memory (the butterfly of the separate kernels), so that the tensor core has the eight MMAs of the
@@ -536,7 +550,7 @@ __global__ void __launch_bounds__(kThreadsTc, 1)
     if (PASS == 0) {
       tmax = warp_max(tmax);
       if (lane == 0) {
-        if (!col_side && !x_row) atomic_absmax(p.max_x, tmax);
+        if (!col_side && !x_row && !p.col_only) atomic_absmax(p.max_x, tmax);
         if (col_side && !w_row) atomic_absmax(p.max_w, tmax);
       }
     } else if (lane == 0) {
@@ -609,6 +623,17 @@ bool go_dual_tc_supported(int64_t L, int64_t O, int64_t ldgo, int dtype, int ord
          q_gw.storage == HOT_STORE_INT8 && q_gx.rounding != HOT_ROUND_STOCH_NOISE && q_gw.rounding != HOT_ROUND_STOCH_NOISE;
 }
 
+// Whether the tensor-core kernels can make the activation buffer: x [L, I] -> INT8 codes of its projection on the 8
+// lowest-sequency rows of H_16 along the tokens, transposed, one scale.
+bool abc_tc_supported(int64_t L, int64_t I, int64_t ldx, int dtype, int order_l, int rank_l, const int32_t* sel_l,
+                      const hot_quant_t& q_x) {
+  if (dtype != HOT_BF16 || order_l != 16 || rank_l != 8) return false;
+  for (int j = 0; j < 8; ++j)
+    if (sel_l[j] != kSlotRowHost[j]) return false;
+  return L % 32 == 0 && L < (1ll << 31) && I % kCh == 0 && I <= (1 << 24) && (ldx * 2) % 16 == 0 && q_x.storage == HOT_STORE_INT8 &&
+         q_x.scale_mode == HOT_SCALE_TENSOR && (q_x.rounding == HOT_ROUND_STOCH_PHILOX || q_x.rounding == HOT_ROUND_NEAREST);
+}
+
 // Whether the layer's weight [O, I] (same dtype and transform order as grad_out) can ride along.
 bool tc_weight_job_supported(int64_t O, int64_t I, int64_t ldw, const hot_quant_t& q_w) {
   return I > 0 && I % 32 == 0 && I <= (1 << 24) && O % 32 == 0 && ldw >= I && q_w.scale_mode == HOT_SCALE_TENSOR &&
@@ -618,8 +643,15 @@ bool tc_weight_job_supported(int64_t O, int64_t I, int64_t ldw, const hot_quant_
 int go_dual_quant_tc(const void* go, int64_t L, int64_t O, int64_t ldgo, const hot_quant_t& q_gx, const hot_quant_t& q_gw,
                      void* q_go, int64_t ld_qgo, float* s_gx, void* q_gw_t, int64_t ld_qgw, float* s_gw, uint32_t* max_x,
                      uint32_t* max_w, uint32_t* counters, size_t counter_words, uint32_t* status, cudaStream_t st,
-                     const TcWeightJob* wj) {
+                     const TcWeightJob* wj, bool col_only) {
+  // col_only: the g_w side alone (q_go, s_gx, max_x unused and may be null; q_gx ignored apart from its validity)
   TcParams p;
+  p.col_only = col_only ? 1 : 0;
+  if (col_only) {
+    q_go = q_gw_t;  // a valid address for the tensor map that is never stored through
+    ld_qgo = ld_qgw;
+    max_x = max_w;
+  }
   p.counters = counters;  // two words: tiles drawn by each pass (the caller may have more words behind them cleared along)
   p.wt = nullptr;
   if (wj) {
@@ -638,7 +670,7 @@ int go_dual_quant_tc(const void* go, int64_t L, int64_t O, int64_t ldgo, const h
   }
   p.L = L;
   p.O = (int)O;
-  p.x_row = q_gx.scale_mode == HOT_SCALE_ROW;
+  p.x_row = !col_only && q_gx.scale_mode == HOT_SCALE_ROW;
   p.w_row = q_gw.scale_mode == HOT_SCALE_ROW;
   p.qx = make_quant_dev(q_gx);
   p.qw = make_quant_dev(q_gw);
@@ -648,22 +680,26 @@ int go_dual_quant_tc(const void* go, int64_t L, int64_t O, int64_t ldgo, const h
   p.max_w = max_w;
   p.status = status;
   p.wait_ns = wait_limit_ns();
-  const bool x4 = q_gx.storage == HOT_STORE_INT4;
+  const bool x4 = !col_only && q_gx.storage == HOT_STORE_INT4;
   CUtensorMap m_in, m_qgo, m_qgw;
   if (int rc = make_map(&m_in, go, L, O * 2, ldgo * 2, 128, kTok, 128)) return rc;
-  if (int rc = make_map(&m_qgo, q_go, L, x4 ? O / 2 : O, ld_qgo, x4 ? 16 : 32, 32, 0)) return rc;
+  if (col_only) {
+    if (int rc = make_map(&m_qgo, q_go, O, L / 2, ld_qgo, 32, 32, 0)) return rc;
+  } else if (int rc = make_map(&m_qgo, q_go, L, x4 ? O / 2 : O, ld_qgo, x4 ? 16 : 32, 32, 0)) {
+    return rc;
+  }
   if (int rc = make_map(&m_qgw, q_gw_t, O, L / 2, ld_qgw, 32, 32, 0)) return rc;
   const int sms = device_sm_count();
   if (sms <= 0) return HOT_ERR_CUDA;
   const int num_tiles = (int)(O / kCh) * (int)((L + kTok - 1) / kTok);
   const int grid = sms < num_tiles ? sms : num_tiles;
-  const size_t nx = p.x_row ? (size_t)L : 1, nw = p.w_row ? (size_t)O : 1;
+  const size_t nx = col_only ? 0 : (p.x_row ? (size_t)L : 1), nw = p.w_row ? (size_t)O : 1;
   // one clear where the scratch words lie close together (they do in every caller of this library), else one each
   struct Span {
     uint32_t* p;
     size_t n;
   } spans[4] = {{max_x, nx}, {max_w, nw}, {counters, counter_words < 2 ? (size_t)2 : counter_words}, {wj ? wj->max_w : max_x, wj ? (size_t)1 : (size_t)0}};
-  uint32_t *lo = max_x, *hi = max_x;
+  uint32_t *lo = max_w, *hi = max_w;
   for (const Span& sp : spans) {
     if (sp.n == 0) continue;
     if (sp.p < lo) lo = sp.p;
@@ -678,7 +714,7 @@ int go_dual_quant_tc(const void* go, int64_t L, int64_t O, int64_t ldgo, const h
       if (sp.n) HOT_CUDA(cudaMemsetAsync(sp.p, 0, sizeof(uint32_t) * sp.n, st));
   }
   if (int rc = launch_tc_pass<0, HOT_ROUND_NEAREST, HOT_ROUND_NEAREST, true>(m_in, m_qgo, m_qgw, p, grid, st)) return rc;
-  const bool px = q_gx.rounding == HOT_ROUND_STOCH_PHILOX, pw = q_gw.rounding == HOT_ROUND_STOCH_PHILOX;
+  const bool px = !col_only && q_gx.rounding == HOT_ROUND_STOCH_PHILOX, pw = q_gw.rounding == HOT_ROUND_STOCH_PHILOX;
   constexpr int N = HOT_ROUND_NEAREST, P = HOT_ROUND_STOCH_PHILOX;
   if (x4) {
     if (px && pw) return launch_tc_pass<1, P, P, true>(m_in, m_qgo, m_qgw, p, grid, st);

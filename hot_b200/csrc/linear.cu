@@ -20,7 +20,9 @@ bool tc_weight_job_supported(int64_t O, int64_t I, int64_t ldw, const hot_quant_
 int go_dual_quant_tc(const void* go, int64_t L, int64_t O, int64_t ldgo, const hot_quant_t& q_gx, const hot_quant_t& q_gw,
                      void* q_go, int64_t ld_qgo, float* s_gx, void* q_gw_t, int64_t ld_qgw, float* s_gw, uint32_t* max_x,
                      uint32_t* max_w, uint32_t* counters, size_t counter_words, uint32_t* status, cudaStream_t st,
-                     const TcWeightJob* wj);
+                     const TcWeightJob* wj, bool col_only = false);
+bool abc_tc_supported(int64_t L, int64_t I, int64_t ldx, int dtype, int order_l, int rank_l, const int32_t* sel_l,
+                      const hot_quant_t& q_x);
 int gemm_i8_dual_ws(const hot_gemm_problem_t* main_problem, const hot_gemm_problem_t* rider_problem, void* workspace,
                     size_t workspace_bytes, uint32_t* counters, uint32_t* status_word, hot_stream_t stream);
 
@@ -143,6 +145,19 @@ extern "C" int hot_abc_compress(const void* x, int64_t L, int64_t I, int64_t ldx
     HOT_FAIL(HOT_ERR_WORKSPACE, "hot_abc_compress: workspace needs %zu bytes, 8-byte aligned (got %zu)", need, workspace_bytes);
   const int64_t pitch = hot_abc_pitch(L, cfg);
   if (pitch == 0) HOT_FAIL(HOT_ERR_ARG, "hot_abc_compress: tokens %lld not a multiple of the low-rank order %d", (long long)L, cfg->order_l);
+  // bf16 with the order-16 token basis: the token side of the tensor-core grad_out kernels on its own (same codes as
+  // the butterfly kernel below unless a 16-term sum is inexact in fp32; HOT_ABC=butterfly keeps that kernel).
+  // Workspace words: 0 abs-max, 1-2 tile counters, 3 status (non-zero afterwards: a device-side wait ran out).
+  const char* abc_env = getenv("HOT_ABC");
+  if (workspace_bytes >= 16 && !(abc_env && abc_env[0] == 'b') &&
+      abc_tc_supported(L, I, ldx, cfg->dtype, cfg->order_l, cfg->rank_l, cfg->sel_l, cfg->q_x)) {
+    if (int rc = validate_quant(&cfg->q_x, "hot_abc_compress")) return rc;
+    if (pitch % 16 != 0 || ((uintptr_t)x_q_t) % 16 != 0 || ((uintptr_t)x) % 16 != 0)
+      HOT_FAIL(HOT_ERR_ARG, "hot_abc_compress: buffers and pitches must be 16-byte aligned");
+    uint32_t* wsw = (uint32_t*)workspace;
+    return go_dual_quant_tc(x, L, I, ldx, cfg->q_x, cfg->q_x, nullptr, 0, nullptr, x_q_t, pitch, scale_x, nullptr, wsw, wsw + 1, 3, wsw + 3,
+                            (cudaStream_t)stream, nullptr, true);
+  }
   return hot_col_ht_quant(x, cfg->dtype, L, I, ldx, cfg->order_l, cfg->sel_l, cfg->rank_l, &cfg->q_x, HOT_LAYOUT_NATURAL,
                           x_q_t, pitch, scale_x, (uint32_t*)workspace, stream);
 }

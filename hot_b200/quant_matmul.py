@@ -272,15 +272,19 @@ class FLinearQ(Function):
     per sample, the low-rank projection runs along the tokens of each sample, grad_weight is the sum
     over samples (utils/quant_matmul.py:180,223-225,288-290,322-324).  With ``args.lowRankPreset``
     set (not in the reference) the batch is flattened to B*L tokens with one scale instead, which
-    is the faster path."""
+    is the faster path.
+    An optional sixth argument is the layer's bias, added by the forward GEMM itself (``F.linear(x, w, bias)``);
+    its gradient, the sum of grad_output over the tokens, then comes from this backward too.  The reference adds the
+    bias after ``apply`` (utils/quant_matmul.py:420-421), a pass of its own over the output."""
 
     @staticmethod
-    def forward(x, w, h_out, h_bs, name):
-        return F.linear(x, w)
+    def forward(x, w, h_out, h_bs, name, bias=None):
+        return F.linear(x, w, bias)
 
     @staticmethod
     def setup_context(ctx, inputs, output):
-        x, w, h_out, h_bs, name = inputs
+        x, w, h_out, h_bs, name = inputs[:5]
+        ctx.n_inputs = len(inputs)
         a = _args()
         _check_scheme(a)
         n_l, sel = _selection(h_bs)
@@ -397,6 +401,9 @@ class FLinearQ(Function):
         gw = gw_luq if gw_luq is not None else gw
         if gx is not None:
             gx = gx.reshape(ctx.x_shape)
+        if ctx.n_inputs > 5:
+            gb = grad_output.reshape(-1, grad_output.shape[-1]).sum(0) if ctx.needs_input_grad[5] else None
+            return gx, gw, None, None, None, gb
         return gx, gw, None, None, None
 
 
@@ -471,6 +478,11 @@ class HQ_Linear(nn.Linear):
             self.hadamard_out = _out_matrix(a, self.out_features, tokens, getattr(a, "lowRankPreset", None),
                                             self.weight.dtype, self.weight.device)
             self._bs_tokens = key
+        # 16-bit tensors: the bias goes into the forward GEMM (one rounding of the output, no pass of its own over
+        # it: at 50,432 x 3,072 that pass was 0.2 ms per layer); float32 keeps the reference's separate addition,
+        # whose result the parity tests pin bit for bit
+        if self.bias is not None and input.dtype in (torch.bfloat16, torch.float16) and self.bias.dtype == input.dtype:
+            return FLinearQ.apply(input, self.weight, self.hadamard_out, self.hadamard_bs, self.layer_name, self.bias)
         output = FLinearQ.apply(input, self.weight, self.hadamard_out, self.hadamard_bs, self.layer_name)
         if self.bias is not None:
             output += self.bias.to(output.device)

@@ -573,6 +573,32 @@ def test_dual_gemm_with_g_w_tiles_cut_along_the_tokens(ops, monkeypatch, L, O, I
         assert torch.equal(out[split][1], out["1"][1]), split
 
 
+@pytest.mark.parametrize("rounding", ["philox", "nearest"])
+@pytest.mark.parametrize("bits", [8, 6])
+@pytest.mark.parametrize("L,I", [(32 * 13, 128), (12608, 768), (640, 3072)])
+def test_activation_buffer_from_the_tensor_core_kernels_matches_the_butterfly_kernel(ops, monkeypatch, rounding, bits, L, I):
+    """bf16 with the order-16 token basis: hot_abc_compress runs the token side of the tensor-core grad_out kernels;
+    HOT_ABC=butterfly keeps hot_col_ht_quant.  Same codes, same scale."""
+    rng = np.random.default_rng(L + I + bits)
+    x = torch.from_numpy(rng.standard_normal((L, I)).astype(np.float32)).cuda().bfloat16()
+    x[:, 5] *= 20.0
+    sel = [int(v) for v in oc.lowrank_preset(16, 8)]
+    cfg = ops.LinearConfig(order_o=16, order_l=16, sel_l=sel, q_x=ops.Quant(bits, "int8", rounding, "tensor", 13, 4))
+    out = {}
+    for mode in ("tc", "butterfly"):
+        if mode == "butterfly":
+            monkeypatch.setenv("HOT_ABC", "butterfly")
+        else:
+            monkeypatch.delenv("HOT_ABC", raising=False)
+        q, s = ops.abc_compress(x, cfg)
+        torch.cuda.synchronize()
+        out[mode] = (q.clone(), s.clone())
+    lp = L // 2
+    assert int(out["tc"][0][:, :lp].view(torch.int8).abs().max()) == (1 << (bits - 1)) - 1
+    assert torch.equal(out["tc"][1], out["butterfly"][1])
+    assert torch.equal(out["tc"][0][:, :lp], out["butterfly"][0][:, :lp])
+
+
 def test_go_dual_quant_rejects_what_it_does_not_cover(ops):
     go = torch.zeros((64, 64), device="cuda")
     cfg = ops.LinearConfig(order_o=16, order_l=32, sel_l=list(oc.wht_selection(6304, 50)[1]))

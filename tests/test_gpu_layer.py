@@ -582,6 +582,32 @@ def test_luq_quantizer_and_layer(hot, golden):
     assert torch.isfinite(x3.grad).all() and torch.isfinite(lin.weight.grad).all()
 
 
+def test_hq_linear_bf16_bias_goes_into_the_forward_gemm(hot):
+    """In 16-bit dtypes HQ_Linear hands its bias to FLinearQ: the forward is F.linear(x, w, b) (what nn.Linear
+    computes), the bias gradient is the sum of grad_output over the tokens, and the other two gradients are the HOT
+    ones (close to the float gradients, as in the layer tests above)."""
+    args, qm = hot
+    args.transform_scheme = "gih_gwlr"
+    args.lowRankPreset = "half16"
+    args.quantBWDGogi = args.quantBWDWgt = args.quantBWDGogw = args.quantBWDAct = "stoch"
+    torch.manual_seed(3)
+    layer = qm.HQ_Linear(96, 128).cuda().to(torch.bfloat16)
+    x = torch.randn(4, 64, 96, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    go = (torch.randn(4, 64, 128, device="cuda") * 1e-2).to(torch.bfloat16)
+    out = layer(x)
+    assert torch.equal(out, nn.functional.linear(x, layer.weight, layer.bias))
+    out.backward(go)
+    torch.testing.assert_close(layer.bias.grad.float(), go.float().sum((0, 1)), rtol=2e-2, atol=1e-3)
+    cos = lambda a, b: float(nn.functional.cosine_similarity(a.float().flatten(), b.float().flatten(), dim=0))
+    assert cos(x.grad, go.float() @ layer.weight.float()) > 0.9
+    # (the low-rank projection keeps 8 of 16 token directions: on white noise that is half the energy, cos ~ 0.71)
+    assert cos(layer.weight.grad, go.float().reshape(-1, 128).t() @ x.detach().float().reshape(-1, 96)) > 0.6
+    # float32 keeps the separate addition
+    layer32 = qm.HQ_Linear(96, 128).cuda()
+    x32 = torch.randn(256, 96, device="cuda")
+    assert torch.equal(layer32(x32), nn.functional.linear(x32, layer32.weight) + layer32.bias)
+
+
 def test_vit_with_hot_linears_trains(hot):
     """A small ViT of the benchmark's architecture: apply_hot swaps exactly the block linears, a few
     SGD steps on a fixed batch reduce the loss, and gradients reach every parameter."""
