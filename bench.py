@@ -661,6 +661,9 @@ def kernel_legs(ops, layers, a, dtype, device, pk, status):
     kern["gemm_gx_gw_one_launch"] = dict(us=t, ops=2 * L * I * O + 2 * O * I * lp, bound="tensor")
     t_layer = _graph_time(lambda i: ops.linear_backward(fc1[i % n]["go"], fc1[i % n]["w"], fc1[i % n]["x_q_t"], fc1[i % n]["s_x"], cfg, status=status), n, device)
     xs = [torch.randn((L, I), device=device).to(dtype) for _ in range(2)]
+    # the forward side: the activation buffer of the layer's input (not part of the timed step)
+    t = _graph_time(lambda i: ops.abc_compress(xs[i % 2], cfg), 8, device)
+    kern["abc_compress_x"] = dict(us=t, bytes=L * I * esz + lp * I, bound="hbm")
     t_fp = _graph_time(lambda i: (torch.matmul(fc1[i % n]["go"], fc1[i % n]["w"]), torch.matmul(fc1[i % n]["go"].t(), xs[i % 2])), n, device)
     # the INT8 ceiling the GEMM fractions are quoted against: measured here, in this run, on a square 8192^3
     # problem by the library GEMM (torch._int_mm) and by this repo's kernel; the larger of the two

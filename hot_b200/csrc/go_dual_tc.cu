@@ -603,7 +603,7 @@ int launch_tc_pass_as(const CUtensorMap& m_in, const CUtensorMap& m_qgo, const C
 template <int PASS, int RX, int RW, bool X4>
 int launch_tc_pass(const CUtensorMap& m_in, const CUtensorMap& m_qgo, const CUtensorMap& m_qgw, const TcParams& p, int grid,
                    cudaStream_t st) {
-  const bool fast = !p.x_row && !p.w_row && p.qx.qmax == 7.0f && p.qw.qmax == 127.0f;
+  const bool fast = !p.w_row && p.qw.qmax == 127.0f && (p.col_only || (!p.x_row && p.qx.qmax == 7.0f));  // (the g_x side does not run in col_only)
   if (PASS == 0) return launch_tc_pass_as<PASS, RX, RW, X4, false>(m_in, m_qgo, m_qgw, p, grid, st);  // nothing of it depends on the widths
   if (fast) return launch_tc_pass_as<PASS, RX, RW, X4, true>(m_in, m_qgo, m_qgw, p, grid, st);
   return launch_tc_pass_as<PASS, RX, RW, X4, false>(m_in, m_qgo, m_qgw, p, grid, st);
