@@ -17,6 +17,9 @@
 // the caller's status word, stops issuing work, frees its tensor memory and returns.
 #include <type_traits>
 #include <cstdlib>
+#include <cstring>
+#include <mutex>
+#include <vector>
 
 #include "tc.cuh"
 
@@ -1269,10 +1272,37 @@ int gemm_i8_dual_ws(const hot_gemm_problem_t* main_problem, const hot_gemm_probl
   // wave; otherwise (or with HOT_GEMM_DUAL=0) the two problems run one after the other.  The tile
   // width, and into how many stretches of k-blocks a rider tile is cut, are those whose busiest worker,
   // replayed on the host, has the least to do.
-  const Plan s0 = make_plan(p0.M, p0.N, p0.num_kb, sms, 0, !a4, a4), s1 = make_plan(p1.M, p1.N, p1.num_kb, sms, 0, true, false);
   const char* env = getenv("HOT_GEMM_DUAL");
   const char* senv = getenv("HOT_GEMM_RIDER_SPLIT");  // 1: rider tiles stay whole; n: cut into n where possible
   const int force_split = senv ? atoi(senv) : 0;
+  // The decision depends on the shapes and the switches only; a training step asks for the same few again and
+  // again, and the replay below costs tens of microseconds of host time, so the answers are kept.
+  struct Decision {
+    int key[13];
+    Plan s0, s1;
+    int dual_bn, dual_split;
+    bool dual;
+  };
+  static std::mutex cache_mutex;
+  static std::vector<Decision> cache;
+  const char* e1 = getenv("HOT_GEMM_SCHEDULE");
+  const char* e2 = getenv("HOT_GEMM_PAIR");
+  const bool split_ok = workspace && counters && ((uintptr_t)workspace) % 16 == 0;
+  const int key[13] = {p0.M, p0.N, p0.K, p1.M, p1.N, p1.K, sms, a4 ? 1 : 0, (env ? env[0] : 0) | ((e1 ? e1[0] : 0) << 8) | ((e2 ? e2[0] : 0) << 16),
+                       force_split, split_ok ? 1 : 0, (int)(uint32_t)(workspace_bytes & 0xFFFFFFFFu), (int)(uint32_t)(workspace_bytes >> 32)};
+  Decision dec;
+  bool have = false;
+  {
+    std::lock_guard<std::mutex> lock(cache_mutex);
+    for (const Decision& d : cache)
+      if (memcmp(d.key, key, sizeof(key)) == 0) {
+        dec = d;
+        have = true;
+        break;
+      }
+  }
+  if (!have) {
+  const Plan s0 = make_plan(p0.M, p0.N, p0.num_kb, sms, 0, !a4, a4), s1 = make_plan(p1.M, p1.N, p1.num_kb, sms, 0, true, false);
   int dual_bn = 0, dual_split = 1;
   double together = 0.0;
   for (int bn : {256, 192}) {
@@ -1303,6 +1333,19 @@ int gemm_i8_dual_ws(const hot_gemm_problem_t* main_problem, const hot_gemm_probl
   bool dual = dual_bn != 0 && !(env && env[0] == '0');
   // a second launch costs about 3 us of ramp-down and ramp-up, some 4000 units of this model
   if (dual && !(env && env[0] == '1')) dual = together < s0.cost + s1.cost + 4000.0;
+    memcpy(dec.key, key, sizeof(key));
+    dec.s0 = s0;
+    dec.s1 = s1;
+    dec.dual_bn = dual_bn;
+    dec.dual_split = dual_split;
+    dec.dual = dual;
+    std::lock_guard<std::mutex> lock(cache_mutex);
+    if (cache.size() >= 256) cache.clear();
+    cache.push_back(dec);
+  }
+  const Plan &s0 = dec.s0, &s1 = dec.s1;
+  const int dual_bn = dec.dual_bn, dual_split = dec.dual_split;
+  const bool dual = dec.dual;
   if (dual) {
     p1.split = dual_split;
     p1.sk_partials = (int32_t*)workspace;

@@ -264,7 +264,7 @@ def _selection(h_bs: Tensor):
 class FLinearQ(Function):
     """``FLinearQ.apply(x, w, h_out, h_bs, name)`` (utils/quant_matmul.py:169-348).
 
-    forward: ``F.linear(x, w)`` in full precision.  setup_context: the activation buffer is the
+    forward: ``F.linear(x, w)`` in full precision.  Its context (the reference's setup_context): the activation buffer is the
     Hadamard low-rank projection of ``x`` along tokens, quantised to INT8 (what the reference
     saves), produced by one fused kernel.  backward: grad_input and grad_weight from the
     integer tensor-core path; exactly two real gradients are returned.
@@ -277,12 +277,17 @@ class FLinearQ(Function):
     its gradient, the sum of grad_output over the tokens, then comes from this backward too.  The reference adds the
     bias after ``apply`` (utils/quant_matmul.py:420-421), a pass of its own over the output."""
 
+    # forward(ctx, ...) rather than forward + setup_context as in the reference: torch binds the default arguments of a
+    # forward that comes with a setup_context through inspect.signature on every call (67 us per layer call on the
+    # benchmark host)
     @staticmethod
-    def forward(x, w, h_out, h_bs, name, bias=None):
+    def forward(ctx, x, w, h_out, h_bs, name, bias=None):
+        FLinearQ._save_context(ctx, (x, w, h_out, h_bs, name) if bias is None else (x, w, h_out, h_bs, name, bias))
         return F.linear(x, w, bias)
 
     @staticmethod
-    def setup_context(ctx, inputs, output):
+    def _save_context(ctx, inputs):
+        """What the reference's setup_context does (utils/quant_matmul.py:177-212)."""
         x, w, h_out, h_bs, name = inputs[:5]
         ctx.n_inputs = len(inputs)
         a = _args()
@@ -566,6 +571,21 @@ def replace_layers(model: nn.Module, old, new) -> None:
             if module.bias is not None:
                 new_layer.bias.data = module.bias.data
             setattr(model, n, new_layer)
+
+
+def ddp_ignore_hot_buffers(model: nn.Module) -> int:
+    """Tell DistributedDataParallel (through the attribute it reads from the module it wraps) not to broadcast the
+    ``hadamard_out`` / ``hadamard_bs`` buffers of the HOT layers under ``model`` at every forward: they are
+    functions of the layer's shapes and the token count alone, hence identical on every rank, and two small
+    tensors per layer (96 for ViT-B/16) cost more host time per step than the backward saves.  Call it on the module
+    that will be wrapped, before wrapping.  Not in the reference, which lets DDP broadcast them.  Returns how many
+    buffers were named."""
+    names = [n + "." + b for n, m in model.named_modules() if isinstance(m, (HQ_Linear, HQ_Conv2d))
+             for b in ("hadamard_out", "hadamard_bs")]
+    names = [n.lstrip(".") for n in names]
+    have = list(getattr(model, "_ddp_params_and_buffers_to_ignore", []))
+    model._ddp_params_and_buffers_to_ignore = have + [n for n in names if n not in have]
+    return len(names)
 
 
 def precision_scheduler(current_epoch, max_bit=8, min_bit=4, milestones=()):

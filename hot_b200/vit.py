@@ -11,7 +11,7 @@ import torch
 import torch.nn as nn
 import torch.nn.functional as F
 
-from .quant_matmul import HQ_Linear, replace_layers
+from .quant_matmul import HQ_Linear, ddp_ignore_hot_buffers, replace_layers
 
 
 class Attention(nn.Module):
@@ -85,4 +85,5 @@ def apply_hot(model: VisionTransformer) -> int:
         if isinstance(layer, HQ_Linear):
             layer.layer_name = name
             count += 1
+    ddp_ignore_hot_buffers(model)   # the model may be wrapped in DistributedDataParallel next
     return count

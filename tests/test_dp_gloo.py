@@ -79,3 +79,25 @@ def test_single_process_is_a_no_op():
     gb.reduce_async(0)
     gb.wait_all()
     assert gb.world_size == 1 and float(gb.view(0, 2)[0, 0]) == 3.0
+
+
+def test_hot_buffers_are_named_for_ddp_to_leave_alone():
+    """apply_hot names the hadamard_out / hadamard_bs buffers of every layer it swapped in the attribute
+    DistributedDataParallel reads from the module it wraps, so they are not broadcast at every forward; DDP over gloo
+    then takes the list (its buffer set has none of them) and a model without HOT layers is left as it is."""
+    import torch.nn as nn
+    import hot_b200.args as hargs
+    from hot_b200.quant_matmul import ddp_ignore_hot_buffers
+    from hot_b200.vit import VisionTransformer, apply_hot
+    hargs.transform_scheme = "gih_gwlr"
+    hargs.lowRankPreset = "half16"
+    model = VisionTransformer(img_size=32, patch=16, dim=32, depth=2, heads=2, num_classes=4)
+    n = apply_hot(model)
+    ignore = model._ddp_params_and_buffers_to_ignore
+    assert n == 8 and len(ignore) == 16 and len(set(ignore)) == 16
+    assert "blocks.0.attn.qkv.hadamard_out" in ignore and "blocks.1.mlp.fc2.hadamard_bs" in ignore
+    buffers = dict(model.named_buffers())
+    assert all(name in buffers for name in ignore)
+    assert ddp_ignore_hot_buffers(model) == 16 and len(model._ddp_params_and_buffers_to_ignore) == 16   # idempotent
+    plain = nn.Sequential(nn.Linear(4, 4))
+    assert ddp_ignore_hot_buffers(plain) == 0 and plain._ddp_params_and_buffers_to_ignore == []
