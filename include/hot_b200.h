@@ -318,6 +318,11 @@ int64_t hot_abc_pitch(int64_t L, const hot_linear_cfg_t* cfg);
 /*
  * Activation-buffer compression (forward side): x [L, I] -> x_q_t [I, L*r/n] int8 codes
  * (pitch hot_abc_pitch) + scale_x [1].  noise layout: HOT_LAYOUT_NATURAL [L*r/n, I].
+ * workspace: hot_col_ht_quant_scratch_words() words at least.  With 16 bytes or more, bf16 input, the
+ * basis "8 lowest-sequency rows of H_16", L % 32 == 0, I % 128 == 0, 16-byte aligned x and pitch, and
+ * nearest or Philox rounding, the tensor-core kernels of hot_go_dual_quant make the buffer (same codes
+ * and scale); they use workspace words 0-3 and leave word 3 non-zero if a device-side wait ran out
+ * (hot_check_status reads it).
  * Stands in for FLinearQ.setup_context (utils/quant_matmul.py:177-212).
  */
 int hot_abc_compress(const void* x, int64_t L, int64_t I, int64_t ldx, const hot_linear_cfg_t* cfg,
@@ -347,9 +352,12 @@ int hot_go_dual_quant(const void* go, int64_t L, int64_t O, int64_t ldgo, const 
  * go [L, O] pitch ldgo, w [O, I] pitch ldw (elements); x_q_t / scale_x from hot_abc_compress.
  * status_word: device word, non-zero after the call completes if a device-side wait ran out.
  * cfg->q_gx / q_gw take HOT_SCALE_TENSOR or HOT_SCALE_ROW (HOT_SCALE_SAWB is for q_w and q_x).
- * The weight is quantised on a helper stream the library keeps per device (one stream and one
- * fork/join event pair): calls on one device must come from one host thread and one stream at a
- * time; the first call on a device creates them and should be made outside stream capture.
+ * Where the tensor-core kernels of hot_go_dual_quant apply (bf16, order_o 16, the basis above, O % 128 == 0,
+ * I % 32 == 0, one scale for the weight) the weight is transformed and quantised inside those two launches
+ * and a call is three kernels on `stream`.  Otherwise the weight is quantised on a helper stream the
+ * library keeps per device (one stream and one fork/join event pair): calls on one device must come
+ * from one host thread and one stream at a time; the first call on a device creates them and should
+ * be made outside stream capture.
  * Stands in for FLinearQ.backward (utils/quant_matmul.py:214-348) and for backward_cuda
  * (cuda_measure/HLQ_backward_kernel.cu:457-737).
  */
