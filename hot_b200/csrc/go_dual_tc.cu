@@ -10,8 +10,10 @@
 // One persistent CTA per SM walks 128-token x 128-channel tiles.  Warp roles:
 //   warp 0      TMA producer: two 128-token x 64-channel boxes (128-byte swizzle) per tile
 //   warp 1      allocates tensor memory and issues, from one lane, 8 MMAs (M 128 tokens, N 16, K 16
-//               channels) for the channel transform and 8 (M 128 channels, N 16 = two token blocks x
-//               8 kept rows, K 16 tokens) for the token projection; accumulators are double-buffered
+//               channels) for the channel transform and, in pass 1, 8 (M 128 channels, N 16 = two token
+//               blocks x 8 kept rows, K 16 tokens) for the token projection; accumulators are
+//               double-buffered.  (In pass 0 the g_w-side warps take the projection's abs-max from the
+//               tile in shared memory with the butterfly of the separate kernels.)
 //   warps 2-17  g_x side: a lane owns a token; each warp reads one 32-channel chunk of the lane's 128
 //               transformed channels from tensor memory, quantises it and hands a 32-token box of
 //               codes to the copy engine
@@ -21,9 +23,10 @@
 //   All 24 epilogue warps work on the same tile and hand its accumulator buffer back as soon as the
 //   values are in registers.  The four warps with the same chunk index wait as a group: one polls the
 //   accumulator's barrier, the others sit at a named barrier.
-// Measured on the ViT-B/16 fc1 gradient (12,608 x 3,072, bf16): the 16 small MMAs of a tile cost about as
-// much as the tile's share of HBM time, so pass 0 runs at the tensor core's issue rate for 128 x 16 x 16
-// products, and pass 1 is bound by the instruction issue of the rounding and packing arithmetic.
+// Measured on the ViT-B/16 fc1 gradient (12,608 x 3,072, bf16): 16 small MMAs per tile cost about as much as
+// the tile's share of HBM time, which is why pass 0 issues eight; pass 1 is bound by the instruction issue of
+// the rounding and packing arithmetic.
+// With col_only set the kernels make the activation buffer of the forward pass (the token side alone).
 //
 // The fp32 sums differ from the fixed-order butterflies of row_ht_quant / col_ht_quant only where a
 // sum of 16 bf16 values is not exact in fp32 (operands more than ~2^13 apart in magnitude); there the
