@@ -149,11 +149,9 @@ extern "C" int hot_abc_compress(const void* x, int64_t L, int64_t I, int64_t ldx
   // the butterfly kernel below unless a 16-term sum is inexact in fp32; HOT_ABC=butterfly keeps that kernel).
   // Workspace words: 0 abs-max, 1-2 tile counters, 3 status (non-zero afterwards: a device-side wait ran out).
   const char* abc_env = getenv("HOT_ABC");
-  if (workspace_bytes >= 16 && !(abc_env && abc_env[0] == 'b') &&
-      abc_tc_supported(L, I, ldx, cfg->dtype, cfg->order_l, cfg->rank_l, cfg->sel_l, cfg->q_x)) {
+  if (workspace_bytes >= 16 && !(abc_env && abc_env[0] == 'b') && pitch % 16 == 0 && ((uintptr_t)x_q_t) % 16 == 0 &&
+      ((uintptr_t)x) % 16 == 0 && abc_tc_supported(L, I, ldx, cfg->dtype, cfg->order_l, cfg->rank_l, cfg->sel_l, cfg->q_x)) {
     if (int rc = validate_quant(&cfg->q_x, "hot_abc_compress")) return rc;
-    if (pitch % 16 != 0 || ((uintptr_t)x_q_t) % 16 != 0 || ((uintptr_t)x) % 16 != 0)
-      HOT_FAIL(HOT_ERR_ARG, "hot_abc_compress: buffers and pitches must be 16-byte aligned");
     uint32_t* wsw = (uint32_t*)workspace;
     return go_dual_quant_tc(x, L, I, ldx, cfg->q_x, cfg->q_x, nullptr, 0, nullptr, x_q_t, pitch, scale_x, nullptr, wsw, wsw + 1, 3, wsw + 3,
                             (cudaStream_t)stream, nullptr, true);
