@@ -54,7 +54,7 @@ def parse():
     p.add_argument("--gx-storage", default="auto", choices=["int4", "int8", "auto"],
                    help="how the 4-bit g_x codes of grad_out are stored between the quantiser and the GEMM: packed two per "
                         "byte and expanded in shared memory, one per byte, or (default) the library's policy "
-                        "ops.gx_code_storage: packed where the contraction is longer than 1024")
+                        "ops.gx_code_storage: packed where the contraction is 4096 or longer")
     p.add_argument("--no-cpu-baseline", action="store_true")
     p.add_argument("--sm-margin", type=int, default=-1,
                    help="SMs left out of the persistent kernels' grids for the all-reduce kernels (multi-GPU; default 0)")
@@ -300,7 +300,7 @@ def run_hot(a):
            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8/int4 codes, int32 accumulate",
            "data": "synthetic", "gpu_launches": n_layers * KERNELS_PER_LAYER[a.dtype] * a.steps,
            "config": {"workload": WORKLOAD, "tokens_per_gpu": a.tokens, "layers": n_layers, "tensor_dtype": a.dtype,
-                      "hadamard_order": 16, "low_rank": "8 of 16 (lowest sequency)", "g_x": "INT4 x INT4, per-tensor, Philox stochastic" + {"int4": "; grad_out codes packed", "int8": "; grad_out codes stored one per byte", "auto": "; grad_out codes packed for qkv and fc1 (contraction > 1024), one per byte for proj and fc2"}[a.gx_storage],
+                      "hadamard_order": 16, "low_rank": "8 of 16 (lowest sequency)", "g_x": "INT4 x INT4, per-tensor, Philox stochastic" + {"int4": "; grad_out codes packed", "int8": "; grad_out codes stored one per byte", "auto": "; grad_out codes stored one per byte (packed only where the contraction is 4096 or longer)"}[a.gx_storage],
                       "g_w": "INT8 x INT8, per-tensor, Philox stochastic", "activation_buffer": "compressed in forward (not timed)",
                       "cache": "inputs 2.1 GB per GPU, distinct per layer (> 126 MB L2)",
                       "parallelism": ("dp%d, grad_w all-reduce (NCCL) in %d buckets of up to %d blocks (%.1f MB per block; the last one holds "

@@ -343,12 +343,13 @@ def _identity_tokens(cfg: "LinearConfig") -> "LinearConfig":
 
 def gx_code_storage(bits: int, k: int) -> str:
     """How the g_x codes of grad_out travel from the quantiser to the GEMM.  Codes of up to 4 bits are
-    packed two per byte and expanded to int8 in the GEMM's shared memory when the contraction is long
-    (k > 1024: the packed tensor saves tens of MB of HBM traffic per layer); for short contractions a
-    tile has few k-blocks to hide the expansion behind and the tensor is small, so the codes are stored
-    one per byte (measured on the 48 ViT-B/16 linears: 4.20 ms per step against 4.43 ms all packed).  The
+    packed two per byte and expanded to int8 in the GEMM's shared memory when the contraction is very long
+    (k >= 4096: the packed tensor saves 30-90 MB of HBM traffic per layer at 16,384 tokens); below that they are
+    stored one per byte, which the GEMM takes as it is.  Measured on the 48 ViT-B/16 linears at 12,608 tokens with the
+    tensor-core quantiser, whose stores are not what bounds it: 3.34 ms per step one per byte everywhere against 3.37 ms
+    with qkv and fc1 (k = 2304, 3072) packed; the GEMM gains 2.8 us per such layer, the quantiser loses 1.7.  The
     codes, scales and results are the same either way."""
-    return "int4" if bits <= 4 and k > 1024 else "int8"
+    return "int4" if bits <= 4 and k >= 4096 else "int8"
 
 
 def go_dual_quant(go: torch.Tensor, cfg: LinearConfig, status: Optional[torch.Tensor] = None):
