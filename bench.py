@@ -644,18 +644,19 @@ def kernel_legs(ops, layers, a, dtype, device, pk, status):
     kern["col_ht_quant_w"] = dict(us=t, bytes=O * I * esz + O * I, bound="hbm")
     # the fused pair the layer runs on grad_out (stats pass + quantise pass, both operands)
     t = _graph_time(lambda i: ops.go_dual_quant(fc1[i % n]["go"], cfg), n, device)
-    kern["go_dual_quant"] = dict(us=t, bytes=L * O * esz + L * O // 2 + lp * O + 8, bound="hbm")
+    gx_bytes = L * O // 2 if cfg.q_gx.storage == "int4" else L * O     # g_x codes packed two per byte, or one per byte
+    kern["go_dual_quant"] = dict(us=t, bytes=L * O * esz + gx_bytes + lp * O + 8, bound="hbm")
     # kernel C: the two integer GEMMs
     q_go, s_go = ops.row_ht_quant(fc1[0]["go"], 16, cfg.q_gx)
     q_w8 = ops.Quant(4, "int8", "philox", "tensor", 0, 9)          # the layer keeps weight codes one per byte
     q_w, s_w, _ = ops.col_ht_quant(fc1[0]["w"], 16, list(range(16)), q_w8, "natural")
     q_gw, s_gw, _ = ops.col_ht_quant(fc1[0]["go"], cfg.order_l, cfg.sel_l, cfg.q_gw, "transposed")
-    t = _graph_time(lambda i: ops.gemm_i8(q_go, "int4", q_w, "int8", L, I, O, s_go, s_w, 1 / 16, dtype, status), 8, device)
-    kern["gemm_gx_int4xint8"] = dict(us=t, ops=2 * L * I * O, bound="tensor")
+    t = _graph_time(lambda i: ops.gemm_i8(q_go, cfg.q_gx.storage, q_w, "int8", L, I, O, s_go, s_w, 1 / 16, dtype, status), 8, device)
+    kern["gemm_gx_4bit_codes_%s" % ("packed" if cfg.q_gx.storage == "int4" else "one_per_byte")] = dict(us=t, ops=2 * L * I * O, bound="tensor")
     t = _graph_time(lambda i: ops.gemm_i8(q_gw, "int8", fc1[0]["x_q_t"], "int8", O, I, lp, s_gw, fc1[0]["s_x"], 1 / 16, dtype, status), 8, device)
     kern["gemm_gw_int8"] = dict(us=t, ops=2 * O * I * lp, bound="tensor")
     # what the layer launches: both products in one persistent kernel
-    g_main = dict(a=q_go, a_storage="int4", b=q_w, M=L, N=I, K=O, scale_a=s_go, scale_b=s_w, post=1 / 16, out_dtype=dtype)
+    g_main = dict(a=q_go, a_storage=cfg.q_gx.storage, b=q_w, M=L, N=I, K=O, scale_a=s_go, scale_b=s_w, post=1 / 16, out_dtype=dtype)
     g_rider = dict(a=q_gw, b=fc1[0]["x_q_t"], M=O, N=I, K=lp, scale_a=s_gw, scale_b=fc1[0]["s_x"], post=1 / 16, out_dtype=dtype)
     t = _graph_time(lambda i: ops.gemm_i8_dual(g_main, g_rider, status), 8, device)
     kern["gemm_gx_gw_one_launch"] = dict(us=t, ops=2 * L * I * O + 2 * O * I * lp, bound="tensor")
@@ -681,11 +682,14 @@ def kernel_legs(ops, layers, a, dtype, device, pk, status):
     in_layer = ["go_dual_quant", "gemm_gx_gw_one_launch"] + ([] if dtype == torch.bfloat16 else ["col_ht_quant_w"])
     top = max(in_layer, key=lambda k: kern[k]["us"])
     tk = kern[top]
-    # DRAM traffic per launch pair, from an ncu capture of this very workload (fc1 gradient, 12,608 x 3,072 bf16,
-    # `bench.py --one-layer fc1`): pass 0 read 77.5 MB + wrote 1.7 MB, pass 1 read 77.5 MB + wrote 5.3 MB (most of its
-    # 38.7 MB of codes were still in L2 when it ended) = 162.0 MB for 116.2 MB of algorithmic bytes; scaled by the
-    # algorithmic bytes for other token counts.  No figure for the other kernels.
-    traffic = round(tk["bytes"] * 162.0 / 116.2) if top == "go_dual_quant" and dtype == torch.bfloat16 else None
+    # DRAM traffic per launch pair, from ncu captures of this very workload (fc1 gradient, 12,608 x 3,072 bf16,
+    # `bench.py --one-layer fc1`, cold caches).  g_x codes one per byte: pass 0 read 82.2 MB + wrote 2.4 MB, pass 1 read
+    # 82.3 MB + wrote 20.5 MB (the rest of its 58 MB of codes were still in L2 when it ended), of which 11.8 MB are the
+    # weight that the layer's launches carry and this leg does not: 175.6 MB for 135.6 MB of algorithmic bytes.  Packed
+    # two per byte: 162.0 MB for 116.2 MB.  Scaled by the algorithmic bytes for other token counts.  No figure for the
+    # other kernels.
+    scale = 162.0 / 116.2 if cfg.q_gx.storage == "int4" else 175.6 / 135.6
+    traffic = round(tk["bytes"] * scale) if top == "go_dual_quant" and dtype == torch.bfloat16 else None
     roof = {"kernel": top + (" (two launches: abs-max pass + quantise pass)" if top == "go_dual_quant" else ""),
             "bound": tk["bound"], "achieved": tk["achieved"], "peak": tk["peak"], "unit": tk["unit"],
             "frac": tk["frac"], "traffic": traffic, "launch_us": tk["us"],
