@@ -639,7 +639,8 @@ bool abc_tc_supported(int64_t L, int64_t I, int64_t ldx, int dtype, int order_l,
 
 // Whether the layer's weight [O, I] (same dtype and transform order as grad_out) can ride along.
 bool tc_weight_job_supported(int64_t O, int64_t I, int64_t ldw, const hot_quant_t& q_w) {
-  return I > 0 && I % 32 == 0 && I <= (1 << 24) && O % 32 == 0 && ldw >= I && q_w.scale_mode == HOT_SCALE_TENSOR &&
+  return I > 0 && I % 32 == 0 && I <= (1 << 24) && O % 32 == 0 && (O >> 5) * (I >> 5) <= (1ll << 30) && ldw >= I &&
+         q_w.scale_mode == HOT_SCALE_TENSOR &&
          (q_w.rounding == HOT_ROUND_STOCH_PHILOX || q_w.rounding == HOT_ROUND_NEAREST) && q_w.bits >= 2 && q_w.bits <= 8;
 }
 
