@@ -94,3 +94,10 @@ def test_host_modules_without_a_device():
     from hot_b200 import ops
     with pytest.raises(RuntimeError, match="CUDA tensors only"):
         ops.row_ht_quant(torch.zeros(4, 64), 16, ops.Quant(4, "int4"))
+    # how the host layers store the 4-bit g_x codes: one per byte below a contraction of 4096, packed from there on
+    assert [ops.gx_code_storage(4, k) for k in (768, 2304, 3072, 4095, 4096, 11008)] == ["int8"] * 4 + ["int4"] * 2
+    assert ops.gx_code_storage(8, 11008) == "int8"
+    # FLinearQ takes the bias as an optional sixth argument and runs on CPU as far as its forward product
+    from hot_b200.quant_matmul import FLinearQ
+    import inspect
+    assert list(inspect.signature(FLinearQ.forward).parameters)[:7] == ["ctx", "x", "w", "h_out", "h_bs", "name", "bias"]
