@@ -106,18 +106,29 @@ def peaks():
 # clocks
 # ---------------------------------------------------------------------------------------------
 class ClockSampler:
-    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+    """nvidia-smi sampling SM clock and throttle reasons every 20 ms.  It is started well before the timed region
+    (nvidia-smi takes a few hundred ms to begin, longer on a box with 8 GPUs, and the timed region of the default run
+    is under 100 ms) and its lines carry a timestamp: `stop` reports the samples that fall between `mark_start` and
+    `mark_end`, or, if the region was too short to catch one, the ones nearest to it."""
+    FIELDS = ("timestamp,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
               "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
               "clocks_event_reasons.sw_power_cap")
 
     def __init__(self, index: int):
         self.proc = None
+        self.t0 = self.t1 = None
         try:
             self.proc = subprocess.Popen(["nvidia-smi", "-i", str(index), "--query-gpu=" + self.FIELDS,
                                           "--format=csv,noheader,nounits", "-lms", "20"], stdout=subprocess.PIPE,
                                          stderr=subprocess.DEVNULL, text=True)
         except OSError:
             pass
+
+    def mark_start(self):
+        self.t0 = time.time()
+
+    def mark_end(self):
+        self.t1 = time.time()
 
     def stop(self):
         if self.proc is None:
@@ -128,24 +139,32 @@ class ClockSampler:
         except subprocess.TimeoutExpired:
             self.proc.kill()
             out, _ = self.proc.communicate()
-        sm, mx, reasons = [], 0.0, set()
+        import datetime
+        rows = []   # (time, sm MHz, max MHz, reasons)
         names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
         for line in out.splitlines():
             f = [v.strip() for v in line.split(",")]
-            if len(f) < 7:
+            if len(f) < 8:
                 continue
             try:
-                sm.append(float(f[0]))
-                mx = max(mx, float(f[1]))
+                t = datetime.datetime.strptime(f[0], "%Y/%m/%d %H:%M:%S.%f").timestamp()
+                rows.append((t, float(f[1]), float(f[2]), {n for n, v in zip(names, f[4:8]) if v.lower().startswith("active")}))
             except ValueError:
                 continue
-            for n, v in zip(names, f[3:7]):
-                if v.lower().startswith("active"):
-                    reasons.add(n)
-        if not sm:
+        if not rows:
             return None
+        window = "timed region"
+        t0, t1 = self.t0 or rows[0][0], self.t1 or rows[-1][0]
+        inside = [r for r in rows if t0 <= r[0] <= t1]
+        if not inside:   # a region shorter than the sampling period: the two samples nearest to it
+            mid = 0.5 * (t0 + t1)
+            inside = sorted(rows, key=lambda r: abs(r[0] - mid))[:2]
+            window = "nearest samples (%.0f ms from the region)" % (1e3 * min(abs(r[0] - mid) for r in inside))
+        sm = [r[1] for r in inside]
+        reasons = set().union(*[r[3] for r in inside])
         busy = [v for v in sm if v > 0.5 * max(sm)] or sm
-        return {"sm_mhz": statistics.median(busy), "sm_max_mhz": mx, "reasons": sorted(reasons), "samples": len(sm)}
+        return {"sm_mhz": statistics.median(busy), "sm_max_mhz": max(r[2] for r in inside), "reasons": sorted(reasons),
+                "samples": len(inside), "window": window}
 
 
 # ---------------------------------------------------------------------------------------------
@@ -199,6 +218,7 @@ def run_hot(a):
     ops.set_sm_margin(margin)
     dtype = torch.bfloat16 if a.dtype == "bf16" else torch.float32
     pk = peaks()
+    sampler = ClockSampler(local) if rank == 0 else None   # started here: it needs a while before its first line
     layers = build_layers(ops, a.tokens, a.blocks, dtype, device, rank, a.gx_storage)
     status = torch.zeros(1, dtype=torch.int32, device=device)
     # gradient buffers: grad_x is consumed by the layer below (one reusable buffer per width);
@@ -264,13 +284,16 @@ def run_hot(a):
     for _ in range(max(a.warmup, 3)):
         step()
     sync_all()
-    sampler = ClockSampler(local) if rank == 0 else None
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    if sampler:
+        sampler.mark_start()
     e0.record()
     for _ in range(a.steps):
         step()
     e1.record()
     sync_all()
+    if sampler:
+        sampler.mark_end()
     ms = torch.tensor([e0.elapsed_time(e1)], device=device)
     if world > 1:
         dist.all_reduce(ms, op=dist.ReduceOp.MAX)
