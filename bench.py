@@ -336,10 +336,12 @@ def run_hot(a):
         out["dp_breakdown"] = breakdown
     if clocks:
         out["clocks"] = clocks
-    if rank == 0 and world == 1:
+    if rank == 0:
+        # the per-kernel legs and the roofline at every GPU count (rank 0's GPU alone, the other ranks wait in the
+        # end-to-end leg's first barrier); the CPU baseline at one GPU only
         if not a.no_kernels:
             out["kernels"], out["roofline"], out["fp_backward_bf16_cublas"] = kernel_legs(ops, layers, a, dtype, device, pk, status)
-        if not a.no_cpu_baseline:
+        if not a.no_cpu_baseline and world == 1:
             out["cpu_baseline"] = cpu_baseline(threads=os.cpu_count() or 1)
     out["e2e"] = e2e_leg(layers, a, dtype, device, flops, world) if a.e2e_steps > 0 else None   # every rank takes part
     if rank == 0:
